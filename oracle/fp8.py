@@ -1,0 +1,228 @@
+"""Oracle restatement of ``xax/nn/fp8.py`` (test infrastructure; parity unpinned).
+
+Strict semantics: a bf16 op is "compute exactly in float32, round to bf16".  A product of
+two bf16 values is exact in float32, so the only rounding is the explicit one.  Type
+promotion follows JAX: bf16 (op) f32 -> f32; Python scalars are weak (take the array's
+dtype); int32 (op) bf16 -> bf16.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import ml_dtypes
+import numpy as np
+
+bfloat16 = ml_dtypes.bfloat16
+float8_e4m3fn = ml_dtypes.float8_e4m3fn
+float8_e5m2 = ml_dtypes.float8_e5m2
+float32 = np.float32
+
+# xax/nn/fp8.py:30-34
+E4M3_MAX = float(ml_dtypes.finfo(float8_e4m3fn).max)
+E5M2_MAX = float(ml_dtypes.finfo(float8_e5m2).max)
+AMAX_HISTORY_LENGTH = 1024
+
+
+def _is_bf16(dt) -> bool:
+    return np.dtype(dt) == np.dtype(bfloat16)
+
+
+def promote(*dts):
+    """JAX-style promotion restricted to {bf16, f32}: any f32 operand makes the result f32."""
+    dts = [np.dtype(d) for d in dts]
+    if all(_is_bf16(d) for d in dts):
+        return np.dtype(bfloat16)
+    return np.dtype(float32)
+
+
+def f32(x) -> np.ndarray:
+    return np.asarray(x).astype(float32)
+
+
+def rb(x) -> np.ndarray:
+    """Round to bf16 (RNE)."""
+    return np.asarray(x, dtype=float32).astype(bfloat16)
+
+
+def rnd(x, dt) -> np.ndarray:
+    """Round a float32 intermediate to the op's result dtype."""
+    return np.asarray(x, dtype=float32).astype(dt)
+
+
+def get_fp8_max(fp8_dtype=float8_e4m3fn, compute_dtype=float32) -> np.ndarray:
+    """xax/nn/fp8.py:37-47."""
+    return np.asarray(float(ml_dtypes.finfo(fp8_dtype).max)).astype(compute_dtype)
+
+
+def compute_scale(amax, scale, fp8_max, margin: int = 0) -> np.ndarray:
+    """xax/nn/fp8.py:50-79: sf = (fp8_max / amax) / 2**margin, previous scale kept when
+    amax <= 0 or non-finite."""
+    amax = np.asarray(amax)
+    scale = np.asarray(scale)
+    fp8_max = np.asarray(fp8_max)
+    dt = promote(amax.dtype, fp8_max.dtype)
+    with np.errstate(divide="ignore", invalid="ignore"):
+        sf = rnd(f32(fp8_max) / f32(amax), dt)
+        sf = rnd(f32(sf) / float32(2**margin), dt)
+    out_dt = promote(dt, scale.dtype)
+    sf = np.where(f32(amax) > 0, sf.astype(out_dt), scale.astype(out_dt))
+    sf = np.where(np.isfinite(f32(amax)), sf, scale.astype(out_dt))
+    return sf.astype(out_dt)
+
+
+def amax_of(x) -> np.ndarray:
+    """max(|x|) in x's dtype; NaN propagates (jnp.max semantics)."""
+    x = np.asarray(x)
+    return np.max(np.abs(f32(x))).astype(x.dtype)
+
+
+def compute_amax_history(x, amax_history) -> np.ndarray:
+    """xax/nn/fp8.py:82-94: roll(-1) then slot 0 <- new amax."""
+    amax_history = np.asarray(amax_history)
+    update = amax_of(x).astype(amax_history.dtype)
+    new_history = np.roll(amax_history, -1, axis=0).copy()
+    new_history[0] = update
+    return new_history
+
+
+def quantize(x, fp8_dtype, scale, compute_dtype=float32) -> np.ndarray:
+    """xax/nn/fp8.py:97-120: clip(x * scale, +-max) in the compute dtype, then cast."""
+    x = np.asarray(x)
+    fp8_max = float(get_fp8_max(fp8_dtype, compute_dtype).astype(float32))
+    s = np.asarray(scale).astype(compute_dtype)
+    dt = promote(x.dtype, compute_dtype)
+    scaled = rnd(f32(x) * f32(s), dt)
+    clipped = np.clip(f32(scaled), -fp8_max, fp8_max).astype(dt)  # NaN propagates
+    return clipped.astype(fp8_dtype)
+
+
+def dequantize(x, compute_dtype, scale) -> np.ndarray:
+    """xax/nn/fp8.py:123-138."""
+    s = np.asarray(scale).astype(compute_dtype)
+    with np.errstate(divide="ignore", invalid="ignore"):
+        return rnd(f32(np.asarray(x).astype(compute_dtype)) / f32(s), compute_dtype)
+
+
+def quantize_dequantize(x, fp8_dtype, scale, compute_dtype=float32) -> np.ndarray:
+    """xax/nn/fp8.py:141-162."""
+    return dequantize(quantize(x, fp8_dtype, scale, compute_dtype), compute_dtype, scale)
+
+
+@dataclass
+class Fp8Scales:
+    """xax/nn/fp8.py:165-175."""
+
+    input_scale: np.ndarray
+    input_amax_history: np.ndarray
+    kernel_scale: np.ndarray
+    kernel_amax_history: np.ndarray
+
+
+def init_fp8_scales(history_length: int = AMAX_HISTORY_LENGTH, compute_dtype=float32) -> Fp8Scales:
+    """xax/nn/fp8.py:178-196."""
+    return Fp8Scales(
+        input_scale=np.ones((), dtype=compute_dtype),
+        input_amax_history=np.zeros((history_length,), dtype=compute_dtype),
+        kernel_scale=np.ones((), dtype=compute_dtype),
+        kernel_amax_history=np.zeros((history_length,), dtype=compute_dtype),
+    )
+
+
+def matmul_nt(a, b, out_dtype) -> np.ndarray:
+    """a[..., K] @ b[N, K].T with float32 accumulation, rounded once to out_dtype."""
+    return rnd(f32(a) @ f32(b).T, out_dtype)
+
+
+def current_scale(x, fp8_dtype, compute_dtype) -> np.ndarray:
+    """xax/nn/fp8.py:329-331: fp8_max / maximum(max|x|, 1e-12), all in the compute dtype."""
+    fp8_max = get_fp8_max(fp8_dtype, compute_dtype)
+    amax = amax_of(np.asarray(x).astype(compute_dtype))
+    floor = np.asarray(1e-12).astype(compute_dtype)
+    denom = np.maximum(f32(amax), f32(floor))  # np.maximum propagates NaN like jnp.maximum
+    return rnd(f32(fp8_max) / denom, compute_dtype)
+
+
+class Fp8Linear:
+    """xax/nn/fp8.py:199-344.  ``weight`` is (out_features, in_features)."""
+
+    def __init__(self, weight, bias=None, *, use_fp8=True, compute_dtype=bfloat16, fp8_dtype=float8_e4m3fn):
+        self.weight = np.asarray(weight)
+        self.bias = None if bias is None else np.asarray(bias)
+        self.out_features, self.in_features = self.weight.shape
+        self.use_fp8 = use_fp8
+        self.compute_dtype = compute_dtype
+        self.fp8_dtype = fp8_dtype
+
+    @classmethod
+    def random(cls, in_features, out_features, rng, *, use_bias=True, **kw) -> "Fp8Linear":
+        """Same distribution as xax/nn/fp8.py:251-271 (U(+-1/sqrt(in))) from a NumPy generator."""
+        bound = 1.0 / np.sqrt(in_features)
+        w = rng.uniform(-bound, bound, (out_features, in_features)).astype(float32).astype(bfloat16)
+        b = rng.uniform(-bound, bound, (out_features,)).astype(float32).astype(bfloat16) if use_bias else None
+        return cls(w, b, **kw)
+
+    def __call__(self, x, scales: Fp8Scales | None = None):
+        x = np.asarray(x)
+        if not self.use_fp8:  # :288-293
+            dt = promote(x.dtype, self.weight.dtype)
+            out = matmul_nt(x, self.weight, dt)
+            if self.bias is not None:
+                out = rnd(f32(out) + f32(self.bias), promote(dt, self.bias.dtype))
+            return out, None
+
+        cd = self.compute_dtype
+        x = x.astype(cd)  # :296-297
+        w = self.weight.astype(cd)
+
+        if scales is not None:  # :299-326
+            input_scale = scales.input_scale
+            kernel_scale = scales.kernel_scale
+            new_in_hist = compute_amax_history(x, scales.input_amax_history)
+            new_k_hist = compute_amax_history(w, scales.kernel_amax_history)
+            fp8_max = get_fp8_max(self.fp8_dtype, cd)
+            new_in_scale = compute_scale(np.max(new_in_hist), input_scale, fp8_max)
+            new_k_scale = compute_scale(np.max(new_k_hist), kernel_scale, fp8_max)
+            updated = Fp8Scales(new_in_scale, new_in_hist, new_k_scale, new_k_hist)
+        else:  # :327-332
+            input_scale = current_scale(x, self.fp8_dtype, cd)
+            kernel_scale = current_scale(w, self.fp8_dtype, cd)
+            updated = None
+
+        x_qdq = quantize_dequantize(x, self.fp8_dtype, input_scale, cd)  # :335-336
+        w_qdq = quantize_dequantize(w, self.fp8_dtype, kernel_scale, cd)
+        out = matmul_nt(x_qdq, w_qdq, cd)  # :339
+        if self.bias is not None:  # :341-342
+            out = rnd(f32(out) + f32(self.bias), promote(cd, self.bias.dtype))
+        return out, updated
+
+    # -- vectorised form of ``jax.vmap(lambda xi: layer(xi, scales=None))(x_flat)`` ------------
+    def call_rows(self, x2d):
+        """Per-row current scaling: what xax/arch/attention.py:279 computes for a (rows, in)
+        input.  Returns (out, row_scales, q_bytes) -- the last two for kernel parity tests."""
+        cd = self.compute_dtype
+        x = np.asarray(x2d).astype(cd)
+        w = self.weight.astype(cd)
+        fp8_max = get_fp8_max(self.fp8_dtype, cd)
+        amax = np.max(np.abs(f32(x)), axis=-1).astype(cd)
+        floor = np.asarray(1e-12).astype(cd)
+        sx = rnd(f32(fp8_max) / np.maximum(f32(amax), f32(floor)), cd)  # (rows,)
+        sw = current_scale(w, self.fp8_dtype, cd)
+        q = quantize(x, self.fp8_dtype, sx[:, None], cd)
+        x_qdq = dequantize(q, cd, sx[:, None])
+        w_qdq = quantize_dequantize(w, self.fp8_dtype, sw, cd)
+        out = matmul_nt(x_qdq, w_qdq, cd)
+        if self.bias is not None:
+            out = rnd(f32(out) + f32(self.bias), promote(cd, self.bias.dtype))
+        return out, sx, q
+
+
+def fp8_matmul(a, b, compute_dtype=bfloat16, fp8_dtype=float8_e4m3fn) -> np.ndarray:
+    """xax/nn/fp8.py:347-378 (a @ b, both current-scaled)."""
+    a = np.asarray(a).astype(compute_dtype)
+    b = np.asarray(b).astype(compute_dtype)
+    a_scale = current_scale(a, fp8_dtype, compute_dtype)
+    b_scale = current_scale(b, fp8_dtype, compute_dtype)
+    a_qdq = quantize_dequantize(a, fp8_dtype, a_scale, compute_dtype)
+    b_qdq = quantize_dequantize(b, fp8_dtype, b_scale, compute_dtype)
+    return rnd(f32(a_qdq) @ f32(b_qdq), compute_dtype)
