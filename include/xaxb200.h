@@ -1,0 +1,224 @@
+/*
+ * C ABI of the B200 (sm_100a) kernels behind the xax FP8 transformer inference path.
+ *
+ * The reference (codekansas/xax) has no FFI layer of its own: its operator interface is
+ * the Equinox module API, and XLA picks library kernels at JIT time.  Each entry point
+ * below names the reference call site (file:line inside the xax source tree) whose device
+ * work it replaces; a `jax.ffi` (or ctypes) binding registers exactly these symbols.
+ *
+ * Conventions
+ *   - every pointer except `ctx`, `stream` and out-parameters of the ctx_* calls is a
+ *     DEVICE pointer owned by the caller; no entry point allocates or frees device memory
+ *     (xaxb_ctx_create allocates one 4-byte status word, released by xaxb_ctx_destroy);
+ *   - `stream` is a cudaStream_t passed as void*; all work is stream-ordered and returns
+ *     without synchronising, so calls may be captured in a CUDA graph;
+ *   - the return value is an xaxb_status; device-side waits that ran out of time are
+ *     reported by xaxb_ctx_status (which synchronises the stream);
+ *   - bf16 tensors are row-major with the stated shape; "e4m3" is float8_e4m3fn bytes.
+ */
+#ifndef XAXB200_H_
+#define XAXB200_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct xaxb_ctx xaxb_ctx;
+
+typedef enum {
+  XAXB_OK = 0,
+  XAXB_BAD_ARGUMENT = 1,    /* null pointer, non-positive size, misaligned pointer or stride */
+  XAXB_UNSUPPORTED = 2,     /* configuration the kernels do not cover (e.g. head_dim != 64/128) */
+  XAXB_WORKSPACE_TOO_SMALL = 3,
+  XAXB_LAUNCH_FAILED = 4,   /* CUDA runtime / driver error; see xaxb_last_error */
+  XAXB_DEVICE_TIMEOUT = 5,  /* a bounded device-side wait gave up */
+  XAXB_CACHE_OVERFLOW = 6   /* position + new tokens > max_len (the reference clamps silently,
+                               xax/arch/attention.py:885-888; this library refuses) */
+} xaxb_status;
+
+/* ---- context ------------------------------------------------------------------------ */
+
+int xaxb_ctx_create(int device, xaxb_ctx** out);
+int xaxb_ctx_destroy(xaxb_ctx* ctx);
+/* Synchronises `stream`, returns and clears the device status word (XAXB_OK or
+ * XAXB_DEVICE_TIMEOUT with the waiting site in *site, may be NULL). */
+int xaxb_ctx_status(xaxb_ctx* ctx, void* stream, int* site);
+int xaxb_num_sms(const xaxb_ctx* ctx);
+const char* xaxb_status_string(int status);
+const char* xaxb_last_error(void);
+
+/* ---- kernel 1: amax / scale / e4m3 cast ------------------------------------------- */
+
+/*
+ * Current scaling (xax/nn/fp8.py:329-331 + quantize :114-120), one scale per group of
+ * `group_rows` consecutive rows of x[rows, cols] (1 = per token, the vmapped call of
+ * xax/arch/attention.py:279; rows = per tensor, xax/arch/attention.py:55):
+ *     amax_g = max|x_g|                      (bf16, NaN propagates)
+ *     s_g    = bf16(448 / max(amax_g, bf16(1e-12)))
+ *     q      = e4m3(clip(bf16(x * s_g), +-448))
+ * Outputs: q[rows, cols] e4m3; scale[rows] and inv_scale[rows] float32 (s_g and 1/s_g
+ * repeated for every row of the group); amax[groups] float32.
+ * `amax` doubles as the cross-CTA reduction scratch and is cleared by the call.
+ * cols must be a multiple of 8; x and q 16-byte aligned.
+ */
+int xaxb_quantize_current(xaxb_ctx* ctx, void* stream, const void* x_bf16, int64_t rows, int64_t cols,
+                          int64_t group_rows, void* q_e4m3, float* scale, float* inv_scale, float* amax);
+
+/*
+ * Delayed scaling (xax/nn/fp8.py:299-326, :82-94, :50-79): quantise with the INCOMING
+ * scale *scale_in (float32, rounded to bf16 for the multiply as quantize :117 does), and
+ * produce the state for the next call:
+ *     history_out = roll(history_in, -1); history_out[0] = max|x|
+ *     scale_out   = 448 / max(history_out)   (previous scale kept if that max is <= 0 or
+ *                                             not finite)
+ * history_in/out float32[history_len] (may alias); amax_scratch: 4 bytes, cleared by the
+ * call.  q_e4m3 may be NULL to update the state only (used for the weight, whose bytes
+ * are quantised once).  inv_scale_out (may be NULL) receives 1 / bf16(*scale_in), the
+ * dequantisation multiplier matching the bytes written.
+ */
+int xaxb_quantize_delayed(xaxb_ctx* ctx, void* stream, const void* x_bf16, int64_t rows, int64_t cols,
+                          const float* scale_in, const float* history_in, int history_len, void* q_e4m3,
+                          float* history_out, float* scale_out, float* inv_scale_out, float* amax_scratch);
+
+/* ---- kernel 2: e4m3 x e4m3 (and bf16 x bf16) GEMM on tcgen05 / TMEM ------------- */
+
+/*
+ * out[M, N] = bf16( (sum_k a[m,k] * b[n,k]) * row_mul[m] * col_mul[n] + bias[n] + residual[m,n] )
+ * replacing x_qdq @ w_qdq.T + bias (xax/nn/fp8.py:339-342) and, with `residual`, the
+ * block's x + attn_out / x + ff_out (xax/arch/attention.py:1481,1508).
+ * a: e4m3 [M, K] row-major (lda bytes between rows); b: e4m3 [N, K] row-major -- the
+ * reference's (out_features, in_features) weight layout; K-contiguous for both.
+ * row_mul: float32, element m at row_mul[m * row_mul_stride] (stride 0 = per-tensor scale,
+ * 1 = per-token); col_mul likewise over n (stride 0, or 1 for fused projections whose
+ * column blocks carry different weight scales).  NULL means 1.0.
+ * bias: bf16 [N] or NULL; residual: bf16 [M, N] with ldr elements between rows, or NULL.
+ * out: bf16, ldo elements between rows.  K * elem must be a multiple of 16 bytes, a/b
+ * 16-byte aligned, N and ldo multiples of 8.
+ */
+int xaxb_gemm_fp8(xaxb_ctx* ctx, void* stream, const void* a_e4m3, int64_t lda, const void* b_e4m3, int64_t ldb,
+                  int64_t M, int64_t N, int64_t K, const float* row_mul, int row_mul_stride, const float* col_mul,
+                  int col_mul_stride, const void* bias_bf16, const void* residual_bf16, int64_t ldr, void* out_bf16,
+                  int64_t ldo);
+
+/* Same contract for bf16 operands (lda/ldb in elements): the un-quantised linear /
+ * lm_head einsum of xax/arch/attention.py:59-67 (xax/arch/llm.py:213-219). */
+int xaxb_gemm_bf16(xaxb_ctx* ctx, void* stream, const void* a_bf16, int64_t lda, const void* b_bf16, int64_t ldb,
+                   int64_t M, int64_t N, int64_t K, const float* row_mul, int row_mul_stride, const float* col_mul,
+                   int col_mul_stride, const void* bias_bf16, const void* residual_bf16, int64_t ldr, void* out_bf16,
+                   int64_t ldo);
+
+/* Plain CUDA-core GEMM with the same contract as xaxb_gemm_fp8 (one thread per output,
+ * float32 accumulation in k order).  A second opinion for the tensor-core kernel in tests;
+ * never used by the module layer. */
+int xaxb_gemm_fp8_check(xaxb_ctx* ctx, void* stream, const void* a_e4m3, int64_t lda, const void* b_e4m3,
+                        int64_t ldb, int64_t M, int64_t N, int64_t K, const float* row_mul, int row_mul_stride,
+                        const float* col_mul, int col_mul_stride, const void* bias_bf16, const void* residual_bf16,
+                        int64_t ldr, void* out_bf16, int64_t ldo);
+
+/* ---- small bandwidth kernels on the path ------------------------------------------- */
+
+/*
+ * RMSNorm (xax/arch/attention.py:96-98) over the last dimension of x[rows, dim] bf16 with
+ * a bf16 weight, every intermediate rounded to bf16 as the reference's bf16 ops do.
+ * y_bf16 may be NULL.  If q_e4m3 is non-NULL the row is also quantised with per-token
+ * current scaling (as xaxb_quantize_current with group_rows = 1) from the normalised
+ * values, writing q, scale and inv_scale.  If group_amax is non-NULL, max|y| of each group
+ * of `group_rows` rows is accumulated into group_amax[row / group_rows] with an atomic max
+ * on the float bits (caller clears it), for a following per-sequence quantisation.
+ */
+int xaxb_rmsnorm(xaxb_ctx* ctx, void* stream, const void* x_bf16, const void* weight_bf16, float eps, int64_t rows,
+                 int64_t dim, void* y_bf16, void* q_e4m3, float* scale, float* inv_scale, float* group_amax,
+                 int64_t group_rows);
+
+/*
+ * h = bf16(silu(gate) * up) with silu = bf16(g * bf16(sigmoid(g))) (xax/arch/attention.py:146).
+ * gate and up are column blocks of one [rows, ld] bf16 buffer (the fused gate|up GEMM
+ * output): gate = gu[:, 0:dim], up = gu[:, dim:2*dim] when up_bf16 is NULL, else separate
+ * buffers with the same ld.  Quantisation outputs as in xaxb_rmsnorm.
+ */
+int xaxb_silu_mul(xaxb_ctx* ctx, void* stream, const void* gate_bf16, const void* up_bf16, int64_t ld, int64_t rows,
+                  int64_t dim, void* h_bf16, void* q_e4m3, float* scale, float* inv_scale, float* group_amax,
+                  int64_t group_rows);
+
+/* Second pass of a per-group quantisation whose amax was accumulated by xaxb_rmsnorm /
+ * xaxb_silu_mul: scales from group_amax, then the cast (same outputs as
+ * xaxb_quantize_current; group_amax is read, not cleared). */
+int xaxb_quantize_with_amax(xaxb_ctx* ctx, void* stream, const void* x_bf16, int64_t rows, int64_t cols,
+                            int64_t group_rows, const float* group_amax, void* q_e4m3, float* scale,
+                            float* inv_scale);
+
+/* x[i, :] = table[tokens[i], :] (xax/arch/llm.py:205-207); bf16 rows of `dim` elements. */
+int xaxb_embed(xaxb_ctx* ctx, void* stream, const int32_t* tokens, int64_t n_tokens, const void* table_bf16,
+               int64_t vocab, int64_t dim, void* x_bf16);
+
+/* out[i] = argmax_j float32(logits[i, j]), first index on ties (xax/arch/llm.py:1466-1470). */
+int xaxb_argmax(xaxb_ctx* ctx, void* stream, const void* logits_bf16, int64_t rows, int64_t vocab, int64_t ld,
+                int32_t* out);
+
+/* ---- kernel 3: GQA attention with RoPE and a bf16 KV cache -------------------------- */
+
+/*
+ * RoPE + cache write for T new tokens of each of B sequences
+ * (xax/arch/attention.py:870-888, rotation :510-515 "concatenated" style, every product
+ * and sum rounded to bf16).  qkv: bf16 [B*T, ld] holding q | k | v column blocks
+ * (Hq*D, Hkv*D, Hkv*D wide) -- the fused projection's output.  positions[b] = number of
+ * tokens already cached for sequence b (the reference's cache["position"]).  cos/sin:
+ * bf16 [table_len, D/2], built on the host in the reference's op order
+ * (xax/arch/attention.py:390-397).
+ * Writes q_rot [B*T, Hq, D] (rotated), k_cache/v_cache [B, max_len, Hkv, D] at rows
+ * positions[b] .. positions[b]+T-1.  store_rotated_k = 1 keeps the reference's cache
+ * contents (post-RoPE K); 0 stores K un-rotated for the rotate-on-load attention variant.
+ * Returns XAXB_CACHE_OVERFLOW through the device status word if positions[b] + T > max_len.
+ */
+int xaxb_kv_append_rope(xaxb_ctx* ctx, void* stream, const void* qkv_bf16, int64_t ld, int64_t B, int64_t T,
+                        int64_t Hq, int64_t Hkv, int64_t D, const int32_t* positions, const void* cos_bf16,
+                        const void* sin_bf16, int64_t table_len, void* q_rot_bf16, void* k_cache_bf16,
+                        void* v_cache_bf16, int64_t max_len, int store_rotated_k);
+
+/* Bytes of float32 scratch xaxb_attn_decode needs for (B, Hq, D, max_len). */
+int64_t xaxb_attn_decode_workspace_bytes(int64_t B, int64_t Hq, int64_t D, int64_t max_len);
+
+/*
+ * Decode attention: one query token per sequence against the cache
+ * (xax/arch/attention.py:910-946 with seq_len = 1; softmax in float32; query head h reads
+ * kv head h / (Hq/Hkv)).  q_rot: bf16 [B, Hq, D] already rotated; the query of sequence b
+ * sits at positions[b] and attends to cache rows 0 .. positions[b] (the row written by the
+ * preceding xaxb_kv_append_rope included).  k_is_rotated = 0 rotates K on load with the
+ * cos/sin table (cos/sin may be NULL otherwise).  out: bf16 [B, Hq, D].
+ * Split over 128-token chunks; per-chunk partial results go through `workspace`
+ * (xaxb_attn_decode_workspace_bytes; contents need no initialisation).
+ */
+int xaxb_attn_decode(xaxb_ctx* ctx, void* stream, const void* q_rot_bf16, const void* k_cache_bf16,
+                     const void* v_cache_bf16, const int32_t* positions, int64_t B, int64_t Hq, int64_t Hkv,
+                     int64_t D, int64_t max_len, float softmax_scale, int k_is_rotated, const void* cos_bf16,
+                     const void* sin_bf16, int64_t table_len, void* out_bf16, void* workspace,
+                     int64_t workspace_bytes);
+
+/*
+ * Causal prefill attention for T new tokens per sequence against the cache (which
+ * already holds them, written by xaxb_kv_append_rope): query i of sequence b sits at
+ * position positions[b] + i and attends to cache rows 0 .. positions[b] + i
+ * (xax/arch/attention.py:914-926).  q_rot: bf16 [B*T, Hq, D]; out: bf16 [B*T, Hq, D].
+ */
+int xaxb_attn_prefill(xaxb_ctx* ctx, void* stream, const void* q_rot_bf16, const void* k_cache_bf16,
+                      const void* v_cache_bf16, const int32_t* positions, int64_t B, int64_t T, int64_t Hq,
+                      int64_t Hkv, int64_t D, int64_t max_len, float softmax_scale, void* out_bf16);
+
+/* Straightforward CUDA-core attention with the contract of xaxb_attn_prefill (T = 1 gives
+ * decode): a second opinion for the tensor-core kernels in tests; never used by the
+ * module layer. */
+int xaxb_attn_check(xaxb_ctx* ctx, void* stream, const void* q_rot_bf16, const void* k_cache_bf16,
+                    const void* v_cache_bf16, const int32_t* positions, int64_t B, int64_t T, int64_t Hq, int64_t Hkv,
+                    int64_t D, int64_t max_len, float softmax_scale, void* out_bf16);
+
+/* positions[b] += delta for b < B (the reference's new_position = p + seq_len,
+ * xax/arch/attention.py:888), kept on the device so a captured decode step can replay. */
+int xaxb_advance_positions(xaxb_ctx* ctx, void* stream, int32_t* positions, int64_t B, int32_t delta);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* XAXB200_H_ */

@@ -1,0 +1,406 @@
+// Kernel 3a: GQA decode attention over a bf16 KV cache, split over 128-token chunks.
+//
+// HBM-bound: every K and V row is read exactly once.  One CTA owns one (sequence, kv head,
+// 128-token chunk).  The chunk's K and V tiles ([128 tokens x D] bf16) are brought in by TMA
+// into 128-byte-swizzled shared memory and consumed in place by tcgen05.mma -- the threads
+// never touch K or V (unless K is stored un-rotated, see below):
+//
+//   S^T[token, g] = K[token, :] . Q[g, :]      UMMA M = 128 tokens, N = 16 (G query heads of
+//                                              the group, zero padded), K = D; A = K tile
+//                                              (K-major), B = Q (K-major)
+//   P = exp(S * scale - max)                   thread t owns token t: tcgen05.ld gives it the
+//                                              G scores of its token; max / sum over tokens
+//                                              are warp-shuffle + shared-memory reductions
+//   O^T[d, g] = sum_token V[token, d] P[token, g]   UMMA M = 128 (for D = 64 the upper 64 rows
+//                                              read a zeroed pad), N = 16, K = 128 tokens;
+//                                              A = V tile (MN-major: D contiguous), B = P^T
+//                                              written to shared memory as bf16 (K-major)
+//
+// Each CTA writes (max, sum, O^T) for its chunk to the workspace; a second kernel merges the
+// chunks of a sequence with the usual log-sum-exp weights and writes bf16 output.
+//
+// With k_is_rotated = 0 the cache holds K as projected and the rotation is applied on load:
+// after the TMA lands, thread t rotates row t of the K tile in shared memory with row
+// (chunk start + t) of the cos/sin table (bf16 arithmetic in the reference's order) before
+// the first MMA.
+#include "common.cuh"
+
+namespace xaxb {
+
+constexpr int kChunk = 128;   // tokens per CTA
+constexpr int kNPad = 16;     // UMMA N: query heads of one group, zero padded
+constexpr int kSiteDecK = 11, kSiteDecV = 12, kSiteDecS = 13, kSiteDecO = 14;
+
+struct DecodeParams {
+  const __nv_bfloat16* q;      // [B, Hq, D] rotated
+  const int32_t* positions;    // [B]; attend to rows 0 .. positions[b]
+  int Hq, Hkv, G;
+  long long max_len;
+  float sm_scale;
+  int k_is_rotated;
+  const __nv_bfloat16* cos_t;  // [table_len, D/2]
+  const __nv_bfloat16* sin_t;
+  long long table_len;
+  float* ws_o;   // [B, Hq, max_chunks, D]
+  float* ws_ml;  // [B, Hq, max_chunks, 2]
+  int max_chunks;
+  int* d_status;
+};
+
+template <int D>
+struct DecodeSmem {
+  static constexpr int kTileBytes = kChunk * D * 2;           // one K or V tile
+  static constexpr int kHalfBytes = kChunk * 128;             // one 64-element-wide TMA box
+  static constexpr int kQBytes = kNPad * D * 2;
+  static constexpr int kPBytes = kNPad * kChunk * 2;
+  static constexpr int kVBytes = 2 * kHalfBytes;               // D = 64: second half is a zero pad
+  static constexpr int kBytes = kTileBytes + kVBytes + kQBytes + kPBytes + 1024 + 512;
+};
+
+template <int D>
+__global__ void __launch_bounds__(128) attn_decode_kernel(const __grid_constant__ CUtensorMap tmap_k,
+                                                          const __grid_constant__ CUtensorMap tmap_v,
+                                                          const DecodeParams p) {
+  using SM = DecodeSmem<D>;
+  constexpr int kBoxes = D / 64;  // 128-byte-wide boxes per row
+  const int chunk = blockIdx.x, hk = blockIdx.y, b = blockIdx.z;
+  const int L = p.positions[b] + 1;
+  const int tok0 = chunk * kChunk;
+  if (tok0 >= L) return;
+  const int valid = min(kChunk, L - tok0);
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sK = smem;
+  uint8_t* sV = sK + SM::kTileBytes;
+  uint8_t* sQ = sV + SM::kVBytes;             // [kBoxes][16 rows x 128 B], swizzled
+  uint8_t* sP = sQ + SM::kQBytes;             // [2][16 rows x 128 B], swizzled (128 tokens)
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sP + SM::kPBytes);
+  uint64_t* bar_k = bars;
+  uint64_t* bar_v = bars + 1;
+  uint64_t* bar_s = bars + 2;
+  uint64_t* bar_o = bars + 3;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 4);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  float* red = reinterpret_cast<float*>(tmem_slot + 2);  // [4 warps][16]
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+
+  if (tid == 0) {
+    mbar_init(bar_k, 1);
+    mbar_init(bar_v, 1);
+    mbar_init(bar_s, 1);
+    mbar_init(bar_o, 1);
+    *abort_flag = 0;
+    fence_mbar_init();
+    mbar_arrive_expect_tx(bar_k, SM::kTileBytes);
+    mbar_arrive_expect_tx(bar_v, SM::kTileBytes);
+#pragma unroll
+    for (int x = 0; x < kBoxes; ++x) tma_load_4d(sK + x * SM::kHalfBytes, &tmap_k, bar_k, x * 64, hk, tok0, b);
+#pragma unroll
+    for (int x = 0; x < kBoxes; ++x) tma_load_4d(sV + x * SM::kHalfBytes, &tmap_v, bar_v, x * 64, hk, tok0, b);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, 32);
+    tmem_relinquish();
+  }
+
+  // Q of this group -> shared memory, K-major rows of D elements, rows >= G zero.
+  {
+    constexpr int kChunksPerRow = D / 8;  // 16-byte chunks
+    for (int i = tid; i < kNPad * kChunksPerRow; i += 128) {
+      const int g = i / kChunksPerRow, c = i % kChunksPerRow;
+      uint4 v = make_uint4(0, 0, 0, 0);
+      if (g < p.G)
+        v = __ldg(reinterpret_cast<const uint4*>(p.q + ((long long)b * p.Hq + hk * p.G + g) * D) + c);
+      const int box = c / 8, cc = c % 8;
+      *reinterpret_cast<uint4*>(sQ + box * (kNPad * 128) + sw128_offset(g, cc)) = v;
+    }
+  }
+  if (D == 64) {  // zero pad standing in for V dims 64..127
+    for (int i = tid; i < SM::kHalfBytes / 16; i += 128)
+      reinterpret_cast<uint4*>(sV + SM::kHalfBytes)[i] = make_uint4(0, 0, 0, 0);
+  }
+  fence_proxy_async_smem();
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tmem_s = tmem_base;        // columns [0, 16)
+  const uint32_t tmem_o = tmem_base + 16;   // columns [16, 32)
+
+  bool ok = mbar_wait(bar_k, 0, abort_flag, p.d_status, XAXB_DEVICE_TIMEOUT * 1000 + kSiteDecK);
+  ok = __syncthreads_and(ok);
+
+  if (!p.k_is_rotated && ok) {
+    // Rotate K row `tid` in place: pair (i, i + D/2) lives in chunk i/8 of box (i / 64) and
+    // chunk (i + D/2)/8 of the other half.
+    const long long pos = tok0 + tid;
+    if (tid < valid && pos < p.table_len) {
+      constexpr int half = D / 2;
+      const __nv_bfloat16* cr = p.cos_t + pos * half;
+      const __nv_bfloat16* sr = p.sin_t + pos * half;
+      for (int c = 0; c < half / 8; ++c) {
+        const int c2 = c + half / 8;
+        uint4* p1 = reinterpret_cast<uint4*>(sK + (c / 8) * SM::kHalfBytes + sw128_offset(tid, c % 8));
+        uint4* p2 = reinterpret_cast<uint4*>(sK + (c2 / 8) * SM::kHalfBytes + sw128_offset(tid, c2 % 8));
+        uint4 a = *p1, bb = *p2;
+        const uint4 cv = __ldg(reinterpret_cast<const uint4*>(cr) + c);
+        const uint4 sv = __ldg(reinterpret_cast<const uint4*>(sr) + c);
+        uint32_t* aw = reinterpret_cast<uint32_t*>(&a);
+        uint32_t* bw = reinterpret_cast<uint32_t*>(&bb);
+        const uint32_t* cw = reinterpret_cast<const uint32_t*>(&cv);
+        const uint32_t* sw = reinterpret_cast<const uint32_t*>(&sv);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          uint32_t o1 = 0, o2 = 0;
+#pragma unroll
+          for (int hsel = 0; hsel < 2; ++hsel) {
+            const int sh = hsel * 16;
+            const float x1 = bf16_bits_to_float((aw[j] >> sh) & 0xFFFFu);
+            const float x2 = bf16_bits_to_float((bw[j] >> sh) & 0xFFFFu);
+            const float cc = bf16_bits_to_float((cw[j] >> sh) & 0xFFFFu);
+            const float ss = bf16_bits_to_float((sw[j] >> sh) & 0xFFFFu);
+            const float r1 = bf16_round(x1 * cc) - bf16_round(x2 * ss);
+            const float r2 = bf16_round(x2 * cc) + bf16_round(x1 * ss);
+            o1 |= (uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(r1)) << sh;
+            o2 |= (uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(r2)) << sh;
+          }
+          aw[j] = o1;
+          bw[j] = o2;
+        }
+        *p1 = a;
+        *p2 = bb;
+      }
+    }
+    fence_proxy_async_smem();
+    __syncthreads();
+  }
+
+  // ---- S^T = K Q^T -----------------------------------------------------------------------
+  if (tid == 0 && ok) {
+    tc_fence_after_sync();
+    constexpr uint32_t idesc = umma_idesc(kFmtBF16, kFmtBF16, 0, 0, 128, kNPad);
+#pragma unroll
+    for (int k = 0; k < D / 16; ++k) {  // 16 bf16 = 32 bytes of K per MMA
+      const uint32_t box = k / 4, off = (k % 4) * 32;
+      const uint64_t a_desc = umma_desc_kmajor_sw128(smem_u32(sK + box * SM::kHalfBytes) + off);
+      const uint64_t b_desc = umma_desc_kmajor_sw128(smem_u32(sQ + box * (kNPad * 128)) + off);
+      umma_f16(tmem_s, a_desc, b_desc, idesc, k != 0);
+    }
+    umma_commit(bar_s);
+  }
+  ok = ok && mbar_wait(bar_s, 0, abort_flag, p.d_status, XAXB_DEVICE_TIMEOUT * 1000 + kSiteDecS);
+  ok = __syncthreads_and(ok);
+
+  float pvals[kNPad];
+  if (ok) {
+    tc_fence_after_sync();
+    uint32_t r[16];
+    tmem_ld_x16(tmem_s + (uint32_t(warp * 32) << 16), r);
+    tmem_ld_wait();
+    const bool tok_ok = tid < valid;
+    float mx[kNPad];
+#pragma unroll
+    for (int g = 0; g < kNPad; ++g) {
+      pvals[g] = tok_ok ? __uint_as_float(r[g]) * p.sm_scale : -INFINITY;
+      mx[g] = pvals[g];
+    }
+#pragma unroll
+    for (int g = 0; g < kNPad; ++g)
+      for (int o = 16; o > 0; o >>= 1) mx[g] = fmaxf(mx[g], __shfl_xor_sync(0xffffffffu, mx[g], o));
+    if (lane == 0) {
+#pragma unroll
+      for (int g = 0; g < kNPad; ++g) red[warp * kNPad + g] = mx[g];
+    }
+  }
+  __syncthreads();
+  float sums[kNPad];
+  if (ok) {
+#pragma unroll
+    for (int g = 0; g < kNPad; ++g) {
+      const float m = fmaxf(fmaxf(red[g], red[kNPad + g]), fmaxf(red[2 * kNPad + g], red[3 * kNPad + g]));
+      const float e = (tid < valid) ? __expf(pvals[g] - m) : 0.0f;
+      pvals[g] = e;
+      sums[g] = e;
+      if (tid == g && g < p.G)
+        p.ws_ml[(((long long)b * p.Hq + hk * p.G + g) * p.max_chunks + chunk) * 2 + 0] = m;
+    }
+#pragma unroll
+    for (int g = 0; g < kNPad; ++g)
+      for (int o = 16; o > 0; o >>= 1) sums[g] += __shfl_xor_sync(0xffffffffu, sums[g], o);
+  }
+  __syncthreads();  // everyone has read the maxima from `red`
+  if (ok) {
+    if (lane == 0) {
+#pragma unroll
+      for (int g = 0; g < kNPad; ++g) red[warp * kNPad + g] = sums[g];
+    }
+    // P^T as the B operand: row g, 128 tokens (two 64-token boxes), K-major, swizzled.
+    const int box = tid / 64, within = tid % 64;
+#pragma unroll
+    for (int g = 0; g < kNPad; ++g) {
+      const uint32_t off = box * (kNPad * 128) + sw128_offset(g, within / 8) + (within % 8) * 2;
+      *reinterpret_cast<__nv_bfloat16*>(sP + off) = __float2bfloat16_rn(g < p.G ? pvals[g] : 0.0f);
+    }
+  }
+  ok = ok && mbar_wait(bar_v, 0, abort_flag, p.d_status, XAXB_DEVICE_TIMEOUT * 1000 + kSiteDecV);
+  if (ok && tid >= valid) {
+    // rows past the sequence end may hold anything: clear them so 0 * garbage stays 0
+#pragma unroll
+    for (int c = 0; c < D / 8; ++c)
+      *reinterpret_cast<uint4*>(sV + (c / 8) * SM::kHalfBytes + sw128_offset(tid, c % 8)) = make_uint4(0, 0, 0, 0);
+  }
+  fence_proxy_async_smem();
+  tc_fence_before_sync();
+  ok = __syncthreads_and(ok);
+  if (tid < p.G && ok) {
+    const float l = red[tid] + red[kNPad + tid] + red[2 * kNPad + tid] + red[3 * kNPad + tid];
+    p.ws_ml[(((long long)b * p.Hq + hk * p.G + tid) * p.max_chunks + chunk) * 2 + 1] = l;
+  }
+
+  // ---- O^T = V^T P -------------------------------------------------------------------------
+  if (tid == 0 && ok) {
+    tc_fence_after_sync();
+    constexpr uint32_t idesc = umma_idesc(kFmtBF16, kFmtBF16, 1, 0, 128, kNPad);
+#pragma unroll
+    for (int k = 0; k < kChunk / 16; ++k) {  // 16 tokens per MMA
+      const uint64_t a_desc = umma_desc_mnmajor_sw128(smem_u32(sV) + k * 16 * 128, SM::kHalfBytes);
+      const uint64_t b_desc = umma_desc_kmajor_sw128(smem_u32(sP + (k / 4) * (kNPad * 128)) + (k % 4) * 32);
+      umma_f16(tmem_o, a_desc, b_desc, idesc, k != 0);
+    }
+    umma_commit(bar_o);
+  }
+  ok = ok && mbar_wait(bar_o, 0, abort_flag, p.d_status, XAXB_DEVICE_TIMEOUT * 1000 + kSiteDecO);
+  ok = __syncthreads_and(ok);
+  if (ok) {
+    tc_fence_after_sync();
+    // accumulator row d (a head dimension) sits in TMEM lane d
+    uint32_t r[16];
+    tmem_ld_x16(tmem_o + (uint32_t(warp * 32) << 16), r);
+    tmem_ld_wait();
+    const int d = tid;
+    if (d < D) {
+#pragma unroll
+      for (int g = 0; g < kNPad; ++g)
+        if (g < p.G)
+          p.ws_o[(((long long)b * p.Hq + hk * p.G + g) * p.max_chunks + chunk) * D + d] = __uint_as_float(r[g]);
+    }
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, 32);
+  }
+}
+
+// Merge the chunks of one (sequence, query head): out = sum_c w_c O_c / sum_c w_c l_c with
+// w_c = exp(m_c - max m).  D threads.
+__global__ void attn_decode_merge_kernel(const float* __restrict__ ws_o, const float* __restrict__ ws_ml,
+                                         const int32_t* __restrict__ positions, int Hq, int D, int max_chunks,
+                                         __nv_bfloat16* __restrict__ out) {
+  const int h = blockIdx.x, b = blockIdx.y, d = threadIdx.x;
+  const int L = positions[b] + 1;
+  const int n = (L + kChunk - 1) / kChunk;
+  const long long base = ((long long)b * Hq + h) * max_chunks;
+  float m = -INFINITY;
+  for (int c = 0; c < n; ++c) m = fmaxf(m, ws_ml[(base + c) * 2]);
+  float num = 0.0f, den = 0.0f;
+  for (int c = 0; c < n; ++c) {
+    const float w = __expf(ws_ml[(base + c) * 2] - m);
+    num = fmaf(w, ws_o[(base + c) * D + d], num);
+    den = fmaf(w, ws_ml[(base + c) * 2 + 1], den);
+  }
+  out[((long long)b * Hq + h) * D + d] = __float2bfloat16_rn(num / den);
+}
+
+static int make_cache_tmap(const Ctx* ctx, CUtensorMap* map, const void* cache, int64_t B, int64_t max_len,
+                           int64_t Hkv, int64_t D) {
+  // cache[b][token][head][d]: dims innermost first (d, head, token, b); box = 64 d x 1 head x 128 tokens x 1.
+  const uint64_t dims[4] = {(uint64_t)D, (uint64_t)Hkv, (uint64_t)max_len, (uint64_t)B};
+  const uint64_t strides[3] = {(uint64_t)D * 2, (uint64_t)Hkv * D * 2, (uint64_t)max_len * Hkv * D * 2};
+  const uint32_t box[4] = {64, 1, (uint32_t)kChunk, 1};
+  return make_tmap_4d(ctx, map, cache, 2, dims, strides, box);
+}
+
+}  // namespace xaxb
+
+using namespace xaxb;
+
+extern "C" {
+
+int64_t xaxb_attn_decode_workspace_bytes(int64_t B, int64_t Hq, int64_t D, int64_t max_len) {
+  const int64_t chunks = (max_len + kChunk - 1) / kChunk;
+  return B * Hq * chunks * (D + 2) * (int64_t)sizeof(float);
+}
+
+int xaxb_attn_decode(xaxb_ctx* ctx_, void* stream, const void* q_rot_bf16, const void* k_cache_bf16,
+                     const void* v_cache_bf16, const int32_t* positions, int64_t B, int64_t Hq, int64_t Hkv, int64_t D,
+                     int64_t max_len, float softmax_scale, int k_is_rotated, const void* cos_bf16,
+                     const void* sin_bf16, int64_t table_len, void* out_bf16, void* workspace,
+                     int64_t workspace_bytes) {
+  if (!ctx_ || !q_rot_bf16 || !k_cache_bf16 || !v_cache_bf16 || !positions || !out_bf16 || !workspace || B <= 0 ||
+      Hq <= 0 || Hkv <= 0 || max_len <= 0) {
+    set_last_error("attn_decode: null pointer or non-positive shape");
+    return XAXB_BAD_ARGUMENT;
+  }
+  if (Hq % Hkv != 0 || Hq / Hkv > kNPad || (D != 128 && D != 64) || Hkv > 65535 || B > 65535) {
+    set_last_error("attn_decode: needs head_dim 64 or 128 and at most %d query heads per kv head", kNPad);
+    return XAXB_UNSUPPORTED;
+  }
+  if (!k_is_rotated && (!cos_bf16 || !sin_bf16 || table_len < max_len)) {
+    set_last_error("attn_decode: rotate-on-load needs cos/sin tables covering max_len");
+    return XAXB_BAD_ARGUMENT;
+  }
+  if (workspace_bytes < xaxb_attn_decode_workspace_bytes(B, Hq, D, max_len)) return XAXB_WORKSPACE_TOO_SMALL;
+  if (reinterpret_cast<uintptr_t>(q_rot_bf16) & 15) return XAXB_BAD_ARGUMENT;
+  const Ctx* ctx = reinterpret_cast<const Ctx*>(ctx_);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  CUtensorMap tk, tv;
+  int rc = make_cache_tmap(ctx, &tk, k_cache_bf16, B, max_len, Hkv, D);
+  if (rc) return rc;
+  rc = make_cache_tmap(ctx, &tv, v_cache_bf16, B, max_len, Hkv, D);
+  if (rc) return rc;
+  const int max_chunks = (int)((max_len + kChunk - 1) / kChunk);
+  DecodeParams p;
+  p.q = static_cast<const __nv_bfloat16*>(q_rot_bf16);
+  p.positions = positions;
+  p.Hq = (int)Hq, p.Hkv = (int)Hkv, p.G = (int)(Hq / Hkv);
+  p.max_len = max_len;
+  p.sm_scale = softmax_scale;
+  p.k_is_rotated = k_is_rotated;
+  p.cos_t = static_cast<const __nv_bfloat16*>(cos_bf16);
+  p.sin_t = static_cast<const __nv_bfloat16*>(sin_bf16);
+  p.table_len = table_len;
+  p.ws_o = static_cast<float*>(workspace);
+  p.ws_ml = p.ws_o + B * Hq * max_chunks * D;
+  p.max_chunks = max_chunks;
+  p.d_status = ctx->d_status;
+  dim3 grid((unsigned)max_chunks, (unsigned)Hkv, (unsigned)B);
+  if (D == 128) {
+    static bool set128 = false;
+    if (!set128) {
+      cudaFuncSetAttribute(attn_decode_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                           DecodeSmem<128>::kBytes);
+      set128 = true;
+    }
+    attn_decode_kernel<128><<<grid, 128, DecodeSmem<128>::kBytes, s>>>(tk, tv, p);
+  } else {
+    static bool set64 = false;
+    if (!set64) {
+      cudaFuncSetAttribute(attn_decode_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                           DecodeSmem<64>::kBytes);
+      set64 = true;
+    }
+    attn_decode_kernel<64><<<grid, 128, DecodeSmem<64>::kBytes, s>>>(tk, tv, p);
+  }
+  rc = check_launch("attn_decode_kernel");
+  if (rc) return rc;
+  dim3 mgrid((unsigned)Hq, (unsigned)B);
+  attn_decode_merge_kernel<<<mgrid, (unsigned)D, 0, s>>>(p.ws_o, p.ws_ml, positions, (int)Hq, (int)D, max_chunks,
+                                                         static_cast<__nv_bfloat16*>(out_bf16));
+  return check_launch("attn_decode_merge_kernel");
+}
+
+}  // extern "C"

@@ -1,0 +1,314 @@
+// Kernel 3b: causal GQA prefill attention against the KV cache (flash-attention style, one
+// pass, float32 online softmax), on tcgen05 tensor cores.
+//
+// One CTA = 128 consecutive queries of one (sequence, query head); 128 threads, thread r owns
+// query row r.  For every 128-token tile of the cache up to the diagonal:
+//   S  = Q K^T      UMMA M = 128 queries, N = 128 tokens, K = D      (A = Q, B = K tile; K-major)
+//   thread r reads row r of S from TMEM, applies the causal mask and the online-softmax
+//   update, writes bf16 probabilities to shared memory (the reference also rounds the
+//   probabilities to the value dtype before P.V),
+//   PV = P V        UMMA M = 128 queries, N = D, K = 128 tokens      (A = P K-major, B = V tile
+//                                                                     MN-major: D contiguous)
+//   thread r reads row r of PV and folds it into its float32 output row: o = o * alpha + PV.
+// K / V tiles arrive by TMA (128-byte swizzle) into a two-stage ring, so the next tile loads
+// while the current one is processed.  Query position i of sequence b is positions[b] + i and
+// sees cache rows 0 .. positions[b] + i.
+#include "common.cuh"
+
+namespace xaxb {
+
+constexpr int kPfTile = 128;
+constexpr int kSitePfKV = 21, kSitePfS = 22, kSitePfO = 23;
+
+struct PrefillParams {
+  const __nv_bfloat16* q;    // [B*T, Hq, D] rotated
+  __nv_bfloat16* out;        // [B*T, Hq, D]
+  const int32_t* positions;  // [B]
+  int T, Hq, Hkv;
+  float sm_scale;
+  int* d_status;
+};
+
+template <int D>
+struct PrefillSmem {
+  static constexpr int kHalfBytes = kPfTile * 128;          // 128 rows x 128 B
+  static constexpr int kQBytes = kPfTile * D * 2;
+  static constexpr int kKVBytes = kPfTile * D * 2;          // one K or one V tile
+  static constexpr int kPBytes = kPfTile * kPfTile * 2;
+  static constexpr int kBytes = kQBytes + 4 * kKVBytes + kPBytes + 1024 + 256;
+  static constexpr int kTmemCols = 256;
+};
+
+template <int D>
+__global__ void __launch_bounds__(128, 1) attn_prefill_kernel(const __grid_constant__ CUtensorMap tmap_k,
+                                                              const __grid_constant__ CUtensorMap tmap_v,
+                                                              const PrefillParams p) {
+  using SM = PrefillSmem<D>;
+  constexpr int kBoxes = D / 64;
+  const int qb = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
+  const int hk = h / (p.Hq / p.Hkv);
+  const int start = p.positions[b];
+  const int q0 = qb * kPfTile;                    // first query index of this CTA
+  const int rows_valid = min(kPfTile, p.T - q0);
+  const int last_pos = start + q0 + rows_valid - 1;  // highest key position any row may see
+  const int n_tiles = last_pos / kPfTile + 1;
+  const int total_len = start + p.T;              // rows of the cache holding this sequence
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sQ = smem;
+  uint8_t* sKV = sQ + SM::kQBytes;                // stage s: K at s*2*kKVBytes, V right after
+  uint8_t* sP = sKV + 4 * SM::kKVBytes;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sP + SM::kPBytes);
+  uint64_t* bar_kv = bars;      // [2]
+  uint64_t* bar_s = bars + 2;
+  uint64_t* bar_o = bars + 3;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 4);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int tid = threadIdx.x, warp = tid >> 5;
+
+  auto issue_tile = [&](int j) {  // thread 0 only
+    const int s = j & 1;
+    uint8_t* k_dst = sKV + s * 2 * SM::kKVBytes;
+    uint8_t* v_dst = k_dst + SM::kKVBytes;
+    mbar_arrive_expect_tx(bar_kv + s, 2 * SM::kKVBytes);
+#pragma unroll
+    for (int x = 0; x < kBoxes; ++x) {
+      tma_load_4d(k_dst + x * SM::kHalfBytes, &tmap_k, bar_kv + s, x * 64, hk, j * kPfTile, b);
+      tma_load_4d(v_dst + x * SM::kHalfBytes, &tmap_v, bar_kv + s, x * 64, hk, j * kPfTile, b);
+    }
+  };
+
+  if (tid == 0) {
+    mbar_init(bar_kv, 1);
+    mbar_init(bar_kv + 1, 1);
+    mbar_init(bar_s, 1);
+    mbar_init(bar_o, 1);
+    *abort_flag = 0;
+    fence_mbar_init();
+    issue_tile(0);
+    if (n_tiles > 1) issue_tile(1);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, SM::kTmemCols);
+    tmem_relinquish();
+  }
+  // Q rows -> shared memory (K-major, swizzled); rows past T are zero.
+  {
+    constexpr int kChunksPerRow = D / 8;
+    for (int i = tid; i < kPfTile * kChunksPerRow; i += 128) {
+      const int r = i / kChunksPerRow, c = i % kChunksPerRow;
+      uint4 v = make_uint4(0, 0, 0, 0);
+      if (r < rows_valid)
+        v = __ldg(reinterpret_cast<const uint4*>(p.q + (((long long)b * p.T + q0 + r) * p.Hq + h) * D) + c);
+      *reinterpret_cast<uint4*>(sQ + (c / 8) * SM::kHalfBytes + sw128_offset(r, c % 8)) = v;
+    }
+  }
+  fence_proxy_async_smem();
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tmem_s = tmem_base;          // columns [0, 128)
+  const uint32_t tmem_pv = tmem_base + 128;   // columns [128, 128 + D)
+  const uint32_t lane_off = uint32_t(warp * 32) << 16;
+
+  float o[D];
+#pragma unroll
+  for (int i = 0; i < D; ++i) o[i] = 0.0f;
+  float m_run = -INFINITY, l_run = 0.0f;
+  const int qpos = start + q0 + min(tid, rows_valid - 1);  // rows past T mirror the last valid row
+  const float scale_log2 = p.sm_scale * 1.4426950408889634f;
+
+  bool ok = true;
+  for (int j = 0; j < n_tiles; ++j) {
+    const int s = j & 1;
+    uint8_t* sK = sKV + s * 2 * SM::kKVBytes;
+    uint8_t* sV = sK + SM::kKVBytes;
+    ok = ok && mbar_wait(bar_kv + s, (j >> 1) & 1, abort_flag, p.d_status, XAXB_DEVICE_TIMEOUT * 1000 + kSitePfKV);
+    // rows of the tile past the sequence's last cached token may hold anything; the mask
+    // zeroes their probabilities, and V is cleared so that 0 * garbage stays 0
+    if (ok && j * kPfTile + tid >= total_len) {
+#pragma unroll
+      for (int c = 0; c < D / 8; ++c)
+        *reinterpret_cast<uint4*>(sV + (c / 8) * SM::kHalfBytes + sw128_offset(tid, c % 8)) = make_uint4(0, 0, 0, 0);
+      fence_proxy_async_smem();
+    }
+    if (tid == 0 && ok) {
+      tc_fence_after_sync();
+      constexpr uint32_t idesc = umma_idesc(kFmtBF16, kFmtBF16, 0, 0, 128, kPfTile);
+#pragma unroll
+      for (int k = 0; k < D / 16; ++k) {
+        const uint32_t box = k / 4, off = (k % 4) * 32;
+        umma_f16(tmem_s, umma_desc_kmajor_sw128(smem_u32(sQ + box * SM::kHalfBytes) + off),
+                 umma_desc_kmajor_sw128(smem_u32(sK + box * SM::kHalfBytes) + off), idesc, k != 0);
+      }
+      umma_commit(bar_s);
+    }
+    ok = ok && mbar_wait(bar_s, j & 1, abort_flag, p.d_status, XAXB_DEVICE_TIMEOUT * 1000 + kSitePfS);
+    ok = __syncthreads_and(ok);
+    if (!ok) break;
+    tc_fence_after_sync();
+
+    // ---- online softmax on row `tid` of S (two sweeps over TMEM: max, then exp) ------------
+    const int kv0 = j * kPfTile;
+    const bool diag = kv0 + kPfTile - 1 > start + q0;  // some (row, col) of this tile is masked
+    float m_tile = -INFINITY;
+#pragma unroll 1
+    for (int c0 = 0; c0 < kPfTile; c0 += 32) {
+      uint32_t r[32];
+      tmem_ld_x32(tmem_s + lane_off + c0, r);
+      tmem_ld_wait();
+#pragma unroll
+      for (int i = 0; i < 32; ++i) {
+        const float v = __uint_as_float(r[i]);
+        if (!diag || kv0 + c0 + i <= qpos) m_tile = fmaxf(m_tile, v);
+      }
+    }
+    const float m_new = fmaxf(m_run, m_tile * scale_log2);  // base-2 domain; column 0 of tile 0 is always visible
+    const float alpha = exp2f(m_run - m_new);
+    float l_tile = 0.0f;
+#pragma unroll 1
+    for (int c0 = 0; c0 < kPfTile; c0 += 32) {
+      uint32_t r[32];
+      tmem_ld_x32(tmem_s + lane_off + c0, r);
+      tmem_ld_wait();
+      uint32_t packed[16];
+#pragma unroll
+      for (int i = 0; i < 32; i += 2) {
+        float e0 = exp2f(__uint_as_float(r[i]) * scale_log2 - m_new);
+        float e1 = exp2f(__uint_as_float(r[i + 1]) * scale_log2 - m_new);
+        if (diag) {
+          if (kv0 + c0 + i > qpos) e0 = 0.0f;
+          if (kv0 + c0 + i + 1 > qpos) e1 = 0.0f;
+        }
+        l_tile += e0 + e1;
+        const uint32_t lo = __bfloat16_as_ushort(__float2bfloat16_rn(e0));
+        const uint32_t hi = __bfloat16_as_ushort(__float2bfloat16_rn(e1));
+        packed[i / 2] = lo | (hi << 16);
+      }
+      // 32 tokens = 4 chunks of 16 bytes in box c0 / 64
+#pragma unroll
+      for (int cc = 0; cc < 4; ++cc) {
+        const int chunk = (c0 % 64) / 8 + cc;
+        *reinterpret_cast<uint4*>(sP + (c0 / 64) * SM::kHalfBytes + sw128_offset(tid, chunk)) =
+            make_uint4(packed[cc * 4], packed[cc * 4 + 1], packed[cc * 4 + 2], packed[cc * 4 + 3]);
+      }
+    }
+    l_run = l_run * alpha + l_tile;
+    m_run = m_new;
+    fence_proxy_async_smem();
+    tc_fence_before_sync();
+    __syncthreads();
+
+    // ---- PV = P V ------------------------------------------------------------------------------
+    if (tid == 0) {
+      tc_fence_after_sync();
+      constexpr uint32_t idesc = umma_idesc(kFmtBF16, kFmtBF16, 0, 1, 128, D);
+#pragma unroll
+      for (int k = 0; k < kPfTile / 16; ++k) {
+        umma_f16(tmem_pv, umma_desc_kmajor_sw128(smem_u32(sP + (k / 4) * SM::kHalfBytes) + (k % 4) * 32),
+                 umma_desc_mnmajor_sw128(smem_u32(sV) + k * 16 * 128, SM::kHalfBytes), idesc, k != 0);
+      }
+      umma_commit(bar_o);
+    }
+    ok = mbar_wait(bar_o, j & 1, abort_flag, p.d_status, XAXB_DEVICE_TIMEOUT * 1000 + kSitePfO);
+    ok = __syncthreads_and(ok);
+    if (!ok) break;
+    tc_fence_after_sync();
+    if (tid == 0 && j + 2 < n_tiles) issue_tile(j + 2);  // stage s is free again
+#pragma unroll
+    for (int c0 = 0; c0 < D; c0 += 32) {
+      uint32_t r[32];
+      tmem_ld_x32(tmem_pv + lane_off + c0, r);
+      tmem_ld_wait();
+#pragma unroll
+      for (int i = 0; i < 32; ++i) o[c0 + i] = fmaf(o[c0 + i], alpha, __uint_as_float(r[i]));
+    }
+    tc_fence_before_sync();
+  }
+
+  if (ok && tid < rows_valid) {
+    const float inv = 1.0f / l_run;
+    __nv_bfloat16* dst = p.out + (((long long)b * p.T + q0 + tid) * p.Hq + h) * D;
+#pragma unroll
+    for (int c = 0; c < D / 8; ++c) {
+      uint4 v;
+      uint32_t* w = reinterpret_cast<uint32_t*>(&v);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const uint32_t lo = __bfloat16_as_ushort(__float2bfloat16_rn(o[c * 8 + 2 * i] * inv));
+        const uint32_t hi = __bfloat16_as_ushort(__float2bfloat16_rn(o[c * 8 + 2 * i + 1] * inv));
+        w[i] = lo | (hi << 16);
+      }
+      *reinterpret_cast<uint4*>(dst + c * 8) = v;
+    }
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, SM::kTmemCols);
+  }
+}
+
+static int make_cache_tmap_pf(const Ctx* ctx, CUtensorMap* map, const void* cache, int64_t B, int64_t max_len,
+                              int64_t Hkv, int64_t D) {
+  const uint64_t dims[4] = {(uint64_t)D, (uint64_t)Hkv, (uint64_t)max_len, (uint64_t)B};
+  const uint64_t strides[3] = {(uint64_t)D * 2, (uint64_t)Hkv * D * 2, (uint64_t)max_len * Hkv * D * 2};
+  const uint32_t box[4] = {64, 1, (uint32_t)kPfTile, 1};
+  return make_tmap_4d(ctx, map, cache, 2, dims, strides, box);
+}
+
+}  // namespace xaxb
+
+using namespace xaxb;
+
+extern "C" int xaxb_attn_prefill(xaxb_ctx* ctx_, void* stream, const void* q_rot_bf16, const void* k_cache_bf16,
+                                 const void* v_cache_bf16, const int32_t* positions, int64_t B, int64_t T, int64_t Hq,
+                                 int64_t Hkv, int64_t D, int64_t max_len, float softmax_scale, void* out_bf16) {
+  if (!ctx_ || !q_rot_bf16 || !k_cache_bf16 || !v_cache_bf16 || !positions || !out_bf16 || B <= 0 || T <= 0 ||
+      Hq <= 0 || Hkv <= 0 || max_len <= 0) {
+    set_last_error("attn_prefill: null pointer or non-positive shape");
+    return XAXB_BAD_ARGUMENT;
+  }
+  if (Hq % Hkv != 0 || (D != 128 && D != 64) || Hq > 65535 || B > 65535) {
+    set_last_error("attn_prefill: needs head_dim 64 or 128 and Hq a multiple of Hkv");
+    return XAXB_UNSUPPORTED;
+  }
+  if ((reinterpret_cast<uintptr_t>(q_rot_bf16) | reinterpret_cast<uintptr_t>(out_bf16)) & 15) return XAXB_BAD_ARGUMENT;
+  const Ctx* ctx = reinterpret_cast<const Ctx*>(ctx_);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  CUtensorMap tk, tv;
+  int rc = make_cache_tmap_pf(ctx, &tk, k_cache_bf16, B, max_len, Hkv, D);
+  if (rc) return rc;
+  rc = make_cache_tmap_pf(ctx, &tv, v_cache_bf16, B, max_len, Hkv, D);
+  if (rc) return rc;
+  PrefillParams p;
+  p.q = static_cast<const __nv_bfloat16*>(q_rot_bf16);
+  p.out = static_cast<__nv_bfloat16*>(out_bf16);
+  p.positions = positions;
+  p.T = (int)T, p.Hq = (int)Hq, p.Hkv = (int)Hkv;
+  p.sm_scale = softmax_scale;
+  p.d_status = ctx->d_status;
+  dim3 grid((unsigned)((T + kPfTile - 1) / kPfTile), (unsigned)Hq, (unsigned)B);
+  if (D == 128) {
+    static bool set128 = false;
+    if (!set128) {
+      cudaFuncSetAttribute(attn_prefill_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                           PrefillSmem<128>::kBytes);
+      set128 = true;
+    }
+    attn_prefill_kernel<128><<<grid, 128, PrefillSmem<128>::kBytes, s>>>(tk, tv, p);
+  } else {
+    static bool set64 = false;
+    if (!set64) {
+      cudaFuncSetAttribute(attn_prefill_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                           PrefillSmem<64>::kBytes);
+      set64 = true;
+    }
+    attn_prefill_kernel<64><<<grid, 128, PrefillSmem<64>::kBytes, s>>>(tk, tv, p);
+  }
+  return check_launch("attn_prefill_kernel");
+}

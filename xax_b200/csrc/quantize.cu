@@ -1,0 +1,226 @@
+// Kernel 1: fused amax reduce, scale computation and e4m3 cast.
+//
+// Bandwidth kernels: 128-bit loads (8 bf16), 64-bit stores (8 e4m3), warp-shuffle
+// reductions.  The arithmetic mirrors the reference's bf16 op sequence so the bytes match:
+// the scale is a bf16 value, the product x * scale is rounded to bf16, clipped to +-448
+// and only then converted to e4m3 (round to nearest even).
+#include "common.cuh"
+#include "quant_device.cuh"
+
+namespace xaxb {
+
+// ---- per-row current scaling: one CTA per row, the row is swept twice (the second sweep
+// hits L1/L2), so HBM sees one read of x and one write of q. ------------------------------
+__global__ void __launch_bounds__(256) quantize_rows_kernel(const uint4* __restrict__ x, int64_t vec_per_row,
+                                                            uint2* __restrict__ q, float* __restrict__ scale,
+                                                            float* __restrict__ inv_scale, float* __restrict__ amax) {
+  const int64_t row = blockIdx.x;
+  const uint4* xr = x + row * vec_per_row;
+  uint32_t m = 0;
+  for (int64_t i = threadIdx.x; i < vec_per_row; i += blockDim.x) m = absmax_bits8(m, __ldg(xr + i));
+  const uint32_t row_bits = block_max_u32(m);
+  const float a = bf16_bits_to_float(row_bits);
+  const float s = current_scale_from_amax(a);
+  uint2* qr = q + row * vec_per_row;
+  for (int64_t i = threadIdx.x; i < vec_per_row; i += blockDim.x) qr[i] = quantize8(__ldg(xr + i), s);
+  if (threadIdx.x == 0) {
+    scale[row] = s;
+    inv_scale[row] = 1.0f / s;
+    amax[row] = a;
+  }
+}
+
+// ---- per-group current scaling, pass 1: amax of each group of rows -------------------------
+__global__ void __launch_bounds__(256) group_amax_kernel(const uint4* __restrict__ x, int64_t vec_per_group,
+                                                         unsigned int* __restrict__ amax_bits) {
+  const int64_t g = blockIdx.y;
+  const uint4* xg = x + g * vec_per_group;
+  uint32_t m = 0;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < vec_per_group;
+       i += (int64_t)gridDim.x * blockDim.x)
+    m = absmax_bits8(m, __ldg(xg + i));
+  const uint32_t r = block_max_u32(m);
+  // bf16 magnitude bits widened to float bits: order-preserving, NaN stays the largest.
+  if (threadIdx.x == 0) atomicMax(amax_bits + g, r << 16);
+}
+
+// ---- pass 2: scale from the group amax, cast ------------------------------------------------
+__global__ void __launch_bounds__(256) group_cast_kernel(const uint4* __restrict__ x, int64_t vec_per_group,
+                                                         int64_t group_rows, const float* __restrict__ amax,
+                                                         uint2* __restrict__ q, float* __restrict__ scale,
+                                                         float* __restrict__ inv_scale) {
+  const int64_t g = blockIdx.y;
+  const float s = current_scale_from_amax(amax[g]);
+  const uint4* xg = x + g * vec_per_group;
+  uint2* qg = q + g * vec_per_group;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < vec_per_group;
+       i += (int64_t)gridDim.x * blockDim.x)
+    qg[i] = quantize8(__ldg(xg + i), s);
+  if (blockIdx.x == 0) {
+    for (int64_t r = threadIdx.x; r < group_rows; r += blockDim.x) {
+      scale[g * group_rows + r] = s;
+      inv_scale[g * group_rows + r] = 1.0f / s;
+    }
+  }
+}
+
+// ---- delayed scaling: cast with the incoming scale while reducing max|x| -------------------
+__global__ void __launch_bounds__(256) delayed_cast_kernel(const uint4* __restrict__ x, int64_t n_vec,
+                                                           const float* __restrict__ scale_in, uint2* __restrict__ q,
+                                                           unsigned int* __restrict__ amax_bits) {
+  const float s = bf16_round(*scale_in);
+  uint32_t m = 0;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n_vec; i += (int64_t)gridDim.x * blockDim.x) {
+    const uint4 v = __ldg(x + i);
+    m = absmax_bits8(m, v);
+    if (q) q[i] = quantize8(v, s);
+  }
+  const uint32_t r = block_max_u32(m);
+  if (threadIdx.x == 0) atomicMax(amax_bits, r << 16);
+}
+
+__device__ __forceinline__ float nan_max(float a, float b) { return (a != a) ? a : ((b != b) ? b : fmaxf(a, b)); }
+
+// history_out = roll(history_in, -1) with slot 0 <- amax; scale_out from max(history_out).
+// One CTA; the history is staged in shared memory so in and out may alias.
+__global__ void __launch_bounds__(256) delayed_state_kernel(const float* __restrict__ amax,
+                                                            const float* __restrict__ scale_in,
+                                                            const float* history_in, int history_len,
+                                                            float* history_out, float* __restrict__ scale_out,
+                                                            float* __restrict__ inv_scale_out) {
+  extern __shared__ float hist[];
+  __shared__ float warp_max[8];
+  for (int i = threadIdx.x; i < history_len; i += blockDim.x) {
+    const int src = (i + 1 == history_len) ? 0 : i + 1;
+    hist[i] = (i == 0) ? *amax : history_in[src];
+  }
+  __syncthreads();
+  float m = -INFINITY;
+  for (int i = threadIdx.x; i < history_len; i += blockDim.x) {
+    history_out[i] = hist[i];
+    m = nan_max(m, hist[i]);
+  }
+  for (int o = 16; o > 0; o >>= 1) m = nan_max(m, __shfl_xor_sync(0xffffffffu, m, o));
+  if ((threadIdx.x & 31) == 0) warp_max[threadIdx.x >> 5] = m;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (int w = 1; w < (int)(blockDim.x >> 5); ++w) m = nan_max(m, warp_max[w]);
+    const float old = *scale_in;
+    float sf = 448.0f / m;  // float32: the bf16 constant promotes against the float32 history
+    sf = (m > 0.0f) ? sf : old;
+    sf = isfinite(m) ? sf : old;
+    *scale_out = sf;
+    if (inv_scale_out) *inv_scale_out = 1.0f / bf16_round(old);
+  }
+}
+
+static int grid_for(int64_t n_vec, int num_sms, int64_t cap_per_group = 0) {
+  int64_t blocks = (n_vec + 255) / 256;
+  int64_t limit = cap_per_group > 0 ? cap_per_group : (int64_t)num_sms * 8;
+  if (blocks > limit) blocks = limit;
+  if (blocks < 1) blocks = 1;
+  return (int)blocks;
+}
+
+}  // namespace xaxb
+
+using namespace xaxb;
+
+static int check_quant_args(const void* x, int64_t rows, int64_t cols) {
+  if (!x || rows <= 0 || cols <= 0) {
+    set_last_error("quantize: null input or non-positive shape (%lld x %lld)", (long long)rows, (long long)cols);
+    return XAXB_BAD_ARGUMENT;
+  }
+  if (cols % 8 != 0 || (reinterpret_cast<uintptr_t>(x) & 15)) {
+    set_last_error("quantize: cols (%lld) must be a multiple of 8 and x 16-byte aligned", (long long)cols);
+    return XAXB_BAD_ARGUMENT;
+  }
+  return XAXB_OK;
+}
+
+extern "C" {
+
+int xaxb_quantize_current(xaxb_ctx* ctx, void* stream, const void* x_bf16, int64_t rows, int64_t cols,
+                          int64_t group_rows, void* q_e4m3, float* scale, float* inv_scale, float* amax) {
+  if (!ctx || !q_e4m3 || !scale || !inv_scale || !amax) return XAXB_BAD_ARGUMENT;
+  int rc = check_quant_args(x_bf16, rows, cols);
+  if (rc) return rc;
+  if (group_rows <= 0 || rows % group_rows != 0 || (reinterpret_cast<uintptr_t>(q_e4m3) & 7)) {
+    set_last_error("quantize_current: rows (%lld) must be a multiple of group_rows (%lld), q 8-byte aligned",
+                   (long long)rows, (long long)group_rows);
+    return XAXB_BAD_ARGUMENT;
+  }
+  const Ctx* c = reinterpret_cast<const Ctx*>(ctx);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const uint4* x = static_cast<const uint4*>(x_bf16);
+  uint2* q = static_cast<uint2*>(q_e4m3);
+  if (group_rows == 1) {
+    const int64_t vec = cols / 8;
+    int threads = (int)((vec + 31) / 32 * 32);
+    if (threads > 256) threads = 256;
+    quantize_rows_kernel<<<(unsigned)rows, threads, 0, s>>>(x, vec, q, scale, inv_scale, amax);
+    return check_launch("quantize_rows_kernel");
+  }
+  const int64_t groups = rows / group_rows;
+  const int64_t vec_per_group = group_rows * cols / 8;
+  if (groups > 65535) {
+    set_last_error("quantize_current: more than 65535 multi-row groups");
+    return XAXB_UNSUPPORTED;
+  }
+  cudaMemsetAsync(amax, 0, groups * sizeof(float), s);
+  int64_t cap = ((int64_t)c->num_sms * 8 + groups - 1) / groups;
+  dim3 grid(grid_for(vec_per_group, c->num_sms, cap), (unsigned)groups);
+  group_amax_kernel<<<grid, 256, 0, s>>>(x, vec_per_group, reinterpret_cast<unsigned int*>(amax));
+  rc = check_launch("group_amax_kernel");
+  if (rc) return rc;
+  group_cast_kernel<<<grid, 256, 0, s>>>(x, vec_per_group, group_rows, amax, q, scale, inv_scale);
+  return check_launch("group_cast_kernel");
+}
+
+int xaxb_quantize_with_amax(xaxb_ctx* ctx, void* stream, const void* x_bf16, int64_t rows, int64_t cols,
+                            int64_t group_rows, const float* group_amax, void* q_e4m3, float* scale,
+                            float* inv_scale) {
+  if (!ctx || !q_e4m3 || !scale || !inv_scale || !group_amax) return XAXB_BAD_ARGUMENT;
+  int rc = check_quant_args(x_bf16, rows, cols);
+  if (rc) return rc;
+  if (group_rows <= 0 || rows % group_rows != 0 || rows / group_rows > 65535) {
+    set_last_error("quantize_with_amax: bad grouping rows=%lld group_rows=%lld", (long long)rows,
+                   (long long)group_rows);
+    return XAXB_BAD_ARGUMENT;
+  }
+  const Ctx* c = reinterpret_cast<const Ctx*>(ctx);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const int64_t groups = rows / group_rows;
+  const int64_t vec_per_group = group_rows * cols / 8;
+  int64_t cap = ((int64_t)c->num_sms * 8 + groups - 1) / groups;
+  dim3 grid(grid_for(vec_per_group, c->num_sms, cap), (unsigned)groups);
+  group_cast_kernel<<<grid, 256, 0, s>>>(static_cast<const uint4*>(x_bf16), vec_per_group, group_rows, group_amax,
+                                         static_cast<uint2*>(q_e4m3), scale, inv_scale);
+  return check_launch("group_cast_kernel");
+}
+
+int xaxb_quantize_delayed(xaxb_ctx* ctx, void* stream, const void* x_bf16, int64_t rows, int64_t cols,
+                          const float* scale_in, const float* history_in, int history_len, void* q_e4m3,
+                          float* history_out, float* scale_out, float* inv_scale_out, float* amax_scratch) {
+  if (!ctx || !scale_in || !history_in || !history_out || !scale_out || !amax_scratch) return XAXB_BAD_ARGUMENT;
+  int rc = check_quant_args(x_bf16, rows, cols);
+  if (rc) return rc;
+  if (history_len <= 0 || history_len > 8192) {
+    set_last_error("quantize_delayed: history_len %d outside [1, 8192]", history_len);
+    return XAXB_BAD_ARGUMENT;
+  }
+  const Ctx* c = reinterpret_cast<const Ctx*>(ctx);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const int64_t n_vec = rows * cols / 8;
+  cudaMemsetAsync(amax_scratch, 0, sizeof(float), s);
+  delayed_cast_kernel<<<grid_for(n_vec, c->num_sms), 256, 0, s>>>(static_cast<const uint4*>(x_bf16), n_vec, scale_in,
+                                                                  static_cast<uint2*>(q_e4m3),
+                                                                  reinterpret_cast<unsigned int*>(amax_scratch));
+  rc = check_launch("delayed_cast_kernel");
+  if (rc) return rc;
+  delayed_state_kernel<<<1, 256, history_len * sizeof(float), s>>>(amax_scratch, scale_in, history_in, history_len,
+                                                                   history_out, scale_out, inv_scale_out);
+  return check_launch("delayed_state_kernel");
+}
+
+}  // extern "C"

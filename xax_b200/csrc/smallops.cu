@@ -1,0 +1,425 @@
+// Small bandwidth kernels on the path (RMSNorm, SiLU*up, embedding gather, arg-max, RoPE +
+// KV-cache append) and the CUDA-core check kernels.  bf16 intermediates are rounded where
+// the reference's bf16 ops round, so outputs match the oracle except for float32 summation
+// order.
+#include "common.cuh"
+#include "quant_device.cuh"
+
+namespace xaxb {
+
+// ---------------------------------------------------------------------------------------
+// RMSNorm: x / sqrt(mean(x^2) + eps) * w, one CTA per row, optional fused per-token cast.
+
+__device__ __forceinline__ void rmsnorm8(const uint4 xv, const uint4 wv, float n, float (&y)[8]) {
+  float x[8], w[8];
+  unpack8(xv, x);
+  unpack8(wv, w);
+#pragma unroll
+  for (int j = 0; j < 8; ++j) y[j] = bf16_round(bf16_round(x[j] / n) * w[j]);
+}
+
+__global__ void __launch_bounds__(256) rmsnorm_kernel(const uint4* __restrict__ x, const uint4* __restrict__ w,
+                                                      float eps, int64_t vec, uint4* __restrict__ y,
+                                                      uint2* __restrict__ q, float* __restrict__ scale,
+                                                      float* __restrict__ inv_scale,
+                                                      unsigned int* __restrict__ group_amax, int64_t group_rows) {
+  const int64_t row = blockIdx.x;
+  const uint4* xr = x + row * vec;
+  float acc = 0.0f;
+  for (int64_t i = threadIdx.x; i < vec; i += blockDim.x) {
+    float f[8];
+    unpack8(__ldg(xr + i), f);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc += bf16_round(f[j] * f[j]);
+  }
+  const float total = block_sum_f32(acc);
+  const float mean = bf16_round(total / (float)(vec * 8));
+  const float n = bf16_round(sqrtf(bf16_round(mean + bf16_round(eps))));
+
+  uint32_t m = 0;
+  for (int64_t i = threadIdx.x; i < vec; i += blockDim.x) {
+    float yv[8];
+    rmsnorm8(__ldg(xr + i), __ldg(w + i), n, yv);
+    if (y) y[row * vec + i] = pack8(yv);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) m = max(m, mag_bits16(yv[j]));
+  }
+  if (!q && !group_amax) return;
+  const uint32_t row_bits = block_max_u32(m);
+  if (group_amax && threadIdx.x == 0) atomicMax(group_amax + row / group_rows, row_bits << 16);
+  if (!q) return;
+  const float s = current_scale_from_amax(bf16_bits_to_float(row_bits));
+  for (int64_t i = threadIdx.x; i < vec; i += blockDim.x) {
+    float yv[8];
+    rmsnorm8(__ldg(xr + i), __ldg(w + i), n, yv);
+    q[row * vec + i] = quantize8f(yv, s);
+  }
+  if (threadIdx.x == 0) {
+    scale[row] = s;
+    inv_scale[row] = 1.0f / s;
+  }
+}
+
+// ---------------------------------------------------------------------------------------
+// h = bf16(silu(g) * u), silu(g) = bf16(g * bf16(sigmoid(g)))
+
+__device__ __forceinline__ void silu_mul8(const uint4 gv, const uint4 uv, float (&h)[8]) {
+  float g[8], u[8];
+  unpack8(gv, g);
+  unpack8(uv, u);
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    const float sig = bf16_round(1.0f / (1.0f + expf(-g[j])));
+    h[j] = bf16_round(bf16_round(g[j] * sig) * u[j]);
+  }
+}
+
+__global__ void __launch_bounds__(256) silu_mul_kernel(const uint4* __restrict__ gate, const uint4* __restrict__ up,
+                                                       int64_t ld_vec, int64_t vec, uint4* __restrict__ h,
+                                                       uint2* __restrict__ q, float* __restrict__ scale,
+                                                       float* __restrict__ inv_scale,
+                                                       unsigned int* __restrict__ group_amax, int64_t group_rows) {
+  const int64_t row = blockIdx.x;
+  const uint4* gr = gate + row * ld_vec;
+  const uint4* ur = up + row * ld_vec;
+  uint32_t m = 0;
+  for (int64_t i = threadIdx.x; i < vec; i += blockDim.x) {
+    float hv[8];
+    silu_mul8(__ldg(gr + i), __ldg(ur + i), hv);
+    if (h) h[row * vec + i] = pack8(hv);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) m = max(m, mag_bits16(hv[j]));
+  }
+  if (!q && !group_amax) return;
+  const uint32_t row_bits = block_max_u32(m);
+  if (group_amax && threadIdx.x == 0) atomicMax(group_amax + row / group_rows, row_bits << 16);
+  if (!q) return;
+  const float s = current_scale_from_amax(bf16_bits_to_float(row_bits));
+  for (int64_t i = threadIdx.x; i < vec; i += blockDim.x) {
+    float hv[8];
+    silu_mul8(__ldg(gr + i), __ldg(ur + i), hv);
+    q[row * vec + i] = quantize8f(hv, s);
+  }
+  if (threadIdx.x == 0) {
+    scale[row] = s;
+    inv_scale[row] = 1.0f / s;
+  }
+}
+
+// ---------------------------------------------------------------------------------------
+
+__global__ void __launch_bounds__(256) embed_kernel(const int32_t* __restrict__ tokens, const uint4* __restrict__ table,
+                                                    int64_t vocab, int64_t vec, uint4* __restrict__ x, int* d_status) {
+  const int64_t i = blockIdx.x;
+  int64_t t = tokens[i];
+  if (t < 0 || t >= vocab) {  // the reference's gather clamps; report and clamp
+    if (threadIdx.x == 0) atomicCAS(d_status, 0, XAXB_BAD_ARGUMENT * 1000 + 31);
+    t = t < 0 ? 0 : vocab - 1;
+  }
+  for (int64_t j = threadIdx.x; j < vec; j += blockDim.x) x[i * vec + j] = __ldg(table + t * vec + j);
+}
+
+// arg-max with jnp.argmax semantics: first index of the maximum, NaN counts as the maximum.
+__device__ __forceinline__ bool better(float v, int i, float bv, int bi) {
+  const bool vn = v != v, bn = bv != bv;
+  if (vn != bn) return vn;
+  if (vn) return i < bi;
+  return v > bv || (v == bv && i < bi);
+}
+
+__global__ void __launch_bounds__(1024) argmax_kernel(const __nv_bfloat16* __restrict__ logits, int64_t vocab,
+                                                      int64_t ld, int32_t* __restrict__ out) {
+  const int64_t row = blockIdx.x;
+  const __nv_bfloat16* lr = logits + row * ld;
+  float bv = -INFINITY;
+  int bi = 0x7FFFFFFF;
+  const int64_t vec = ((reinterpret_cast<uintptr_t>(lr) & 15) == 0) ? vocab / 8 : 0;
+  for (int64_t i = threadIdx.x; i < vec; i += blockDim.x) {
+    float f[8];
+    unpack8(__ldg(reinterpret_cast<const uint4*>(lr) + i), f);
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+      if (better(f[j], (int)(i * 8 + j), bv, bi)) bv = f[j], bi = (int)(i * 8 + j);
+  }
+  for (int64_t i = vec * 8 + threadIdx.x; i < vocab; i += blockDim.x) {
+    const float v = __bfloat162float(lr[i]);
+    if (better(v, (int)i, bv, bi)) bv = v, bi = (int)i;
+  }
+  __shared__ float sv[32];
+  __shared__ int si[32];
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+    if (better(ov, oi, bv, bi)) bv = ov, bi = oi;
+  }
+  if ((threadIdx.x & 31) == 0) sv[threadIdx.x >> 5] = bv, si[threadIdx.x >> 5] = bi;
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    const int nw = (blockDim.x + 31) >> 5;
+    bv = threadIdx.x < nw ? sv[threadIdx.x] : -INFINITY;
+    bi = threadIdx.x < nw ? si[threadIdx.x] : 0x7FFFFFFF;
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+      if (better(ov, oi, bv, bi)) bv = ov, bi = oi;
+    }
+    if (threadIdx.x == 0) out[row] = bi;
+  }
+}
+
+// ---------------------------------------------------------------------------------------
+// RoPE ("concatenated" halves) + cache append.  Grid (B*T, Hq + 2*Hkv); D/2 threads: thread i
+// owns the pair (i, i + D/2).  out1 = bf16(bf16(x1*c) - bf16(x2*s)), out2 = bf16(bf16(x2*c) + bf16(x1*s)).
+
+__global__ void kv_append_rope_kernel(const __nv_bfloat16* __restrict__ qkv, int64_t ld, int T, int Hq, int Hkv, int D,
+                                      const int32_t* __restrict__ positions, const __nv_bfloat16* __restrict__ cos_t,
+                                      const __nv_bfloat16* __restrict__ sin_t, int64_t table_len,
+                                      __nv_bfloat16* __restrict__ q_rot, __nv_bfloat16* __restrict__ k_cache,
+                                      __nv_bfloat16* __restrict__ v_cache, int64_t max_len, int store_rotated_k,
+                                      int* d_status) {
+  const int64_t bt = blockIdx.x;
+  const int b = (int)(bt / T), t = (int)(bt % T);
+  const int head = blockIdx.y;
+  const int i = threadIdx.x, half = D / 2;
+  const int64_t pos = (int64_t)positions[b] + t;
+  if (pos >= max_len || pos >= table_len || pos < 0) {
+    if (i == 0) atomicCAS(d_status, 0, XAXB_CACHE_OVERFLOW * 1000 + 41);
+    return;
+  }
+  const __nv_bfloat16* src = qkv + bt * ld + (int64_t)head * D;
+  const float x1 = __bfloat162float(src[i]), x2 = __bfloat162float(src[i + half]);
+  const float c = __bfloat162float(cos_t[pos * half + i]), s = __bfloat162float(sin_t[pos * half + i]);
+  const float r1 = bf16_round(bf16_round(x1 * c) - bf16_round(x2 * s));
+  const float r2 = bf16_round(bf16_round(x2 * c) + bf16_round(x1 * s));
+  if (head < Hq) {
+    __nv_bfloat16* dst = q_rot + (bt * Hq + head) * D;
+    dst[i] = __float2bfloat16_rn(r1);
+    dst[i + half] = __float2bfloat16_rn(r2);
+  } else if (head < Hq + Hkv) {
+    __nv_bfloat16* dst = k_cache + (((int64_t)b * max_len + pos) * Hkv + (head - Hq)) * D;
+    dst[i] = store_rotated_k ? __float2bfloat16_rn(r1) : src[i];
+    dst[i + half] = store_rotated_k ? __float2bfloat16_rn(r2) : src[i + half];
+  } else {
+    __nv_bfloat16* dst = v_cache + (((int64_t)b * max_len + pos) * Hkv + (head - Hq - Hkv)) * D;
+    dst[i] = src[i];
+    dst[i + half] = src[i + half];
+  }
+}
+
+__global__ void advance_positions_kernel(int32_t* positions, int B, int32_t delta) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < B) positions[i] += delta;
+}
+
+// ---------------------------------------------------------------------------------------
+// Check kernels (CUDA cores, reference order of operations).
+
+__global__ void gemm_fp8_check_kernel(const __nv_fp8_storage_t* __restrict__ a, int64_t lda,
+                                      const __nv_fp8_storage_t* __restrict__ b, int64_t ldb, int64_t M, int64_t N,
+                                      int64_t K, const float* row_mul, int rms, const float* col_mul, int cms,
+                                      const __nv_bfloat16* bias, const __nv_bfloat16* residual, int64_t ldr,
+                                      __nv_bfloat16* out, int64_t ldo) {
+  const int64_t n = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const int64_t m = blockIdx.y;
+  if (n >= N || m >= M) return;
+  float acc = 0.0f;
+  for (int64_t k = 0; k < K; ++k) {
+    const float av = __half2float(__half(__nv_cvt_fp8_to_halfraw(a[m * lda + k], __NV_E4M3)));
+    const float bv = __half2float(__half(__nv_cvt_fp8_to_halfraw(b[n * ldb + k], __NV_E4M3)));
+    acc = fmaf(av, bv, acc);
+  }
+  float v = acc * (row_mul ? row_mul[m * rms] : 1.0f) * (col_mul ? col_mul[n * cms] : 1.0f);
+  if (bias) v += __bfloat162float(bias[n]);
+  if (residual) v += __bfloat162float(residual[m * ldr + n]);
+  out[m * ldo + n] = __float2bfloat16_rn(v);
+}
+
+// One CTA per (query, head): logits to shared memory, float32 softmax, probabilities
+// rounded to bf16, P.V accumulated in float32.
+__global__ void __launch_bounds__(128) attn_check_kernel(const __nv_bfloat16* __restrict__ q,
+                                                         const __nv_bfloat16* __restrict__ kc,
+                                                         const __nv_bfloat16* __restrict__ vc,
+                                                         const int32_t* __restrict__ positions, int T, int Hq, int Hkv,
+                                                         int D, int64_t max_len, float sm_scale,
+                                                         __nv_bfloat16* __restrict__ out) {
+  extern __shared__ float logits[];
+  __shared__ float red[4];
+  const int h = blockIdx.x;
+  const int64_t bt = blockIdx.y;
+  const int b = (int)(bt / T), t = (int)(bt % T);
+  const int g = h / (Hq / Hkv);
+  const int L = positions[b] + t + 1;
+  const __nv_bfloat16* qv = q + (bt * Hq + h) * D;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  for (int j = warp; j < L; j += 4) {
+    const __nv_bfloat16* kr = kc + (((int64_t)b * max_len + j) * Hkv + g) * D;
+    float p = 0.0f;
+    for (int d = lane; d < D; d += 32) p = fmaf(__bfloat162float(qv[d]), __bfloat162float(kr[d]), p);
+    for (int o = 16; o > 0; o >>= 1) p += __shfl_xor_sync(0xffffffffu, p, o);
+    if (lane == 0) logits[j] = p * sm_scale;
+  }
+  __syncthreads();
+  float m = -INFINITY;
+  for (int j = threadIdx.x; j < L; j += blockDim.x) m = fmaxf(m, logits[j]);
+  for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+  if (lane == 0) red[warp] = m;
+  __syncthreads();
+  m = fmaxf(fmaxf(red[0], red[1]), fmaxf(red[2], red[3]));
+  __syncthreads();
+  float sum = 0.0f;
+  for (int j = threadIdx.x; j < L; j += blockDim.x) {
+    const float e = expf(logits[j] - m);
+    logits[j] = e;
+    sum += e;
+  }
+  for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+  if (lane == 0) red[warp] = sum;
+  __syncthreads();
+  sum = red[0] + red[1] + red[2] + red[3];
+  for (int d = threadIdx.x; d < D; d += blockDim.x) {
+    float acc = 0.0f;
+    for (int j = 0; j < L; ++j) {
+      const float p = bf16_round(logits[j] / sum);
+      acc = fmaf(p, __bfloat162float(vc[(((int64_t)b * max_len + j) * Hkv + g) * D + d]), acc);
+    }
+    out[(bt * Hq + h) * D + d] = __float2bfloat16_rn(acc);
+  }
+}
+
+}  // namespace xaxb
+
+using namespace xaxb;
+
+static int row_threads(int64_t vec) {
+  int t = (int)((vec + 31) / 32 * 32);
+  return t > 256 ? 256 : (t < 32 ? 32 : t);
+}
+
+extern "C" {
+
+int xaxb_rmsnorm(xaxb_ctx* ctx, void* stream, const void* x_bf16, const void* weight_bf16, float eps, int64_t rows,
+                 int64_t dim, void* y_bf16, void* q_e4m3, float* scale, float* inv_scale, float* group_amax,
+                 int64_t group_rows) {
+  if (!ctx || !x_bf16 || !weight_bf16 || rows <= 0 || dim <= 0 || dim % 8 != 0) {
+    set_last_error("rmsnorm: null pointer, or dim (%lld) not a positive multiple of 8", (long long)dim);
+    return XAXB_BAD_ARGUMENT;
+  }
+  if (q_e4m3 && (!scale || !inv_scale)) return XAXB_BAD_ARGUMENT;
+  if (group_amax && group_rows <= 0) return XAXB_BAD_ARGUMENT;
+  if ((reinterpret_cast<uintptr_t>(x_bf16) | reinterpret_cast<uintptr_t>(weight_bf16) |
+       reinterpret_cast<uintptr_t>(y_bf16)) & 15) {
+    set_last_error("rmsnorm: pointers must be 16-byte aligned");
+    return XAXB_BAD_ARGUMENT;
+  }
+  const int64_t vec = dim / 8;
+  rmsnorm_kernel<<<(unsigned)rows, row_threads(vec), 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const uint4*>(x_bf16), static_cast<const uint4*>(weight_bf16), eps, vec, static_cast<uint4*>(y_bf16),
+      static_cast<uint2*>(q_e4m3), scale, inv_scale, reinterpret_cast<unsigned int*>(group_amax),
+      group_rows > 0 ? group_rows : 1);
+  return check_launch("rmsnorm_kernel");
+}
+
+int xaxb_silu_mul(xaxb_ctx* ctx, void* stream, const void* gate_bf16, const void* up_bf16, int64_t ld, int64_t rows,
+                  int64_t dim, void* h_bf16, void* q_e4m3, float* scale, float* inv_scale, float* group_amax,
+                  int64_t group_rows) {
+  if (!ctx || !gate_bf16 || rows <= 0 || dim <= 0 || dim % 8 != 0 || ld % 8 != 0) {
+    set_last_error("silu_mul: null pointer, or dim/ld not positive multiples of 8");
+    return XAXB_BAD_ARGUMENT;
+  }
+  if (q_e4m3 && (!scale || !inv_scale)) return XAXB_BAD_ARGUMENT;
+  if (group_amax && group_rows <= 0) return XAXB_BAD_ARGUMENT;
+  const uint4* gate = static_cast<const uint4*>(gate_bf16);
+  const uint4* up = up_bf16 ? static_cast<const uint4*>(up_bf16) : gate + dim / 8;
+  if ((reinterpret_cast<uintptr_t>(gate) | reinterpret_cast<uintptr_t>(up) | reinterpret_cast<uintptr_t>(h_bf16)) &
+      15) {
+    set_last_error("silu_mul: pointers must be 16-byte aligned");
+    return XAXB_BAD_ARGUMENT;
+  }
+  const int64_t vec = dim / 8;
+  silu_mul_kernel<<<(unsigned)rows, row_threads(vec), 0, static_cast<cudaStream_t>(stream)>>>(
+      gate, up, ld / 8, vec, static_cast<uint4*>(h_bf16), static_cast<uint2*>(q_e4m3), scale, inv_scale,
+      reinterpret_cast<unsigned int*>(group_amax), group_rows > 0 ? group_rows : 1);
+  return check_launch("silu_mul_kernel");
+}
+
+int xaxb_embed(xaxb_ctx* ctx, void* stream, const int32_t* tokens, int64_t n_tokens, const void* table_bf16,
+               int64_t vocab, int64_t dim, void* x_bf16) {
+  if (!ctx || !tokens || !table_bf16 || !x_bf16 || n_tokens <= 0 || dim <= 0 || dim % 8 != 0 || vocab <= 0)
+    return XAXB_BAD_ARGUMENT;
+  Ctx* c = reinterpret_cast<Ctx*>(ctx);
+  embed_kernel<<<(unsigned)n_tokens, row_threads(dim / 8), 0, static_cast<cudaStream_t>(stream)>>>(
+      tokens, static_cast<const uint4*>(table_bf16), vocab, dim / 8, static_cast<uint4*>(x_bf16), c->d_status);
+  return check_launch("embed_kernel");
+}
+
+int xaxb_argmax(xaxb_ctx* ctx, void* stream, const void* logits_bf16, int64_t rows, int64_t vocab, int64_t ld,
+                int32_t* out) {
+  if (!ctx || !logits_bf16 || !out || rows <= 0 || vocab <= 0 || ld < vocab) return XAXB_BAD_ARGUMENT;
+  argmax_kernel<<<(unsigned)rows, 1024, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(logits_bf16), vocab, ld, out);
+  return check_launch("argmax_kernel");
+}
+
+int xaxb_kv_append_rope(xaxb_ctx* ctx, void* stream, const void* qkv_bf16, int64_t ld, int64_t B, int64_t T,
+                        int64_t Hq, int64_t Hkv, int64_t D, const int32_t* positions, const void* cos_bf16,
+                        const void* sin_bf16, int64_t table_len, void* q_rot_bf16, void* k_cache_bf16,
+                        void* v_cache_bf16, int64_t max_len, int store_rotated_k) {
+  if (!ctx || !qkv_bf16 || !positions || !cos_bf16 || !sin_bf16 || !q_rot_bf16 || !k_cache_bf16 || !v_cache_bf16 ||
+      B <= 0 || T <= 0 || Hq <= 0 || Hkv <= 0 || max_len <= 0)
+    return XAXB_BAD_ARGUMENT;
+  if (D % 2 != 0 || D < 2 || D > 2048 || ld < (Hq + 2 * Hkv) * D) {
+    set_last_error("kv_append_rope: head_dim %lld / ld %lld not supported", (long long)D, (long long)ld);
+    return XAXB_UNSUPPORTED;
+  }
+  if (Hq + 2 * Hkv > 65535) return XAXB_UNSUPPORTED;
+  Ctx* c = reinterpret_cast<Ctx*>(ctx);
+  dim3 grid((unsigned)(B * T), (unsigned)(Hq + 2 * Hkv));
+  kv_append_rope_kernel<<<grid, (unsigned)(D / 2), 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(qkv_bf16), ld, (int)T, (int)Hq, (int)Hkv, (int)D, positions,
+      static_cast<const __nv_bfloat16*>(cos_bf16), static_cast<const __nv_bfloat16*>(sin_bf16), table_len,
+      static_cast<__nv_bfloat16*>(q_rot_bf16), static_cast<__nv_bfloat16*>(k_cache_bf16),
+      static_cast<__nv_bfloat16*>(v_cache_bf16), max_len, store_rotated_k, c->d_status);
+  return check_launch("kv_append_rope_kernel");
+}
+
+int xaxb_advance_positions(xaxb_ctx* ctx, void* stream, int32_t* positions, int64_t B, int32_t delta) {
+  if (!ctx || !positions || B <= 0) return XAXB_BAD_ARGUMENT;
+  advance_positions_kernel<<<(unsigned)((B + 127) / 128), 128, 0, static_cast<cudaStream_t>(stream)>>>(positions,
+                                                                                                        (int)B, delta);
+  return check_launch("advance_positions_kernel");
+}
+
+int xaxb_gemm_fp8_check(xaxb_ctx* ctx, void* stream, const void* a_e4m3, int64_t lda, const void* b_e4m3,
+                        int64_t ldb, int64_t M, int64_t N, int64_t K, const float* row_mul, int row_mul_stride,
+                        const float* col_mul, int col_mul_stride, const void* bias_bf16, const void* residual_bf16,
+                        int64_t ldr, void* out_bf16, int64_t ldo) {
+  if (!ctx || !a_e4m3 || !b_e4m3 || !out_bf16 || M <= 0 || N <= 0 || K <= 0 || M > 65535) return XAXB_BAD_ARGUMENT;
+  dim3 grid((unsigned)((N + 127) / 128), (unsigned)M);
+  gemm_fp8_check_kernel<<<grid, 128, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_fp8_storage_t*>(a_e4m3), lda, static_cast<const __nv_fp8_storage_t*>(b_e4m3), ldb, M, N,
+      K, row_mul, row_mul_stride, col_mul, col_mul_stride, static_cast<const __nv_bfloat16*>(bias_bf16),
+      static_cast<const __nv_bfloat16*>(residual_bf16), ldr, static_cast<__nv_bfloat16*>(out_bf16), ldo);
+  return check_launch("gemm_fp8_check_kernel");
+}
+
+int xaxb_attn_check(xaxb_ctx* ctx, void* stream, const void* q_rot_bf16, const void* k_cache_bf16,
+                    const void* v_cache_bf16, const int32_t* positions, int64_t B, int64_t T, int64_t Hq, int64_t Hkv,
+                    int64_t D, int64_t max_len, float softmax_scale, void* out_bf16) {
+  if (!ctx || !q_rot_bf16 || !k_cache_bf16 || !v_cache_bf16 || !positions || !out_bf16 || B <= 0 || T <= 0 ||
+      Hq <= 0 || Hkv <= 0 || Hq % Hkv != 0 || B * T > 65535)
+    return XAXB_BAD_ARGUMENT;
+  const size_t smem = (size_t)max_len * sizeof(float);
+  if (smem > 200 * 1024) {
+    set_last_error("attn_check: max_len %lld too long for the check kernel", (long long)max_len);
+    return XAXB_UNSUPPORTED;
+  }
+  cudaFuncSetAttribute(attn_check_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  dim3 grid((unsigned)Hq, (unsigned)(B * T));
+  attn_check_kernel<<<grid, 128, smem, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(q_rot_bf16), static_cast<const __nv_bfloat16*>(k_cache_bf16),
+      static_cast<const __nv_bfloat16*>(v_cache_bf16), positions, (int)T, (int)Hq, (int)Hkv, (int)D, max_len,
+      softmax_scale, static_cast<__nv_bfloat16*>(out_bf16));
+  return check_launch("attn_check_kernel");
+}
+
+}  // extern "C"

@@ -1,0 +1,293 @@
+"""Functional layer over the C ABI: torch tensors in, torch tensors out.
+
+torch is used for device memory and streams only; every computation on the path is one of
+the library's sm_100a kernels.  All functions run on the current CUDA stream and do not
+synchronise.
+"""
+
+from __future__ import annotations
+
+import math
+
+import numpy as np
+import torch
+
+from . import _lib
+from ._lib import check, ptr
+
+E4M3 = torch.float8_e4m3fn
+BF16 = torch.bfloat16
+
+
+def _c():
+    return _lib.ctx(), _lib.stream_ptr(), _lib.load()
+
+
+def _req(t: torch.Tensor, dtype, name: str) -> torch.Tensor:
+    if not t.is_cuda:
+        raise ValueError(f"{name} must be a CUDA tensor (there is no CPU fallback)")
+    if t.dtype != dtype:
+        raise ValueError(f"{name} must be {dtype}, got {t.dtype}")
+    return t if t.is_contiguous() else t.contiguous()
+
+
+# ---------------------------------------------------------------------------------------
+# kernel 1
+
+
+def quantize_current(x: torch.Tensor, group_rows: int = 1):
+    """x[rows, cols] bf16 -> (q e4m3, scale[rows] f32, inv_scale[rows] f32, amax[groups] f32).
+
+    group_rows = 1: a scale per row (per token); group_rows = rows: one scale per tensor."""
+    x = _req(x, BF16, "x")
+    rows, cols = x.shape
+    ctx, st, lib = _c()
+    q = torch.empty((rows, cols), dtype=E4M3, device=x.device)
+    scale = torch.empty((rows,), dtype=torch.float32, device=x.device)
+    inv = torch.empty((rows,), dtype=torch.float32, device=x.device)
+    amax = torch.empty((rows // max(group_rows, 1),), dtype=torch.float32, device=x.device)
+    check(lib.xaxb_quantize_current(ctx, st, ptr(x), rows, cols, group_rows, ptr(q), ptr(scale), ptr(inv), ptr(amax)),
+          "quantize_current")
+    return q, scale, inv, amax
+
+
+def quantize_with_amax(x: torch.Tensor, group_amax: torch.Tensor, group_rows: int):
+    x = _req(x, BF16, "x")
+    rows, cols = x.shape
+    ctx, st, lib = _c()
+    q = torch.empty((rows, cols), dtype=E4M3, device=x.device)
+    scale = torch.empty((rows,), dtype=torch.float32, device=x.device)
+    inv = torch.empty((rows,), dtype=torch.float32, device=x.device)
+    check(lib.xaxb_quantize_with_amax(ctx, st, ptr(x), rows, cols, group_rows, ptr(group_amax), ptr(q), ptr(scale),
+                                      ptr(inv)), "quantize_with_amax")
+    return q, scale, inv
+
+
+def quantize_delayed(x: torch.Tensor, scale_in: torch.Tensor, history: torch.Tensor, *, cast: bool = True):
+    """Delayed scaling: returns (q or None, new_history, new_scale, inv_scale_used)."""
+    x = _req(x, BF16, "x")
+    x2 = x.reshape(-1, x.shape[-1])
+    rows, cols = x2.shape
+    scale_in = _req(scale_in, torch.float32, "scale_in")
+    history = _req(history, torch.float32, "history")
+    ctx, st, lib = _c()
+    q = torch.empty((rows, cols), dtype=E4M3, device=x.device) if cast else None
+    new_hist = torch.empty_like(history)
+    new_scale = torch.empty((), dtype=torch.float32, device=x.device)
+    inv = torch.empty((1,), dtype=torch.float32, device=x.device)
+    scratch = torch.empty((1,), dtype=torch.float32, device=x.device)
+    check(lib.xaxb_quantize_delayed(ctx, st, ptr(x2), rows, cols, ptr(scale_in), ptr(history), history.numel(), ptr(q),
+                                    ptr(new_hist), ptr(new_scale), ptr(inv), ptr(scratch)), "quantize_delayed")
+    return q, new_hist, new_scale, inv
+
+
+# ---------------------------------------------------------------------------------------
+# kernel 2
+
+
+def _mul_arg(m, n_expected: int, name: str):
+    if m is None:
+        return None, 0
+    if m.dtype != torch.float32 or not m.is_cuda:
+        raise ValueError(f"{name} must be a float32 CUDA tensor")
+    if m.numel() == 1:
+        return m, 0
+    if m.numel() != n_expected:
+        raise ValueError(f"{name} has {m.numel()} elements, expected 1 or {n_expected}")
+    return m.contiguous(), 1
+
+
+def _gemm(fn_name, a, b, row_mul, col_mul, bias, residual, out):
+    ctx, st, lib = _c()
+    M, K = a.shape
+    N, Kb = b.shape
+    if K != Kb:
+        raise ValueError(f"gemm: inner dimensions differ ({K} vs {Kb})")
+    if a.stride(1) != 1 or b.stride(1) != 1:
+        raise ValueError("gemm: operands must be K-contiguous")
+    if out is None:
+        out = torch.empty((M, N), dtype=BF16, device=a.device)
+    row_mul, rs = _mul_arg(row_mul, M, "row_mul")
+    col_mul, cs = _mul_arg(col_mul, N, "col_mul")
+    ldr = residual.stride(0) if residual is not None else 0
+    fn = getattr(lib, fn_name)
+    check(fn(ctx, st, ptr(a), a.stride(0), ptr(b), b.stride(0), M, N, K, ptr(row_mul), rs, ptr(col_mul), cs, ptr(bias),
+             ptr(residual), ldr, ptr(out), out.stride(0)), fn_name)
+    return out
+
+
+def gemm_fp8(a_q, b_q, row_mul=None, col_mul=None, bias=None, residual=None, out=None):
+    """bf16( (a_q @ b_q.T) * row_mul[:, None] * col_mul[None, :] + bias + residual )."""
+    if a_q.dtype != E4M3 or b_q.dtype != E4M3:
+        raise ValueError("gemm_fp8 needs float8_e4m3fn operands")
+    return _gemm("xaxb_gemm_fp8", a_q, b_q, row_mul, col_mul, bias, residual, out)
+
+
+def gemm_fp8_check(a_q, b_q, row_mul=None, col_mul=None, bias=None, residual=None, out=None):
+    return _gemm("xaxb_gemm_fp8_check", a_q, b_q, row_mul, col_mul, bias, residual, out)
+
+
+def gemm_bf16(a, b, row_mul=None, col_mul=None, bias=None, residual=None, out=None):
+    if a.dtype != BF16 or b.dtype != BF16:
+        raise ValueError("gemm_bf16 needs bfloat16 operands")
+    return _gemm("xaxb_gemm_bf16", a, b, row_mul, col_mul, bias, residual, out)
+
+
+# ---------------------------------------------------------------------------------------
+# small ops
+
+
+def rmsnorm(x, weight, eps, *, want_y=True, quantize=False, group_amax=None, group_rows=0):
+    """Returns (y or None, (q, scale, inv_scale) or None)."""
+    x = _req(x, BF16, "x")
+    weight = _req(weight, BF16, "weight")
+    rows, dim = x.shape
+    ctx, st, lib = _c()
+    y = torch.empty_like(x) if want_y else None
+    q = scale = inv = None
+    if quantize:
+        q = torch.empty((rows, dim), dtype=E4M3, device=x.device)
+        scale = torch.empty((rows,), dtype=torch.float32, device=x.device)
+        inv = torch.empty((rows,), dtype=torch.float32, device=x.device)
+    check(lib.xaxb_rmsnorm(ctx, st, ptr(x), ptr(weight), float(eps), rows, dim, ptr(y), ptr(q), ptr(scale), ptr(inv),
+                           ptr(group_amax), group_rows), "rmsnorm")
+    return y, ((q, scale, inv) if quantize else None)
+
+
+def silu_mul(gate_up, dim, *, want_h=True, quantize=False, group_amax=None, group_rows=0):
+    """gate_up[rows, 2*dim] bf16 (gate | up) -> (h or None, (q, scale, inv_scale) or None)."""
+    gate_up = _req(gate_up, BF16, "gate_up")
+    rows, ld = gate_up.shape
+    ctx, st, lib = _c()
+    h = torch.empty((rows, dim), dtype=BF16, device=gate_up.device) if want_h else None
+    q = scale = inv = None
+    if quantize:
+        q = torch.empty((rows, dim), dtype=E4M3, device=gate_up.device)
+        scale = torch.empty((rows,), dtype=torch.float32, device=gate_up.device)
+        inv = torch.empty((rows,), dtype=torch.float32, device=gate_up.device)
+    check(lib.xaxb_silu_mul(ctx, st, ptr(gate_up), None, ld, rows, dim, ptr(h), ptr(q), ptr(scale), ptr(inv),
+                            ptr(group_amax), group_rows), "silu_mul")
+    return h, ((q, scale, inv) if quantize else None)
+
+
+def embed(tokens, table):
+    table = _req(table, BF16, "table")
+    tokens = _req(tokens, torch.int32, "tokens").reshape(-1)
+    ctx, st, lib = _c()
+    x = torch.empty((tokens.numel(), table.shape[1]), dtype=BF16, device=table.device)
+    check(lib.xaxb_embed(ctx, st, ptr(tokens), tokens.numel(), ptr(table), table.shape[0], table.shape[1], ptr(x)),
+          "embed")
+    return x
+
+
+def argmax(logits, out=None):
+    logits = _req(logits, BF16, "logits")
+    rows, vocab = logits.shape
+    ctx, st, lib = _c()
+    if out is None:
+        out = torch.empty((rows,), dtype=torch.int32, device=logits.device)
+    check(lib.xaxb_argmax(ctx, st, ptr(logits), rows, vocab, logits.stride(0), ptr(out)), "argmax")
+    return out
+
+
+# ---------------------------------------------------------------------------------------
+# kernel 3
+
+
+def rope_tables(head_dim: int, base: float, length: int, device=None):
+    """cos/sin tables [length, head_dim/2] bf16 for positions 0..length-1, built on the host
+    in the reference's op order and dtype (xax/arch/attention.py:390-397 with bf16
+    activations): bf16 frequencies, positions converted to bf16, bf16 angles."""
+    import ml_dtypes
+
+    bf = ml_dtypes.bfloat16
+    f32 = np.float32
+
+    def rb(a):
+        return np.asarray(a, dtype=f32).astype(bf)
+
+    dim = head_dim // 2
+    i = np.arange(0, dim).astype(bf)
+    t = rb(rb(-i.astype(f32)).astype(f32) * np.asarray(np.log(f32(base))).astype(bf).astype(f32))
+    t = rb(t.astype(f32) / f32(dim))
+    freqs = rb(np.exp(t.astype(f32)))
+    pos = np.arange(length, dtype=np.int32).astype(bf)
+    ang = rb(pos.astype(f32)[:, None] * freqs.astype(f32)[None, :])
+    cos = rb(np.cos(ang.astype(f32)))
+    sin = rb(np.sin(ang.astype(f32)))
+
+    def to_torch(a):
+        tt = torch.from_numpy(a.view(np.uint16).astype(np.int32)).to(torch.int16).view(BF16)
+        return tt.to(device) if device is not None else tt
+
+    return to_torch(cos), to_torch(sin)
+
+
+def kv_append_rope(qkv, B, T, Hq, Hkv, D, positions, cos, sin, k_cache, v_cache, *, store_rotated_k=True, q_rot=None):
+    """RoPE on q and k of the fused projection output, K/V written into the cache at
+    positions[b] .. +T-1.  Returns q_rot [B*T, Hq, D]."""
+    qkv = _req(qkv, BF16, "qkv")
+    ctx, st, lib = _c()
+    if q_rot is None:
+        q_rot = torch.empty((B * T, Hq, D), dtype=BF16, device=qkv.device)
+    max_len = k_cache.shape[1]
+    check(lib.xaxb_kv_append_rope(ctx, st, ptr(qkv), qkv.stride(0), B, T, Hq, Hkv, D, ptr(positions), ptr(cos), ptr(sin),
+                                  cos.shape[0], ptr(q_rot), ptr(k_cache), ptr(v_cache), max_len,
+                                  1 if store_rotated_k else 0), "kv_append_rope")
+    return q_rot
+
+
+def attn_decode_workspace(B, Hq, D, max_len, device):
+    n = _lib.load().xaxb_attn_decode_workspace_bytes(B, Hq, D, max_len)
+    return torch.empty((n // 4,), dtype=torch.float32, device=device)
+
+
+def attn_decode(q_rot, k_cache, v_cache, positions, *, scale=None, k_is_rotated=True, cos=None, sin=None,
+                workspace=None, out=None):
+    """One query token per sequence; attends to cache rows 0 .. positions[b]."""
+    B, Hq, D = q_rot.shape
+    _, max_len, Hkv, _ = k_cache.shape
+    ctx, st, lib = _c()
+    if workspace is None:
+        workspace = attn_decode_workspace(B, Hq, D, max_len, q_rot.device)
+    if out is None:
+        out = torch.empty_like(q_rot)
+    if scale is None:
+        scale = 1.0 / math.sqrt(D)
+    check(lib.xaxb_attn_decode(ctx, st, ptr(q_rot), ptr(k_cache), ptr(v_cache), ptr(positions), B, Hq, Hkv, D, max_len,
+                               float(scale), 1 if k_is_rotated else 0, ptr(cos), ptr(sin),
+                               0 if cos is None else cos.shape[0], ptr(out), ptr(workspace),
+                               workspace.numel() * 4), "attn_decode")
+    return out
+
+
+def attn_prefill(q_rot, k_cache, v_cache, positions, B, T, *, scale=None, out=None):
+    """Causal attention of T new tokens per sequence (already in the cache) against the cache."""
+    _, Hq, D = q_rot.shape
+    _, max_len, Hkv, _ = k_cache.shape
+    ctx, st, lib = _c()
+    if out is None:
+        out = torch.empty_like(q_rot)
+    if scale is None:
+        scale = 1.0 / math.sqrt(D)
+    check(lib.xaxb_attn_prefill(ctx, st, ptr(q_rot), ptr(k_cache), ptr(v_cache), ptr(positions), B, T, Hq, Hkv, D,
+                                max_len, float(scale), ptr(out)), "attn_prefill")
+    return out
+
+
+def attn_check(q_rot, k_cache, v_cache, positions, B, T, *, scale=None):
+    _, Hq, D = q_rot.shape
+    _, max_len, Hkv, _ = k_cache.shape
+    ctx, st, lib = _c()
+    out = torch.empty_like(q_rot)
+    if scale is None:
+        scale = 1.0 / math.sqrt(D)
+    check(lib.xaxb_attn_check(ctx, st, ptr(q_rot), ptr(k_cache), ptr(v_cache), ptr(positions), B, T, Hq, Hkv, D,
+                              max_len, float(scale), ptr(out)), "attn_check")
+    return out
+
+
+def advance_positions(positions, delta: int):
+    ctx, st, lib = _c()
+    check(lib.xaxb_advance_positions(ctx, st, ptr(positions), positions.numel(), int(delta)), "advance_positions")
+    return positions
