@@ -143,6 +143,24 @@ def current_scale(x, fp8_dtype, compute_dtype) -> np.ndarray:
     return rnd(f32(fp8_max) / denom, compute_dtype)
 
 
+# How the quantised operands are multiplied.  "qdq" is what the reference's Python executes
+# on CPU: dequantise to bf16, bf16 matmul (xax/nn/fp8.py:335-339).  "fp8_gemm" is what the
+# reference's module docstring (xax/nn/fp8.py:3-11) says XLA substitutes on a GPU: a hardware
+# FP8 matmul of the quantised operands with float32 accumulation, the dequantisation applied
+# to the accumulator.  The e4m3 bytes and scales are the same in both; outputs differ by
+# ~4e-3 relative per layer, and because every following FP8 cast is discontinuous that
+# difference grows to several per cent over a stack of layers.
+MATMUL_MODE = "qdq"
+
+
+def _fp8_product(q_x, s_x, q_w, s_w, cd, mode):
+    if mode == "qdq":
+        return matmul_nt(dequantize(q_x, cd, s_x), dequantize(q_w, cd, s_w), cd)
+    acc = (f32(q_x) @ f32(q_w).T).astype(float32)
+    acc = acc * (float32(1.0) / f32(np.asarray(s_x).astype(cd))) * (float32(1.0) / f32(np.asarray(s_w).astype(cd)))
+    return acc  # float32: the bias joins before the single bf16 rounding
+
+
 class Fp8Linear:
     """xax/nn/fp8.py:199-344.  ``weight`` is (out_features, in_features)."""
 
@@ -189,12 +207,12 @@ class Fp8Linear:
             kernel_scale = current_scale(w, self.fp8_dtype, cd)
             updated = None
 
-        x_qdq = quantize_dequantize(x, self.fp8_dtype, input_scale, cd)  # :335-336
-        w_qdq = quantize_dequantize(w, self.fp8_dtype, kernel_scale, cd)
-        out = matmul_nt(x_qdq, w_qdq, cd)  # :339
+        q_x = quantize(x, self.fp8_dtype, input_scale, cd)  # :335-336
+        q_w = quantize(w, self.fp8_dtype, kernel_scale, cd)
+        out = _fp8_product(q_x, input_scale, q_w, kernel_scale, cd, MATMUL_MODE)  # :339
         if self.bias is not None:  # :341-342
             out = rnd(f32(out) + f32(self.bias), promote(cd, self.bias.dtype))
-        return out, updated
+        return rnd(out, cd) if out.dtype == float32 and self.bias is None else out, updated
 
     # -- vectorised form of ``jax.vmap(lambda xi: layer(xi, scales=None))(x_flat)`` ------------
     def call_rows(self, x2d):
@@ -209,12 +227,11 @@ class Fp8Linear:
         sx = rnd(f32(fp8_max) / np.maximum(f32(amax), f32(floor)), cd)  # (rows,)
         sw = current_scale(w, self.fp8_dtype, cd)
         q = quantize(x, self.fp8_dtype, sx[:, None], cd)
-        x_qdq = dequantize(q, cd, sx[:, None])
-        w_qdq = quantize_dequantize(w, self.fp8_dtype, sw, cd)
-        out = matmul_nt(x_qdq, w_qdq, cd)
+        q_w = quantize(w, self.fp8_dtype, sw, cd)
+        out = _fp8_product(q, sx[:, None], q_w, sw, cd, MATMUL_MODE)
         if self.bias is not None:
             out = rnd(f32(out) + f32(self.bias), promote(cd, self.bias.dtype))
-        return out, sx, q
+        return (rnd(out, cd) if out.dtype == float32 else out), sx, q
 
 
 def fp8_matmul(a, b, compute_dtype=bfloat16, fp8_dtype=float8_e4m3fn) -> np.ndarray:

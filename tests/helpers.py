@@ -46,3 +46,51 @@ def cfg1_inputs(M=2048, K=2048, N=8192, seed=0):
     w = (rng.standard_normal((K, N)) * 0.02).astype(np.float32).T.copy()
     b = (rng.standard_normal((N,)) * 0.01).astype(np.float32)
     return x.astype(bf16), w.astype(bf16), b.astype(bf16), rng
+
+
+# ---------------------------------------------------------------------------------------
+# oracle model -> device model (same weights), so both sides of a parity test share parameters
+
+
+def _lin_from_oracle(o, device="cuda"):
+    from xax_b200.arch.attention import Linear
+    from xax_b200.nn.fp8 import Fp8Linear
+
+    w = to_torch(o.weight, device)
+    b = None if o.bias is None else to_torch(o.bias, device)
+    if type(o).__name__ == "Fp8Linear":
+        return Fp8Linear(w.shape[1], w.shape[0], weight=w, bias=b, use_bias=b is not None, use_fp8=o.use_fp8)
+    return Linear(w.shape[1], w.shape[0], use_bias=b is not None, weight=w, bias=b)
+
+
+def block_from_oracle(ob, device="cuda"):
+    from xax_b200.arch.attention import RMSNorm, RotaryEmbedding, SelfAttentionBlock, SwiGLU, TransformerBlock
+
+    a = ob.self_attn
+    attn = SelfAttentionBlock(
+        _lin_from_oracle(a.q_proj, device), _lin_from_oracle(a.k_proj, device), _lin_from_oracle(a.v_proj, device),
+        _lin_from_oracle(a.output_proj, device),
+        RotaryEmbedding.build(a.head_dim, a.rotary_emb.base, a.rotary_emb.style),
+        num_heads=a.num_heads, num_kv_heads=a.num_kv_heads, head_dim=a.head_dim, causal=a.causal)
+    f = ob.feed_forward
+    ff = SwiGLU(_lin_from_oracle(f.gate, device), _lin_from_oracle(f.up, device), _lin_from_oracle(f.down, device))
+    return TransformerBlock(attn, ff, RMSNorm(to_torch(ob.attn_norm.weight, device), ob.attn_norm.eps),
+                            RMSNorm(to_torch(ob.mlp_norm.weight, device), ob.mlp_norm.eps),
+                            num_heads=a.num_heads, head_dim=a.head_dim, causal=a.causal)
+
+
+def llm_from_oracle(om, device="cuda"):
+    from xax_b200.arch.attention import Embedding, Linear, RMSNorm
+    from xax_b200.arch.llm import LLM, LLMConfig
+
+    c = om.config
+    cfg = LLMConfig(vocab_size=c.vocab_size, embed_dim=c.embed_dim, q_heads=c.q_heads, kv_heads=c.kv_heads,
+                    head_dim=c.head_dim, num_layers=c.num_layers, max_tsz=c.max_tsz, rope_theta=c.rope_theta,
+                    mlp_mult=c.mlp_mult, mlp_hidden_dim=c.mlp_hidden_dim, rms_eps=c.rms_eps)
+    ew = to_torch(om.embed.weight, device)
+    embed = Embedding(ew.shape[0], ew.shape[1], weight=ew)
+    tied = om.lm_head.weight is om.embed.weight
+    hw = ew if tied else to_torch(om.lm_head.weight, device)
+    head = Linear(hw.shape[1], hw.shape[0], use_bias=False, weight=hw)
+    return LLM(embed, [block_from_oracle(b, device) for b in om.blocks],
+               RMSNorm(to_torch(om.norm.weight, device), om.norm.eps), head, cfg)

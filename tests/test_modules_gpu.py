@@ -1,0 +1,259 @@
+"""Module-level parity on the GPU: the xax-shaped API (Fp8Linear, TransformerBlock, LLM,
+greedy generation) against the CPU oracle with shared weights and seeded inputs.
+
+Tolerances: relative Frobenius error <= 1e-2 against the oracle's strict reference path;
+greedy tokens equal on the toy model and >= 99 % top-1 agreement on the larger one."""
+
+import numpy as np
+import pytest
+import torch
+
+from helpers import (bf16, block_from_oracle, cfg1_inputs, e4m3, f32, llm_from_oracle, rel_fro, to_numpy, to_torch)
+
+pytestmark = pytest.mark.gpu
+TOL = 1e-2
+
+
+@pytest.fixture(scope="module", autouse=True)
+def _status():
+    yield
+    from xax_b200 import _lib
+
+    _lib.device_status()
+
+
+def test_fp8_linear_modes_vs_oracle():
+    from oracle import fp8 as ofp8
+    from xax_b200.nn.fp8 import Fp8Linear, Fp8Scales, init_fp8_scales
+
+    x, w, b, rng = cfg1_inputs(M=96, K=512, N=256)
+    ol = ofp8.Fp8Linear(w, b)
+    layer = Fp8Linear(512, 256, weight=to_torch(w), bias=to_torch(b))
+    # current scaling, whole tensor (apply_linear semantics)
+    exp, _ = ol(x)
+    out, sc = layer(to_torch(x))
+    assert sc is None and out.shape == (96, 256)
+    assert rel_fro(f32(to_numpy(out)), f32(exp)) < TOL
+    # per-row (vmapped) semantics
+    exp_r = ol.call_rows(x)[0]
+    out_r, _ = layer(to_torch(x), per_row=True)
+    assert rel_fro(f32(to_numpy(out_r)), f32(exp_r)) < TOL
+    # a single vector, as the reference's own test calls it (tests/nn/test_fp8.py:112-118)
+    s0 = init_fp8_scales(16)
+    o1, ns = layer(to_torch(x[0]), scales=s0)
+    e1, es = ol(x[0], ofp8.init_fp8_scales(16))
+    assert o1.shape == (256,) and float(ns.input_amax_history.abs().max()) != 0.0
+    assert np.array_equal(to_numpy(ns.input_amax_history), es.input_amax_history)
+    assert np.array_equal(to_numpy(ns.kernel_amax_history), es.kernel_amax_history)
+    assert to_numpy(ns.input_scale) == es.input_scale and to_numpy(ns.kernel_scale) == es.kernel_scale
+    assert rel_fro(f32(to_numpy(o1)), f32(e1)) < 0.1  # unit scales: values underflow e4m3, loose like the reference
+    # second call with the updated scales
+    o2, ns2 = layer(to_torch(x), scales=ns)
+    e2, es2 = ol(x, es)
+    assert rel_fro(f32(to_numpy(o2)), f32(e2)) < TOL
+    assert np.array_equal(to_numpy(ns2.input_amax_history), es2.input_amax_history)
+    # FP8 disabled == plain matmul (tests/nn/test_fp8.py:99-105)
+    plain = Fp8Linear(512, 256, weight=to_torch(w), bias=to_torch(b), use_fp8=False)
+    op, sp = plain(to_torch(x))
+    ep, _ = ofp8.Fp8Linear(w, b, use_fp8=False)(x)
+    assert sp is None and rel_fro(f32(to_numpy(op)), f32(ep)) < 5e-3
+    # FP8 close to plain, the reference's own loose bound (tests/nn/test_fp8.py:107-110)
+    assert np.allclose(f32(to_numpy(out)), f32(to_numpy(op)), atol=1.0, rtol=0.1)
+
+
+def test_fp8_free_functions():
+    from oracle import fp8 as ofp8
+    from xax_b200.nn import fp8
+
+    rng = np.random.default_rng(42)
+    x = rng.standard_normal((16, 16)).astype(np.float32).astype(bf16)
+    scale = np.float32(448.0) / np.max(np.abs(f32(x)))
+    q = fp8.quantize(to_torch(x), torch.float8_e4m3fn, torch.tensor(float(scale)), torch.bfloat16)
+    assert np.array_equal(to_numpy(q).view(np.uint8), ofp8.quantize(x, e4m3, scale, bf16).view(np.uint8))
+    r = fp8.quantize_dequantize(to_torch(x), torch.float8_e4m3fn, torch.tensor(float(scale)), torch.bfloat16)
+    rel = np.abs(f32(to_numpy(r)) - f32(x)) / (np.abs(f32(x)) + 1e-6)
+    assert rel.mean() < 0.05  # tests/nn/test_fp8.py:63-67
+    big = fp8.quantize(torch.tensor([[1000.0, -1000.0] + [0.0] * 6], device="cuda"), torch.float8_e4m3fn,
+                       torch.tensor(1.0))
+    assert float(big.float().abs().max()) <= 448.0  # tests/nn/test_fp8.py:75-78
+    h = fp8.compute_amax_history(torch.tensor([1.0, -5.0, 3.0, 0, 0, 0, 0, 0], device="cuda"),
+                                 torch.zeros(4, device="cuda"))
+    assert float(h[0]) == 5.0 and h.numel() == 4  # tests/nn/test_fp8.py:47-53
+    with pytest.raises(ValueError, match="unsupported"):
+        fp8.quantize(to_torch(x), torch.float8_e5m2, torch.tensor(1.0))
+    a = rng.standard_normal((4, 16)).astype(np.float32).astype(bf16)
+    b = rng.standard_normal((16, 8)).astype(np.float32).astype(bf16)
+    got = fp8.fp8_matmul(to_torch(a), to_torch(b))
+    assert np.allclose(f32(to_numpy(got)), f32(a) @ f32(b), atol=0.5, rtol=0.1)  # tests/nn/test_fp8.py:121-135
+    assert rel_fro(f32(to_numpy(got)), f32(ofp8.fp8_matmul(a, b))) < TOL
+
+
+@pytest.mark.parametrize("fp8_attn,fp8_mlp,T,start", [(True, True, 160, 0), (True, False, 40, 0), (False, False, 130, 0),
+                                                      (True, True, 1, 37)])
+def test_transformer_block_vs_oracle(fp8_attn, fp8_mlp, T, start):
+    """A reduced BASELINE config 2: pre-norm block, GQA 8/2 heads x 64, SwiGLU, RoPE, prefill
+    (and one decode step at a non-zero position) of B = 2 sequences."""
+    from oracle.attention import build_block
+
+    B, H, Hq, Hkv, D, F = 2, 256, 8, 2, 64, 640
+    rng = np.random.default_rng(5)
+    ob = build_block(rng, embed_dim=H, num_heads=Hq, num_kv_heads=Hkv, head_dim=D, ff_dim=F, rope_theta=10000.0,
+                     norm_eps=1e-5, fp8_attn=fp8_attn, fp8_mlp=fp8_mlp, out_scale=1.0 / np.sqrt(2 * 22))
+    blk = block_from_oracle(ob)
+    x = rng.standard_normal((B, T, H)).astype(np.float32).astype(bf16)
+    max_len = start + T + 3
+    cache = blk.self_attn.init_cache(max_len, batch=B)
+    ocaches = [ob.init_cache(max_len) for _ in range(B)]
+    if start:  # warm the caches with `start` tokens first, on both sides
+        x0 = rng.standard_normal((B, start, H)).astype(np.float32).astype(bf16)
+        _, cache = blk.forward_tokens(to_torch(x0).reshape(B * start, H), B, start, cache=cache)
+        for b in range(B):
+            _, ocaches[b] = ob.forward(x0[b], cache=ocaches[b])
+    out, cache = blk.forward_tokens(to_torch(x).reshape(B * T, H), B, T, cache=cache)
+    got = to_numpy(out).reshape(B, T, H)
+    for b in range(B):
+        exp, oc = ob.forward(x[b], cache=ocaches[b])
+        err = rel_fro(f32(got[b]), f32(exp))
+        assert err < TOL, (b, err)
+        n = start + T
+        kerr = rel_fro(f32(to_numpy(cache["k"])[b, :n]), f32(oc["self_attn"]["k"][:n]))
+        assert kerr < TOL, kerr
+    assert to_numpy(cache["position"]).tolist() == [start + T] * B
+
+
+def test_block_unbatched_api_and_donation():
+    from oracle.attention import build_block
+
+    H, Hq, Hkv, D, F, T = 128, 2, 1, 64, 256, 9
+    rng = np.random.default_rng(9)
+    ob = build_block(rng, embed_dim=H, num_heads=Hq, num_kv_heads=Hkv, head_dim=D, ff_dim=F, fp8_attn=True, fp8_mlp=True)
+    blk = block_from_oracle(ob)
+    x = rng.standard_normal((T, H)).astype(np.float32).astype(bf16)
+    cache = blk.init_cache(max_len=16)
+    assert cache["self_attn"]["k"].shape == (16, Hkv, D) and int(cache["self_attn"]["position"]) == 0
+    y, c2 = blk.forward(to_torch(x), cache=cache, donate=False)
+    assert int(cache["self_attn"]["position"]) == 0 and int(c2["self_attn"]["position"]) == T
+    assert float(cache["self_attn"]["k"].float().abs().max()) == 0.0  # input cache untouched
+    exp, _ = ob.forward(x, cache=ob.init_cache(16))
+    assert rel_fro(f32(to_numpy(y)), f32(exp)) < TOL
+    with pytest.raises(ValueError):
+        blk.forward(to_torch(x).reshape(1, T, H))
+    with pytest.raises(ValueError, match="max_len"):
+        blk.self_attn.init_cache(None)
+
+
+def _toy(use_fp8, std=0.2, dtype=bf16, seed=0, layers=2):
+    from oracle import llm as ollm
+
+    cfg = ollm.LLMConfig(vocab_size=256, embed_dim=64, q_heads=4, kv_heads=2, head_dim=64, num_layers=layers,
+                         max_tsz=128, mlp_hidden_dim=128)
+    om = ollm.LLM.build(cfg, np.random.default_rng(seed), use_fp8=use_fp8, std=std, dtype=dtype)
+    return om, llm_from_oracle(om)
+
+
+def test_llm_forward_shape_and_tying():
+    from xax_b200.arch.llm import tie_embedding_and_head
+
+    om, m = _toy(True)
+    toks = torch.tensor([[1, 2, 3, 4, 5], [9, 8, 7, 6, 5]], dtype=torch.int32, device="cuda")
+    logits, _ = m.forward_batch(toks)
+    assert logits.shape == (2, 5, 256)  # xax tests/nn/test_llm.py:20-26
+    tied = tie_embedding_and_head(m)
+    assert tied.lm_head.weight is tied.embed.weight  # tests/nn/test_llm.py:29-32
+
+
+def test_cached_decode_matches_full_forward():
+    """xax tests/nn/test_attention.py:10-43 / 72-102: token-by-token and chunked (3+2+3) cached
+    forward equal the one-shot forward (plain bf16 linears, so scales do not depend on T)."""
+    om, m = _toy(False, std=0.3)
+    toks = torch.tensor([5, 77, 130, 2, 9, 201, 33, 64], dtype=torch.int32, device="cuda")
+    full = f32(to_numpy(m.forward(toks)))
+    for chunks in ([1] * 8, [3, 2, 3]):
+        caches = m.init_cache(8)
+        outs, i = [], 0
+        for n in chunks:
+            lg, caches = m.forward(toks[i:i + n], caches=caches)
+            outs.append(f32(to_numpy(lg)))
+            i += n
+        got = np.concatenate(outs)
+        assert rel_fro(got, full) < 5e-3, chunks
+
+
+def test_greedy_generation_matches_oracle():
+    """xax tests/nn/test_llm.py:49-112: generation equals the cache-decode loop token for token."""
+    from oracle import llm as ollm
+    from xax_b200.arch.llm import llm_generate, llm_generate_batch, llm_generate_jit
+
+    om, m = _toy(True)
+    prompt = [11, 17, 23]
+    exp, exp_len = ollm.llm_generate_greedy(om, prompt, -1, 6)
+    toks, n = llm_generate_jit(m, torch.tensor(prompt, dtype=torch.int32, device="cuda"), -1, 6)
+    assert n == exp_len and np.array_equal(toks.cpu().numpy(), exp)
+    assert len(llm_generate(m, prompt, None, max_new_tokens=3)) == len(prompt) + 3  # tests/nn/test_llm.py:35-46
+    # batched, graph replay and eager stepping agree
+    pb = torch.tensor([prompt, [5, 6, 7]], dtype=torch.int32, device="cuda")
+    g, _ = llm_generate_batch(m, pb, 6, use_graph=True)
+    e, _ = llm_generate_batch(m, pb, 6, use_graph=False)
+    assert torch.equal(g, e) and np.array_equal(g[0].cpu().numpy(), exp)
+    exp2, _ = ollm.llm_generate_greedy(om, [5, 6, 7], -1, 6)
+    assert np.array_equal(g[1].cpu().numpy(), exp2)
+    # EOS stops the sequence (reference: done flag, :1582,1609)
+    eos = int(exp[4])
+    t2, n2 = llm_generate_jit(m, torch.tensor(prompt, dtype=torch.int32, device="cuda"), eos, 6)
+    e2, en2 = ollm.llm_generate_greedy(om, prompt, eos, 6)
+    assert n2 == en2 and np.array_equal(t2.cpu().numpy()[:n2], e2[:en2])
+
+
+def test_llm_reduced_cfg4_layerwise_and_logits():
+    """Reduced BASELINE config 4 (4 layers, hidden 512, 8/2 heads x 64, SwiGLU 1408, vocab 2048).
+
+    Every FP8 cast is discontinuous, so two correct FP8 pipelines that differ in the last bit of
+    one GEMM output drift apart over a stack of layers (the reference's own CPU "dequantise,
+    bf16 matmul" and GPU "FP8 matmul" executions differ by 6-13 % on these logits).  Parity is
+    therefore checked the way a deep FP8 model can be checked:
+      * layer by layer with the oracle's activations as input: every block <= 1e-2;
+      * logits from the oracle's final hidden state: <= 1e-2 and >= 99 % top-1 agreement;
+      * free-running logits against the oracle executed with FP8-matmul semantics (what the
+        reference's docstring says XLA runs on a GPU): bounded, with >= 90 % top-1 agreement."""
+    from oracle import fp8 as ofp8
+    from oracle import llm as ollm
+
+    cfg = ollm.LLMConfig(vocab_size=2048, embed_dim=512, q_heads=8, kv_heads=2, head_dim=64, num_layers=4,
+                         mlp_hidden_dim=1408, rms_eps=1e-5)
+    om = ollm.LLM.build(cfg, np.random.default_rng(1), use_fp8=True, std=0.05)
+    m = llm_from_oracle(om)
+    rng = np.random.default_rng(2)
+    B, T = 2, 96
+    toks = rng.integers(0, 2048, (B, T)).astype(np.int32)
+    # oracle pass, strict reference semantics, keeping every layer's input
+    layer_in, finals, exp_logits = [[] for _ in om.blocks], [], []
+    for b in range(B):
+        x = om.embed_tokens(toks[b])
+        for i, blk in enumerate(om.blocks):
+            layer_in[i].append(x)
+            x, _ = blk.forward(x)
+        finals.append(x)
+        exp_logits.append(om.get_logits(om.norm(x)))
+    for i, blk in enumerate(m.blocks):
+        xin = to_torch(np.stack(layer_in[i])).reshape(B * T, -1)
+        out, _ = blk.forward_tokens(xin, B, T)
+        nxt = np.stack(layer_in[i + 1]) if i + 1 < len(m.blocks) else np.stack(finals)
+        err = rel_fro(f32(to_numpy(out)).reshape(B, T, -1), f32(nxt))
+        assert err < TOL, (i, err)
+    h = m.norm(to_torch(np.stack(finals)).reshape(B * T, -1))
+    got = f32(to_numpy(m.get_logits(h))).reshape(B, T, -1)
+    exp = f32(np.stack(exp_logits))
+    assert rel_fro(got, exp) < TOL
+    assert np.mean(np.argmax(got, -1) == np.argmax(exp, -1)) >= 0.99
+    # free-running
+    logits, _ = m.forward_batch(to_torch(toks))
+    free = f32(to_numpy(logits))
+    ofp8.MATMUL_MODE = "fp8_gemm"
+    try:
+        exp_fp8 = f32(np.stack([om.forward(toks[b]) for b in range(B)]))
+    finally:
+        ofp8.MATMUL_MODE = "qdq"
+    e_fp8, e_qdq = rel_fro(free, exp_fp8), rel_fro(free, exp)
+    agree = np.mean(np.argmax(free, -1) == np.argmax(exp_fp8, -1))
+    print(f"free-running logits: {e_fp8:.3e} vs FP8-matmul oracle (top-1 {agree:.3f}), {e_qdq:.3e} vs QDQ oracle")
+    assert e_fp8 < 0.1 and e_qdq < 0.3 and agree >= 0.9

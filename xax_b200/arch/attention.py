@@ -1,0 +1,524 @@
+"""B200-native mirror of the hot-path modules of ``xax/arch/attention.py``.
+
+Same class names, fields, ``build`` keyword arguments and call signatures as the reference
+for: ``apply_linear``, ``RMSNorm``, ``SwiGLU``, ``RotaryEmbedding``, ``SelfAttentionBlock``,
+``TransformerBlock`` and the cache dictionaries.  Arrays are torch CUDA tensors (bf16
+activations); every computation is one of the library's sm_100a kernels.
+
+The reference is unbatched and batches with ``jax.vmap``; here every module also has a
+``*_batch`` entry that takes ``B`` sequences of ``T`` tokens at once -- numerically the
+vmapped reference: per-token activation scales inside attention projections
+(xax/arch/attention.py:279), per-sequence scales inside the SwiGLU (xax/arch/attention.py:55).
+
+Caches are donated: ``forward(..., cache=c)`` appends into ``c``'s buffers and returns a
+cache sharing them (the reference donates at its jit boundary, xax/arch/llm.py:1446).
+Pass ``donate=False`` to copy first.  Outside the path (not built): cross-attention, LoRA,
+QK-norm, attention sinks, sliding windows, LayerNorm / MLP feed-forward.
+"""
+
+from __future__ import annotations
+
+import math
+import warnings
+from typing import Literal, NotRequired, TypedDict
+
+import torch
+
+from .. import ops
+from ..nn.fp8 import Fp8Linear, Fp8Scales, init_fp8_scales
+
+BF16 = torch.bfloat16
+
+
+class Linear:
+    """Stand-in for ``eqx.nn.Linear``: weight (out_features, in_features), optional bias."""
+
+    def __init__(self, in_features: int, out_features: int, use_bias: bool = True, *, key=None, weight=None, bias=None,
+                 dtype=BF16, device=None):
+        self.in_features, self.out_features, self.use_bias = in_features, out_features, use_bias
+        if weight is None:
+            gen = key if isinstance(key, torch.Generator) else torch.Generator(device="cpu").manual_seed(int(key or 0))
+            lim = 1.0 / math.sqrt(in_features)
+            dev = torch.device("cuda", torch.cuda.current_device()) if device is None else device
+            weight = ((torch.rand((out_features, in_features), generator=gen) * 2 - 1) * lim).to(dtype).to(dev)
+            bias = ((torch.rand((out_features,), generator=gen) * 2 - 1) * lim).to(dtype).to(dev) if use_bias else None
+        self.weight, self.bias = weight, bias
+
+    def __call__(self, x):
+        return apply_linear(x, self)
+
+
+class Embedding:
+    """Stand-in for ``eqx.nn.Embedding``: weight (num_embeddings, embedding_size)."""
+
+    def __init__(self, num_embeddings: int, embedding_size: int, *, key=None, weight=None, dtype=BF16, device=None):
+        if weight is None:
+            gen = key if isinstance(key, torch.Generator) else torch.Generator(device="cpu").manual_seed(int(key or 0))
+            dev = torch.device("cuda", torch.cuda.current_device()) if device is None else device
+            weight = torch.randn((num_embeddings, embedding_size), generator=gen).to(dtype).to(dev)
+        self.weight = weight
+        self.num_embeddings, self.embedding_size = weight.shape
+
+    def __call__(self, token):
+        return ops.embed(torch.as_tensor(token, dtype=torch.int32, device=self.weight.device).reshape(-1), self.weight)[0]
+
+
+def apply_linear(x: torch.Tensor, linear, *, residual: torch.Tensor | None = None) -> torch.Tensor:
+    """xax/arch/attention.py:30-69: dispatch on the layer type.  An Fp8Linear is applied to the
+    whole tensor at once (one activation scale, scales dropped).  A leading batch dimension
+    (rank 3) reproduces the vmapped reference: one activation scale per sequence."""
+    if isinstance(linear, Fp8Linear):
+        if x.dim() == 3 and linear.use_fp8:
+            B, T, _ = x.shape
+            x2 = x.reshape(B * T, -1).to(BF16).contiguous()
+            xq, _, x_inv, _ = ops.quantize_current(x2, T)
+            res2 = None if residual is None else residual.reshape(B * T, -1)
+            return linear.forward_quantized(xq, x_inv, res2).reshape(B, T, -1)
+        return linear(x, residual=residual)[0]
+    if isinstance(linear, Linear):
+        x2 = x.reshape(-1, x.shape[-1]).to(BF16).contiguous()
+        res2 = None if residual is None else residual.reshape(-1, linear.out_features)
+        return ops.gemm_bf16(x2, linear.weight, None, None, linear.bias, res2).reshape(*x.shape[:-1], -1)
+    if isinstance(linear, Embedding):
+        x2 = x.reshape(-1, x.shape[-1]).to(BF16).contiguous()
+        return ops.gemm_bf16(x2, linear.weight).reshape(*x.shape[:-1], -1)
+    raise ValueError(f"Unsupported linear layer type: {type(linear)}")
+
+
+class RMSNorm:
+    """xax/arch/attention.py:72-98.  ``build`` makes a float32 weight of ones like the
+    reference; the kernel runs in bf16, so the weight is cast to bf16 at use (exact for ones)."""
+
+    def __init__(self, weight: torch.Tensor, eps: float = 1e-6):
+        self.weight, self.eps = weight, eps
+        self._w16 = None
+
+    @classmethod
+    def build(cls, dim: int, eps: float = 1e-6, device=None) -> "RMSNorm":
+        dev = torch.device("cuda", torch.cuda.current_device()) if device is None else device
+        return cls(torch.ones((dim,), dtype=torch.float32, device=dev), eps)
+
+    def weight_bf16(self) -> torch.Tensor:
+        if self._w16 is None or self._w16.device != self.weight.device:
+            self._w16 = self.weight.to(BF16).contiguous()
+        return self._w16
+
+    def __call__(self, x: torch.Tensor) -> torch.Tensor:
+        x2 = x.reshape(-1, x.shape[-1]).to(BF16).contiguous()
+        y, _ = ops.rmsnorm(x2, self.weight_bf16(), self.eps)
+        return y.reshape(x.shape)
+
+
+class SwiGLU:
+    """xax/arch/attention.py:101-147: down(silu(gate(x)) * up(x)).  ``build`` uses plain
+    linears like the reference (:138-140); pass ``use_fp8=True`` (an extension) or swap
+    Fp8Linear instances into ``gate`` / ``up`` / ``down`` for the FP8 MLP."""
+
+    def __init__(self, gate, up, down):
+        self.gate, self.up, self.down = gate, up, down
+        self._fused = None
+
+    @classmethod
+    def build(cls, embed_dim: int, hidden_dim: int | None = None, *, key=None, use_bias: bool = False,
+              use_fp8: bool = False, device=None) -> "SwiGLU":
+        if hidden_dim is None:
+            hidden_dim = embed_dim * 4
+        seed = int(key or 0) if not isinstance(key, torch.Generator) else int(key.initial_seed())
+        if use_fp8:
+            mk = lambda i, o, k: Fp8Linear(i, o, key=k, use_bias=use_bias, device=device)  # noqa: E731
+        else:
+            mk = lambda i, o, k: Linear(i, o, use_bias=use_bias, key=k, device=device)  # noqa: E731
+        return cls(mk(embed_dim, hidden_dim, seed + 1), mk(embed_dim, hidden_dim, seed + 2),
+                   mk(hidden_dim, embed_dim, seed + 3))
+
+    def is_fp8(self) -> bool:
+        return all(isinstance(m, Fp8Linear) and m.use_fp8 for m in (self.gate, self.up, self.down))
+
+    def fused_gate_up(self):
+        """gate | up weights stacked into one [2F, H] operand so one GEMM reads x once."""
+        if self._fused is None:
+            if self.is_fp8():
+                gq, g_inv = self.gate.weight_q_current()
+                uq, u_inv = self.up.weight_q_current()
+                F = gq.shape[0]
+                wq = torch.cat([gq.view(torch.uint8), uq.view(torch.uint8)], 0).view(torch.float8_e4m3fn)
+                col = torch.cat([g_inv.expand(F), u_inv.expand(F)]).contiguous()
+            else:
+                wq = torch.cat([self.gate.weight, self.up.weight], 0).contiguous()
+                col = None
+            biases = [self.gate.bias, self.up.bias]
+            bias = None if biases[0] is None else torch.cat(biases).contiguous()
+            self._fused = (wq, col, bias)
+        return self._fused
+
+    def __call__(self, x: torch.Tensor) -> torch.Tensor:
+        if x.dim() not in (2, 3):
+            raise ValueError(f"SwiGLU expects rank 2 or 3 input, got rank {x.dim()}")
+        B, T = (1, x.shape[0]) if x.dim() == 2 else x.shape[:2]
+        x2 = x.reshape(B * T, -1).to(BF16).contiguous()
+        return self.forward_tokens(x2, B, T).reshape(x.shape)
+
+    def forward_tokens(self, y: torch.Tensor, B: int, T: int, *, residual=None, y_q=None) -> torch.Tensor:
+        """y: normalised activations [B*T, H].  One activation scale per sequence (T rows).
+        ``y_q`` = (q, inv_scale) when the preceding RMSNorm already cast y."""
+        wq, col, bias = self.fused_gate_up()
+        F = self.gate.out_features
+        if self.is_fp8():
+            if y_q is None:
+                q, _, inv, _ = ops.quantize_current(y, T)
+            else:
+                q, inv = y_q
+            gu = ops.gemm_fp8(q, wq, inv, col, bias)
+            if T == 1:
+                _, (hq, _, h_inv) = ops.silu_mul(gu, F, want_h=False, quantize=True)
+            else:
+                amax = torch.zeros((B,), dtype=torch.float32, device=y.device)
+                h, _ = ops.silu_mul(gu, F, group_amax=amax, group_rows=T)
+                hq, _, h_inv = ops.quantize_with_amax(h, amax, T)
+            return self.down.forward_quantized(hq, h_inv, residual)
+        gu = ops.gemm_bf16(y, wq, None, None, bias)
+        h, _ = ops.silu_mul(gu, F)
+        return apply_linear(h, self.down, residual=residual)
+
+
+def can_use_cudnn_attention(dtype, head_dim: int, seq_len: int, has_bias: bool = False) -> bool:
+    """xax/arch/attention.py:150-179 (kept for API compatibility; this library never calls cuDNN)."""
+    return dtype in (torch.float16, torch.bfloat16) and head_dim <= 128 and head_dim % 8 == 0 and seq_len % 64 == 0 \
+        and not has_bias
+
+
+class AttentionCache(TypedDict):
+    k: torch.Tensor
+    v: torch.Tensor
+    position: torch.Tensor
+
+
+class Fp8ScalesCache(TypedDict):
+    q_proj: NotRequired[Fp8Scales]
+    k_proj: NotRequired[Fp8Scales]
+    v_proj: NotRequired[Fp8Scales]
+    output_proj: NotRequired[Fp8Scales]
+
+
+class TransformerBlockCache(TypedDict):
+    self_attn: AttentionCache
+    self_attn_fp8: NotRequired[Fp8ScalesCache]
+
+
+def _make_linear(in_features, out_features, key, use_bias=True, use_fp8=False, compute_dtype=BF16, device=None):
+    """xax/arch/attention.py:212-241 (an FP8 layer always gets a bias, like the reference)."""
+    if use_fp8:
+        return Fp8Linear(in_features, out_features, key=key, use_fp8=True, compute_dtype=compute_dtype, device=device)
+    return Linear(in_features, out_features, use_bias=use_bias, key=key, device=device)
+
+
+def _init_fp8_scales_cache(history_length: int) -> Fp8ScalesCache:
+    """xax/arch/attention.py:290-304."""
+    return {k: init_fp8_scales(history_length) for k in ("q_proj", "k_proj", "v_proj", "output_proj")}
+
+
+RotaryEmbeddingStyle = Literal["concatenated", "interleaved"]
+
+
+class RotaryEmbedding:
+    """xax/arch/attention.py:310-526.  The kernels implement the "concatenated" (LLaMA) style
+    that the LLM builds (xax/arch/llm.py:134) from cos/sin tables computed in the reference's
+    op order and dtype (bf16 frequencies, positions and angles)."""
+
+    def __init__(self, head_dim: int, base: float = 10000.0, style: RotaryEmbeddingStyle = "interleaved",
+                 factor: float = 1.0, original_max_position_embeddings: int | None = None, beta_slow: float = 1.0,
+                 beta_fast: float = 32.0):
+        self.head_dim, self.base, self.style, self.factor = head_dim, base, style, factor
+        self.original_max_position_embeddings = original_max_position_embeddings
+        self.beta_slow, self.beta_fast = beta_slow, beta_fast
+        self._tables: dict = {}
+
+    @classmethod
+    def build(cls, head_dim, base=10000.0, style="interleaved", factor=1.0, original_max_position_embeddings=None,
+              beta_slow=1.0, beta_fast=32.0) -> "RotaryEmbedding":
+        return cls(head_dim, base, style, factor, original_max_position_embeddings, beta_slow, beta_fast)
+
+    @property
+    def uses_yarn(self) -> bool:
+        return self.factor > 1.0 and self.original_max_position_embeddings is not None
+
+    def tables(self, length: int, device):
+        """(cos, sin) bf16 [>= length, head_dim / 2] on ``device`` (cached, grown on demand)."""
+        if self.uses_yarn:
+            raise ValueError("YaRN scaling is outside the path this library covers")
+        if self.style != "concatenated":
+            raise ValueError("the kernels implement the 'concatenated' RoPE style only")
+        key = str(device)
+        cur = self._tables.get(key)
+        if cur is None or cur[0].shape[0] < length:
+            n = max(length, 256)
+            self._tables[key] = cur = ops.rope_tables(self.head_dim, self.base, n, device)
+        return cur
+
+
+class SelfAttentionBlock:
+    """xax/arch/attention.py:529-980 restricted to causal GQA self-attention with optional RoPE
+    and a KV cache."""
+
+    def __init__(self, q_proj, k_proj, v_proj, output_proj, rotary_emb, q_norm=None, k_norm=None, sinks=None, *,
+                 num_heads: int, num_kv_heads: int, head_dim: int, causal: bool, local_window_size: int | None = None,
+                 use_fp8: bool = False):
+        if q_norm is not None or k_norm is not None or sinks is not None or local_window_size is not None:
+            raise ValueError("QK-norm, attention sinks and sliding windows are outside the path this library covers")
+        self.q_proj, self.k_proj, self.v_proj, self.output_proj = q_proj, k_proj, v_proj, output_proj
+        self.rotary_emb, self.q_norm, self.k_norm, self.sinks = rotary_emb, q_norm, k_norm, sinks
+        self.num_heads, self.num_kv_heads, self.head_dim = num_heads, num_kv_heads, head_dim
+        self.causal, self.local_window_size, self.use_fp8 = causal, local_window_size, use_fp8
+        self._fused = None
+
+    @classmethod
+    def build(cls, embed_dim: int, num_heads: int, *, key=None, num_kv_heads: int | None = None,
+              head_dim: int | None = None, use_bias: bool = True, causal: bool = False,
+              context_length: int | None = None, use_rotary_embeddings: bool = False, rotary_base: float = 10000.0,
+              rotary_style: RotaryEmbeddingStyle = "concatenated", rotary_factor: float = 1.0,
+              rotary_original_max_position_embeddings: int | None = None, rotary_beta_slow: float = 1.0,
+              rotary_beta_fast: float = 32.0, use_qk_norm: bool = False, qk_norm_eps: float = 1e-6,
+              use_attention_sinks: bool = False, use_fp8: bool = False, compute_dtype=BF16,
+              device=None) -> "SelfAttentionBlock":
+        if context_length is not None or use_qk_norm or use_attention_sinks:
+            raise ValueError("sliding windows, QK-norm and attention sinks are outside the path this library covers")
+        kv = num_kv_heads if num_kv_heads is not None else num_heads
+        hd = head_dim if head_dim is not None else embed_dim // num_heads
+        assert num_heads % kv == 0, "num_heads must be divisible by num_kv_heads"  # :620
+        seed = int(key or 0) if not isinstance(key, torch.Generator) else int(key.initial_seed())
+        qd, kd = num_heads * hd, kv * hd
+        mk = lambda i, o, k: _make_linear(i, o, k, use_bias, use_fp8, compute_dtype, device)  # noqa: E731
+        rope = RotaryEmbedding.build(hd, rotary_base, rotary_style, rotary_factor,
+                                     rotary_original_max_position_embeddings, rotary_beta_slow,
+                                     rotary_beta_fast) if use_rotary_embeddings else None
+        return cls(mk(embed_dim, qd, seed + 1), mk(embed_dim, kd, seed + 2), mk(embed_dim, kd, seed + 3),
+                   mk(qd, embed_dim, seed + 4), rope, num_heads=num_heads, num_kv_heads=kv, head_dim=hd, causal=causal,
+                   use_fp8=use_fp8)
+
+    @property
+    def embed_dim(self) -> int:
+        return self.head_dim * self.num_heads
+
+    def _is_fp8(self) -> bool:
+        return all(isinstance(m, Fp8Linear) and m.use_fp8 for m in (self.q_proj, self.k_proj, self.v_proj))
+
+    def fused_qkv(self):
+        """q | k | v weights stacked into one [(Hq + 2 Hkv) D, H] operand; per-column
+        dequantisation multipliers keep each projection's own weight scale."""
+        if self._fused is None:
+            projs = (self.q_proj, self.k_proj, self.v_proj)
+            if self._is_fp8():
+                qs = [p.weight_q_current() for p in projs]
+                wq = torch.cat([q.view(torch.uint8) for q, _ in qs], 0).view(torch.float8_e4m3fn)
+                col = torch.cat([inv.expand(q.shape[0]) for q, inv in qs]).contiguous()
+            else:
+                wq = torch.cat([p.weight for p in projs], 0).contiguous()
+                col = None
+            if all(p.bias is None for p in projs):
+                bias = None
+            else:
+                bias = torch.cat([p.bias if p.bias is not None else
+                                  torch.zeros((p.out_features,), dtype=BF16, device=p.weight.device)
+                                  for p in projs]).contiguous()
+            self._fused = (wq, col, bias)
+        return self._fused
+
+    def init_cache(self, max_len: int | None = None, dtype=None, batch: int | None = None, device=None) -> AttentionCache:
+        """xax/arch/attention.py:775-794; ``batch`` adds a leading sequence dimension."""
+        if max_len is None:
+            max_len = self.local_window_size
+        if max_len is None:
+            raise ValueError("context_length or max_len must be set for caching")
+        if dtype not in (None, BF16):
+            raise ValueError("the KV cache is bfloat16")
+        dev = self.q_proj.weight.device if device is None else device
+        lead = () if batch is None else (batch,)
+        shape = (*lead, max_len, self.num_kv_heads, self.head_dim)
+        return {"k": torch.zeros(shape, dtype=BF16, device=dev), "v": torch.zeros(shape, dtype=BF16, device=dev),
+                "position": torch.zeros(lead, dtype=torch.int32, device=dev)}
+
+    def init_mask(self, seq_len: int, add_cache: bool = False, batch_dim: bool = False) -> torch.Tensor:
+        """xax/arch/attention.py:796-824 (boolean mask; informational -- the kernels mask by position)."""
+        if add_cache:
+            raise ValueError("local_window_size must be set for caching")
+        mask = torch.tril(torch.ones((seq_len, seq_len), dtype=torch.bool))
+        return mask.reshape(1, 1, seq_len, seq_len) if batch_dim else mask
+
+    # -- forward --------------------------------------------------------------------------------
+    def forward(self, x_tn: torch.Tensor, *, mask=None, cache: AttentionCache | None = None, fp8_scales=None,
+                donate: bool = True):
+        """xax/arch/attention.py:826-980 for one sequence (T, H)."""
+        if x_tn.dim() != 2:
+            raise ValueError(f"expected rank 2 input, got rank {x_tn.dim()}")
+        if mask is not None:
+            raise ValueError("explicit masks are outside the path this library covers (causal masking is built in)")
+        if fp8_scales is not None:
+            raise ValueError("delayed scaling through the attention block is undefined in the reference "
+                             "(its Fp8Scales is not a pytree); call Fp8Linear directly with scales")
+        bc = None
+        if cache is not None:
+            bc = {"k": cache["k"].unsqueeze(0), "v": cache["v"].unsqueeze(0), "position": cache["position"].reshape(1)}
+        out, nc = self.forward_tokens(x_tn, 1, x_tn.shape[0], cache=bc, donate=donate)
+        return out, {"k": nc["k"][0], "v": nc["v"][0], "position": nc["position"].reshape(())}, None
+
+    def forward_tokens(self, y: torch.Tensor, B: int, T: int, *, cache=None, donate: bool = True, y_q=None,
+                       residual=None, workspace=None, advance: bool = True, reduce_amax=None):
+        """y: [B*T, H] (normalised) activations of B sequences, T new tokens each.  Returns
+        (attention output [B*T, H] (+ residual), updated batched cache).  ``advance=False``
+        leaves cache["position"] untouched (a caller sharing one position vector between layers
+        advances it once per step).  ``reduce_amax`` (tensor-parallel runs) is applied to the
+        per-token amax of the row-parallel output projection's input."""
+        if not self.causal:
+            raise ValueError("the attention kernels are causal")
+        Hq, Hkv, D = self.num_heads, self.num_kv_heads, self.head_dim
+        dev = y.device
+        if cache is None:  # no cache given: attend within the T new tokens, scratch cache
+            cache = self.init_cache(T, batch=B, device=dev)
+        elif not donate:
+            cache = {"k": cache["k"].clone(), "v": cache["v"].clone(), "position": cache["position"].clone()}
+        max_len = cache["k"].shape[1]
+        wq, col, bias = self.fused_qkv()
+        if self._is_fp8():  # per-token activation scales (vmapped layer, :279)
+            if y_q is None:
+                q, _, inv, _ = ops.quantize_current(y.to(BF16).contiguous(), 1)
+            else:
+                q, inv = y_q
+            qkv = ops.gemm_fp8(q, wq, inv, col, bias)
+        else:
+            qkv = ops.gemm_bf16(y.to(BF16).contiguous(), wq, None, None, bias)
+        if self.rotary_emb is None:
+            raise ValueError("the attention kernels expect rotary embeddings (as the LLM builds them)")
+        cos, sin = self.rotary_emb.tables(max_len, dev)
+        pos = cache["position"]
+        q_rot = ops.kv_append_rope(qkv, B, T, Hq, Hkv, D, pos, cos, sin, cache["k"], cache["v"])
+        scale = 1.0 / math.sqrt(D)
+        if T == 1:
+            attn = ops.attn_decode(q_rot, cache["k"], cache["v"], pos, scale=scale, workspace=workspace)
+        else:
+            attn = ops.attn_prefill(q_rot, cache["k"], cache["v"], pos, B, T, scale=scale)
+        attn2 = attn.reshape(B * T, Hq * D)
+        op = self.output_proj
+        if isinstance(op, Fp8Linear) and op.use_fp8:
+            if reduce_amax is None:
+                aq, _, a_inv, _ = ops.quantize_current(attn2, 1)
+            else:
+                amax = ops.row_amax(attn2)
+                reduce_amax(amax)
+                aq, _, a_inv = ops.quantize_with_amax(attn2, amax, 1)
+            out = op.forward_quantized(aq, a_inv, residual)
+        else:
+            out = apply_linear(attn2, op, residual=residual)
+        if advance:
+            ops.advance_positions(pos, T)  # new_position = p + seq_len (:888), on the device
+        new_cache = {"k": cache["k"], "v": cache["v"], "position": pos}
+        return out, new_cache
+
+
+class TransformerBlock:
+    """xax/arch/attention.py:1214-1510: pre-norm block, x + attn(norm(x)), x + ffn(norm(x))."""
+
+    def __init__(self, self_attn: SelfAttentionBlock, feed_forward: SwiGLU, attn_norm: RMSNorm, mlp_norm: RMSNorm, *,
+                 num_heads: int, head_dim: int, causal: bool, use_fp8: bool = False, cross_attn=None,
+                 cross_attn_norm=None, context_length: int | None = None):
+        if cross_attn is not None or cross_attn_norm is not None or context_length is not None:
+            raise ValueError("cross-attention and sliding windows are outside the path this library covers")
+        self.self_attn, self.feed_forward, self.attn_norm, self.mlp_norm = self_attn, feed_forward, attn_norm, mlp_norm
+        self.num_heads, self.head_dim, self.causal, self.use_fp8 = num_heads, head_dim, causal, use_fp8
+        self.cross_attn, self.cross_attn_norm, self.context_length = None, None, None
+
+    @classmethod
+    def build(cls, embed_dim: int, num_heads: int, ff_dim: int, *, key=None, num_kv_heads: int | None = None,
+              head_dim: int | None = None, causal: bool = False, cross_attention: bool = False,
+              context_length: int | None = None, use_rotary_embeddings: bool = False, rotary_base: float = 10000.0,
+              rotary_style: RotaryEmbeddingStyle = "concatenated", rotary_factor: float = 1.0,
+              rotary_original_max_position_embeddings: int | None = None, rotary_beta_slow: float = 1.0,
+              rotary_beta_fast: float = 32.0, use_qk_norm: bool = False, qk_norm_eps: float = 1e-6,
+              use_attention_sinks: bool = False, norm_type: str = "layernorm", norm_eps: float = 1e-6,
+              feedforward_type: str = "mlp", use_fp8: bool = False, compute_dtype=BF16, fp8_mlp: bool | None = None,
+              device=None) -> "TransformerBlock":
+        """Same keyword arguments as the reference.  ``norm_type`` must be "rmsnorm" and
+        ``feedforward_type`` "swiglu" (the LLM path).  Like the reference, ``use_fp8`` makes the
+        four attention projections FP8 and leaves the SwiGLU on plain linears (:1354-1355);
+        ``fp8_mlp=True`` (an extension) builds the SwiGLU from Fp8Linear too."""
+        if cross_attention:
+            raise ValueError("cross-attention is outside the path this library covers")
+        if norm_type != "rmsnorm" or feedforward_type != "swiglu":
+            raise ValueError("only norm_type='rmsnorm' with feedforward_type='swiglu' is on the path this library covers")
+        seed = int(key or 0) if not isinstance(key, torch.Generator) else int(key.initial_seed())
+        hd = head_dim if head_dim is not None else embed_dim // num_heads
+        attn = SelfAttentionBlock.build(
+            embed_dim, num_heads, key=seed * 3 + 1, num_kv_heads=num_kv_heads, head_dim=head_dim, causal=causal,
+            context_length=context_length, use_rotary_embeddings=use_rotary_embeddings, rotary_base=rotary_base,
+            rotary_style=rotary_style, rotary_factor=rotary_factor,
+            rotary_original_max_position_embeddings=rotary_original_max_position_embeddings,
+            rotary_beta_slow=rotary_beta_slow, rotary_beta_fast=rotary_beta_fast, use_qk_norm=use_qk_norm,
+            qk_norm_eps=qk_norm_eps, use_attention_sinks=use_attention_sinks, use_fp8=use_fp8,
+            compute_dtype=compute_dtype, device=device)
+        ff = SwiGLU.build(embed_dim, ff_dim, key=seed * 3 + 2, use_fp8=bool(fp8_mlp), device=device)
+        return cls(attn, ff, RMSNorm.build(embed_dim, norm_eps, device), RMSNorm.build(embed_dim, norm_eps, device),
+                   num_heads=num_heads, head_dim=hd, causal=causal, use_fp8=use_fp8)
+
+    @property
+    def embed_dim(self) -> int:
+        return self.head_dim * self.num_heads
+
+    def init_cache(self, max_len: int | None = None, dtype=None, context_sn=None, fp8_history_length: int | None = None,
+                   batch: int | None = None) -> TransformerBlockCache:
+        """xax/arch/attention.py:1384-1419."""
+        cache: TransformerBlockCache = {"self_attn": self.self_attn.init_cache(max_len=max_len, dtype=dtype, batch=batch)}
+        if fp8_history_length is not None and self.self_attn.use_fp8:
+            cache["self_attn_fp8"] = _init_fp8_scales_cache(fp8_history_length)
+        return cache
+
+    def init_mask(self, seq_len: int, add_cache: bool = False, batch_dim: bool = False) -> torch.Tensor:
+        return self.self_attn.init_mask(seq_len, add_cache=add_cache, batch_dim=batch_dim)
+
+    def __call__(self, x_tn, *, context_sn=None, mask=None, cache=None, donate: bool = True):
+        return self.forward(x_tn, context_sn=context_sn, mask=mask, cache=cache, donate=donate)
+
+    def forward(self, x_tn: torch.Tensor, *, context_sn=None, mask=None, cache: TransformerBlockCache | None = None,
+                donate: bool = True):
+        """xax/arch/attention.py:1443-1510 for one sequence (T, H)."""
+        if x_tn.dim() != 2:
+            raise ValueError(f"expected rank 2 input, got rank {x_tn.dim()}")
+        if context_sn is not None or mask is not None:
+            raise ValueError("cross-attention context and explicit masks are outside the path this library covers")
+        bc = None
+        if cache is not None:
+            a = cache["self_attn"]
+            bc = {"k": a["k"].unsqueeze(0), "v": a["v"].unsqueeze(0), "position": a["position"].reshape(1)}
+        x, nc = self.forward_tokens(x_tn.to(BF16).contiguous(), 1, x_tn.shape[0], cache=bc, donate=donate)
+        out_cache: TransformerBlockCache = {
+            "self_attn": {"k": nc["k"][0], "v": nc["v"][0], "position": nc["position"].reshape(())}}
+        return x, out_cache
+
+    def forward_tokens(self, x: torch.Tensor, B: int, T: int, *, cache=None, donate: bool = True, workspace=None,
+                       advance: bool = True):
+        """x: [B*T, H] bf16 residual stream of B sequences, T new tokens each; returns the new
+        residual stream and the updated batched attention cache.  Kernel sequence:
+        RMSNorm(+cast) -> QKV GEMM -> RoPE + cache append -> attention -> cast -> out-proj GEMM
+        (+x) -> RMSNorm(+cast / amax) -> gate|up GEMM -> SiLU*up(+cast / amax) -> down GEMM (+x)."""
+        attn, ff = self.self_attn, self.feed_forward
+        wn = self.attn_norm.weight_bf16()
+        if attn._is_fp8():
+            _, yq = ops.rmsnorm(x, wn, self.attn_norm.eps, want_y=False, quantize=True)
+            x1, new_cache = attn.forward_tokens(x, B, T, cache=cache, donate=donate, y_q=(yq[0], yq[2]), residual=x,
+                                                workspace=workspace, advance=advance)
+        else:
+            y, _ = ops.rmsnorm(x, wn, self.attn_norm.eps)
+            x1, new_cache = attn.forward_tokens(y, B, T, cache=cache, donate=donate, residual=x, workspace=workspace,
+                                                advance=advance)
+        wm = self.mlp_norm.weight_bf16()
+        if ff.is_fp8():
+            if T == 1:  # one token per sequence: the per-sequence scale is the per-token scale
+                _, yq = ops.rmsnorm(x1, wm, self.mlp_norm.eps, want_y=False, quantize=True)
+                x2 = ff.forward_tokens(x1, B, T, residual=x1, y_q=(yq[0], yq[2]))
+            else:
+                amax = torch.zeros((B,), dtype=torch.float32, device=x.device)
+                y, _ = ops.rmsnorm(x1, wm, self.mlp_norm.eps, group_amax=amax, group_rows=T)
+                q, _, inv = ops.quantize_with_amax(y, amax, T)
+                x2 = ff.forward_tokens(y, B, T, residual=x1, y_q=(q, inv))
+        else:
+            y, _ = ops.rmsnorm(x1, wm, self.mlp_norm.eps)
+            x2 = ff.forward_tokens(y, B, T, residual=x1)
+        return x2, new_cache
