@@ -1,0 +1,407 @@
+"""Benchmark of the FP8 transformer inference path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload cfg5|cfg4]
+
+A step is one greedy decode step of the whole batch (BASELINE config 5: 8B-shape decoder,
+FP8 linears, batch 128, prompt 2048; config 4: 1.1B shape, batch 64, prompt 512).  The KV
+cache is filled by a real prefill before the timed region.  Rank 0 prints ONE JSON line:
+tokens/s device-timed over K CUDA-graph replays (`value`), the same through the host-facing
+step API with pinned host token buffers (`e2e`), the roofline of the dominant kernel (decode
+attention), the CPU oracle timed on a bounded sample (`cpu_baseline`), SM clocks sampled
+during the timed region, and per-kernel figures for BASELINE configs 1 and 3 (`kernels`).
+With N > 1 (torchrun) the model is tensor-parallel over N GPUs: strong scaling.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+WORKLOADS = {
+    "cfg5": dict(name="cfg5: 8B-shape decoder LLM, FP8 linears, greedy decode", layers=32, hidden=4096, q_heads=32,
+                 kv_heads=8, head_dim=128, ffn=14336, vocab=128256, theta=500000.0, batch=128, prompt=2048, tied=False,
+                 prefill_chunk=8),
+    "cfg4": dict(name="cfg4: 1.1B-shape decoder LLM, FP8 linears, greedy decode", layers=22, hidden=2048, q_heads=32,
+                 kv_heads=4, head_dim=64, ffn=5632, vocab=32000, theta=10000.0, batch=64, prompt=512, tied=True,
+                 prefill_chunk=16),
+}
+
+
+def measured_peaks() -> tuple[float, str]:
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    except Exception:  # noqa: BLE001
+        return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """nvidia-smi clocks / throttle reasons every 200 ms while the timed region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.rows: list[list[str]] = []
+        self.proc = None
+        self.gpu = gpu_index
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.gpu), f"--query-gpu={self.FIELDS}",
+                                          "--format=csv,noheader,nounits", "-lms", "200"], stdout=subprocess.PIPE,
+                                         stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except Exception:  # noqa: BLE001
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.25)
+        self.proc.terminate()
+        sm = sorted(float(r[0]) for r in self.rows if r and r[0].replace(".", "").isdigit())
+        mx = [float(r[1]) for r in self.rows if len(r) > 1 and r[1].replace(".", "").isdigit()]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [n for i, n in enumerate(names) if any(len(r) > 3 + i and r[3 + i] == "Active" for r in self.rows)]
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": mx[0] if mx else None, "reasons": reasons,
+                "samples": len(sm)}
+
+
+# ---------------------------------------------------------------------------------------
+# CPU oracle arm
+
+
+def oracle_decode_sample(w: dict, seconds_budget: float, steps: int, warmup: int):
+    """Times the CPU oracle (the reference's algorithm restated in NumPy) on a bounded sample of
+    the decode workload: ONE transformer layer of the workload's shape plus the lm_head, ONE
+    sequence, a short context; a full step is extrapolated as layers * t_layer + t_head."""
+    import numpy as np
+
+    from oracle import llm as ollm
+
+    cfg = ollm.LLMConfig(vocab_size=w["vocab"], embed_dim=w["hidden"], q_heads=w["q_heads"], kv_heads=w["kv_heads"],
+                         head_dim=w["head_dim"], num_layers=1, mlp_hidden_dim=w["ffn"], rope_theta=w["theta"],
+                         rms_eps=1e-5)
+    rng = np.random.default_rng(0)
+    om = ollm.LLM.build(cfg, rng, use_fp8=True, tie=w["tied"])
+    ctx = 64
+    caches = om.init_cache(ctx + warmup + steps + 1)
+    toks = rng.integers(0, w["vocab"], ctx).astype(np.int32)
+    x = om.embed_tokens(toks)
+    _, c0 = om.blocks[0].forward(x, cache=caches[0])
+    caches = [c0]
+    t_layer, t_head = [], []
+    t_start = time.perf_counter()
+    tok = np.array([1], np.int32)
+    done = 0
+    for i in range(warmup + steps):
+        t0 = time.perf_counter()
+        x = om.embed_tokens(tok)
+        x, c = om.blocks[0].forward(x, cache=caches[0])
+        caches = [c]
+        t1 = time.perf_counter()
+        logits = om.get_logits(om.norm(x))
+        tok = np.array([ollm.greedy_token(logits[-1])], np.int32)
+        t2 = time.perf_counter()
+        if i >= warmup:
+            t_layer.append(t1 - t0)
+            t_head.append(t2 - t1)
+            done += 1
+        if time.perf_counter() - t_start > seconds_budget and done >= 1:
+            break
+    tl, th = float(np.median(t_layer)), float(np.median(t_head))
+    step_s = w["layers"] * tl + th  # one sequence
+    return {"tokens_per_s": 1.0 / step_s, "step_s_one_sequence": step_s, "steps_timed": done,
+            "sample": f"NumPy oracle, 1 of {w['layers']} layers + lm_head, 1 of {w['batch']} sequences, context {ctx} "
+                      f"(not {w['prompt']}+); step time extrapolated as {w['layers']}*t_layer+t_head; "
+                      f"{done} steps timed; the reference re-quantises every weight on every call and so does this"}
+
+
+def host_threads() -> int:
+    try:
+        return len(os.sched_getaffinity(0))
+    except Exception:  # noqa: BLE001
+        return os.cpu_count() or 1
+
+
+# ---------------------------------------------------------------------------------------
+# per-kernel figures (BASELINE configs 1 and 3)
+
+
+def _time_kernel(fn, iters=20, warm=3, flush=None):
+    import torch
+
+    for _ in range(warm):
+        fn()
+    total = 0.0
+    for _ in range(iters):
+        if flush is not None:
+            flush.zero_()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        fn()
+        e1.record()
+        e1.synchronize()
+        total += e0.elapsed_time(e1)
+    return total / iters * 1e-3
+
+
+def kernel_figures(peak_gbs: float) -> dict:
+    """cfg1: quantize (HBM) and FP8 GEMM (tensor); cfg3: decode attention (HBM).  L2 is flushed
+    (a 512 MiB buffer is rewritten) between timed launches."""
+    import numpy as np
+    import torch
+
+    from xax_b200 import ops
+
+    dev = "cuda"
+    out = {}
+    flush = torch.empty(512 << 20, dtype=torch.uint8, device=dev)
+    g = torch.Generator(device=dev).manual_seed(0)
+    # ---- cfg1: x[2048,2048] bf16 N(0,1) with 0.1 % x20 outliers, W (8192,2048) N(0,0.02^2)
+    M, K, N = 2048, 2048, 8192
+    x = torch.randn((M, K), generator=g, device=dev)
+    x = torch.where(torch.rand((M, K), generator=g, device=dev) < 1e-3, x * 20, x).to(torch.bfloat16)
+    w = (torch.randn((N, K), generator=g, device=dev) * 0.02).to(torch.bfloat16)
+    bias = (torch.randn((N,), generator=g, device=dev) * 0.01).to(torch.bfloat16)
+    scale = torch.tensor(448.0 / 100.0, device=dev)
+    hist = torch.zeros(16, device=dev)
+    t = _time_kernel(lambda: ops.quantize_delayed(x, scale, hist), flush=flush)
+    out["quantize_cfg1"] = {"gbs": M * K * 3 / t / 1e9, "frac_of_hbm_peak": M * K * 3 / t / 1e9 / peak_gbs,
+                            "us": t * 1e6, "bytes": M * K * 3}
+    xq, _, _, x_inv = ops.quantize_delayed(x, scale, hist)
+    wq, _, w_inv, _ = ops.quantize_current(w, N)
+    o = torch.empty((M, N), dtype=torch.bfloat16, device=dev)
+    t = _time_kernel(lambda: ops.gemm_fp8(xq, wq, x_inv, w_inv[:1], bias, out=o), flush=flush)
+    out["gemm_fp8_cfg1"] = {"tflops": 2.0 * M * N * K / t / 1e12, "us": t * 1e6,
+                            "frac_of_4500_nominal": 2.0 * M * N * K / t / 4.5e15}
+    M2 = N2 = K2 = 8192
+    a8 = (torch.randn((M2, K2), generator=g, device=dev)).to(torch.float8_e4m3fn)
+    b8 = (torch.randn((N2, K2), generator=g, device=dev)).to(torch.float8_e4m3fn)
+    o2 = torch.empty((M2, N2), dtype=torch.bfloat16, device=dev)
+    t = _time_kernel(lambda: ops.gemm_fp8(a8, b8, None, None, None, out=o2), iters=10, flush=flush)
+    out["gemm_fp8_8192"] = {"tflops": 2.0 * M2 * N2 * K2 / t / 1e12, "us": t * 1e6,
+                            "frac_of_4500_nominal": 2.0 * M2 * N2 * K2 / t / 4.5e15}
+    del a8, b8, o2
+    # ---- cfg3: B=32, 32q/8kv x 128, lengths U[512, 8192], theta 5e5
+    B, Hq, Hkv, D, max_len = 32, 32, 8, 128, 8192
+    lens = torch.from_numpy(np.random.default_rng(0).integers(512, 8193, B).astype(np.int32)).to(dev)
+    kc = torch.randn((B, max_len, Hkv, D), generator=g, device=dev, dtype=torch.bfloat16)
+    vc = torch.randn((B, max_len, Hkv, D), generator=g, device=dev, dtype=torch.bfloat16)
+    q = torch.randn((B, Hq, D), generator=g, device=dev, dtype=torch.bfloat16)
+    pos = lens - 1
+    ws = ops.attn_decode_workspace(B, Hq, D, max_len, dev)
+    ao = torch.empty_like(q)
+    cos, sin = ops.rope_tables(D, 500000.0, max_len, dev)
+    nbytes = int(lens.sum().item()) * (2 * Hkv * D * 2) + 2 * B * Hq * D * 2
+    t = _time_kernel(lambda: ops.attn_decode(q, kc, vc, pos, workspace=ws, out=ao), flush=flush)
+    out["attn_decode_cfg3"] = {"gbs": nbytes / t / 1e9, "frac_of_hbm_peak": nbytes / t / 1e9 / peak_gbs, "us": t * 1e6,
+                               "bytes": nbytes}
+    t = _time_kernel(lambda: ops.attn_decode(q, kc, vc, pos, workspace=ws, out=ao, k_is_rotated=False, cos=cos,
+                                             sin=sin), flush=flush)
+    out["attn_decode_cfg3_rope_on_load"] = {"gbs": nbytes / t / 1e9, "frac_of_hbm_peak": nbytes / t / 1e9 / peak_gbs,
+                                            "us": t * 1e6}
+    return out
+
+
+# ---------------------------------------------------------------------------------------
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=128)
+    ap.add_argument("--warmup", type=int, default=4)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="cfg5", choices=sorted(WORKLOADS))
+    ap.add_argument("--no-kernels", action="store_true", help="skip the per-kernel figures")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU oracle timing")
+    ap.add_argument("--synthetic-kv", action="store_true", help="fill the KV cache with N(0,1) instead of a prefill")
+    args = ap.parse_args()
+    w = WORKLOADS[args.workload]
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    warmup = max(args.warmup, 3)
+    metric, unit = "llm_decode_tokens_per_s", "tokens/s"
+    base = {"metric": metric, "unit": unit, "n_gpus": args.gpus, "steps": args.steps, "warmup": warmup,
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "fp8_e4m3 (bf16 activations)",
+            "data": "synthetic", "config": {"workload": w["name"], "batch": w["batch"], "prompt": w["prompt"],
+                                            "layers": w["layers"], "hidden": w["hidden"],
+                                            "parallelism": f"tp{args.gpus}",
+                                            "l2": "inputs (weights + KV cache) far larger than L2"}}
+
+    if args.impl == "reference":
+        if rank != 0:
+            return
+        r = oracle_decode_sample(w, seconds_budget=150.0, steps=args.steps, warmup=1)
+        line = dict(base)
+        line.update({"impl": "reference", "value": r["tokens_per_s"], "ms_per_step": r["step_s_one_sequence"] * 1e3,
+                     "dtype": "bf16/e4m3 emulated in float32 (NumPy)",
+                     "cpu_baseline": {"value": r["tokens_per_s"], "unit": unit, "cores": host_threads(),
+                                      "kind": "port", "sample": r["sample"]},
+                     "e2e": {"value": r["tokens_per_s"], "unit": unit, "h2d_bytes_per_step": 0,
+                             "d2h_bytes_per_step": 0},
+                     "gpu_launches": 0})
+        print(json.dumps(line), flush=True)
+        return
+
+    import torch
+    import torch.distributed as dist
+
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    tp = None
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+        from xax_b200.parallel import TensorParallel
+
+        tp = TensorParallel(rank, world)
+    from xax_b200 import _lib, ops
+    from xax_b200.arch.llm import LLM, DecodeState, LLMConfig, tie_embedding_and_head
+
+    cfg = LLMConfig(vocab_size=w["vocab"], embed_dim=w["hidden"], q_heads=w["q_heads"], kv_heads=w["kv_heads"],
+                    head_dim=w["head_dim"], num_layers=w["layers"], mlp_hidden_dim=w["ffn"], rope_theta=w["theta"],
+                    rms_eps=1e-5)
+    model = LLM.build(cfg, key=0, use_fp8=True, init_std=0.02, device=dev, tp_rank=rank, tp_size=world)
+    if w["tied"]:
+        model = tie_embedding_and_head(model)
+    if tp is not None:
+        tp.shard_lm_head(model)
+    B, T0 = w["batch"], w["prompt"]
+    K = args.steps
+    max_len = (T0 + warmup + K + 8 + 127) // 128 * 128
+    st = DecodeState(model, B, max_len, tp=tp)
+    gen = torch.Generator(device=dev).manual_seed(1)
+    t_prefill = None
+    if args.synthetic_kv:
+        for c in st.caches:
+            c["k"][:, :T0].normal_(generator=gen)
+            c["v"][:, :T0].normal_(generator=gen)
+        st.positions.fill_(T0)
+        st.cur.copy_(torch.randint(0, w["vocab"], (B,), generator=gen, device=dev, dtype=torch.int32))
+        st.step()  # builds the weight caches
+    else:
+        prompt = torch.randint(0, w["vocab"], (B, T0), generator=gen, device=dev, dtype=torch.int32)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        st.prefill(prompt[:w["prefill_chunk"]].contiguous(), w["prefill_chunk"])  # warm: quantises the weights
+        st.positions.zero_()
+        torch.cuda.synchronize()
+        e0.record()
+        st.prefill(prompt, w["prefill_chunk"])
+        e1.record()
+        torch.cuda.synchronize()
+        t_prefill = e0.elapsed_time(e1) * 1e-3
+    _lib.device_status()
+    ops.LAUNCH_COUNT = 0
+    st.capture()
+    launches_per_step = ops.LAUNCH_COUNT // 2  # capture() runs the step twice (warm-up + capture)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(warmup):
+        st.replay()
+    sampler = ClockSampler(local_rank)
+    barrier()
+    sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(K):
+        st.replay()
+    e1.record()
+    barrier()
+    clocks = sampler.stop()
+    elapsed = e0.elapsed_time(e1) * 1e-3
+    if world > 1:
+        tmax = torch.tensor([elapsed], device=dev)
+        dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
+        elapsed = float(tmax.item())
+    _lib.device_status()
+    mean_len_timed = T0 + warmup + (K + 1) / 2.0
+
+    # ---- e2e: the same steps through the host-facing API (pinned host tokens in and out)
+    tin = torch.empty((B,), dtype=torch.int32).pin_memory()
+    tout = torch.empty((B,), dtype=torch.int32).pin_memory()
+    tin.copy_(st.cur.cpu())
+    st.positions.fill_(T0 + warmup)  # same context range as the device-timed region
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(K):
+        st.step_host(tin, tout)
+        tin, tout = tout, tin
+    barrier()
+    e2e_elapsed = time.perf_counter() - t0
+    if world > 1:
+        tmax = torch.tensor([e2e_elapsed], device=dev)
+        dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
+        e2e_elapsed = float(tmax.item())
+    _lib.device_status()
+
+    # ---- roofline of the dominant kernel: eager steps with CUDA events around every decode-attention launch
+    peak, peak_kind = measured_peaks()
+    hkv_local, hq_local, D = w["kv_heads"] // world, w["q_heads"] // world, w["head_dim"]
+    st.positions.fill_(int(mean_len_timed) - 1)  # representative length: the mean of the timed region
+    ops.KERNEL_TIMES = []
+    n_eager = 2
+    for _ in range(n_eager):
+        st.step()
+    torch.cuda.synchronize()
+    durs = [a.elapsed_time(b) * 1e-3 for name, a, b in ops.KERNEL_TIMES if name == "attn_decode"]
+    ops.KERNEL_TIMES = None
+    attn_len = int(mean_len_timed) + 0.5
+    attn_bytes = B * attn_len * (2 * hkv_local * D * 2) + 2 * B * hq_local * D * 2
+    avg = sum(durs) / max(len(durs), 1)
+    roofline = {"bound": "hbm", "kernel": "attn_decode_kernel (+ its merge pass)", "achieved": attn_bytes / avg / 1e9,
+                "peak": peak, "peak_kind": f"of {peak_kind} copy bandwidth", "unit": "GB/s",
+                "frac": attn_bytes / avg / 1e9 / peak, "traffic": None, "bytes_per_launch": attn_bytes,
+                "avg_launch_us": avg * 1e6, "launches_timed": len(durs)}
+    _lib.device_status()
+
+    if rank != 0:
+        if world > 1:
+            dist.barrier()
+        return
+    line = dict(base)
+    line.update({"value": B * K / elapsed, "ms_per_step": elapsed / K * 1e3, "clocks": clocks,
+                 "e2e": {"value": B * K / e2e_elapsed, "unit": unit, "h2d_bytes_per_step": B * 4,
+                         "d2h_bytes_per_step": B * 4, "ms_per_step": e2e_elapsed / K * 1e3},
+                 "gpu_launches": launches_per_step * K, "launches_per_step": launches_per_step,
+                 "roofline": roofline, "prefill_s": t_prefill,
+                 "mean_context_timed": mean_len_timed})
+    if not args.no_kernels:
+        del st
+        torch.cuda.empty_cache()
+        try:
+            line["kernels"] = kernel_figures(peak)
+        except Exception as e:  # noqa: BLE001
+            line["kernels"] = {"error": repr(e)}
+    if not args.no_cpu:
+        r = oracle_decode_sample(w, seconds_budget=20.0, steps=2, warmup=0)
+        line["cpu_baseline"] = {"value": r["tokens_per_s"], "unit": unit, "cores": host_threads(), "kind": "port",
+                                "sample": r["sample"]}
+    else:
+        line["cpu_baseline"] = None
+    print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+
+
+if __name__ == "__main__":
+    main()

@@ -317,7 +317,7 @@ def build_block(rng, *, embed_dim, num_heads, num_kv_heads, head_dim, ff_dim, ro
     attention; for the MLP they are swapped into SwiGLU, which apply_linear accepts :52)."""
 
     def w(o, i, s=1.0):
-        return (rng.standard_normal((o, i)) * std * s).astype(float32).astype(dtype)
+        return (rng.standard_normal((o, i), dtype=float32) * float32(std * s)).astype(dtype)
 
     def lin(o, i, fp8, s=1.0, bias=False):
         b = np.zeros((o,), dtype) if bias else None

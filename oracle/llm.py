@@ -40,7 +40,7 @@ class LLM:
     @classmethod
     def build(cls, config: LLMConfig, rng, *, use_fp8=True, tie=True, std=0.02, dtype=bfloat16) -> "LLM":
         """Random-init model: N(0, std^2) weights, bf16, FP8 projections when ``use_fp8``."""
-        embed = Embedding((rng.standard_normal((config.vocab_size, config.embed_dim)) * std).astype(float32).astype(dtype))
+        embed = Embedding((rng.standard_normal((config.vocab_size, config.embed_dim), dtype=float32) * float32(std)).astype(dtype))
         width = config.mlp_hidden_dim or config.embed_dim * config.mlp_mult  # :109
         blocks = [
             build_block(rng, embed_dim=config.embed_dim, num_heads=config.q_heads, num_kv_heads=config.kv_heads,
@@ -52,7 +52,7 @@ class LLM:
         if tie:  # tie_embedding_and_head, :713-715
             head = Linear(embed.weight)
         else:
-            head = Linear((rng.standard_normal((config.vocab_size, config.embed_dim)) * std).astype(float32).astype(dtype))
+            head = Linear((rng.standard_normal((config.vocab_size, config.embed_dim), dtype=float32) * float32(std)).astype(dtype))
         return cls(embed, blocks, norm, head, config)
 
     def embed_tokens(self, tokens_t):  # :205-211

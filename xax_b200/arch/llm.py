@@ -355,6 +355,20 @@ class DecodeState:
         self.graph.replay()
         return self.cur
 
+    def step_host(self, tokens_in: torch.Tensor, tokens_out: torch.Tensor) -> torch.Tensor:
+        """One decode step driven from the host: ``tokens_in`` (pinned host int32 [B], the token
+        each sequence consumes) is copied to the device, the step runs (graph replay when
+        captured), and the produced tokens are copied into ``tokens_out`` (pinned host int32 [B])
+        and returned once they have arrived."""
+        self.cur.copy_(tokens_in, non_blocking=True)
+        if self.graph is not None:
+            self.graph.replay()
+        else:
+            self.step()
+        tokens_out.copy_(self.cur, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+        return tokens_out
+
 
 def llm_generate_batch(model: LLM, tokens_bt: torch.Tensor, max_new_tokens: int, *, eos_id: int = -1,
                        use_graph: bool = True, prefill_chunk: int | None = None, tp=None):

@@ -18,9 +18,35 @@ from ._lib import check, ptr
 E4M3 = torch.float8_e4m3fn
 BF16 = torch.bfloat16
 
+# Kernel launches issued through this module since the counter was last cleared (graph
+# replays re-issue the launches recorded at capture time; callers account for that).
+LAUNCH_COUNT = 0
+# When set to a list, (name, start_event, end_event) is appended around selected kernels.
+KERNEL_TIMES: list | None = None
 
-def _c():
+
+def _c(launches: int = 1):
+    global LAUNCH_COUNT
+    LAUNCH_COUNT += launches
     return _lib.ctx(), _lib.stream_ptr(), _lib.load()
+
+
+class _Timed:
+    def __init__(self, name: str):
+        self.name = name
+
+    def __enter__(self):
+        if KERNEL_TIMES is not None:
+            self.e0 = torch.cuda.Event(enable_timing=True)
+            self.e0.record()
+        return self
+
+    def __exit__(self, *exc):
+        if KERNEL_TIMES is not None:
+            e1 = torch.cuda.Event(enable_timing=True)
+            e1.record()
+            KERNEL_TIMES.append((self.name, self.e0, e1))
+        return False
 
 
 def _req(t: torch.Tensor, dtype, name: str) -> torch.Tensor:
@@ -41,7 +67,7 @@ def quantize_current(x: torch.Tensor, group_rows: int = 1):
     group_rows = 1: a scale per row (per token); group_rows = rows: one scale per tensor."""
     x = _req(x, BF16, "x")
     rows, cols = x.shape
-    ctx, st, lib = _c()
+    ctx, st, lib = _c(1 if group_rows == 1 else 2)
     q = torch.empty((rows, cols), dtype=E4M3, device=x.device)
     scale = torch.empty((rows,), dtype=torch.float32, device=x.device)
     inv = torch.empty((rows,), dtype=torch.float32, device=x.device)
@@ -70,7 +96,7 @@ def quantize_delayed(x: torch.Tensor, scale_in: torch.Tensor, history: torch.Ten
     rows, cols = x2.shape
     scale_in = _req(scale_in, torch.float32, "scale_in")
     history = _req(history, torch.float32, "history")
-    ctx, st, lib = _c()
+    ctx, st, lib = _c(2)
     q = torch.empty((rows, cols), dtype=E4M3, device=x.device) if cast else None
     new_hist = torch.empty_like(history)
     new_scale = torch.empty((), dtype=torch.float32, device=x.device)
@@ -111,8 +137,9 @@ def _gemm(fn_name, a, b, row_mul, col_mul, bias, residual, out):
     col_mul, cs = _mul_arg(col_mul, N, "col_mul")
     ldr = residual.stride(0) if residual is not None else 0
     fn = getattr(lib, fn_name)
-    check(fn(ctx, st, ptr(a), a.stride(0), ptr(b), b.stride(0), M, N, K, ptr(row_mul), rs, ptr(col_mul), cs, ptr(bias),
-             ptr(residual), ldr, ptr(out), out.stride(0)), fn_name)
+    with _Timed(fn_name):
+        check(fn(ctx, st, ptr(a), a.stride(0), ptr(b), b.stride(0), M, N, K, ptr(row_mul), rs, ptr(col_mul), cs,
+                 ptr(bias), ptr(residual), ldr, ptr(out), out.stride(0)), fn_name)
     return out
 
 
@@ -247,17 +274,18 @@ def attn_decode(q_rot, k_cache, v_cache, positions, *, scale=None, k_is_rotated=
     """One query token per sequence; attends to cache rows 0 .. positions[b]."""
     B, Hq, D = q_rot.shape
     _, max_len, Hkv, _ = k_cache.shape
-    ctx, st, lib = _c()
+    ctx, st, lib = _c(2)
     if workspace is None:
         workspace = attn_decode_workspace(B, Hq, D, max_len, q_rot.device)
     if out is None:
         out = torch.empty_like(q_rot)
     if scale is None:
         scale = 1.0 / math.sqrt(D)
-    check(lib.xaxb_attn_decode(ctx, st, ptr(q_rot), ptr(k_cache), ptr(v_cache), ptr(positions), B, Hq, Hkv, D, max_len,
-                               float(scale), 1 if k_is_rotated else 0, ptr(cos), ptr(sin),
-                               0 if cos is None else cos.shape[0], ptr(out), ptr(workspace),
-                               workspace.numel() * 4), "attn_decode")
+    with _Timed("attn_decode"):
+        check(lib.xaxb_attn_decode(ctx, st, ptr(q_rot), ptr(k_cache), ptr(v_cache), ptr(positions), B, Hq, Hkv, D,
+                                   max_len, float(scale), 1 if k_is_rotated else 0, ptr(cos), ptr(sin),
+                                   0 if cos is None else cos.shape[0], ptr(out), ptr(workspace),
+                                   workspace.numel() * 4), "attn_decode")
     return out
 
 
