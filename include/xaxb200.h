@@ -197,6 +197,25 @@ int xaxb_attn_decode(xaxb_ctx* ctx, void* stream, const void* q_rot_bf16, const 
                      int64_t workspace_bytes);
 
 /*
+ * Decode attention without any memory from the caller beyond inputs and outputs.
+ * No counterpart in the reference: this entry exists for callers that cannot allocate --
+ * custom-call handlers that only see pre-declared buffers, serving loops that ban cudaMalloc
+ * because it synchronises the device, embedders that keep the allocator to themselves.
+ * Same contract and results as xaxb_attn_decode, but the per-chunk partial results go into
+ * a 16 MiB array built into the library image (held by every GPU that loads the library until
+ * the process exits; xaxb_attn_decode_static_capacity_bytes).  Shapes whose scratch
+ * (xaxb_attn_decode_workspace_bytes) exceeds that are refused with XAXB_WORKSPACE_TOO_SMALL.
+ * The context's device must be current.  The first call on a device looks up the array's
+ * device address; make that first call outside any stream capture.  All calls share the
+ * array: calls that overlap on the GPU race and must be serialised by the caller.
+ */
+int64_t xaxb_attn_decode_static_capacity_bytes(void);
+int xaxb_attn_decode_static(xaxb_ctx* ctx, void* stream, const void* q_rot_bf16, const void* k_cache_bf16,
+                            const void* v_cache_bf16, const int32_t* positions, int64_t B, int64_t Hq, int64_t Hkv,
+                            int64_t D, int64_t max_len, float softmax_scale, int k_is_rotated, const void* cos_bf16,
+                            const void* sin_bf16, int64_t table_len, void* out_bf16);
+
+/*
  * Causal prefill attention for T new tokens per sequence against the cache (which
  * already holds them, written by xaxb_kv_append_rope): query i of sequence b sits at
  * position positions[b] + i and attends to cache rows 0 .. positions[b] + i

@@ -404,3 +404,73 @@ int xaxb_attn_decode(xaxb_ctx* ctx_, void* stream, const void* q_rot_bf16, const
 }
 
 }  // extern "C"
+
+// ---------------------------------------------------------------------------------------
+// Allocation-free variant of decode attention.
+//
+// Some callers cannot obtain device memory at the point where they run attention: code
+// that executes inside a framework's custom-call handler where only the buffers declared
+// up front exist, real-time serving loops that forbid cudaMalloc because it synchronises
+// the device, and embedders that own the allocator and hand this library nothing but input
+// and output pointers.  For them the per-chunk partial results live in a fixed array that is
+// part of the loaded library image instead of a caller-provided workspace.
+//
+// The array costs every GPU that loads the library kStaticScratchBytes of device memory until
+// the process exits.  It is shared by all calls and keeps whatever the previous call left in
+// it; the decode kernel writes every slot it later reads, so nothing needs clearing.  Two
+// calls that overlap on the GPU (different streams) would write the same slots: callers must
+// serialise them.
+
+namespace xaxb {
+
+constexpr long long kStaticScratchBytes = 16ll << 20;  // 16 MiB per GPU
+constexpr int kMaxDevices = 64;
+
+static __device__ __align__(256) unsigned char g_decode_scratch[kStaticScratchBytes];
+
+// Device address of g_decode_scratch per device ordinal.  In host code the array's name is
+// only a handle for the runtime, not an address a kernel could use, so the address is looked
+// up once per device (with that device current) and cached.
+static void* g_decode_scratch_addr[kMaxDevices] = {nullptr};
+
+}  // namespace xaxb
+
+extern "C" int64_t xaxb_attn_decode_static_capacity_bytes(void) { return xaxb::kStaticScratchBytes; }
+
+extern "C" int xaxb_attn_decode_static(xaxb_ctx* ctx_, void* stream, const void* q_rot_bf16, const void* k_cache_bf16,
+                                       const void* v_cache_bf16, const int32_t* positions, int64_t B, int64_t Hq,
+                                       int64_t Hkv, int64_t D, int64_t max_len, float softmax_scale, int k_is_rotated,
+                                       const void* cos_bf16, const void* sin_bf16, int64_t table_len, void* out_bf16) {
+  if (!ctx_) return XAXB_BAD_ARGUMENT;
+  const Ctx* ctx = reinterpret_cast<const Ctx*>(ctx_);
+  if (B <= 0 || Hq <= 0 || D <= 0 || max_len <= 0) {
+    set_last_error("attn_decode_static: non-positive shape");
+    return XAXB_BAD_ARGUMENT;
+  }
+  const int64_t need = xaxb_attn_decode_workspace_bytes(B, Hq, D, max_len);
+  if (need > kStaticScratchBytes) {
+    set_last_error("attn_decode_static: B=%lld Hq=%lld D=%lld max_len=%lld needs %lld bytes of scratch, the built-in "
+                   "array holds %lld; use xaxb_attn_decode with a caller-provided workspace",
+                   (long long)B, (long long)Hq, (long long)D, (long long)max_len, (long long)need,
+                   (long long)kStaticScratchBytes);
+    return XAXB_WORKSPACE_TOO_SMALL;
+  }
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess || dev < 0 || dev >= kMaxDevices || dev != ctx->device) {
+    set_last_error("attn_decode_static: the context's device (%d) must be current (current: %d)", ctx->device, dev);
+    return XAXB_BAD_ARGUMENT;
+  }
+  if (!g_decode_scratch_addr[dev]) {  // first call on this device: not inside a stream capture
+    void* p = nullptr;
+    e = cudaGetSymbolAddress(&p, g_decode_scratch);
+    if (e != cudaSuccess || !p) {
+      set_last_error("attn_decode_static: cudaGetSymbolAddress: %s", cudaGetErrorString(e));
+      return XAXB_LAUNCH_FAILED;
+    }
+    g_decode_scratch_addr[dev] = p;
+  }
+  return xaxb_attn_decode(ctx_, stream, q_rot_bf16, k_cache_bf16, v_cache_bf16, positions, B, Hq, Hkv, D, max_len,
+                          softmax_scale, k_is_rotated, cos_bf16, sin_bf16, table_len, out_bf16,
+                          g_decode_scratch_addr[dev], kStaticScratchBytes);
+}

@@ -289,6 +289,27 @@ def attn_decode(q_rot, k_cache, v_cache, positions, *, scale=None, k_is_rotated=
     return out
 
 
+def attn_decode_static(q_rot, k_cache, v_cache, positions, *, scale=None, k_is_rotated=True, cos=None, sin=None,
+                       out=None):
+    """Decode attention for callers that can hand over no scratch memory: identical to
+    ``attn_decode`` except that the partial results live in an array inside the library (16 MiB
+    per GPU).  Shapes needing more raise; calls must not overlap on the GPU."""
+    B, Hq, D = q_rot.shape
+    _, max_len, Hkv, _ = k_cache.shape
+    ctx, st, lib = _c(2)
+    if out is None:
+        out = torch.empty_like(q_rot)
+    if scale is None:
+        scale = 1.0 / math.sqrt(D)
+    rc = lib.xaxb_attn_decode_static(ctx, st, ptr(q_rot), ptr(k_cache), ptr(v_cache), ptr(positions), B, Hq, Hkv, D,
+                                     max_len, float(scale), 1 if k_is_rotated else 0, ptr(cos), ptr(sin),
+                                     0 if cos is None else cos.shape[0], ptr(out))
+    if rc == _lib.WORKSPACE_TOO_SMALL:
+        raise ValueError(f"attn_decode_static: {lib.xaxb_last_error().decode()}")
+    check(rc, "attn_decode_static")
+    return out
+
+
 def attn_prefill(q_rot, k_cache, v_cache, positions, B, T, *, scale=None, out=None):
     """Causal attention of T new tokens per sequence (already in the cache) against the cache."""
     _, Hq, D = q_rot.shape
