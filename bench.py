@@ -281,6 +281,7 @@ def main() -> None:
     if w["tied"]:
         model = tie_embedding_and_head(model)
     if tp is not None:
+        tp.prepare_model(model)
         tp.shard_lm_head(model)
     B, T0 = w["batch"], w["prompt"]
     K = args.steps

@@ -142,6 +142,12 @@ int xaxb_silu_mul(xaxb_ctx* ctx, void* stream, const void* gate_bf16, const void
                   int64_t dim, void* h_bf16, void* q_e4m3, float* scale, float* inv_scale, float* group_amax,
                   int64_t group_rows);
 
+/* amax[g] = max|x| over group g of `group_rows` rows (float32; cleared by the call): the first
+ * pass of xaxb_quantize_current on its own, for tensor-parallel ranks that must max-reduce the
+ * amax of a row-parallel layer's input across ranks before casting. */
+int xaxb_group_amax(xaxb_ctx* ctx, void* stream, const void* x_bf16, int64_t rows, int64_t cols, int64_t group_rows,
+                    float* amax);
+
 /* Second pass of a per-group quantisation whose amax was accumulated by xaxb_rmsnorm /
  * xaxb_silu_mul: scales from group_amax, then the cast (same outputs as
  * xaxb_quantize_current; group_amax is read, not cleared). */
@@ -153,9 +159,16 @@ int xaxb_quantize_with_amax(xaxb_ctx* ctx, void* stream, const void* x_bf16, int
 int xaxb_embed(xaxb_ctx* ctx, void* stream, const int32_t* tokens, int64_t n_tokens, const void* table_bf16,
                int64_t vocab, int64_t dim, void* x_bf16);
 
-/* out[i] = argmax_j float32(logits[i, j]), first index on ties (xax/arch/llm.py:1466-1470). */
+/* out[i] = argmax_j float32(logits[i, j]), first index on ties, NaN counted as the maximum
+ * (xax/arch/llm.py:1466-1470).  max_out (may be NULL) receives the winning value. */
 int xaxb_argmax(xaxb_ctx* ctx, void* stream, const void* logits_bf16, int64_t rows, int64_t vocab, int64_t ld,
-                int32_t* out);
+                int32_t* out, float* max_out);
+
+/* Arg-max over a vocabulary split into `parts` slices of `slice` columns (the column-parallel
+ * lm_head of xax/arch/llm.py:970-972): part_max / part_idx are [parts, rows] results of
+ * xaxb_argmax on each slice; out[i] is the global index, lower index on ties. */
+int xaxb_argmax_merge(xaxb_ctx* ctx, void* stream, const float* part_max, const int32_t* part_idx, int64_t parts,
+                      int64_t rows, int64_t slice, int32_t* out);
 
 /* ---- kernel 3: GQA attention with RoPE and a bf16 KV cache -------------------------- */
 

@@ -46,7 +46,9 @@ SIGNATURES: dict[str, tuple] = {
     "xaxb_rmsnorm": (_I, [_P, _P, _P, _P, _F, _I64, _I64, _P, _P, _P, _P, _P, _I64]),
     "xaxb_silu_mul": (_I, [_P, _P, _P, _P, _I64, _I64, _I64, _P, _P, _P, _P, _P, _I64]),
     "xaxb_embed": (_I, [_P, _P, _P, _I64, _P, _I64, _I64, _P]),
-    "xaxb_argmax": (_I, [_P, _P, _P, _I64, _I64, _I64, _P]),
+    "xaxb_argmax": (_I, [_P, _P, _P, _I64, _I64, _I64, _P, _P]),
+    "xaxb_argmax_merge": (_I, [_P, _P, _P, _P, _I64, _I64, _I64, _P]),
+    "xaxb_group_amax": (_I, [_P, _P, _P, _I64, _I64, _I64, _P]),
     "xaxb_kv_append_rope": (_I, [_P, _P, _P, _I64, _I64, _I64, _I64, _I64, _I64, _P, _P, _P, _I64, _P, _P, _P, _I64, _I]),
     "xaxb_attn_decode_workspace_bytes": (_I64, [_I64, _I64, _I64, _I64]),
     "xaxb_attn_decode": (_I, [_P, _P, _P, _P, _P, _P, _I64, _I64, _I64, _I64, _I64, _F, _I, _P, _P, _I64, _P, _P, _I64]),

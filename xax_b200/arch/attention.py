@@ -402,7 +402,7 @@ class SelfAttentionBlock:
             if reduce_amax is None:
                 aq, _, a_inv, _ = ops.quantize_current(attn2, 1)
             else:
-                amax = ops.row_amax(attn2)
+                amax = ops.group_amax(attn2, 1)
                 reduce_amax(amax)
                 aq, _, a_inv = ops.quantize_with_amax(attn2, amax, 1)
             out = op.forward_quantized(aq, a_inv, residual)

@@ -108,6 +108,8 @@ class LLM:
 
         def lin(o, i, name, bias):
             w = shard(_randn((o, i), std, gen, dev), name)
+            if tp_shard_dim(name, 2) == 1 and tp_rank > 0:
+                bias = False  # a row-parallel layer's bias is added once, by rank 0
             b = torch.zeros((w.shape[0],), dtype=BF16, device=dev) if bias else None
             if use_fp8:
                 return Fp8Linear(w.shape[1], w.shape[0], weight=w, bias=b, use_bias=bias)

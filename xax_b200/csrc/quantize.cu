@@ -177,6 +177,27 @@ int xaxb_quantize_current(xaxb_ctx* ctx, void* stream, const void* x_bf16, int64
   return check_launch("group_cast_kernel");
 }
 
+int xaxb_group_amax(xaxb_ctx* ctx, void* stream, const void* x_bf16, int64_t rows, int64_t cols, int64_t group_rows,
+                    float* amax) {
+  if (!ctx || !amax) return XAXB_BAD_ARGUMENT;
+  int rc = check_quant_args(x_bf16, rows, cols);
+  if (rc) return rc;
+  if (group_rows <= 0 || rows % group_rows != 0 || rows / group_rows > 65535) {
+    set_last_error("group_amax: bad grouping rows=%lld group_rows=%lld", (long long)rows, (long long)group_rows);
+    return XAXB_BAD_ARGUMENT;
+  }
+  const Ctx* c = reinterpret_cast<const Ctx*>(ctx);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const int64_t groups = rows / group_rows;
+  const int64_t vec_per_group = group_rows * cols / 8;
+  cudaMemsetAsync(amax, 0, groups * sizeof(float), s);
+  int64_t cap = ((int64_t)c->num_sms * 8 + groups - 1) / groups;
+  dim3 grid(grid_for(vec_per_group, c->num_sms, cap), (unsigned)groups);
+  group_amax_kernel<<<grid, 256, 0, s>>>(static_cast<const uint4*>(x_bf16), vec_per_group,
+                                         reinterpret_cast<unsigned int*>(amax));
+  return check_launch("group_amax_kernel");
+}
+
 int xaxb_quantize_with_amax(xaxb_ctx* ctx, void* stream, const void* x_bf16, int64_t rows, int64_t cols,
                             int64_t group_rows, const float* group_amax, void* q_e4m3, float* scale,
                             float* inv_scale) {

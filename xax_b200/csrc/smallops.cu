@@ -128,7 +128,8 @@ __device__ __forceinline__ bool better(float v, int i, float bv, int bi) {
 }
 
 __global__ void __launch_bounds__(1024) argmax_kernel(const __nv_bfloat16* __restrict__ logits, int64_t vocab,
-                                                      int64_t ld, int32_t* __restrict__ out) {
+                                                      int64_t ld, int32_t* __restrict__ out,
+                                                      float* __restrict__ max_out) {
   const int64_t row = blockIdx.x;
   const __nv_bfloat16* lr = logits + row * ld;
   float bv = -INFINITY;
@@ -163,8 +164,28 @@ __global__ void __launch_bounds__(1024) argmax_kernel(const __nv_bfloat16* __res
       const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
       if (better(ov, oi, bv, bi)) bv = ov, bi = oi;
     }
-    if (threadIdx.x == 0) out[row] = bi;
+    if (threadIdx.x == 0) {
+      out[row] = bi;
+      if (max_out) max_out[row] = bv;
+    }
   }
+}
+
+// Vocabulary-sharded arg-max: part p holds (max value, local index) of vocabulary slice p for
+// every row; the winner's global index is p * slice + local index.  Lower part wins ties, which
+// is the lower global index.
+__global__ void argmax_merge_kernel(const float* __restrict__ vals, const int32_t* __restrict__ idx, int parts,
+                                    int rows, int slice, int32_t* __restrict__ out) {
+  const int r = blockIdx.x * blockDim.x + threadIdx.x;
+  if (r >= rows) return;
+  float bv = vals[r];
+  int bi = idx[r];
+  for (int p = 1; p < parts; ++p) {
+    const float v = vals[p * rows + r];
+    const int i = p * slice + idx[p * rows + r];
+    if (better(v, i, bv, bi)) bv = v, bi = i;
+  }
+  out[r] = bi;
 }
 
 // ---------------------------------------------------------------------------------------
@@ -353,11 +374,19 @@ int xaxb_embed(xaxb_ctx* ctx, void* stream, const int32_t* tokens, int64_t n_tok
 }
 
 int xaxb_argmax(xaxb_ctx* ctx, void* stream, const void* logits_bf16, int64_t rows, int64_t vocab, int64_t ld,
-                int32_t* out) {
+                int32_t* out, float* max_out) {
   if (!ctx || !logits_bf16 || !out || rows <= 0 || vocab <= 0 || ld < vocab) return XAXB_BAD_ARGUMENT;
   argmax_kernel<<<(unsigned)rows, 1024, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<const __nv_bfloat16*>(logits_bf16), vocab, ld, out);
+      static_cast<const __nv_bfloat16*>(logits_bf16), vocab, ld, out, max_out);
   return check_launch("argmax_kernel");
+}
+
+int xaxb_argmax_merge(xaxb_ctx* ctx, void* stream, const float* part_max, const int32_t* part_idx, int64_t parts,
+                      int64_t rows, int64_t slice, int32_t* out) {
+  if (!ctx || !part_max || !part_idx || !out || parts <= 0 || rows <= 0 || slice <= 0) return XAXB_BAD_ARGUMENT;
+  argmax_merge_kernel<<<(unsigned)((rows + 127) / 128), 128, 0, static_cast<cudaStream_t>(stream)>>>(
+      part_max, part_idx, (int)parts, (int)rows, (int)slice, out);
+  return check_launch("argmax_merge_kernel");
 }
 
 int xaxb_kv_append_rope(xaxb_ctx* ctx, void* stream, const void* qkv_bf16, int64_t ld, int64_t B, int64_t T,

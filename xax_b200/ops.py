@@ -207,13 +207,33 @@ def embed(tokens, table):
     return x
 
 
-def argmax(logits, out=None):
+def argmax(logits, out=None, max_out=None):
     logits = _req(logits, BF16, "logits")
     rows, vocab = logits.shape
     ctx, st, lib = _c()
     if out is None:
         out = torch.empty((rows,), dtype=torch.int32, device=logits.device)
-    check(lib.xaxb_argmax(ctx, st, ptr(logits), rows, vocab, logits.stride(0), ptr(out)), "argmax")
+    check(lib.xaxb_argmax(ctx, st, ptr(logits), rows, vocab, logits.stride(0), ptr(out), ptr(max_out)), "argmax")
+    return out
+
+
+def argmax_merge(part_max, part_idx, slice_cols: int, out):
+    """Global arg-max from per-slice (max, index) pairs [parts, rows]."""
+    parts, rows = part_max.shape
+    ctx, st, lib = _c()
+    check(lib.xaxb_argmax_merge(ctx, st, ptr(part_max), ptr(part_idx), parts, rows, slice_cols, ptr(out)),
+          "argmax_merge")
+    return out
+
+
+def group_amax(x, group_rows: int = 1, out=None):
+    """max|x| per group of rows, float32 [rows / group_rows]."""
+    x = _req(x, BF16, "x")
+    rows, cols = x.shape
+    ctx, st, lib = _c()
+    if out is None:
+        out = torch.empty((rows // group_rows,), dtype=torch.float32, device=x.device)
+    check(lib.xaxb_group_amax(ctx, st, ptr(x), rows, cols, group_rows, ptr(out)), "group_amax")
     return out
 
 

@@ -1,0 +1,155 @@
+"""Tensor parallelism over the GPUs of one NVSwitch box, one process per GPU.
+
+Placement follows xax/arch/llm.py:931-975 (``get_model_parallel_sharding_spec``): q/k/v/gate/up
+and lm_head are split along ``out`` (column parallel), o_proj/down_proj along ``in`` (row
+parallel); embeddings, norms and 1-D tensors are replicated.  The reference leaves the
+collectives to XLA/GSPMD (an all-reduce after every row-parallel matmul); here they are explicit:
+
+  * the partial outputs of o_proj and down_proj are summed across ranks (``all_reduce_sum``);
+  * the activation feeding a row-parallel FP8 layer is sharded along the reduction dimension,
+    so its amax (per token for o_proj, per sequence for down_proj) is max-reduced across ranks
+    before the cast -- the e4m3 bytes then equal the unsharded model's;
+  * greedy decoding needs no logits gather: each rank arg-maxes its vocabulary slice and the
+    (value, index) pairs are all-gathered and merged.
+
+Collectives go through ``torch.distributed`` (NCCL over NVLink on GPUs, gloo in CPU tests).
+"""
+
+from __future__ import annotations
+
+import torch
+import torch.distributed as dist
+
+from .arch.llm import get_model_parallel_sharding_spec, tp_shard_dim  # noqa: F401  (re-exported)
+
+
+def setup_model_parallel_mesh(mp_size: int | None = None) -> dict:
+    """xax/arch/llm.py:907-928 for one-process-per-GPU launches: returns {"axis": "model",
+    "size", "rank"} from the initialised process group (``mp_size`` must equal its size)."""
+    if not dist.is_initialized():
+        if mp_size not in (None, 1):
+            raise ValueError(f"mp_size ({mp_size}) > available devices (1): launch one process per GPU with torchrun")
+        return {"axis": "model", "size": 1, "rank": 0}
+    world = dist.get_world_size()
+    if mp_size is not None and mp_size > world:
+        raise ValueError(f"mp_size ({mp_size}) > available devices ({world})")
+    if mp_size is not None and mp_size != world:
+        raise ValueError("a tensor-parallel group smaller than the launch is not supported")
+    return {"axis": "model", "size": world, "rank": dist.get_rank()}
+
+
+def shard_weight(weight: torch.Tensor, weight_name: str, rank: int, size: int) -> torch.Tensor:
+    """This rank's slice of a weight under the placement rule (replicated weights are returned whole)."""
+    dim = tp_shard_dim(weight_name, weight.dim())
+    if size == 1 or dim is None:
+        return weight
+    if weight.shape[dim] % size:
+        raise ValueError(f"{weight_name}: dimension {dim} of {tuple(weight.shape)} does not divide by {size}")
+    n = weight.shape[dim] // size
+    return weight.narrow(dim, rank * n, n).contiguous()
+
+
+class TensorParallel:
+    """Collectives and the tensor-parallel forward of one transformer block."""
+
+    def __init__(self, rank: int, size: int, group=None):
+        self.rank, self.size, self.group = rank, size, group
+
+    # -- collectives ------------------------------------------------------------------------------
+    def all_reduce_sum(self, t: torch.Tensor) -> torch.Tensor:
+        if self.size > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.SUM, group=self.group)
+        return t
+
+    def all_reduce_max(self, t: torch.Tensor) -> torch.Tensor:
+        if self.size > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX, group=self.group)
+        return t
+
+    def all_gather(self, t: torch.Tensor) -> torch.Tensor:
+        out = torch.empty((self.size, *t.shape), dtype=t.dtype, device=t.device)
+        if self.size == 1:
+            out[0] = t
+        elif t.is_cuda:
+            dist.all_gather_into_tensor(out, t.contiguous(), group=self.group)
+        else:  # gloo
+            parts = [torch.empty_like(t) for _ in range(self.size)]
+            dist.all_gather(parts, t.contiguous(), group=self.group)
+            out = torch.stack(parts)
+        return out
+
+    # -- model pieces -----------------------------------------------------------------------------
+    def prepare_model(self, model) -> None:
+        """Quantise every sharded FP8 weight with the amax of the WHOLE weight (max over ranks),
+        so each rank's e4m3 bytes are the corresponding slice of the unsharded model's."""
+        from . import ops
+        from .nn.fp8 import Fp8Linear
+
+        for block in model.blocks:
+            a, f = block.self_attn, block.feed_forward
+            for lin in (a.q_proj, a.k_proj, a.v_proj, a.output_proj, f.gate, f.up, f.down):
+                if isinstance(lin, Fp8Linear) and lin.use_fp8:
+                    w = lin.weight.to(torch.bfloat16).contiguous()
+                    amax = ops.group_amax(w, w.shape[0])
+                    self.all_reduce_max(amax)
+                    q, _, inv = ops.quantize_with_amax(w, amax, w.shape[0])
+                    lin._wq_current = (q, inv[:1].clone())
+            a._fused = None
+            f._fused = None
+
+    def shard_lm_head(self, model) -> None:
+        """Keep only this rank's vocabulary slice of the lm_head (column parallel, :970-972)."""
+        from .arch.attention import Linear
+
+        w = model.lm_head.weight
+        if w.shape[0] % self.size:
+            raise ValueError(f"vocabulary {w.shape[0]} does not divide by {self.size}")
+        n = w.shape[0] // self.size
+        model.lm_head = Linear(w.shape[1], n, use_bias=False, weight=w.narrow(0, self.rank * n, n).contiguous())
+        model.vocab_slice = n
+
+    def greedy_tokens(self, model, hidden_bh: torch.Tensor, out: torch.Tensor) -> None:
+        """argmax over the full vocabulary from per-rank slices, written to ``out`` int32 [B]."""
+        from . import ops
+
+        logits = ops.gemm_bf16(hidden_bh.contiguous(), model.lm_head.weight)
+        B = logits.shape[0]
+        idx = torch.empty((B,), dtype=torch.int32, device=logits.device)
+        val = torch.empty((B,), dtype=torch.float32, device=logits.device)
+        ops.argmax(logits, out=idx, max_out=val)
+        ops.argmax_merge(self.all_gather(val), self.all_gather(idx), logits.shape[1], out)
+
+    def block_forward(self, block, x: torch.Tensor, B: int, T: int, *, cache=None, workspace=None,
+                      advance: bool = True):
+        """One pre-norm block with this rank's weight shards.  x [B*T, H] is replicated on entry
+        and on exit.  The residual is added by rank 0's GEMM epilogue only, so the sum of the
+        partial outputs is x + f(x)."""
+        from . import ops
+
+        attn, ff = block.self_attn, block.feed_forward
+        first = self.rank == 0
+        if not (attn._is_fp8() and ff.is_fp8()):
+            raise ValueError("the tensor-parallel path covers FP8 projections (use_fp8=True)")
+        _, yq = ops.rmsnorm(x, block.attn_norm.weight_bf16(), block.attn_norm.eps, want_y=False, quantize=True)
+        part, new_cache = attn.forward_tokens(x, B, T, cache=cache, y_q=(yq[0], yq[2]), residual=x if first else None,
+                                              workspace=workspace, advance=advance, reduce_amax=self.all_reduce_max)
+        x1 = self.all_reduce_sum(part)
+
+        wq, col, bias = ff.fused_gate_up()
+        F = ff.gate.out_features  # local width
+        wm = block.mlp_norm.weight_bf16()
+        if T == 1:
+            _, yq = ops.rmsnorm(x1, wm, block.mlp_norm.eps, want_y=False, quantize=True)
+            q, inv = yq[0], yq[2]
+        else:
+            amax = torch.zeros((B,), dtype=torch.float32, device=x.device)
+            y, _ = ops.rmsnorm(x1, wm, block.mlp_norm.eps, group_amax=amax, group_rows=T)
+            q, _, inv = ops.quantize_with_amax(y, amax, T)
+        gu = ops.gemm_fp8(q, wq, inv, col, bias)
+        hmax = torch.zeros((B,), dtype=torch.float32, device=x.device)
+        h, _ = ops.silu_mul(gu, F, group_amax=hmax, group_rows=T)
+        self.all_reduce_max(hmax)  # the down projection's input spans all ranks
+        hq, _, h_inv = ops.quantize_with_amax(h, hmax, T)
+        part = ff.down.forward_quantized(hq, h_inv, x1 if first else None)
+        x2 = self.all_reduce_sum(part)
+        return x2, new_cache
