@@ -378,6 +378,7 @@ def main() -> None:
     if rank != 0:
         if world > 1:
             dist.barrier()
+            _leave()
         return
     line = dict(base)
     line.update({"value": B * K / elapsed, "ms_per_step": elapsed / K * 1e3, "clocks": clocks,
@@ -402,6 +403,18 @@ def main() -> None:
     print(json.dumps(line), flush=True)
     if world > 1:
         dist.barrier()
+        _leave()
+
+
+def _leave() -> None:
+    """Multi-rank exit.  Tearing down an NCCL process group whose collectives were captured in a
+    CUDA graph can block forever, so the ranks synchronise, flush and leave without it."""
+    import torch
+
+    torch.cuda.synchronize()
+    sys.stdout.flush()
+    sys.stderr.flush()
+    os._exit(0)
 
 
 if __name__ == "__main__":

@@ -71,7 +71,11 @@ def _worker(rank: int, world: int, port: int, results):
 
         results[rank] = traceback.format_exc()
     finally:
-        dist.destroy_process_group()
+        # A process group whose collectives were captured in a CUDA graph can block in
+        # destroy_process_group; leave without tearing NCCL down (results are already stored).
+        torch.cuda.synchronize()
+        sys.stdout.flush()
+        os._exit(0)
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
