@@ -109,6 +109,12 @@ int xaxb_gemm_bf16(xaxb_ctx* ctx, void* stream, const void* a_bf16, int64_t lda,
                    int col_mul_stride, const void* bias_bf16, const void* residual_bf16, int64_t ldr, void* out_bf16,
                    int64_t ldo);
 
+/* Test hook: force the tile width (32/64/128/256, 0 = automatic) and the split-K factor
+ * (1/2/4/8, 0 = automatic; > 1 needs M <= 128) of the following xaxb_gemm_* calls in this
+ * process, so that tests can drive every kernel variant on the same inputs.  No counterpart
+ * in the reference. */
+int xaxb_gemm_force_plan(int bn, int split);
+
 /* Plain CUDA-core GEMM with the same contract as xaxb_gemm_fp8 (one thread per output,
  * float32 accumulation in k order).  A second opinion for the tensor-core kernel in tests;
  * never used by the module layer. */
@@ -208,6 +214,19 @@ int xaxb_attn_decode(xaxb_ctx* ctx, void* stream, const void* q_rot_bf16, const 
                      int64_t D, int64_t max_len, float softmax_scale, int k_is_rotated, const void* cos_bf16,
                      const void* sin_bf16, int64_t table_len, void* out_bf16, void* workspace,
                      int64_t workspace_bytes);
+
+/*
+ * xaxb_attn_decode with the per-token current-scaling cast of its output fused into the merge
+ * pass: the row [Hq * D] of each sequence -- what the output projection consumes under the
+ * vmapped Fp8Linear of xax/arch/attention.py:279 and :959-961 -- is written as e4m3 bytes with
+ * row_scale / row_inv_scale (float32 [B]), bit-identical to xaxb_quantize_current(group_rows = 1)
+ * applied to the bf16 output.  out_bf16 may be NULL.  Needs Hq <= 64 and Hq * D <= 4096.
+ */
+int xaxb_attn_decode_cast(xaxb_ctx* ctx, void* stream, const void* q_rot_bf16, const void* k_cache_bf16,
+                          const void* v_cache_bf16, const int32_t* positions, int64_t B, int64_t Hq, int64_t Hkv,
+                          int64_t D, int64_t max_len, float softmax_scale, int k_is_rotated, const void* cos_bf16,
+                          const void* sin_bf16, int64_t table_len, void* out_bf16, void* q_e4m3, float* row_scale,
+                          float* row_inv_scale, void* workspace, int64_t workspace_bytes);
 
 /*
  * Decode attention without any memory from the caller beyond inputs and outputs.

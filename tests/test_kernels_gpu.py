@@ -168,6 +168,34 @@ def test_gemm_fp8_epilogue_variants(ops, M, N, K, row_mode, col_mode, use_bias, 
     assert rel_fro(f32(to_numpy(out)), f32(to_numpy(chk))) < TOL_SELF
 
 
+@pytest.mark.parametrize("M,N,K,bn,split", [(128, 4096, 4096, 128, 4), (64, 768, 2048, 256, 8), (1, 512, 1024, 64, 2),
+                                             (100, 1000, 1792, 32, 4), (128, 2048, 14336, 128, 2),
+                                             (77, 264, 528, 64, 8), (128, 6144, 4096, 0, 0)])
+def test_gemm_fp8_split_k_cluster_variants(ops, M, N, K, bn, split):
+    """The split-K kernel (thread-block cluster, partial tiles summed through distributed shared
+    memory) against the CUDA-core kernel, for forced (tile width, split) plans and the automatic
+    plan; two runs must agree bit for bit (fixed summation order)."""
+    from xax_b200 import _lib
+
+    a, b, rng = _gemm_inputs(M, N, K, 21)
+    rm = to_torch(rng.uniform(0.005, 0.02, M).astype(np.float32))
+    cm = to_torch(rng.uniform(0.01, 0.03, N).astype(np.float32))
+    bias = to_torch((rng.standard_normal(N) * 0.5).astype(bf16))
+    res = to_torch(rng.standard_normal((M, N)).astype(bf16))
+    at, bt = to_torch(a), to_torch(b)
+    chk = ops.gemm_fp8_check(at, bt, rm, cm, bias, res)
+    lib = _lib.load()
+    assert lib.xaxb_gemm_force_plan(bn, split) == 0
+    try:
+        out1 = ops.gemm_fp8(at, bt, rm, cm, bias, res)
+        out2 = ops.gemm_fp8(at, bt, rm, cm, bias, res)
+    finally:
+        lib.xaxb_gemm_force_plan(0, 0)
+    assert torch.equal(out1, out2)
+    assert rel_fro(f32(to_numpy(out1)), f32(to_numpy(chk))) < TOL_SELF
+    _lib.device_status()
+
+
 @pytest.mark.parametrize("M,N,K", [(128, 256, 512), (200, 1000, 1088), (64, 32000, 2048)])
 def test_gemm_bf16(ops, M, N, K):
     rng = np.random.default_rng(3)
@@ -248,6 +276,26 @@ def test_silu_mul_and_group_amax(ops):
     q3, s3, _ = ops.quantize_with_amax(h, amax, 4)
     q4, s4, _, _ = ops.quantize_current(h, 4)
     assert torch.equal(q3.view(torch.uint8), q4.view(torch.uint8)) and torch.equal(s3, s4)
+
+
+@pytest.mark.parametrize("rows,dim", [(5, 14336), (3, 5632), (130, 2048), (2, 4096)])
+def test_silu_mul_row_spread_over_a_cluster(ops, rows, dim):
+    """Wide rows are spread over a thread-block cluster; the fused cast must still equal the
+    stand-alone cast of the kernel's own h, and h the oracle's."""
+    from oracle.attention import silu
+
+    rng = np.random.default_rng(dim)
+    gu = (rng.standard_normal((rows, 2 * dim)) * 2).astype(np.float32).astype(bf16)
+    exp = (f32(silu(gu[:, :dim])) * f32(gu[:, dim:])).astype(bf16)
+    amax = torch.zeros(rows, device="cuda")
+    h, (q, scale, inv) = ops.silu_mul(to_torch(gu), dim, quantize=True, group_amax=amax, group_rows=1)
+    got = to_numpy(h)
+    assert np.mean(got.view(np.uint16) != exp.view(np.uint16)) < 0.01
+    q2, s2, i2, a2 = ops.quantize_current(h, 1)
+    assert torch.equal(q.view(torch.uint8), q2.view(torch.uint8)) and torch.equal(scale, s2) and torch.equal(inv, i2)
+    assert torch.equal(amax, a2)
+    _, (q3, s3, _) = ops.silu_mul(to_torch(gu), dim, want_h=False, quantize=True)
+    assert torch.equal(q3.view(torch.uint8), q.view(torch.uint8)) and torch.equal(s3, scale)
 
 
 def test_embed_and_argmax(ops):
@@ -334,6 +382,19 @@ def test_attn_decode_vs_oracle(ops, Hq, Hkv, D, starts):
     err = rel_fro(f32(to_numpy(out)), f32(exp))
     assert err < TOL_REF, err
     assert rel_fro(f32(to_numpy(out)), f32(to_numpy(chk))) < 5e-3
+
+
+@pytest.mark.parametrize("Hq,Hkv,D,starts", [(32, 8, 128, [0, 127, 128, 700]), (32, 4, 64, [5, 300]), (8, 2, 128, [64])])
+def test_attn_decode_fused_cast_equals_separate_cast(ops, Hq, Hkv, D, starts):
+    B, max_len = len(starts), max(starts) + 9
+    q_rot, kc, vc, pos, cos, sin, exp = _attn_setup(ops, B, 1, Hq, Hkv, D, max_len, starts, 10000.0, 23)
+    out = ops.attn_decode(q_rot, kc, vc, pos)
+    o2, q, rs, ri = ops.attn_decode_cast(q_rot, kc, vc, pos, want_out=True)
+    assert torch.equal(o2, out)
+    q_ref, s_ref, i_ref, _ = ops.quantize_current(out.reshape(B, Hq * D), 1)
+    assert torch.equal(q.view(torch.uint8), q_ref.view(torch.uint8)) and torch.equal(rs, s_ref) and torch.equal(ri, i_ref)
+    _, q3, _, _ = ops.attn_decode_cast(q_rot, kc, vc, pos)
+    assert torch.equal(q3.view(torch.uint8), q.view(torch.uint8))
 
 
 def test_attn_decode_rotate_on_load(ops):

@@ -42,6 +42,7 @@ SIGNATURES: dict[str, tuple] = {
     "xaxb_quantize_with_amax": (_I, [_P, _P, _P, _I64, _I64, _I64, _P, _P, _P, _P]),
     "xaxb_gemm_fp8": (_I, [_P, _P, _P, _I64, _P, _I64, _I64, _I64, _I64, _P, _I, _P, _I, _P, _P, _I64, _P, _I64]),
     "xaxb_gemm_bf16": (_I, [_P, _P, _P, _I64, _P, _I64, _I64, _I64, _I64, _P, _I, _P, _I, _P, _P, _I64, _P, _I64]),
+    "xaxb_gemm_force_plan": (_I, [_I, _I]),
     "xaxb_gemm_fp8_check": (_I, [_P, _P, _P, _I64, _P, _I64, _I64, _I64, _I64, _P, _I, _P, _I, _P, _P, _I64, _P, _I64]),
     "xaxb_rmsnorm": (_I, [_P, _P, _P, _P, _F, _I64, _I64, _P, _P, _P, _P, _P, _I64]),
     "xaxb_silu_mul": (_I, [_P, _P, _P, _P, _I64, _I64, _I64, _P, _P, _P, _P, _P, _I64]),
@@ -52,6 +53,8 @@ SIGNATURES: dict[str, tuple] = {
     "xaxb_kv_append_rope": (_I, [_P, _P, _P, _I64, _I64, _I64, _I64, _I64, _I64, _P, _P, _P, _I64, _P, _P, _P, _I64, _I]),
     "xaxb_attn_decode_workspace_bytes": (_I64, [_I64, _I64, _I64, _I64]),
     "xaxb_attn_decode": (_I, [_P, _P, _P, _P, _P, _P, _I64, _I64, _I64, _I64, _I64, _F, _I, _P, _P, _I64, _P, _P, _I64]),
+    "xaxb_attn_decode_cast": (_I, [_P, _P, _P, _P, _P, _P, _I64, _I64, _I64, _I64, _I64, _F, _I, _P, _P, _I64, _P, _P, _P,
+                                   _P, _P, _I64]),
     "xaxb_attn_decode_static_capacity_bytes": (_I64, []),
     "xaxb_attn_decode_static": (_I, [_P, _P, _P, _P, _P, _P, _I64, _I64, _I64, _I64, _I64, _F, _I, _P, _P, _I64, _P]),
     "xaxb_attn_prefill": (_I, [_P, _P, _P, _P, _P, _P, _I64, _I64, _I64, _I64, _I64, _I64, _F, _P]),

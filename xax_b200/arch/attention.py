@@ -392,13 +392,21 @@ class SelfAttentionBlock:
         pos = cache["position"]
         q_rot = ops.kv_append_rope(qkv, B, T, Hq, Hkv, D, pos, cos, sin, cache["k"], cache["v"])
         scale = 1.0 / math.sqrt(D)
+        op = self.output_proj
+        op_fp8 = isinstance(op, Fp8Linear) and op.use_fp8
+        if T == 1 and op_fp8 and reduce_amax is None and Hq <= 64 and Hq * D <= 4096:
+            # decode: the per-token cast of the attention output happens inside the merge pass
+            _, aq, _, a_inv = ops.attn_decode_cast(q_rot, cache["k"], cache["v"], pos, scale=scale, workspace=workspace)
+            out = op.forward_quantized(aq, a_inv, residual)
+            if advance:
+                ops.advance_positions(pos, T)
+            return out, {"k": cache["k"], "v": cache["v"], "position": pos}
         if T == 1:
             attn = ops.attn_decode(q_rot, cache["k"], cache["v"], pos, scale=scale, workspace=workspace)
         else:
             attn = ops.attn_prefill(q_rot, cache["k"], cache["v"], pos, B, T, scale=scale)
         attn2 = attn.reshape(B * T, Hq * D)
-        op = self.output_proj
-        if isinstance(op, Fp8Linear) and op.use_fp8:
+        if op_fp8:
             if reduce_amax is None:
                 aq, _, a_inv, _ = ops.quantize_current(attn2, 1)
             else:

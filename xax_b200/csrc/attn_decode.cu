@@ -24,6 +24,7 @@
 // (chunk start + t) of the cos/sin table (bf16 arithmetic in the reference's order) before
 // the first MMA.
 #include "common.cuh"
+#include "quant_device.cuh"
 
 namespace xaxb {
 
@@ -315,6 +316,69 @@ __global__ void attn_decode_merge_kernel(const float* __restrict__ ws_o, const f
   out[((long long)b * Hq + h) * D + d] = __float2bfloat16_rn(num / den);
 }
 
+// Merge + per-token cast in one pass: one CTA per sequence merges the chunks of ALL its query
+// heads (the row [Hq * D] that the output projection consumes), keeps the merged values in
+// registers, reduces the row's amax and writes e4m3 bytes with the row's scale -- the same
+// result as the merge kernel followed by the per-token cast, without the bf16 round trip.
+// Work item = (head, 8 consecutive dims); at most 2 items per thread (Hq * D <= 4096).
+__global__ void __launch_bounds__(256) attn_decode_merge_cast_kernel(
+    const float* __restrict__ ws_o, const float* __restrict__ ws_ml, const int32_t* __restrict__ positions, int Hq,
+    int D, int max_chunks, uint4* __restrict__ out, uint2* __restrict__ q, float* __restrict__ scale,
+    float* __restrict__ inv_scale) {
+  __shared__ float s_max[64], s_inv_den[64];
+  const int b = blockIdx.x;
+  const int L = positions[b] + 1;
+  const int n = (L + kChunk - 1) / kChunk;
+  for (int h = threadIdx.x; h < Hq; h += blockDim.x) {
+    const long long base = ((long long)b * Hq + h) * max_chunks;
+    float m = -INFINITY;
+    for (int c = 0; c < n; ++c) m = fmaxf(m, ws_ml[(base + c) * 2]);
+    float den = 0.0f;
+    for (int c = 0; c < n; ++c) den = fmaf(__expf(ws_ml[(base + c) * 2] - m), ws_ml[(base + c) * 2 + 1], den);
+    s_max[h] = m;
+    s_inv_den[h] = 1.0f / den;
+  }
+  __syncthreads();
+  const int dv = D / 8;
+  const int items = Hq * dv;
+  float v[2][8];
+  uint32_t mbits = 0;
+#pragma unroll
+  for (int k = 0; k < 2; ++k) {
+    const int it = threadIdx.x + k * 256;
+    if (it < items) {
+      const int h = it / dv, d0 = (it % dv) * 8;
+      const long long base = ((long long)b * Hq + h) * max_chunks;
+      float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+      for (int c = 0; c < n; ++c) {
+        const float w = __expf(ws_ml[(base + c) * 2] - s_max[h]);
+        const float4 lo = *reinterpret_cast<const float4*>(ws_o + (base + c) * D + d0);
+        const float4 hi = *reinterpret_cast<const float4*>(ws_o + (base + c) * D + d0 + 4);
+        acc[0] = fmaf(w, lo.x, acc[0]), acc[1] = fmaf(w, lo.y, acc[1]), acc[2] = fmaf(w, lo.z, acc[2]);
+        acc[3] = fmaf(w, lo.w, acc[3]), acc[4] = fmaf(w, hi.x, acc[4]), acc[5] = fmaf(w, hi.y, acc[5]);
+        acc[6] = fmaf(w, hi.z, acc[6]), acc[7] = fmaf(w, hi.w, acc[7]);
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        v[k][j] = bf16_round(acc[j] * s_inv_den[h]);
+        mbits = max(mbits, mag_bits16(v[k][j]));
+      }
+      if (out) out[(long long)b * items + it] = pack8(v[k]);
+    }
+  }
+  const uint32_t row_bits = block_max_u32(mbits);
+  const float s = current_scale_from_amax(bf16_bits_to_float(row_bits));
+#pragma unroll
+  for (int k = 0; k < 2; ++k) {
+    const int it = threadIdx.x + k * 256;
+    if (it < items) q[(long long)b * items + it] = quantize8f(v[k], s);
+  }
+  if (threadIdx.x == 0) {
+    scale[b] = s;
+    inv_scale[b] = 1.0f / s;
+  }
+}
+
 static int make_cache_tmap(const Ctx* ctx, CUtensorMap* map, const void* cache, int64_t B, int64_t max_len,
                            int64_t Hkv, int64_t D) {
   // cache[b][token][head][d]: dims innermost first (d, head, token, b); box = 64 d x 1 head x 128 tokens x 1.
@@ -335,12 +399,12 @@ int64_t xaxb_attn_decode_workspace_bytes(int64_t B, int64_t Hq, int64_t D, int64
   return B * Hq * chunks * (D + 2) * (int64_t)sizeof(float);
 }
 
-int xaxb_attn_decode(xaxb_ctx* ctx_, void* stream, const void* q_rot_bf16, const void* k_cache_bf16,
-                     const void* v_cache_bf16, const int32_t* positions, int64_t B, int64_t Hq, int64_t Hkv, int64_t D,
-                     int64_t max_len, float softmax_scale, int k_is_rotated, const void* cos_bf16,
-                     const void* sin_bf16, int64_t table_len, void* out_bf16, void* workspace,
-                     int64_t workspace_bytes) {
-  if (!ctx_ || !q_rot_bf16 || !k_cache_bf16 || !v_cache_bf16 || !positions || !out_bf16 || !workspace || B <= 0 ||
+static int decode_launch(xaxb_ctx* ctx_, void* stream, const void* q_rot_bf16, const void* k_cache_bf16,
+                         const void* v_cache_bf16, const int32_t* positions, int64_t B, int64_t Hq, int64_t Hkv,
+                         int64_t D, int64_t max_len, float softmax_scale, int k_is_rotated, const void* cos_bf16,
+                         const void* sin_bf16, int64_t table_len, void* out_bf16, void* q_e4m3, float* row_scale,
+                         float* row_inv_scale, void* workspace, int64_t workspace_bytes) {
+  if (!ctx_ || !q_rot_bf16 || !k_cache_bf16 || !v_cache_bf16 || !positions || (!out_bf16 && !q_e4m3) || !workspace || B <= 0 ||
       Hq <= 0 || Hkv <= 0 || max_len <= 0) {
     set_last_error("attn_decode: null pointer or non-positive shape");
     return XAXB_BAD_ARGUMENT;
@@ -397,10 +461,43 @@ int xaxb_attn_decode(xaxb_ctx* ctx_, void* stream, const void* q_rot_bf16, const
   }
   rc = check_launch("attn_decode_kernel");
   if (rc) return rc;
+  if (q_e4m3) {
+    attn_decode_merge_cast_kernel<<<(unsigned)B, 256, 0, s>>>(p.ws_o, p.ws_ml, positions, (int)Hq, (int)D, max_chunks,
+                                                             static_cast<uint4*>(out_bf16),
+                                                             static_cast<uint2*>(q_e4m3), row_scale, row_inv_scale);
+    return check_launch("attn_decode_merge_cast_kernel");
+  }
   dim3 mgrid((unsigned)Hq, (unsigned)B);
   attn_decode_merge_kernel<<<mgrid, (unsigned)D, 0, s>>>(p.ws_o, p.ws_ml, positions, (int)Hq, (int)D, max_chunks,
                                                          static_cast<__nv_bfloat16*>(out_bf16));
   return check_launch("attn_decode_merge_kernel");
+}
+
+int xaxb_attn_decode(xaxb_ctx* ctx_, void* stream, const void* q_rot_bf16, const void* k_cache_bf16,
+                     const void* v_cache_bf16, const int32_t* positions, int64_t B, int64_t Hq, int64_t Hkv, int64_t D,
+                     int64_t max_len, float softmax_scale, int k_is_rotated, const void* cos_bf16,
+                     const void* sin_bf16, int64_t table_len, void* out_bf16, void* workspace,
+                     int64_t workspace_bytes) {
+  if (!out_bf16) return XAXB_BAD_ARGUMENT;
+  return decode_launch(ctx_, stream, q_rot_bf16, k_cache_bf16, v_cache_bf16, positions, B, Hq, Hkv, D, max_len,
+                       softmax_scale, k_is_rotated, cos_bf16, sin_bf16, table_len, out_bf16, nullptr, nullptr, nullptr,
+                       workspace, workspace_bytes);
+}
+
+int xaxb_attn_decode_cast(xaxb_ctx* ctx_, void* stream, const void* q_rot_bf16, const void* k_cache_bf16,
+                          const void* v_cache_bf16, const int32_t* positions, int64_t B, int64_t Hq, int64_t Hkv,
+                          int64_t D, int64_t max_len, float softmax_scale, int k_is_rotated, const void* cos_bf16,
+                          const void* sin_bf16, int64_t table_len, void* out_bf16, void* q_e4m3, float* row_scale,
+                          float* row_inv_scale, void* workspace, int64_t workspace_bytes) {
+  if (!q_e4m3 || !row_scale || !row_inv_scale) return XAXB_BAD_ARGUMENT;
+  if (Hq > 64 || Hq * D > 4096 || (reinterpret_cast<uintptr_t>(q_e4m3) & 7) ||
+      (reinterpret_cast<uintptr_t>(out_bf16) & 15)) {
+    set_last_error("attn_decode_cast: needs Hq <= 64, Hq * D <= 4096 and aligned outputs");
+    return XAXB_UNSUPPORTED;
+  }
+  return decode_launch(ctx_, stream, q_rot_bf16, k_cache_bf16, v_cache_bf16, positions, B, Hq, Hkv, D, max_len,
+                       softmax_scale, k_is_rotated, cos_bf16, sin_bf16, table_len, out_bf16, q_e4m3, row_scale,
+                       row_inv_scale, workspace, workspace_bytes);
 }
 
 }  // extern "C"

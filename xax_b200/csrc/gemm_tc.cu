@@ -42,10 +42,51 @@ struct GemmParams {
 template <int BN>
 struct GemmCfg {
   static constexpr int kStageBytes = kBM * kBKBytes + BN * kBKBytes;
-  static constexpr int kStages = (200 * 1024) / kStageBytes > 12 ? 12 : (200 * 1024) / kStageBytes;
+  // epilogue staging: a [128 x kEpiCols] float32 slab of the accumulator, rows padded by 4 floats
+  static constexpr int kEpiCols = 32;  // small on purpose: shared memory is worth more as load stages
+  static constexpr int kEpiRowFloats = kEpiCols + 4;
+  static constexpr int kEpiBytes = kBM * kEpiRowFloats * 4;
+  static constexpr int kStagesFit = (200 * 1024 - kEpiBytes) / kStageBytes;
+  static constexpr int kStages = kStagesFit > 12 ? 12 : kStagesFit;
   static constexpr int kTmemCols = 2 * BN < 32 ? 32 : 2 * BN;
-  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
+  static constexpr int kSmemBytes = kStages * kStageBytes + kEpiBytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
 };
+
+// f[j] *= row multiplier * column multiplier of column n + j (n a multiple of 8)
+__device__ __forceinline__ void apply_muls(float (&f)[8], float rm, const float* col_mul, int col_mul_stride, int n) {
+  if (!col_mul) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) f[j] *= rm;
+  } else if (col_mul_stride == 0) {
+    const float c = __ldg(col_mul) * rm;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) f[j] *= c;
+  } else if (col_mul_stride == 1 && (reinterpret_cast<uintptr_t>(col_mul) & 15) == 0) {
+    const float4 a = __ldg(reinterpret_cast<const float4*>(col_mul + n));
+    const float4 b = __ldg(reinterpret_cast<const float4*>(col_mul + n + 4));
+    f[0] *= rm * a.x, f[1] *= rm * a.y, f[2] *= rm * a.z, f[3] *= rm * a.w;
+    f[4] *= rm * b.x, f[5] *= rm * b.y, f[6] *= rm * b.z, f[7] *= rm * b.w;
+  } else {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) f[j] *= rm * __ldg(col_mul + (long long)(n + j) * col_mul_stride);
+  }
+}
+
+// all-of vote over the 128 epilogue threads on named barrier 1
+__device__ __forceinline__ bool epilogue_all(bool pred) {
+  uint32_t r;
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\t"
+      "setp.ne.u32 q, %1, 0;\n\t"
+      "bar.red.and.pred p, 1, 128, q;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(r)
+      : "r"((uint32_t)pred)
+      : "memory");
+  return r != 0;
+}
+
+__device__ __forceinline__ void epilogue_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
 
 template <int BN, bool IS_FP8>
 __global__ void __launch_bounds__(kGemmThreads, 1)
@@ -61,7 +102,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* smem_a = smem;                                  // kStages x 16 KiB
   uint8_t* smem_b = smem + kStages * kBM * kBKBytes;       // kStages x BN*128 B
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kStages * Cfg::kStageBytes);
+  float* estage = reinterpret_cast<float*>(smem + kStages * Cfg::kStageBytes);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kStages * Cfg::kStageBytes + Cfg::kEpiBytes);
   uint64_t* full = bars;                 // [kStages]
   uint64_t* empty = bars + kStages;      // [kStages]
   uint64_t* acc_full = bars + 2 * kStages;   // [2]
@@ -105,12 +147,16 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
         const int m0 = (tile % p.tiles_m) * kBM;
         const int n0 = (tile / p.tiles_m) * BN;
+        // Each tile walks K from its own starting block: CTAs that share an operand tile (all
+        // N tiles read the same rows of A) then ask L2 for different lines at any moment.
+        int kk = (int)(((long long)tile * 5) % p.num_k_blocks);
         for (int kb = 0; kb < p.num_k_blocks; ++kb) {
           ok = mbar_wait(empty + stage, phase ^ 1, abort_flag, p.d_status, XAXB_DEVICE_TIMEOUT * 1000 + kSiteProducer);
           if (!ok) break;
           mbar_arrive_expect_tx(full + stage, Cfg::kStageBytes);
-          tma_load_2d(smem_a + stage * kBM * kBKBytes, &tmap_a, full + stage, kb * kBKElems, m0);
-          tma_load_2d(smem_b + stage * BN * kBKBytes, &tmap_b, full + stage, kb * kBKElems, n0);
+          tma_load_2d(smem_a + stage * kBM * kBKBytes, &tmap_a, full + stage, kk * kBKElems, m0);
+          tma_load_2d(smem_b + stage * BN * kBKBytes, &tmap_b, full + stage, kk * kBKElems, n0);
+          if (++kk == p.num_k_blocks) kk = 0;
           if (++stage == kStages) stage = 0, phase ^= 1;
         }
       }
@@ -153,75 +199,94 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     }
   } else {
     // ------------------------------------------------------------------ epilogue (warps 2..5)
+    // Per slab of kEpiCols columns: (A) thread = row pulls its accumulator values out of TMEM
+    // and parks them in shared memory; (B) work item = (row, 8 consecutive columns), consecutive
+    // threads take consecutive column groups of a row, so the residual read and the bf16 store
+    // are contiguous 128-byte runs instead of one 16-byte piece per row.
+    constexpr int kEpiCols = Cfg::kEpiCols, kRowF = Cfg::kEpiRowFloats, kGroups = kEpiCols / 8;
     const int quarter = warp & 3;          // TMEM lanes this warp may read
     const int row_in_tile = quarter * 32 + lane;
+    const int t = threadIdx.x - 64;        // 0..127
     int acc = 0;
     uint32_t acc_phase = 0;
-    bool ok = true;
-    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
       const int m0 = (tile % p.tiles_m) * kBM;
       const int n0 = (tile / p.tiles_m) * BN;
-      ok = mbar_wait(acc_full + acc, acc_phase, abort_flag, p.d_status, XAXB_DEVICE_TIMEOUT * 1000 + kSiteEpilogue);
-      ok = __all_sync(0xffffffffu, ok);
-      if (!ok) break;
+      bool ok = mbar_wait(acc_full + acc, acc_phase, abort_flag, p.d_status, XAXB_DEVICE_TIMEOUT * 1000 + kSiteEpilogue);
+      if (!epilogue_all(ok)) break;
       tc_fence_after_sync();
-      const int m = m0 + row_in_tile;
-      const bool row_ok = m < p.M;
-      const float rm = (row_ok && p.row_mul) ? p.row_mul[(long long)m * p.row_mul_stride] : 1.0f;
       const uint32_t taddr = tmem_base + (uint32_t(quarter * 32) << 16) + acc * BN;
 #pragma unroll 1
-      for (int c0 = 0; c0 < BN; c0 += 32) {
-        uint32_t r[32];
-        tmem_ld_x32(taddr + c0, r);
-        tmem_ld_wait();
-        const int nbase = n0 + c0;
-        if (row_ok && nbase < p.N) {
-          __nv_bfloat16* orow = p.out + (long long)m * p.ldo + nbase;
-          const __nv_bfloat16* rrow = p.residual ? p.residual + (long long)m * p.ldr + nbase : nullptr;
+      for (int c0 = 0; c0 < BN; c0 += kEpiCols) {
+        float* srow = estage + row_in_tile * kRowF;
 #pragma unroll
-          for (int v = 0; v < 4; ++v) {
-            const int n = nbase + v * 8;
-            if (n >= p.N) break;  // N is a multiple of 8: whole vectors only
-            float f[8];
+        for (int h = 0; h < kEpiCols; h += 32) {
+          uint32_t r[32];
+          tmem_ld_x32(taddr + c0 + h, r);
+          tmem_ld_wait();
 #pragma unroll
-            for (int j = 0; j < 8; ++j) {
-              float x = __uint_as_float(r[v * 8 + j]) * rm;
-              if (p.col_mul) x *= __ldg(p.col_mul + (long long)(n + j) * p.col_mul_stride);
-              f[j] = x;
-            }
-            if (p.bias) {
-              const uint4 bv = __ldg(reinterpret_cast<const uint4*>(p.bias + n));
-              const uint32_t bw[4] = {bv.x, bv.y, bv.z, bv.w};
+          for (int i = 0; i < 32; i += 4)
+            *reinterpret_cast<float4*>(srow + h + i) = make_float4(__uint_as_float(r[i]), __uint_as_float(r[i + 1]),
+                                                                   __uint_as_float(r[i + 2]), __uint_as_float(r[i + 3]));
+        }
+        if (c0 + kEpiCols >= BN) {  // the accumulator has been read out: the MMA warp may reuse it
+          tc_fence_before_sync();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(acc_empty + acc);
+        }
+        epilogue_sync();
+        // items of this thread in the slab: (row, 8 columns); residual pieces are fetched first
+        // so their latency overlaps instead of adding up
+        constexpr int kItems = kBM * kGroups / 128;
+        uint4 resv[kItems];
 #pragma unroll
-              for (int j = 0; j < 4; ++j) {
-                f[2 * j] += bf16_bits_to_float(bw[j] & 0xFFFFu);
-                f[2 * j + 1] += bf16_bits_to_float(bw[j] >> 16);
-              }
-            }
-            if (rrow) {
-              const uint4 rv = *reinterpret_cast<const uint4*>(rrow + v * 8);
-              const uint32_t rw[4] = {rv.x, rv.y, rv.z, rv.w};
+        for (int k = 0; k < kItems; ++k) {
+          const int it = t + k * 128;
+          const int m = m0 + it / kGroups, n = n0 + c0 + (it % kGroups) * 8;
+          resv[k] = make_uint4(0, 0, 0, 0);
+          if (p.residual && m < p.M && n < p.N)
+            resv[k] = *reinterpret_cast<const uint4*>(p.residual + (long long)m * p.ldr + n);
+        }
 #pragma unroll
-              for (int j = 0; j < 4; ++j) {
-                f[2 * j] += bf16_bits_to_float(rw[j] & 0xFFFFu);
-                f[2 * j + 1] += bf16_bits_to_float(rw[j] >> 16);
-              }
-            }
-            uint4 o;
-            uint32_t* ow = reinterpret_cast<uint32_t*>(&o);
+        for (int k = 0; k < kItems; ++k) {
+          const int it = t + k * 128;
+          const int rr = it / kGroups, g8 = it % kGroups;
+          const int m = m0 + rr, n = n0 + c0 + g8 * 8;
+          if (m >= p.M || n >= p.N) continue;
+          const float4 lo = *reinterpret_cast<const float4*>(estage + rr * kRowF + g8 * 8);
+          const float4 hi = *reinterpret_cast<const float4*>(estage + rr * kRowF + g8 * 8 + 4);
+          float f[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
+          const float rm = p.row_mul ? __ldg(p.row_mul + (long long)m * p.row_mul_stride) : 1.0f;
+          apply_muls(f, rm, p.col_mul, p.col_mul_stride, n);
+          if (p.bias) {
+            const uint4 bv = __ldg(reinterpret_cast<const uint4*>(p.bias + n));
+            const uint32_t bw[4] = {bv.x, bv.y, bv.z, bv.w};
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
-              const uint32_t lo = __bfloat16_as_ushort(__float2bfloat16_rn(f[2 * j]));
-              const uint32_t hi = __bfloat16_as_ushort(__float2bfloat16_rn(f[2 * j + 1]));
-              ow[j] = lo | (hi << 16);
+              f[2 * j] += bf16_bits_to_float(bw[j] & 0xFFFFu);
+              f[2 * j + 1] += bf16_bits_to_float(bw[j] >> 16);
             }
-            *reinterpret_cast<uint4*>(orow + v * 8) = o;
           }
+          if (p.residual) {
+            const uint32_t rw[4] = {resv[k].x, resv[k].y, resv[k].z, resv[k].w};
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              f[2 * j] += bf16_bits_to_float(rw[j] & 0xFFFFu);
+              f[2 * j + 1] += bf16_bits_to_float(rw[j] >> 16);
+            }
+          }
+          uint4 o;
+          uint32_t* ow = reinterpret_cast<uint32_t*>(&o);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const uint32_t lo16 = __bfloat16_as_ushort(__float2bfloat16_rn(f[2 * j]));
+            const uint32_t hi16 = __bfloat16_as_ushort(__float2bfloat16_rn(f[2 * j + 1]));
+            ow[j] = lo16 | (hi16 << 16);
+          }
+          *reinterpret_cast<uint4*>(p.out + (long long)m * p.ldo + n) = o;
         }
+        epilogue_sync();  // the slab is free for the next columns
       }
-      tc_fence_before_sync();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(acc_empty + acc);
       if (++acc == 2) acc = 0, acc_phase ^= 1;
     }
   }
@@ -233,6 +298,297 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     tc_fence_after_sync();
     tmem_dealloc(tmem_base, Cfg::kTmemCols);
   }
+}
+
+// ---------------------------------------------------------------------------------------
+// Split-K variant for M <= 128 (decode): weight streaming.  A thread-block cluster of S CTAs
+// shares one [128 x BN] output tile; CTA r multiplies K slice r into its own TMEM accumulator,
+// parks it as float32 in its shared memory, and after a cluster barrier every CTA sums one
+// row slice of the tile over the S CTAs through distributed shared memory (fixed order
+// r = 0..S-1, so results are reproducible), applies the epilogue and stores bf16.  No global
+// scratch, one launch, and each CTA reads only 1/S of A.
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
+// Address of this CTA's shared-memory location `local_smem_addr` as seen in CTA `cta` of the cluster.
+__device__ __forceinline__ uint32_t dsmem_addr(uint32_t local_smem_addr, uint32_t cta) {
+  uint32_t remote;
+  asm("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_smem_addr), "r"(cta));
+  return remote;
+}
+
+// Plain (schedulable) distributed-shared-memory load; ordering against the writers comes from
+// the cluster barrier that precedes the reads.
+__device__ __forceinline__ float4 ld_dsmem_f4(uint32_t remote_addr) {
+  float4 v;
+  asm("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];"
+      : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
+      : "r"(remote_addr));
+  return v;
+}
+
+constexpr int kSiteSkProducer = 5, kSiteSkMma = 6, kSiteSkEpilogue = 7;
+
+template <int BN>
+struct SplitKCfg {
+  static constexpr int kStageBytes = kBM * kBKBytes + BN * kBKBytes;
+  static constexpr int kStages = (192 * 1024) / kStageBytes > 12 ? 12 : (192 * 1024) / kStageBytes;
+  static constexpr int kRowFloats = BN + 4;  // padded row: conflict-free float4 access by row
+  static constexpr int kStagingBytes = kBM * kRowFloats * 4;
+  static constexpr int kPipeBytes = kStages * kStageBytes;
+  static constexpr int kSmemBytes = (kPipeBytes > kStagingBytes ? kPipeBytes : kStagingBytes) + 1024 + 256;
+  static constexpr int kTmemCols = BN < 32 ? 32 : BN;
+};
+
+template <int BN, bool IS_FP8>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+gemm_splitk_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                   const GemmParams p, const int S) {
+  using Cfg = SplitKCfg<BN>;
+  constexpr int kStages = Cfg::kStages;
+  constexpr int kElemBytes = IS_FP8 ? 1 : 2;
+  constexpr int kBKElems = kBKBytes / kElemBytes;
+  constexpr uint32_t kIdesc = umma_idesc(IS_FP8 ? kFmtE4M3 : kFmtBF16, IS_FP8 ? kFmtE4M3 : kFmtBF16, 0, 0, kBM, BN);
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* smem_a = smem;
+  uint8_t* smem_b = smem + kStages * kBM * kBKBytes;
+  float* staging = reinterpret_cast<float*>(smem);  // reused once the main loop has drained
+  constexpr int kBarOff = Cfg::kPipeBytes > Cfg::kStagingBytes ? Cfg::kPipeBytes : Cfg::kStagingBytes;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kBarOff);
+  uint64_t* full = bars;
+  uint64_t* empty = bars + kStages;
+  uint64_t* acc_full = bars + 2 * kStages;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_full + 1);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int r = (int)cluster_ctarank();
+  const int tile_n = blockIdx.x / S;
+  const int n0 = tile_n * BN;
+  // K blocks of this CTA: an even split of num_k_blocks over the S ranks
+  const int kb0 = (int)((long long)p.num_k_blocks * r / S);
+  const int kb1 = (int)((long long)p.num_k_blocks * (r + 1) / S);
+  const int nkb = kb1 - kb0;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(full + s, 1);
+      mbar_init(empty + s, 1);
+    }
+    mbar_init(acc_full, 1);
+    *abort_flag = 0;
+    fence_mbar_init();
+    prefetch_tmap(&tmap_a);
+    prefetch_tmap(&tmap_b);
+  }
+  if (warp == 2) {
+    tmem_alloc(tmem_slot, Cfg::kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      int kk = nkb > 0 ? kb0 + (tile_n * 3) % nkb : kb0;  // staggered start, see gemm_tc_kernel
+      for (int i = 0; i < nkb; ++i) {
+        if (!mbar_wait(empty + stage, phase ^ 1, abort_flag, p.d_status, XAXB_DEVICE_TIMEOUT * 1000 + kSiteSkProducer))
+          break;
+        mbar_arrive_expect_tx(full + stage, Cfg::kStageBytes);
+        tma_load_2d(smem_a + stage * kBM * kBKBytes, &tmap_a, full + stage, kk * kBKElems, 0);
+        tma_load_2d(smem_b + stage * BN * kBKBytes, &tmap_b, full + stage, kk * kBKElems, n0);
+        if (++kk == kb1) kk = kb0;
+        if (++stage == kStages) stage = 0, phase ^= 1;
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int i = 0; i < nkb; ++i) {
+        ok = mbar_wait(full + stage, phase, abort_flag, p.d_status, XAXB_DEVICE_TIMEOUT * 1000 + kSiteSkMma);
+        if (!ok) break;
+        tc_fence_after_sync();
+        const uint64_t a_desc = umma_desc_kmajor_sw128(smem_u32(smem_a + stage * kBM * kBKBytes));
+        const uint64_t b_desc = umma_desc_kmajor_sw128(smem_u32(smem_b + stage * BN * kBKBytes));
+#pragma unroll
+        for (int k = 0; k < kBKBytes / 32; ++k) {
+          if (IS_FP8)
+            umma_f8(tmem_base, a_desc + 2 * k, b_desc + 2 * k, kIdesc, (i | k) != 0);
+          else
+            umma_f16(tmem_base, a_desc + 2 * k, b_desc + 2 * k, kIdesc, (i | k) != 0);
+        }
+        umma_commit(empty + stage);
+        if (++stage == kStages) stage = 0, phase ^= 1;
+      }
+      if (ok) umma_commit(acc_full);  // with nkb == 0 this arrives at once: nothing was issued
+    }
+  }
+
+  // ---- park the partial accumulator in shared memory (epilogue warps) ------------------------
+  const int quarter = warp & 3;
+  const int row = quarter * 32 + lane;
+  bool ok = true;
+  if (warp >= 2) {
+    ok = mbar_wait(acc_full, 0, abort_flag, p.d_status, XAXB_DEVICE_TIMEOUT * 1000 + kSiteSkEpilogue);
+    ok = __all_sync(0xffffffffu, ok);
+    if (ok) {
+      tc_fence_after_sync();
+      const uint32_t taddr = tmem_base + (uint32_t(quarter * 32) << 16);
+      float* srow = staging + row * Cfg::kRowFloats;
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN; c0 += 32) {
+        uint32_t v[32];
+        if (nkb > 0) {
+          tmem_ld_x32(taddr + c0, v);
+          tmem_ld_wait();
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) v[i] = 0u;
+        }
+#pragma unroll
+        for (int i = 0; i < 32; i += 4)
+          *reinterpret_cast<float4*>(srow + c0 + i) = make_float4(__uint_as_float(v[i]), __uint_as_float(v[i + 1]),
+                                                                  __uint_as_float(v[i + 2]), __uint_as_float(v[i + 3]));
+      }
+    }
+    tc_fence_before_sync();
+  }
+  __syncwarp();
+  cluster_sync_all();  // every CTA's partial tile is visible cluster-wide
+
+  // ---- reduce this CTA's row slice over the S ranks, epilogue, store ---------------------------
+  // CTA r owns rows [r * 128/S, (r+1) * 128/S) of the tile.  Work item = (row, 8 consecutive
+  // columns), consecutive threads take consecutive column groups of a row, so shared-memory
+  // reads (local and remote), the residual read and the bf16 store are all contiguous.
+  if (warp >= 2 && ok) {
+    const int t = threadIdx.x - 64;          // 0..127
+    const int rows_per = kBM / S;
+    constexpr int kGroups = BN / 8;
+    uint32_t peer[8];
+#pragma unroll
+    for (int src = 0; src < 8; ++src) peer[src] = dsmem_addr(smem_u32(staging), (uint32_t)(src < S ? src : 0));
+    for (int it = t; it < rows_per * kGroups; it += 128) {
+      const int m = r * rows_per + it / kGroups;
+      const int g8 = it % kGroups;
+      const int n = n0 + g8 * 8;
+      if (m >= p.M || n >= p.N) continue;
+      const uint32_t off = (uint32_t)(m * Cfg::kRowFloats + g8 * 8) * 4u;
+      uint4 rv = make_uint4(0, 0, 0, 0);
+      if (p.residual) rv = *reinterpret_cast<const uint4*>(p.residual + (long long)m * p.ldr + n);
+      float4 lo[8], hi[8];
+#pragma unroll
+      for (int src = 0; src < 8; ++src) {
+        if (src < S) {
+          lo[src] = ld_dsmem_f4(peer[src] + off);
+          hi[src] = ld_dsmem_f4(peer[src] + off + 16);
+        }
+      }
+      float f[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+#pragma unroll
+      for (int src = 0; src < 8; ++src) {
+        if (src < S) {
+          f[0] += lo[src].x, f[1] += lo[src].y, f[2] += lo[src].z, f[3] += lo[src].w;
+          f[4] += hi[src].x, f[5] += hi[src].y, f[6] += hi[src].z, f[7] += hi[src].w;
+        }
+      }
+      const float rm = p.row_mul ? p.row_mul[(long long)m * p.row_mul_stride] : 1.0f;
+      apply_muls(f, rm, p.col_mul, p.col_mul_stride, n);
+      if (p.bias) {
+        const uint4 bv = __ldg(reinterpret_cast<const uint4*>(p.bias + n));
+        const uint32_t bw[4] = {bv.x, bv.y, bv.z, bv.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          f[2 * j] += bf16_bits_to_float(bw[j] & 0xFFFFu);
+          f[2 * j + 1] += bf16_bits_to_float(bw[j] >> 16);
+        }
+      }
+      if (p.residual) {
+        const uint32_t rw[4] = {rv.x, rv.y, rv.z, rv.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          f[2 * j] += bf16_bits_to_float(rw[j] & 0xFFFFu);
+          f[2 * j + 1] += bf16_bits_to_float(rw[j] >> 16);
+        }
+      }
+      uint4 o;
+      uint32_t* ow = reinterpret_cast<uint32_t*>(&o);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const uint32_t lo16 = __bfloat16_as_ushort(__float2bfloat16_rn(f[2 * j]));
+        const uint32_t hi16 = __bfloat16_as_ushort(__float2bfloat16_rn(f[2 * j + 1]));
+        ow[j] = lo16 | (hi16 << 16);
+      }
+      *reinterpret_cast<uint4*>(p.out + (long long)m * p.ldo + n) = o;
+    }
+  }
+  __syncwarp();
+  cluster_sync_all();  // peers have finished reading this CTA's shared memory
+  __syncthreads();
+  if (warp == 2) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, Cfg::kTmemCols);
+  }
+}
+
+template <int BN, bool IS_FP8>
+static int launch_splitk(const Ctx* ctx, cudaStream_t stream, const void* a, long long lda_bytes, const void* b,
+                         long long ldb_bytes, GemmParams& p, int S) {
+  using Cfg = SplitKCfg<BN>;
+  constexpr int kElemBytes = IS_FP8 ? 1 : 2;
+  CUtensorMap ta, tb;
+  int rc = make_tmap_2d(ctx, &ta, a, kElemBytes, (uint64_t)p.K, (uint64_t)p.M, (uint64_t)lda_bytes,
+                        kBKBytes / kElemBytes, kBM);
+  if (rc) return rc;
+  rc = make_tmap_2d(ctx, &tb, b, kElemBytes, (uint64_t)p.K, (uint64_t)p.N, (uint64_t)ldb_bytes, kBKBytes / kElemBytes,
+                    BN);
+  if (rc) return rc;
+  p.tiles_m = 1;
+  p.tiles_n = (p.N + BN - 1) / BN;
+  p.num_k_blocks = (int)(((long long)p.K * kElemBytes + kBKBytes - 1) / kBKBytes);
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_splitk_kernel<BN, IS_FP8>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         Cfg::kSmemBytes);
+    if (e != cudaSuccess) {
+      set_last_error("gemm split-K: cudaFuncSetAttribute(%d bytes): %s", Cfg::kSmemBytes, cudaGetErrorString(e));
+      return XAXB_LAUNCH_FAILED;
+    }
+    attr_set = true;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)(p.tiles_n * S), 1, 1);
+  cfg.blockDim = dim3(kGemmThreads, 1, 1);
+  cfg.dynamicSmemBytes = Cfg::kSmemBytes;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = (unsigned)S;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_splitk_kernel<BN, IS_FP8>, ta, tb, p, S);
+  if (e != cudaSuccess) {
+    set_last_error("gemm_splitk_kernel launch: %s", cudaGetErrorString(e));
+    return XAXB_LAUNCH_FAILED;
+  }
+  return check_launch("gemm_splitk_kernel");
 }
 
 template <int BN, bool IS_FP8>
@@ -266,15 +622,51 @@ static int launch_gemm(const Ctx* ctx, cudaStream_t stream, const void* a, long 
   return check_launch("gemm_tc_kernel");
 }
 
-// Tile width: the widest N tile that still gives every SM a tile.
-static int pick_bn(long long M, long long N, int num_sms) {
+// Tile width (and, for M <= 128, the split-K factor) from a small cost model: a CTA ingests
+// operand bytes at a bounded rate, the GPU as a whole at HBM rate, and the tensor core has its
+// own rate.  Narrow tiles give more CTAs but re-read A once per N tile; splitting K gives more
+// CTAs without that cost, at the price of a cluster-wide reduction.
+struct GemmPlan {
+  int bn;
+  int split;
+};
+
+static int g_force_bn = 0, g_force_split = 0;  // test hook (xaxb_gemm_force_plan)
+
+static GemmPlan pick_plan(long long M, long long N, long long K, int elem_bytes, int num_sms) {
+  // Fitted to measurements on B200 (decode shapes, weights streamed from HBM): a CTA whose
+  // shared memory is all load stages ingests ~60 GB/s (in-flight bytes / loaded latency); a
+  // launch has ~2.4 us of fixed time; every further wave of tiles on the persistent kernel
+  // ~2 us; a cluster reduction 1.8 us (2 CTAs) or 3.9 us (4 CTAs) plus 0.02 us per tile column.
+  // Clusters of 8 schedule poorly next to ~200 KB of shared memory per CTA and are not used;
+  // split-K is only used when all its CTAs are resident at once.
   const long long tiles_m = (M + kBM - 1) / kBM;
+  const double rows_a = (double)(M < kBM ? M : kBM);
+  const double r_sm = 60e9, r_hbm = 6.0e12, r_mma = (elem_bytes == 1 ? 4.5e15 : 2.25e15) / 148.0 * 0.75;
+  const long long nkb = (K * elem_bytes + kBKBytes - 1) / kBKBytes;
   const int cand[4] = {256, 128, 64, 32};
+  GemmPlan best = {32, 1};
+  double best_t = 1e30;
   for (int i = 0; i < 4; ++i) {
-    const long long tiles = tiles_m * ((N + cand[i] - 1) / cand[i]);
-    if (tiles >= num_sms || i == 3) return cand[i];
+    const int bn = cand[i];
+    if (bn > 32 && bn >= 2 * N) continue;
+    for (int s = 1; s <= 4; s *= 2) {
+      const long long ctas = tiles_m * ((N + bn - 1) / bn) * s;
+      if (s > 1 && (tiles_m != 1 || nkb < 2 * s || ctas > num_sms)) continue;
+      const double waves = (double)((ctas + num_sms - 1) / num_sms);
+      const double t_sm = waves * (rows_a + bn) * (double)K / s * elem_bytes / r_sm;
+      const double t_mma = waves * 2.0 * kBM * bn * (double)K / s / r_mma;
+      const double t_hbm = (double)(N + M) * K * elem_bytes / r_hbm;
+      double t = t_sm > t_mma ? t_sm : t_mma;
+      if (t_hbm > t) t = t_hbm;
+      t += 2.4e-6 + (waves - 1) * 2e-6;
+      if (s > 1) t += (s == 2 ? 1.8e-6 : 3.9e-6) + 0.02e-6 * bn;
+      if (t < best_t) best_t = t, best = {bn, s};
+    }
   }
-  return 32;
+  if (g_force_bn) best.bn = g_force_bn;
+  if (g_force_split) best.split = g_force_split;
+  return best;
 }
 
 template <bool IS_FP8>
@@ -306,7 +698,20 @@ static int gemm_entry(xaxb_ctx* ctx_, void* stream, const void* a, int64_t lda, 
   p.ldo = ldo;
   p.d_status = ctx->d_status;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  switch (pick_bn(M, N, ctx->num_sms)) {
+  const GemmPlan plan = pick_plan(M, N, K, eb, ctx->num_sms);
+  if (plan.split > 1) {
+    if (M > kBM || plan.split > 8) {
+      set_last_error("gemm: split-K plan (bn=%d, split=%d) is invalid for M=%lld", plan.bn, plan.split, (long long)M);
+      return XAXB_BAD_ARGUMENT;
+    }
+    switch (plan.bn) {
+      case 256: return launch_splitk<256, IS_FP8>(ctx, s, a, lda * eb, b, ldb * eb, p, plan.split);
+      case 128: return launch_splitk<128, IS_FP8>(ctx, s, a, lda * eb, b, ldb * eb, p, plan.split);
+      case 64: return launch_splitk<64, IS_FP8>(ctx, s, a, lda * eb, b, ldb * eb, p, plan.split);
+      default: return launch_splitk<32, IS_FP8>(ctx, s, a, lda * eb, b, ldb * eb, p, plan.split);
+    }
+  }
+  switch (plan.bn) {
     case 256: return launch_gemm<256, IS_FP8>(ctx, s, a, lda * eb, b, ldb * eb, p);
     case 128: return launch_gemm<128, IS_FP8>(ctx, s, a, lda * eb, b, ldb * eb, p);
     case 64: return launch_gemm<64, IS_FP8>(ctx, s, a, lda * eb, b, ldb * eb, p);
@@ -319,6 +724,15 @@ static int gemm_entry(xaxb_ctx* ctx_, void* stream, const void* a, int64_t lda, 
 using namespace xaxb;
 
 extern "C" {
+
+int xaxb_gemm_force_plan(int bn, int split) {
+  if ((bn != 0 && bn != 32 && bn != 64 && bn != 128 && bn != 256) ||
+      (split != 0 && split != 1 && split != 2 && split != 4 && split != 8))
+    return XAXB_BAD_ARGUMENT;
+  g_force_bn = bn;
+  g_force_split = split;
+  return XAXB_OK;
+}
 
 int xaxb_gemm_fp8(xaxb_ctx* ctx, void* stream, const void* a_e4m3, int64_t lda, const void* b_e4m3, int64_t ldb,
                   int64_t M, int64_t N, int64_t K, const float* row_mul, int row_mul_stride, const float* col_mul,

@@ -106,6 +106,173 @@ __global__ void __launch_bounds__(256) silu_mul_kernel(const uint4* __restrict__
   }
 }
 
+
+// Register-resident variant for rows of up to 256 * VPT * 8 elements: the row is read from
+// global memory once and stays in registers through the three phases (sum of squares,
+// normalise + amax, cast).
+template <int VPT>
+__global__ void __launch_bounds__(256) rmsnorm_reg_kernel(const uint4* __restrict__ x, const uint4* __restrict__ w,
+                                                          float eps, int vec, uint4* __restrict__ y,
+                                                          uint2* __restrict__ q, float* __restrict__ scale,
+                                                          float* __restrict__ inv_scale,
+                                                          unsigned int* __restrict__ group_amax, int64_t group_rows) {
+  const int64_t row = blockIdx.x;
+  const uint4* xr = x + row * vec;
+  float v[VPT][8];
+  float acc = 0.0f;
+#pragma unroll
+  for (int k = 0; k < VPT; ++k) {
+    const int i = threadIdx.x + k * 256;
+    if (i < vec) {
+      unpack8(__ldg(xr + i), v[k]);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc += bf16_round(v[k][j] * v[k][j]);
+    }
+  }
+  const float total = block_sum_f32(acc);
+  const float mean = bf16_round(total / (float)(vec * 8));
+  const float n = bf16_round(sqrtf(bf16_round(mean + bf16_round(eps))));
+  uint32_t m = 0;
+#pragma unroll
+  for (int k = 0; k < VPT; ++k) {
+    const int i = threadIdx.x + k * 256;
+    if (i < vec) {
+      float wv[8];
+      unpack8(__ldg(w + i), wv);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        v[k][j] = bf16_round(bf16_round(v[k][j] / n) * wv[j]);
+        m = max(m, mag_bits16(v[k][j]));
+      }
+      if (y) y[row * vec + i] = pack8(v[k]);
+    }
+  }
+  if (!q && !group_amax) return;
+  const uint32_t row_bits = block_max_u32(m);
+  if (group_amax && threadIdx.x == 0) atomicMax(group_amax + row / group_rows, row_bits << 16);
+  if (!q) return;
+  const float s = current_scale_from_amax(bf16_bits_to_float(row_bits));
+#pragma unroll
+  for (int k = 0; k < VPT; ++k) {
+    const int i = threadIdx.x + k * 256;
+    if (i < vec) q[row * vec + i] = quantize8f(v[k], s);
+  }
+  if (threadIdx.x == 0) {
+    scale[row] = s;
+    inv_scale[row] = 1.0f / s;
+  }
+}
+
+// SiLU*up with the row spread over a thread-block cluster of C CTAs (C <= 8): every CTA keeps
+// its slice of h in registers, the row's amax is the max of the C CTAs' partial maxima read
+// through distributed shared memory, and the cast happens from registers.  gate and up are read
+// once and h never travels through global memory unless the caller asks for it.
+__device__ __forceinline__ uint32_t ld_dsmem_u32(uint32_t local_smem_addr, uint32_t cta) {
+  uint32_t remote, v;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_smem_addr), "r"(cta));
+  asm volatile("ld.shared::cluster.u32 %0, [%1];" : "=r"(v) : "r"(remote) : "memory");
+  return v;
+}
+
+template <int VPT>
+__global__ void __launch_bounds__(256) silu_mul_cluster_kernel(const uint4* __restrict__ gate,
+                                                               const uint4* __restrict__ up, int64_t ld_vec, int vec,
+                                                               int C, uint4* __restrict__ h, uint2* __restrict__ q,
+                                                               float* __restrict__ scale,
+                                                               float* __restrict__ inv_scale,
+                                                               unsigned int* __restrict__ group_amax,
+                                                               int64_t group_rows) {
+  __shared__ uint32_t cta_max;
+  const int64_t row = blockIdx.y;
+  const int part = blockIdx.x;  // == rank in the cluster (cluster spans grid x)
+  const int per = (vec + C - 1) / C;
+  const int i0 = part * per;
+  const int i1 = min(vec, i0 + per);
+  const uint4* gr = gate + row * ld_vec;
+  const uint4* ur = up + row * ld_vec;
+  float hv[VPT][8];
+  uint32_t m = 0;
+#pragma unroll
+  for (int k = 0; k < VPT; ++k) {
+    const int i = i0 + threadIdx.x + k * 256;
+    if (i < i1) {
+      silu_mul8(__ldg(gr + i), __ldg(ur + i), hv[k]);
+      if (h) h[row * vec + i] = pack8(hv[k]);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) m = max(m, mag_bits16(hv[k][j]));
+    }
+  }
+  const uint32_t mine = block_max_u32(m);
+  if (threadIdx.x == 0) cta_max = mine;
+  // cluster barrier: every CTA's partial maximum is published
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+  uint32_t row_bits = 0;
+  for (int c = 0; c < C; ++c) row_bits = max(row_bits, ld_dsmem_u32(smem_u32(&cta_max), (uint32_t)c));
+  // second barrier: nobody leaves (and frees its shared memory) while a peer may still read it
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+  if (group_amax && part == 0 && threadIdx.x == 0) atomicMax(group_amax + row / group_rows, row_bits << 16);
+  if (!q) return;
+  const float s = current_scale_from_amax(bf16_bits_to_float(row_bits));
+#pragma unroll
+  for (int k = 0; k < VPT; ++k) {
+    const int i = i0 + threadIdx.x + k * 256;
+    if (i < i1) q[row * vec + i] = quantize8f(hv[k], s);
+  }
+  if (part == 0 && threadIdx.x == 0) {
+    scale[row] = s;
+    inv_scale[row] = 1.0f / s;
+  }
+}
+
+// RoPE + cache append, one CTA per new token, 16-byte accesses: work item = (head, 8 consecutive
+// pair indices); q and k heads are rotated, v heads copied.
+__global__ void __launch_bounds__(256) kv_append_rope_vec_kernel(
+    const uint4* __restrict__ qkv, int64_t ld_vec, int T, int Hq, int Hkv, int D, const int32_t* __restrict__ positions,
+    const uint4* __restrict__ cos_t, const uint4* __restrict__ sin_t, int64_t table_len, uint4* __restrict__ q_rot,
+    uint4* __restrict__ k_cache, uint4* __restrict__ v_cache, int64_t max_len, int store_rotated_k, int* d_status) {
+  const int64_t bt = blockIdx.x;
+  const int b = (int)(bt / T), t = (int)(bt % T);
+  const int64_t pos = (int64_t)positions[b] + t;
+  if (pos >= max_len || pos >= table_len || pos < 0) {
+    if (threadIdx.x == 0) atomicCAS(d_status, 0, XAXB_CACHE_OVERFLOW * 1000 + 41);
+    return;
+  }
+  const int hv = D / 16;       // 16-byte chunks per half head
+  const int dv = D / 8;        // 16-byte chunks per head
+  const int heads = Hq + 2 * Hkv;
+  const uint4* src_row = qkv + bt * ld_vec;
+  for (int w = threadIdx.x; w < heads * hv; w += blockDim.x) {
+    const int head = w / hv, c = w % hv;
+    const uint4* src = src_row + (int64_t)head * dv;
+    const uint4 a = __ldg(src + c), bb = __ldg(src + c + hv);
+    uint4 o1 = a, o2 = bb;
+    if (head < Hq + Hkv && (head < Hq || store_rotated_k)) {
+      const uint4 cv = __ldg(cos_t + pos * hv + c), sv = __ldg(sin_t + pos * hv + c);
+      float x1[8], x2[8], cc[8], ss[8], r1[8], r2[8];
+      unpack8(a, x1);
+      unpack8(bb, x2);
+      unpack8(cv, cc);
+      unpack8(sv, ss);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        r1[j] = bf16_round(x1[j] * cc[j]) - bf16_round(x2[j] * ss[j]);
+        r2[j] = bf16_round(x2[j] * cc[j]) + bf16_round(x1[j] * ss[j]);
+      }
+      o1 = pack8(r1);
+      o2 = pack8(r2);
+    }
+    uint4* dst;
+    if (head < Hq)
+      dst = q_rot + (bt * Hq + head) * dv;
+    else if (head < Hq + Hkv)
+      dst = k_cache + (((int64_t)b * max_len + pos) * Hkv + (head - Hq)) * dv;
+    else
+      dst = v_cache + (((int64_t)b * max_len + pos) * Hkv + (head - Hq - Hkv)) * dv;
+    dst[c] = o1;
+    dst[c + hv] = o2;
+  }
+}
+
 // ---------------------------------------------------------------------------------------
 
 __global__ void __launch_bounds__(256) embed_kernel(const int32_t* __restrict__ tokens, const uint4* __restrict__ table,
@@ -333,10 +500,21 @@ int xaxb_rmsnorm(xaxb_ctx* ctx, void* stream, const void* x_bf16, const void* we
     return XAXB_BAD_ARGUMENT;
   }
   const int64_t vec = dim / 8;
-  rmsnorm_kernel<<<(unsigned)rows, row_threads(vec), 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<const uint4*>(x_bf16), static_cast<const uint4*>(weight_bf16), eps, vec, static_cast<uint4*>(y_bf16),
-      static_cast<uint2*>(q_e4m3), scale, inv_scale, reinterpret_cast<unsigned int*>(group_amax),
-      group_rows > 0 ? group_rows : 1);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const uint4* xp = static_cast<const uint4*>(x_bf16);
+  const uint4* wp = static_cast<const uint4*>(weight_bf16);
+  uint4* yp = static_cast<uint4*>(y_bf16);
+  uint2* qp = static_cast<uint2*>(q_e4m3);
+  unsigned int* gp = reinterpret_cast<unsigned int*>(group_amax);
+  const int64_t gr = group_rows > 0 ? group_rows : 1;
+  if (vec > 64 && vec <= 256)
+    rmsnorm_reg_kernel<1><<<(unsigned)rows, 256, 0, st>>>(xp, wp, eps, (int)vec, yp, qp, scale, inv_scale, gp, gr);
+  else if (vec > 256 && vec <= 512)
+    rmsnorm_reg_kernel<2><<<(unsigned)rows, 256, 0, st>>>(xp, wp, eps, (int)vec, yp, qp, scale, inv_scale, gp, gr);
+  else if (vec > 512 && vec <= 1024)
+    rmsnorm_reg_kernel<4><<<(unsigned)rows, 256, 0, st>>>(xp, wp, eps, (int)vec, yp, qp, scale, inv_scale, gp, gr);
+  else
+    rmsnorm_kernel<<<(unsigned)rows, row_threads(vec), 0, st>>>(xp, wp, eps, vec, yp, qp, scale, inv_scale, gp, gr);
   return check_launch("rmsnorm_kernel");
 }
 
@@ -357,9 +535,44 @@ int xaxb_silu_mul(xaxb_ctx* ctx, void* stream, const void* gate_bf16, const void
     return XAXB_BAD_ARGUMENT;
   }
   const int64_t vec = dim / 8;
-  silu_mul_kernel<<<(unsigned)rows, row_threads(vec), 0, static_cast<cudaStream_t>(stream)>>>(
-      gate, up, ld / 8, vec, static_cast<uint4*>(h_bf16), static_cast<uint2*>(q_e4m3), scale, inv_scale,
-      reinterpret_cast<unsigned int*>(group_amax), group_rows > 0 ? group_rows : 1);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  uint4* hp = static_cast<uint4*>(h_bf16);
+  uint2* qp = static_cast<uint2*>(q_e4m3);
+  unsigned int* gp = reinterpret_cast<unsigned int*>(group_amax);
+  const int64_t gr = group_rows > 0 ? group_rows : 1;
+  // rows wide enough to be worth spreading, few enough rows that one CTA per row starves the GPU
+  if (vec >= 256 && rows <= 65535 && rows < 2048) {
+    int C = (int)((vec + 255) / 256);
+    if (C > 8) C = 8;
+    const int64_t per = (vec + C - 1) / C;
+    const int vpt = (int)((per + 255) / 256);
+    if (vpt <= 2) {
+      cudaLaunchConfig_t cfg = {};
+      cfg.gridDim = dim3((unsigned)C, (unsigned)rows, 1);
+      cfg.blockDim = dim3(256, 1, 1);
+      cfg.stream = st;
+      cudaLaunchAttribute attr[1];
+      attr[0].id = cudaLaunchAttributeClusterDimension;
+      attr[0].val.clusterDim.x = (unsigned)C;
+      attr[0].val.clusterDim.y = 1;
+      attr[0].val.clusterDim.z = 1;
+      cfg.attrs = attr;
+      cfg.numAttrs = 1;
+      cudaError_t e;
+      if (vpt == 1)
+        e = cudaLaunchKernelEx(&cfg, silu_mul_cluster_kernel<1>, gate, up, ld / 8, (int)vec, C, hp, qp, scale, inv_scale,
+                               gp, gr);
+      else
+        e = cudaLaunchKernelEx(&cfg, silu_mul_cluster_kernel<2>, gate, up, ld / 8, (int)vec, C, hp, qp, scale, inv_scale,
+                               gp, gr);
+      if (e != cudaSuccess) {
+        set_last_error("silu_mul_cluster_kernel launch: %s", cudaGetErrorString(e));
+        return XAXB_LAUNCH_FAILED;
+      }
+      return check_launch("silu_mul_cluster_kernel");
+    }
+  }
+  silu_mul_kernel<<<(unsigned)rows, row_threads(vec), 0, st>>>(gate, up, ld / 8, vec, hp, qp, scale, inv_scale, gp, gr);
   return check_launch("silu_mul_kernel");
 }
 
@@ -402,6 +615,20 @@ int xaxb_kv_append_rope(xaxb_ctx* ctx, void* stream, const void* qkv_bf16, int64
   }
   if (Hq + 2 * Hkv > 65535) return XAXB_UNSUPPORTED;
   Ctx* c = reinterpret_cast<Ctx*>(ctx);
+  if (D % 16 == 0 && ld % 8 == 0 &&
+      ((reinterpret_cast<uintptr_t>(qkv_bf16) | reinterpret_cast<uintptr_t>(cos_bf16) |
+        reinterpret_cast<uintptr_t>(sin_bf16) | reinterpret_cast<uintptr_t>(q_rot_bf16) |
+        reinterpret_cast<uintptr_t>(k_cache_bf16) | reinterpret_cast<uintptr_t>(v_cache_bf16)) & 15) == 0) {
+    const int items = (int)((Hq + 2 * Hkv) * (D / 16));
+    int threads = (items + 31) / 32 * 32;
+    if (threads > 256) threads = 256;
+    kv_append_rope_vec_kernel<<<(unsigned)(B * T), threads, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const uint4*>(qkv_bf16), ld / 8, (int)T, (int)Hq, (int)Hkv, (int)D, positions,
+        static_cast<const uint4*>(cos_bf16), static_cast<const uint4*>(sin_bf16), table_len,
+        static_cast<uint4*>(q_rot_bf16), static_cast<uint4*>(k_cache_bf16), static_cast<uint4*>(v_cache_bf16), max_len,
+        store_rotated_k, c->d_status);
+    return check_launch("kv_append_rope_vec_kernel");
+  }
   dim3 grid((unsigned)(B * T), (unsigned)(Hq + 2 * Hkv));
   kv_append_rope_kernel<<<grid, (unsigned)(D / 2), 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const __nv_bfloat16*>(qkv_bf16), ld, (int)T, (int)Hq, (int)Hkv, (int)D, positions,

@@ -309,6 +309,29 @@ def attn_decode(q_rot, k_cache, v_cache, positions, *, scale=None, k_is_rotated=
     return out
 
 
+def attn_decode_cast(q_rot, k_cache, v_cache, positions, *, scale=None, k_is_rotated=True, cos=None, sin=None,
+                     workspace=None, want_out=False):
+    """Decode attention whose output row [Hq*D] per sequence is cast to e4m3 with a per-token
+    scale inside the merge pass.  Returns (out bf16 or None, q e4m3 [B, Hq*D], row_scale, row_inv_scale)."""
+    B, Hq, D = q_rot.shape
+    _, max_len, Hkv, _ = k_cache.shape
+    ctx, st, lib = _c(2)
+    if workspace is None:
+        workspace = attn_decode_workspace(B, Hq, D, max_len, q_rot.device)
+    out = torch.empty_like(q_rot) if want_out else None
+    q = torch.empty((B, Hq * D), dtype=E4M3, device=q_rot.device)
+    rs = torch.empty((B,), dtype=torch.float32, device=q_rot.device)
+    ri = torch.empty((B,), dtype=torch.float32, device=q_rot.device)
+    if scale is None:
+        scale = 1.0 / math.sqrt(D)
+    with _Timed("attn_decode"):
+        check(lib.xaxb_attn_decode_cast(ctx, st, ptr(q_rot), ptr(k_cache), ptr(v_cache), ptr(positions), B, Hq, Hkv, D,
+                                        max_len, float(scale), 1 if k_is_rotated else 0, ptr(cos), ptr(sin),
+                                        0 if cos is None else cos.shape[0], ptr(out), ptr(q), ptr(rs), ptr(ri),
+                                        ptr(workspace), workspace.numel() * 4), "attn_decode_cast")
+    return out, q, rs, ri
+
+
 def attn_decode_static(q_rot, k_cache, v_cache, positions, *, scale=None, k_is_rotated=True, cos=None, sin=None,
                        out=None):
     """Decode attention for callers that can hand over no scratch memory: identical to
