@@ -366,13 +366,26 @@ def _attn_setup(ops, B, T, Hq, Hkv, D, max_len, starts, theta, seed, rotated=Tru
     return q_rot, kct, vct, pos, cos, sin, exp_out
 
 
+@pytest.fixture(params=[2, 1], ids=["pipelined", "cta-per-chunk"])
+def decode_variant(request):
+    """Run a test with each decode-attention kernel (2 = persistent pipeline, the default; 1 = one CTA per chunk)."""
+    from xax_b200 import _lib
+
+    lib = _lib.load()
+    assert lib.xaxb_attn_decode_force_variant(request.param) == 0
+    yield request.param
+    lib.xaxb_attn_decode_force_variant(0)
+    _lib.device_status()
+
+
 @pytest.mark.parametrize("Hq,Hkv,D,starts", [
     (8, 2, 128, [0, 62, 63, 64, 127, 128, 300, 1000]),
     (32, 8, 128, [511, 2047, 4000]),
     (32, 4, 64, [5, 129, 640, 767]),
     (4, 4, 128, [10, 200]),
+    (16, 1, 128, [700] * 40),
 ])
-def test_attn_decode_vs_oracle(ops, Hq, Hkv, D, starts):
+def test_attn_decode_vs_oracle(ops, decode_variant, Hq, Hkv, D, starts):
     B, max_len = len(starts), max(starts) + 1 + 37
     theta = 500000.0 if D == 128 else 10000.0
     q_rot, kc, vc, pos, cos, sin, exp = _attn_setup(ops, B, 1, Hq, Hkv, D, max_len, starts, theta, 11)
@@ -385,7 +398,7 @@ def test_attn_decode_vs_oracle(ops, Hq, Hkv, D, starts):
 
 
 @pytest.mark.parametrize("Hq,Hkv,D,starts", [(32, 8, 128, [0, 127, 128, 700]), (32, 4, 64, [5, 300]), (8, 2, 128, [64])])
-def test_attn_decode_fused_cast_equals_separate_cast(ops, Hq, Hkv, D, starts):
+def test_attn_decode_fused_cast_equals_separate_cast(ops, decode_variant, Hq, Hkv, D, starts):
     B, max_len = len(starts), max(starts) + 9
     q_rot, kc, vc, pos, cos, sin, exp = _attn_setup(ops, B, 1, Hq, Hkv, D, max_len, starts, 10000.0, 23)
     out = ops.attn_decode(q_rot, kc, vc, pos)
@@ -397,7 +410,7 @@ def test_attn_decode_fused_cast_equals_separate_cast(ops, Hq, Hkv, D, starts):
     assert torch.equal(q3.view(torch.uint8), q.view(torch.uint8))
 
 
-def test_attn_decode_rotate_on_load(ops):
+def test_attn_decode_rotate_on_load(ops, decode_variant):
     starts = [0, 100, 129, 515]
     B, Hq, Hkv, D = 4, 8, 2, 128
     max_len = 700
