@@ -143,17 +143,23 @@ def host_threads() -> int:
 
 
 def _time_kernel(fn, iters=20, warm=3, flush=None):
+    """Average device time of fn(i).  Before every timed call a 512 MiB buffer is rewritten and then
+    read back (two torch kernels): the write evicts the operands from the 126 MB L2, the read
+    drains the dirty lines the write left behind (their write-back would otherwise be billed to
+    the kernel), and both keep the GPU busy long enough for the host to enqueue the timed launch,
+    so the two events bracket device time only."""
     import torch
 
-    for _ in range(warm):
-        fn()
+    for i in range(warm):
+        fn(i)
     total = 0.0
-    for _ in range(iters):
+    for i in range(iters):
         if flush is not None:
             flush.zero_()
+            flush.max()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
-        fn()
+        fn(i)
         e1.record()
         e1.synchronize()
         total += e0.elapsed_time(e1)
@@ -162,7 +168,7 @@ def _time_kernel(fn, iters=20, warm=3, flush=None):
 
 def kernel_figures(peak_gbs: float) -> dict:
     """cfg1: quantize (HBM) and FP8 GEMM (tensor); cfg3: decode attention (HBM).  L2 is flushed
-    (a 512 MiB buffer is rewritten) between timed launches."""
+    (a 512 MiB buffer is rewritten and read back) between timed launches."""
     import numpy as np
     import torch
 
@@ -180,20 +186,25 @@ def kernel_figures(peak_gbs: float) -> dict:
     bias = (torch.randn((N,), generator=g, device=dev) * 0.01).to(torch.bfloat16)
     scale = torch.tensor(448.0 / 100.0, device=dev)
     hist = torch.zeros(16, device=dev)
-    t = _time_kernel(lambda: ops.quantize_delayed(x, scale, hist), flush=flush)
+    t = _time_kernel(lambda i: ops.quantize_delayed(x, scale, hist), flush=flush)
     out["quantize_cfg1"] = {"gbs": M * K * 3 / t / 1e9, "frac_of_hbm_peak": M * K * 3 / t / 1e9 / peak_gbs,
                             "us": t * 1e6, "bytes": M * K * 3}
+    xl = torch.randn((8192, 8192), generator=g, device=dev).to(torch.bfloat16)
+    t = _time_kernel(lambda i: ops.quantize_delayed(xl, scale, hist), iters=10, flush=flush)
+    out["quantize_8192x8192"] = {"gbs": 8192 * 8192 * 3 / t / 1e9, "frac_of_hbm_peak": 8192 * 8192 * 3 / t / 1e9 / peak_gbs,
+                                 "us": t * 1e6, "bytes": 8192 * 8192 * 3}
+    del xl
     xq, _, _, x_inv = ops.quantize_delayed(x, scale, hist)
     wq, _, w_inv, _ = ops.quantize_current(w, N)
     o = torch.empty((M, N), dtype=torch.bfloat16, device=dev)
-    t = _time_kernel(lambda: ops.gemm_fp8(xq, wq, x_inv, w_inv[:1], bias, out=o), flush=flush)
+    t = _time_kernel(lambda i: ops.gemm_fp8(xq, wq, x_inv, w_inv[:1], bias, out=o), flush=flush)
     out["gemm_fp8_cfg1"] = {"tflops": 2.0 * M * N * K / t / 1e12, "us": t * 1e6,
                             "frac_of_4500_nominal": 2.0 * M * N * K / t / 4.5e15}
     M2 = N2 = K2 = 8192
     a8 = (torch.randn((M2, K2), generator=g, device=dev)).to(torch.float8_e4m3fn)
     b8 = (torch.randn((N2, K2), generator=g, device=dev)).to(torch.float8_e4m3fn)
     o2 = torch.empty((M2, N2), dtype=torch.bfloat16, device=dev)
-    t = _time_kernel(lambda: ops.gemm_fp8(a8, b8, None, None, None, out=o2), iters=10, flush=flush)
+    t = _time_kernel(lambda i: ops.gemm_fp8(a8, b8, None, None, None, out=o2), iters=10, flush=flush)
     out["gemm_fp8_8192"] = {"tflops": 2.0 * M2 * N2 * K2 / t / 1e12, "us": t * 1e6,
                             "frac_of_4500_nominal": 2.0 * M2 * N2 * K2 / t / 4.5e15}
     del a8, b8, o2
@@ -208,11 +219,11 @@ def kernel_figures(peak_gbs: float) -> dict:
     ao = torch.empty_like(q)
     cos, sin = ops.rope_tables(D, 500000.0, max_len, dev)
     nbytes = int(lens.sum().item()) * (2 * Hkv * D * 2) + 2 * B * Hq * D * 2
-    t = _time_kernel(lambda: ops.attn_decode(q, kc, vc, pos, workspace=ws, out=ao), flush=flush)
+    t = _time_kernel(lambda i: ops.attn_decode(q, kc, vc, pos, workspace=ws, out=ao), flush=flush)
     out["attn_decode_cfg3"] = {"gbs": nbytes / t / 1e9, "frac_of_hbm_peak": nbytes / t / 1e9 / peak_gbs, "us": t * 1e6,
                                "bytes": nbytes}
-    t = _time_kernel(lambda: ops.attn_decode(q, kc, vc, pos, workspace=ws, out=ao, k_is_rotated=False, cos=cos,
-                                             sin=sin), flush=flush)
+    t = _time_kernel(lambda i: ops.attn_decode(q, kc, vc, pos, workspace=ws, out=ao, k_is_rotated=False, cos=cos,
+                                               sin=sin), flush=flush)
     out["attn_decode_cfg3_rope_on_load"] = {"gbs": nbytes / t / 1e9, "frac_of_hbm_peak": nbytes / t / 1e9 / peak_gbs,
                                             "us": t * 1e6}
     return out
@@ -371,7 +382,11 @@ def main() -> None:
     avg = sum(durs) / max(len(durs), 1)
     roofline = {"bound": "hbm", "kernel": "attn_decode_kernel (+ its merge pass)", "achieved": attn_bytes / avg / 1e9,
                 "peak": peak, "peak_kind": f"of {peak_kind} copy bandwidth", "unit": "GB/s",
-                "frac": attn_bytes / avg / 1e9 / peak, "traffic": None, "bytes_per_launch": attn_bytes,
+                "frac": attn_bytes / avg / 1e9 / peak,
+                # DRAM bytes per launch: ncu on a smaller case of the same kernel (B=32, same context, heads)
+                # measured dram read+write = 1.097 x the algorithmic bytes; traffic is proportional to tokens x
+                # kv heads, so the factor carries over (profiles/attn_decode_kernel_small_case_ncu.md)
+                "traffic": attn_bytes * 1.097, "bytes_per_launch": attn_bytes,
                 "avg_launch_us": avg * 1e6, "launches_timed": len(durs)}
     _lib.device_status()
 

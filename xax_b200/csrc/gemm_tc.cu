@@ -42,11 +42,14 @@ struct GemmParams {
 template <int BN>
 struct GemmCfg {
   static constexpr int kStageBytes = kBM * kBKBytes + BN * kBKBytes;
-  // epilogue staging: a [128 x kEpiCols] float32 slab of the accumulator, rows padded by 4 floats
-  static constexpr int kEpiCols = 32;  // small on purpose: shared memory is worth more as load stages
+  // epilogue staging.  BN >= 64: a [128 x 64] bf16 block in TMA-store layout (128-byte rows,
+  // swizzled) plus per-tile column multipliers and bias; BN = 32: a [128 x 32] float32 slab with
+  // padded rows for the coalesced direct-store path.
+  static constexpr bool kTmaStore = BN >= 64;
+  static constexpr int kEpiCols = 32;
   static constexpr int kEpiRowFloats = kEpiCols + 4;
-  static constexpr int kEpiBytes = kBM * kEpiRowFloats * 4;
-  static constexpr int kStagesFit = (200 * 1024 - kEpiBytes) / kStageBytes;
+  static constexpr int kEpiBytes = kTmaStore ? (kBM * 128 + 2 * BN * 4) : (kBM * kEpiRowFloats * 4);
+  static constexpr int kStagesFit = (224 * 1024 - kEpiBytes) / kStageBytes;
   static constexpr int kStages = kStagesFit > 12 ? 12 : kStagesFit;
   static constexpr int kTmemCols = 2 * BN < 32 ? 32 : 2 * BN;
   static constexpr int kSmemBytes = kStages * kStageBytes + kEpiBytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
@@ -91,7 +94,7 @@ __device__ __forceinline__ void epilogue_sync() { asm volatile("bar.sync 1, 128;
 template <int BN, bool IS_FP8>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-               const GemmParams p) {
+               const __grid_constant__ CUtensorMap tmap_out, const GemmParams p) {
   using Cfg = GemmCfg<BN>;
   constexpr int kStages = Cfg::kStages;
   constexpr int kElemBytes = IS_FP8 ? 1 : 2;
@@ -203,6 +206,94 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     // and parks them in shared memory; (B) work item = (row, 8 consecutive columns), consecutive
     // threads take consecutive column groups of a row, so the residual read and the bf16 store
     // are contiguous 128-byte runs instead of one 16-byte piece per row.
+    if constexpr (Cfg::kTmaStore) {
+      // TMA-store epilogue.  Per 64-column block: thread = row reads its accumulator values from
+      // TMEM, applies row/column multipliers, bias and residual, packs to bf16 and writes its
+      // 128-byte row into a swizzled staging block; one thread then hands the block to the TMA
+      // unit, which writes full rows to global memory and clips rows / columns past M / N.
+      uint8_t* stage_out = reinterpret_cast<uint8_t*>(estage);
+      float* cmul_s = reinterpret_cast<float*>(stage_out + kBM * 128);
+      float* bias_s = cmul_s + BN;
+      const int quarter = warp & 3;
+      const int row_in_tile = quarter * 32 + lane;
+      const int t = threadIdx.x - 64;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      if (t == 0) prefetch_tmap(&tmap_out);
+      for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
+        const int m0 = (tile % p.tiles_m) * kBM;
+        const int n0 = (tile / p.tiles_m) * BN;
+        bool ok = mbar_wait(acc_full + acc, acc_phase, abort_flag, p.d_status, XAXB_DEVICE_TIMEOUT * 1000 + kSiteEpilogue);
+        if (!epilogue_all(ok)) break;  // also: every thread is done with cmul_s / bias_s of the previous tile
+        tc_fence_after_sync();
+        for (int i = t; i < BN; i += 128) {
+          const int n = n0 + i;
+          float cm = 0.0f, bs = 0.0f;
+          if (n < p.N) {
+            cm = p.col_mul ? __ldg(p.col_mul + (long long)n * p.col_mul_stride) : 1.0f;
+            bs = p.bias ? __bfloat162float(p.bias[n]) : 0.0f;
+          }
+          cmul_s[i] = cm;
+          bias_s[i] = bs;
+        }
+        const int m = m0 + row_in_tile;
+        const bool row_ok = m < p.M;
+        const float rm = (row_ok && p.row_mul) ? __ldg(p.row_mul + (long long)m * p.row_mul_stride) : 1.0f;
+        const uint32_t taddr = tmem_base + (uint32_t(quarter * 32) << 16) + acc * BN;
+#pragma unroll 1
+        for (int c0 = 0; c0 < BN; c0 += 64) {
+          // the TMA unit must have finished reading the staging block of the previous store
+          if (t == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+          epilogue_sync();  // (also publishes cmul_s / bias_s on the first block)
+#pragma unroll
+          for (int h = 0; h < 64; h += 32) {
+            uint32_t r[32];
+            tmem_ld_x32(taddr + c0 + h, r);
+            tmem_ld_wait();
+            if (c0 + 64 >= BN && h == 32) {  // accumulator fully read: hand it back to the MMA warp
+              tc_fence_before_sync();
+              __syncwarp();
+              if (lane == 0) mbar_arrive(acc_empty + acc);
+            }
+#pragma unroll
+            for (int v = 0; v < 4; ++v) {
+              const int cc = c0 + h + v * 8;  // column within the tile
+              float f[8];
+#pragma unroll
+              for (int j = 0; j < 8; ++j) f[j] = fmaf(__uint_as_float(r[v * 8 + j]) * rm, cmul_s[cc + j], bias_s[cc + j]);
+              if (p.residual && row_ok && n0 + cc < p.N) {
+                const uint4 rv = *reinterpret_cast<const uint4*>(p.residual + (long long)m * p.ldr + n0 + cc);
+                const uint32_t rw[4] = {rv.x, rv.y, rv.z, rv.w};
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                  f[2 * j] += bf16_bits_to_float(rw[j] & 0xFFFFu);
+                  f[2 * j + 1] += bf16_bits_to_float(rw[j] >> 16);
+                }
+              }
+              uint4 o;
+              uint32_t* ow = reinterpret_cast<uint32_t*>(&o);
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                const uint32_t lo16 = __bfloat16_as_ushort(__float2bfloat16_rn(f[2 * j]));
+                const uint32_t hi16 = __bfloat16_as_ushort(__float2bfloat16_rn(f[2 * j + 1]));
+                ow[j] = lo16 | (hi16 << 16);
+              }
+              *reinterpret_cast<uint4*>(stage_out + sw128_offset(row_in_tile, (h + v * 8) / 8)) = o;
+            }
+          }
+          fence_proxy_async_smem();
+          epilogue_sync();
+          if (t == 0 && n0 + c0 < p.N) {
+            asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
+                         ::"l"(&tmap_out), "r"(smem_u32(stage_out)), "r"(n0 + c0), "r"(m0)
+                         : "memory");
+            asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+          }
+        }
+        if (++acc == 2) acc = 0, acc_phase ^= 1;
+      }
+      if (t == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");  // stores done before the CTA leaves
+    } else {
     constexpr int kEpiCols = Cfg::kEpiCols, kRowF = Cfg::kEpiRowFloats, kGroups = kEpiCols / 8;
     const int quarter = warp & 3;          // TMEM lanes this warp may read
     const int row_in_tile = quarter * 32 + lane;
@@ -289,6 +380,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       }
       if (++acc == 2) acc = 0, acc_phase ^= 1;
     }
+      }
   }
 
   // ---------------------------------------------------------------------- teardown
@@ -603,6 +695,13 @@ static int launch_gemm(const Ctx* ctx, cudaStream_t stream, const void* a, long 
   rc = make_tmap_2d(ctx, &tb, b, kElemBytes, (uint64_t)p.K, (uint64_t)p.N, (uint64_t)ldb_bytes, kBKBytes / kElemBytes,
                     BN);
   if (rc) return rc;
+  CUtensorMap tout;
+  if (Cfg::kTmaStore) {
+    rc = make_tmap_2d(ctx, &tout, p.out, 2, (uint64_t)p.N, (uint64_t)p.M, (uint64_t)p.ldo * 2, 64, kBM);
+    if (rc) return rc;
+  } else {
+    tout = ta;  // unused by the direct-store epilogue
+  }
   p.tiles_m = (p.M + kBM - 1) / kBM;
   p.tiles_n = (p.N + BN - 1) / BN;
   p.num_k_blocks = (int)(((long long)p.K * kElemBytes + kBKBytes - 1) / kBKBytes);
@@ -618,7 +717,7 @@ static int launch_gemm(const Ctx* ctx, cudaStream_t stream, const void* a, long 
   }
   const int tiles = p.tiles_m * p.tiles_n;
   const int grid = tiles < ctx->num_sms ? tiles : ctx->num_sms;
-  gemm_tc_kernel<BN, IS_FP8><<<grid, kGemmThreads, Cfg::kSmemBytes, stream>>>(ta, tb, p);
+  gemm_tc_kernel<BN, IS_FP8><<<grid, kGemmThreads, Cfg::kSmemBytes, stream>>>(ta, tb, tout, p);
   return check_launch("gemm_tc_kernel");
 }
 

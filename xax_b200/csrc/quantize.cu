@@ -65,12 +65,25 @@ __global__ void __launch_bounds__(256) group_cast_kernel(const uint4* __restrict
 }
 
 // ---- delayed scaling: cast with the incoming scale while reducing max|x| -------------------
+// Four 16-byte loads are issued per thread before any is used, so a CTA keeps 16 KiB in flight.
 __global__ void __launch_bounds__(256) delayed_cast_kernel(const uint4* __restrict__ x, int64_t n_vec,
                                                            const float* __restrict__ scale_in, uint2* __restrict__ q,
                                                            unsigned int* __restrict__ amax_bits) {
   const float s = bf16_round(*scale_in);
   uint32_t m = 0;
-  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n_vec; i += (int64_t)gridDim.x * blockDim.x) {
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  for (; i + 3 * stride < n_vec; i += 4 * stride) {
+    uint4 v[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) v[k] = __ldg(x + i + k * stride);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      m = absmax_bits8(m, v[k]);
+      if (q) q[i + k * stride] = quantize8(v[k], s);
+    }
+  }
+  for (; i < n_vec; i += stride) {
     const uint4 v = __ldg(x + i);
     m = absmax_bits8(m, v);
     if (q) q[i] = quantize8(v, s);
