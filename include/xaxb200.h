@@ -109,7 +109,8 @@ int xaxb_gemm_bf16(xaxb_ctx* ctx, void* stream, const void* a_bf16, int64_t lda,
                    int col_mul_stride, const void* bias_bf16, const void* residual_bf16, int64_t ldr, void* out_bf16,
                    int64_t ldo);
 
-/* Test hook: force the tile width (32/64/128/256, 0 = automatic) and the split-K factor
+/* Test hook: force the tile width (32/64/128/256, 512 = the CTA-pair kernel with 256 x 256 tiles
+ * where M > 128 and N >= 256, 0 = automatic) and the split-K factor
  * (1/2/4/8, 0 = automatic; > 1 needs M <= 128) of the following xaxb_gemm_* calls in this
  * process, so that tests can drive every kernel variant on the same inputs.  No counterpart
  * in the reference. */

@@ -196,6 +196,39 @@ def test_gemm_fp8_split_k_cluster_variants(ops, M, N, K, bn, split):
     _lib.device_status()
 
 
+@pytest.mark.parametrize("M,N,K,fp8", [(256, 256, 128, True), (512, 768, 1024, True), (300, 520, 272, True),
+                                           (1024, 2048, 2048, True), (129, 256, 4096, True), (512, 512, 512, False),
+                                           (2048, 8192, 2048, True)])
+def test_gemm_cta_pair_kernel(ops, M, N, K, fp8):
+    """The CTA-pair kernel (tcgen05.mma.cta_group::2, 256 x 256 tiles) against the single-CTA kernel
+    on the same inputs, with every epilogue term; integer-valued operands make both exact."""
+    from xax_b200 import _lib
+
+    rng = np.random.default_rng(M + N)
+    if fp8:
+        a = to_torch(rng.integers(-3, 4, (M, K)).astype(np.float32).astype(e4m3))
+        b = to_torch(rng.integers(-3, 4, (N, K)).astype(np.float32).astype(e4m3))
+        f = ops.gemm_fp8
+    else:
+        a = to_torch(rng.integers(-3, 4, (M, K)).astype(np.float32).astype(bf16))
+        b = to_torch(rng.integers(-3, 4, (N, K)).astype(np.float32).astype(bf16))
+        f = ops.gemm_bf16
+    rm = to_torch(rng.uniform(0.005, 0.02, M).astype(np.float32))
+    cm = to_torch(rng.uniform(0.01, 0.03, N).astype(np.float32))
+    bias = to_torch((rng.standard_normal(N) * 0.5).astype(bf16))
+    res = to_torch(rng.standard_normal((M, N)).astype(bf16))
+    lib = _lib.load()
+    outs = {}
+    for bn in (256, 512):
+        assert lib.xaxb_gemm_force_plan(bn, 1) == 0
+        try:
+            outs[bn] = f(a, b, rm, cm, bias, res)
+        finally:
+            lib.xaxb_gemm_force_plan(0, 0)
+    _lib.device_status()
+    assert torch.equal(outs[256], outs[512])
+
+
 @pytest.mark.parametrize("M,N,K", [(128, 256, 512), (200, 1000, 1088), (64, 32000, 2048)])
 def test_gemm_bf16(ops, M, N, K):
     rng = np.random.default_rng(3)

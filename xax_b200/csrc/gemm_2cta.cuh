@@ -1,0 +1,340 @@
+// Kernel 2, large-M variant (exact, but measured at about half the single-CTA kernel's rate, so
+// the dispatcher uses it only when a test forces it): 256 x 256 output tiles computed by PAIRS of CTAs (a thread-block
+// cluster of two SMs issuing tcgen05.mma.cta_group::2).
+//
+// The single-CTA kernel's 128 x 256 tile pulls 48 KiB of operands out of L2 for every
+// 128 x 256 x 128-byte MMA block and is bound by the SM's L2 read port (~105 GB/s per SM
+// measured), not by the tensor core.  With a CTA pair, CTA r loads rows [r*128, r*128+128) of
+// the A tile and rows [r*128, r*128+128) of the B tile -- 32 KiB per CTA for the same MMA work
+// per SM -- and one tcgen05.mma reads A and B halves from both CTAs' shared memory and writes
+// each CTA's 128 accumulator rows into that CTA's tensor memory.  No multicast is involved: each
+// CTA fetches its own halves with ordinary TMA tile loads.
+//
+// Synchronisation (leader = CTA rank 0 of the pair):
+//   full[s]      in the leader, 2 arrivals (one arrive.expect_tx per CTA) + both CTAs' TMA bytes;
+//   empty[s]     in each CTA; the leader's MMA thread commits to both (one local, one remote commit);
+//   acc_full[b]  in each CTA; committed to both by the leader after the tile's last MMA;
+//   acc_empty[b] in the leader, 8 arrivals (4 epilogue warps x 2 CTAs; the peer arrives remotely).
+// Included by gemm_tc.cu (shares GemmParams, the planner and the epilogue helpers).
+#pragma once
+
+namespace xaxb {
+
+constexpr int kSite2Producer = 31, kSite2Mma = 32, kSite2Epilogue = 33, kSite2MmaAcc = 34;
+
+__device__ __forceinline__ void mbar_arrive_expect_tx_cluster(uint32_t cluster_addr, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.release.cluster.shared::cluster.b64 _, [%0], %1;" ::"r"(cluster_addr), "r"(bytes)
+               : "memory");
+}
+
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+
+// TMA tile load whose completion bytes are credited to a barrier that may live in the peer CTA.
+__device__ __forceinline__ void tma_load_2d_pair(void* smem_dst, const CUtensorMap* map, uint32_t bar_cluster_addr, int x,
+                                                 int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(smem_u32(smem_dst)), "l"(map), "r"(bar_cluster_addr), "r"(x), "r"(y)
+      : "memory");
+}
+
+__device__ __forceinline__ void umma_commit_pair(uint32_t bar_cluster_addr) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar_cluster_addr)
+               : "memory");
+}
+
+template <bool IS_FP8>
+__device__ __forceinline__ void umma_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                          uint32_t accumulate) {
+  if (IS_FP8) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+  } else {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+  }
+}
+
+struct Gemm2Cfg {
+  static constexpr int kBN = 256;                       // columns per pair tile
+  static constexpr int kStageBytes = 2 * kBM * kBKBytes;  // per CTA: 128 rows of A + 128 rows of B
+  static constexpr int kEpiBytes = kBM * 128 + 2 * kBN * 4;
+  static constexpr int kStages = 6;
+  static constexpr int kTmemCols = 512;                 // two 256-column accumulators
+  static constexpr int kSmemBytes = kStages * kStageBytes + kEpiBytes + 1024 + 256;
+};
+
+template <bool IS_FP8>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+gemm_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                 const __grid_constant__ CUtensorMap tmap_out, const GemmParams p) {
+  using Cfg = Gemm2Cfg;
+  constexpr int kStages = Cfg::kStages, BN = Cfg::kBN;
+  constexpr int kElemBytes = IS_FP8 ? 1 : 2;
+  constexpr int kBKElems = kBKBytes / kElemBytes;
+  constexpr uint32_t kIdesc = umma_idesc(IS_FP8 ? kFmtE4M3 : kFmtBF16, IS_FP8 ? kFmtE4M3 : kFmtBF16, 0, 0, 2 * kBM, BN);
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* smem_a = smem;                              // kStages x 16 KiB
+  uint8_t* smem_b = smem + kStages * kBM * kBKBytes;   // kStages x 16 KiB
+  uint8_t* stage_out = smem + kStages * Cfg::kStageBytes;
+  float* cmul_s = reinterpret_cast<float*>(stage_out + kBM * 128);
+  float* bias_s = cmul_s + BN;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(stage_out + Cfg::kEpiBytes);
+  uint64_t* full = bars;
+  uint64_t* empty = bars + kStages;
+  uint64_t* acc_full = bars + 2 * kStages;
+  uint64_t* acc_empty = acc_full + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();  // 0 = leader
+  const int pair = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
+  const int num_tiles = p.tiles_m * p.tiles_n;  // 256 x 256 tiles
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(full + s, 2);
+      mbar_init(empty + s, 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(acc_full + i, 1);
+      mbar_init(acc_empty + i, 8);
+    }
+    *abort_flag = 0;
+    fence_mbar_init();
+    prefetch_tmap(&tmap_a);
+    prefetch_tmap(&tmap_b);
+    prefetch_tmap(&tmap_out);
+  }
+  if (warp == 2) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+                 "r"((uint32_t)Cfg::kTmemCols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  __syncwarp();
+  cluster_sync_all();  // both CTAs' barriers exist before anyone signals across the pair
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer (both CTAs)
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = pair; tile < num_tiles && ok; tile += num_pairs) {
+        const int m0 = (tile % p.tiles_m) * (2 * kBM) + (int)rank * kBM;
+        const int n0 = (tile / p.tiles_m) * BN + (int)rank * kBM;
+        int kk = (int)(((long long)tile * 5) % p.num_k_blocks);
+        for (int kb = 0; kb < p.num_k_blocks; ++kb) {
+          ok = mbar_wait(empty + stage, phase ^ 1, abort_flag, p.d_status, XAXB_DEVICE_TIMEOUT * 1000 + kSite2Producer);
+          if (!ok) break;
+          const uint32_t leader_full = dsmem_addr(smem_u32(full + stage), 0);
+          mbar_arrive_expect_tx_cluster(leader_full, Cfg::kStageBytes);
+          tma_load_2d_pair(smem_a + stage * kBM * kBKBytes, &tmap_a, leader_full, kk * kBKElems, m0);
+          tma_load_2d_pair(smem_b + stage * kBM * kBKBytes, &tmap_b, leader_full, kk * kBKElems, n0);
+          if (++kk == p.num_k_blocks) kk = 0;
+          if (++stage == kStages) stage = 0, phase ^= 1;
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer (leader only)
+    if (lane == 0 && rank == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      bool ok = true;
+      for (int tile = pair; tile < num_tiles && ok; tile += num_pairs) {
+        ok = mbar_wait(acc_empty + acc, acc_phase ^ 1, abort_flag, p.d_status, XAXB_DEVICE_TIMEOUT * 1000 + kSite2MmaAcc);
+        if (!ok) break;
+        tc_fence_after_sync();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = 0; kb < p.num_k_blocks; ++kb) {
+          ok = mbar_wait(full + stage, phase, abort_flag, p.d_status, XAXB_DEVICE_TIMEOUT * 1000 + kSite2Mma);
+          if (!ok) break;
+          tc_fence_after_sync();
+          const uint64_t a_desc = umma_desc_kmajor_sw128(smem_u32(smem_a + stage * kBM * kBKBytes));
+          const uint64_t b_desc = umma_desc_kmajor_sw128(smem_u32(smem_b + stage * kBM * kBKBytes));
+#pragma unroll
+          for (int k = 0; k < kBKBytes / 32; ++k)
+            umma_pair<IS_FP8>(d_tmem, a_desc + 2 * k, b_desc + 2 * k, kIdesc, (kb | k) != 0);
+          umma_commit_pair(smem_u32(empty + stage));
+          umma_commit_pair(dsmem_addr(smem_u32(empty + stage), 1));
+          if (++stage == kStages) stage = 0, phase ^= 1;
+        }
+        if (!ok) break;
+        umma_commit_pair(smem_u32(acc_full + acc));
+        umma_commit_pair(dsmem_addr(smem_u32(acc_full + acc), 1));
+        if (++acc == 2) acc = 0, acc_phase ^= 1;
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue (both CTAs)
+    const int quarter = warp & 3;
+    const int row_in_tile = quarter * 32 + lane;
+    const int t = threadIdx.x - 64;
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    for (int tile = pair; tile < num_tiles; tile += num_pairs) {
+      const int m0 = (tile % p.tiles_m) * (2 * kBM) + (int)rank * kBM;
+      const int n0 = (tile / p.tiles_m) * BN;
+      bool ok = mbar_wait(acc_full + acc, acc_phase, abort_flag, p.d_status, XAXB_DEVICE_TIMEOUT * 1000 + kSite2Epilogue);
+      if (!epilogue_all(ok)) break;
+      tc_fence_after_sync();
+      for (int i = t; i < BN; i += 128) {
+        const int n = n0 + i;
+        float cm = 0.0f, bs = 0.0f;
+        if (n < p.N) {
+          cm = p.col_mul ? __ldg(p.col_mul + (long long)n * p.col_mul_stride) : 1.0f;
+          bs = p.bias ? __bfloat162float(p.bias[n]) : 0.0f;
+        }
+        cmul_s[i] = cm;
+        bias_s[i] = bs;
+      }
+      const int m = m0 + row_in_tile;
+      const bool row_ok = m < p.M;
+      const float rm = (row_ok && p.row_mul) ? __ldg(p.row_mul + (long long)m * p.row_mul_stride) : 1.0f;
+      const uint32_t taddr = tmem_base + (uint32_t(quarter * 32) << 16) + acc * BN;
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN; c0 += 64) {
+        if (t == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+        epilogue_sync();
+#pragma unroll
+        for (int h = 0; h < 64; h += 32) {
+          uint32_t r[32];
+          tmem_ld_x32(taddr + c0 + h, r);
+          tmem_ld_wait();
+          if (c0 + 64 >= BN && h == 32) {  // accumulator read out: tell the leader's MMA thread
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(dsmem_addr(smem_u32(acc_empty + acc), 0));
+          }
+#pragma unroll
+          for (int v = 0; v < 4; ++v) {
+            const int cc = c0 + h + v * 8;
+            float f[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) f[j] = fmaf(__uint_as_float(r[v * 8 + j]) * rm, cmul_s[cc + j], bias_s[cc + j]);
+            if (p.residual && row_ok && n0 + cc < p.N) {
+              const uint4 rv = *reinterpret_cast<const uint4*>(p.residual + (long long)m * p.ldr + n0 + cc);
+              const uint32_t rw[4] = {rv.x, rv.y, rv.z, rv.w};
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                f[2 * j] += bf16_bits_to_float(rw[j] & 0xFFFFu);
+                f[2 * j + 1] += bf16_bits_to_float(rw[j] >> 16);
+              }
+            }
+            uint4 o;
+            uint32_t* ow = reinterpret_cast<uint32_t*>(&o);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const uint32_t lo16 = __bfloat16_as_ushort(__float2bfloat16_rn(f[2 * j]));
+              const uint32_t hi16 = __bfloat16_as_ushort(__float2bfloat16_rn(f[2 * j + 1]));
+              ow[j] = lo16 | (hi16 << 16);
+            }
+            *reinterpret_cast<uint4*>(stage_out + sw128_offset(row_in_tile, (h + v * 8) / 8)) = o;
+          }
+        }
+        fence_proxy_async_smem();
+        epilogue_sync();
+        if (t == 0 && n0 + c0 < p.N && m0 < p.M) {
+          asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
+                       ::"l"(&tmap_out), "r"(smem_u32(stage_out)), "r"(n0 + c0), "r"(m0)
+                       : "memory");
+          asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+        }
+      }
+      if (++acc == 2) acc = 0, acc_phase ^= 1;
+    }
+    if (t == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+  }
+
+  // ---------------------------------------------------------------------- teardown
+  tc_fence_before_sync();
+  __syncthreads();
+  __syncwarp();
+  cluster_sync_all();  // no remote arrival or operand read can still target a CTA that leaves
+  if (warp == 2) {
+    tc_fence_after_sync();
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)Cfg::kTmemCols)
+                 : "memory");
+  }
+}
+
+template <bool IS_FP8>
+static int launch_gemm_2cta(const Ctx* ctx, cudaStream_t stream, const void* a, long long lda_bytes, const void* b,
+                            long long ldb_bytes, GemmParams& p) {
+  using Cfg = Gemm2Cfg;
+  constexpr int kElemBytes = IS_FP8 ? 1 : 2;
+  CUtensorMap ta, tb, tout;
+  int rc = make_tmap_2d(ctx, &ta, a, kElemBytes, (uint64_t)p.K, (uint64_t)p.M, (uint64_t)lda_bytes,
+                        kBKBytes / kElemBytes, kBM);
+  if (rc) return rc;
+  rc = make_tmap_2d(ctx, &tb, b, kElemBytes, (uint64_t)p.K, (uint64_t)p.N, (uint64_t)ldb_bytes, kBKBytes / kElemBytes,
+                    kBM);
+  if (rc) return rc;
+  rc = make_tmap_2d(ctx, &tout, p.out, 2, (uint64_t)p.N, (uint64_t)p.M, (uint64_t)p.ldo * 2, 64, kBM);
+  if (rc) return rc;
+  p.tiles_m = (p.M + 2 * kBM - 1) / (2 * kBM);
+  p.tiles_n = (p.N + Cfg::kBN - 1) / Cfg::kBN;
+  p.num_k_blocks = (int)(((long long)p.K * kElemBytes + kBKBytes - 1) / kBKBytes);
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_2cta_kernel<IS_FP8>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         Cfg::kSmemBytes);
+    if (e != cudaSuccess) {
+      set_last_error("gemm 2-CTA: cudaFuncSetAttribute(%d bytes): %s", Cfg::kSmemBytes, cudaGetErrorString(e));
+      return XAXB_LAUNCH_FAILED;
+    }
+    attr_set = true;
+  }
+  const int tiles = p.tiles_m * p.tiles_n;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)(2 * (ctx->num_sms / 2)), 1, 1);
+  cfg.blockDim = dim3(kGemmThreads, 1, 1);
+  cfg.dynamicSmemBytes = Cfg::kSmemBytes;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  // The kernel is persistent: every pair must be resident at once.  Not every SM has a partner
+  // it can form a pair with, so ask how many pairs fit instead of assuming num_sms / 2.
+  static int max_pairs = 0;
+  if (max_pairs == 0) {
+    int n = 0;
+    cudaError_t qe = cudaOccupancyMaxActiveClusters(&n, gemm_2cta_kernel<IS_FP8>, &cfg);
+    max_pairs = (qe == cudaSuccess && n > 0) ? n : ctx->num_sms / 2 - 8;
+  }
+  const int pairs = tiles < max_pairs ? tiles : max_pairs;
+  cfg.gridDim = dim3((unsigned)(2 * pairs), 1, 1);
+  cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_2cta_kernel<IS_FP8>, ta, tb, tout, p);
+  if (e != cudaSuccess) {
+    set_last_error("gemm_2cta_kernel launch: %s", cudaGetErrorString(e));
+    return XAXB_LAUNCH_FAILED;
+  }
+  return check_launch("gemm_2cta_kernel");
+}
+
+}  // namespace xaxb

@@ -721,6 +721,12 @@ static int launch_gemm(const Ctx* ctx, cudaStream_t stream, const void* a, long 
   return check_launch("gemm_tc_kernel");
 }
 
+}  // namespace xaxb
+
+#include "gemm_2cta.cuh"
+
+namespace xaxb {
+
 // Tile width (and, for M <= 128, the split-K factor) from a small cost model: a CTA ingests
 // operand bytes at a bounded rate, the GPU as a whole at HBM rate, and the tensor core has its
 // own rate.  Narrow tiles give more CTAs but re-read A once per N tile; splitting K gives more
@@ -763,7 +769,7 @@ static GemmPlan pick_plan(long long M, long long N, long long K, int elem_bytes,
       if (t < best_t) best_t = t, best = {bn, s};
     }
   }
-  if (g_force_bn) best.bn = g_force_bn;
+  if (g_force_bn && g_force_bn != 512) best.bn = g_force_bn;
   if (g_force_split) best.split = g_force_split;
   return best;
 }
@@ -798,6 +804,9 @@ static int gemm_entry(xaxb_ctx* ctx_, void* stream, const void* a, int64_t lda, 
   p.d_status = ctx->d_status;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const GemmPlan plan = pick_plan(M, N, K, eb, ctx->num_sms);
+  // The CTA-pair kernel (256 x 256 tiles, a third less operand traffic per SM) is exact but
+  // measured at about half the single-CTA kernel's rate, so it runs only when a test forces it.
+  if (g_force_bn == 512 && M > kBM && N >= 256) return launch_gemm_2cta<IS_FP8>(ctx, s, a, lda * eb, b, ldb * eb, p);
   if (plan.split > 1) {
     if (M > kBM || plan.split > 8) {
       set_last_error("gemm: split-K plan (bn=%d, split=%d) is invalid for M=%lld", plan.bn, plan.split, (long long)M);
@@ -825,7 +834,7 @@ using namespace xaxb;
 extern "C" {
 
 int xaxb_gemm_force_plan(int bn, int split) {
-  if ((bn != 0 && bn != 32 && bn != 64 && bn != 128 && bn != 256) ||
+  if ((bn != 0 && bn != 32 && bn != 64 && bn != 128 && bn != 256 && bn != 512) ||
       (split != 0 && split != 1 && split != 2 && split != 4 && split != 8))
     return XAXB_BAD_ARGUMENT;
   g_force_bn = bn;
