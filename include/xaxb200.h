@@ -216,9 +216,10 @@ int xaxb_attn_decode(xaxb_ctx* ctx, void* stream, const void* q_rot_bf16, const 
                      const void* sin_bf16, int64_t table_len, void* out_bf16, void* workspace,
                      int64_t workspace_bytes);
 
-/* Test hook: 0 = automatic choice of the decode-attention kernel (currently 1), 1 = one CTA per
- * 128-token chunk, 2 = persistent software-pipelined kernel.  Process-wide.  No counterpart in the
- * reference. */
+/* Test hook: 0 = automatic choice of the decode-attention kernel (currently 1), 1 = the
+ * chunk-walking kernel with its own choice of chunks per CTA, 2 = persistent software-pipelined
+ * kernel, 10 + n (n = 1 .. 64) = the chunk-walking kernel with n 128-token chunks per CTA.
+ * Process-wide.  No counterpart in the reference. */
 int xaxb_attn_decode_force_variant(int variant);
 
 /*

@@ -399,9 +399,10 @@ def _attn_setup(ops, B, T, Hq, Hkv, D, max_len, starts, theta, seed, rotated=Tru
     return q_rot, kct, vct, pos, cos, sin, exp_out
 
 
-@pytest.fixture(params=[2, 1], ids=["pipelined", "cta-per-chunk"])
+@pytest.fixture(params=[2, 1, 11, 13], ids=["pipelined", "chunk-walk", "one-chunk-per-cta", "three-chunks-per-cta"])
 def decode_variant(request):
-    """Run a test with each decode-attention kernel (2 = persistent pipeline, the default; 1 = one CTA per chunk)."""
+    """Run a test with each decode-attention kernel (1 = chunk-walking kernel, the default; 10 + n = the same
+    with n chunks per CTA; 2 = persistent pipeline)."""
     from xax_b200 import _lib
 
     lib = _lib.load()

@@ -1,7 +1,9 @@
 // Kernel 3a: GQA decode attention over a bf16 KV cache, split over 128-token chunks.
 //
-// HBM-bound: every K and V row is read exactly once.  One CTA owns one (sequence, kv head,
-// 128-token chunk).  The chunk's K and V tiles ([128 tokens x D] bf16) are brought in by TMA
+// HBM-bound: every K and V row is read exactly once.  The chunks of one (sequence, kv head) are
+// dealt to a few CTAs; a CTA walks its chunks one at a time, requesting the next chunk's K tile
+// as soon as the first MMA has consumed the current one and the next V tile as soon as the
+// second MMA has, so that loads stay in flight under the softmax.  The chunk's K and V tiles ([128 tokens x D] bf16) are brought in by TMA
 // into 128-byte-swizzled shared memory and consumed in place by tcgen05.mma -- the threads
 // never touch K or V (unless K is stored un-rotated, see below):
 //
@@ -16,8 +18,9 @@
 //                                              A = V tile (MN-major: D contiguous), B = P^T
 //                                              written to shared memory as bf16 (K-major)
 //
-// Each CTA writes (max, sum, O^T) for its chunk to the workspace; a second kernel merges the
-// chunks of a sequence with the usual log-sum-exp weights and writes bf16 output.
+// Each CTA merges its chunks in registers (running max / sum / O^T) and writes one partial
+// result to the workspace; a second kernel merges the partial results of a sequence with the
+// usual log-sum-exp weights and writes bf16 output.
 //
 // With k_is_rotated = 0 the cache holds K as projected and the rotation is applied on load:
 // after the TMA lands, thread t rotates row t of the K tile in shared memory with row
@@ -55,20 +58,28 @@ struct DecodeSmem {
   static constexpr int kQBytes = kNPad * D * 2;
   static constexpr int kPBytes = kNPad * kChunk * 2;
   static constexpr int kVBytes = 2 * kHalfBytes;               // D = 64: second half is a zero pad
-  static constexpr int kBytes = kTileBytes + kVBytes + kQBytes + kPBytes + 1024 + 512;
+  static constexpr int kBytes = kTileBytes + kVBytes + kQBytes + kPBytes + 1024 /*alignment*/ + 1024;
 };
 
-template <int D>
+__device__ __forceinline__ float warp_max_f32(float v) {
+  float r;
+  asm volatile("redux.sync.max.f32 %0, %1, 0xffffffff;" : "=f"(r) : "f"(v));
+  return r;
+}
+
+// GT = the group size rounded up to a power of two: only GT of the 16 UMMA columns are read back,
+// reduced and written as P^T.  (Column n of either product depends on row n of its B operand
+// only, so whatever the unused rows of Q and P^T hold never reaches a column that is read.)
+template <int D, int GT>
 __global__ void __launch_bounds__(128) attn_decode_kernel(const __grid_constant__ CUtensorMap tmap_k,
                                                           const __grid_constant__ CUtensorMap tmap_v,
                                                           const DecodeParams p) {
   using SM = DecodeSmem<D>;
   constexpr int kBoxes = D / 64;  // 128-byte-wide boxes per row
-  const int chunk = blockIdx.x, hk = blockIdx.y, b = blockIdx.z;
+  const int first = blockIdx.x, stride = gridDim.x, hk = blockIdx.y, b = blockIdx.z;
   const int L = p.positions[b] + 1;
-  const int tok0 = chunk * kChunk;
-  if (tok0 >= L) return;
-  const int valid = min(kChunk, L - tok0);
+  const int n_chunks = (L + kChunk - 1) / kChunk;
+  if (first >= n_chunks) return;
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -83,7 +94,8 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(const __grid_constant_
   uint64_t* bar_o = bars + 3;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 4);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-  float* red = reinterpret_cast<float*>(tmem_slot + 2);  // [4 warps][16]
+  float* red_max = reinterpret_cast<float*>(tmem_slot + 2);  // [4 warps][16]
+  float* red_sum = red_max + 4 * kNPad;                       // [4 warps][16]
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
 
@@ -97,19 +109,21 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(const __grid_constant_
     mbar_arrive_expect_tx(bar_k, SM::kTileBytes);
     mbar_arrive_expect_tx(bar_v, SM::kTileBytes);
 #pragma unroll
-    for (int x = 0; x < kBoxes; ++x) tma_load_4d(sK + x * SM::kHalfBytes, &tmap_k, bar_k, x * 64, hk, tok0, b);
+    for (int x = 0; x < kBoxes; ++x)
+      tma_load_4d(sK + x * SM::kHalfBytes, &tmap_k, bar_k, x * 64, hk, first * kChunk, b);
 #pragma unroll
-    for (int x = 0; x < kBoxes; ++x) tma_load_4d(sV + x * SM::kHalfBytes, &tmap_v, bar_v, x * 64, hk, tok0, b);
+    for (int x = 0; x < kBoxes; ++x)
+      tma_load_4d(sV + x * SM::kHalfBytes, &tmap_v, bar_v, x * 64, hk, first * kChunk, b);
   }
   if (warp == 1) {
     tmem_alloc(tmem_slot, 32);
     tmem_relinquish();
   }
 
-  // Q of this group -> shared memory, K-major rows of D elements, rows >= G zero.
+  // Q of this group -> shared memory, K-major rows of D elements; rows G .. GT-1 zero.
   {
     constexpr int kChunksPerRow = D / 8;  // 16-byte chunks
-    for (int i = tid; i < kNPad * kChunksPerRow; i += 128) {
+    for (int i = tid; i < GT * kChunksPerRow; i += 128) {
       const int g = i / kChunksPerRow, c = i % kChunksPerRow;
       uint4 v = make_uint4(0, 0, 0, 0);
       if (g < p.G)
@@ -130,162 +144,199 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(const __grid_constant_
   const uint32_t tmem_s = tmem_base;        // columns [0, 16)
   const uint32_t tmem_o = tmem_base + 16;   // columns [16, 32)
 
-  bool ok = mbar_wait(bar_k, 0, abort_flag, p.d_status, XAXB_DEVICE_TIMEOUT * 1000 + kSiteDecK);
-  ok = __syncthreads_and(ok);
+  // Running log-sum-exp merge of this CTA's chunks: thread d keeps O^T[d, g] for its head
+  // dimension d; every thread keeps the running maximum and denominator of every head.
+  float m_run[GT], l_run[GT], o_acc[GT];
+#pragma unroll
+  for (int g = 0; g < GT; ++g) m_run[g] = -INFINITY, l_run[g] = 0.0f, o_acc[g] = 0.0f;
 
-  if (!p.k_is_rotated && ok) {
-    // Rotate K row `tid` in place: pair (i, i + D/2) lives in chunk i/8 of box (i / 64) and
-    // chunk (i + D/2)/8 of the other half.
-    const long long pos = tok0 + tid;
-    if (tid < valid && pos < p.table_len) {
-      constexpr int half = D / 2;
-      const __nv_bfloat16* cr = p.cos_t + pos * half;
-      const __nv_bfloat16* sr = p.sin_t + pos * half;
-      for (int c = 0; c < half / 8; ++c) {
-        const int c2 = c + half / 8;
-        uint4* p1 = reinterpret_cast<uint4*>(sK + (c / 8) * SM::kHalfBytes + sw128_offset(tid, c % 8));
-        uint4* p2 = reinterpret_cast<uint4*>(sK + (c2 / 8) * SM::kHalfBytes + sw128_offset(tid, c2 % 8));
-        uint4 a = *p1, bb = *p2;
-        const uint4 cv = __ldg(reinterpret_cast<const uint4*>(cr) + c);
-        const uint4 sv = __ldg(reinterpret_cast<const uint4*>(sr) + c);
-        uint32_t* aw = reinterpret_cast<uint32_t*>(&a);
-        uint32_t* bw = reinterpret_cast<uint32_t*>(&bb);
-        const uint32_t* cw = reinterpret_cast<const uint32_t*>(&cv);
-        const uint32_t* sw = reinterpret_cast<const uint32_t*>(&sv);
+  // A CTA walks chunks first, first + stride, ...: the next chunk's K tile is requested as soon
+  // as S^T has been computed from the current one, and its V tile as soon as O^T has, so loads
+  // stay in flight under the softmax / second-MMA tail.  Every barrier completes once per
+  // iteration: parity = iteration & 1.
+  bool ok = true;
+  uint32_t ph = 0;
+  for (int chunk = first; chunk < n_chunks; chunk += stride, ph ^= 1) {
+    const int tok0 = chunk * kChunk;
+    const int valid = min(kChunk, L - tok0);
+    const int next = chunk + stride;
+
+    if (!p.k_is_rotated) {
+      // Rotate K row `tid` in place: pair (i, i + D/2) lives in chunk i/8 of box (i / 64) and
+      // chunk (i + D/2)/8 of the other half.
+      ok = mbar_wait(bar_k, ph, abort_flag, p.d_status, XAXB_DEVICE_TIMEOUT * 1000 + kSiteDecK);
+      const long long pos = tok0 + tid;
+      if (ok && tid < valid && pos < p.table_len) {
+        constexpr int half = D / 2;
+        const __nv_bfloat16* cr = p.cos_t + pos * half;
+        const __nv_bfloat16* sr = p.sin_t + pos * half;
+        for (int c = 0; c < half / 8; ++c) {
+          const int c2 = c + half / 8;
+          uint4* p1 = reinterpret_cast<uint4*>(sK + (c / 8) * SM::kHalfBytes + sw128_offset(tid, c % 8));
+          uint4* p2 = reinterpret_cast<uint4*>(sK + (c2 / 8) * SM::kHalfBytes + sw128_offset(tid, c2 % 8));
+          uint4 a = *p1, bb = *p2;
+          const uint4 cv = __ldg(reinterpret_cast<const uint4*>(cr) + c);
+          const uint4 sv = __ldg(reinterpret_cast<const uint4*>(sr) + c);
+          uint32_t* aw = reinterpret_cast<uint32_t*>(&a);
+          uint32_t* bw = reinterpret_cast<uint32_t*>(&bb);
+          const uint32_t* cw = reinterpret_cast<const uint32_t*>(&cv);
+          const uint32_t* sw = reinterpret_cast<const uint32_t*>(&sv);
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          uint32_t o1 = 0, o2 = 0;
+          for (int j = 0; j < 4; ++j) {
+            uint32_t o1 = 0, o2 = 0;
 #pragma unroll
-          for (int hsel = 0; hsel < 2; ++hsel) {
-            const int sh = hsel * 16;
-            const float x1 = bf16_bits_to_float((aw[j] >> sh) & 0xFFFFu);
-            const float x2 = bf16_bits_to_float((bw[j] >> sh) & 0xFFFFu);
-            const float cc = bf16_bits_to_float((cw[j] >> sh) & 0xFFFFu);
-            const float ss = bf16_bits_to_float((sw[j] >> sh) & 0xFFFFu);
-            const float r1 = bf16_round(x1 * cc) - bf16_round(x2 * ss);
-            const float r2 = bf16_round(x2 * cc) + bf16_round(x1 * ss);
-            o1 |= (uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(r1)) << sh;
-            o2 |= (uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(r2)) << sh;
+            for (int hsel = 0; hsel < 2; ++hsel) {
+              const int sh = hsel * 16;
+              const float x1 = bf16_bits_to_float((aw[j] >> sh) & 0xFFFFu);
+              const float x2 = bf16_bits_to_float((bw[j] >> sh) & 0xFFFFu);
+              const float cc = bf16_bits_to_float((cw[j] >> sh) & 0xFFFFu);
+              const float ss = bf16_bits_to_float((sw[j] >> sh) & 0xFFFFu);
+              const float r1 = bf16_round(x1 * cc) - bf16_round(x2 * ss);
+              const float r2 = bf16_round(x2 * cc) + bf16_round(x1 * ss);
+              o1 |= (uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(r1)) << sh;
+              o2 |= (uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(r2)) << sh;
+            }
+            aw[j] = o1;
+            bw[j] = o2;
           }
-          aw[j] = o1;
-          bw[j] = o2;
+          *p1 = a;
+          *p2 = bb;
         }
-        *p1 = a;
-        *p2 = bb;
+      }
+      fence_proxy_async_smem();
+      ok = __syncthreads_and(ok);
+      if (!ok) break;
+    }
+
+    // ---- S^T = K Q^T ---------------------------------------------------------------------
+    if (tid == 0) {
+      if (mbar_wait(bar_k, ph, abort_flag, p.d_status, XAXB_DEVICE_TIMEOUT * 1000 + kSiteDecK)) {
+        tc_fence_after_sync();
+        constexpr uint32_t idesc = umma_idesc(kFmtBF16, kFmtBF16, 0, 0, 128, kNPad);
+#pragma unroll
+        for (int k = 0; k < D / 16; ++k) {  // 16 bf16 = 32 bytes of K per MMA
+          const uint32_t box = k / 4, off = (k % 4) * 32;
+          const uint64_t a_desc = umma_desc_kmajor_sw128(smem_u32(sK + box * SM::kHalfBytes) + off);
+          const uint64_t b_desc = umma_desc_kmajor_sw128(smem_u32(sQ + box * (kNPad * 128)) + off);
+          umma_f16(tmem_s, a_desc, b_desc, idesc, k != 0);
+        }
+        umma_commit(bar_s);
       }
     }
+    ok = mbar_wait(bar_s, ph, abort_flag, p.d_status, XAXB_DEVICE_TIMEOUT * 1000 + kSiteDecS);
+    if (tid == 0 && ok && next < n_chunks) {  // the K tile has been consumed: fetch the next one
+      mbar_arrive_expect_tx(bar_k, SM::kTileBytes);
+#pragma unroll
+      for (int x = 0; x < kBoxes; ++x)
+        tma_load_4d(sK + x * SM::kHalfBytes, &tmap_k, bar_k, x * 64, hk, next * kChunk, b);
+    }
+
+    // ---- softmax numerators: thread = token ------------------------------------------------
+    float pvals[GT];
+    if (ok) {
+      tc_fence_after_sync();
+      uint32_t r[16];
+      tmem_ld_x16(tmem_s + (uint32_t(warp * 32) << 16), r);
+      tmem_ld_wait();
+      tc_fence_before_sync();
+      const bool tok_ok = tid < valid;
+#pragma unroll
+      for (int g = 0; g < GT; ++g) {
+        pvals[g] = tok_ok ? __uint_as_float(r[g]) * p.sm_scale : -INFINITY;
+        const float wm = warp_max_f32(pvals[g]);
+        if (lane == 0) red_max[warp * kNPad + g] = wm;
+      }
+    }
+    ok = __syncthreads_and(ok);
+    if (!ok) break;
+    float m_c[GT];
+    {
+      // P^T as the B operand: row g, 128 tokens (two 64-token boxes), K-major, swizzled.
+      const int box = tid / 64, within = tid % 64;
+#pragma unroll
+      for (int g = 0; g < GT; ++g) {
+        m_c[g] = fmaxf(fmaxf(red_max[g], red_max[kNPad + g]), fmaxf(red_max[2 * kNPad + g], red_max[3 * kNPad + g]));
+        const float e = (tid < valid) ? __expf(pvals[g] - m_c[g]) : 0.0f;
+        pvals[g] = e;
+        const uint32_t off = box * (kNPad * 128) + sw128_offset(g, within / 8) + (within % 8) * 2;
+        *reinterpret_cast<__nv_bfloat16*>(sP + off) = __float2bfloat16_rn(e);
+      }
+    }
+    ok = mbar_wait(bar_v, ph, abort_flag, p.d_status, XAXB_DEVICE_TIMEOUT * 1000 + kSiteDecV);
+    if (ok && tid >= valid) {
+      // rows past the sequence end may hold anything: clear them so 0 * garbage stays 0
+#pragma unroll
+      for (int c = 0; c < D / 8; ++c)
+        *reinterpret_cast<uint4*>(sV + (c / 8) * SM::kHalfBytes + sw128_offset(tid, c % 8)) = make_uint4(0, 0, 0, 0);
+    }
     fence_proxy_async_smem();
+    ok = __syncthreads_and(ok);
+    if (!ok) break;
+
+    // ---- O^T = V^T P ---------------------------------------------------------------------
+    if (tid == 0) {
+      tc_fence_after_sync();
+      constexpr uint32_t idesc = umma_idesc(kFmtBF16, kFmtBF16, 1, 0, 128, kNPad);
+#pragma unroll
+      for (int k = 0; k < kChunk / 16; ++k) {  // 16 tokens per MMA
+        const uint64_t a_desc = umma_desc_mnmajor_sw128(smem_u32(sV) + k * 16 * 128, SM::kHalfBytes);
+        const uint64_t b_desc = umma_desc_kmajor_sw128(smem_u32(sP + (k / 4) * (kNPad * 128)) + (k % 4) * 32);
+        umma_f16(tmem_o, a_desc, b_desc, idesc, k != 0);
+      }
+      umma_commit(bar_o);
+    }
+    // The denominators are reduced while the second MMA runs.
+#pragma unroll
+    for (int g = 0; g < GT; ++g) {
+      float s = pvals[g];
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+      if (lane == 0) red_sum[warp * kNPad + g] = s;
+    }
     __syncthreads();
-  }
-
-  // ---- S^T = K Q^T -----------------------------------------------------------------------
-  if (tid == 0 && ok) {
-    tc_fence_after_sync();
-    constexpr uint32_t idesc = umma_idesc(kFmtBF16, kFmtBF16, 0, 0, 128, kNPad);
+    float wa[GT], wb[GT];  // weights of the running state and of this chunk in the merged state
 #pragma unroll
-    for (int k = 0; k < D / 16; ++k) {  // 16 bf16 = 32 bytes of K per MMA
-      const uint32_t box = k / 4, off = (k % 4) * 32;
-      const uint64_t a_desc = umma_desc_kmajor_sw128(smem_u32(sK + box * SM::kHalfBytes) + off);
-      const uint64_t b_desc = umma_desc_kmajor_sw128(smem_u32(sQ + box * (kNPad * 128)) + off);
-      umma_f16(tmem_s, a_desc, b_desc, idesc, k != 0);
+    for (int g = 0; g < GT; ++g) {
+      const float l_c = red_sum[g] + red_sum[kNPad + g] + red_sum[2 * kNPad + g] + red_sum[3 * kNPad + g];
+      const float m_new = fmaxf(m_run[g], m_c[g]);  // m_c is finite: every chunk has a valid token
+      wa[g] = __expf(m_run[g] - m_new);
+      wb[g] = __expf(m_c[g] - m_new);
+      l_run[g] = l_run[g] * wa[g] + l_c * wb[g];
+      m_run[g] = m_new;
     }
-    umma_commit(bar_s);
-  }
-  ok = ok && mbar_wait(bar_s, 0, abort_flag, p.d_status, XAXB_DEVICE_TIMEOUT * 1000 + kSiteDecS);
-  ok = __syncthreads_and(ok);
-
-  float pvals[kNPad];
-  if (ok) {
-    tc_fence_after_sync();
-    uint32_t r[16];
-    tmem_ld_x16(tmem_s + (uint32_t(warp * 32) << 16), r);
-    tmem_ld_wait();
-    const bool tok_ok = tid < valid;
-    float mx[kNPad];
+    ok = mbar_wait(bar_o, ph, abort_flag, p.d_status, XAXB_DEVICE_TIMEOUT * 1000 + kSiteDecO);
+    if (tid == 0 && ok && next < n_chunks) {  // the V tile has been consumed: fetch the next one
+      mbar_arrive_expect_tx(bar_v, SM::kTileBytes);
 #pragma unroll
-    for (int g = 0; g < kNPad; ++g) {
-      pvals[g] = tok_ok ? __uint_as_float(r[g]) * p.sm_scale : -INFINITY;
-      mx[g] = pvals[g];
+      for (int x = 0; x < kBoxes; ++x)
+        tma_load_4d(sV + x * SM::kHalfBytes, &tmap_v, bar_v, x * 64, hk, next * kChunk, b);
     }
+    if (ok) {
+      tc_fence_after_sync();
+      // accumulator row d (a head dimension) sits in TMEM lane d
+      uint32_t r[16];
+      tmem_ld_x16(tmem_o + (uint32_t(warp * 32) << 16), r);
+      tmem_ld_wait();
+      tc_fence_before_sync();
 #pragma unroll
-    for (int g = 0; g < kNPad; ++g)
-      for (int o = 16; o > 0; o >>= 1) mx[g] = fmaxf(mx[g], __shfl_xor_sync(0xffffffffu, mx[g], o));
-    if (lane == 0) {
-#pragma unroll
-      for (int g = 0; g < kNPad; ++g) red[warp * kNPad + g] = mx[g];
+      for (int g = 0; g < GT; ++g) o_acc[g] = o_acc[g] * wa[g] + __uint_as_float(r[g]) * wb[g];
     }
+    // A thread whose wait gave up leaves with everyone else at the next barrier it shares.
   }
-  __syncthreads();
-  float sums[kNPad];
-  if (ok) {
-#pragma unroll
-    for (int g = 0; g < kNPad; ++g) {
-      const float m = fmaxf(fmaxf(red[g], red[kNPad + g]), fmaxf(red[2 * kNPad + g], red[3 * kNPad + g]));
-      const float e = (tid < valid) ? __expf(pvals[g] - m) : 0.0f;
-      pvals[g] = e;
-      sums[g] = e;
-      if (tid == g && g < p.G)
-        p.ws_ml[(((long long)b * p.Hq + hk * p.G + g) * p.max_chunks + chunk) * 2 + 0] = m;
-    }
-#pragma unroll
-    for (int g = 0; g < kNPad; ++g)
-      for (int o = 16; o > 0; o >>= 1) sums[g] += __shfl_xor_sync(0xffffffffu, sums[g], o);
-  }
-  __syncthreads();  // everyone has read the maxima from `red`
-  if (ok) {
-    if (lane == 0) {
-#pragma unroll
-      for (int g = 0; g < kNPad; ++g) red[warp * kNPad + g] = sums[g];
-    }
-    // P^T as the B operand: row g, 128 tokens (two 64-token boxes), K-major, swizzled.
-    const int box = tid / 64, within = tid % 64;
-#pragma unroll
-    for (int g = 0; g < kNPad; ++g) {
-      const uint32_t off = box * (kNPad * 128) + sw128_offset(g, within / 8) + (within % 8) * 2;
-      *reinterpret_cast<__nv_bfloat16*>(sP + off) = __float2bfloat16_rn(g < p.G ? pvals[g] : 0.0f);
-    }
-  }
-  ok = ok && mbar_wait(bar_v, 0, abort_flag, p.d_status, XAXB_DEVICE_TIMEOUT * 1000 + kSiteDecV);
-  if (ok && tid >= valid) {
-    // rows past the sequence end may hold anything: clear them so 0 * garbage stays 0
-#pragma unroll
-    for (int c = 0; c < D / 8; ++c)
-      *reinterpret_cast<uint4*>(sV + (c / 8) * SM::kHalfBytes + sw128_offset(tid, c % 8)) = make_uint4(0, 0, 0, 0);
-  }
-  fence_proxy_async_smem();
-  tc_fence_before_sync();
-  ok = __syncthreads_and(ok);
-  if (tid < p.G && ok) {
-    const float l = red[tid] + red[kNPad + tid] + red[2 * kNPad + tid] + red[3 * kNPad + tid];
-    p.ws_ml[(((long long)b * p.Hq + hk * p.G + tid) * p.max_chunks + chunk) * 2 + 1] = l;
-  }
-
-  // ---- O^T = V^T P -------------------------------------------------------------------------
-  if (tid == 0 && ok) {
-    tc_fence_after_sync();
-    constexpr uint32_t idesc = umma_idesc(kFmtBF16, kFmtBF16, 1, 0, 128, kNPad);
-#pragma unroll
-    for (int k = 0; k < kChunk / 16; ++k) {  // 16 tokens per MMA
-      const uint64_t a_desc = umma_desc_mnmajor_sw128(smem_u32(sV) + k * 16 * 128, SM::kHalfBytes);
-      const uint64_t b_desc = umma_desc_kmajor_sw128(smem_u32(sP + (k / 4) * (kNPad * 128)) + (k % 4) * 32);
-      umma_f16(tmem_o, a_desc, b_desc, idesc, k != 0);
-    }
-    umma_commit(bar_o);
-  }
-  ok = ok && mbar_wait(bar_o, 0, abort_flag, p.d_status, XAXB_DEVICE_TIMEOUT * 1000 + kSiteDecO);
   ok = __syncthreads_and(ok);
   if (ok) {
-    tc_fence_after_sync();
-    // accumulator row d (a head dimension) sits in TMEM lane d
-    uint32_t r[16];
-    tmem_ld_x16(tmem_o + (uint32_t(warp * 32) << 16), r);
-    tmem_ld_wait();
+    // One partial result per CTA, in slot `first` of the (sequence, head)'s row of the workspace.
     const int d = tid;
-    if (d < D) {
 #pragma unroll
-      for (int g = 0; g < kNPad; ++g)
-        if (g < p.G)
-          p.ws_o[(((long long)b * p.Hq + hk * p.G + g) * p.max_chunks + chunk) * D + d] = __uint_as_float(r[g]);
+    for (int g = 0; g < GT; ++g) {
+      if (g < p.G) {
+        const long long slot = ((long long)b * p.Hq + hk * p.G + g) * p.max_chunks + first;
+        if (d < D) p.ws_o[slot * D + d] = o_acc[g];
+        if (tid == g) {
+          p.ws_ml[slot * 2 + 0] = m_run[g];
+          p.ws_ml[slot * 2 + 1] = l_run[g];
+        }
+      }
     }
   }
   tc_fence_before_sync();
@@ -732,16 +783,17 @@ attn_decode_pipe_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid
   }
 }
 
-static int g_decode_variant = 0;  // 0 = automatic, 1 = one CTA per chunk, 2 = persistent pipeline
+static int g_decode_variant = 0;  // 0 / 1 = chunk-walking kernel, 2 = persistent pipeline, 10 + n = n chunks per CTA
 
-// Merge the chunks of one (sequence, query head): out = sum_c w_c O_c / sum_c w_c l_c with
-// w_c = exp(m_c - max m).  D threads.
+// Merge the partial results of one (sequence, query head): out = sum_c w_c O_c / sum_c w_c l_c
+// with w_c = exp(m_c - max m).  A sequence of n chunks has min(n, lanes) partial results, in the
+// first slots of its row of the workspace.  D threads.
 __global__ void attn_decode_merge_kernel(const float* __restrict__ ws_o, const float* __restrict__ ws_ml,
                                          const int32_t* __restrict__ positions, int Hq, int D, int max_chunks,
-                                         __nv_bfloat16* __restrict__ out) {
+                                         int lanes, __nv_bfloat16* __restrict__ out) {
   const int h = blockIdx.x, b = blockIdx.y, d = threadIdx.x;
   const int L = positions[b] + 1;
-  const int n = (L + kChunk - 1) / kChunk;
+  const int n = min((L + kChunk - 1) / kChunk, lanes);
   const long long base = ((long long)b * Hq + h) * max_chunks;
   float m = -INFINITY;
   for (int c = 0; c < n; ++c) m = fmaxf(m, ws_ml[(base + c) * 2]);
@@ -754,19 +806,19 @@ __global__ void attn_decode_merge_kernel(const float* __restrict__ ws_o, const f
   out[((long long)b * Hq + h) * D + d] = __float2bfloat16_rn(num / den);
 }
 
-// Merge + per-token cast in one pass: one CTA per sequence merges the chunks of ALL its query
+// Merge + per-token cast in one pass: one CTA per sequence merges the partial results of ALL its query
 // heads (the row [Hq * D] that the output projection consumes), keeps the merged values in
 // registers, reduces the row's amax and writes e4m3 bytes with the row's scale -- the same
 // result as the merge kernel followed by the per-token cast, without the bf16 round trip.
 // Work item = (head, 8 consecutive dims); at most 2 items per thread (Hq * D <= 4096).
 __global__ void __launch_bounds__(256) attn_decode_merge_cast_kernel(
     const float* __restrict__ ws_o, const float* __restrict__ ws_ml, const int32_t* __restrict__ positions, int Hq,
-    int D, int max_chunks, uint4* __restrict__ out, uint2* __restrict__ q, float* __restrict__ scale,
+    int D, int max_chunks, int lanes, uint4* __restrict__ out, uint2* __restrict__ q, float* __restrict__ scale,
     float* __restrict__ inv_scale) {
   __shared__ float s_max[64], s_inv_den[64];
   const int b = blockIdx.x;
   const int L = positions[b] + 1;
-  const int n = (L + kChunk - 1) / kChunk;
+  const int n = min((L + kChunk - 1) / kChunk, lanes);
   for (int h = threadIdx.x; h < Hq; h += blockDim.x) {
     const long long base = ((long long)b * Hq + h) * max_chunks;
     float m = -INFINITY;
@@ -879,6 +931,7 @@ static int decode_launch(xaxb_ctx* ctx_, void* stream, const void* q_rot_bf16, c
   p.ws_ml = p.ws_o + B * Hq * max_chunks * D;
   p.max_chunks = max_chunks;
   p.d_status = ctx->d_status;
+  int lanes = max_chunks;  // partial results per (sequence, head) row of the workspace
   const bool use_pipe = g_decode_variant == 2 && (long long)B * Hkv * max_chunks < (1ll << 31);
   if (use_pipe) {
     CUtensorMap tq;
@@ -921,36 +974,45 @@ static int decode_launch(xaxb_ctx* ctx_, void* stream, const void* q_rot_bf16, c
       attn_decode_pipe_kernel<64><<<grid_p, kPipeThreads, PipeSmem<64>::kBytes, s>>>(tq, tk, tv, p, (int)B);
     }
   } else {
-  dim3 grid((unsigned)max_chunks, (unsigned)Hkv, (unsigned)B);
-  if (D == 128) {
-    static bool set128 = false;
-    if (!set128) {
-      cudaFuncSetAttribute(attn_decode_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                           DecodeSmem<128>::kBytes);
-      set128 = true;
-    }
-    attn_decode_kernel<128><<<grid, 128, DecodeSmem<128>::kBytes, s>>>(tk, tv, p);
-  } else {
-    static bool set64 = false;
-    if (!set64) {
-      cudaFuncSetAttribute(attn_decode_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                           DecodeSmem<64>::kBytes);
-      set64 = true;
-    }
-    attn_decode_kernel<64><<<grid, 128, DecodeSmem<64>::kBytes, s>>>(tk, tv, p);
+    // Chunks are dealt to `lanes` CTAs per (sequence, kv head); each CTA walks its chunks with
+    // the next tile's loads in flight.  About four chunks per CTA amortise the set-up; fewer when
+    // that would leave SMs without work.
+    int per_cta = 4;
+    if (g_decode_variant >= 11) per_cta = g_decode_variant - 10;
+    lanes = (max_chunks + per_cta - 1) / per_cta;
+    const long long groups = (long long)B * Hkv;
+    const long long want = 2ll * 3 * ctx->num_sms;
+    if (g_decode_variant < 11 && groups * lanes < want) lanes = (int)((want + groups - 1) / groups);
+    if (lanes > max_chunks) lanes = max_chunks;
+    dim3 grid((unsigned)lanes, (unsigned)Hkv, (unsigned)B);
+    const int G = p.G;
+    const int gt = G <= 1 ? 1 : G <= 2 ? 2 : G <= 4 ? 4 : G <= 8 ? 8 : 16;
+#define XAXB_DECODE_CASE(DD, GG)                                                                    \
+  if (D == DD && gt == GG) {                                                                        \
+    static bool set = false;                                                                        \
+    if (!set) {                                                                                     \
+      cudaFuncSetAttribute(attn_decode_kernel<DD, GG>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
+                           DecodeSmem<DD>::kBytes);                                                 \
+      set = true;                                                                                   \
+    }                                                                                               \
+    attn_decode_kernel<DD, GG><<<grid, 128, DecodeSmem<DD>::kBytes, s>>>(tk, tv, p);                \
   }
+    XAXB_DECODE_CASE(128, 1) XAXB_DECODE_CASE(128, 2) XAXB_DECODE_CASE(128, 4) XAXB_DECODE_CASE(128, 8)
+    XAXB_DECODE_CASE(128, 16) XAXB_DECODE_CASE(64, 1) XAXB_DECODE_CASE(64, 2) XAXB_DECODE_CASE(64, 4)
+    XAXB_DECODE_CASE(64, 8) XAXB_DECODE_CASE(64, 16)
+#undef XAXB_DECODE_CASE
   }
   rc = check_launch("attn_decode_kernel");
   if (rc) return rc;
   if (q_e4m3) {
     attn_decode_merge_cast_kernel<<<(unsigned)B, 256, 0, s>>>(p.ws_o, p.ws_ml, positions, (int)Hq, (int)D, max_chunks,
-                                                             static_cast<uint4*>(out_bf16),
+                                                             lanes, static_cast<uint4*>(out_bf16),
                                                              static_cast<uint2*>(q_e4m3), row_scale, row_inv_scale);
     return check_launch("attn_decode_merge_cast_kernel");
   }
   dim3 mgrid((unsigned)Hq, (unsigned)B);
   attn_decode_merge_kernel<<<mgrid, (unsigned)D, 0, s>>>(p.ws_o, p.ws_ml, positions, (int)Hq, (int)D, max_chunks,
-                                                         static_cast<__nv_bfloat16*>(out_bf16));
+                                                         lanes, static_cast<__nv_bfloat16*>(out_bf16));
   return check_launch("attn_decode_merge_kernel");
 }
 
@@ -1014,7 +1076,7 @@ static void* g_decode_scratch_addr[kMaxDevices] = {nullptr};
 }  // namespace xaxb
 
 extern "C" int xaxb_attn_decode_force_variant(int variant) {
-  if (variant < 0 || variant > 2) return XAXB_BAD_ARGUMENT;
+  if (variant < 0 || (variant > 2 && variant < 11) || variant > 74) return XAXB_BAD_ARGUMENT;
   xaxb::g_decode_variant = variant;
   return XAXB_OK;
 }
