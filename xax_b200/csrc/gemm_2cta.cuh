@@ -1,5 +1,4 @@
-// Kernel 2, large-M variant (exact, but measured at about half the single-CTA kernel's rate, so
-// the dispatcher uses it only when a test forces it): 256 x 256 output tiles computed by PAIRS of CTAs (a thread-block
+// Kernel 2, large-problem variant: 256 x 256 output tiles computed by PAIRS of CTAs (a thread-block
 // cluster of two SMs issuing tcgen05.mma.cta_group::2).
 //
 // The single-CTA kernel's 128 x 256 tile pulls 48 KiB of operands out of L2 for every
@@ -139,8 +138,10 @@ gemm_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       uint32_t phase = 0;
       bool ok = true;
       for (int tile = pair; tile < num_tiles && ok; tile += num_pairs) {
-        const int m0 = (tile % p.tiles_m) * (2 * kBM) + (int)rank * kBM;
-        const int n0 = (tile / p.tiles_m) * BN + (int)rank * kBM;
+        int tm, tn;
+        tile_coords<8>(tile, p.tiles_m, p.tiles_n, tm, tn);
+        const int m0 = tm * (2 * kBM) + (int)rank * kBM;
+        const int n0 = tn * BN + (int)rank * kBM;
         int kk = (int)(((long long)tile * 5) % p.num_k_blocks);
         for (int kb = 0; kb < p.num_k_blocks; ++kb) {
           ok = mbar_wait(empty + stage, phase ^ 1, abort_flag, p.d_status, XAXB_DEVICE_TIMEOUT * 1000 + kSite2Producer);
@@ -194,8 +195,10 @@ gemm_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     int acc = 0;
     uint32_t acc_phase = 0;
     for (int tile = pair; tile < num_tiles; tile += num_pairs) {
-      const int m0 = (tile % p.tiles_m) * (2 * kBM) + (int)rank * kBM;
-      const int n0 = (tile / p.tiles_m) * BN;
+      int tm, tn;
+      tile_coords<8>(tile, p.tiles_m, p.tiles_n, tm, tn);
+      const int m0 = tm * (2 * kBM) + (int)rank * kBM;
+      const int n0 = tn * BN;
       bool ok = mbar_wait(acc_full + acc, acc_phase, abort_flag, p.d_status, XAXB_DEVICE_TIMEOUT * 1000 + kSite2Epilogue);
       if (!epilogue_all(ok)) break;
       tc_fence_after_sync();

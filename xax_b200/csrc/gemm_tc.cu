@@ -39,6 +39,18 @@ struct GemmParams {
   int* d_status;
 };
 
+// Tile order: bands of kBand tile rows, column by column inside a band (row index fastest).  The
+// tiles in flight at any moment then share a few row blocks of A and a few column blocks of B
+// -- a working set that stays in L2 -- instead of sweeping all of A for every column of tiles.
+template <int kBand>
+__device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, int& tm, int& tn) {
+  const int per_band = kBand * tiles_n;
+  const int band = tile / per_band, r = tile - band * per_band;
+  const int rows = min(kBand, tiles_m - band * kBand);
+  tn = r / rows;
+  tm = band * kBand + (r - tn * rows);
+}
+
 template <int BN>
 struct GemmCfg {
   static constexpr int kStageBytes = kBM * kBKBytes + BN * kBKBytes;
@@ -148,8 +160,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       uint32_t phase = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-        const int m0 = (tile % p.tiles_m) * kBM;
-        const int n0 = (tile / p.tiles_m) * BN;
+        int tm, tn;
+        tile_coords<16>(tile, p.tiles_m, p.tiles_n, tm, tn);
+        const int m0 = tm * kBM, n0 = tn * BN;
         // Each tile walks K from its own starting block: CTAs that share an operand tile (all
         // N tiles read the same rows of A) then ask L2 for different lines at any moment.
         int kk = (int)(((long long)tile * 5) % p.num_k_blocks);
@@ -221,8 +234,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       uint32_t acc_phase = 0;
       if (t == 0) prefetch_tmap(&tmap_out);
       for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
-        const int m0 = (tile % p.tiles_m) * kBM;
-        const int n0 = (tile / p.tiles_m) * BN;
+        int tm, tn;
+        tile_coords<16>(tile, p.tiles_m, p.tiles_n, tm, tn);
+        const int m0 = tm * kBM, n0 = tn * BN;
         bool ok = mbar_wait(acc_full + acc, acc_phase, abort_flag, p.d_status, XAXB_DEVICE_TIMEOUT * 1000 + kSiteEpilogue);
         if (!epilogue_all(ok)) break;  // also: every thread is done with cmul_s / bias_s of the previous tile
         tc_fence_after_sync();
@@ -301,8 +315,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     int acc = 0;
     uint32_t acc_phase = 0;
     for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
-      const int m0 = (tile % p.tiles_m) * kBM;
-      const int n0 = (tile / p.tiles_m) * BN;
+      int tm, tn;
+      tile_coords<16>(tile, p.tiles_m, p.tiles_n, tm, tn);
+      const int m0 = tm * kBM, n0 = tn * BN;
       bool ok = mbar_wait(acc_full + acc, acc_phase, abort_flag, p.d_status, XAXB_DEVICE_TIMEOUT * 1000 + kSiteEpilogue);
       if (!epilogue_all(ok)) break;
       tc_fence_after_sync();
@@ -804,9 +819,13 @@ static int gemm_entry(xaxb_ctx* ctx_, void* stream, const void* a, int64_t lda, 
   p.d_status = ctx->d_status;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const GemmPlan plan = pick_plan(M, N, K, eb, ctx->num_sms);
-  // The CTA-pair kernel (256 x 256 tiles, a third less operand traffic per SM) is exact but
-  // measured at about half the single-CTA kernel's rate, so it runs only when a test forces it.
-  if (g_force_bn == 512 && M > kBM && N >= 256) return launch_gemm_2cta<IS_FP8>(ctx, s, a, lda * eb, b, ldb * eb, p);
+  // Large problems go to the CTA-pair kernel: 256 x 256 tiles need a third less operand traffic
+  // per SM, which is what bounds the single-CTA kernel.  It wants at least two waves of tiles.
+  const bool pair_ok = M > kBM && N >= 256;
+  const long long pair_tiles = ((long long)(M + 255) / 256) * ((N + 255) / 256);
+  if ((g_force_bn == 512 && pair_ok) ||
+      (g_force_bn == 0 && pair_ok && plan.bn == 256 && plan.split == 1 && pair_tiles >= ctx->num_sms))
+    return launch_gemm_2cta<IS_FP8>(ctx, s, a, lda * eb, b, ldb * eb, p);
   if (plan.split > 1) {
     if (M > kBM || plan.split > 8) {
       set_last_error("gemm: split-K plan (bn=%d, split=%d) is invalid for M=%lld", plan.bn, plan.split, (long long)M);
