@@ -294,6 +294,9 @@ def main() -> None:
     if tp is not None:
         tp.prepare_model(model)
         tp.shard_lm_head(model)
+        if os.environ.get("XAXB_TP_EXCHANGE", "peer") != "nccl":
+            tp.enable_peer_exchange(dev, rows=w["batch"], cols=w["hidden"])
+        base["config"]["tp_exchange"] = "peer-memory kernels" if tp.peer is not None else "nccl"
     B, T0 = w["batch"], w["prompt"]
     K = args.steps
     max_len = (T0 + warmup + K + 8 + 127) // 128 * 128

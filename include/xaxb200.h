@@ -275,6 +275,39 @@ int xaxb_attn_check(xaxb_ctx* ctx, void* stream, const void* q_rot_bf16, const v
  * xax/arch/attention.py:888), kept on the device so a captured decode step can replay. */
 int xaxb_advance_positions(xaxb_ctx* ctx, void* stream, int32_t* positions, int64_t B, int32_t delta);
 
+/* ---- tensor-parallel exchange over NVLink peer memory ------------------------------- */
+
+/*
+ * The reference leaves tensor parallelism to XLA/GSPMD: xax/arch/llm.py:931-975 only names the
+ * placement (o_proj and down are split along `in`), and the compiler inserts an all-reduce after
+ * every row-parallel matmul.  These two entry points are that all-reduce for the decode step, on
+ * buffers the caller has made visible to every GPU of the box ("symmetric" buffers: same size and
+ * layout on every rank; peer_bases[r] is THIS process's mapping of rank r's buffer, a host array
+ * of `world` device pointers, world <= 8).  The library allocates and maps nothing.
+ *
+ * Each exchange kind owns a flag region of xaxb_tp_sync_bytes() bytes inside the symmetric buffer
+ * (sync_offset_bytes; zero-filled once, before the first call, on every rank).  Every rank must
+ * issue the same sequence of calls.  One rank per GPU: these kernels wait for the matching kernel
+ * on the other GPUs (bounded: XAXB_DEVICE_TIMEOUT in the status word when a peer never shows up).
+ */
+int64_t xaxb_tp_sync_bytes(void);
+int64_t xaxb_tp_max_inbox_bytes(void);
+
+/* out[rows, cols] (bf16, local) = sum over ranks of the bf16 partial outputs that every rank has
+ * written at data_offset_bytes of its symmetric buffer; float32 accumulation in rank order, so
+ * all ranks get the same bits.  rows <= 1024, cols % 8 == 0.  The caller alternates between two
+ * data offsets from one call to the next (a buffer is free again two exchanges later). */
+int xaxb_tp_allreduce_sum_bf16(xaxb_ctx* ctx, void* stream, void* const* peer_bases, int rank, int world,
+                               int64_t data_offset_bytes, int64_t sync_offset_bytes, int64_t rows, int64_t cols,
+                               void* out_bf16);
+
+/* out[i] = max over ranks of in[i] for i < n <= 1024 (non-negative float32: the per-token amax
+ * feeding a row-parallel FP8 projection; NaN wins, as in the quantiser).  inbox_offset_bytes
+ * points at xaxb_tp_max_inbox_bytes() bytes of the symmetric buffer. */
+int xaxb_tp_allreduce_max_f32(xaxb_ctx* ctx, void* stream, void* const* peer_bases, int rank, int world,
+                              int64_t inbox_offset_bytes, int64_t sync_offset_bytes, const float* in, float* out,
+                              int64_t n);
+
 #ifdef __cplusplus
 }
 #endif

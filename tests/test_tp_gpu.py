@@ -1,4 +1,5 @@
-"""Tensor-parallel run on two GPUs (NCCL) against the unsharded model on one GPU, same seed.
+"""Tensor-parallel run on two GPUs (NCCL, then the peer-memory exchange kernels) against the unsharded model on
+one GPU, same seed.
 Skipped when fewer than two GPUs are visible."""
 
 import os
@@ -65,7 +66,36 @@ def _worker(rank: int, world: int, port: int, results):
         gathered = [torch.empty_like(first) for _ in range(world)]
         dist.all_gather(gathered, first)
         consistent = all(bool(torch.equal(g, first)) for g in gathered)
-        results[rank] = dict(err=err, same_bytes=same_bytes, agree=agree, consistent=consistent)
+        # the same decode through the library's own peer-memory exchange kernels instead of NCCL
+        tp2 = TensorParallel(rank, world)
+        tp2.enable_peer_exchange(dev, rows=B, cols=512)
+        vals = (torch.arange(B, device=dev, dtype=torch.float32) + 1) * (rank + 1)
+        vmax = tp2.all_reduce_max(vals.clone())
+        max_ok = bool(torch.equal(vmax, (torch.arange(B, device=dev, dtype=torch.float32) + 1) * world))
+        sum_ok = True
+        for it in range(5):  # alternates the two data buffers; compared with a gather + rank-ordered sum
+            part = tp2.partial_out(B, 512)
+            part.copy_(torch.randn((B, 512), generator=torch.Generator(device=dev).manual_seed(100 * it + rank),
+                                   device=dev).to(torch.bfloat16))
+            parts = [torch.empty_like(part) for _ in range(world)]
+            dist.all_gather(parts, part.clone())
+            want = torch.zeros((B, 512), dtype=torch.float32, device=dev)
+            for q in parts:
+                want += q.float()
+            got = tp2.all_reduce_sum(part)
+            sum_ok = sum_ok and bool(torch.equal(got, want.to(torch.bfloat16)))
+        if tp2.peer.exchanges & 1:  # keep the buffer alternation even before capturing a graph
+            tp2.all_reduce_sum(tp2.partial_out(B, 512).zero_())
+        st2 = DecodeState(m, B, T + 8, tp=tp2)
+        first2 = st2.prefill(toks).clone()
+        st2.capture()
+        seq2 = [first2]
+        for _ in range(3):
+            seq2.append(st2.replay().clone())
+        _lib.device_status()
+        peer_same = all(bool(torch.equal(a, b)) for a, b in zip(seq, seq2))
+        results[rank] = dict(err=err, same_bytes=same_bytes, agree=agree, consistent=consistent, max_ok=max_ok,
+                             sum_ok=sum_ok, peer_same=peer_same)
     except Exception:  # noqa: BLE001
         import traceback
 
@@ -94,3 +124,6 @@ def test_tensor_parallel_two_gpus_matches_one_gpu():
         assert res[r]["err"] < 3e-2, res[r]
         assert res[r]["same_bytes"] and res[r]["consistent"], res[r]
         assert res[r]["agree"] >= 0.5, res[r]
+        # peer-memory exchange: exact maximum, rank-ordered float32 sum, and (two ranks: one rounding of
+        # a + b either way) the same greedy tokens as the NCCL run, prefill and three replayed steps
+        assert res[r]["max_ok"] and res[r]["sum_ok"] and res[r]["peer_same"], res[r]

@@ -61,6 +61,10 @@ SIGNATURES: dict[str, tuple] = {
     "xaxb_attn_prefill": (_I, [_P, _P, _P, _P, _P, _P, _I64, _I64, _I64, _I64, _I64, _I64, _F, _P]),
     "xaxb_attn_check": (_I, [_P, _P, _P, _P, _P, _P, _I64, _I64, _I64, _I64, _I64, _I64, _F, _P]),
     "xaxb_advance_positions": (_I, [_P, _P, _P, _I64, c_int32]),
+    "xaxb_tp_sync_bytes": (_I64, []),
+    "xaxb_tp_max_inbox_bytes": (_I64, []),
+    "xaxb_tp_allreduce_sum_bf16": (_I, [_P, _P, _P, _I, _I, _I64, _I64, _I64, _I64, _P]),
+    "xaxb_tp_allreduce_max_f32": (_I, [_P, _P, _P, _I, _I, _I64, _I64, _P, _P, _I64]),
 }
 
 

@@ -362,12 +362,13 @@ class SelfAttentionBlock:
         return out, {"k": nc["k"][0], "v": nc["v"][0], "position": nc["position"].reshape(())}, None
 
     def forward_tokens(self, y: torch.Tensor, B: int, T: int, *, cache=None, donate: bool = True, y_q=None,
-                       residual=None, workspace=None, advance: bool = True, reduce_amax=None):
+                       residual=None, workspace=None, advance: bool = True, reduce_amax=None, out=None):
         """y: [B*T, H] (normalised) activations of B sequences, T new tokens each.  Returns
         (attention output [B*T, H] (+ residual), updated batched cache).  ``advance=False``
         leaves cache["position"] untouched (a caller sharing one position vector between layers
         advances it once per step).  ``reduce_amax`` (tensor-parallel runs) is applied to the
-        per-token amax of the row-parallel output projection's input."""
+        per-token amax of the row-parallel output projection's input; ``out`` is where the output
+        projection writes (a buffer the other ranks can read, in tensor-parallel runs)."""
         if not self.causal:
             raise ValueError("the attention kernels are causal")
         Hq, Hkv, D = self.num_heads, self.num_kv_heads, self.head_dim
@@ -397,7 +398,7 @@ class SelfAttentionBlock:
         if T == 1 and op_fp8 and reduce_amax is None and Hq <= 64 and Hq * D <= 4096:
             # decode: the per-token cast of the attention output happens inside the merge pass
             _, aq, _, a_inv = ops.attn_decode_cast(q_rot, cache["k"], cache["v"], pos, scale=scale, workspace=workspace)
-            out = op.forward_quantized(aq, a_inv, residual)
+            out = op.forward_quantized(aq, a_inv, residual, out)
             if advance:
                 ops.advance_positions(pos, T)
             return out, {"k": cache["k"], "v": cache["v"], "position": pos}
@@ -413,7 +414,7 @@ class SelfAttentionBlock:
                 amax = ops.group_amax(attn2, 1)
                 reduce_amax(amax)
                 aq, _, a_inv = ops.quantize_with_amax(attn2, amax, 1)
-            out = op.forward_quantized(aq, a_inv, residual)
+            out = op.forward_quantized(aq, a_inv, residual, out)
         else:
             out = apply_linear(attn2, op, residual=residual)
         if advance:

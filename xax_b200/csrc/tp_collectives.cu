@@ -1,0 +1,246 @@
+// Tensor-parallel exchange steps of the decode path over NVLink peer memory.
+//
+// Every rank owns one "symmetric" buffer (same size and layout on every rank) that all ranks of
+// the box have mapped; a kernel gets the table of those mappings.  Two exchanges are needed per
+// transformer block (xax/arch/llm.py:931-975: o_proj and down are row-parallel):
+//
+//   sum   the [tokens, hidden] bf16 partial outputs of a row-parallel projection.  The GEMM
+//         writes its partial output straight into this rank's symmetric buffer; one CTA per
+//         token row then waits until every rank's row is ready, reads the row from every rank
+//         (plain peer loads, 16 bytes per thread), adds in float32 in rank order -- so every rank
+//         computes the same bits -- and writes the bf16 row to local memory.
+//   max   the per-token amax (float32 [tokens]) of the input of a row-parallel FP8 projection,
+//         which spans all ranks.  Every rank stores its vector into every rank's inbox, raises a
+//         flag there, waits for the others' flags and takes the maximum of its inbox.
+//
+// Readiness is signalled through 32-bit epoch counters in the symmetric buffer: slot (row, src)
+// on rank dst holds the number of the last exchange whose data from `src` may be read by `dst`.
+// Epochs only grow, every rank runs the same sequence of exchanges, and the local copy of the
+// current epoch lives next to the flags, so a captured CUDA graph can be replayed.  All waits are
+// bounded (the limit of every device-side wait in this library); a wait that gives up records
+// XAXB_DEVICE_TIMEOUT with its site in the context's status word and the kernel carries on to its
+// end with whatever it has -- nothing spins for ever and nothing traps.
+//
+// Data buffers are reused by the caller in alternation (two per exchange kind): a rank can only
+// pass the flag wait of exchange k+1 after every other rank has finished reading exchange k, so
+// the buffer of exchange k is free again at exchange k+2.  The max inbox alternates by epoch
+// parity inside the kernel for the same reason.
+//
+// These kernels wait for kernels on OTHER GPUs.  They must never be launched as several ranks on
+// one GPU: nothing guarantees that two such launches run at the same time.
+#include "common.cuh"
+
+namespace xaxb {
+
+constexpr int kTpMaxWorld = 8;
+constexpr int kTpMaxSlots = 1024;
+constexpr int kSiteTpSum = 41, kSiteTpMax = 42;
+
+// Flag region of one exchange kind: flags[kTpMaxSlots][kTpMaxWorld] then epoch[kTpMaxSlots].
+constexpr int64_t kTpSyncBytes = (int64_t)(kTpMaxSlots * kTpMaxWorld + kTpMaxSlots) * 4;
+
+struct PeerTable {
+  uint8_t* base[kTpMaxWorld];
+};
+
+__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ uint4 ld_relaxed_sys_v4(const void* p) {
+  uint4 v;
+  asm volatile("ld.relaxed.sys.global.v4.u32 {%0, %1, %2, %3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p)
+               : "memory");
+  return v;
+}
+__device__ __forceinline__ float ld_relaxed_sys_f32(const float* p) {
+  float v;
+  asm volatile("ld.relaxed.sys.global.f32 %0, [%1];" : "=f"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_relaxed_sys_f32(float* p, float v) {
+  asm volatile("st.relaxed.sys.global.f32 [%0], %1;" ::"l"(p), "f"(v) : "memory");
+}
+
+// Raise this rank's flag for `slot` on every rank and wait until every rank has raised its
+// flag here.  Called by all threads of the CTA; threads 0 .. world-1 do the work.  Returns the
+// epoch of this exchange (the same in every thread).  `s_epoch` is one uint32 of shared memory.
+__device__ __forceinline__ uint32_t tp_exchange_flags(const PeerTable& peers, int64_t sync_off, int rank, int world,
+                                                      int slot, uint32_t* s_epoch, int* d_status, int site) {
+  uint32_t* my_flags = reinterpret_cast<uint32_t*>(peers.base[rank] + sync_off);
+  uint32_t* my_epoch = my_flags + kTpMaxSlots * kTpMaxWorld + slot;
+  if (threadIdx.x == 0) {
+    const uint32_t e = *my_epoch + 1;
+    *my_epoch = e;
+    *s_epoch = e;
+  }
+  __syncthreads();  // also: every thread's earlier stores precede the release stores below
+  const uint32_t epoch = *s_epoch;
+  if ((int)threadIdx.x < world) {
+    const int r = threadIdx.x;
+    uint32_t* theirs = reinterpret_cast<uint32_t*>(peers.base[r] + sync_off) + slot * kTpMaxWorld + rank;
+    __threadfence_system();
+    st_release_sys(theirs, epoch);
+    const uint32_t* mine = my_flags + slot * kTpMaxWorld + r;
+    if ((int32_t)(ld_acquire_sys(mine) - epoch) < 0) {
+      const unsigned long long t0 = globaltimer_ns();
+      while ((int32_t)(ld_acquire_sys(mine) - epoch) < 0) {
+        if (globaltimer_ns() - t0 > kWaitLimitNs) {
+          atomicCAS(d_status, 0, XAXB_DEVICE_TIMEOUT * 1000 + site);
+          break;
+        }
+      }
+    }
+  }
+  __syncthreads();
+  return epoch;
+}
+
+// One CTA per token row.  data_off: where every rank's [rows, cols] bf16 partial output starts
+// in its symmetric buffer.
+__global__ void __launch_bounds__(256) tp_allreduce_sum_kernel(const PeerTable peers, int64_t data_off,
+                                                               int64_t sync_off, int rank, int world, int cols,
+                                                               uint4* __restrict__ out, int* d_status) {
+  __shared__ uint32_t s_epoch;
+  const int row = blockIdx.x;
+  tp_exchange_flags(peers, sync_off, rank, world, row, &s_epoch, d_status, kSiteTpSum);
+  const int vec = cols / 8;
+  const int64_t row_off = data_off + (int64_t)row * cols * 2;
+  for (int c = threadIdx.x; c < vec; c += blockDim.x) {
+    float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    uint4 v[kTpMaxWorld];
+#pragma unroll
+    for (int r = 0; r < kTpMaxWorld; ++r)
+      if (r < world) v[r] = ld_relaxed_sys_v4(peers.base[r] + row_off + (int64_t)c * 16);
+#pragma unroll
+    for (int r = 0; r < kTpMaxWorld; ++r) {
+      if (r < world) {
+        const uint32_t w[4] = {v[r].x, v[r].y, v[r].z, v[r].w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          acc[2 * j] += bf16_bits_to_float(w[j] & 0xFFFFu);
+          acc[2 * j + 1] += bf16_bits_to_float(w[j] >> 16);
+        }
+      }
+    }
+    uint4 o;
+    uint32_t* ow = reinterpret_cast<uint32_t*>(&o);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const uint32_t lo = __bfloat16_as_ushort(__float2bfloat16_rn(acc[2 * j]));
+      const uint32_t hi = __bfloat16_as_ushort(__float2bfloat16_rn(acc[2 * j + 1]));
+      ow[j] = lo | (hi << 16);
+    }
+    out[(int64_t)row * vec + c] = o;
+  }
+}
+
+// One CTA; n <= 1024 values.  inbox_off: float32 [2][kTpMaxWorld][kTpMaxSlots] in the symmetric
+// buffer (two copies, used in alternation by epoch parity).
+__global__ void __launch_bounds__(1024) tp_allreduce_max_kernel(const PeerTable peers, int64_t inbox_off,
+                                                                int64_t sync_off, int rank, int world, int n,
+                                                                const float* __restrict__ in, float* __restrict__ out,
+                                                                int* d_status) {
+  __shared__ uint32_t s_epoch;
+  const int i = threadIdx.x;
+  // the epoch this exchange will get decides which inbox copy it uses
+  const uint32_t* my_epoch =
+      reinterpret_cast<const uint32_t*>(peers.base[rank] + sync_off) + kTpMaxSlots * kTpMaxWorld;
+  const uint32_t parity = (*my_epoch + 1) & 1;
+  const int64_t box = inbox_off + (int64_t)parity * kTpMaxWorld * kTpMaxSlots * 4;
+  const float mine = i < n ? in[i] : 0.0f;
+  if (i < n) {
+#pragma unroll
+    for (int r = 0; r < kTpMaxWorld; ++r)
+      if (r < world)
+        st_relaxed_sys_f32(reinterpret_cast<float*>(peers.base[r] + box) + rank * kTpMaxSlots + i, mine);
+  }
+  __syncthreads();  // every thread has read the epoch before thread 0 advances it
+  tp_exchange_flags(peers, sync_off, rank, world, 0, &s_epoch, d_status, kSiteTpMax);
+  if (i < n) {
+    // NaN propagates like the packed magnitude max of the quantiser: compare the bit patterns
+    // of the (non-negative) amax values as unsigned integers.
+    uint32_t m = 0;
+    const float* inbox = reinterpret_cast<const float*>(peers.base[rank] + box);
+#pragma unroll
+    for (int r = 0; r < kTpMaxWorld; ++r)
+      if (r < world) m = max(m, __float_as_uint(ld_relaxed_sys_f32(inbox + r * kTpMaxSlots + i)));
+    out[i] = __uint_as_float(m);
+  }
+}
+
+static int fill_peers(PeerTable& t, void* const* peer_bases, int rank, int world, const char* what) {
+  if (!peer_bases || world < 1 || world > kTpMaxWorld || rank < 0 || rank >= world) {
+    set_last_error("%s: needs 1 <= world <= %d, 0 <= rank < world and the table of peer mappings", what, kTpMaxWorld);
+    return XAXB_BAD_ARGUMENT;
+  }
+  for (int r = 0; r < kTpMaxWorld; ++r) t.base[r] = nullptr;
+  for (int r = 0; r < world; ++r) {
+    if (!peer_bases[r] || (reinterpret_cast<uintptr_t>(peer_bases[r]) & 15)) {
+      set_last_error("%s: mapping of rank %d is null or not 16-byte aligned", what, r);
+      return XAXB_BAD_ARGUMENT;
+    }
+    t.base[r] = static_cast<uint8_t*>(peer_bases[r]);
+  }
+  return XAXB_OK;
+}
+
+}  // namespace xaxb
+
+using namespace xaxb;
+
+extern "C" {
+
+int64_t xaxb_tp_sync_bytes(void) { return kTpSyncBytes; }
+
+int64_t xaxb_tp_max_inbox_bytes(void) { return 2ll * kTpMaxWorld * kTpMaxSlots * 4; }
+
+int xaxb_tp_allreduce_sum_bf16(xaxb_ctx* ctx_, void* stream, void* const* peer_bases, int rank, int world,
+                               int64_t data_offset_bytes, int64_t sync_offset_bytes, int64_t rows, int64_t cols,
+                               void* out_bf16) {
+  PeerTable t;
+  int rc = fill_peers(t, peer_bases, rank, world, "tp_allreduce_sum");
+  if (rc) return rc;
+  if (!ctx_ || !out_bf16 || rows <= 0 || cols <= 0 || (data_offset_bytes & 15) || (sync_offset_bytes & 15) ||
+      (reinterpret_cast<uintptr_t>(out_bf16) & 15)) {
+    set_last_error("tp_allreduce_sum: null pointer, non-positive shape or misaligned offset");
+    return XAXB_BAD_ARGUMENT;
+  }
+  if (rows > kTpMaxSlots || cols % 8 != 0) {
+    set_last_error("tp_allreduce_sum: at most %d rows and a multiple of 8 columns", kTpMaxSlots);
+    return XAXB_UNSUPPORTED;
+  }
+  const Ctx* ctx = reinterpret_cast<const Ctx*>(ctx_);
+  tp_allreduce_sum_kernel<<<(unsigned)rows, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      t, data_offset_bytes, sync_offset_bytes, rank, world, (int)cols, static_cast<uint4*>(out_bf16), ctx->d_status);
+  return check_launch("tp_allreduce_sum_kernel");
+}
+
+int xaxb_tp_allreduce_max_f32(xaxb_ctx* ctx_, void* stream, void* const* peer_bases, int rank, int world,
+                              int64_t inbox_offset_bytes, int64_t sync_offset_bytes, const float* in, float* out,
+                              int64_t n) {
+  PeerTable t;
+  int rc = fill_peers(t, peer_bases, rank, world, "tp_allreduce_max");
+  if (rc) return rc;
+  if (!ctx_ || !in || !out || n <= 0 || (inbox_offset_bytes & 15) || (sync_offset_bytes & 15)) {
+    set_last_error("tp_allreduce_max: null pointer, non-positive size or misaligned offset");
+    return XAXB_BAD_ARGUMENT;
+  }
+  if (n > kTpMaxSlots) {
+    set_last_error("tp_allreduce_max: at most %d values", kTpMaxSlots);
+    return XAXB_UNSUPPORTED;
+  }
+  const Ctx* ctx = reinterpret_cast<const Ctx*>(ctx_);
+  const unsigned threads = (unsigned)((n + 31) / 32 * 32) < 32u ? 32u : (unsigned)((n + 31) / 32 * 32);
+  tp_allreduce_max_kernel<<<1, threads, 0, static_cast<cudaStream_t>(stream)>>>(
+      t, inbox_offset_bytes, sync_offset_bytes, rank, world, (int)n, in, out, ctx->d_status);
+  return check_launch("tp_allreduce_max_kernel");
+}
+
+}  // extern "C"

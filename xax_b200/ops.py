@@ -226,6 +226,25 @@ def argmax_merge(part_max, part_idx, slice_cols: int, out):
     return out
 
 
+def tp_allreduce_sum(peer_ptrs, rank: int, world: int, data_offset: int, sync_offset: int, rows: int, cols: int, out):
+    """Sum of every rank's bf16 [rows, cols] partial output (at ``data_offset`` of its symmetric
+    buffer) into the local tensor ``out``.  ``peer_ptrs``: ctypes array of ``world`` mappings."""
+    ctx, st, lib = _c()
+    check(lib.xaxb_tp_allreduce_sum_bf16(ctx, st, peer_ptrs, rank, world, data_offset, sync_offset, rows, cols,
+                                         ptr(out)), "tp_allreduce_sum")
+    return out
+
+
+def tp_allreduce_max(peer_ptrs, rank: int, world: int, inbox_offset: int, sync_offset: int, values, out=None):
+    """Element-wise maximum over ranks of a float32 vector of at most 1024 values."""
+    ctx, st, lib = _c()
+    if out is None:
+        out = values
+    check(lib.xaxb_tp_allreduce_max_f32(ctx, st, peer_ptrs, rank, world, inbox_offset, sync_offset, ptr(values),
+                                        ptr(out), values.numel()), "tp_allreduce_max")
+    return out
+
+
 def group_amax(x, group_rows: int = 1, out=None):
     """max|x| per group of rows, float32 [rows / group_rows]."""
     x = _req(x, BF16, "x")

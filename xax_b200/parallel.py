@@ -12,7 +12,11 @@ collectives to XLA/GSPMD (an all-reduce after every row-parallel matmul); here t
   * greedy decoding needs no logits gather: each rank arg-maxes its vocabulary slice and the
     (value, index) pairs are all-gathered and merged.
 
-Collectives go through ``torch.distributed`` (NCCL over NVLink on GPUs, gloo in CPU tests).
+Collectives go through ``torch.distributed`` (NCCL over NVLink on GPUs, gloo in CPU tests).  On
+GPUs the two exchanges of the decode step can instead run as this library's own kernels over
+peer memory (``TensorParallel.enable_peer_exchange``): the row-parallel GEMM writes its partial
+output into a buffer that every GPU of the box has mapped, and one kernel per exchange waits on
+flags in that buffer and reads the peers' rows directly over NVLink.
 """
 
 from __future__ import annotations
@@ -49,20 +53,108 @@ def shard_weight(weight: torch.Tensor, weight_name: str, rank: int, size: int) -
     return weight.narrow(dim, rank * n, n).contiguous()
 
 
+class PeerExchange:
+    """One symmetric buffer per rank, mapped by every rank of the box, laid out as
+    [sum flags | max flags | max inbox | data 0 | data 1], and the kernels that exchange through
+    it.  The buffer and its mappings come from ``torch.distributed._symmetric_memory`` (plumbing);
+    flags, protocol and kernels are this library's (``csrc/tp_collectives.cu``)."""
+
+    MAX_ROWS = 1024
+
+    def __init__(self, rank: int, size: int, group, device, rows: int, cols: int):
+        import ctypes
+
+        import torch.distributed._symmetric_memory as symm
+
+        from . import _lib
+
+        lib = _lib.load()
+        if not 1 <= rows <= self.MAX_ROWS or cols % 8:
+            raise ValueError(f"peer exchange covers up to {self.MAX_ROWS} rows and a multiple of 8 columns")
+        self.rank, self.size, self.rows, self.cols = rank, size, rows, cols
+
+        def up(n):
+            return (n + 4095) // 4096 * 4096
+
+        sync = up(lib.xaxb_tp_sync_bytes())
+        self.sum_sync, self.max_sync = 0, sync
+        self.inbox = 2 * sync
+        self.data = [self.inbox + up(lib.xaxb_tp_max_inbox_bytes())]
+        self.data.append(self.data[0] + up(rows * cols * 2))
+        total = self.data[1] + up(rows * cols * 2)
+        self.buf = symm.empty(total, dtype=torch.uint8, device=device)
+        self.buf.zero_()
+        self.handle = symm.rendezvous(self.buf, group if group is not None else dist.group.WORLD)
+        ptrs = list(self.handle.buffer_ptrs)
+        if len(ptrs) != size or ptrs[rank] != self.buf.data_ptr():
+            raise RuntimeError("symmetric-memory rendezvous returned an unexpected mapping table")
+        self.peer_ptrs = (ctypes.c_void_p * size)(*ptrs)
+        torch.cuda.synchronize(device)
+        dist.barrier(group)  # every rank's flags are zero before anyone raises one
+        self.exchanges = 0  # sum exchanges issued (or captured) so far: picks the data buffer
+
+    def partial_out(self, rows: int, cols: int) -> torch.Tensor:
+        """Where the next row-parallel GEMM must write its partial output (bf16 [rows, cols])."""
+        if rows > self.rows or cols != self.cols:
+            raise ValueError(f"peer exchange was sized for [{self.rows}, {self.cols}], got [{rows}, {cols}]")
+        off = self.data[self.exchanges & 1]
+        return self.buf[off:off + rows * cols * 2].view(torch.bfloat16).view(rows, cols)
+
+    def all_reduce_sum(self, partial: torch.Tensor) -> torch.Tensor:
+        from . import ops
+
+        off = self.data[self.exchanges & 1]
+        if partial.data_ptr() != self.buf.data_ptr() + off:
+            raise ValueError("the partial output must be the tensor partial_out() returned for this exchange")
+        rows, cols = partial.shape
+        out = torch.empty((rows, cols), dtype=torch.bfloat16, device=partial.device)
+        ops.tp_allreduce_sum(self.peer_ptrs, self.rank, self.size, off, self.sum_sync, rows, cols, out)
+        self.exchanges += 1
+        return out
+
+    def all_reduce_max(self, values: torch.Tensor) -> torch.Tensor:
+        from . import ops
+
+        return ops.tp_allreduce_max(self.peer_ptrs, self.rank, self.size, self.inbox, self.max_sync, values)
+
+
 class TensorParallel:
     """Collectives and the tensor-parallel forward of one transformer block."""
 
     def __init__(self, rank: int, size: int, group=None):
         self.rank, self.size, self.group = rank, size, group
+        self.peer: PeerExchange | None = None
+
+    def enable_peer_exchange(self, device, rows: int, cols: int) -> None:
+        """Route the decode step's exchanges ([<= rows, cols] partial outputs, <= rows amax values)
+        through peer memory instead of NCCL.  Larger shapes (prefill) keep using NCCL.  A captured
+        CUDA graph must hold an even number of sum exchanges (two per block: it does), so that the
+        two data buffers keep alternating from one replay to the next."""
+        if self.size > 1:
+            self.peer = PeerExchange(self.rank, self.size, self.group, device, rows, cols)
+
+    def _peer_fits(self, rows: int, cols: int) -> bool:
+        return self.peer is not None and rows <= self.peer.rows and cols == self.peer.cols
 
     # -- collectives ------------------------------------------------------------------------------
+    def partial_out(self, rows: int, cols: int):
+        """Output tensor for a row-parallel GEMM whose result all_reduce_sum will take next
+        (None: let the GEMM allocate; the exchange then goes through NCCL)."""
+        return self.peer.partial_out(rows, cols) if self._peer_fits(rows, cols) else None
+
     def all_reduce_sum(self, t: torch.Tensor) -> torch.Tensor:
         if self.size > 1:
+            if self.peer is not None and t.dim() == 2 and self._peer_fits(*t.shape) and \
+                    t.data_ptr() == self.peer.partial_out(*t.shape).data_ptr():
+                return self.peer.all_reduce_sum(t)
             dist.all_reduce(t, op=dist.ReduceOp.SUM, group=self.group)
         return t
 
     def all_reduce_max(self, t: torch.Tensor) -> torch.Tensor:
         if self.size > 1:
+            if self.peer is not None and t.is_cuda and t.dtype == torch.float32 and t.dim() == 1 and \
+                    t.numel() <= PeerExchange.MAX_ROWS and t.is_contiguous():
+                return self.peer.all_reduce_max(t)
             dist.all_reduce(t, op=dist.ReduceOp.MAX, group=self.group)
         return t
 
@@ -132,7 +224,8 @@ class TensorParallel:
             raise ValueError("the tensor-parallel path covers FP8 projections (use_fp8=True)")
         _, yq = ops.rmsnorm(x, block.attn_norm.weight_bf16(), block.attn_norm.eps, want_y=False, quantize=True)
         part, new_cache = attn.forward_tokens(x, B, T, cache=cache, y_q=(yq[0], yq[2]), residual=x if first else None,
-                                              workspace=workspace, advance=advance, reduce_amax=self.all_reduce_max)
+                                              workspace=workspace, advance=advance, reduce_amax=self.all_reduce_max,
+                                              out=self.partial_out(B * T, x.shape[1]))
         x1 = self.all_reduce_sum(part)
 
         wq, col, bias = ff.fused_gate_up()
@@ -150,6 +243,6 @@ class TensorParallel:
         h, _ = ops.silu_mul(gu, F, group_amax=hmax, group_rows=T)
         self.all_reduce_max(hmax)  # the down projection's input spans all ranks
         hq, _, h_inv = ops.quantize_with_amax(h, hmax, T)
-        part = ff.down.forward_quantized(hq, h_inv, x1 if first else None)
+        part = ff.down.forward_quantized(hq, h_inv, x1 if first else None, self.partial_out(B * T, x.shape[1]))
         x2 = self.all_reduce_sum(part)
         return x2, new_cache
