@@ -301,6 +301,16 @@ int xaxb_tp_allreduce_sum_bf16(xaxb_ctx* ctx, void* stream, void* const* peer_ba
                                int64_t data_offset_bytes, int64_t sync_offset_bytes, int64_t rows, int64_t cols,
                                void* out_bf16);
 
+/* xaxb_tp_allreduce_sum_bf16 with the RMSNorm (xax/arch/attention.py:72-98) and the per-token
+ * current-scaling e4m3 cast of the next FP8 projection applied to each summed row while it is in
+ * registers: x_bf16 [rows, cols] receives the sum (the residual stream), q_e4m3 [rows, cols] and
+ * row_scale / row_inv_scale [rows] what xaxb_rmsnorm(x, weight, eps) with a fused cast would have
+ * produced from it, bit for bit.  cols <= 8192. */
+int xaxb_tp_allreduce_sum_rmsnorm(xaxb_ctx* ctx, void* stream, void* const* peer_bases, int rank, int world,
+                                  int64_t data_offset_bytes, int64_t sync_offset_bytes, int64_t rows, int64_t cols,
+                                  void* x_bf16, const void* weight_bf16, float eps, void* q_e4m3, float* row_scale,
+                                  float* row_inv_scale);
+
 /* out[i] = max over ranks of in[i] for i < n <= 1024 (non-negative float32: the per-token amax
  * feeding a row-parallel FP8 projection; NaN wins, as in the quantiser).  inbox_offset_bytes
  * points at xaxb_tp_max_inbox_bytes() bytes of the symmetric buffer. */

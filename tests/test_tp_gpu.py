@@ -84,6 +84,22 @@ def _worker(rank: int, world: int, port: int, results):
                 want += q.float()
             got = tp2.all_reduce_sum(part)
             sum_ok = sum_ok and bool(torch.equal(got, want.to(torch.bfloat16)))
+        # the exchange fused with RMSNorm + per-token cast against exchange, then rmsnorm with a fused cast
+        from xax_b200 import ops
+        norm = m.blocks[0].mlp_norm
+        fused_ok = True
+        for it in range(2):
+            src = torch.randn((B, 512), generator=torch.Generator(device=dev).manual_seed(500 + 10 * it + rank),
+                              device=dev).to(torch.bfloat16)
+            part = tp2.partial_out(B, 512)
+            part.copy_(src)
+            x_a = tp2.all_reduce_sum(part)
+            _, (q_a, _, inv_a) = ops.rmsnorm(x_a, norm.weight_bf16(), norm.eps, want_y=False, quantize=True)
+            part = tp2.partial_out(B, 512)
+            part.copy_(src)
+            x_b, q_b, inv_b = tp2.all_reduce_sum_norm(part, norm)
+            fused_ok = fused_ok and bool(torch.equal(x_a, x_b) and torch.equal(inv_a, inv_b)
+                                         and torch.equal(q_a.view(torch.uint8), q_b.view(torch.uint8)))
         if tp2.peer.exchanges & 1:  # keep the buffer alternation even before capturing a graph
             tp2.all_reduce_sum(tp2.partial_out(B, 512).zero_())
         st2 = DecodeState(m, B, T + 8, tp=tp2)
@@ -95,7 +111,7 @@ def _worker(rank: int, world: int, port: int, results):
         _lib.device_status()
         peer_same = all(bool(torch.equal(a, b)) for a, b in zip(seq, seq2))
         results[rank] = dict(err=err, same_bytes=same_bytes, agree=agree, consistent=consistent, max_ok=max_ok,
-                             sum_ok=sum_ok, peer_same=peer_same)
+                             sum_ok=sum_ok, peer_same=peer_same, fused_ok=fused_ok)
     except Exception:  # noqa: BLE001
         import traceback
 
@@ -126,4 +142,4 @@ def test_tensor_parallel_two_gpus_matches_one_gpu():
         assert res[r]["agree"] >= 0.5, res[r]
         # peer-memory exchange: exact maximum, rank-ordered float32 sum, and (two ranks: one rounding of
         # a + b either way) the same greedy tokens as the NCCL run, prefill and three replayed steps
-        assert res[r]["max_ok"] and res[r]["sum_ok"] and res[r]["peer_same"], res[r]
+        assert res[r]["max_ok"] and res[r]["sum_ok"] and res[r]["fused_ok"] and res[r]["peer_same"], res[r]

@@ -190,12 +190,15 @@ class LLM:
         if context_btn is not None:  # x = context + embedding, :274-275
             x = (context_btn.reshape(B * T, -1).to(BF16) + x).to(BF16)
         out_caches = []
+        x_q = None  # (q, inv_scale) of attn_norm(x) when the previous block's closing exchange made it
         for i, block in enumerate(self.blocks):
             c = None if caches is None else caches[i]
             if tp is None:
                 x, nc = block.forward_tokens(x, B, T, cache=c, donate=donate, workspace=workspace, advance=advance)
             else:
-                x, nc = tp.block_forward(block, x, B, T, cache=c, workspace=workspace, advance=advance)
+                nxt = self.blocks[i + 1].attn_norm if T == 1 and i + 1 < len(self.blocks) else None
+                x, nc, x_q = tp.block_forward_chain(block, x, B, T, cache=c, workspace=workspace, advance=advance,
+                                                    x_q=x_q, next_norm=nxt)
             out_caches.append(nc)
         y, _ = ops.rmsnorm(x, self.norm.weight_bf16(), self.norm.eps)
         return y.reshape(B, T, -1), (out_caches if caches is not None else None)

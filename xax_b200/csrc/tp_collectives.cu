@@ -29,6 +29,7 @@
 // These kernels wait for kernels on OTHER GPUs.  They must never be launched as several ranks on
 // one GPU: nothing guarantees that two such launches run at the same time.
 #include "common.cuh"
+#include "quant_device.cuh"
 
 namespace xaxb {
 
@@ -141,6 +142,78 @@ __global__ void __launch_bounds__(256) tp_allreduce_sum_kernel(const PeerTable p
   }
 }
 
+// The same exchange with the RMSNorm and per-token e4m3 cast that follow it in the block
+// (xax/arch/attention.py:1487-1510: x + attn(..) feeds mlp_norm, x + ffn(..) feeds the next
+// block's attn_norm) done on the summed row while it is still in registers: x (bf16) goes to
+// local memory for the residual path, the normalised row only as e4m3 bytes and its scale.
+// Arithmetic and rounding are those of rmsnorm_reg_kernel, so the bytes equal the unfused path's.
+template <int VPT>
+__global__ void __launch_bounds__(256) tp_allreduce_sum_norm_kernel(
+    const PeerTable peers, int64_t data_off, int64_t sync_off, int rank, int world, int vec, uint4* __restrict__ x_out,
+    const uint4* __restrict__ w, float eps, uint2* __restrict__ q, float* __restrict__ scale,
+    float* __restrict__ inv_scale, int* d_status) {
+  __shared__ uint32_t s_epoch;
+  const int64_t row = blockIdx.x;
+  tp_exchange_flags(peers, sync_off, rank, world, (int)row, &s_epoch, d_status, kSiteTpSum);
+  const int64_t row_off = data_off + row * vec * 16;
+  float v[VPT][8];
+  float acc = 0.0f;
+#pragma unroll
+  for (int k = 0; k < VPT; ++k) {
+    const int i = threadIdx.x + k * 256;
+    if (i < vec) {
+      uint4 part[kTpMaxWorld];
+#pragma unroll
+      for (int r = 0; r < kTpMaxWorld; ++r)
+        if (r < world) part[r] = ld_relaxed_sys_v4(peers.base[r] + row_off + (int64_t)i * 16);
+      float s[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+#pragma unroll
+      for (int r = 0; r < kTpMaxWorld; ++r) {
+        if (r < world) {
+          float f[8];
+          unpack8(part[r], f);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) s[j] += f[j];
+        }
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        v[k][j] = bf16_round(s[j]);
+        acc += bf16_round(v[k][j] * v[k][j]);
+      }
+      x_out[row * vec + i] = pack8(v[k]);
+    }
+  }
+  const float total = block_sum_f32(acc);
+  const float mean = bf16_round(total / (float)(vec * 8));
+  const float n = bf16_round(sqrtf(bf16_round(mean + bf16_round(eps))));
+  uint32_t m = 0;
+#pragma unroll
+  for (int k = 0; k < VPT; ++k) {
+    const int i = threadIdx.x + k * 256;
+    if (i < vec) {
+      float wv[8];
+      unpack8(__ldg(w + i), wv);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        v[k][j] = bf16_round(bf16_round(v[k][j] / n) * wv[j]);
+        m = max(m, mag_bits16(v[k][j]));
+      }
+    }
+  }
+  const uint32_t row_bits = block_max_u32(m);
+  const float s = current_scale_from_amax(bf16_bits_to_float(row_bits));
+#pragma unroll
+  for (int k = 0; k < VPT; ++k) {
+    const int i = threadIdx.x + k * 256;
+    if (i < vec) q[row * vec + i] = quantize8f(v[k], s);
+  }
+  if (threadIdx.x == 0) {
+    scale[row] = s;
+    inv_scale[row] = 1.0f / s;
+  }
+}
+
 // One CTA; n <= 1024 values.  inbox_off: float32 [2][kTpMaxWorld][kTpMaxSlots] in the symmetric
 // buffer (two copies, used in alternation by epoch parity).
 __global__ void __launch_bounds__(1024) tp_allreduce_max_kernel(const PeerTable peers, int64_t inbox_off,
@@ -220,6 +293,45 @@ int xaxb_tp_allreduce_sum_bf16(xaxb_ctx* ctx_, void* stream, void* const* peer_b
   tp_allreduce_sum_kernel<<<(unsigned)rows, 256, 0, static_cast<cudaStream_t>(stream)>>>(
       t, data_offset_bytes, sync_offset_bytes, rank, world, (int)cols, static_cast<uint4*>(out_bf16), ctx->d_status);
   return check_launch("tp_allreduce_sum_kernel");
+}
+
+int xaxb_tp_allreduce_sum_rmsnorm(xaxb_ctx* ctx_, void* stream, void* const* peer_bases, int rank, int world,
+                                  int64_t data_offset_bytes, int64_t sync_offset_bytes, int64_t rows, int64_t cols,
+                                  void* x_bf16, const void* weight_bf16, float eps, void* q_e4m3, float* row_scale,
+                                  float* row_inv_scale) {
+  PeerTable t;
+  int rc = fill_peers(t, peer_bases, rank, world, "tp_allreduce_sum_rmsnorm");
+  if (rc) return rc;
+  if (!ctx_ || !x_bf16 || !weight_bf16 || !q_e4m3 || !row_scale || !row_inv_scale || rows <= 0 || cols <= 0 ||
+      (data_offset_bytes & 15) || (sync_offset_bytes & 15) || (reinterpret_cast<uintptr_t>(x_bf16) & 15) ||
+      (reinterpret_cast<uintptr_t>(weight_bf16) & 15) || (reinterpret_cast<uintptr_t>(q_e4m3) & 7)) {
+    set_last_error("tp_allreduce_sum_rmsnorm: null pointer, non-positive shape or misaligned pointer / offset");
+    return XAXB_BAD_ARGUMENT;
+  }
+  if (rows > kTpMaxSlots || cols % 8 != 0 || cols > 256 * 4 * 8) {
+    set_last_error("tp_allreduce_sum_rmsnorm: at most %d rows; columns a multiple of 8, at most 8192", kTpMaxSlots);
+    return XAXB_UNSUPPORTED;
+  }
+  const Ctx* ctx = reinterpret_cast<const Ctx*>(ctx_);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const int vec = (int)(cols / 8);
+  const int vpt = (vec + 255) / 256;
+  uint4* xo = static_cast<uint4*>(x_bf16);
+  const uint4* wp = static_cast<const uint4*>(weight_bf16);
+  uint2* qp = static_cast<uint2*>(q_e4m3);
+  if (vpt == 1)
+    tp_allreduce_sum_norm_kernel<1><<<(unsigned)rows, 256, 0, s>>>(t, data_offset_bytes, sync_offset_bytes, rank, world,
+                                                                 vec, xo, wp, eps, qp, row_scale, row_inv_scale,
+                                                                 ctx->d_status);
+  else if (vpt == 2)
+    tp_allreduce_sum_norm_kernel<2><<<(unsigned)rows, 256, 0, s>>>(t, data_offset_bytes, sync_offset_bytes, rank, world,
+                                                                 vec, xo, wp, eps, qp, row_scale, row_inv_scale,
+                                                                 ctx->d_status);
+  else
+    tp_allreduce_sum_norm_kernel<4><<<(unsigned)rows, 256, 0, s>>>(t, data_offset_bytes, sync_offset_bytes, rank, world,
+                                                                 vec, xo, wp, eps, qp, row_scale, row_inv_scale,
+                                                                 ctx->d_status);
+  return check_launch("tp_allreduce_sum_norm_kernel");
 }
 
 int xaxb_tp_allreduce_max_f32(xaxb_ctx* ctx_, void* stream, void* const* peer_bases, int rank, int world,

@@ -235,6 +235,22 @@ def tp_allreduce_sum(peer_ptrs, rank: int, world: int, data_offset: int, sync_of
     return out
 
 
+def tp_allreduce_sum_rmsnorm(peer_ptrs, rank: int, world: int, data_offset: int, sync_offset: int, rows: int, cols: int,
+                             weight, eps: float):
+    """tp_allreduce_sum followed by RMSNorm and the per-token e4m3 cast, in one kernel.  Returns
+    (x bf16 [rows, cols], q e4m3 [rows, cols], scale [rows], inv_scale [rows])."""
+    ctx, st, lib = _c()
+    dev = weight.device
+    x = torch.empty((rows, cols), dtype=BF16, device=dev)
+    q = torch.empty((rows, cols), dtype=torch.float8_e4m3fn, device=dev)
+    scale = torch.empty((rows,), dtype=torch.float32, device=dev)
+    inv = torch.empty((rows,), dtype=torch.float32, device=dev)
+    check(lib.xaxb_tp_allreduce_sum_rmsnorm(ctx, st, peer_ptrs, rank, world, data_offset, sync_offset, rows, cols,
+                                            ptr(x), ptr(_req(weight, BF16, "weight")), float(eps), ptr(q), ptr(scale),
+                                            ptr(inv)), "tp_allreduce_sum_rmsnorm")
+    return x, q, scale, inv
+
+
 def tp_allreduce_max(peer_ptrs, rank: int, world: int, inbox_offset: int, sync_offset: int, values, out=None):
     """Element-wise maximum over ranks of a float32 vector of at most 1024 values."""
     ctx, st, lib = _c()

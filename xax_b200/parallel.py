@@ -112,6 +112,20 @@ class PeerExchange:
         self.exchanges += 1
         return out
 
+    def all_reduce_sum_norm(self, partial: torch.Tensor, weight_bf16: torch.Tensor, eps: float):
+        """all_reduce_sum fused with RMSNorm and the per-token e4m3 cast of the summed rows:
+        (x bf16, q e4m3, inv_scale float32 [rows])."""
+        from . import ops
+
+        off = self.data[self.exchanges & 1]
+        if partial.data_ptr() != self.buf.data_ptr() + off:
+            raise ValueError("the partial output must be the tensor partial_out() returned for this exchange")
+        rows, cols = partial.shape
+        x, q, _, inv = ops.tp_allreduce_sum_rmsnorm(self.peer_ptrs, self.rank, self.size, off, self.sum_sync, rows, cols,
+                                                    weight_bf16, eps)
+        self.exchanges += 1
+        return x, q, inv
+
     def all_reduce_max(self, values: torch.Tensor) -> torch.Tensor:
         from . import ops
 
@@ -149,6 +163,19 @@ class TensorParallel:
                 return self.peer.all_reduce_sum(t)
             dist.all_reduce(t, op=dist.ReduceOp.SUM, group=self.group)
         return t
+
+    def all_reduce_sum_norm(self, t: torch.Tensor, norm):
+        """Sum of the partial outputs, then ``norm`` (an RMSNorm) and the per-token e4m3 cast of the
+        result: (x, q, inv_scale).  One kernel on the peer-memory path."""
+        from . import ops
+
+        w = norm.weight_bf16()
+        if self.size > 1 and self.peer is not None and t.dim() == 2 and self._peer_fits(*t.shape) and \
+                t.shape[1] <= 8192 and t.data_ptr() == self.peer.partial_out(*t.shape).data_ptr():
+            return self.peer.all_reduce_sum_norm(t, w, norm.eps)
+        x = self.all_reduce_sum(t)
+        _, yq = ops.rmsnorm(x, w, norm.eps, want_y=False, quantize=True)
+        return x, yq[0], yq[2]
 
     def all_reduce_max(self, t: torch.Tensor) -> torch.Tensor:
         if self.size > 1:
@@ -216,27 +243,35 @@ class TensorParallel:
         """One pre-norm block with this rank's weight shards.  x [B*T, H] is replicated on entry
         and on exit.  The residual is added by rank 0's GEMM epilogue only, so the sum of the
         partial outputs is x + f(x)."""
+        x2, new_cache, _ = self.block_forward_chain(block, x, B, T, cache=cache, workspace=workspace, advance=advance)
+        return x2, new_cache
+
+    def block_forward_chain(self, block, x: torch.Tensor, B: int, T: int, *, cache=None, workspace=None,
+                            advance: bool = True, x_q=None, next_norm=None):
+        """block_forward for a chain of blocks in a decode step: ``x_q`` = (q, inv_scale), the
+        attn_norm + cast of x if the previous block's closing exchange already produced it;
+        ``next_norm`` = the norm that will consume this block's output (the next block's attn_norm),
+        to be fused into this block's closing exchange.  Returns (x, cache, next x_q or None)."""
         from . import ops
 
         attn, ff = block.self_attn, block.feed_forward
         first = self.rank == 0
         if not (attn._is_fp8() and ff.is_fp8()):
             raise ValueError("the tensor-parallel path covers FP8 projections (use_fp8=True)")
-        _, yq = ops.rmsnorm(x, block.attn_norm.weight_bf16(), block.attn_norm.eps, want_y=False, quantize=True)
-        part, new_cache = attn.forward_tokens(x, B, T, cache=cache, y_q=(yq[0], yq[2]), residual=x if first else None,
+        if x_q is None:
+            _, yq = ops.rmsnorm(x, block.attn_norm.weight_bf16(), block.attn_norm.eps, want_y=False, quantize=True)
+            x_q = (yq[0], yq[2])
+        part, new_cache = attn.forward_tokens(x, B, T, cache=cache, y_q=x_q, residual=x if first else None,
                                               workspace=workspace, advance=advance, reduce_amax=self.all_reduce_max,
                                               out=self.partial_out(B * T, x.shape[1]))
-        x1 = self.all_reduce_sum(part)
-
         wq, col, bias = ff.fused_gate_up()
         F = ff.gate.out_features  # local width
-        wm = block.mlp_norm.weight_bf16()
         if T == 1:
-            _, yq = ops.rmsnorm(x1, wm, block.mlp_norm.eps, want_y=False, quantize=True)
-            q, inv = yq[0], yq[2]
+            x1, q, inv = self.all_reduce_sum_norm(part, block.mlp_norm)
         else:
+            x1 = self.all_reduce_sum(part)
             amax = torch.zeros((B,), dtype=torch.float32, device=x.device)
-            y, _ = ops.rmsnorm(x1, wm, block.mlp_norm.eps, group_amax=amax, group_rows=T)
+            y, _ = ops.rmsnorm(x1, block.mlp_norm.weight_bf16(), block.mlp_norm.eps, group_amax=amax, group_rows=T)
             q, _, inv = ops.quantize_with_amax(y, amax, T)
         gu = ops.gemm_fp8(q, wq, inv, col, bias)
         hmax = torch.zeros((B,), dtype=torch.float32, device=x.device)
@@ -244,5 +279,7 @@ class TensorParallel:
         self.all_reduce_max(hmax)  # the down projection's input spans all ranks
         hq, _, h_inv = ops.quantize_with_amax(h, hmax, T)
         part = ff.down.forward_quantized(hq, h_inv, x1 if first else None, self.partial_out(B * T, x.shape[1]))
-        x2 = self.all_reduce_sum(part)
-        return x2, new_cache
+        if next_norm is not None and T == 1:
+            x2, q2, inv2 = self.all_reduce_sum_norm(part, next_norm)
+            return x2, new_cache, (q2, inv2)
+        return self.all_reduce_sum(part), new_cache, None
