@@ -311,6 +311,30 @@ int xaxb_tp_allreduce_sum_rmsnorm(xaxb_ctx* ctx, void* stream, void* const* peer
                                   void* x_bf16, const void* weight_bf16, float eps, void* q_e4m3, float* row_scale,
                                   float* row_inv_scale);
 
+/* The two places of a block where an activation amax spans the ranks, with the exchange done
+ * inside the kernel that produces the activation (each CTA owns one token row: it pushes the
+ * row's local amax to every rank, waits for theirs and casts with the maximum):
+ *
+ * xaxb_silu_mul_cast_tp: xaxb_silu_mul with the per-row e4m3 cast, the row being this rank's slice
+ *   of the SwiGLU hidden activation that feeds the row-parallel down projection
+ *   (xax/arch/attention.py:141-147 under the placement of xax/arch/llm.py:931-975).
+ * xaxb_attn_decode_cast_tp: xaxb_attn_decode_cast (e4m3 output only) for this rank's query heads,
+ *   feeding the row-parallel output projection (xax/arch/attention.py:959-961).
+ *
+ * rows / B <= 1024.  inbox_offset_bytes points at xaxb_tp_max_inbox_bytes() bytes and
+ * sync_offset_bytes at xaxb_tp_sync_bytes() bytes of the symmetric buffer, both private to the
+ * call site's exchange kind. */
+int xaxb_silu_mul_cast_tp(xaxb_ctx* ctx, void* stream, const void* gate_bf16, const void* up_bf16, int64_t ld,
+                          int64_t rows, int64_t dim, void* q_e4m3, float* scale, float* inv_scale,
+                          void* const* peer_bases, int rank, int world, int64_t inbox_offset_bytes,
+                          int64_t sync_offset_bytes);
+int xaxb_attn_decode_cast_tp(xaxb_ctx* ctx, void* stream, const void* q_rot_bf16, const void* k_cache_bf16,
+                             const void* v_cache_bf16, const int32_t* positions, int64_t B, int64_t Hq, int64_t Hkv,
+                             int64_t D, int64_t max_len, float softmax_scale, int k_is_rotated, const void* cos_bf16,
+                             const void* sin_bf16, int64_t table_len, void* q_e4m3, float* row_scale,
+                             float* row_inv_scale, void* workspace, int64_t workspace_bytes, void* const* peer_bases,
+                             int rank, int world, int64_t inbox_offset_bytes, int64_t sync_offset_bytes);
+
 /* out[i] = max over ranks of in[i] for i < n <= 1024 (non-negative float32: the per-token amax
  * feeding a row-parallel FP8 projection; NaN wins, as in the quantiser).  inbox_offset_bytes
  * points at xaxb_tp_max_inbox_bytes() bytes of the symmetric buffer. */

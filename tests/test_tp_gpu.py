@@ -100,6 +100,17 @@ def _worker(rank: int, world: int, port: int, results):
             x_b, q_b, inv_b = tp2.all_reduce_sum_norm(part, norm)
             fused_ok = fused_ok and bool(torch.equal(x_a, x_b) and torch.equal(inv_a, inv_b)
                                          and torch.equal(q_a.view(torch.uint8), q_b.view(torch.uint8)))
+        # SiLU*up with the row-amax exchange inside the kernel against kernel, NCCL max, cast
+        gu = torch.randn((B, 2 * 256), generator=torch.Generator(device=dev).manual_seed(900 + rank), device=dev
+                         ).to(torch.bfloat16)
+        hmax = torch.zeros((B,), dtype=torch.float32, device=dev)
+        h, _ = ops.silu_mul(gu, 256, group_amax=hmax, group_rows=1)
+        tp.all_reduce_max(hmax)
+        hq_a, _, hinv_a = ops.quantize_with_amax(h, hmax, 1)
+        for _ in range(3):  # repeated: the inbox copies alternate
+            hq_b, _, hinv_b = ops.silu_mul_cast_tp(gu, 256, tp2.peer.silu_site())
+            fused_ok = fused_ok and bool(torch.equal(hq_a.view(torch.uint8), hq_b.view(torch.uint8))
+                                         and torch.equal(hinv_a, hinv_b))
         if tp2.peer.exchanges & 1:  # keep the buffer alternation even before capturing a graph
             tp2.all_reduce_sum(tp2.partial_out(B, 512).zero_())
         st2 = DecodeState(m, B, T + 8, tp=tp2)

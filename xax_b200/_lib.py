@@ -65,6 +65,9 @@ SIGNATURES: dict[str, tuple] = {
     "xaxb_tp_max_inbox_bytes": (_I64, []),
     "xaxb_tp_allreduce_sum_bf16": (_I, [_P, _P, _P, _I, _I, _I64, _I64, _I64, _I64, _P]),
     "xaxb_tp_allreduce_sum_rmsnorm": (_I, [_P, _P, _P, _I, _I, _I64, _I64, _I64, _I64, _P, _P, _F, _P, _P, _P]),
+    "xaxb_silu_mul_cast_tp": (_I, [_P, _P, _P, _P, _I64, _I64, _I64, _P, _P, _P, _P, _I, _I, _I64, _I64]),
+    "xaxb_attn_decode_cast_tp": (_I, [_P, _P, _P, _P, _P, _P, _I64, _I64, _I64, _I64, _I64, _F, _I, _P, _P, _I64, _P, _P,
+                                      _P, _P, _I64, _P, _I, _I, _I64, _I64]),
     "xaxb_tp_allreduce_max_f32": (_I, [_P, _P, _P, _I, _I, _I64, _I64, _P, _P, _I64]),
 }
 

@@ -362,13 +362,16 @@ class SelfAttentionBlock:
         return out, {"k": nc["k"][0], "v": nc["v"][0], "position": nc["position"].reshape(())}, None
 
     def forward_tokens(self, y: torch.Tensor, B: int, T: int, *, cache=None, donate: bool = True, y_q=None,
-                       residual=None, workspace=None, advance: bool = True, reduce_amax=None, out=None):
+                       residual=None, workspace=None, advance: bool = True, reduce_amax=None, out=None,
+                       peer_site=None):
         """y: [B*T, H] (normalised) activations of B sequences, T new tokens each.  Returns
         (attention output [B*T, H] (+ residual), updated batched cache).  ``advance=False``
         leaves cache["position"] untouched (a caller sharing one position vector between layers
         advances it once per step).  ``reduce_amax`` (tensor-parallel runs) is applied to the
         per-token amax of the row-parallel output projection's input; ``out`` is where the output
-        projection writes (a buffer the other ranks can read, in tensor-parallel runs)."""
+        projection writes (a buffer the other ranks can read, in tensor-parallel runs);
+        ``peer_site`` routes the amax exchange of a decode step through peer memory, inside the
+        attention merge pass (ops.attn_decode_cast_tp), instead of ``reduce_amax``."""
         if not self.causal:
             raise ValueError("the attention kernels are causal")
         Hq, Hkv, D = self.num_heads, self.num_kv_heads, self.head_dim
@@ -395,6 +398,13 @@ class SelfAttentionBlock:
         scale = 1.0 / math.sqrt(D)
         op = self.output_proj
         op_fp8 = isinstance(op, Fp8Linear) and op.use_fp8
+        if T == 1 and op_fp8 and peer_site is not None and Hq <= 64 and Hq * D <= 4096:
+            aq, _, a_inv = ops.attn_decode_cast_tp(q_rot, cache["k"], cache["v"], pos, peer_site, scale=scale,
+                                                   workspace=workspace)
+            out = op.forward_quantized(aq, a_inv, residual, out)
+            if advance:
+                ops.advance_positions(pos, T)
+            return out, {"k": cache["k"], "v": cache["v"], "position": pos}
         if T == 1 and op_fp8 and reduce_amax is None and Hq <= 64 and Hq * D <= 4096:
             # decode: the per-token cast of the attention output happens inside the merge pass
             _, aq, _, a_inv = ops.attn_decode_cast(q_rot, cache["k"], cache["v"], pos, scale=scale, workspace=workspace)

@@ -28,6 +28,7 @@
 // the first MMA.
 #include "common.cuh"
 #include "quant_device.cuh"
+#include "tp_device.cuh"
 
 namespace xaxb {
 
@@ -814,8 +815,9 @@ __global__ void attn_decode_merge_kernel(const float* __restrict__ ws_o, const f
 __global__ void __launch_bounds__(256) attn_decode_merge_cast_kernel(
     const float* __restrict__ ws_o, const float* __restrict__ ws_ml, const int32_t* __restrict__ positions, int Hq,
     int D, int max_chunks, int lanes, uint4* __restrict__ out, uint2* __restrict__ q, float* __restrict__ scale,
-    float* __restrict__ inv_scale) {
+    float* __restrict__ inv_scale, const TpRowMax tp, int* d_status) {
   __shared__ float s_max[64], s_inv_den[64];
+  __shared__ uint32_t s_tp[2];
   const int b = blockIdx.x;
   const int L = positions[b] + 1;
   const int n = min((L + kChunk - 1) / kChunk, lanes);
@@ -856,7 +858,10 @@ __global__ void __launch_bounds__(256) attn_decode_merge_cast_kernel(
       if (out) out[(long long)b * items + it] = pack8(v[k]);
     }
   }
-  const uint32_t row_bits = block_max_u32(mbits);
+  uint32_t row_bits = block_max_u32(mbits);
+  // tensor-parallel runs: the other ranks hold the other heads of this token's row (the output
+  // projection's input is split along its width); the scale comes from the amax over all of them
+  if (tp.world > 1) row_bits = tp_cta_max_u32(tp, b, row_bits, s_tp, d_status, kSiteTpAttn);
   const float s = current_scale_from_amax(bf16_bits_to_float(row_bits));
 #pragma unroll
   for (int k = 0; k < 2; ++k) {
@@ -893,7 +898,8 @@ static int decode_launch(xaxb_ctx* ctx_, void* stream, const void* q_rot_bf16, c
                          const void* v_cache_bf16, const int32_t* positions, int64_t B, int64_t Hq, int64_t Hkv,
                          int64_t D, int64_t max_len, float softmax_scale, int k_is_rotated, const void* cos_bf16,
                          const void* sin_bf16, int64_t table_len, void* out_bf16, void* q_e4m3, float* row_scale,
-                         float* row_inv_scale, void* workspace, int64_t workspace_bytes) {
+                         float* row_inv_scale, void* workspace, int64_t workspace_bytes,
+                         const TpRowMax* tp = nullptr) {
   if (!ctx_ || !q_rot_bf16 || !k_cache_bf16 || !v_cache_bf16 || !positions || (!out_bf16 && !q_e4m3) || !workspace || B <= 0 ||
       Hq <= 0 || Hkv <= 0 || max_len <= 0) {
     set_last_error("attn_decode: null pointer or non-positive shape");
@@ -1007,7 +1013,8 @@ static int decode_launch(xaxb_ctx* ctx_, void* stream, const void* q_rot_bf16, c
   if (q_e4m3) {
     attn_decode_merge_cast_kernel<<<(unsigned)B, 256, 0, s>>>(p.ws_o, p.ws_ml, positions, (int)Hq, (int)D, max_chunks,
                                                              lanes, static_cast<uint4*>(out_bf16),
-                                                             static_cast<uint2*>(q_e4m3), row_scale, row_inv_scale);
+                                                             static_cast<uint2*>(q_e4m3), row_scale, row_inv_scale,
+                                                             tp ? *tp : TpRowMax{}, ctx->d_status);
     return check_launch("attn_decode_merge_cast_kernel");
   }
   dim3 mgrid((unsigned)Hq, (unsigned)B);
@@ -1074,6 +1081,27 @@ static __device__ __align__(256) unsigned char g_decode_scratch[kStaticScratchBy
 static void* g_decode_scratch_addr[kMaxDevices] = {nullptr};
 
 }  // namespace xaxb
+
+extern "C" int xaxb_attn_decode_cast_tp(xaxb_ctx* ctx_, void* stream, const void* q_rot_bf16, const void* k_cache_bf16,
+                             const void* v_cache_bf16, const int32_t* positions, int64_t B, int64_t Hq, int64_t Hkv,
+                             int64_t D, int64_t max_len, float softmax_scale, int k_is_rotated, const void* cos_bf16,
+                             const void* sin_bf16, int64_t table_len, void* q_e4m3, float* row_scale,
+                             float* row_inv_scale, void* workspace, int64_t workspace_bytes, void* const* peer_bases,
+                             int rank, int world, int64_t inbox_offset_bytes, int64_t sync_offset_bytes) {
+  if (!q_e4m3 || !row_scale || !row_inv_scale) return XAXB_BAD_ARGUMENT;
+  if (Hq > 64 || Hq * D > 4096 || B > xaxb::kTpMaxSlots || (reinterpret_cast<uintptr_t>(q_e4m3) & 7)) {
+    set_last_error("attn_decode_cast_tp: needs Hq <= 64, Hq * D <= 4096, B <= %d and an aligned output",
+                   xaxb::kTpMaxSlots);
+    return XAXB_UNSUPPORTED;
+  }
+  xaxb::TpRowMax tp;
+  int rc = xaxb::fill_tp_rowmax(tp, peer_bases, rank, world, inbox_offset_bytes, sync_offset_bytes,
+                                "attn_decode_cast_tp");
+  if (rc) return rc;
+  return decode_launch(ctx_, stream, q_rot_bf16, k_cache_bf16, v_cache_bf16, positions, B, Hq, Hkv, D, max_len,
+                       softmax_scale, k_is_rotated, cos_bf16, sin_bf16, table_len, nullptr, q_e4m3, row_scale,
+                       row_inv_scale, workspace, workspace_bytes, &tp);
+}
 
 extern "C" int xaxb_attn_decode_force_variant(int variant) {
   if (variant < 0 || (variant > 2 && variant < 11) || variant > 74) return XAXB_BAD_ARGUMENT;

@@ -4,6 +4,7 @@
 // order.
 #include "common.cuh"
 #include "quant_device.cuh"
+#include "tp_device.cuh"
 
 namespace xaxb {
 
@@ -78,7 +79,9 @@ __global__ void __launch_bounds__(256) silu_mul_kernel(const uint4* __restrict__
                                                        int64_t ld_vec, int64_t vec, uint4* __restrict__ h,
                                                        uint2* __restrict__ q, float* __restrict__ scale,
                                                        float* __restrict__ inv_scale,
-                                                       unsigned int* __restrict__ group_amax, int64_t group_rows) {
+                                                       unsigned int* __restrict__ group_amax, int64_t group_rows,
+                                                       const TpRowMax tp, int* d_status) {
+  __shared__ uint32_t s_tp[2];
   const int64_t row = blockIdx.x;
   const uint4* gr = gate + row * ld_vec;
   const uint4* ur = up + row * ld_vec;
@@ -91,7 +94,10 @@ __global__ void __launch_bounds__(256) silu_mul_kernel(const uint4* __restrict__
     for (int j = 0; j < 8; ++j) m = max(m, mag_bits16(hv[j]));
   }
   if (!q && !group_amax) return;
-  const uint32_t row_bits = block_max_u32(m);
+  uint32_t row_bits = block_max_u32(m);
+  // tensor-parallel runs: the row continues on the other ranks (the down projection's input is
+  // split along its width), so the amax that sets the scale is the maximum over ranks
+  if (tp.world > 1) row_bits = tp_cta_max_u32(tp, (int)row, row_bits, s_tp, d_status, kSiteTpSilu);
   if (group_amax && threadIdx.x == 0) atomicMax(group_amax + row / group_rows, row_bits << 16);
   if (!q) return;
   const float s = current_scale_from_amax(bf16_bits_to_float(row_bits));
@@ -572,8 +578,37 @@ int xaxb_silu_mul(xaxb_ctx* ctx, void* stream, const void* gate_bf16, const void
       return check_launch("silu_mul_cluster_kernel");
     }
   }
-  silu_mul_kernel<<<(unsigned)rows, row_threads(vec), 0, st>>>(gate, up, ld / 8, vec, hp, qp, scale, inv_scale, gp, gr);
+  silu_mul_kernel<<<(unsigned)rows, row_threads(vec), 0, st>>>(gate, up, ld / 8, vec, hp, qp, scale, inv_scale, gp, gr,
+                                                               TpRowMax{}, nullptr);
   return check_launch("silu_mul_kernel");
+}
+
+int xaxb_silu_mul_cast_tp(xaxb_ctx* ctx, void* stream, const void* gate_bf16, const void* up_bf16, int64_t ld,
+                          int64_t rows, int64_t dim, void* q_e4m3, float* scale, float* inv_scale,
+                          void* const* peer_bases, int rank, int world, int64_t inbox_offset_bytes,
+                          int64_t sync_offset_bytes) {
+  if (!ctx || !gate_bf16 || !q_e4m3 || !scale || !inv_scale || rows <= 0 || dim <= 0 || dim % 8 != 0 || ld % 8 != 0) {
+    set_last_error("silu_mul_cast_tp: null pointer, or dim/ld not positive multiples of 8");
+    return XAXB_BAD_ARGUMENT;
+  }
+  if (rows > kTpMaxSlots) {
+    set_last_error("silu_mul_cast_tp: at most %d rows", kTpMaxSlots);
+    return XAXB_UNSUPPORTED;
+  }
+  TpRowMax tp;
+  int rc = fill_tp_rowmax(tp, peer_bases, rank, world, inbox_offset_bytes, sync_offset_bytes, "silu_mul_cast_tp");
+  if (rc) return rc;
+  const uint4* gate = static_cast<const uint4*>(gate_bf16);
+  const uint4* up = up_bf16 ? static_cast<const uint4*>(up_bf16) : gate + dim / 8;
+  if ((reinterpret_cast<uintptr_t>(gate) | reinterpret_cast<uintptr_t>(up)) & 15) {
+    set_last_error("silu_mul_cast_tp: pointers must be 16-byte aligned");
+    return XAXB_BAD_ARGUMENT;
+  }
+  const int64_t vec = dim / 8;
+  silu_mul_kernel<<<(unsigned)rows, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      gate, up, ld / 8, vec, nullptr, static_cast<uint2*>(q_e4m3), scale, inv_scale, nullptr, 1, tp,
+      reinterpret_cast<Ctx*>(ctx)->d_status);
+  return check_launch("silu_mul_kernel (tensor-parallel)");
 }
 
 int xaxb_embed(xaxb_ctx* ctx, void* stream, const int32_t* tokens, int64_t n_tokens, const void* table_bf16,

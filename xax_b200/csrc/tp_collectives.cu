@@ -30,78 +30,9 @@
 // one GPU: nothing guarantees that two such launches run at the same time.
 #include "common.cuh"
 #include "quant_device.cuh"
+#include "tp_device.cuh"
 
 namespace xaxb {
-
-constexpr int kTpMaxWorld = 8;
-constexpr int kTpMaxSlots = 1024;
-constexpr int kSiteTpSum = 41, kSiteTpMax = 42;
-
-// Flag region of one exchange kind: flags[kTpMaxSlots][kTpMaxWorld] then epoch[kTpMaxSlots].
-constexpr int64_t kTpSyncBytes = (int64_t)(kTpMaxSlots * kTpMaxWorld + kTpMaxSlots) * 4;
-
-struct PeerTable {
-  uint8_t* base[kTpMaxWorld];
-};
-
-__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
-  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-}
-__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
-  uint32_t v;
-  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-  return v;
-}
-__device__ __forceinline__ uint4 ld_relaxed_sys_v4(const void* p) {
-  uint4 v;
-  asm volatile("ld.relaxed.sys.global.v4.u32 {%0, %1, %2, %3}, [%4];"
-               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
-               : "l"(p)
-               : "memory");
-  return v;
-}
-__device__ __forceinline__ float ld_relaxed_sys_f32(const float* p) {
-  float v;
-  asm volatile("ld.relaxed.sys.global.f32 %0, [%1];" : "=f"(v) : "l"(p) : "memory");
-  return v;
-}
-__device__ __forceinline__ void st_relaxed_sys_f32(float* p, float v) {
-  asm volatile("st.relaxed.sys.global.f32 [%0], %1;" ::"l"(p), "f"(v) : "memory");
-}
-
-// Raise this rank's flag for `slot` on every rank and wait until every rank has raised its
-// flag here.  Called by all threads of the CTA; threads 0 .. world-1 do the work.  Returns the
-// epoch of this exchange (the same in every thread).  `s_epoch` is one uint32 of shared memory.
-__device__ __forceinline__ uint32_t tp_exchange_flags(const PeerTable& peers, int64_t sync_off, int rank, int world,
-                                                      int slot, uint32_t* s_epoch, int* d_status, int site) {
-  uint32_t* my_flags = reinterpret_cast<uint32_t*>(peers.base[rank] + sync_off);
-  uint32_t* my_epoch = my_flags + kTpMaxSlots * kTpMaxWorld + slot;
-  if (threadIdx.x == 0) {
-    const uint32_t e = *my_epoch + 1;
-    *my_epoch = e;
-    *s_epoch = e;
-  }
-  __syncthreads();  // also: every thread's earlier stores precede the release stores below
-  const uint32_t epoch = *s_epoch;
-  if ((int)threadIdx.x < world) {
-    const int r = threadIdx.x;
-    uint32_t* theirs = reinterpret_cast<uint32_t*>(peers.base[r] + sync_off) + slot * kTpMaxWorld + rank;
-    __threadfence_system();
-    st_release_sys(theirs, epoch);
-    const uint32_t* mine = my_flags + slot * kTpMaxWorld + r;
-    if ((int32_t)(ld_acquire_sys(mine) - epoch) < 0) {
-      const unsigned long long t0 = globaltimer_ns();
-      while ((int32_t)(ld_acquire_sys(mine) - epoch) < 0) {
-        if (globaltimer_ns() - t0 > kWaitLimitNs) {
-          atomicCAS(d_status, 0, XAXB_DEVICE_TIMEOUT * 1000 + site);
-          break;
-        }
-      }
-    }
-  }
-  __syncthreads();
-  return epoch;
-}
 
 // One CTA per token row.  data_off: where every rank's [rows, cols] bf16 partial output starts
 // in its symmetric buffer.

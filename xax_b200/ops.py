@@ -367,6 +367,45 @@ def attn_decode_cast(q_rot, k_cache, v_cache, positions, *, scale=None, k_is_rot
     return out, q, rs, ri
 
 
+def attn_decode_cast_tp(q_rot, k_cache, v_cache, positions, peer, *, scale=None, workspace=None):
+    """attn_decode_cast for this rank's heads of a tensor-parallel model: the per-token scale comes
+    from the amax over ALL ranks' heads, exchanged inside the merge pass.  ``peer`` = (ctypes table of
+    peer mappings, rank, world, inbox offset, flag offset).  Returns (q e4m3 [B, Hq*D], scale, inv_scale)."""
+    B, Hq, D = q_rot.shape
+    _, max_len, Hkv, _ = k_cache.shape
+    ctx, st, lib = _c(2)
+    if workspace is None:
+        workspace = attn_decode_workspace(B, Hq, D, max_len, q_rot.device)
+    q = torch.empty((B, Hq * D), dtype=E4M3, device=q_rot.device)
+    rs = torch.empty((B,), dtype=torch.float32, device=q_rot.device)
+    ri = torch.empty((B,), dtype=torch.float32, device=q_rot.device)
+    if scale is None:
+        scale = 1.0 / math.sqrt(D)
+    ptrs, rank, world, inbox, sync = peer
+    with _Timed("attn_decode"):
+        check(lib.xaxb_attn_decode_cast_tp(ctx, st, ptr(q_rot), ptr(k_cache), ptr(v_cache), ptr(positions), B, Hq, Hkv,
+                                           D, max_len, float(scale), 1, None, None, 0, ptr(q), ptr(rs), ptr(ri),
+                                           ptr(workspace), workspace.numel() * 4, ptrs, rank, world, inbox, sync),
+              "attn_decode_cast_tp")
+    return q, rs, ri
+
+
+def silu_mul_cast_tp(gate_up, dim: int, peer):
+    """silu(gate) * up of this rank's slice of the hidden width, cast per row with the amax over all
+    ranks (exchanged inside the kernel).  gate_up: bf16 [rows, 2*dim] (gate | up).  Returns
+    (q e4m3 [rows, dim], scale, inv_scale)."""
+    gate_up = _req(gate_up, BF16, "gate_up")
+    rows, ld = gate_up.shape
+    ctx, st, lib = _c()
+    q = torch.empty((rows, dim), dtype=E4M3, device=gate_up.device)
+    rs = torch.empty((rows,), dtype=torch.float32, device=gate_up.device)
+    ri = torch.empty((rows,), dtype=torch.float32, device=gate_up.device)
+    ptrs, rank, world, inbox, sync = peer
+    check(lib.xaxb_silu_mul_cast_tp(ctx, st, ptr(gate_up), None, ld, rows, dim, ptr(q), ptr(rs), ptr(ri), ptrs, rank,
+                                    world, inbox, sync), "silu_mul_cast_tp")
+    return q, rs, ri
+
+
 def attn_decode_static(q_rot, k_cache, v_cache, positions, *, scale=None, k_is_rotated=True, cos=None, sin=None,
                        out=None):
     """Decode attention for callers that can hand over no scratch memory: identical to

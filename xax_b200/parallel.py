@@ -77,9 +77,12 @@ class PeerExchange:
             return (n + 4095) // 4096 * 4096
 
         sync = up(lib.xaxb_tp_sync_bytes())
-        self.sum_sync, self.max_sync = 0, sync
-        self.inbox = 2 * sync
-        self.data = [self.inbox + up(lib.xaxb_tp_max_inbox_bytes())]
+        box = up(lib.xaxb_tp_max_inbox_bytes())
+        # flag regions: sum, vector max, per-row max inside SiLU*up, per-row max inside attention
+        self.sum_sync, self.max_sync, self.silu_sync, self.attn_sync = 0, sync, 2 * sync, 3 * sync
+        self.inbox = 4 * sync
+        self.silu_inbox, self.attn_inbox = self.inbox + box, self.inbox + 2 * box
+        self.data = [self.inbox + 3 * box]
         self.data.append(self.data[0] + up(rows * cols * 2))
         total = self.data[1] + up(rows * cols * 2)
         self.buf = symm.empty(total, dtype=torch.uint8, device=device)
@@ -125,6 +128,13 @@ class PeerExchange:
                                                     weight_bf16, eps)
         self.exchanges += 1
         return x, q, inv
+
+    def silu_site(self):
+        """Arguments that route the SiLU*up kernel's row-amax exchange through this buffer."""
+        return (self.peer_ptrs, self.rank, self.size, self.silu_inbox, self.silu_sync)
+
+    def attn_site(self):
+        return (self.peer_ptrs, self.rank, self.size, self.attn_inbox, self.attn_sync)
 
     def all_reduce_max(self, values: torch.Tensor) -> torch.Tensor:
         from . import ops
@@ -261,9 +271,11 @@ class TensorParallel:
         if x_q is None:
             _, yq = ops.rmsnorm(x, block.attn_norm.weight_bf16(), block.attn_norm.eps, want_y=False, quantize=True)
             x_q = (yq[0], yq[2])
+        fused = T == 1 and self._peer_fits(B, x.shape[1])  # amax exchanges inside the producing kernels
         part, new_cache = attn.forward_tokens(x, B, T, cache=cache, y_q=x_q, residual=x if first else None,
                                               workspace=workspace, advance=advance, reduce_amax=self.all_reduce_max,
-                                              out=self.partial_out(B * T, x.shape[1]))
+                                              out=self.partial_out(B * T, x.shape[1]),
+                                              peer_site=self.peer.attn_site() if fused else None)
         wq, col, bias = ff.fused_gate_up()
         F = ff.gate.out_features  # local width
         if T == 1:
@@ -274,10 +286,13 @@ class TensorParallel:
             y, _ = ops.rmsnorm(x1, block.mlp_norm.weight_bf16(), block.mlp_norm.eps, group_amax=amax, group_rows=T)
             q, _, inv = ops.quantize_with_amax(y, amax, T)
         gu = ops.gemm_fp8(q, wq, inv, col, bias)
-        hmax = torch.zeros((B,), dtype=torch.float32, device=x.device)
-        h, _ = ops.silu_mul(gu, F, group_amax=hmax, group_rows=T)
-        self.all_reduce_max(hmax)  # the down projection's input spans all ranks
-        hq, _, h_inv = ops.quantize_with_amax(h, hmax, T)
+        if fused:
+            hq, _, h_inv = ops.silu_mul_cast_tp(gu, F, self.peer.silu_site())
+        else:
+            hmax = torch.zeros((B,), dtype=torch.float32, device=x.device)
+            h, _ = ops.silu_mul(gu, F, group_amax=hmax, group_rows=T)
+            self.all_reduce_max(hmax)  # the down projection's input spans all ranks
+            hq, _, h_inv = ops.quantize_with_amax(h, hmax, T)
         part = ff.down.forward_quantized(hq, h_inv, x1 if first else None, self.partial_out(B * T, x.shape[1]))
         if next_norm is not None and T == 1:
             x2, q2, inv2 = self.all_reduce_sum_norm(part, next_norm)
