@@ -73,8 +73,9 @@ int xaxb_quantize_current(xaxb_ctx* ctx, void* stream, const void* x_bf16, int64
  *     history_out = roll(history_in, -1); history_out[0] = max|x|
  *     scale_out   = 448 / max(history_out)   (previous scale kept if that max is <= 0 or
  *                                             not finite)
- * history_in/out float32[history_len] (may alias); amax_scratch: 4 bytes, cleared by the
- * call.  q_e4m3 may be NULL to update the state only (used for the weight, whose bytes
+ * history_in/out float32[history_len] (may alias); amax_scratch: 8 bytes that are zero when
+ * the call starts and zero again when it has finished (zero them once; calls that may overlap on
+ * the device need a scratch each).  One kernel launch.  q_e4m3 may be NULL to update the state only (used for the weight, whose bytes
  * are quantised once).  inv_scale_out (may be NULL) receives 1 / bf16(*scale_in), the
  * dequantisation multiplier matching the bytes written.
  */

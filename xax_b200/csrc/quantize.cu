@@ -64,12 +64,26 @@ __global__ void __launch_bounds__(256) group_cast_kernel(const uint4* __restrict
   }
 }
 
-// ---- delayed scaling: cast with the incoming scale while reducing max|x| -------------------
-// Four 16-byte loads are issued per thread before any is used, so a CTA keeps 16 KiB in flight.
+__device__ __forceinline__ float nan_max(float a, float b) { return (a != a) ? a : ((b != b) ? b : fmaxf(a, b)); }
+
+// ---- delayed scaling: cast with the incoming scale while reducing max|x|; the CTA that finishes
+// last then produces the state for the next call:
+//   history_out = roll(history_in, -1) with slot 0 <- amax; scale_out from max(history_out).
+// One launch.  Four 16-byte loads are issued per thread before any is used, so a CTA keeps 16 KiB
+// in flight.  scratch[0] collects max|x| (bf16 bits << 16), scratch[1] counts finished CTAs; both
+// are zero on entry and the last CTA leaves them zero.  The history is staged in shared memory,
+// so history_in and history_out may alias; scale_out may alias scale_in (every CTA has read it
+// before the last one can finish).
 __global__ void __launch_bounds__(256) delayed_cast_kernel(const uint4* __restrict__ x, int64_t n_vec,
-                                                           const float* __restrict__ scale_in, uint2* __restrict__ q,
-                                                           unsigned int* __restrict__ amax_bits) {
-  const float s = bf16_round(*scale_in);
+                                                           const float* scale_in, uint2* __restrict__ q,
+                                                           unsigned int* scratch, const float* history_in,
+                                                           int history_len, float* history_out, float* scale_out,
+                                                           float* inv_scale_out) {
+  extern __shared__ float hist[];
+  __shared__ float warp_max[8];
+  __shared__ int is_last;
+  const float old = *scale_in;
+  const float s = bf16_round(old);
   uint32_t m = 0;
   const int64_t stride = (int64_t)gridDim.x * blockDim.x;
   int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -89,41 +103,37 @@ __global__ void __launch_bounds__(256) delayed_cast_kernel(const uint4* __restri
     if (q) q[i] = quantize8(v, s);
   }
   const uint32_t r = block_max_u32(m);
-  if (threadIdx.x == 0) atomicMax(amax_bits, r << 16);
-}
-
-__device__ __forceinline__ float nan_max(float a, float b) { return (a != a) ? a : ((b != b) ? b : fmaxf(a, b)); }
-
-// history_out = roll(history_in, -1) with slot 0 <- amax; scale_out from max(history_out).
-// One CTA; the history is staged in shared memory so in and out may alias.
-__global__ void __launch_bounds__(256) delayed_state_kernel(const float* __restrict__ amax,
-                                                            const float* __restrict__ scale_in,
-                                                            const float* history_in, int history_len,
-                                                            float* history_out, float* __restrict__ scale_out,
-                                                            float* __restrict__ inv_scale_out) {
-  extern __shared__ float hist[];
-  __shared__ float warp_max[8];
-  for (int i = threadIdx.x; i < history_len; i += blockDim.x) {
-    const int src = (i + 1 == history_len) ? 0 : i + 1;
-    hist[i] = (i == 0) ? *amax : history_in[src];
+  if (threadIdx.x == 0) {
+    atomicMax(scratch, r << 16);
+    __threadfence();
+    is_last = atomicAdd(scratch + 1, 1u) == gridDim.x - 1;
   }
   __syncthreads();
-  float m = -INFINITY;
-  for (int i = threadIdx.x; i < history_len; i += blockDim.x) {
-    history_out[i] = hist[i];
-    m = nan_max(m, hist[i]);
+  if (!is_last) return;
+  __threadfence();
+  const float amax = __uint_as_float(atomicOr(scratch, 0u));
+  for (int j = threadIdx.x; j < history_len; j += blockDim.x) {
+    const int src = (j + 1 == history_len) ? 0 : j + 1;
+    hist[j] = (j == 0) ? amax : history_in[src];
   }
-  for (int o = 16; o > 0; o >>= 1) m = nan_max(m, __shfl_xor_sync(0xffffffffu, m, o));
-  if ((threadIdx.x & 31) == 0) warp_max[threadIdx.x >> 5] = m;
+  __syncthreads();
+  float hm = -INFINITY;
+  for (int j = threadIdx.x; j < history_len; j += blockDim.x) {
+    history_out[j] = hist[j];
+    hm = nan_max(hm, hist[j]);
+  }
+  for (int o = 16; o > 0; o >>= 1) hm = nan_max(hm, __shfl_xor_sync(0xffffffffu, hm, o));
+  if ((threadIdx.x & 31) == 0) warp_max[threadIdx.x >> 5] = hm;
   __syncthreads();
   if (threadIdx.x == 0) {
-    for (int w = 1; w < (int)(blockDim.x >> 5); ++w) m = nan_max(m, warp_max[w]);
-    const float old = *scale_in;
-    float sf = 448.0f / m;  // float32: the bf16 constant promotes against the float32 history
-    sf = (m > 0.0f) ? sf : old;
-    sf = isfinite(m) ? sf : old;
+    for (int w = 1; w < (int)(blockDim.x >> 5); ++w) hm = nan_max(hm, warp_max[w]);
+    float sf = 448.0f / hm;  // float32: the bf16 constant promotes against the float32 history
+    sf = (hm > 0.0f) ? sf : old;
+    sf = isfinite(hm) ? sf : old;
     *scale_out = sf;
-    if (inv_scale_out) *inv_scale_out = 1.0f / bf16_round(old);
+    if (inv_scale_out) *inv_scale_out = 1.0f / s;
+    scratch[0] = 0u;
+    scratch[1] = 0u;
   }
 }
 
@@ -246,15 +256,10 @@ int xaxb_quantize_delayed(xaxb_ctx* ctx, void* stream, const void* x_bf16, int64
   const Ctx* c = reinterpret_cast<const Ctx*>(ctx);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const int64_t n_vec = rows * cols / 8;
-  cudaMemsetAsync(amax_scratch, 0, sizeof(float), s);
-  delayed_cast_kernel<<<grid_for(n_vec, c->num_sms), 256, 0, s>>>(static_cast<const uint4*>(x_bf16), n_vec, scale_in,
-                                                                  static_cast<uint2*>(q_e4m3),
-                                                                  reinterpret_cast<unsigned int*>(amax_scratch));
-  rc = check_launch("delayed_cast_kernel");
-  if (rc) return rc;
-  delayed_state_kernel<<<1, 256, history_len * sizeof(float), s>>>(amax_scratch, scale_in, history_in, history_len,
-                                                                   history_out, scale_out, inv_scale_out);
-  return check_launch("delayed_state_kernel");
+  delayed_cast_kernel<<<grid_for(n_vec, c->num_sms), 256, history_len * sizeof(float), s>>>(
+      static_cast<const uint4*>(x_bf16), n_vec, scale_in, static_cast<uint2*>(q_e4m3),
+      reinterpret_cast<unsigned int*>(amax_scratch), history_in, history_len, history_out, scale_out, inv_scale_out);
+  return check_launch("delayed_cast_kernel");
 }
 
 }  // extern "C"

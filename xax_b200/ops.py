@@ -89,6 +89,9 @@ def quantize_with_amax(x: torch.Tensor, group_amax: torch.Tensor, group_rows: in
     return q, scale, inv
 
 
+_DELAYED_SCRATCH: dict = {}
+
+
 def quantize_delayed(x: torch.Tensor, scale_in: torch.Tensor, history: torch.Tensor, *, cast: bool = True):
     """Delayed scaling: returns (q or None, new_history, new_scale, inv_scale_used)."""
     x = _req(x, BF16, "x")
@@ -96,12 +99,16 @@ def quantize_delayed(x: torch.Tensor, scale_in: torch.Tensor, history: torch.Ten
     rows, cols = x2.shape
     scale_in = _req(scale_in, torch.float32, "scale_in")
     history = _req(history, torch.float32, "history")
-    ctx, st, lib = _c(2)
+    ctx, st, lib = _c(1)
     q = torch.empty((rows, cols), dtype=E4M3, device=x.device) if cast else None
     new_hist = torch.empty_like(history)
     new_scale = torch.empty((), dtype=torch.float32, device=x.device)
     inv = torch.empty((1,), dtype=torch.float32, device=x.device)
-    scratch = torch.empty((1,), dtype=torch.float32, device=x.device)
+    # the kernel needs 8 zero bytes and leaves them zero: one scratch per (device, stream), made once
+    key = (x.device.index, st)
+    scratch = _DELAYED_SCRATCH.get(key)
+    if scratch is None:
+        scratch = _DELAYED_SCRATCH[key] = torch.zeros((2,), dtype=torch.float32, device=x.device)
     check(lib.xaxb_quantize_delayed(ctx, st, ptr(x2), rows, cols, ptr(scale_in), ptr(history), history.numel(), ptr(q),
                                     ptr(new_hist), ptr(new_scale), ptr(inv), ptr(scratch)), "quantize_delayed")
     return q, new_hist, new_scale, inv
