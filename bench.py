@@ -387,9 +387,9 @@ def main() -> None:
                 "peak": peak, "peak_kind": f"of {peak_kind} copy bandwidth", "unit": "GB/s",
                 "frac": attn_bytes / avg / 1e9 / peak,
                 # DRAM bytes per launch: ncu on a smaller case of the same kernel (B=32, same context, heads)
-                # measured dram read+write = 1.084 x the algorithmic bytes; traffic is proportional to tokens x
+                # measured dram read+write = 1.088 x the algorithmic bytes; traffic is proportional to tokens x
                 # kv heads, so the factor carries over (profiles/attn_decode_kernel_small_case_ncu.md)
-                "traffic": attn_bytes * 1.084, "bytes_per_launch": attn_bytes,
+                "traffic": attn_bytes * 1.088, "bytes_per_launch": attn_bytes,
                 "avg_launch_us": avg * 1e6, "launches_timed": len(durs)}
     _lib.device_status()
 
