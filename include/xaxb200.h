@@ -343,6 +343,16 @@ int xaxb_tp_allreduce_max_f32(xaxb_ctx* ctx, void* stream, void* const* peer_bas
                               int64_t inbox_offset_bytes, int64_t sync_offset_bytes, const float* in, float* out,
                               int64_t n);
 
+/* out[i] = arg-max over the whole vocabulary from per-rank slices: part_max / part_idx [rows] are
+ * this rank's xaxb_argmax results on its `slice` columns (rank r holds columns r*slice ..), exchanged
+ * through the symmetric buffer; every rank gets the same out (xax/arch/llm.py:970-972 shards the
+ * lm_head along the vocabulary, :1466-1470 is the arg-max).  rows <= 1024; inbox_offset_bytes
+ * points at xaxb_tp_argmax_inbox_bytes() bytes. */
+int64_t xaxb_tp_argmax_inbox_bytes(void);
+int xaxb_tp_argmax(xaxb_ctx* ctx, void* stream, void* const* peer_bases, int rank, int world,
+                   int64_t inbox_offset_bytes, int64_t sync_offset_bytes, const float* part_max,
+                   const int32_t* part_idx, int64_t rows, int64_t slice, int32_t* out);
+
 #ifdef __cplusplus
 }
 #endif

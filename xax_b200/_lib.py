@@ -68,6 +68,8 @@ SIGNATURES: dict[str, tuple] = {
     "xaxb_silu_mul_cast_tp": (_I, [_P, _P, _P, _P, _I64, _I64, _I64, _P, _P, _P, _P, _I, _I, _I64, _I64]),
     "xaxb_attn_decode_cast_tp": (_I, [_P, _P, _P, _P, _P, _P, _I64, _I64, _I64, _I64, _I64, _F, _I, _P, _P, _I64, _P, _P,
                                       _P, _P, _I64, _P, _I, _I, _I64, _I64]),
+    "xaxb_tp_argmax_inbox_bytes": (_I64, []),
+    "xaxb_tp_argmax": (_I, [_P, _P, _P, _I, _I, _I64, _I64, _P, _P, _I64, _I64, _P]),
     "xaxb_tp_allreduce_max_f32": (_I, [_P, _P, _P, _I, _I, _I64, _I64, _P, _P, _I64]),
 }
 

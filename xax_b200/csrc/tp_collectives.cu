@@ -179,6 +179,54 @@ __global__ void __launch_bounds__(1024) tp_allreduce_max_kernel(const PeerTable 
   }
 }
 
+// arg-max over a vocabulary split across ranks (the column-parallel lm_head of
+// xax/arch/llm.py:970-972): every rank pushes its slice's (max, local index) per row into every
+// rank's inbox, flags, and every rank picks the winner -- jnp.argmax semantics over the whole
+// vocabulary: NaN counts as the maximum, the lower global index wins ties.  One CTA, rows <= 1024.
+// inbox: uint2 [2][kTpMaxWorld][kTpMaxSlots], alternating by epoch parity.
+__global__ void __launch_bounds__(1024) tp_argmax_kernel(const PeerTable peers, int64_t inbox_off, int64_t sync_off,
+                                                         int rank, int world, int rows, int slice,
+                                                         const float* __restrict__ part_max,
+                                                         const int32_t* __restrict__ part_idx, int32_t* __restrict__ out,
+                                                         int* d_status) {
+  __shared__ uint32_t s_epoch;
+  const int i = threadIdx.x;
+  const uint32_t* my_epoch =
+      reinterpret_cast<const uint32_t*>(peers.base[rank] + sync_off) + kTpMaxSlots * kTpMaxWorld;
+  const uint32_t parity = (*my_epoch + 1) & 1;
+  const int64_t box = inbox_off + (int64_t)parity * kTpMaxWorld * kTpMaxSlots * 8;
+  if (i < rows) {
+    const unsigned long long mine =
+        ((unsigned long long)(uint32_t)part_idx[i] << 32) | (unsigned long long)__float_as_uint(part_max[i]);
+#pragma unroll
+    for (int r = 0; r < kTpMaxWorld; ++r)
+      if (r < world) {
+        unsigned long long* dst = reinterpret_cast<unsigned long long*>(peers.base[r] + box) + rank * kTpMaxSlots + i;
+        asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(dst), "l"(mine) : "memory");
+      }
+  }
+  __syncthreads();  // every thread has read the epoch before thread 0 advances it
+  tp_exchange_flags(peers, sync_off, rank, world, 0, &s_epoch, d_status, kSiteTpMax);
+  if (i < rows) {
+    const unsigned long long* inbox = reinterpret_cast<const unsigned long long*>(peers.base[rank] + box);
+    float bv = 0.0f;
+    int bi = 0;
+#pragma unroll
+    for (int r = 0; r < kTpMaxWorld; ++r) {
+      if (r < world) {
+        unsigned long long w;
+        asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(w) : "l"(inbox + r * kTpMaxSlots + i) : "memory");
+        const float v = __uint_as_float((uint32_t)w);
+        const int gi = r * slice + (int)(uint32_t)(w >> 32);
+        const bool vn = v != v, bn = bv != bv;
+        const bool wins = r == 0 || (vn != bn ? vn : (vn ? gi < bi : (v > bv || (v == bv && gi < bi))));
+        if (wins) bv = v, bi = gi;
+      }
+    }
+    out[i] = bi;
+  }
+}
+
 static int fill_peers(PeerTable& t, void* const* peer_bases, int rank, int world, const char* what) {
   if (!peer_bases || world < 1 || world > kTpMaxWorld || rank < 0 || rank >= world) {
     set_last_error("%s: needs 1 <= world <= %d, 0 <= rank < world and the table of peer mappings", what, kTpMaxWorld);
@@ -263,6 +311,31 @@ int xaxb_tp_allreduce_sum_rmsnorm(xaxb_ctx* ctx_, void* stream, void* const* pee
                                                                  vec, xo, wp, eps, qp, row_scale, row_inv_scale,
                                                                  ctx->d_status);
   return check_launch("tp_allreduce_sum_norm_kernel");
+}
+
+int64_t xaxb_tp_argmax_inbox_bytes(void) { return 2ll * kTpMaxWorld * kTpMaxSlots * 8; }
+
+int xaxb_tp_argmax(xaxb_ctx* ctx_, void* stream, void* const* peer_bases, int rank, int world,
+                   int64_t inbox_offset_bytes, int64_t sync_offset_bytes, const float* part_max,
+                   const int32_t* part_idx, int64_t rows, int64_t slice, int32_t* out) {
+  PeerTable t;
+  int rc = fill_peers(t, peer_bases, rank, world, "tp_argmax");
+  if (rc) return rc;
+  if (!ctx_ || !part_max || !part_idx || !out || rows <= 0 || slice <= 0 || (inbox_offset_bytes & 15) ||
+      (sync_offset_bytes & 15)) {
+    set_last_error("tp_argmax: null pointer, non-positive size or misaligned offset");
+    return XAXB_BAD_ARGUMENT;
+  }
+  if (rows > kTpMaxSlots || slice * (int64_t)world > 2147483647ll) {
+    set_last_error("tp_argmax: at most %d rows and a vocabulary below 2^31", kTpMaxSlots);
+    return XAXB_UNSUPPORTED;
+  }
+  const Ctx* ctx = reinterpret_cast<const Ctx*>(ctx_);
+  const unsigned threads = (unsigned)((rows + 31) / 32 * 32);
+  tp_argmax_kernel<<<1, threads, 0, static_cast<cudaStream_t>(stream)>>>(
+      t, inbox_offset_bytes, sync_offset_bytes, rank, world, (int)rows, (int)slice, part_max, part_idx, out,
+      ctx->d_status);
+  return check_launch("tp_argmax_kernel");
 }
 
 int xaxb_tp_allreduce_max_f32(xaxb_ctx* ctx_, void* stream, void* const* peer_bases, int rank, int world,

@@ -258,6 +258,15 @@ def tp_allreduce_sum_rmsnorm(peer_ptrs, rank: int, world: int, data_offset: int,
     return x, q, scale, inv
 
 
+def tp_argmax(peer_ptrs, rank: int, world: int, inbox_offset: int, sync_offset: int, part_max, part_idx, slice_cols: int,
+              out):
+    """Global arg-max (int32 [rows] into ``out``) from every rank's (max, local index) of its vocabulary slice."""
+    ctx, st, lib = _c()
+    check(lib.xaxb_tp_argmax(ctx, st, peer_ptrs, rank, world, inbox_offset, sync_offset, ptr(part_max), ptr(part_idx),
+                             part_max.numel(), slice_cols, ptr(out)), "tp_argmax")
+    return out
+
+
 def tp_allreduce_max(peer_ptrs, rank: int, world: int, inbox_offset: int, sync_offset: int, values, out=None):
     """Element-wise maximum over ranks of a float32 vector of at most 1024 values."""
     ctx, st, lib = _c()

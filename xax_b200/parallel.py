@@ -55,7 +55,7 @@ def shard_weight(weight: torch.Tensor, weight_name: str, rank: int, size: int) -
 
 class PeerExchange:
     """One symmetric buffer per rank, mapped by every rank of the box, laid out as
-    [sum flags | max flags | max inbox | data 0 | data 1], and the kernels that exchange through
+    [flag regions | amax inboxes | arg-max inbox and flags | data 0 | data 1], and the kernels that exchange through
     it.  The buffer and its mappings come from ``torch.distributed._symmetric_memory`` (plumbing);
     flags, protocol and kernels are this library's (``csrc/tp_collectives.cu``)."""
 
@@ -82,7 +82,9 @@ class PeerExchange:
         self.sum_sync, self.max_sync, self.silu_sync, self.attn_sync = 0, sync, 2 * sync, 3 * sync
         self.inbox = 4 * sync
         self.silu_inbox, self.attn_inbox = self.inbox + box, self.inbox + 2 * box
-        self.data = [self.inbox + 3 * box]
+        self.argmax_inbox = self.inbox + 3 * box
+        self.argmax_sync = self.argmax_inbox + up(lib.xaxb_tp_argmax_inbox_bytes())
+        self.data = [self.argmax_sync + sync]
         self.data.append(self.data[0] + up(rows * cols * 2))
         total = self.data[1] + up(rows * cols * 2)
         self.buf = symm.empty(total, dtype=torch.uint8, device=device)
@@ -154,8 +156,23 @@ class TensorParallel:
         through peer memory instead of NCCL.  Larger shapes (prefill) keep using NCCL.  A captured
         CUDA graph must hold an even number of sum exchanges (two per block: it does), so that the
         two data buffers keep alternating from one replay to the next."""
-        if self.size > 1:
-            self.peer = PeerExchange(self.rank, self.size, self.group, device, rows, cols)
+        if self.size <= 1:
+            return
+        # Every rank must end up on the same path: if setting up the shared buffer fails anywhere
+        # (no peer access, symmetric memory unavailable), all ranks stay on NCCL.
+        peer, err = None, None
+        try:
+            peer = PeerExchange(self.rank, self.size, self.group, device, rows, cols)
+        except Exception as e:  # noqa: BLE001
+            err = e
+        ok = torch.tensor([0 if peer is None else 1], dtype=torch.int32, device=device)
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN, group=self.group)
+        if int(ok.item()) == 1:
+            self.peer = peer
+        elif self.rank == 0:
+            import warnings
+
+            warnings.warn(f"peer-memory exchange unavailable ({err!r}); tensor-parallel exchanges stay on NCCL")
 
     def _peer_fits(self, rows: int, cols: int) -> bool:
         return self.peer is not None and rows <= self.peer.rows and cols == self.peer.cols
@@ -246,7 +263,11 @@ class TensorParallel:
         idx = torch.empty((B,), dtype=torch.int32, device=logits.device)
         val = torch.empty((B,), dtype=torch.float32, device=logits.device)
         ops.argmax(logits, out=idx, max_out=val)
-        ops.argmax_merge(self.all_gather(val), self.all_gather(idx), logits.shape[1], out)
+        if self.peer is not None and B <= PeerExchange.MAX_ROWS:
+            p = self.peer
+            ops.tp_argmax(p.peer_ptrs, p.rank, p.size, p.argmax_inbox, p.argmax_sync, val, idx, logits.shape[1], out)
+        else:
+            ops.argmax_merge(self.all_gather(val), self.all_gather(idx), logits.shape[1], out)
 
     def block_forward(self, block, x: torch.Tensor, B: int, T: int, *, cache=None, workspace=None,
                       advance: bool = True):
