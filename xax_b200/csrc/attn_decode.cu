@@ -36,6 +36,14 @@ constexpr int kChunk = 128;   // tokens per CTA
 constexpr int kNPad = 16;     // UMMA N: query heads of one group, zero padded
 constexpr int kSiteDecK = 11, kSiteDecV = 12, kSiteDecS = 13, kSiteDecO = 14;
 
+// Where the merged, cast row of a sequence goes (see merge_cast_row).
+struct MergeOut {
+  uint4* out;  // bf16 row, may be null
+  uint2* q;
+  float* scale;
+  float* inv_scale;
+};
+
 struct DecodeParams {
   const __nv_bfloat16* q;      // [B, Hq, D] rotated
   const int32_t* positions;    // [B]; attend to rows 0 .. positions[b]
@@ -50,6 +58,12 @@ struct DecodeParams {
   float* ws_ml;  // [B, Hq, max_chunks, 2]
   int max_chunks;
   int* d_status;
+  // merge + cast fused into the kernel (null tickets: a separate merge kernel follows): the CTA
+  // that finishes a sequence last -- tickets[b] counts the sequence's CTAs and wraps to zero --
+  // merges the sequence's partial results and casts its row.
+  unsigned int* tickets;  // [B], zero when the kernel starts
+  MergeOut merge;
+  TpRowMax tp;
 };
 
 template <int D>
@@ -61,6 +75,82 @@ struct DecodeSmem {
   static constexpr int kVBytes = 2 * kHalfBytes;               // D = 64: second half is a zero pad
   static constexpr int kBytes = kTileBytes + kVBytes + kQBytes + kPBytes + 1024 /*alignment*/ + 1024;
 };
+
+// Merge + per-token cast of one sequence's row [Hq * D] (what the output projection consumes):
+// the partial results of ALL its query heads are combined with log-sum-exp weights, kept in
+// registers, the row's amax is reduced and e4m3 bytes are written with the row's scale -- the
+// same result as the merge kernel followed by the per-token cast, without the bf16 round trip.
+// Work item = (head, 8 consecutive dims); Hq * D <= 4096, so at most 512 / NT items per thread.
+// Called by all NT threads of a CTA.  kFresh: the partial results were written by other CTAs of
+// the running kernel, so they are read past the (non-coherent) L1.
+template <bool kFresh>
+__device__ __forceinline__ float ws_ld(const float* p) {
+  return kFresh ? __ldcg(p) : *p;
+}
+template <bool kFresh>
+__device__ __forceinline__ float4 ws_ld4(const float* p) {
+  return kFresh ? __ldcg(reinterpret_cast<const float4*>(p)) : *reinterpret_cast<const float4*>(p);
+}
+
+template <int NT, bool kFresh>
+__device__ __forceinline__ void merge_cast_row(const float* __restrict__ ws_o, const float* __restrict__ ws_ml, int b,
+                                               int n, int Hq, int D, int max_chunks, const MergeOut mo,
+                                               const TpRowMax& tp, int* d_status, float* s_max, float* s_inv_den,
+                                               uint32_t* s_tp) {
+  constexpr int kPer = 512 / NT;
+  for (int h = threadIdx.x; h < Hq; h += NT) {
+    const long long base = ((long long)b * Hq + h) * max_chunks;
+    float m = -INFINITY;
+    for (int c = 0; c < n; ++c) m = fmaxf(m, ws_ld<kFresh>(ws_ml + (base + c) * 2));
+    float den = 0.0f;
+    for (int c = 0; c < n; ++c)
+      den = fmaf(__expf(ws_ld<kFresh>(ws_ml + (base + c) * 2) - m), ws_ld<kFresh>(ws_ml + (base + c) * 2 + 1), den);
+    s_max[h] = m;
+    s_inv_den[h] = 1.0f / den;
+  }
+  __syncthreads();
+  const int dv = D / 8;
+  const int items = Hq * dv;
+  float v[kPer][8];
+  uint32_t mbits = 0;
+#pragma unroll
+  for (int k = 0; k < kPer; ++k) {
+    const int it = threadIdx.x + k * NT;
+    if (it < items) {
+      const int h = it / dv, d0 = (it % dv) * 8;
+      const long long base = ((long long)b * Hq + h) * max_chunks;
+      float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+      for (int c = 0; c < n; ++c) {
+        const float w = __expf(ws_ld<kFresh>(ws_ml + (base + c) * 2) - s_max[h]);
+        const float4 lo = ws_ld4<kFresh>(ws_o + (base + c) * D + d0);
+        const float4 hi = ws_ld4<kFresh>(ws_o + (base + c) * D + d0 + 4);
+        acc[0] = fmaf(w, lo.x, acc[0]), acc[1] = fmaf(w, lo.y, acc[1]), acc[2] = fmaf(w, lo.z, acc[2]);
+        acc[3] = fmaf(w, lo.w, acc[3]), acc[4] = fmaf(w, hi.x, acc[4]), acc[5] = fmaf(w, hi.y, acc[5]);
+        acc[6] = fmaf(w, hi.z, acc[6]), acc[7] = fmaf(w, hi.w, acc[7]);
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        v[k][j] = bf16_round(acc[j] * s_inv_den[h]);
+        mbits = max(mbits, mag_bits16(v[k][j]));
+      }
+      if (mo.out) mo.out[(long long)b * items + it] = pack8(v[k]);
+    }
+  }
+  uint32_t row_bits = block_max_u32(mbits);
+  // tensor-parallel runs: the other ranks hold the other heads of this token's row (the output
+  // projection's input is split along its width); the scale comes from the amax over all of them
+  if (tp.world > 1) row_bits = tp_cta_max_u32(tp, b, row_bits, s_tp, d_status, kSiteTpAttn);
+  const float s = current_scale_from_amax(bf16_bits_to_float(row_bits));
+#pragma unroll
+  for (int k = 0; k < kPer; ++k) {
+    const int it = threadIdx.x + k * NT;
+    if (it < items) mo.q[(long long)b * items + it] = quantize8f(v[k], s);
+  }
+  if (threadIdx.x == 0) {
+    mo.scale[b] = s;
+    mo.inv_scale[b] = 1.0f / s;
+  }
+}
 
 __device__ __forceinline__ float warp_max_f32(float v) {
   float r;
@@ -97,6 +187,9 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(const __grid_constant_
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   float* red_max = reinterpret_cast<float*>(tmem_slot + 2);  // [4 warps][16]
   float* red_sum = red_max + 4 * kNPad;                       // [4 warps][16]
+  __shared__ float s_mmax[64], s_minv[64];
+  __shared__ uint32_t s_tp[2];
+  __shared__ int s_last;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
 
@@ -345,6 +438,22 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(const __grid_constant_
   if (warp == 1) {
     tc_fence_after_sync();
     tmem_dealloc(tmem_base, 32);
+  }
+  if (p.tickets) {
+    // Every thread's partial-result stores are made visible device-wide, then the CTA takes a
+    // ticket; the CTA that draws the sequence's last ticket sees all the others' results.
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) {
+      const unsigned int total = (unsigned int)(p.Hkv * min(stride, n_chunks));
+      s_last = atomicInc(p.tickets + b, total - 1) == total - 1;
+    }
+    __syncthreads();
+    if (s_last) {
+      __threadfence();
+      merge_cast_row<128, true>(p.ws_o, p.ws_ml, b, min(stride, n_chunks), p.Hq, D, p.max_chunks, p.merge, p.tp,
+                                p.d_status, s_mmax, s_minv, s_tp);
+    }
   }
 }
 
@@ -807,71 +916,17 @@ __global__ void attn_decode_merge_kernel(const float* __restrict__ ws_o, const f
   out[((long long)b * Hq + h) * D + d] = __float2bfloat16_rn(num / den);
 }
 
-// Merge + per-token cast in one pass: one CTA per sequence merges the partial results of ALL its query
-// heads (the row [Hq * D] that the output projection consumes), keeps the merged values in
-// registers, reduces the row's amax and writes e4m3 bytes with the row's scale -- the same
-// result as the merge kernel followed by the per-token cast, without the bf16 round trip.
-// Work item = (head, 8 consecutive dims); at most 2 items per thread (Hq * D <= 4096).
+// Merge + per-token cast as a kernel of its own (one CTA per sequence), for the kernels that do
+// not merge themselves.
 __global__ void __launch_bounds__(256) attn_decode_merge_cast_kernel(
     const float* __restrict__ ws_o, const float* __restrict__ ws_ml, const int32_t* __restrict__ positions, int Hq,
-    int D, int max_chunks, int lanes, uint4* __restrict__ out, uint2* __restrict__ q, float* __restrict__ scale,
-    float* __restrict__ inv_scale, const TpRowMax tp, int* d_status) {
+    int D, int max_chunks, int lanes, const MergeOut mo, const TpRowMax tp, int* d_status) {
   __shared__ float s_max[64], s_inv_den[64];
   __shared__ uint32_t s_tp[2];
   const int b = blockIdx.x;
   const int L = positions[b] + 1;
   const int n = min((L + kChunk - 1) / kChunk, lanes);
-  for (int h = threadIdx.x; h < Hq; h += blockDim.x) {
-    const long long base = ((long long)b * Hq + h) * max_chunks;
-    float m = -INFINITY;
-    for (int c = 0; c < n; ++c) m = fmaxf(m, ws_ml[(base + c) * 2]);
-    float den = 0.0f;
-    for (int c = 0; c < n; ++c) den = fmaf(__expf(ws_ml[(base + c) * 2] - m), ws_ml[(base + c) * 2 + 1], den);
-    s_max[h] = m;
-    s_inv_den[h] = 1.0f / den;
-  }
-  __syncthreads();
-  const int dv = D / 8;
-  const int items = Hq * dv;
-  float v[2][8];
-  uint32_t mbits = 0;
-#pragma unroll
-  for (int k = 0; k < 2; ++k) {
-    const int it = threadIdx.x + k * 256;
-    if (it < items) {
-      const int h = it / dv, d0 = (it % dv) * 8;
-      const long long base = ((long long)b * Hq + h) * max_chunks;
-      float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-      for (int c = 0; c < n; ++c) {
-        const float w = __expf(ws_ml[(base + c) * 2] - s_max[h]);
-        const float4 lo = *reinterpret_cast<const float4*>(ws_o + (base + c) * D + d0);
-        const float4 hi = *reinterpret_cast<const float4*>(ws_o + (base + c) * D + d0 + 4);
-        acc[0] = fmaf(w, lo.x, acc[0]), acc[1] = fmaf(w, lo.y, acc[1]), acc[2] = fmaf(w, lo.z, acc[2]);
-        acc[3] = fmaf(w, lo.w, acc[3]), acc[4] = fmaf(w, hi.x, acc[4]), acc[5] = fmaf(w, hi.y, acc[5]);
-        acc[6] = fmaf(w, hi.z, acc[6]), acc[7] = fmaf(w, hi.w, acc[7]);
-      }
-#pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        v[k][j] = bf16_round(acc[j] * s_inv_den[h]);
-        mbits = max(mbits, mag_bits16(v[k][j]));
-      }
-      if (out) out[(long long)b * items + it] = pack8(v[k]);
-    }
-  }
-  uint32_t row_bits = block_max_u32(mbits);
-  // tensor-parallel runs: the other ranks hold the other heads of this token's row (the output
-  // projection's input is split along its width); the scale comes from the amax over all of them
-  if (tp.world > 1) row_bits = tp_cta_max_u32(tp, b, row_bits, s_tp, d_status, kSiteTpAttn);
-  const float s = current_scale_from_amax(bf16_bits_to_float(row_bits));
-#pragma unroll
-  for (int k = 0; k < 2; ++k) {
-    const int it = threadIdx.x + k * 256;
-    if (it < items) q[(long long)b * items + it] = quantize8f(v[k], s);
-  }
-  if (threadIdx.x == 0) {
-    scale[b] = s;
-    inv_scale[b] = 1.0f / s;
-  }
+  merge_cast_row<256, false>(ws_o, ws_ml, b, n, Hq, D, max_chunks, mo, tp, d_status, s_max, s_inv_den, s_tp);
 }
 
 static int make_cache_tmap(const Ctx* ctx, CUtensorMap* map, const void* cache, int64_t B, int64_t max_len,
@@ -891,7 +946,8 @@ extern "C" {
 
 int64_t xaxb_attn_decode_workspace_bytes(int64_t B, int64_t Hq, int64_t D, int64_t max_len) {
   const int64_t chunks = (max_len + kChunk - 1) / kChunk;
-  return B * Hq * chunks * (D + 2) * (int64_t)sizeof(float);
+  // partial results [B, Hq, chunks, D + 2] float32, then one ticket word per sequence
+  return B * Hq * chunks * (D + 2) * (int64_t)sizeof(float) + (B + 3) / 4 * 16;
 }
 
 static int decode_launch(xaxb_ctx* ctx_, void* stream, const void* q_rot_bf16, const void* k_cache_bf16,
@@ -937,7 +993,20 @@ static int decode_launch(xaxb_ctx* ctx_, void* stream, const void* q_rot_bf16, c
   p.ws_ml = p.ws_o + B * Hq * max_chunks * D;
   p.max_chunks = max_chunks;
   p.d_status = ctx->d_status;
+  p.tickets = nullptr;
+  p.merge = MergeOut{static_cast<uint4*>(out_bf16), static_cast<uint2*>(q_e4m3), row_scale, row_inv_scale};
+  p.tp = tp ? *tp : TpRowMax{};
   int lanes = max_chunks;  // partial results per (sequence, head) row of the workspace
+  // The chunk-walking kernel merges and casts by itself when the cast is wanted; its tickets
+  // are cleared by a memset node ahead of it (no state is carried from call to call).
+  // (With a tensor-parallel exchange inside the merge, the merging CTAs wait for other GPUs while
+  // holding an SM slot: fused only while they cannot crowd out the CTAs still working.)
+  const bool fuse_merge =
+      q_e4m3 != nullptr && g_decode_variant != 2 && (!tp || tp->world <= 1 || B <= 2 * ctx->num_sms);
+  if (fuse_merge) {
+    p.tickets = reinterpret_cast<unsigned int*>(p.ws_ml + B * Hq * max_chunks * 2);
+    cudaMemsetAsync(p.tickets, 0, (size_t)B * sizeof(unsigned int), s);
+  }
   const bool use_pipe = g_decode_variant == 2 && (long long)B * Hkv * max_chunks < (1ll << 31);
   if (use_pipe) {
     CUtensorMap tq;
@@ -987,7 +1056,7 @@ static int decode_launch(xaxb_ctx* ctx_, void* stream, const void* q_rot_bf16, c
     if (g_decode_variant >= 11) per_cta = g_decode_variant - 10;
     lanes = (max_chunks + per_cta - 1) / per_cta;
     const long long groups = (long long)B * Hkv;
-    const long long want = 2ll * 3 * ctx->num_sms;
+    const long long want = 3ll * ctx->num_sms;  // one resident wave (three CTAs fit an SM)
     if (g_decode_variant < 11 && groups * lanes < want) lanes = (int)((want + groups - 1) / groups);
     if (lanes > max_chunks) lanes = max_chunks;
     dim3 grid((unsigned)lanes, (unsigned)Hkv, (unsigned)B);
@@ -1010,11 +1079,10 @@ static int decode_launch(xaxb_ctx* ctx_, void* stream, const void* q_rot_bf16, c
   }
   rc = check_launch("attn_decode_kernel");
   if (rc) return rc;
+  if (fuse_merge) return XAXB_OK;
   if (q_e4m3) {
     attn_decode_merge_cast_kernel<<<(unsigned)B, 256, 0, s>>>(p.ws_o, p.ws_ml, positions, (int)Hq, (int)D, max_chunks,
-                                                             lanes, static_cast<uint4*>(out_bf16),
-                                                             static_cast<uint2*>(q_e4m3), row_scale, row_inv_scale,
-                                                             tp ? *tp : TpRowMax{}, ctx->d_status);
+                                                             lanes, p.merge, p.tp, ctx->d_status);
     return check_launch("attn_decode_merge_cast_kernel");
   }
   dim3 mgrid((unsigned)Hq, (unsigned)B);
