@@ -48,6 +48,12 @@ int xaxb_ctx_status(xaxb_ctx* ctx, void* stream, int* site);
 int xaxb_num_sms(const xaxb_ctx* ctx);
 const char* xaxb_status_string(int status);
 const char* xaxb_last_error(void);
+/* Process-wide switch (default on; off when XAXB_PROGRAMMATIC_LAUNCH=0 is in the environment at
+ * load time) for programmatic dependent launch: every kernel of the library is launched so that it
+ * may be scheduled while its predecessor in the stream still runs, and waits on the device for that
+ * predecessor before touching memory another kernel touches.  Results do not depend on it; 0
+ * restores plain stream-ordered launches.  No counterpart in the reference. */
+int xaxb_set_programmatic_launch(int on);
 
 /* ---- kernel 1: amax / scale / e4m3 cast ------------------------------------------- */
 

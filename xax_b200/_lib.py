@@ -37,6 +37,7 @@ SIGNATURES: dict[str, tuple] = {
     "xaxb_num_sms": (_I, [_P]),
     "xaxb_status_string": (c_char_p, [_I]),
     "xaxb_last_error": (c_char_p, []),
+    "xaxb_set_programmatic_launch": (_I, [_I]),
     "xaxb_quantize_current": (_I, [_P, _P, _P, _I64, _I64, _I64, _P, _P, _P, _P]),
     "xaxb_quantize_delayed": (_I, [_P, _P, _P, _I64, _I64, _P, _P, _I, _P, _P, _P, _P, _P]),
     "xaxb_quantize_with_amax": (_I, [_P, _P, _P, _I64, _I64, _I64, _P, _P, _P, _P]),

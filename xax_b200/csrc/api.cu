@@ -1,6 +1,7 @@
 // Context, status reporting and tensor-map construction for the C ABI.
 #include <cstdarg>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 
 #include "common.cuh"
@@ -15,6 +16,15 @@ void set_last_error(const char* fmt, ...) {
   vsnprintf(g_last_error, sizeof(g_last_error), fmt, ap);
   va_end(ap);
 }
+
+// On unless the environment says XAXB_PROGRAMMATIC_LAUNCH=0 (or xaxb_set_programmatic_launch(0)).
+static bool pdl_default() {
+  const char* v = getenv("XAXB_PROGRAMMATIC_LAUNCH");
+  return !(v && v[0] == '0');
+}
+static bool g_pdl = pdl_default();
+bool pdl_enabled() { return g_pdl; }
+void set_pdl_enabled(bool on) { g_pdl = on; }
 
 int check_launch(const char* what) {
   cudaError_t e = cudaGetLastError();
@@ -177,5 +187,10 @@ const char* xaxb_status_string(int status) {
 }
 
 const char* xaxb_last_error(void) { return g_last_error; }
+
+int xaxb_set_programmatic_launch(int on) {
+  xaxb::set_pdl_enabled(on != 0);
+  return XAXB_OK;
+}
 
 }  // extern "C"

@@ -58,12 +58,6 @@ struct DecodeParams {
   float* ws_ml;  // [B, Hq, max_chunks, 2]
   int max_chunks;
   int* d_status;
-  // merge + cast fused into the kernel (null tickets: a separate merge kernel follows): the CTA
-  // that finishes a sequence last -- tickets[b] counts the sequence's CTAs and wraps to zero --
-  // merges the sequence's partial results and casts its row.
-  unsigned int* tickets;  // [B], zero when the kernel starts
-  MergeOut merge;
-  TpRowMax tp;
 };
 
 template <int D>
@@ -82,7 +76,9 @@ struct DecodeSmem {
 // same result as the merge kernel followed by the per-token cast, without the bf16 round trip.
 // Work item = (head, 8 consecutive dims); Hq * D <= 4096, so at most 512 / NT items per thread.
 // Called by all NT threads of a CTA.  kFresh: the partial results were written by other CTAs of
-// the running kernel, so they are read past the (non-coherent) L1.
+// a kernel that is still running, so they are read past the (non-coherent) L1.  (Merging inside
+// the attention kernel -- the CTA that finishes a sequence last -- was tried: the fence and the
+// ticket each CTA then needs before it can leave cost more SM residency than the merge launch.)
 template <bool kFresh>
 __device__ __forceinline__ float ws_ld(const float* p) {
   return kFresh ? __ldcg(p) : *p;
@@ -165,6 +161,7 @@ template <int D, int GT>
 __global__ void __launch_bounds__(128) attn_decode_kernel(const __grid_constant__ CUtensorMap tmap_k,
                                                           const __grid_constant__ CUtensorMap tmap_v,
                                                           const DecodeParams p) {
+  pdl_wait();  // nothing below may run ahead of the previous kernel in the stream
   using SM = DecodeSmem<D>;
   constexpr int kBoxes = D / 64;  // 128-byte-wide boxes per row
   const int first = blockIdx.x, stride = gridDim.x, hk = blockIdx.y, b = blockIdx.z;
@@ -187,9 +184,6 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(const __grid_constant_
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   float* red_max = reinterpret_cast<float*>(tmem_slot + 2);  // [4 warps][16]
   float* red_sum = red_max + 4 * kNPad;                       // [4 warps][16]
-  __shared__ float s_mmax[64], s_minv[64];
-  __shared__ uint32_t s_tp[2];
-  __shared__ int s_last;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
 
@@ -235,6 +229,7 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(const __grid_constant_
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
+  pdl_trigger();  // tensor memory is allocated: the next kernel may be scheduled
   const uint32_t tmem_s = tmem_base;        // columns [0, 16)
   const uint32_t tmem_o = tmem_base + 16;   // columns [16, 32)
 
@@ -439,22 +434,6 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(const __grid_constant_
     tc_fence_after_sync();
     tmem_dealloc(tmem_base, 32);
   }
-  if (p.tickets) {
-    // Every thread's partial-result stores are made visible device-wide, then the CTA takes a
-    // ticket; the CTA that draws the sequence's last ticket sees all the others' results.
-    __threadfence();
-    __syncthreads();
-    if (tid == 0) {
-      const unsigned int total = (unsigned int)(p.Hkv * min(stride, n_chunks));
-      s_last = atomicInc(p.tickets + b, total - 1) == total - 1;
-    }
-    __syncthreads();
-    if (s_last) {
-      __threadfence();
-      merge_cast_row<128, true>(p.ws_o, p.ws_ml, b, min(stride, n_chunks), p.Hq, D, p.max_chunks, p.merge, p.tp,
-                                p.d_status, s_mmax, s_minv, s_tp);
-    }
-  }
 }
 
 // ---------------------------------------------------------------------------------------
@@ -515,6 +494,7 @@ template <int D>
 __global__ void __launch_bounds__(kPipeThreads, 1)
 attn_decode_pipe_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                         const __grid_constant__ CUtensorMap tmap_v, const DecodeParams p, const int B) {
+  pdl_wait();  // nothing below may run ahead of the previous kernel in the stream
   using SM = PipeSmem<D>;
   constexpr int kStages = SM::kStages;
   constexpr int kBoxes = D / 64;
@@ -579,6 +559,7 @@ attn_decode_pipe_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
+  pdl_trigger();  // tensor memory is allocated: the next kernel may be scheduled
 
   // work item w -> (b, hk, chunk), chunk fastest; an item is valid if its chunk starts inside the sequence
   auto decode = [&](int w, int& b, int& hk, int& chunk) -> bool {
@@ -901,6 +882,8 @@ static int g_decode_variant = 0;  // 0 / 1 = chunk-walking kernel, 2 = persisten
 __global__ void attn_decode_merge_kernel(const float* __restrict__ ws_o, const float* __restrict__ ws_ml,
                                          const int32_t* __restrict__ positions, int Hq, int D, int max_chunks,
                                          int lanes, __nv_bfloat16* __restrict__ out) {
+  pdl_trigger();
+  pdl_wait();
   const int h = blockIdx.x, b = blockIdx.y, d = threadIdx.x;
   const int L = positions[b] + 1;
   const int n = min((L + kChunk - 1) / kChunk, lanes);
@@ -921,6 +904,8 @@ __global__ void attn_decode_merge_kernel(const float* __restrict__ ws_o, const f
 __global__ void __launch_bounds__(256) attn_decode_merge_cast_kernel(
     const float* __restrict__ ws_o, const float* __restrict__ ws_ml, const int32_t* __restrict__ positions, int Hq,
     int D, int max_chunks, int lanes, const MergeOut mo, const TpRowMax tp, int* d_status) {
+  pdl_trigger();
+  pdl_wait();
   __shared__ float s_max[64], s_inv_den[64];
   __shared__ uint32_t s_tp[2];
   const int b = blockIdx.x;
@@ -946,8 +931,7 @@ extern "C" {
 
 int64_t xaxb_attn_decode_workspace_bytes(int64_t B, int64_t Hq, int64_t D, int64_t max_len) {
   const int64_t chunks = (max_len + kChunk - 1) / kChunk;
-  // partial results [B, Hq, chunks, D + 2] float32, then one ticket word per sequence
-  return B * Hq * chunks * (D + 2) * (int64_t)sizeof(float) + (B + 3) / 4 * 16;
+  return B * Hq * chunks * (D + 2) * (int64_t)sizeof(float);
 }
 
 static int decode_launch(xaxb_ctx* ctx_, void* stream, const void* q_rot_bf16, const void* k_cache_bf16,
@@ -993,20 +977,7 @@ static int decode_launch(xaxb_ctx* ctx_, void* stream, const void* q_rot_bf16, c
   p.ws_ml = p.ws_o + B * Hq * max_chunks * D;
   p.max_chunks = max_chunks;
   p.d_status = ctx->d_status;
-  p.tickets = nullptr;
-  p.merge = MergeOut{static_cast<uint4*>(out_bf16), static_cast<uint2*>(q_e4m3), row_scale, row_inv_scale};
-  p.tp = tp ? *tp : TpRowMax{};
   int lanes = max_chunks;  // partial results per (sequence, head) row of the workspace
-  // The chunk-walking kernel merges and casts by itself when the cast is wanted; its tickets
-  // are cleared by a memset node ahead of it (no state is carried from call to call).
-  // (With a tensor-parallel exchange inside the merge, the merging CTAs wait for other GPUs while
-  // holding an SM slot: fused only while they cannot crowd out the CTAs still working.)
-  const bool fuse_merge =
-      q_e4m3 != nullptr && g_decode_variant != 2 && (!tp || tp->world <= 1 || B <= 2 * ctx->num_sms);
-  if (fuse_merge) {
-    p.tickets = reinterpret_cast<unsigned int*>(p.ws_ml + B * Hq * max_chunks * 2);
-    cudaMemsetAsync(p.tickets, 0, (size_t)B * sizeof(unsigned int), s);
-  }
   const bool use_pipe = g_decode_variant == 2 && (long long)B * Hkv * max_chunks < (1ll << 31);
   if (use_pipe) {
     CUtensorMap tq;
@@ -1038,7 +1009,7 @@ static int decode_launch(xaxb_ctx* ctx_, void* stream, const void* q_rot_bf16, c
                              PipeSmem<128>::kBytes);
         setp128 = true;
       }
-      attn_decode_pipe_kernel<128><<<grid_p, kPipeThreads, PipeSmem<128>::kBytes, s>>>(tq, tk, tv, p, (int)B);
+      launch_kernel(attn_decode_pipe_kernel<128>, grid_p, dim3(kPipeThreads), PipeSmem<128>::kBytes, s, 1, tq, tk, tv, p, (int)B);
     } else {
       static bool setp64 = false;
       if (!setp64) {
@@ -1046,7 +1017,7 @@ static int decode_launch(xaxb_ctx* ctx_, void* stream, const void* q_rot_bf16, c
                              PipeSmem<64>::kBytes);
         setp64 = true;
       }
-      attn_decode_pipe_kernel<64><<<grid_p, kPipeThreads, PipeSmem<64>::kBytes, s>>>(tq, tk, tv, p, (int)B);
+      launch_kernel(attn_decode_pipe_kernel<64>, grid_p, dim3(kPipeThreads), PipeSmem<64>::kBytes, s, 1, tq, tk, tv, p, (int)B);
     }
   } else {
     // Chunks are dealt to `lanes` CTAs per (sequence, kv head); each CTA walks its chunks with
@@ -1070,7 +1041,7 @@ static int decode_launch(xaxb_ctx* ctx_, void* stream, const void* q_rot_bf16, c
                            DecodeSmem<DD>::kBytes);                                                 \
       set = true;                                                                                   \
     }                                                                                               \
-    attn_decode_kernel<DD, GG><<<grid, 128, DecodeSmem<DD>::kBytes, s>>>(tk, tv, p);                \
+    launch_kernel(attn_decode_kernel<DD, GG>, grid, dim3(128), DecodeSmem<DD>::kBytes, s, 1, tk, tv, p);                \
   }
     XAXB_DECODE_CASE(128, 1) XAXB_DECODE_CASE(128, 2) XAXB_DECODE_CASE(128, 4) XAXB_DECODE_CASE(128, 8)
     XAXB_DECODE_CASE(128, 16) XAXB_DECODE_CASE(64, 1) XAXB_DECODE_CASE(64, 2) XAXB_DECODE_CASE(64, 4)
@@ -1079,14 +1050,15 @@ static int decode_launch(xaxb_ctx* ctx_, void* stream, const void* q_rot_bf16, c
   }
   rc = check_launch("attn_decode_kernel");
   if (rc) return rc;
-  if (fuse_merge) return XAXB_OK;
   if (q_e4m3) {
-    attn_decode_merge_cast_kernel<<<(unsigned)B, 256, 0, s>>>(p.ws_o, p.ws_ml, positions, (int)Hq, (int)D, max_chunks,
-                                                             lanes, p.merge, p.tp, ctx->d_status);
+    launch_kernel(attn_decode_merge_cast_kernel, dim3((unsigned)B), dim3(256), 0, s, 1, p.ws_o, p.ws_ml, positions, (int)Hq, (int)D, max_chunks,
+                                                             lanes,
+                  MergeOut{static_cast<uint4*>(out_bf16), static_cast<uint2*>(q_e4m3), row_scale, row_inv_scale},
+                  tp ? *tp : TpRowMax{}, ctx->d_status);
     return check_launch("attn_decode_merge_cast_kernel");
   }
   dim3 mgrid((unsigned)Hq, (unsigned)B);
-  attn_decode_merge_kernel<<<mgrid, (unsigned)D, 0, s>>>(p.ws_o, p.ws_ml, positions, (int)Hq, (int)D, max_chunks,
+  launch_kernel(attn_decode_merge_kernel, mgrid, dim3((unsigned)D), 0, s, 1, p.ws_o, p.ws_ml, positions, (int)Hq, (int)D, max_chunks,
                                                          lanes, static_cast<__nv_bfloat16*>(out_bf16));
   return check_launch("attn_decode_merge_kernel");
 }

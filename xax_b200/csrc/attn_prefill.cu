@@ -43,6 +43,7 @@ template <int D>
 __global__ void __launch_bounds__(128, 1) attn_prefill_kernel(const __grid_constant__ CUtensorMap tmap_k,
                                                               const __grid_constant__ CUtensorMap tmap_v,
                                                               const PrefillParams p) {
+  pdl_wait();  // nothing below may run ahead of the previous kernel in the stream
   using SM = PrefillSmem<D>;
   constexpr int kBoxes = D / 64;
   const int qb = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
@@ -110,6 +111,7 @@ __global__ void __launch_bounds__(128, 1) attn_prefill_kernel(const __grid_const
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
+  pdl_trigger();  // tensor memory is allocated: the next kernel may be scheduled
   const uint32_t tmem_s = tmem_base;          // columns [0, 128)
   const uint32_t tmem_pv = tmem_base + 128;   // columns [128, 128 + D)
   const uint32_t lane_off = uint32_t(warp * 32) << 16;
@@ -300,7 +302,7 @@ extern "C" int xaxb_attn_prefill(xaxb_ctx* ctx_, void* stream, const void* q_rot
                            PrefillSmem<128>::kBytes);
       set128 = true;
     }
-    attn_prefill_kernel<128><<<grid, 128, PrefillSmem<128>::kBytes, s>>>(tk, tv, p);
+    launch_kernel(attn_prefill_kernel<128>, grid, dim3(128), PrefillSmem<128>::kBytes, s, 1, tk, tv, p);
   } else {
     static bool set64 = false;
     if (!set64) {
@@ -308,7 +310,7 @@ extern "C" int xaxb_attn_prefill(xaxb_ctx* ctx_, void* stream, const void* q_rot
                            PrefillSmem<64>::kBytes);
       set64 = true;
     }
-    attn_prefill_kernel<64><<<grid, 128, PrefillSmem<64>::kBytes, s>>>(tk, tv, p);
+    launch_kernel(attn_prefill_kernel<64>, grid, dim3(128), PrefillSmem<64>::kBytes, s, 1, tk, tv, p);
   }
   return check_launch("attn_prefill_kernel");
 }

@@ -30,6 +30,11 @@ __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
 }
 
+// Programmatic dependent launch (see launch_kernel below).  Both are no-ops in a kernel that
+// was launched without the attribute.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 __device__ __forceinline__ unsigned long long globaltimer_ns() {
   unsigned long long t;
   asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
@@ -123,6 +128,12 @@ __device__ __forceinline__ void tma_load_4d(void* smem_dst, const CUtensorMap* m
       "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
       ::"r"(smem_u32(smem_dst)), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y), "r"(z), "r"(w)
       : "memory");
+}
+
+// Asks L2 for a tile without waiting for it or touching shared memory.  L2 is the point of
+// coherence, so this is safe even when the tile is still being written.
+__device__ __forceinline__ void tma_prefetch_l2_2d(const CUtensorMap* map, int x, int y) {
+  asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];" ::"l"(map), "r"(x), "r"(y) : "memory");
 }
 
 __device__ __forceinline__ void prefetch_tmap(const CUtensorMap* map) {
@@ -258,5 +269,43 @@ int make_tmap_4d(const Ctx* ctx, CUtensorMap* map, const void* base, int elem_by
                  const uint64_t strides_bytes[3], const uint32_t box[4]);
 void set_last_error(const char* fmt, ...);
 int check_launch(const char* what);
+
+// Every kernel of the library is launched through launch_kernel().  With programmatic dependent
+// launch on (the default) a kernel may be scheduled while its predecessor in the stream is still
+// running: its CTAs run up to their pdl_wait() -- which every kernel executes before it reads or
+// writes global memory that another kernel touches -- and block there until the predecessor has
+// completed and its writes are visible.  That takes launch latency, CTA start-up and (for the
+// GEMMs) the first trip to HBM off the critical path of a chain of short kernels, inside CUDA
+// graphs as well.  A kernel lets its successor go with pdl_trigger(); kernels that own tensor
+// memory trigger only after their allocation, so a successor that is already resident can never
+// hold the columns a CTA of the running kernel still needs.
+bool pdl_enabled();
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                 unsigned cluster_x, Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[2];
+  unsigned n = 0;
+  if (cluster_x > 1) {
+    attr[n].id = cudaLaunchAttributeClusterDimension;
+    attr[n].val.clusterDim.x = cluster_x;
+    attr[n].val.clusterDim.y = 1;
+    attr[n].val.clusterDim.z = 1;
+    ++n;
+  }
+  if (pdl_enabled()) {
+    attr[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[n].val.programmaticStreamSerializationAllowed = 1;
+    ++n;
+  }
+  cfg.attrs = attr;
+  cfg.numAttrs = n;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
 
 }  // namespace xaxb

@@ -77,6 +77,7 @@ template <bool IS_FP8>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                  const __grid_constant__ CUtensorMap tmap_out, const GemmParams p) {
+  pdl_wait();  // nothing below may run ahead of the previous kernel in the stream
   using Cfg = Gemm2Cfg;
   constexpr int kStages = Cfg::kStages, BN = Cfg::kBN;
   constexpr int kElemBytes = IS_FP8 ? 1 : 2;
@@ -130,6 +131,7 @@ gemm_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   cluster_sync_all();  // both CTAs' barriers exist before anyone signals across the pair
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
+  pdl_trigger();  // tensor memory is allocated: the next kernel may be scheduled
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer (both CTAs)
@@ -331,8 +333,8 @@ static int launch_gemm_2cta(const Ctx* ctx, cudaStream_t stream, const void* a, 
     max_pairs = (qe == cudaSuccess && n > 0) ? n : ctx->num_sms / 2 - 8;
   }
   const int pairs = tiles < max_pairs ? tiles : max_pairs;
-  cfg.gridDim = dim3((unsigned)(2 * pairs), 1, 1);
-  cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_2cta_kernel<IS_FP8>, ta, tb, tout, p);
+  cudaError_t e = launch_kernel(gemm_2cta_kernel<IS_FP8>, dim3((unsigned)(2 * pairs), 1, 1), dim3(kGemmThreads),
+                                Cfg::kSmemBytes, stream, 2u, ta, tb, tout, p);
   if (e != cudaSuccess) {
     set_last_error("gemm_2cta_kernel launch: %s", cudaGetErrorString(e));
     return XAXB_LAUNCH_FAILED;

@@ -37,6 +37,7 @@ struct GemmParams {
   __nv_bfloat16* out;
   long long ldo;
   int* d_status;
+  int prefetch_b;  // the launch may overlap the previous kernel: ask L2 for B ahead of the wait
 };
 
 // Tile order: bands of kBand tile rows, column by column inside a band (row index fastest).  The
@@ -50,6 +51,9 @@ __device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, 
   tn = r / rows;
   tm = band * kBand + (r - tn * rows);
 }
+
+// K blocks of operand B that a producer asks L2 for ahead of the wait on the previous kernel.
+constexpr int kMaxPrefetchBlocks = 4;
 
 template <int BN>
 struct GemmCfg {
@@ -150,8 +154,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
+  pdl_trigger();  // tensor memory is allocated: the next kernel may be scheduled
 
   const int num_tiles = p.tiles_m * p.tiles_n;
+  // Everything that reads or writes global memory waits for the previous kernel in the stream;
+  // the producer thread first asks L2 for operand B of its first tile (below).
+  if (threadIdx.x != 0) pdl_wait();
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
@@ -159,6 +167,20 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
+      // While the previous kernel is still running, pull this CTA's first B tile (the weights:
+      // what a decode-sized GEMM streams from HBM) towards L2.  A prefetch carries no data into
+      // the SM, and L2 is the point of coherence, so this is safe whatever wrote B and whenever.
+      if (p.prefetch_b && (int)blockIdx.x < num_tiles) {
+        int tm, tn;
+        tile_coords<16>((int)blockIdx.x, p.tiles_m, p.tiles_n, tm, tn);
+        int kk = (int)(((long long)blockIdx.x * 5) % p.num_k_blocks);
+        const int n_pre = p.num_k_blocks < kMaxPrefetchBlocks ? p.num_k_blocks : kMaxPrefetchBlocks;
+        for (int i = 0; i < n_pre; ++i) {
+          tma_prefetch_l2_2d(&tmap_b, kk * kBKElems, tn * BN);
+          if (++kk == p.num_k_blocks) kk = 0;
+        }
+      }
+      pdl_wait();
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
         int tm, tn;
         tile_coords<16>(tile, p.tiles_m, p.tiles_n, tm, tn);
@@ -506,12 +528,23 @@ gemm_splitk_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
+  pdl_trigger();  // tensor memory is allocated: the next kernel may be scheduled
+  if (threadIdx.x != 0) pdl_wait();
 
   if (warp == 0) {
     if (lane == 0) {
       int stage = 0;
       uint32_t phase = 0;
       int kk = nkb > 0 ? kb0 + (tile_n * 3) % nkb : kb0;  // staggered start, see gemm_tc_kernel
+      if (p.prefetch_b) {  // B towards L2 while the previous kernel is still running (see gemm_tc_kernel)
+        int k2 = kk;
+        const int n_pre = nkb < kMaxPrefetchBlocks ? nkb : kMaxPrefetchBlocks;
+        for (int i = 0; i < n_pre; ++i) {
+          tma_prefetch_l2_2d(&tmap_b, k2 * kBKElems, n0);
+          if (++k2 == kb1) k2 = kb0;
+        }
+      }
+      pdl_wait();
       for (int i = 0; i < nkb; ++i) {
         if (!mbar_wait(empty + stage, phase ^ 1, abort_flag, p.d_status, XAXB_DEVICE_TIMEOUT * 1000 + kSiteSkProducer))
           break;
@@ -678,19 +711,8 @@ static int launch_splitk(const Ctx* ctx, cudaStream_t stream, const void* a, lon
     }
     attr_set = true;
   }
-  cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3((unsigned)(p.tiles_n * S), 1, 1);
-  cfg.blockDim = dim3(kGemmThreads, 1, 1);
-  cfg.dynamicSmemBytes = Cfg::kSmemBytes;
-  cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeClusterDimension;
-  attr[0].val.clusterDim.x = (unsigned)S;
-  attr[0].val.clusterDim.y = 1;
-  attr[0].val.clusterDim.z = 1;
-  cfg.attrs = attr;
-  cfg.numAttrs = 1;
-  cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_splitk_kernel<BN, IS_FP8>, ta, tb, p, S);
+  cudaError_t e = launch_kernel(gemm_splitk_kernel<BN, IS_FP8>, dim3((unsigned)(p.tiles_n * S), 1, 1), dim3(kGemmThreads),
+                                Cfg::kSmemBytes, stream, (unsigned)S, ta, tb, p, S);
   if (e != cudaSuccess) {
     set_last_error("gemm_splitk_kernel launch: %s", cudaGetErrorString(e));
     return XAXB_LAUNCH_FAILED;
@@ -732,7 +754,7 @@ static int launch_gemm(const Ctx* ctx, cudaStream_t stream, const void* a, long 
   }
   const int tiles = p.tiles_m * p.tiles_n;
   const int grid = tiles < ctx->num_sms ? tiles : ctx->num_sms;
-  gemm_tc_kernel<BN, IS_FP8><<<grid, kGemmThreads, Cfg::kSmemBytes, stream>>>(ta, tb, tout, p);
+  launch_kernel(gemm_tc_kernel<BN, IS_FP8>, grid, dim3(kGemmThreads), Cfg::kSmemBytes, stream, 1, ta, tb, tout, p);
   return check_launch("gemm_tc_kernel");
 }
 
@@ -817,6 +839,7 @@ static int gemm_entry(xaxb_ctx* ctx_, void* stream, const void* a, int64_t lda, 
   p.out = static_cast<__nv_bfloat16*>(out);
   p.ldo = ldo;
   p.d_status = ctx->d_status;
+  p.prefetch_b = pdl_enabled() ? 1 : 0;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const GemmPlan plan = pick_plan(M, N, K, eb, ctx->num_sms);
   // Large problems go to the CTA-pair kernel: 256 x 256 tiles need a third less operand traffic

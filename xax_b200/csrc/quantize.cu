@@ -14,6 +14,8 @@ namespace xaxb {
 __global__ void __launch_bounds__(256) quantize_rows_kernel(const uint4* __restrict__ x, int64_t vec_per_row,
                                                             uint2* __restrict__ q, float* __restrict__ scale,
                                                             float* __restrict__ inv_scale, float* __restrict__ amax) {
+  pdl_trigger();
+  pdl_wait();
   const int64_t row = blockIdx.x;
   const uint4* xr = x + row * vec_per_row;
   uint32_t m = 0;
@@ -33,6 +35,8 @@ __global__ void __launch_bounds__(256) quantize_rows_kernel(const uint4* __restr
 // ---- per-group current scaling, pass 1: amax of each group of rows -------------------------
 __global__ void __launch_bounds__(256) group_amax_kernel(const uint4* __restrict__ x, int64_t vec_per_group,
                                                          unsigned int* __restrict__ amax_bits) {
+  pdl_trigger();
+  pdl_wait();
   const int64_t g = blockIdx.y;
   const uint4* xg = x + g * vec_per_group;
   uint32_t m = 0;
@@ -49,6 +53,8 @@ __global__ void __launch_bounds__(256) group_cast_kernel(const uint4* __restrict
                                                          int64_t group_rows, const float* __restrict__ amax,
                                                          uint2* __restrict__ q, float* __restrict__ scale,
                                                          float* __restrict__ inv_scale) {
+  pdl_trigger();
+  pdl_wait();
   const int64_t g = blockIdx.y;
   const float s = current_scale_from_amax(amax[g]);
   const uint4* xg = x + g * vec_per_group;
@@ -79,6 +85,8 @@ __global__ void __launch_bounds__(256) delayed_cast_kernel(const uint4* __restri
                                                            unsigned int* scratch, const float* history_in,
                                                            int history_len, float* history_out, float* scale_out,
                                                            float* inv_scale_out) {
+  pdl_trigger();
+  pdl_wait();
   extern __shared__ float hist[];
   __shared__ float warp_max[8];
   __shared__ int is_last;
@@ -181,7 +189,7 @@ int xaxb_quantize_current(xaxb_ctx* ctx, void* stream, const void* x_bf16, int64
     const int64_t vec = cols / 8;
     int threads = (int)((vec + 31) / 32 * 32);
     if (threads > 256) threads = 256;
-    quantize_rows_kernel<<<(unsigned)rows, threads, 0, s>>>(x, vec, q, scale, inv_scale, amax);
+    launch_kernel(quantize_rows_kernel, dim3((unsigned)rows), dim3(threads), 0, s, 1, x, vec, q, scale, inv_scale, amax);
     return check_launch("quantize_rows_kernel");
   }
   const int64_t groups = rows / group_rows;
@@ -193,10 +201,10 @@ int xaxb_quantize_current(xaxb_ctx* ctx, void* stream, const void* x_bf16, int64
   cudaMemsetAsync(amax, 0, groups * sizeof(float), s);
   int64_t cap = ((int64_t)c->num_sms * 8 + groups - 1) / groups;
   dim3 grid(grid_for(vec_per_group, c->num_sms, cap), (unsigned)groups);
-  group_amax_kernel<<<grid, 256, 0, s>>>(x, vec_per_group, reinterpret_cast<unsigned int*>(amax));
+  launch_kernel(group_amax_kernel, grid, dim3(256), 0, s, 1, x, vec_per_group, reinterpret_cast<unsigned int*>(amax));
   rc = check_launch("group_amax_kernel");
   if (rc) return rc;
-  group_cast_kernel<<<grid, 256, 0, s>>>(x, vec_per_group, group_rows, amax, q, scale, inv_scale);
+  launch_kernel(group_cast_kernel, grid, dim3(256), 0, s, 1, x, vec_per_group, group_rows, amax, q, scale, inv_scale);
   return check_launch("group_cast_kernel");
 }
 
@@ -216,7 +224,7 @@ int xaxb_group_amax(xaxb_ctx* ctx, void* stream, const void* x_bf16, int64_t row
   cudaMemsetAsync(amax, 0, groups * sizeof(float), s);
   int64_t cap = ((int64_t)c->num_sms * 8 + groups - 1) / groups;
   dim3 grid(grid_for(vec_per_group, c->num_sms, cap), (unsigned)groups);
-  group_amax_kernel<<<grid, 256, 0, s>>>(static_cast<const uint4*>(x_bf16), vec_per_group,
+  launch_kernel(group_amax_kernel, grid, dim3(256), 0, s, 1, static_cast<const uint4*>(x_bf16), vec_per_group,
                                          reinterpret_cast<unsigned int*>(amax));
   return check_launch("group_amax_kernel");
 }
@@ -238,7 +246,7 @@ int xaxb_quantize_with_amax(xaxb_ctx* ctx, void* stream, const void* x_bf16, int
   const int64_t vec_per_group = group_rows * cols / 8;
   int64_t cap = ((int64_t)c->num_sms * 8 + groups - 1) / groups;
   dim3 grid(grid_for(vec_per_group, c->num_sms, cap), (unsigned)groups);
-  group_cast_kernel<<<grid, 256, 0, s>>>(static_cast<const uint4*>(x_bf16), vec_per_group, group_rows, group_amax,
+  launch_kernel(group_cast_kernel, grid, dim3(256), 0, s, 1, static_cast<const uint4*>(x_bf16), vec_per_group, group_rows, group_amax,
                                          static_cast<uint2*>(q_e4m3), scale, inv_scale);
   return check_launch("group_cast_kernel");
 }
@@ -256,7 +264,7 @@ int xaxb_quantize_delayed(xaxb_ctx* ctx, void* stream, const void* x_bf16, int64
   const Ctx* c = reinterpret_cast<const Ctx*>(ctx);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const int64_t n_vec = rows * cols / 8;
-  delayed_cast_kernel<<<grid_for(n_vec, c->num_sms), 256, history_len * sizeof(float), s>>>(
+  launch_kernel(delayed_cast_kernel, dim3(grid_for(n_vec, c->num_sms)), dim3(256), history_len * sizeof(float), s, 1, 
       static_cast<const uint4*>(x_bf16), n_vec, scale_in, static_cast<uint2*>(q_e4m3),
       reinterpret_cast<unsigned int*>(amax_scratch), history_in, history_len, history_out, scale_out, inv_scale_out);
   return check_launch("delayed_cast_kernel");

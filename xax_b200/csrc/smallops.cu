@@ -24,6 +24,8 @@ __global__ void __launch_bounds__(256) rmsnorm_kernel(const uint4* __restrict__ 
                                                       uint2* __restrict__ q, float* __restrict__ scale,
                                                       float* __restrict__ inv_scale,
                                                       unsigned int* __restrict__ group_amax, int64_t group_rows) {
+  pdl_trigger();
+  pdl_wait();
   const int64_t row = blockIdx.x;
   const uint4* xr = x + row * vec;
   float acc = 0.0f;
@@ -81,6 +83,8 @@ __global__ void __launch_bounds__(256) silu_mul_kernel(const uint4* __restrict__
                                                        float* __restrict__ inv_scale,
                                                        unsigned int* __restrict__ group_amax, int64_t group_rows,
                                                        const TpRowMax tp, int* d_status) {
+  pdl_trigger();
+  pdl_wait();
   __shared__ uint32_t s_tp[2];
   const int64_t row = blockIdx.x;
   const uint4* gr = gate + row * ld_vec;
@@ -122,6 +126,8 @@ __global__ void __launch_bounds__(256) rmsnorm_reg_kernel(const uint4* __restric
                                                           uint2* __restrict__ q, float* __restrict__ scale,
                                                           float* __restrict__ inv_scale,
                                                           unsigned int* __restrict__ group_amax, int64_t group_rows) {
+  pdl_trigger();
+  pdl_wait();
   const int64_t row = blockIdx.x;
   const uint4* xr = x + row * vec;
   float v[VPT][8];
@@ -188,6 +194,8 @@ __global__ void __launch_bounds__(256) silu_mul_cluster_kernel(const uint4* __re
                                                                float* __restrict__ inv_scale,
                                                                unsigned int* __restrict__ group_amax,
                                                                int64_t group_rows) {
+  pdl_trigger();
+  pdl_wait();
   __shared__ uint32_t cta_max;
   const int64_t row = blockIdx.y;
   const int part = blockIdx.x;  // == rank in the cluster (cluster spans grid x)
@@ -236,6 +244,8 @@ __global__ void __launch_bounds__(256) kv_append_rope_vec_kernel(
     const uint4* __restrict__ qkv, int64_t ld_vec, int T, int Hq, int Hkv, int D, const int32_t* __restrict__ positions,
     const uint4* __restrict__ cos_t, const uint4* __restrict__ sin_t, int64_t table_len, uint4* __restrict__ q_rot,
     uint4* __restrict__ k_cache, uint4* __restrict__ v_cache, int64_t max_len, int store_rotated_k, int* d_status) {
+  pdl_trigger();
+  pdl_wait();
   const int64_t bt = blockIdx.x;
   const int b = (int)(bt / T), t = (int)(bt % T);
   const int64_t pos = (int64_t)positions[b] + t;
@@ -283,6 +293,8 @@ __global__ void __launch_bounds__(256) kv_append_rope_vec_kernel(
 
 __global__ void __launch_bounds__(256) embed_kernel(const int32_t* __restrict__ tokens, const uint4* __restrict__ table,
                                                     int64_t vocab, int64_t vec, uint4* __restrict__ x, int* d_status) {
+  pdl_trigger();
+  pdl_wait();
   const int64_t i = blockIdx.x;
   int64_t t = tokens[i];
   if (t < 0 || t >= vocab) {  // the reference's gather clamps; report and clamp
@@ -303,6 +315,8 @@ __device__ __forceinline__ bool better(float v, int i, float bv, int bi) {
 __global__ void __launch_bounds__(1024) argmax_kernel(const __nv_bfloat16* __restrict__ logits, int64_t vocab,
                                                       int64_t ld, int32_t* __restrict__ out,
                                                       float* __restrict__ max_out) {
+  pdl_trigger();
+  pdl_wait();
   const int64_t row = blockIdx.x;
   const __nv_bfloat16* lr = logits + row * ld;
   float bv = -INFINITY;
@@ -349,6 +363,8 @@ __global__ void __launch_bounds__(1024) argmax_kernel(const __nv_bfloat16* __res
 // is the lower global index.
 __global__ void argmax_merge_kernel(const float* __restrict__ vals, const int32_t* __restrict__ idx, int parts,
                                     int rows, int slice, int32_t* __restrict__ out) {
+  pdl_trigger();
+  pdl_wait();
   const int r = blockIdx.x * blockDim.x + threadIdx.x;
   if (r >= rows) return;
   float bv = vals[r];
@@ -371,6 +387,8 @@ __global__ void kv_append_rope_kernel(const __nv_bfloat16* __restrict__ qkv, int
                                       __nv_bfloat16* __restrict__ q_rot, __nv_bfloat16* __restrict__ k_cache,
                                       __nv_bfloat16* __restrict__ v_cache, int64_t max_len, int store_rotated_k,
                                       int* d_status) {
+  pdl_trigger();
+  pdl_wait();
   const int64_t bt = blockIdx.x;
   const int b = (int)(bt / T), t = (int)(bt % T);
   const int head = blockIdx.y;
@@ -401,6 +419,8 @@ __global__ void kv_append_rope_kernel(const __nv_bfloat16* __restrict__ qkv, int
 }
 
 __global__ void advance_positions_kernel(int32_t* positions, int B, int32_t delta) {
+  pdl_trigger();
+  pdl_wait();
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i < B) positions[i] += delta;
 }
@@ -413,6 +433,8 @@ __global__ void gemm_fp8_check_kernel(const __nv_fp8_storage_t* __restrict__ a, 
                                       int64_t K, const float* row_mul, int rms, const float* col_mul, int cms,
                                       const __nv_bfloat16* bias, const __nv_bfloat16* residual, int64_t ldr,
                                       __nv_bfloat16* out, int64_t ldo) {
+  pdl_trigger();
+  pdl_wait();
   const int64_t n = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   const int64_t m = blockIdx.y;
   if (n >= N || m >= M) return;
@@ -436,6 +458,8 @@ __global__ void __launch_bounds__(128) attn_check_kernel(const __nv_bfloat16* __
                                                          const int32_t* __restrict__ positions, int T, int Hq, int Hkv,
                                                          int D, int64_t max_len, float sm_scale,
                                                          __nv_bfloat16* __restrict__ out) {
+  pdl_trigger();
+  pdl_wait();
   extern __shared__ float logits[];
   __shared__ float red[4];
   const int h = blockIdx.x;
@@ -514,13 +538,13 @@ int xaxb_rmsnorm(xaxb_ctx* ctx, void* stream, const void* x_bf16, const void* we
   unsigned int* gp = reinterpret_cast<unsigned int*>(group_amax);
   const int64_t gr = group_rows > 0 ? group_rows : 1;
   if (vec > 64 && vec <= 256)
-    rmsnorm_reg_kernel<1><<<(unsigned)rows, 256, 0, st>>>(xp, wp, eps, (int)vec, yp, qp, scale, inv_scale, gp, gr);
+    launch_kernel(rmsnorm_reg_kernel<1>, dim3((unsigned)rows), dim3(256), 0, st, 1, xp, wp, eps, (int)vec, yp, qp, scale, inv_scale, gp, gr);
   else if (vec > 256 && vec <= 512)
-    rmsnorm_reg_kernel<2><<<(unsigned)rows, 256, 0, st>>>(xp, wp, eps, (int)vec, yp, qp, scale, inv_scale, gp, gr);
+    launch_kernel(rmsnorm_reg_kernel<2>, dim3((unsigned)rows), dim3(256), 0, st, 1, xp, wp, eps, (int)vec, yp, qp, scale, inv_scale, gp, gr);
   else if (vec > 512 && vec <= 1024)
-    rmsnorm_reg_kernel<4><<<(unsigned)rows, 256, 0, st>>>(xp, wp, eps, (int)vec, yp, qp, scale, inv_scale, gp, gr);
+    launch_kernel(rmsnorm_reg_kernel<4>, dim3((unsigned)rows), dim3(256), 0, st, 1, xp, wp, eps, (int)vec, yp, qp, scale, inv_scale, gp, gr);
   else
-    rmsnorm_kernel<<<(unsigned)rows, row_threads(vec), 0, st>>>(xp, wp, eps, vec, yp, qp, scale, inv_scale, gp, gr);
+    launch_kernel(rmsnorm_kernel, dim3((unsigned)rows), dim3(row_threads(vec)), 0, st, 1, xp, wp, eps, vec, yp, qp, scale, inv_scale, gp, gr);
   return check_launch("rmsnorm_kernel");
 }
 
@@ -553,24 +577,14 @@ int xaxb_silu_mul(xaxb_ctx* ctx, void* stream, const void* gate_bf16, const void
     const int64_t per = (vec + C - 1) / C;
     const int vpt = (int)((per + 255) / 256);
     if (vpt <= 2) {
-      cudaLaunchConfig_t cfg = {};
-      cfg.gridDim = dim3((unsigned)C, (unsigned)rows, 1);
-      cfg.blockDim = dim3(256, 1, 1);
-      cfg.stream = st;
-      cudaLaunchAttribute attr[1];
-      attr[0].id = cudaLaunchAttributeClusterDimension;
-      attr[0].val.clusterDim.x = (unsigned)C;
-      attr[0].val.clusterDim.y = 1;
-      attr[0].val.clusterDim.z = 1;
-      cfg.attrs = attr;
-      cfg.numAttrs = 1;
+      const dim3 cgrid((unsigned)C, (unsigned)rows, 1);
       cudaError_t e;
       if (vpt == 1)
-        e = cudaLaunchKernelEx(&cfg, silu_mul_cluster_kernel<1>, gate, up, ld / 8, (int)vec, C, hp, qp, scale, inv_scale,
-                               gp, gr);
+        e = launch_kernel(silu_mul_cluster_kernel<1>, cgrid, dim3(256), 0, st, (unsigned)C, gate, up, ld / 8, (int)vec, C,
+                          hp, qp, scale, inv_scale, gp, gr);
       else
-        e = cudaLaunchKernelEx(&cfg, silu_mul_cluster_kernel<2>, gate, up, ld / 8, (int)vec, C, hp, qp, scale, inv_scale,
-                               gp, gr);
+        e = launch_kernel(silu_mul_cluster_kernel<2>, cgrid, dim3(256), 0, st, (unsigned)C, gate, up, ld / 8, (int)vec, C,
+                          hp, qp, scale, inv_scale, gp, gr);
       if (e != cudaSuccess) {
         set_last_error("silu_mul_cluster_kernel launch: %s", cudaGetErrorString(e));
         return XAXB_LAUNCH_FAILED;
@@ -578,7 +592,7 @@ int xaxb_silu_mul(xaxb_ctx* ctx, void* stream, const void* gate_bf16, const void
       return check_launch("silu_mul_cluster_kernel");
     }
   }
-  silu_mul_kernel<<<(unsigned)rows, row_threads(vec), 0, st>>>(gate, up, ld / 8, vec, hp, qp, scale, inv_scale, gp, gr,
+  launch_kernel(silu_mul_kernel, dim3((unsigned)rows), dim3(row_threads(vec)), 0, st, 1, gate, up, ld / 8, vec, hp, qp, scale, inv_scale, gp, gr,
                                                                TpRowMax{}, nullptr);
   return check_launch("silu_mul_kernel");
 }
@@ -605,7 +619,7 @@ int xaxb_silu_mul_cast_tp(xaxb_ctx* ctx, void* stream, const void* gate_bf16, co
     return XAXB_BAD_ARGUMENT;
   }
   const int64_t vec = dim / 8;
-  silu_mul_kernel<<<(unsigned)rows, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+  launch_kernel(silu_mul_kernel, dim3((unsigned)rows), dim3(256), 0, static_cast<cudaStream_t>(stream), 1, 
       gate, up, ld / 8, vec, nullptr, static_cast<uint2*>(q_e4m3), scale, inv_scale, nullptr, 1, tp,
       reinterpret_cast<Ctx*>(ctx)->d_status);
   return check_launch("silu_mul_kernel (tensor-parallel)");
@@ -616,7 +630,7 @@ int xaxb_embed(xaxb_ctx* ctx, void* stream, const int32_t* tokens, int64_t n_tok
   if (!ctx || !tokens || !table_bf16 || !x_bf16 || n_tokens <= 0 || dim <= 0 || dim % 8 != 0 || vocab <= 0)
     return XAXB_BAD_ARGUMENT;
   Ctx* c = reinterpret_cast<Ctx*>(ctx);
-  embed_kernel<<<(unsigned)n_tokens, row_threads(dim / 8), 0, static_cast<cudaStream_t>(stream)>>>(
+  launch_kernel(embed_kernel, dim3((unsigned)n_tokens), dim3(row_threads(dim / 8)), 0, static_cast<cudaStream_t>(stream), 1, 
       tokens, static_cast<const uint4*>(table_bf16), vocab, dim / 8, static_cast<uint4*>(x_bf16), c->d_status);
   return check_launch("embed_kernel");
 }
@@ -624,7 +638,7 @@ int xaxb_embed(xaxb_ctx* ctx, void* stream, const int32_t* tokens, int64_t n_tok
 int xaxb_argmax(xaxb_ctx* ctx, void* stream, const void* logits_bf16, int64_t rows, int64_t vocab, int64_t ld,
                 int32_t* out, float* max_out) {
   if (!ctx || !logits_bf16 || !out || rows <= 0 || vocab <= 0 || ld < vocab) return XAXB_BAD_ARGUMENT;
-  argmax_kernel<<<(unsigned)rows, 1024, 0, static_cast<cudaStream_t>(stream)>>>(
+  launch_kernel(argmax_kernel, dim3((unsigned)rows), dim3(1024), 0, static_cast<cudaStream_t>(stream), 1, 
       static_cast<const __nv_bfloat16*>(logits_bf16), vocab, ld, out, max_out);
   return check_launch("argmax_kernel");
 }
@@ -632,7 +646,7 @@ int xaxb_argmax(xaxb_ctx* ctx, void* stream, const void* logits_bf16, int64_t ro
 int xaxb_argmax_merge(xaxb_ctx* ctx, void* stream, const float* part_max, const int32_t* part_idx, int64_t parts,
                       int64_t rows, int64_t slice, int32_t* out) {
   if (!ctx || !part_max || !part_idx || !out || parts <= 0 || rows <= 0 || slice <= 0) return XAXB_BAD_ARGUMENT;
-  argmax_merge_kernel<<<(unsigned)((rows + 127) / 128), 128, 0, static_cast<cudaStream_t>(stream)>>>(
+  launch_kernel(argmax_merge_kernel, dim3((unsigned)((rows + 127) / 128)), dim3(128), 0, static_cast<cudaStream_t>(stream), 1, 
       part_max, part_idx, (int)parts, (int)rows, (int)slice, out);
   return check_launch("argmax_merge_kernel");
 }
@@ -657,7 +671,7 @@ int xaxb_kv_append_rope(xaxb_ctx* ctx, void* stream, const void* qkv_bf16, int64
     const int items = (int)((Hq + 2 * Hkv) * (D / 16));
     int threads = (items + 31) / 32 * 32;
     if (threads > 256) threads = 256;
-    kv_append_rope_vec_kernel<<<(unsigned)(B * T), threads, 0, static_cast<cudaStream_t>(stream)>>>(
+    launch_kernel(kv_append_rope_vec_kernel, dim3((unsigned)(B * T)), dim3(threads), 0, static_cast<cudaStream_t>(stream), 1, 
         static_cast<const uint4*>(qkv_bf16), ld / 8, (int)T, (int)Hq, (int)Hkv, (int)D, positions,
         static_cast<const uint4*>(cos_bf16), static_cast<const uint4*>(sin_bf16), table_len,
         static_cast<uint4*>(q_rot_bf16), static_cast<uint4*>(k_cache_bf16), static_cast<uint4*>(v_cache_bf16), max_len,
@@ -665,7 +679,7 @@ int xaxb_kv_append_rope(xaxb_ctx* ctx, void* stream, const void* qkv_bf16, int64
     return check_launch("kv_append_rope_vec_kernel");
   }
   dim3 grid((unsigned)(B * T), (unsigned)(Hq + 2 * Hkv));
-  kv_append_rope_kernel<<<grid, (unsigned)(D / 2), 0, static_cast<cudaStream_t>(stream)>>>(
+  launch_kernel(kv_append_rope_kernel, grid, dim3((unsigned)(D / 2)), 0, static_cast<cudaStream_t>(stream), 1, 
       static_cast<const __nv_bfloat16*>(qkv_bf16), ld, (int)T, (int)Hq, (int)Hkv, (int)D, positions,
       static_cast<const __nv_bfloat16*>(cos_bf16), static_cast<const __nv_bfloat16*>(sin_bf16), table_len,
       static_cast<__nv_bfloat16*>(q_rot_bf16), static_cast<__nv_bfloat16*>(k_cache_bf16),
@@ -675,7 +689,7 @@ int xaxb_kv_append_rope(xaxb_ctx* ctx, void* stream, const void* qkv_bf16, int64
 
 int xaxb_advance_positions(xaxb_ctx* ctx, void* stream, int32_t* positions, int64_t B, int32_t delta) {
   if (!ctx || !positions || B <= 0) return XAXB_BAD_ARGUMENT;
-  advance_positions_kernel<<<(unsigned)((B + 127) / 128), 128, 0, static_cast<cudaStream_t>(stream)>>>(positions,
+  launch_kernel(advance_positions_kernel, dim3((unsigned)((B + 127) / 128)), dim3(128), 0, static_cast<cudaStream_t>(stream), 1, positions,
                                                                                                         (int)B, delta);
   return check_launch("advance_positions_kernel");
 }
@@ -686,7 +700,7 @@ int xaxb_gemm_fp8_check(xaxb_ctx* ctx, void* stream, const void* a_e4m3, int64_t
                         int64_t ldr, void* out_bf16, int64_t ldo) {
   if (!ctx || !a_e4m3 || !b_e4m3 || !out_bf16 || M <= 0 || N <= 0 || K <= 0 || M > 65535) return XAXB_BAD_ARGUMENT;
   dim3 grid((unsigned)((N + 127) / 128), (unsigned)M);
-  gemm_fp8_check_kernel<<<grid, 128, 0, static_cast<cudaStream_t>(stream)>>>(
+  launch_kernel(gemm_fp8_check_kernel, grid, dim3(128), 0, static_cast<cudaStream_t>(stream), 1, 
       static_cast<const __nv_fp8_storage_t*>(a_e4m3), lda, static_cast<const __nv_fp8_storage_t*>(b_e4m3), ldb, M, N,
       K, row_mul, row_mul_stride, col_mul, col_mul_stride, static_cast<const __nv_bfloat16*>(bias_bf16),
       static_cast<const __nv_bfloat16*>(residual_bf16), ldr, static_cast<__nv_bfloat16*>(out_bf16), ldo);
@@ -706,7 +720,7 @@ int xaxb_attn_check(xaxb_ctx* ctx, void* stream, const void* q_rot_bf16, const v
   }
   cudaFuncSetAttribute(attn_check_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   dim3 grid((unsigned)Hq, (unsigned)(B * T));
-  attn_check_kernel<<<grid, 128, smem, static_cast<cudaStream_t>(stream)>>>(
+  launch_kernel(attn_check_kernel, grid, dim3(128), smem, static_cast<cudaStream_t>(stream), 1, 
       static_cast<const __nv_bfloat16*>(q_rot_bf16), static_cast<const __nv_bfloat16*>(k_cache_bf16),
       static_cast<const __nv_bfloat16*>(v_cache_bf16), positions, (int)T, (int)Hq, (int)Hkv, (int)D, max_len,
       softmax_scale, static_cast<__nv_bfloat16*>(out_bf16));

@@ -39,6 +39,8 @@ namespace xaxb {
 __global__ void __launch_bounds__(256) tp_allreduce_sum_kernel(const PeerTable peers, int64_t data_off,
                                                                int64_t sync_off, int rank, int world, int cols,
                                                                uint4* __restrict__ out, int* d_status) {
+  pdl_trigger();
+  pdl_wait();
   __shared__ uint32_t s_epoch;
   const int row = blockIdx.x;
   tp_exchange_flags(peers, sync_off, rank, world, row, &s_epoch, d_status, kSiteTpSum);
@@ -83,6 +85,8 @@ __global__ void __launch_bounds__(256) tp_allreduce_sum_norm_kernel(
     const PeerTable peers, int64_t data_off, int64_t sync_off, int rank, int world, int vec, uint4* __restrict__ x_out,
     const uint4* __restrict__ w, float eps, uint2* __restrict__ q, float* __restrict__ scale,
     float* __restrict__ inv_scale, int* d_status) {
+  pdl_trigger();
+  pdl_wait();
   __shared__ uint32_t s_epoch;
   const int64_t row = blockIdx.x;
   tp_exchange_flags(peers, sync_off, rank, world, (int)row, &s_epoch, d_status, kSiteTpSum);
@@ -151,6 +155,8 @@ __global__ void __launch_bounds__(1024) tp_allreduce_max_kernel(const PeerTable 
                                                                 int64_t sync_off, int rank, int world, int n,
                                                                 const float* __restrict__ in, float* __restrict__ out,
                                                                 int* d_status) {
+  pdl_trigger();
+  pdl_wait();
   __shared__ uint32_t s_epoch;
   const int i = threadIdx.x;
   // the epoch this exchange will get decides which inbox copy it uses
@@ -189,6 +195,8 @@ __global__ void __launch_bounds__(1024) tp_argmax_kernel(const PeerTable peers, 
                                                          const float* __restrict__ part_max,
                                                          const int32_t* __restrict__ part_idx, int32_t* __restrict__ out,
                                                          int* d_status) {
+  pdl_trigger();
+  pdl_wait();
   __shared__ uint32_t s_epoch;
   const int i = threadIdx.x;
   const uint32_t* my_epoch =
@@ -269,7 +277,7 @@ int xaxb_tp_allreduce_sum_bf16(xaxb_ctx* ctx_, void* stream, void* const* peer_b
     return XAXB_UNSUPPORTED;
   }
   const Ctx* ctx = reinterpret_cast<const Ctx*>(ctx_);
-  tp_allreduce_sum_kernel<<<(unsigned)rows, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+  launch_kernel(tp_allreduce_sum_kernel, dim3((unsigned)rows), dim3(256), 0, static_cast<cudaStream_t>(stream), 1, 
       t, data_offset_bytes, sync_offset_bytes, rank, world, (int)cols, static_cast<uint4*>(out_bf16), ctx->d_status);
   return check_launch("tp_allreduce_sum_kernel");
 }
@@ -299,15 +307,15 @@ int xaxb_tp_allreduce_sum_rmsnorm(xaxb_ctx* ctx_, void* stream, void* const* pee
   const uint4* wp = static_cast<const uint4*>(weight_bf16);
   uint2* qp = static_cast<uint2*>(q_e4m3);
   if (vpt == 1)
-    tp_allreduce_sum_norm_kernel<1><<<(unsigned)rows, 256, 0, s>>>(t, data_offset_bytes, sync_offset_bytes, rank, world,
+    launch_kernel(tp_allreduce_sum_norm_kernel<1>, dim3((unsigned)rows), dim3(256), 0, s, 1, t, data_offset_bytes, sync_offset_bytes, rank, world,
                                                                  vec, xo, wp, eps, qp, row_scale, row_inv_scale,
                                                                  ctx->d_status);
   else if (vpt == 2)
-    tp_allreduce_sum_norm_kernel<2><<<(unsigned)rows, 256, 0, s>>>(t, data_offset_bytes, sync_offset_bytes, rank, world,
+    launch_kernel(tp_allreduce_sum_norm_kernel<2>, dim3((unsigned)rows), dim3(256), 0, s, 1, t, data_offset_bytes, sync_offset_bytes, rank, world,
                                                                  vec, xo, wp, eps, qp, row_scale, row_inv_scale,
                                                                  ctx->d_status);
   else
-    tp_allreduce_sum_norm_kernel<4><<<(unsigned)rows, 256, 0, s>>>(t, data_offset_bytes, sync_offset_bytes, rank, world,
+    launch_kernel(tp_allreduce_sum_norm_kernel<4>, dim3((unsigned)rows), dim3(256), 0, s, 1, t, data_offset_bytes, sync_offset_bytes, rank, world,
                                                                  vec, xo, wp, eps, qp, row_scale, row_inv_scale,
                                                                  ctx->d_status);
   return check_launch("tp_allreduce_sum_norm_kernel");
@@ -332,7 +340,7 @@ int xaxb_tp_argmax(xaxb_ctx* ctx_, void* stream, void* const* peer_bases, int ra
   }
   const Ctx* ctx = reinterpret_cast<const Ctx*>(ctx_);
   const unsigned threads = (unsigned)((rows + 31) / 32 * 32);
-  tp_argmax_kernel<<<1, threads, 0, static_cast<cudaStream_t>(stream)>>>(
+  launch_kernel(tp_argmax_kernel, dim3(1), dim3(threads), 0, static_cast<cudaStream_t>(stream), 1, 
       t, inbox_offset_bytes, sync_offset_bytes, rank, world, (int)rows, (int)slice, part_max, part_idx, out,
       ctx->d_status);
   return check_launch("tp_argmax_kernel");
@@ -354,7 +362,7 @@ int xaxb_tp_allreduce_max_f32(xaxb_ctx* ctx_, void* stream, void* const* peer_ba
   }
   const Ctx* ctx = reinterpret_cast<const Ctx*>(ctx_);
   const unsigned threads = (unsigned)((n + 31) / 32 * 32) < 32u ? 32u : (unsigned)((n + 31) / 32 * 32);
-  tp_allreduce_max_kernel<<<1, threads, 0, static_cast<cudaStream_t>(stream)>>>(
+  launch_kernel(tp_allreduce_max_kernel, dim3(1), dim3(threads), 0, static_cast<cudaStream_t>(stream), 1, 
       t, inbox_offset_bytes, sync_offset_bytes, rank, world, (int)n, in, out, ctx->d_status);
   return check_launch("tp_allreduce_max_kernel");
 }

@@ -366,7 +366,7 @@ def attn_decode_cast(q_rot, k_cache, v_cache, positions, *, scale=None, k_is_rot
     scale inside the merge pass.  Returns (out bf16 or None, q e4m3 [B, Hq*D], row_scale, row_inv_scale)."""
     B, Hq, D = q_rot.shape
     _, max_len, Hkv, _ = k_cache.shape
-    ctx, st, lib = _c(1)  # the attention kernel merges and casts by itself
+    ctx, st, lib = _c(2)
     if workspace is None:
         workspace = attn_decode_workspace(B, Hq, D, max_len, q_rot.device)
     out = torch.empty_like(q_rot) if want_out else None
@@ -389,7 +389,7 @@ def attn_decode_cast_tp(q_rot, k_cache, v_cache, positions, peer, *, scale=None,
     peer mappings, rank, world, inbox offset, flag offset).  Returns (q e4m3 [B, Hq*D], scale, inv_scale)."""
     B, Hq, D = q_rot.shape
     _, max_len, Hkv, _ = k_cache.shape
-    ctx, st, lib = _c(1)  # the attention kernel merges and casts by itself
+    ctx, st, lib = _c(2)
     if workspace is None:
         workspace = attn_decode_workspace(B, Hq, D, max_len, q_rot.device)
     q = torch.empty((B, Hq * D), dtype=E4M3, device=q_rot.device)
