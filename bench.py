@@ -297,6 +297,8 @@ def main() -> None:
         if os.environ.get("XAXB_TP_EXCHANGE", "peer") != "nccl":
             tp.enable_peer_exchange(dev, rows=w["batch"], cols=w["hidden"])
         base["config"]["tp_exchange"] = "peer-memory kernels" if tp.peer is not None else "nccl"
+    base["config"]["launch"] = ("stream-ordered" if world > 1 or os.environ.get("XAXB_PROGRAMMATIC_LAUNCH", "1")[:1] == "0"
+                                else "programmatic dependent launch")
     B, T0 = w["batch"], w["prompt"]
     K = args.steps
     max_len = (T0 + warmup + K + 8 + 127) // 128 * 128
