@@ -281,7 +281,7 @@ def main() -> None:
         dist.init_process_group("nccl", device_id=dev)
         from xax_b200.parallel import TensorParallel
 
-        tp = TensorParallel(rank, world)
+        tp = TensorParallel(rank, world, local_amax=os.environ.get("XAXB_TP_AMAX", "global") == "local")
     from xax_b200 import _lib, ops
     from xax_b200.arch.llm import LLM, DecodeState, LLMConfig, tie_embedding_and_head
 
@@ -297,6 +297,8 @@ def main() -> None:
         if os.environ.get("XAXB_TP_EXCHANGE", "peer") != "nccl":
             tp.enable_peer_exchange(dev, rows=w["batch"], cols=w["hidden"])
         base["config"]["tp_exchange"] = "peer-memory kernels" if tp.peer is not None else "nccl"
+        base["config"]["tp_amax"] = ("per-rank slice (deviation from the reference)" if tp.local_amax
+                                     else "max over ranks (the reference's per-token scale)")
     base["config"]["launch"] = ("stream-ordered" if world > 1 or os.environ.get("XAXB_PROGRAMMATIC_LAUNCH", "1")[:1] == "0"
                                 else "programmatic dependent launch")
     B, T0 = w["batch"], w["prompt"]

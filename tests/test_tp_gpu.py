@@ -121,7 +121,21 @@ def _worker(rank: int, world: int, port: int, results):
             seq2.append(st2.replay().clone())
         _lib.device_status()
         peer_same = all(bool(torch.equal(a, b)) for a, b in zip(seq, seq2))
+        # per-rank-slice scaling (opt-in deviation): still the projection's output, to FP8 accuracy
+        tp3 = TensorParallel(rank, world, local_amax=True)
+        tp3.peer = tp2.peer
+        y_loc, _ = tp3.block_forward(m.blocks[0], x, B, T)
+        err_local = float((y_loc.float() - y_1.float()).norm() / y_1.float().norm())
+        xd = x[:B].contiguous()
+        cache_a = m.blocks[0].self_attn.init_cache(16, batch=B, device=dev)
+        cache_b = m.blocks[0].self_attn.init_cache(16, batch=B, device=dev)
+        if tp2.peer.exchanges & 1:
+            tp2.all_reduce_sum(tp2.partial_out(B, 512).zero_())
+        yd_g, _ = tp2.block_forward(m.blocks[0], xd, B, 1, cache=cache_a)
+        yd_l, _ = tp3.block_forward(m.blocks[0], xd, B, 1, cache=cache_b)
+        err_local_decode = float((yd_l.float() - yd_g.float()).norm() / yd_g.float().norm())
         results[rank] = dict(err=err, same_bytes=same_bytes, agree=agree, consistent=consistent, max_ok=max_ok,
+                             err_local=err_local, err_local_decode=err_local_decode,
                              sum_ok=sum_ok, peer_same=peer_same, fused_ok=fused_ok)
     except Exception:  # noqa: BLE001
         import traceback
@@ -153,4 +167,7 @@ def test_tensor_parallel_two_gpus_matches_one_gpu():
         assert res[r]["agree"] >= 0.5, res[r]
         # peer-memory exchange: exact maximum, rank-ordered float32 sum, and (two ranks: one rounding of
         # a + b either way) the same greedy tokens as the NCCL run, prefill and three replayed steps
+        # per-rank-slice scales put the e4m3 grid elsewhere than the unsharded model's: the block output moves
+        # by FP8 rounding noise (the reference's own two executions of one block differ by 7e-2)
+        assert res[r]["err_local"] < 6e-2 and res[r]["err_local_decode"] < 6e-2, res[r]
         assert res[r]["max_ok"] and res[r]["sum_ok"] and res[r]["fused_ok"] and res[r]["peer_same"], res[r]

@@ -147,8 +147,15 @@ class PeerExchange:
 class TensorParallel:
     """Collectives and the tensor-parallel forward of one transformer block."""
 
-    def __init__(self, rank: int, size: int, group=None):
+    def __init__(self, rank: int, size: int, group=None, local_amax: bool = False):
+        """``local_amax=False`` (default) keeps the reference's numerics: the activations feeding the
+        row-parallel FP8 layers are cast with the amax of the WHOLE row, max-reduced over the ranks, so
+        their e4m3 bytes equal the unsharded model's.  ``local_amax=True`` casts each rank's slice with
+        the slice's own amax (the partial products are dequantised per rank, so the sum is still the
+        projection's output, at a finer scaling granularity than the reference's): two of the four
+        exchanges per block disappear.  It is a deviation from the reference and is never the default."""
         self.rank, self.size, self.group = rank, size, group
+        self.local_amax = bool(local_amax)
         self.peer: PeerExchange | None = None
         if size > 1 and torch.cuda.is_available():
             # Kernels that wait for other GPUs do not mix well with successors that are scheduled
@@ -299,9 +306,11 @@ class TensorParallel:
         if x_q is None:
             _, yq = ops.rmsnorm(x, block.attn_norm.weight_bf16(), block.attn_norm.eps, want_y=False, quantize=True)
             x_q = (yq[0], yq[2])
-        fused = T == 1 and self._peer_fits(B, x.shape[1])  # amax exchanges inside the producing kernels
+        local = self.local_amax
+        fused = T == 1 and not local and self._peer_fits(B, x.shape[1])  # amax exchanges inside the producers
         part, new_cache = attn.forward_tokens(x, B, T, cache=cache, y_q=x_q, residual=x if first else None,
-                                              workspace=workspace, advance=advance, reduce_amax=self.all_reduce_max,
+                                              workspace=workspace, advance=advance,
+                                              reduce_amax=None if local else self.all_reduce_max,
                                               out=self.partial_out(B * T, x.shape[1]),
                                               peer_site=self.peer.attn_site() if fused else None)
         wq, col, bias = ff.fused_gate_up()
@@ -316,6 +325,12 @@ class TensorParallel:
         gu = ops.gemm_fp8(q, wq, inv, col, bias)
         if fused:
             hq, _, h_inv = ops.silu_mul_cast_tp(gu, F, self.peer.silu_site())
+        elif local and T == 1:
+            _, (hq, _, h_inv) = ops.silu_mul(gu, F, want_h=False, quantize=True)
+        elif local:
+            hmax = torch.zeros((B,), dtype=torch.float32, device=x.device)
+            h, _ = ops.silu_mul(gu, F, group_amax=hmax, group_rows=T)
+            hq, _, h_inv = ops.quantize_with_amax(h, hmax, T)
         else:
             hmax = torch.zeros((B,), dtype=torch.float32, device=x.device)
             h, _ = ops.silu_mul(gu, F, group_amax=hmax, group_rows=T)
