@@ -2,13 +2,13 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload cfg5|cfg4]
 
-A step is one greedy decode step of the whole batch (BASELINE config 5: 8B-shape decoder,
+A step is one greedy decode step of the whole batch (benchmark config 5: 8B-shape decoder,
 FP8 linears, batch 128, prompt 2048; config 4: 1.1B shape, batch 64, prompt 512).  The KV
 cache is filled by a real prefill before the timed region.  Rank 0 prints ONE JSON line:
 tokens/s device-timed over K CUDA-graph replays (`value`), the same through the host-facing
 step API with pinned host token buffers (`e2e`), the roofline of the dominant kernel (decode
 attention), the CPU oracle timed on a bounded sample (`cpu_baseline`), SM clocks sampled
-during the timed region, and per-kernel figures for BASELINE configs 1 and 3 (`kernels`).
+during the timed region, and per-kernel figures for benchmark configs 1 and 3 (`kernels`).
 With N > 1 (torchrun) the model is tensor-parallel over N GPUs: strong scaling.
 """
 
@@ -139,7 +139,7 @@ def host_threads() -> int:
 
 
 # ---------------------------------------------------------------------------------------
-# per-kernel figures (BASELINE configs 1 and 3)
+# per-kernel figures (benchmark configs 1 and 3)
 
 
 def _time_kernel(fn, iters=20, warm=3, flush=None):

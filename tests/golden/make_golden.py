@@ -5,7 +5,7 @@
 The reference (JAX) cannot run in this environment and its own tests hold no golden values
 for this path, so these vectors pin the ORACLE (oracle/), not the reference: they keep the
 oracle from drifting unnoticed and give the GPU tests byte-level targets that do not need the
-oracle's code at hand.  Inputs are seeded NumPy draws with BASELINE.json's distributions at
+oracle's code at hand.  Inputs are seeded NumPy draws with the benchmark's distributions at
 reduced sizes.
 """
 
@@ -29,7 +29,7 @@ def u16(a):
 
 
 def fp8_linear_cfg1_reduced():
-    """BASELINE config 1 at M=64, K=256, N=128: delayed scaling with a 16-deep pre-filled history."""
+    """benchmark config 1 at M=64, K=256, N=128: delayed scaling with a 16-deep pre-filled history."""
     x, w, b, rng = cfg1_inputs(M=64, K=256, N=128, seed=0)
     hist = np.zeros(16, np.float32)
     for _ in range(16):
@@ -53,7 +53,7 @@ def fp8_linear_cfg1_reduced():
 
 
 def rope_and_decode_attention():
-    """RoPE table rows (theta 5e5, D=128) and a reduced BASELINE config 3: B=3, 8q/2kv heads."""
+    """RoPE table rows (theta 5e5, D=128) and a reduced benchmark config 3: B=3, 8q/2kv heads."""
     rope = oattn.RotaryEmbedding(128, 500000.0, "concatenated")
     pos = np.array([0, 1, 2, 255, 256, 257, 513, 1023, 4097, 8191], np.int32)
     cos, sin = rope.get_rotary_embeddings(pos, bf16)

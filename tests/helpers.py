@@ -38,7 +38,7 @@ def rel_fro(a, b) -> float:
 
 
 def cfg1_inputs(M=2048, K=2048, N=8192, seed=0):
-    """BASELINE config 1 distributions: x ~ N(0,1) with 0.1 % of entries x20, W ~ N(0, 0.02^2)
+    """benchmark config 1 distributions: x ~ N(0,1) with 0.1 % of entries x20, W ~ N(0, 0.02^2)
     stored (N, K), bias ~ N(0, 0.01^2); all bf16."""
     rng = np.random.default_rng(seed)
     x = rng.standard_normal((M, K)).astype(np.float32)

@@ -14,7 +14,7 @@ from helpers import bf16, cfg1_inputs, e4m3, f32, rel_fro, to_numpy, to_torch
 
 pytestmark = pytest.mark.gpu
 
-TOL_REF = 1e-2      # vs the oracle's QDQ / strict-bf16 path (BASELINE north_star)
+TOL_REF = 1e-2      # vs the oracle's QDQ / strict-bf16 path (the stated tolerance of the path)
 TOL_SELF = 2e-3     # vs a float32 restatement of the kernel's own arithmetic
 
 
@@ -80,7 +80,7 @@ def test_quantize_special_values(ops, ofp8):
 
 @pytest.mark.parametrize("hist_len", [16, 1024])
 def test_quantize_delayed_matches_oracle(ops, ofp8, hist_len):
-    """BASELINE config 1's scaling: history pre-filled from seeded draws, quantise with the
+    """benchmark config 1's scaling: history pre-filled from seeded draws, quantise with the
     incoming scale, new history / scale bit-exact."""
     x, w, _, rng = cfg1_inputs(M=256, K=512, N=128)
     hist = np.zeros(hist_len, np.float32)
@@ -240,7 +240,7 @@ def test_gemm_bf16(ops, M, N, K):
 
 
 def test_fp8_linear_cfg1_reduced_vs_oracle(ops, ofp8):
-    """Reduced BASELINE config 1 (M=256, K=2048, N=512), delayed scaling: quantised bytes exact,
+    """Reduced benchmark config 1 (M=256, K=2048, N=512), delayed scaling: quantised bytes exact,
     output within 1e-2 of the oracle's QDQ path."""
     x, w, bias, rng = cfg1_inputs(M=256, K=2048, N=512)
     layer = ofp8.Fp8Linear(w, bias)

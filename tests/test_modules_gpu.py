@@ -91,7 +91,7 @@ def test_fp8_free_functions():
 @pytest.mark.parametrize("fp8_attn,fp8_mlp,T,start", [(True, True, 160, 0), (True, False, 40, 0), (False, False, 130, 0),
                                                       (True, True, 1, 37)])
 def test_transformer_block_vs_oracle(fp8_attn, fp8_mlp, T, start):
-    """A reduced BASELINE config 2: pre-norm block, GQA 8/2 heads x 64, SwiGLU, RoPE, prefill
+    """A reduced benchmark config 2: pre-norm block, GQA 8/2 heads x 64, SwiGLU, RoPE, prefill
     (and one decode step at a non-zero position) of B = 2 sequences."""
     from oracle.attention import build_block
 
@@ -245,7 +245,7 @@ def _oracle_pass(om, toks):
 
 
 def test_llm_reduced_cfg4_layerwise_and_logits():
-    """Reduced BASELINE config 4 (4 layers, hidden 512, 8/2 heads x 64, SwiGLU 1408, vocab 2048).
+    """Reduced benchmark config 4 (4 layers, hidden 512, 8/2 heads x 64, SwiGLU 1408, vocab 2048).
 
     Every FP8 cast is discontinuous, so two correct FP8 pipelines that differ in the last bit of
     one GEMM output drift apart over chained layers: the reference's own two executions of this
