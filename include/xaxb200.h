@@ -278,6 +278,15 @@ int xaxb_attn_check(xaxb_ctx* ctx, void* stream, const void* q_rot_bf16, const v
                     const void* v_cache_bf16, const int32_t* positions, int64_t B, int64_t T, int64_t Hq, int64_t Hkv,
                     int64_t D, int64_t max_len, float softmax_scale, void* out_bf16);
 
+/* Rotary embedding on its own (RotaryEmbedding.apply_rotary_embeddings / _apply_rotary_4d,
+ * xax/arch/attention.py:443-526): x and out bf16 [rows, heads, D], row r rotated with row
+ * positions[r] of the cos / sin tables (bf16 [table_len, D/2]); interleaved = 0 is the
+ * "concatenated" (LLaMA) style, 1 the "interleaved" (GPT-NeoX) style.  bf16 arithmetic in the
+ * reference's op order; a position outside the table sets XAXB_CACHE_OVERFLOW. */
+int xaxb_rope_apply(xaxb_ctx* ctx, void* stream, const void* x_bf16, int64_t rows, int64_t heads, int64_t D,
+                    const int32_t* positions, const void* cos_bf16, const void* sin_bf16, int64_t table_len,
+                    int interleaved, void* out_bf16);
+
 /* positions[b] += delta for b < B (the reference's new_position = p + seq_len,
  * xax/arch/attention.py:888), kept on the device so a captured decode step can replay. */
 int xaxb_advance_positions(xaxb_ctx* ctx, void* stream, int32_t* positions, int64_t B, int32_t delta);

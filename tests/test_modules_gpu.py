@@ -290,3 +290,120 @@ def test_llm_reduced_cfg4_layerwise_and_logits():
           f"oracle vs oracle {oo:.3e}")
     # no further from either execution of the reference than they are from each other (+25 %)
     assert max(errs) < 0.1 and e_fp8 < 1.25 * oo and e_qdq < 1.25 * oo
+
+
+@pytest.mark.parametrize("style", ["concatenated", "interleaved"])
+def test_rotary_embedding_methods_match_oracle_bit_for_bit(style):
+    """RotaryEmbedding.apply_rotary_embeddings / _apply_rotary_4d / _get_rotary_embeddings, both styles,
+    default and explicit positions (position 257 rounds to 256 in bf16, there and here)."""
+    from oracle import attention as oattn
+    from xax_b200.arch.attention import RotaryEmbedding
+
+    rng = np.random.default_rng(5)
+    T, H, D = 300, 3, 64
+    x = bf16(rng.standard_normal((T, H, D), dtype=np.float32))
+    orope = oattn.RotaryEmbedding(D, base=10000.0, style=style)
+    rope = RotaryEmbedding.build(D, base=10000.0, style=style)
+    exp = orope.apply_rotary_embeddings(x)
+    got = rope.apply_rotary_embeddings(to_torch(x))
+    assert np.array_equal(to_numpy(got).view(np.uint16), np.asarray(exp).view(np.uint16))
+    pos = np.array([0, 1, 255, 256, 257, 258, 1000, 7], dtype=np.int32)
+    exp_p = orope.apply_rotary_embeddings(x[:8], pos.astype(x.dtype))
+    got_p = rope.apply_rotary_embeddings(to_torch(x[:8]), torch.from_numpy(pos).cuda())
+    assert np.array_equal(to_numpy(got_p).view(np.uint16), np.asarray(exp_p).view(np.uint16))
+    # 4-D: (batch, seq, heads, head_dim) with per-sequence positions
+    x4 = x[:24].reshape(2, 12, H, D)
+    pos4 = np.stack([np.arange(12), np.arange(100, 112)]).astype(np.int32)
+    got4 = rope.apply_rotary_embeddings(to_torch(x4), torch.from_numpy(pos4).cuda())
+    exp4 = np.stack([np.asarray(orope.apply_rotary_embeddings(x4[b], pos4[b].astype(x.dtype))) for b in range(2)])
+    assert np.array_equal(to_numpy(got4).view(np.uint16), exp4.view(np.uint16))
+    cos, sin = rope._get_rotary_embeddings(torch.from_numpy(pos).cuda())
+    ecos, esin = orope.get_rotary_embeddings(pos.astype(x.dtype), x.dtype)
+    assert np.array_equal(to_numpy(cos).view(np.uint16), np.asarray(ecos).view(np.uint16))
+    assert np.array_equal(to_numpy(sin).view(np.uint16), np.asarray(esin).view(np.uint16))
+
+
+def test_apply_linear_batched_and_greedy_sampling_helper():
+    """_apply_linear_batched (per-row current scaling; delayed scaling keeps the last row's update) and
+    _sample_next_token's greedy branch."""
+    from oracle import attention as oattn
+    from oracle import fp8 as ofp8
+    from xax_b200.arch.attention import _apply_linear_batched
+    from xax_b200.arch.llm import _sample_next_token
+    from xax_b200.nn.fp8 import Fp8Linear, init_fp8_scales
+
+    x, w, b, rng = cfg1_inputs(M=24, K=256, N=128)
+    ol = ofp8.Fp8Linear(w, b)
+    layer = Fp8Linear(256, 128, weight=to_torch(w), bias=to_torch(b))
+    x3 = x.reshape(2, 12, 256)
+    exp, es = oattn.apply_linear_batched(ol, x3)
+    got, gs = _apply_linear_batched(layer, to_torch(x3))
+    assert es is None and gs is None and got.shape == (2, 12, 128)
+    assert rel_fro(f32(to_numpy(got)), f32(exp)) < TOL
+    s0 = ofp8.init_fp8_scales(16)
+    s0 = ofp8.Fp8Scales(np.float32(4.0), s0.input_amax_history, np.float32(2000.0), s0.kernel_amax_history)
+    g0 = init_fp8_scales(16)
+    g0 = type(g0)(torch.tensor(4.0, device="cuda"), g0.input_amax_history, torch.tensor(2000.0, device="cuda"),
+                  g0.kernel_amax_history)
+    exp_d, es_d = oattn.apply_linear_batched(ol, x3, s0)
+    got_d, gs_d = _apply_linear_batched(layer, to_torch(x3), g0)
+    assert rel_fro(f32(to_numpy(got_d)), f32(exp_d)) < TOL
+    assert np.array_equal(to_numpy(gs_d.input_amax_history), es_d.input_amax_history)  # the LAST row's amax
+    assert to_numpy(gs_d.input_scale) == es_d.input_scale and to_numpy(gs_d.kernel_scale) == es_d.kernel_scale
+    logits = bf16(rng.standard_normal((5, 1000), dtype=np.float32))
+    logits[2, 10] = logits[2, 900] = 50.0  # tie: first index wins
+    tok = _sample_next_token(to_torch(logits), 0.0, 0.9)
+    assert tok.shape == (5, 1) and np.array_equal(to_numpy(tok)[:, 0], np.argmax(f32(logits), axis=-1))
+    with pytest.raises(ValueError):
+        _sample_next_token(to_torch(logits), 0.7, 0.9)
+
+
+def _write_hf_checkpoint(om, path, *, prefix="model.", transpose_o=False, tied=True):
+    """The oracle model's weights under HuggingFace names (seeded synthetic tensors, no published model)."""
+    import json
+
+    from safetensors.torch import save_file
+
+    c = om.config
+    st = {f"{prefix}embed_tokens.weight": to_torch(om.embed.weight, "cpu")}
+    for i, b in enumerate(om.blocks):
+        a, f = b.self_attn, b.feed_forward
+        for name, lin in (("q_proj", a.q_proj), ("k_proj", a.k_proj), ("v_proj", a.v_proj), ("o_proj", a.output_proj)):
+            w = to_torch(lin.weight, "cpu")
+            st[f"{prefix}layers.{i}.self_attn.{name}.weight"] = w.t().contiguous() if (transpose_o and name == "q_proj") else w
+        for name, lin in (("gate_proj", f.gate), ("up_proj", f.up), ("down_proj", f.down)):
+            st[f"{prefix}layers.{i}.mlp.{name}.weight"] = to_torch(lin.weight, "cpu")
+        st[f"{prefix}layers.{i}.input_layernorm.weight"] = to_torch(b.attn_norm.weight, "cpu")
+        st[f"{prefix}layers.{i}.post_attention_layernorm.weight"] = to_torch(b.mlp_norm.weight, "cpu")
+    st[f"{prefix}norm.weight"] = to_torch(om.norm.weight, "cpu")
+    if not tied:
+        st["lm_head.weight"] = to_torch(om.lm_head.weight, "cpu")
+    save_file({k: v.contiguous() for k, v in st.items()}, str(path / "model.safetensors"))
+    cfg = {"hidden_size": c.embed_dim, "num_attention_heads": c.q_heads, "num_key_value_heads": c.kv_heads,
+           "num_hidden_layers": c.num_layers, "vocab_size": c.vocab_size, "intermediate_size": c.mlp_hidden_dim,
+           "rope_theta": c.rope_theta, "rms_norm_eps": c.rms_eps, "head_dim": c.head_dim, "model_type": "llama"}
+    (path / "config.json").write_text(json.dumps(cfg))
+
+
+@pytest.mark.parametrize("use_fp8,tied,prefix", [(True, True, "model."), (False, False, "")])
+def test_pretrained_checkpoint_round_trip(tmp_path, use_fp8, tied, prefix):
+    """A synthetic checkpoint in the HuggingFace naming scheme loads into the same model as handing the
+    tensors over directly: logits equal bit for bit (tied and untied head, both name prefixes, a
+    transposed projection)."""
+    from oracle import llm as ollm
+    from xax_b200.arch.hf import build_pretrained_llm, hf_config_to_llm_config, load_hf_config
+
+    cfg = ollm.LLMConfig(vocab_size=256, embed_dim=128, q_heads=4, kv_heads=2, head_dim=64, num_layers=2, max_tsz=128,
+                         mlp_hidden_dim=256, rope_theta=500000.0, rms_eps=1e-5)
+    om = ollm.LLM.build(cfg, np.random.default_rng(3), use_fp8=use_fp8, tie=tied, std=0.2)
+    _write_hf_checkpoint(om, tmp_path, prefix=prefix, transpose_o=True, tied=tied)
+    parsed = hf_config_to_llm_config(load_hf_config(str(tmp_path)))
+    assert (parsed.embed_dim, parsed.q_heads, parsed.kv_heads, parsed.head_dim, parsed.mlp_hidden_dim) == (128, 4, 2, 64, 256)
+    assert parsed.rope_theta == 500000.0 and parsed.rms_eps == 1e-5 and not parsed.use_qk_norm
+    loaded = build_pretrained_llm(str(tmp_path), use_fp8=use_fp8)
+    direct = llm_from_oracle(om)
+    toks = torch.tensor([[1, 2, 3, 4, 5, 6], [9, 8, 7, 6, 5, 4]], dtype=torch.int32, device="cuda")
+    l1, _ = loaded.forward_batch(toks)
+    l2, _ = direct.forward_batch(toks)
+    assert torch.equal(l1, l2)
+    assert (loaded.lm_head.weight is loaded.embed.weight) == tied

@@ -225,3 +225,25 @@ def test_golden_toy_llm():
     toks, n = ollm.llm_generate_greedy(om, [11, 17, 23], -1, 6)
     assert np.array_equal(toks, g["tokens"]) and n == int(g["final_len"])
     assert np.array_equal(om.forward(np.array([11, 17, 23], np.int32)).view(np.uint16), g["prompt_logits"])
+
+
+def test_hf_config_parsing_defaults_and_aliases():
+    """hf_config_to_llm_config: the reference's defaults and alias names (xax/arch/llm.py:1027-1188)."""
+    import pytest
+
+    from xax_b200.arch.hf import hf_config_to_llm_config
+
+    c = hf_config_to_llm_config({"n_embd": 512, "n_head": 8, "n_layer": 3, "vocab_size": 1000})
+    assert (c.embed_dim, c.q_heads, c.kv_heads, c.head_dim, c.num_layers) == (512, 8, 4, 64, 3)
+    assert c.mlp_hidden_dim == 2048 and c.mlp_mult == 4 and c.rope_theta == 10000.0 and c.rms_eps == 1e-6
+    assert not c.attention_bias and not c.mlp_bias and not c.use_qk_norm and not c.uses_yarn
+    q = hf_config_to_llm_config({"hidden_size": 1024, "num_attention_heads": 16, "num_key_value_heads": 8, "head_dim": 128,
+                                 "num_hidden_layers": 2, "vocab_size": 5, "intermediate_size": 3072, "model_type": "qwen3",
+                                 "rope_theta": 1e6, "rms_norm_eps": 1e-6, "attention_bias": True,
+                                 "rope_scaling": {"rope_type": "yarn", "factor": 4.0,
+                                                  "original_max_position_embeddings": 32768}})
+    assert q.head_dim == 128 and q.use_qk_norm and q.attention_bias and q.mlp_mult == 3
+    assert q.uses_yarn and q.rope_factor == 4.0 and q.rope_original_max_position_embeddings == 32768
+    assert q.rope_beta_slow == 1.0 and q.rope_beta_fast == 32.0
+    with pytest.raises(ValueError, match="hidden_size"):
+        hf_config_to_llm_config({"num_attention_heads": 8, "num_hidden_layers": 1, "vocab_size": 10})

@@ -21,10 +21,11 @@ NAME_MAP = {
     "LLM": "arch.llm", "LLMConfig": "arch.llm", "llm_generate": "arch.llm", "llm_generate_jit": "arch.llm",
     "llm_generate_batch": "arch.llm", "tie_embedding_and_head": "arch.llm",
     "get_model_parallel_sharding_spec": "arch.llm", "DecodeState": "arch.llm",
+    "build_pretrained_llm": "arch.hf", "hf_config_to_llm_config": "arch.hf", "load_hf_weights_into_llm": "arch.hf",
     # xax.nn.fp8 (not re-exported by xax at top level; offered here for convenience)
     "Fp8Linear": "nn.fp8", "Fp8Scales": "nn.fp8", "init_fp8_scales": "nn.fp8", "fp8_matmul": "nn.fp8",
     # tensor parallelism
-    "setup_model_parallel_mesh": "parallel", "TensorParallel": "parallel",
+    "setup_model_parallel_mesh": "parallel", "TensorParallel": "parallel", "make_sharded_array": "parallel",
 }
 
 __all__ = sorted(NAME_MAP)

@@ -85,6 +85,21 @@ def apply_linear(x: torch.Tensor, linear, *, residual: torch.Tensor | None = Non
     raise ValueError(f"Unsupported linear layer type: {type(linear)}")
 
 
+def _apply_linear_batched(layer, x: torch.Tensor, scales=None):
+    """xax/arch/attention.py:244-287: the layer applied to every row of x on its own.  Current
+    scaling: every row gets its own scale (:279).  Delayed scaling: all rows are cast with the
+    incoming scales and the updated scales of the LAST row are returned (:273-275)."""
+    if isinstance(layer, Fp8Linear):
+        flat = x.reshape(-1, x.shape[-1])
+        if scales is not None and layer.use_fp8:
+            out, _ = layer(flat, scales)            # shared incoming scales: same bytes row by row
+            _, new_scales = layer(flat[-1:], scales)  # history slot 0 <- amax of the last row
+            return out.reshape(*x.shape[:-1], -1), new_scales
+        out, _ = layer(flat, per_row=True)
+        return out.reshape(*x.shape[:-1], -1), None
+    return apply_linear(x, layer), None  # :286
+
+
 class RMSNorm:
     """xax/arch/attention.py:72-98.  ``build`` makes a float32 weight of ones like the
     reference; the kernel runs in bf16, so the weight is cast to bf16 at use (exact for ones)."""
@@ -242,18 +257,57 @@ class RotaryEmbedding:
     def uses_yarn(self) -> bool:
         return self.factor > 1.0 and self.original_max_position_embeddings is not None
 
-    def tables(self, length: int, device):
+    def tables(self, length: int, device, any_style: bool = False):
         """(cos, sin) bf16 [>= length, head_dim / 2] on ``device`` (cached, grown on demand)."""
         if self.uses_yarn:
             raise ValueError("YaRN scaling is outside the path this library covers")
-        if self.style != "concatenated":
-            raise ValueError("the kernels implement the 'concatenated' RoPE style only")
+        if self.style != "concatenated" and not any_style:
+            raise ValueError("the attention kernels implement the 'concatenated' RoPE style only")
         key = str(device)
         cur = self._tables.get(key)
         if cur is None or cur[0].shape[0] < length:
             n = max(length, 256)
             self._tables[key] = cur = ops.rope_tables(self.head_dim, self.base, n, device)
         return cur
+
+
+    def _get_rotary_embeddings(self, positions: torch.Tensor, dtype=BF16):
+        """xax/arch/attention.py:374-399: (cos, sin) [n, head_dim / 2] for integer positions [n]
+        (rows of the table, which is built in the reference's bf16 op order)."""
+        if dtype != BF16:
+            raise ValueError("the tables are built for bf16 activations (the compute dtype of this path)")
+        pos = positions.reshape(-1).to(torch.int64)
+        n = int(pos.max().item()) + 1 if pos.numel() else 1
+        cos, sin = self.tables(n, positions.device, any_style=True)
+        return cos.index_select(0, pos), sin.index_select(0, pos)
+
+    def apply_rotary_embeddings(self, x: torch.Tensor, positions: torch.Tensor | None = None) -> torch.Tensor:
+        """xax/arch/attention.py:443-483: x (seq_len, heads, head_dim) or (batch, seq_len, heads,
+        head_dim); positions (seq_len,) / (batch, seq_len) integers, default 0 .. seq_len-1."""
+        if x.dim() == 4:
+            bsz, seq_len = x.shape[:2]
+            if positions is None:
+                positions = torch.arange(seq_len, device=x.device, dtype=torch.int32)[None, :].expand(bsz, seq_len)
+            return self._apply_rotary_4d(x, positions)
+        if x.dim() != 3:
+            raise ValueError(f"expected a 3-D or 4-D tensor, got shape {tuple(x.shape)}")
+        seq_len, _, head_dim = x.shape
+        assert head_dim == self.head_dim, f"Expected head_dim {self.head_dim}, got {head_dim}"  # :468
+        if self.style not in ("concatenated", "interleaved"):
+            raise ValueError(f"Unknown RoPE style: {self.style}. Use 'concatenated' or 'interleaved'.")  # :483
+        if positions is None:
+            positions = torch.arange(seq_len, device=x.device, dtype=torch.int32)
+        pos = positions.reshape(-1).to(torch.int32).contiguous()
+        n = int(pos.max().item()) + 1 if pos.numel() else 1
+        cos, sin = self.tables(n, x.device, any_style=True)
+        return ops.rope_apply(x.to(BF16).contiguous(), pos, cos, sin, interleaved=self.style == "interleaved")
+
+    def _apply_rotary_4d(self, x: torch.Tensor, positions: torch.Tensor) -> torch.Tensor:
+        """xax/arch/attention.py:485-508."""
+        bsz, seq_len, heads, head_dim = x.shape
+        assert head_dim == self.head_dim  # :488
+        out = self.apply_rotary_embeddings(x.reshape(bsz * seq_len, heads, head_dim), positions.reshape(-1))
+        return out.reshape(bsz, seq_len, heads, head_dim)
 
 
 class SelfAttentionBlock:

@@ -375,6 +375,20 @@ class DecodeState:
         return tokens_out
 
 
+def _sample_next_token(logits_tv: torch.Tensor, temperature: float, top_p: float, key=None, num_samples: int = 1):
+    """xax/arch/llm.py:1446-1489 for the greedy case (``temperature <= 0``, :1469-1470 and :1489):
+    arg-max over the vocabulary in float32, first index on ties, shape (tsz, 1).  Temperature /
+    top-p sampling needs the reference's PRNG stream and is outside the path this library covers."""
+    if temperature > 0:
+        raise ValueError("temperature / top-p sampling is outside the path this library covers (greedy only)")
+    if num_samples != 1:
+        raise ValueError("greedy decoding yields one token per position")
+    if logits_tv.dtype != BF16:
+        raise ValueError("the logits of this path are bf16 (the arg-max compares them as float32)")
+    logits = logits_tv
+    return ops.argmax(logits.reshape(-1, logits.shape[-1]).contiguous()).reshape(*logits.shape[:-1], 1)
+
+
 def llm_generate_batch(model: LLM, tokens_bt: torch.Tensor, max_new_tokens: int, *, eos_id: int = -1,
                        use_graph: bool = True, prefill_chunk: int | None = None, tp=None):
     """Batched greedy generation: the loop of xax/arch/llm.py:1572-1613 for B prompts of equal

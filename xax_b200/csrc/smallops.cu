@@ -378,6 +378,33 @@ __global__ void argmax_merge_kernel(const float* __restrict__ vals, const int32_
 }
 
 // ---------------------------------------------------------------------------------------
+// RoPE on its own (xax/arch/attention.py:443-526): x [rows, heads, D] bf16, row r at position
+// positions[r].  Grid (rows, heads), D/2 threads; thread i owns pair i of the chosen style:
+// "concatenated" pairs (i, i + D/2), "interleaved" pairs (2i, 2i + 1).  Every product and
+// sum rounds to bf16, as the reference's bf16 arithmetic does.
+__global__ void rope_apply_kernel(const __nv_bfloat16* __restrict__ x, int heads, int D,
+                                  const int32_t* __restrict__ positions, const __nv_bfloat16* __restrict__ cos_t,
+                                  const __nv_bfloat16* __restrict__ sin_t, int64_t table_len, int interleaved,
+                                  __nv_bfloat16* __restrict__ out, int* d_status) {
+  pdl_trigger();
+  pdl_wait();
+  const int64_t row = blockIdx.x;
+  const int head = blockIdx.y, i = threadIdx.x, half = D / 2;
+  const int64_t pos = positions[row];
+  if (pos < 0 || pos >= table_len) {
+    if (i == 0) atomicCAS(d_status, 0, XAXB_CACHE_OVERFLOW * 1000 + 45);
+    return;
+  }
+  const int64_t base = (row * heads + head) * D;
+  const int ia = interleaved ? 2 * i : i, ib = interleaved ? 2 * i + 1 : i + half;
+  const float xa = __bfloat162float(x[base + ia]), xb = __bfloat162float(x[base + ib]);
+  const float c = __bfloat162float(cos_t[pos * half + i]), s = __bfloat162float(sin_t[pos * half + i]);
+  out[base + ia] = __float2bfloat16_rn(bf16_round(xa * c) - bf16_round(xb * s));
+  out[base + ib] = interleaved ? __float2bfloat16_rn(bf16_round(xa * s) + bf16_round(xb * c))
+                               : __float2bfloat16_rn(bf16_round(xb * c) + bf16_round(xa * s));
+}
+
+// ---------------------------------------------------------------------------------------
 // RoPE ("concatenated" halves) + cache append.  Grid (B*T, Hq + 2*Hkv); D/2 threads: thread i
 // owns the pair (i, i + D/2).  out1 = bf16(bf16(x1*c) - bf16(x2*s)), out2 = bf16(bf16(x2*c) + bf16(x1*s)).
 
@@ -685,6 +712,25 @@ int xaxb_kv_append_rope(xaxb_ctx* ctx, void* stream, const void* qkv_bf16, int64
       static_cast<__nv_bfloat16*>(q_rot_bf16), static_cast<__nv_bfloat16*>(k_cache_bf16),
       static_cast<__nv_bfloat16*>(v_cache_bf16), max_len, store_rotated_k, c->d_status);
   return check_launch("kv_append_rope_kernel");
+}
+
+int xaxb_rope_apply(xaxb_ctx* ctx, void* stream, const void* x_bf16, int64_t rows, int64_t heads, int64_t D,
+                    const int32_t* positions, const void* cos_bf16, const void* sin_bf16, int64_t table_len,
+                    int interleaved, void* out_bf16) {
+  if (!ctx || !x_bf16 || !positions || !cos_bf16 || !sin_bf16 || !out_bf16 || rows <= 0 || heads <= 0 ||
+      table_len <= 0)
+    return XAXB_BAD_ARGUMENT;
+  if (D % 2 != 0 || D < 2 || D > 2048 || heads > 65535) {
+    set_last_error("rope_apply: head_dim %lld / heads %lld not supported", (long long)D, (long long)heads);
+    return XAXB_UNSUPPORTED;
+  }
+  Ctx* c = reinterpret_cast<Ctx*>(ctx);
+  dim3 grid((unsigned)rows, (unsigned)heads);
+  launch_kernel(rope_apply_kernel, grid, dim3((unsigned)(D / 2)), 0, static_cast<cudaStream_t>(stream), 1,
+                static_cast<const __nv_bfloat16*>(x_bf16), (int)heads, (int)D, positions,
+                static_cast<const __nv_bfloat16*>(cos_bf16), static_cast<const __nv_bfloat16*>(sin_bf16), table_len,
+                interleaved, static_cast<__nv_bfloat16*>(out_bf16), c->d_status);
+  return check_launch("rope_apply_kernel");
 }
 
 int xaxb_advance_positions(xaxb_ctx* ctx, void* stream, int32_t* positions, int64_t B, int32_t delta) {

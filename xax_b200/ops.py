@@ -321,6 +321,17 @@ def rope_tables(head_dim: int, base: float, length: int, device=None):
     return to_torch(cos), to_torch(sin)
 
 
+def rope_apply(x, positions, cos, sin, *, interleaved: bool = False):
+    """Rotary embedding of x bf16 [rows, heads, D] at int32 positions [rows]."""
+    x = _req(x, BF16, "x")
+    rows, heads, D = x.shape
+    out = torch.empty_like(x)
+    ctx, st, lib = _c()
+    check(lib.xaxb_rope_apply(ctx, st, ptr(x), rows, heads, D, ptr(positions), ptr(cos), ptr(sin), cos.shape[0],
+                              1 if interleaved else 0, ptr(out)), "rope_apply")
+    return out
+
+
 def kv_append_rope(qkv, B, T, Hq, Hkv, D, positions, cos, sin, k_cache, v_cache, *, store_rotated_k=True, q_rot=None):
     """RoPE on q and k of the fused projection output, K/V written into the cache at
     positions[b] .. +T-1.  Returns q_rot [B*T, Hq, D]."""

@@ -53,6 +53,14 @@ def shard_weight(weight: torch.Tensor, weight_name: str, rank: int, size: int) -
     return weight.narrow(dim, rank * n, n).contiguous()
 
 
+def make_sharded_array(arr: torch.Tensor, weight_name: str, rank: int, size: int, device=None) -> torch.Tensor:
+    """What the checkpoint loader's ``make_sharded_array`` (xax/arch/llm.py:1244-1265) hands one
+    device: this rank's slice of ``arr`` under the placement rule, or all of it when the rule
+    replicates the tensor."""
+    out = shard_weight(arr, weight_name, rank, size) if size > 1 else arr
+    return out.to(device) if device is not None else out
+
+
 class PeerExchange:
     """One symmetric buffer per rank, mapped by every rank of the box, laid out as
     [flag regions | amax inboxes | arg-max inbox and flags | data 0 | data 1], and the kernels that exchange through
