@@ -278,6 +278,13 @@ int xaxb_attn_check(xaxb_ctx* ctx, void* stream, const void* q_rot_bf16, const v
                     const void* v_cache_bf16, const int32_t* positions, int64_t B, int64_t T, int64_t Hq, int64_t Hkv,
                     int64_t D, int64_t max_len, float softmax_scale, void* out_bf16);
 
+/* QK-norm (xax/arch/attention.py:864-867, the Qwen3 family): RMSNorm over head_dim of every query
+ * and key head, in place on the fused projection output qkv [rows, (Hq + 2 Hkv) * D] (row stride
+ * ld elements), to be called before xaxb_kv_append_rope.  Weights bf16 [D]; either may be NULL to
+ * leave that side alone. */
+int xaxb_qk_norm(xaxb_ctx* ctx, void* stream, void* qkv_bf16, int64_t ld, int64_t rows, int64_t Hq, int64_t Hkv,
+                 int64_t D, const void* q_weight_bf16, const void* k_weight_bf16, float eps);
+
 /* Rotary embedding on its own (RotaryEmbedding.apply_rotary_embeddings / _apply_rotary_4d,
  * xax/arch/attention.py:443-526): x and out bf16 [rows, heads, D], row r rotated with row
  * positions[r] of the cos / sin tables (bf16 [table_len, D/2]); interleaved = 0 is the

@@ -233,13 +233,14 @@ def dot_product_attention(q, k, v, *, mask=None, is_causal=False, scale=None):
 
 class SelfAttentionBlock:
     """xax/arch/attention.py:529-980 restricted to the path: GQA, optional RoPE, causal,
-    KV cache; no QK-norm, sinks or sliding window."""
+    KV cache, optional QK-norm (:864-867); no sinks or sliding window."""
 
     def __init__(self, q_proj, k_proj, v_proj, output_proj, rotary_emb, *, num_heads, num_kv_heads, head_dim,
-                 causal=True):
+                 causal=True, q_norm=None, k_norm=None):
         assert num_heads % num_kv_heads == 0  # :620
         self.q_proj, self.k_proj, self.v_proj, self.output_proj = q_proj, k_proj, v_proj, output_proj
         self.rotary_emb = rotary_emb
+        self.q_norm, self.k_norm = q_norm, k_norm
         self.num_heads, self.num_kv_heads, self.head_dim = num_heads, num_kv_heads, head_dim
         self.causal = causal
 
@@ -261,6 +262,10 @@ class SelfAttentionBlock:
         q = q.reshape(T, self.num_heads, self.head_dim)
         k = k.reshape(T, self.num_kv_heads, self.head_dim)
         v = v.reshape(T, self.num_kv_heads, self.head_dim)
+        if self.q_norm is not None:  # :864-867, per head, before RoPE
+            q = self.q_norm(q)
+        if self.k_norm is not None:
+            k = self.k_norm(k)
         start = int(cache["position"]) if cache is not None else 0
         if self.rotary_emb is not None:  # :870-878
             positions = (np.arange(T) + start).astype(np.int32)
@@ -311,7 +316,8 @@ class TransformerBlock:
 
 
 def build_block(rng, *, embed_dim, num_heads, num_kv_heads, head_dim, ff_dim, rope_theta=10000.0, norm_eps=1e-6,
-                fp8_attn=True, fp8_mlp=True, out_scale=1.0, std=0.02, dtype=bfloat16, attn_bias=False):
+                fp8_attn=True, fp8_mlp=True, out_scale=1.0, std=0.02, dtype=bfloat16, attn_bias=False,
+                use_qk_norm=False, qk_norm_eps=1e-6):
     """Random block with N(0, std^2) weights; output projections scaled by ``out_scale``.
     FP8 projections are Fp8Linear instances (as xax/arch/attention.py:233-240 builds for
     attention; for the MLP they are swapped into SwiGLU, which apply_linear accepts :52)."""
@@ -328,7 +334,10 @@ def build_block(rng, *, embed_dim, num_heads, num_kv_heads, head_dim, ff_dim, ro
         lin(qd, embed_dim, fp8_attn, bias=attn_bias), lin(kd, embed_dim, fp8_attn, bias=attn_bias),
         lin(kd, embed_dim, fp8_attn, bias=attn_bias), lin(embed_dim, qd, fp8_attn, out_scale, bias=attn_bias),
         RotaryEmbedding(head_dim, base=rope_theta, style="concatenated"),
-        num_heads=num_heads, num_kv_heads=num_kv_heads, head_dim=head_dim, causal=True)
+        num_heads=num_heads, num_kv_heads=num_kv_heads, head_dim=head_dim, causal=True,
+        # :665-669 builds ones; seeded weights around one make the test see them
+        q_norm=RMSNorm((1 + 0.1 * rng.standard_normal(head_dim, dtype=float32)).astype(dtype), qk_norm_eps) if use_qk_norm else None,
+        k_norm=RMSNorm((1 + 0.1 * rng.standard_normal(head_dim, dtype=float32)).astype(dtype), qk_norm_eps) if use_qk_norm else None)
     ff = SwiGLU(lin(ff_dim, embed_dim, fp8_mlp), lin(ff_dim, embed_dim, fp8_mlp),
                 lin(embed_dim, ff_dim, fp8_mlp, out_scale))
     return TransformerBlock(attn, ff, RMSNorm.build(embed_dim, norm_eps, dtype), RMSNorm.build(embed_dim, norm_eps, dtype))

@@ -358,7 +358,7 @@ def test_apply_linear_batched_and_greedy_sampling_helper():
         _sample_next_token(to_torch(logits), 0.7, 0.9)
 
 
-def _write_hf_checkpoint(om, path, *, prefix="model.", transpose_o=False, tied=True):
+def _write_hf_checkpoint(om, path, *, prefix="model.", transpose_o=False, tied=True, qk_norm=False):
     """The oracle model's weights under HuggingFace names (seeded synthetic tensors, no published model)."""
     import json
 
@@ -378,11 +378,19 @@ def _write_hf_checkpoint(om, path, *, prefix="model.", transpose_o=False, tied=T
     st[f"{prefix}norm.weight"] = to_torch(om.norm.weight, "cpu")
     if not tied:
         st["lm_head.weight"] = to_torch(om.lm_head.weight, "cpu")
+    if qk_norm:
+        g = np.random.default_rng(99)
+        for i in range(len(om.blocks)):
+            for n in ("q_norm", "k_norm"):
+                st[f"model.layers.{i}.self_attn.{n}.weight"] = to_torch(
+                    bf16(1 + 0.1 * g.standard_normal(c.head_dim, dtype=np.float32)), "cpu")
     save_file({k: v.contiguous() for k, v in st.items()}, str(path / "model.safetensors"))
     cfg = {"hidden_size": c.embed_dim, "num_attention_heads": c.q_heads, "num_key_value_heads": c.kv_heads,
            "num_hidden_layers": c.num_layers, "vocab_size": c.vocab_size, "intermediate_size": c.mlp_hidden_dim,
-           "rope_theta": c.rope_theta, "rms_norm_eps": c.rms_eps, "head_dim": c.head_dim, "model_type": "llama"}
+           "rope_theta": c.rope_theta, "rms_norm_eps": c.rms_eps, "head_dim": c.head_dim,
+           "model_type": "qwen3" if qk_norm else "llama"}
     (path / "config.json").write_text(json.dumps(cfg))
+    return st
 
 
 @pytest.mark.parametrize("use_fp8,tied,prefix", [(True, True, "model."), (False, False, "")])
@@ -407,3 +415,72 @@ def test_pretrained_checkpoint_round_trip(tmp_path, use_fp8, tied, prefix):
     l2, _ = direct.forward_batch(toks)
     assert torch.equal(l1, l2)
     assert (loaded.lm_head.weight is loaded.embed.weight) == tied
+
+
+@pytest.mark.parametrize("fp8", [False, True])
+def test_qk_norm_block_vs_oracle_prefill_and_decode(fp8):
+    """QK-norm (xax/arch/attention.py:864-867) before RoPE: one block, prefill of 40 tokens then two cached
+    decode steps, against the oracle with the same seeded norm weights."""
+    from oracle import attention as oattn
+
+    rng = np.random.default_rng(11)
+    ob = oattn.build_block(rng, embed_dim=256, num_heads=4, num_kv_heads=2, head_dim=64, ff_dim=512, rope_theta=1e6,
+                           norm_eps=1e-6, fp8_attn=fp8, fp8_mlp=fp8, std=0.05, use_qk_norm=True)
+    blk = block_from_oracle(ob)
+    assert blk.self_attn.q_norm is not None and blk.self_attn.k_norm is not None
+    x = bf16(rng.standard_normal((42, 256), dtype=np.float32))
+    cache_o = ob.init_cache(64)
+    cache = blk.init_cache(64)
+    exp, cache_o = ob.forward(x[:40], cache=cache_o)
+    got, cache = blk.forward(to_torch(x[:40]), cache=cache)
+    # normalised q and k sharpen the softmax, which amplifies the one-step e4m3 flips that separate any two
+    # executions of chained FP8 linears (2e-2 between the reference's own two executions of two linears)
+    assert rel_fro(f32(to_numpy(got)), f32(exp)) < (TOL if not fp8 else 3e-2)
+    for t in (40, 41):
+        exp, cache_o = ob.forward(x[t:t + 1], cache=cache_o)
+        got, cache = blk.forward(to_torch(x[t:t + 1]), cache=cache)
+        assert rel_fro(f32(to_numpy(got)), f32(exp)) < (TOL if not fp8 else 3e-2)
+    # the cache holds normalised, rotated keys: compare the rows written so far
+    kc = f32(to_numpy(cache["self_attn"]["k"]))[:42]
+    assert rel_fro(kc, f32(cache_o["self_attn"]["k"])[:42]) < 5e-3
+
+
+def test_pretrained_checkpoint_with_qk_norm(tmp_path):
+    """A qwen3-style checkpoint (model_type qwen3, q_norm / k_norm weights per layer) loads with QK-norm on,
+    and the norm weights change the logits."""
+    from oracle import llm as ollm
+    from xax_b200.arch.hf import build_pretrained_llm
+
+    cfg = ollm.LLMConfig(vocab_size=256, embed_dim=128, q_heads=4, kv_heads=2, head_dim=64, num_layers=2, max_tsz=128,
+                         mlp_hidden_dim=256, rope_theta=1e6, rms_eps=1e-6)
+    om = ollm.LLM.build(cfg, np.random.default_rng(4), use_fp8=False, tie=True, std=0.2)
+    st = _write_hf_checkpoint(om, tmp_path, qk_norm=True)
+    m = build_pretrained_llm(str(tmp_path), use_fp8=False)
+    a0 = m.blocks[0].self_attn
+    assert m.config.use_qk_norm and a0.q_norm is not None and a0.k_norm is not None and a0.q_norm.eps == 1e-6
+    assert torch.equal(a0.q_norm.weight.cpu(), st["model.layers.0.self_attn.q_norm.weight"])
+    toks = torch.tensor([[1, 2, 3, 4, 5, 6]], dtype=torch.int32, device="cuda")
+    l_qk, _ = m.forward_batch(toks)
+    l_plain, _ = llm_from_oracle(om).forward_batch(toks)
+    assert l_qk.shape == l_plain.shape and not torch.equal(l_qk, l_plain)
+
+
+def test_yarn_tables_match_oracle_and_feed_the_block():
+    """YaRN (xax/arch/attention.py:401-441): tables bit-equal to the oracle's float32 computation, applied
+    through the same kernels."""
+    from oracle import attention as oattn
+    from xax_b200.arch.attention import RotaryEmbedding
+
+    kw = dict(base=1e6, style="concatenated", factor=4.0, original_max_position_embeddings=64, beta_slow=1.0, beta_fast=32.0)
+    orope = oattn.RotaryEmbedding(64, **kw)
+    rope = RotaryEmbedding.build(64, **kw)
+    assert rope.uses_yarn
+    pos = np.arange(300, dtype=np.int32)
+    ecos, esin = orope.get_rotary_embeddings(pos, bf16(np.zeros(1)).dtype)
+    cos, sin = rope.tables(300, "cuda")
+    assert np.array_equal(to_numpy(cos)[:300].view(np.uint16), np.asarray(ecos).view(np.uint16))
+    assert np.array_equal(to_numpy(sin)[:300].view(np.uint16), np.asarray(esin).view(np.uint16))
+    x = bf16(np.random.default_rng(2).standard_normal((300, 2, 64), dtype=np.float32))
+    exp = orope.apply_rotary_embeddings(x, pos)
+    got = rope.apply_rotary_embeddings(to_torch(x))
+    assert np.array_equal(to_numpy(got).view(np.uint16), np.asarray(exp).view(np.uint16))

@@ -61,6 +61,7 @@ SIGNATURES: dict[str, tuple] = {
     "xaxb_attn_decode_static": (_I, [_P, _P, _P, _P, _P, _P, _I64, _I64, _I64, _I64, _I64, _F, _I, _P, _P, _I64, _P]),
     "xaxb_attn_prefill": (_I, [_P, _P, _P, _P, _P, _P, _I64, _I64, _I64, _I64, _I64, _I64, _F, _P]),
     "xaxb_attn_check": (_I, [_P, _P, _P, _P, _P, _P, _I64, _I64, _I64, _I64, _I64, _I64, _F, _P]),
+    "xaxb_qk_norm": (_I, [_P, _P, _P, _I64, _I64, _I64, _I64, _I64, _P, _P, _F]),
     "xaxb_rope_apply": (_I, [_P, _P, _P, _I64, _I64, _I64, _P, _P, _P, _I64, _I, _P]),
     "xaxb_advance_positions": (_I, [_P, _P, _P, _I64, c_int32]),
     "xaxb_tp_sync_bytes": (_I64, []),

@@ -259,15 +259,18 @@ class RotaryEmbedding:
 
     def tables(self, length: int, device, any_style: bool = False):
         """(cos, sin) bf16 [>= length, head_dim / 2] on ``device`` (cached, grown on demand)."""
-        if self.uses_yarn:
-            raise ValueError("YaRN scaling is outside the path this library covers")
         if self.style != "concatenated" and not any_style:
             raise ValueError("the attention kernels implement the 'concatenated' RoPE style only")
         key = str(device)
         cur = self._tables.get(key)
         if cur is None or cur[0].shape[0] < length:
             n = max(length, 256)
-            self._tables[key] = cur = ops.rope_tables(self.head_dim, self.base, n, device)
+            if self.uses_yarn:  # :401-441: interpolated frequencies, float32, attention scaling folded in
+                cur = ops.rope_tables_yarn(self.head_dim, self.base, self.factor, self.original_max_position_embeddings,
+                                           self.beta_slow, self.beta_fast, n, device)
+            else:
+                cur = ops.rope_tables(self.head_dim, self.base, n, device)
+            self._tables[key] = cur
         return cur
 
 
@@ -317,8 +320,8 @@ class SelfAttentionBlock:
     def __init__(self, q_proj, k_proj, v_proj, output_proj, rotary_emb, q_norm=None, k_norm=None, sinks=None, *,
                  num_heads: int, num_kv_heads: int, head_dim: int, causal: bool, local_window_size: int | None = None,
                  use_fp8: bool = False):
-        if q_norm is not None or k_norm is not None or sinks is not None or local_window_size is not None:
-            raise ValueError("QK-norm, attention sinks and sliding windows are outside the path this library covers")
+        if sinks is not None or local_window_size is not None:
+            raise ValueError("attention sinks and sliding windows are outside the path this library covers")
         self.q_proj, self.k_proj, self.v_proj, self.output_proj = q_proj, k_proj, v_proj, output_proj
         self.rotary_emb, self.q_norm, self.k_norm, self.sinks = rotary_emb, q_norm, k_norm, sinks
         self.num_heads, self.num_kv_heads, self.head_dim = num_heads, num_kv_heads, head_dim
@@ -334,8 +337,8 @@ class SelfAttentionBlock:
               rotary_beta_fast: float = 32.0, use_qk_norm: bool = False, qk_norm_eps: float = 1e-6,
               use_attention_sinks: bool = False, use_fp8: bool = False, compute_dtype=BF16,
               device=None) -> "SelfAttentionBlock":
-        if context_length is not None or use_qk_norm or use_attention_sinks:
-            raise ValueError("sliding windows, QK-norm and attention sinks are outside the path this library covers")
+        if context_length is not None or use_attention_sinks:
+            raise ValueError("sliding windows and attention sinks are outside the path this library covers")
         kv = num_kv_heads if num_kv_heads is not None else num_heads
         hd = head_dim if head_dim is not None else embed_dim // num_heads
         assert num_heads % kv == 0, "num_heads must be divisible by num_kv_heads"  # :620
@@ -345,9 +348,11 @@ class SelfAttentionBlock:
         rope = RotaryEmbedding.build(hd, rotary_base, rotary_style, rotary_factor,
                                      rotary_original_max_position_embeddings, rotary_beta_slow,
                                      rotary_beta_fast) if use_rotary_embeddings else None
+        qn = RMSNorm.build(hd, qk_norm_eps, device) if use_qk_norm else None  # :665-669
+        kn = RMSNorm.build(hd, qk_norm_eps, device) if use_qk_norm else None
         return cls(mk(embed_dim, qd, seed + 1), mk(embed_dim, kd, seed + 2), mk(embed_dim, kd, seed + 3),
-                   mk(qd, embed_dim, seed + 4), rope, num_heads=num_heads, num_kv_heads=kv, head_dim=hd, causal=causal,
-                   use_fp8=use_fp8)
+                   mk(qd, embed_dim, seed + 4), rope, qn, kn, num_heads=num_heads, num_kv_heads=kv, head_dim=hd,
+                   causal=causal, use_fp8=use_fp8)
 
     @property
     def embed_dim(self) -> int:
@@ -446,6 +451,13 @@ class SelfAttentionBlock:
             qkv = ops.gemm_bf16(y.to(BF16).contiguous(), wq, None, None, bias)
         if self.rotary_emb is None:
             raise ValueError("the attention kernels expect rotary embeddings (as the LLM builds them)")
+        if self.q_norm is not None or self.k_norm is not None:  # QK-norm before RoPE (:864-867)
+            nq, nk = self.q_norm, self.k_norm
+            eps = (nq if nq is not None else nk).eps
+            if nq is not None and nk is not None and nq.eps != nk.eps:
+                raise ValueError("q_norm and k_norm must share one eps")
+            ops.qk_norm(qkv, Hq, Hkv, D, None if nq is None else nq.weight_bf16(),
+                        None if nk is None else nk.weight_bf16(), eps)
         cos, sin = self.rotary_emb.tables(max_len, dev)
         pos = cache["position"]
         q_rot = ops.kv_append_rope(qkv, B, T, Hq, Hkv, D, pos, cos, sin, cache["k"], cache["v"])

@@ -176,8 +176,10 @@ def load_hf_weights_into_llm(model: LLM, repo_id: str | dict, revision: str | No
     for idx, old in enumerate(model.blocks):
         a, f = old.self_attn, old.feed_forward
         sa, mlp, blk = f"layers.{idx}.self_attn", f"layers.{idx}.mlp", f"layers.{idx}"
-        if f"model.{sa}.q_norm.weight" in state or f"model.{sa}.k_norm.weight" in state:
-            raise ValueError("QK-norm checkpoints (qwen3 family) are outside the path this library covers")
+        # QK-norm (Qwen3 style): taken when the checkpoint has the weights (:1331-1342), replicated
+        qn_w, kn_w = state.get(f"model.{sa}.q_norm.weight"), state.get(f"model.{sa}.k_norm.weight")
+        qn = a.q_norm if qn_w is None else RMSNorm(qn_w.to(device=dev, dtype=BF16).contiguous(), model.config.rms_eps)
+        kn = a.k_norm if kn_w is None else RMSNorm(kn_w.to(device=dev, dtype=BF16).contiguous(), model.config.rms_eps)
 
         def proj(layer, prefix, name, tp_name):
             return map_linear(layer, _get_weight(state, *both(prefix, f"{name}.weight")),
@@ -186,8 +188,8 @@ def load_hf_weights_into_llm(model: LLM, repo_id: str | dict, revision: str | No
         attn = SelfAttentionBlock(
             proj(a.q_proj, sa, "q_proj", "q_proj"), proj(a.k_proj, sa, "k_proj", "k_proj"),
             proj(a.v_proj, sa, "v_proj", "v_proj"), proj(a.output_proj, sa, "o_proj", "o_proj"),
-            RotaryEmbedding.build(a.rotary_emb.head_dim, a.rotary_emb.base, a.rotary_emb.style) if a.rotary_emb else None,
-            num_heads=a.num_heads, num_kv_heads=a.num_kv_heads, head_dim=a.head_dim, causal=a.causal, use_fp8=a.use_fp8)
+            a.rotary_emb,
+            qn, kn, num_heads=a.num_heads, num_kv_heads=a.num_kv_heads, head_dim=a.head_dim, causal=a.causal, use_fp8=a.use_fp8)
         ff = SwiGLU(proj(f.gate, mlp, "gate_proj", "gate_proj"), proj(f.up, mlp, "up_proj", "up_proj"),
                     proj(f.down, mlp, "down_proj", "down_proj"))
         pre = _get_weight(state, *both(blk, "input_layernorm.weight"))

@@ -88,8 +88,8 @@ class LLM:
         shard of each weight per get_model_parallel_sharding_spec (same seed on every rank)."""
         if extra_tokens is not None:
             raise ValueError("extra-token embeddings are outside the path this library covers")
-        if config.uses_yarn or config.use_qk_norm or config.use_attention_sinks or config.layer_attention_types:
-            raise ValueError("YaRN, QK-norm, attention sinks and sliding-window layers are outside the path this library covers")
+        if config.use_attention_sinks or config.layer_attention_types:
+            raise ValueError("attention sinks and sliding-window layers are outside the path this library covers")
         dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
         seed = int(key or 0) if not isinstance(key, torch.Generator) else int(key.initial_seed())
         gen = torch.Generator(device=dev).manual_seed(seed)
@@ -125,7 +125,11 @@ class LLM:
                 lin(config.kv_heads * D, H, "k_proj", config.attention_bias),
                 lin(config.kv_heads * D, H, "v_proj", config.attention_bias),
                 lin(H, config.q_heads * D, "o_proj", config.attention_bias),
-                RotaryEmbedding.build(D, config.rope_theta, "concatenated"),
+                RotaryEmbedding.build(D, config.rope_theta, "concatenated", config.rope_factor,
+                                      config.rope_original_max_position_embeddings, config.rope_beta_slow,
+                                      config.rope_beta_fast),
+                RMSNorm.build(D, 1e-6, dev) if config.use_qk_norm else None,  # :123-141 leaves qk_norm_eps at its default
+                RMSNorm.build(D, 1e-6, dev) if config.use_qk_norm else None,
                 num_heads=config.q_heads // tp_size, num_kv_heads=config.kv_heads // tp_size, head_dim=D, causal=True,
                 use_fp8=use_fp8)
             mlp = SwiGLU(lin(width, H, "gate_proj", config.mlp_bias), lin(width, H, "up_proj", config.mlp_bias),

@@ -141,7 +141,7 @@ gemm_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       bool ok = true;
       for (int tile = pair; tile < num_tiles && ok; tile += num_pairs) {
         int tm, tn;
-        tile_coords<8>(tile, p.tiles_m, p.tiles_n, tm, tn);
+        tile_coords(p.band, tile, p.tiles_m, p.tiles_n, tm, tn);
         const int m0 = tm * (2 * kBM) + (int)rank * kBM;
         const int n0 = tn * BN + (int)rank * kBM;
         int kk = (int)(((long long)tile * 5) % p.num_k_blocks);
@@ -198,7 +198,7 @@ gemm_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     uint32_t acc_phase = 0;
     for (int tile = pair; tile < num_tiles; tile += num_pairs) {
       int tm, tn;
-      tile_coords<8>(tile, p.tiles_m, p.tiles_n, tm, tn);
+      tile_coords(p.band, tile, p.tiles_m, p.tiles_n, tm, tn);
       const int m0 = tm * (2 * kBM) + (int)rank * kBM;
       const int n0 = tn * BN;
       bool ok = mbar_wait(acc_full + acc, acc_phase, abort_flag, p.d_status, XAXB_DEVICE_TIMEOUT * 1000 + kSite2Epilogue);
@@ -299,6 +299,7 @@ static int launch_gemm_2cta(const Ctx* ctx, cudaStream_t stream, const void* a, 
   rc = make_tmap_2d(ctx, &tout, p.out, 2, (uint64_t)p.N, (uint64_t)p.M, (uint64_t)p.ldo * 2, 64, kBM);
   if (rc) return rc;
   p.tiles_m = (p.M + 2 * kBM - 1) / (2 * kBM);
+  if (!getenv("XAXB_GEMM_BAND")) p.band = 16;
   p.tiles_n = (p.N + Cfg::kBN - 1) / Cfg::kBN;
   p.num_k_blocks = (int)(((long long)p.K * kElemBytes + kBKBytes - 1) / kBKBytes);
   static bool attr_set = false;

@@ -38,13 +38,13 @@ struct GemmParams {
   long long ldo;
   int* d_status;
   int prefetch_b;  // the launch may overlap the previous kernel: ask L2 for B ahead of the wait
+  int band;        // tile rows per band of the tile order (see tile_coords)
 };
 
 // Tile order: bands of kBand tile rows, column by column inside a band (row index fastest).  The
 // tiles in flight at any moment then share a few row blocks of A and a few column blocks of B
 // -- a working set that stays in L2 -- instead of sweeping all of A for every column of tiles.
-template <int kBand>
-__device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, int& tm, int& tn) {
+__device__ __forceinline__ void tile_coords(int kBand, int tile, int tiles_m, int tiles_n, int& tm, int& tn) {
   const int per_band = kBand * tiles_n;
   const int band = tile / per_band, r = tile - band * per_band;
   const int rows = min(kBand, tiles_m - band * kBand);
@@ -172,7 +172,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       // the SM, and L2 is the point of coherence, so this is safe whatever wrote B and whenever.
       if (p.prefetch_b && (int)blockIdx.x < num_tiles) {
         int tm, tn;
-        tile_coords<16>((int)blockIdx.x, p.tiles_m, p.tiles_n, tm, tn);
+        tile_coords(p.band, (int)blockIdx.x, p.tiles_m, p.tiles_n, tm, tn);
         int kk = (int)(((long long)blockIdx.x * 5) % p.num_k_blocks);
         const int n_pre = p.num_k_blocks < kMaxPrefetchBlocks ? p.num_k_blocks : kMaxPrefetchBlocks;
         for (int i = 0; i < n_pre; ++i) {
@@ -183,7 +183,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       pdl_wait();
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
         int tm, tn;
-        tile_coords<16>(tile, p.tiles_m, p.tiles_n, tm, tn);
+        tile_coords(p.band, tile, p.tiles_m, p.tiles_n, tm, tn);
         const int m0 = tm * kBM, n0 = tn * BN;
         // Each tile walks K from its own starting block: CTAs that share an operand tile (all
         // N tiles read the same rows of A) then ask L2 for different lines at any moment.
@@ -257,7 +257,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       if (t == 0) prefetch_tmap(&tmap_out);
       for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
         int tm, tn;
-        tile_coords<16>(tile, p.tiles_m, p.tiles_n, tm, tn);
+        tile_coords(p.band, tile, p.tiles_m, p.tiles_n, tm, tn);
         const int m0 = tm * kBM, n0 = tn * BN;
         bool ok = mbar_wait(acc_full + acc, acc_phase, abort_flag, p.d_status, XAXB_DEVICE_TIMEOUT * 1000 + kSiteEpilogue);
         if (!epilogue_all(ok)) break;  // also: every thread is done with cmul_s / bias_s of the previous tile
@@ -338,7 +338,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     uint32_t acc_phase = 0;
     for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
       int tm, tn;
-      tile_coords<16>(tile, p.tiles_m, p.tiles_n, tm, tn);
+      tile_coords(p.band, tile, p.tiles_m, p.tiles_n, tm, tn);
       const int m0 = tm * kBM, n0 = tn * BN;
       bool ok = mbar_wait(acc_full + acc, acc_phase, abort_flag, p.d_status, XAXB_DEVICE_TIMEOUT * 1000 + kSiteEpilogue);
       if (!epilogue_all(ok)) break;
@@ -840,6 +840,8 @@ static int gemm_entry(xaxb_ctx* ctx_, void* stream, const void* a, int64_t lda, 
   p.ldo = ldo;
   p.d_status = ctx->d_status;
   p.prefetch_b = pdl_enabled() ? 1 : 0;
+  p.band = 32;  // measured best for 128-row tiles at 8192^3 (2, 4, 8, 16, 32 tried); 16 for the pair kernel
+  if (const char* e = getenv("XAXB_GEMM_BAND")) p.band = atoi(e) > 0 ? atoi(e) : 32;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const GemmPlan plan = pick_plan(M, N, K, eb, ctx->num_sms);
   // Large problems go to the CTA-pair kernel: 256 x 256 tiles need a third less operand traffic

@@ -378,6 +378,34 @@ __global__ void argmax_merge_kernel(const float* __restrict__ vals, const int32_
 }
 
 // ---------------------------------------------------------------------------------------
+// QK-norm (xax/arch/attention.py:864-867): RMSNorm over head_dim of every query and key head,
+// in place on the fused projection output qkv [rows, (Hq + 2 Hkv) * D] (row stride ld), before
+// RoPE.  One warp per (row, head); arithmetic and rounding are RMSNorm's (rmsnorm_kernel).
+__global__ void __launch_bounds__(32) qk_norm_kernel(__nv_bfloat16* __restrict__ qkv, int64_t ld, int Hq, int Hkv, int D,
+                                                     const __nv_bfloat16* __restrict__ wq,
+                                                     const __nv_bfloat16* __restrict__ wk, float eps) {
+  pdl_trigger();
+  pdl_wait();
+  const int64_t row = blockIdx.x;
+  const int head = blockIdx.y;  // 0 .. Hq + Hkv - 1: query heads, then key heads
+  const __nv_bfloat16* w = head < Hq ? wq : wk;
+  if (!w) return;
+  __nv_bfloat16* x = qkv + row * ld + (int64_t)head * D;
+  float acc = 0.0f;
+  for (int i = threadIdx.x; i < D; i += 32) {
+    const float v = __bfloat162float(x[i]);
+    acc += bf16_round(v * v);
+  }
+  for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+  const float mean = bf16_round(acc / (float)D);
+  const float n = bf16_round(sqrtf(bf16_round(mean + bf16_round(eps))));
+  for (int i = threadIdx.x; i < D; i += 32) {
+    const float v = __bfloat162float(x[i]);
+    x[i] = __float2bfloat16_rn(bf16_round(v / n) * __bfloat162float(w[i]));
+  }
+}
+
+// ---------------------------------------------------------------------------------------
 // RoPE on its own (xax/arch/attention.py:443-526): x [rows, heads, D] bf16, row r at position
 // positions[r].  Grid (rows, heads), D/2 threads; thread i owns pair i of the chosen style:
 // "concatenated" pairs (i, i + D/2), "interleaved" pairs (2i, 2i + 1).  Every product and
@@ -712,6 +740,19 @@ int xaxb_kv_append_rope(xaxb_ctx* ctx, void* stream, const void* qkv_bf16, int64
       static_cast<__nv_bfloat16*>(q_rot_bf16), static_cast<__nv_bfloat16*>(k_cache_bf16),
       static_cast<__nv_bfloat16*>(v_cache_bf16), max_len, store_rotated_k, c->d_status);
   return check_launch("kv_append_rope_kernel");
+}
+
+int xaxb_qk_norm(xaxb_ctx* ctx, void* stream, void* qkv_bf16, int64_t ld, int64_t rows, int64_t Hq, int64_t Hkv,
+                 int64_t D, const void* q_weight_bf16, const void* k_weight_bf16, float eps) {
+  if (!ctx || !qkv_bf16 || rows <= 0 || Hq <= 0 || Hkv <= 0 || D <= 0 || ld < (Hq + 2 * Hkv) * D ||
+      (!q_weight_bf16 && !k_weight_bf16))
+    return XAXB_BAD_ARGUMENT;
+  if (Hq + Hkv > 65535) return XAXB_UNSUPPORTED;
+  dim3 grid((unsigned)rows, (unsigned)(Hq + Hkv));
+  launch_kernel(qk_norm_kernel, grid, dim3(32), 0, static_cast<cudaStream_t>(stream), 1,
+                static_cast<__nv_bfloat16*>(qkv_bf16), ld, (int)Hq, (int)Hkv, (int)D,
+                static_cast<const __nv_bfloat16*>(q_weight_bf16), static_cast<const __nv_bfloat16*>(k_weight_bf16), eps);
+  return check_launch("qk_norm_kernel");
 }
 
 int xaxb_rope_apply(xaxb_ctx* ctx, void* stream, const void* x_bf16, int64_t rows, int64_t heads, int64_t D,

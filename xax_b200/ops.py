@@ -321,6 +321,48 @@ def rope_tables(head_dim: int, base: float, length: int, device=None):
     return to_torch(cos), to_torch(sin)
 
 
+def rope_tables_yarn(head_dim: int, base: float, factor: float, original_max_position_embeddings: int, beta_slow: float,
+                     beta_fast: float, length: int, device=None):
+    """cos/sin tables [length, head_dim/2] bf16 with YaRN frequency interpolation and attention
+    scaling (xax/arch/attention.py:401-441): float32 throughout, cast to bf16 at the end."""
+    import math
+
+    import ml_dtypes
+
+    f32 = np.float32
+    dim = head_dim // 2
+    omp = original_max_position_embeddings
+    low = (head_dim * math.log(omp / (beta_fast * 2 * math.pi))) / (2 * math.log(base))
+    high = (head_dim * math.log(omp / (beta_slow * 2 * math.pi))) / (2 * math.log(base))
+    low, high = max(low, 0), min(high, head_dim - 1)
+    timescale = (f32(base) ** (np.arange(0, head_dim, 2, dtype=f32) / f32(head_dim))).astype(f32)
+    extra = (f32(1.0) / timescale).astype(f32)
+    inter = (f32(1.0) / (f32(factor) * timescale)).astype(f32)
+    high = high if low != high else (high + 0.001)
+    idx = np.arange(dim, dtype=f32)
+    interp = (1 - np.clip((idx - f32(low)) / f32(high - low), 0.0, 1.0)).astype(f32)
+    freq = (inter * (1 - interp) + extra * interp).astype(f32)
+    angles = (np.arange(length, dtype=f32)[:, None] * freq[None, :]).astype(f32)
+    scaling = f32(0.1 * 1.0 * math.log(factor) + 1.0)
+    cos = (np.cos(angles) * scaling).astype(ml_dtypes.bfloat16)
+    sin = (np.sin(angles) * scaling).astype(ml_dtypes.bfloat16)
+
+    def to_torch(a):
+        tt = torch.from_numpy(a.view(np.uint16).astype(np.int32)).to(torch.int16).view(BF16)
+        return tt.to(device) if device is not None else tt
+
+    return to_torch(cos), to_torch(sin)
+
+
+def qk_norm(qkv, Hq: int, Hkv: int, D: int, q_weight, k_weight, eps: float):
+    """RMSNorm over head_dim of the query and key heads of the fused projection output, in place."""
+    qkv = _req(qkv, BF16, "qkv")
+    rows, ld = qkv.shape
+    ctx, st, lib = _c()
+    check(lib.xaxb_qk_norm(ctx, st, ptr(qkv), ld, rows, Hq, Hkv, D, ptr(q_weight), ptr(k_weight), float(eps)), "qk_norm")
+    return qkv
+
+
 def rope_apply(x, positions, cos, sin, *, interleaved: bool = False):
     """Rotary embedding of x bf16 [rows, heads, D] at int32 positions [rows]."""
     x = _req(x, BF16, "x")
