@@ -259,9 +259,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         int tm, tn;
         tile_coords(p.band, tile, p.tiles_m, p.tiles_n, tm, tn);
         const int m0 = tm * kBM, n0 = tn * BN;
-        bool ok = mbar_wait(acc_full + acc, acc_phase, abort_flag, p.d_status, XAXB_DEVICE_TIMEOUT * 1000 + kSiteEpilogue);
-        if (!epilogue_all(ok)) break;  // also: every thread is done with cmul_s / bias_s of the previous tile
-        tc_fence_after_sync();
+        // The tile's multipliers and bias are fetched while its main loop is still running (every
+        // thread passed the previous tile's last barrier after its last read of cmul_s / bias_s).
         for (int i = t; i < BN; i += 128) {
           const int n = n0 + i;
           float cm = 0.0f, bs = 0.0f;
@@ -275,6 +274,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         const int m = m0 + row_in_tile;
         const bool row_ok = m < p.M;
         const float rm = (row_ok && p.row_mul) ? __ldg(p.row_mul + (long long)m * p.row_mul_stride) : 1.0f;
+        bool ok = mbar_wait(acc_full + acc, acc_phase, abort_flag, p.d_status, XAXB_DEVICE_TIMEOUT * 1000 + kSiteEpilogue);
+        if (!epilogue_all(ok)) break;  // (also publishes cmul_s / bias_s)
+        tc_fence_after_sync();
         const uint32_t taddr = tmem_base + (uint32_t(quarter * 32) << 16) + acc * BN;
 #pragma unroll 1
         for (int c0 = 0; c0 < BN; c0 += 64) {
@@ -446,6 +448,12 @@ __device__ __forceinline__ uint32_t cluster_ctarank() {
 __device__ __forceinline__ void cluster_sync_all() {
   asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
+__device__ __forceinline__ void cluster_arrive() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void cluster_wait() {
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
 
 // Address of this CTA's shared-memory location `local_smem_addr` as seen in CTA `cta` of the cluster.
 __device__ __forceinline__ uint32_t dsmem_addr(uint32_t local_smem_addr, uint32_t cta) {
@@ -476,6 +484,31 @@ struct SplitKCfg {
   static constexpr int kSmemBytes = (kPipeBytes > kStagingBytes ? kPipeBytes : kStagingBytes) + 1024 + 256;
   static constexpr int kTmemCols = BN < 32 ? 32 : BN;
 };
+
+// One work item of the split-K epilogue: f = the K-reduced accumulators of 8 consecutive columns
+// of row m; multipliers and bias come from shared memory.
+__device__ __forceinline__ void splitk_finish_item(const GemmParams& p, float (&f)[8], const uint4 rv, float rm,
+                                                   const float* cm, const float* bias, int m, int n) {
+#pragma unroll
+  for (int j = 0; j < 8; ++j) f[j] = fmaf(f[j] * rm, cm[j], bias[j]);
+  if (p.residual) {
+    const uint32_t rw[4] = {rv.x, rv.y, rv.z, rv.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      f[2 * j] += bf16_bits_to_float(rw[j] & 0xFFFFu);
+      f[2 * j + 1] += bf16_bits_to_float(rw[j] >> 16);
+    }
+  }
+  uint4 o;
+  uint32_t* ow = reinterpret_cast<uint32_t*>(&o);
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const uint32_t lo16 = __bfloat16_as_ushort(__float2bfloat16_rn(f[2 * j]));
+    const uint32_t hi16 = __bfloat16_as_ushort(__float2bfloat16_rn(f[2 * j + 1]));
+    ow[j] = lo16 | (hi16 << 16);
+  }
+  *reinterpret_cast<uint4*>(p.out + (long long)m * p.ldo + n) = o;
+}
 
 template <int BN, bool IS_FP8>
 __global__ void __launch_bounds__(kGemmThreads, 1)
@@ -580,6 +613,23 @@ gemm_splitk_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
     }
   }
 
+  // ---- epilogue inputs, fetched while the main loop runs (the epilogue warps are idle until the
+  // accumulator is complete): row multipliers of the tile's rows, column multipliers and bias of
+  // its columns.  Reading them inside the reduction put a trip to L2 into every work item.
+  __shared__ float s_rm[kBM], s_cm[BN], s_bias[BN];
+  if (warp >= 2) {
+    const int t = threadIdx.x - 64;
+    {
+      const int m = t;
+      s_rm[t] = (p.row_mul && m < p.M) ? __ldg(p.row_mul + (long long)m * p.row_mul_stride) : 1.0f;
+    }
+    for (int j = t; j < BN; j += 128) {
+      const int n = n0 + j;
+      s_cm[j] = (p.col_mul && n < p.N) ? __ldg(p.col_mul + (long long)n * p.col_mul_stride) : 1.0f;
+      s_bias[j] = (p.bias && n < p.N) ? __bfloat162float(p.bias[n]) : 0.0f;
+    }
+  }
+
   // ---- park the partial accumulator in shared memory (epilogue warps) ------------------------
   const int quarter = warp & 3;
   const int row = quarter * 32 + lane;
@@ -615,70 +665,94 @@ gemm_splitk_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
   // ---- reduce this CTA's row slice over the S ranks, epilogue, store ---------------------------
   // CTA r owns rows [r * 128/S, (r+1) * 128/S) of the tile.  Work item = (row, 8 consecutive
   // columns), consecutive threads take consecutive column groups of a row, so shared-memory
-  // reads (local and remote), the residual read and the bf16 store are all contiguous.
+  // reads (local and remote), the residual read and the bf16 store are all contiguous.  A thread
+  // first sums its items over the ranks (all its remote reads), then the CTA tells the cluster it
+  // is done reading -- so the peers' exit does not wait for this CTA's stores -- and only then
+  // applies multipliers, bias and residual and stores.
+  constexpr int kGroups = BN / 8;
+  constexpr int kMaxItems = 8;  // per thread: rows_per * kGroups / 128
+  const int rows_per = kBM / S;
+  const int n_items = rows_per * kGroups;
+  const bool fast = n_items <= kMaxItems * 128;
+  float fsum[kMaxItems][8];
+  uint4 resv[kMaxItems];
   if (warp >= 2 && ok) {
     const int t = threadIdx.x - 64;          // 0..127
-    const int rows_per = kBM / S;
-    constexpr int kGroups = BN / 8;
     uint32_t peer[8];
 #pragma unroll
     for (int src = 0; src < 8; ++src) peer[src] = dsmem_addr(smem_u32(staging), (uint32_t)(src < S ? src : 0));
-    for (int it = t; it < rows_per * kGroups; it += 128) {
-      const int m = r * rows_per + it / kGroups;
-      const int g8 = it % kGroups;
-      const int n = n0 + g8 * 8;
-      if (m >= p.M || n >= p.N) continue;
-      const uint32_t off = (uint32_t)(m * Cfg::kRowFloats + g8 * 8) * 4u;
-      uint4 rv = make_uint4(0, 0, 0, 0);
-      if (p.residual) rv = *reinterpret_cast<const uint4*>(p.residual + (long long)m * p.ldr + n);
-      float4 lo[8], hi[8];
+    if (fast) {
 #pragma unroll
-      for (int src = 0; src < 8; ++src) {
-        if (src < S) {
-          lo[src] = ld_dsmem_f4(peer[src] + off);
-          hi[src] = ld_dsmem_f4(peer[src] + off + 16);
+      for (int k = 0; k < kMaxItems; ++k) {
+        const int it = t + k * 128;
+        resv[k] = make_uint4(0, 0, 0, 0);
+        if (it < n_items && p.residual) {
+          const int m = r * rows_per + it / kGroups, n = n0 + (it % kGroups) * 8;
+          if (m < p.M && n < p.N) resv[k] = *reinterpret_cast<const uint4*>(p.residual + (long long)m * p.ldr + n);
         }
       }
-      float f[8] = {0, 0, 0, 0, 0, 0, 0, 0};
 #pragma unroll
-      for (int src = 0; src < 8; ++src) {
-        if (src < S) {
-          f[0] += lo[src].x, f[1] += lo[src].y, f[2] += lo[src].z, f[3] += lo[src].w;
-          f[4] += hi[src].x, f[5] += hi[src].y, f[6] += hi[src].z, f[7] += hi[src].w;
+      for (int k = 0; k < kMaxItems; ++k) {
+        const int it = t + k * 128;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) fsum[k][j] = 0.0f;
+        if (it < n_items) {
+          const int m = r * rows_per + it / kGroups, g8 = it % kGroups;
+          const uint32_t off = (uint32_t)(m * Cfg::kRowFloats + g8 * 8) * 4u;
+          float4 lo[8], hi[8];
+#pragma unroll
+          for (int src = 0; src < 8; ++src) {
+            if (src < S) {
+              lo[src] = ld_dsmem_f4(peer[src] + off);
+              hi[src] = ld_dsmem_f4(peer[src] + off + 16);
+            }
+          }
+#pragma unroll
+          for (int src = 0; src < 8; ++src) {
+            if (src < S) {
+              fsum[k][0] += lo[src].x, fsum[k][1] += lo[src].y, fsum[k][2] += lo[src].z, fsum[k][3] += lo[src].w;
+              fsum[k][4] += hi[src].x, fsum[k][5] += hi[src].y, fsum[k][6] += hi[src].z, fsum[k][7] += hi[src].w;
+            }
+          }
         }
       }
-      const float rm = p.row_mul ? p.row_mul[(long long)m * p.row_mul_stride] : 1.0f;
-      apply_muls(f, rm, p.col_mul, p.col_mul_stride, n);
-      if (p.bias) {
-        const uint4 bv = __ldg(reinterpret_cast<const uint4*>(p.bias + n));
-        const uint32_t bw[4] = {bv.x, bv.y, bv.z, bv.w};
+    } else {
+      for (int it = t; it < n_items; it += 128) {
+        const int m = r * rows_per + it / kGroups;
+        const int g8 = it % kGroups;
+        const int n = n0 + g8 * 8;
+        if (m >= p.M || n >= p.N) continue;
+        const uint32_t off = (uint32_t)(m * Cfg::kRowFloats + g8 * 8) * 4u;
+        uint4 rv = make_uint4(0, 0, 0, 0);
+        if (p.residual) rv = *reinterpret_cast<const uint4*>(p.residual + (long long)m * p.ldr + n);
+        float f[8] = {0, 0, 0, 0, 0, 0, 0, 0};
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          f[2 * j] += bf16_bits_to_float(bw[j] & 0xFFFFu);
-          f[2 * j + 1] += bf16_bits_to_float(bw[j] >> 16);
+        for (int src = 0; src < 8; ++src) {
+          if (src < S) {
+            const float4 lo = ld_dsmem_f4(peer[src] + off), hi = ld_dsmem_f4(peer[src] + off + 16);
+            f[0] += lo.x, f[1] += lo.y, f[2] += lo.z, f[3] += lo.w;
+            f[4] += hi.x, f[5] += hi.y, f[6] += hi.z, f[7] += hi.w;
+          }
         }
+        splitk_finish_item(p, f, rv, s_rm[m], s_cm + g8 * 8, s_bias + g8 * 8, m, n);
       }
-      if (p.residual) {
-        const uint32_t rw[4] = {rv.x, rv.y, rv.z, rv.w};
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          f[2 * j] += bf16_bits_to_float(rw[j] & 0xFFFFu);
-          f[2 * j + 1] += bf16_bits_to_float(rw[j] >> 16);
-        }
-      }
-      uint4 o;
-      uint32_t* ow = reinterpret_cast<uint32_t*>(&o);
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const uint32_t lo16 = __bfloat16_as_ushort(__float2bfloat16_rn(f[2 * j]));
-        const uint32_t hi16 = __bfloat16_as_ushort(__float2bfloat16_rn(f[2 * j + 1]));
-        ow[j] = lo16 | (hi16 << 16);
-      }
-      *reinterpret_cast<uint4*>(p.out + (long long)m * p.ldo + n) = o;
     }
   }
   __syncwarp();
-  cluster_sync_all();  // peers have finished reading this CTA's shared memory
+  cluster_arrive();  // this CTA has finished reading its peers' shared memory
+  if (warp >= 2 && ok && fast) {
+    const int t = threadIdx.x - 64;
+#pragma unroll
+    for (int k = 0; k < kMaxItems; ++k) {
+      const int it = t + k * 128;
+      if (it < n_items) {
+        const int m = r * rows_per + it / kGroups, g8 = it % kGroups, n = n0 + g8 * 8;
+        if (m < p.M && n < p.N) splitk_finish_item(p, fsum[k], resv[k], s_rm[m], s_cm + g8 * 8, s_bias + g8 * 8, m, n);
+      }
+    }
+  }
+  __syncwarp();
+  cluster_wait();  // the peers have finished reading this CTA's shared memory
   __syncthreads();
   if (warp == 2) {
     tc_fence_after_sync();
