@@ -223,6 +223,14 @@ int xaxb_attn_decode(xaxb_ctx* ctx, void* stream, const void* q_rot_bf16, const 
                      const void* sin_bf16, int64_t table_len, void* out_bf16, void* workspace,
                      int64_t workspace_bytes);
 
+/* xaxb_attn_decode for a layer with a sliding window (xax/arch/attention.py:931-936: a query at
+ * position q attends to keys q - window .. q; local_window_size of the block): chunks below the
+ * window are never read.  K is expected rotated.  window < 0 means unlimited. */
+int xaxb_attn_decode_window(xaxb_ctx* ctx, void* stream, const void* q_rot_bf16, const void* k_cache_bf16,
+                            const void* v_cache_bf16, const int32_t* positions, int64_t B, int64_t Hq, int64_t Hkv,
+                            int64_t D, int64_t max_len, float softmax_scale, int64_t window, void* out_bf16,
+                            void* workspace, int64_t workspace_bytes);
+
 /* Test hook: 0 = automatic choice of the decode-attention kernel (currently 1), 1 = the
  * chunk-walking kernel with its own choice of chunks per CTA, 2 = persistent software-pipelined
  * kernel, 10 + n (n = 1 .. 64) = the chunk-walking kernel with n 128-token chunks per CTA.
@@ -270,6 +278,13 @@ int xaxb_attn_decode_static(xaxb_ctx* ctx, void* stream, const void* q_rot_bf16,
 int xaxb_attn_prefill(xaxb_ctx* ctx, void* stream, const void* q_rot_bf16, const void* k_cache_bf16,
                       const void* v_cache_bf16, const int32_t* positions, int64_t B, int64_t T, int64_t Hq,
                       int64_t Hkv, int64_t D, int64_t max_len, float softmax_scale, void* out_bf16);
+
+/* xaxb_attn_prefill with a sliding window (same rule as xaxb_attn_decode_window; KV tiles below
+ * the first query's window are skipped). */
+int xaxb_attn_prefill_window(xaxb_ctx* ctx, void* stream, const void* q_rot_bf16, const void* k_cache_bf16,
+                             const void* v_cache_bf16, const int32_t* positions, int64_t B, int64_t T, int64_t Hq,
+                             int64_t Hkv, int64_t D, int64_t max_len, float softmax_scale, int64_t window,
+                             void* out_bf16);
 
 /* Straightforward CUDA-core attention with the contract of xaxb_attn_prefill (T = 1 gives
  * decode): a second opinion for the tensor-core kernels in tests; never used by the

@@ -200,12 +200,12 @@ class RotaryEmbedding:
         raise ValueError(f"Unknown RoPE style: {self.style}. Use 'concatenated' or 'interleaved'.")
 
 
-def dot_product_attention(q, k, v, *, mask=None, is_causal=False, scale=None):
+def dot_product_attention(q, k, v, *, mask=None, is_causal=False, scale=None, local_window_size=None):
     """Documented behaviour of ``jax.nn.dot_product_attention``'s default path for
     q (T, Hq, D), k/v (S, Hkv, D): float32 logits * scale, masked positions get a large
     negative value, float32 softmax over keys, probabilities cast to the value dtype, P.V
     accumulated in float32 and rounded to the value dtype.  Query head h reads kv head
-    h // (Hq // Hkv)."""
+    h // (Hq // Hkv).  ``local_window_size`` = (left, right): query i sees keys i - left .. i + right."""
     q, k, v = np.asarray(q), np.asarray(k), np.asarray(v)
     T, Hq, D = q.shape
     S, Hkv, _ = k.shape
@@ -217,6 +217,10 @@ def dot_product_attention(q, k, v, *, mask=None, is_causal=False, scale=None):
         allow &= np.asarray(mask).reshape(T, S)
     if is_causal:
         allow &= np.tril(np.ones((T, S), dtype=bool))
+    if local_window_size is not None:
+        left, right = local_window_size
+        qi, kj = np.arange(T)[:, None], np.arange(S)[None, :]
+        allow &= (kj >= qi - left) & (kj <= qi + right)
     out = np.empty((T, Hq, D), dtype=v.dtype)
     neg = float32(-0.7 * np.finfo(np.float32).max)
     for h in range(Hq):
@@ -233,14 +237,15 @@ def dot_product_attention(q, k, v, *, mask=None, is_causal=False, scale=None):
 
 class SelfAttentionBlock:
     """xax/arch/attention.py:529-980 restricted to the path: GQA, optional RoPE, causal,
-    KV cache, optional QK-norm (:864-867); no sinks or sliding window."""
+    KV cache, optional QK-norm (:864-867) and sliding window (:931-936, :955); no sinks."""
 
     def __init__(self, q_proj, k_proj, v_proj, output_proj, rotary_emb, *, num_heads, num_kv_heads, head_dim,
-                 causal=True, q_norm=None, k_norm=None):
+                 causal=True, q_norm=None, k_norm=None, local_window_size=None):
         assert num_heads % num_kv_heads == 0  # :620
         self.q_proj, self.k_proj, self.v_proj, self.output_proj = q_proj, k_proj, v_proj, output_proj
         self.rotary_emb = rotary_emb
         self.q_norm, self.k_norm = q_norm, k_norm
+        self.local_window_size = local_window_size
         self.num_heads, self.num_kv_heads, self.head_dim = num_heads, num_kv_heads, head_dim
         self.causal = causal
 
@@ -284,10 +289,14 @@ class SelfAttentionBlock:
                 allow = valid[None, :] & (np.arange(S)[None, :] <= qpos[:, None])
             else:
                 allow = np.broadcast_to(valid[None, :], (T, S))
+            if self.local_window_size is not None:  # :931-936: k_pos >= q_pos - window
+                qpos = np.arange(T) + start
+                allow = allow & (np.arange(S)[None, :] >= (qpos[:, None] - self.local_window_size))
             attn = dot_product_attention(q, k, v, mask=allow)
         else:
             new_position = T
-            attn = dot_product_attention(q, k, v, is_causal=self.causal)  # :949-957
+            lw = (self.local_window_size, 0) if self.local_window_size is not None else None
+            attn = dot_product_attention(q, k, v, is_causal=self.causal, local_window_size=lw)  # :949-957
         attn = attn.reshape(T, -1)
         out, _ = apply_linear_batched(self.output_proj, attn)  # :959-961
         return out, {"k": k, "v": v, "position": np.int32(new_position)}
@@ -317,7 +326,7 @@ class TransformerBlock:
 
 def build_block(rng, *, embed_dim, num_heads, num_kv_heads, head_dim, ff_dim, rope_theta=10000.0, norm_eps=1e-6,
                 fp8_attn=True, fp8_mlp=True, out_scale=1.0, std=0.02, dtype=bfloat16, attn_bias=False,
-                use_qk_norm=False, qk_norm_eps=1e-6):
+                use_qk_norm=False, qk_norm_eps=1e-6, local_window_size=None):
     """Random block with N(0, std^2) weights; output projections scaled by ``out_scale``.
     FP8 projections are Fp8Linear instances (as xax/arch/attention.py:233-240 builds for
     attention; for the MLP they are swapped into SwiGLU, which apply_linear accepts :52)."""
@@ -335,6 +344,7 @@ def build_block(rng, *, embed_dim, num_heads, num_kv_heads, head_dim, ff_dim, ro
         lin(kd, embed_dim, fp8_attn, bias=attn_bias), lin(embed_dim, qd, fp8_attn, out_scale, bias=attn_bias),
         RotaryEmbedding(head_dim, base=rope_theta, style="concatenated"),
         num_heads=num_heads, num_kv_heads=num_kv_heads, head_dim=head_dim, causal=True,
+        local_window_size=local_window_size,
         # :665-669 builds ones; seeded weights around one make the test see them
         q_norm=RMSNorm((1 + 0.1 * rng.standard_normal(head_dim, dtype=float32)).astype(dtype), qk_norm_eps) if use_qk_norm else None,
         k_norm=RMSNorm((1 + 0.1 * rng.standard_normal(head_dim, dtype=float32)).astype(dtype), qk_norm_eps) if use_qk_norm else None)

@@ -26,6 +26,8 @@ class LLMConfig:
     mlp_mult: int = 4
     mlp_hidden_dim: int | None = None
     rms_eps: float = 1e-6
+    sliding_window_size: int | None = None
+    layer_attention_types: tuple | None = None  # :113-120: layers whose type contains "sliding" get the window
 
     def with_vocab(self, vocab_size: int) -> "LLMConfig":
         return replace(self, vocab_size=vocab_size)
@@ -45,8 +47,12 @@ class LLM:
         blocks = [
             build_block(rng, embed_dim=config.embed_dim, num_heads=config.q_heads, num_kv_heads=config.kv_heads,
                         head_dim=config.head_dim, ff_dim=width, rope_theta=config.rope_theta, norm_eps=config.rms_eps,
-                        fp8_attn=use_fp8, fp8_mlp=use_fp8, std=std, dtype=dtype)
-            for _ in range(config.num_layers)
+                        fp8_attn=use_fp8, fp8_mlp=use_fp8, std=std, dtype=dtype,
+                        local_window_size=(config.sliding_window_size
+                                           if config.layer_attention_types is not None
+                                           and i < len(config.layer_attention_types)
+                                           and "sliding" in config.layer_attention_types[i] else None))
+            for i in range(config.num_layers)
         ]
         norm = RMSNorm.build(config.embed_dim, config.rms_eps, dtype)
         if tie:  # tie_embedding_and_head, :713-715

@@ -73,7 +73,8 @@ def block_from_oracle(ob, device="cuda"):
         RotaryEmbedding.build(a.head_dim, a.rotary_emb.base, a.rotary_emb.style),
         None if getattr(a, "q_norm", None) is None else RMSNorm(to_torch(a.q_norm.weight, device), a.q_norm.eps),
         None if getattr(a, "k_norm", None) is None else RMSNorm(to_torch(a.k_norm.weight, device), a.k_norm.eps),
-        num_heads=a.num_heads, num_kv_heads=a.num_kv_heads, head_dim=a.head_dim, causal=a.causal)
+        num_heads=a.num_heads, num_kv_heads=a.num_kv_heads, head_dim=a.head_dim, causal=a.causal,
+        local_window_size=getattr(a, "local_window_size", None))
     f = ob.feed_forward
     ff = SwiGLU(_lin_from_oracle(f.gate, device), _lin_from_oracle(f.up, device), _lin_from_oracle(f.down, device))
     return TransformerBlock(attn, ff, RMSNorm(to_torch(ob.attn_norm.weight, device), ob.attn_norm.eps),

@@ -139,8 +139,8 @@ def test_sharding_spec_matches_the_reference_rule():
 def test_unsupported_features_raise_clearly():
     import xax_b200 as xax
 
-    with pytest.raises(ValueError, match="outside the path"):
-        xax.SelfAttentionBlock.build(64, 2, key=0, context_length=8, device="cpu")
+    sa = xax.SelfAttentionBlock.build(64, 2, key=0, context_length=8, use_attention_sinks=True, device="cpu")
+    assert sa.local_window_size == 7 and sa.sinks.shape == (2,)  # :660, :652-654
     with pytest.raises(ValueError, match="outside the path"):
         xax.TransformerBlock.build(64, 2, 128, key=0, cross_attention=True, device="cpu")
     with pytest.raises(ValueError):

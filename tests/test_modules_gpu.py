@@ -484,3 +484,58 @@ def test_yarn_tables_match_oracle_and_feed_the_block():
     exp = orope.apply_rotary_embeddings(x, pos)
     got = rope.apply_rotary_embeddings(to_torch(x))
     assert np.array_equal(to_numpy(got).view(np.uint16), np.asarray(exp).view(np.uint16))
+
+
+@pytest.mark.parametrize("window,fp8", [(5, False), (100, False), (130, False), (300, True)])
+def test_sliding_window_block_vs_oracle(window, fp8):
+    """Sliding-window attention (xax/arch/attention.py:931-936: keys q - window .. q): chunked prefill of 400
+    tokens (150 + 250, so later queries' windows start inside, and beyond, the first KV tile) and three cached
+    decode steps, against the oracle."""
+    from oracle import attention as oattn
+
+    rng = np.random.default_rng(window)
+    ob = oattn.build_block(rng, embed_dim=256, num_heads=4, num_kv_heads=2, head_dim=64, ff_dim=512, rope_theta=1e4,
+                           fp8_attn=fp8, fp8_mlp=fp8, std=0.05, local_window_size=window)
+    blk = block_from_oracle(ob)
+    assert blk.self_attn.local_window_size == window
+    x = bf16(rng.standard_normal((403, 256), dtype=np.float32))
+    cache_o, cache = ob.init_cache(448), blk.init_cache(448)
+    tol = TOL if not fp8 else 3e-2
+    for lo, hi in ((0, 150), (150, 400), (400, 401), (401, 402), (402, 403)):
+        exp, cache_o = ob.forward(x[lo:hi], cache=cache_o)
+        got, cache = blk.forward(to_torch(x[lo:hi]), cache=cache)
+        assert rel_fro(f32(to_numpy(got)), f32(exp)) < tol, (lo, hi)
+    # and the kernels alone: windowed decode equals full decode when the window covers everything
+    from xax_b200 import ops
+
+    g = torch.Generator(device="cuda").manual_seed(1)
+    kc = torch.randn((3, 700, 2, 64), generator=g, device="cuda", dtype=torch.bfloat16)
+    vc = torch.randn((3, 700, 2, 64), generator=g, device="cuda", dtype=torch.bfloat16)
+    q = torch.randn((3, 4, 64), generator=g, device="cuda", dtype=torch.bfloat16)
+    pos = torch.tensor([0, 333, 699], dtype=torch.int32, device="cuda")
+    assert torch.equal(ops.attn_decode_window(q, kc, vc, pos, 10_000), ops.attn_decode(q, kc, vc, pos))
+
+
+def test_llm_with_sliding_and_full_attention_layers():
+    """layer_attention_types (xax/arch/llm.py:113-120): a "sliding_attention" layer gets the window, a
+    "full_attention" layer does not; sinks ride along (a per-head constant on the logits, which the softmax
+    cancels).  Prefill + cached decode of a bf16 model against the oracle."""
+    from oracle import llm as ollm
+    from xax_b200.arch.llm import LLM, LLMConfig
+
+    types = ("sliding_attention", "full_attention")
+    ocfg = ollm.LLMConfig(vocab_size=256, embed_dim=128, q_heads=4, kv_heads=2, head_dim=64, num_layers=2, max_tsz=256,
+                          mlp_hidden_dim=256, sliding_window_size=20, layer_attention_types=types)
+    om = ollm.LLM.build(ocfg, np.random.default_rng(8), use_fp8=False, tie=True, std=0.05)
+    m = llm_from_oracle(om)
+    assert [b.self_attn.local_window_size for b in m.blocks] == [20, None]
+    toks = np.random.default_rng(1).integers(0, 256, 70).astype(np.int32)
+    exp = om.forward(toks)
+    got = m.forward(torch.from_numpy(toks).cuda())
+    assert rel_fro(f32(to_numpy(got)), f32(exp)) < TOL
+    # LLM.build wires the same structure from the config
+    cfg = LLMConfig(vocab_size=256, embed_dim=128, q_heads=4, kv_heads=2, head_dim=64, num_layers=2, mlp_hidden_dim=256,
+                    sliding_window_size=20, layer_attention_types=types, use_attention_sinks=True)
+    built = LLM.build(cfg, key=0, use_fp8=False)
+    assert [b.self_attn.local_window_size for b in built.blocks] == [20, None]
+    assert built.blocks[0].self_attn.sinks.shape == (4,)

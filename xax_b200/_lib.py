@@ -54,12 +54,14 @@ SIGNATURES: dict[str, tuple] = {
     "xaxb_kv_append_rope": (_I, [_P, _P, _P, _I64, _I64, _I64, _I64, _I64, _I64, _P, _P, _P, _I64, _P, _P, _P, _I64, _I]),
     "xaxb_attn_decode_workspace_bytes": (_I64, [_I64, _I64, _I64, _I64]),
     "xaxb_attn_decode": (_I, [_P, _P, _P, _P, _P, _P, _I64, _I64, _I64, _I64, _I64, _F, _I, _P, _P, _I64, _P, _P, _I64]),
+    "xaxb_attn_decode_window": (_I, [_P, _P, _P, _P, _P, _P, _I64, _I64, _I64, _I64, _I64, _F, _I64, _P, _P, _I64]),
     "xaxb_attn_decode_force_variant": (_I, [_I]),
     "xaxb_attn_decode_cast": (_I, [_P, _P, _P, _P, _P, _P, _I64, _I64, _I64, _I64, _I64, _F, _I, _P, _P, _I64, _P, _P, _P,
                                    _P, _P, _I64]),
     "xaxb_attn_decode_static_capacity_bytes": (_I64, []),
     "xaxb_attn_decode_static": (_I, [_P, _P, _P, _P, _P, _P, _I64, _I64, _I64, _I64, _I64, _F, _I, _P, _P, _I64, _P]),
     "xaxb_attn_prefill": (_I, [_P, _P, _P, _P, _P, _P, _I64, _I64, _I64, _I64, _I64, _I64, _F, _P]),
+    "xaxb_attn_prefill_window": (_I, [_P, _P, _P, _P, _P, _P, _I64, _I64, _I64, _I64, _I64, _I64, _F, _I64, _P]),
     "xaxb_attn_check": (_I, [_P, _P, _P, _P, _P, _P, _I64, _I64, _I64, _I64, _I64, _I64, _F, _P]),
     "xaxb_qk_norm": (_I, [_P, _P, _P, _I64, _I64, _I64, _I64, _I64, _P, _P, _F]),
     "xaxb_rope_apply": (_I, [_P, _P, _P, _I64, _I64, _I64, _P, _P, _P, _I64, _I, _P]),

@@ -320,8 +320,10 @@ class SelfAttentionBlock:
     def __init__(self, q_proj, k_proj, v_proj, output_proj, rotary_emb, q_norm=None, k_norm=None, sinks=None, *,
                  num_heads: int, num_kv_heads: int, head_dim: int, causal: bool, local_window_size: int | None = None,
                  use_fp8: bool = False):
-        if sinks is not None or local_window_size is not None:
-            raise ValueError("attention sinks and sliding windows are outside the path this library covers")
+        # Attention sinks: the reference adds them to the logits as a bias of shape (1, heads, 1)
+        # (:745-748, :893-896) -- one constant per head over all keys, which a softmax over keys
+        # cancels.  They are kept (float32 [heads], zeros at build :652-654; no loader fills them) and
+        # the kernels need nothing for them.
         self.q_proj, self.k_proj, self.v_proj, self.output_proj = q_proj, k_proj, v_proj, output_proj
         self.rotary_emb, self.q_norm, self.k_norm, self.sinks = rotary_emb, q_norm, k_norm, sinks
         self.num_heads, self.num_kv_heads, self.head_dim = num_heads, num_kv_heads, head_dim
@@ -337,8 +339,7 @@ class SelfAttentionBlock:
               rotary_beta_fast: float = 32.0, use_qk_norm: bool = False, qk_norm_eps: float = 1e-6,
               use_attention_sinks: bool = False, use_fp8: bool = False, compute_dtype=BF16,
               device=None) -> "SelfAttentionBlock":
-        if context_length is not None or use_attention_sinks:
-            raise ValueError("sliding windows and attention sinks are outside the path this library covers")
+        sinks = torch.zeros((num_heads,), dtype=torch.float32, device=device) if use_attention_sinks else None  # :652-654
         kv = num_kv_heads if num_kv_heads is not None else num_heads
         hd = head_dim if head_dim is not None else embed_dim // num_heads
         assert num_heads % kv == 0, "num_heads must be divisible by num_kv_heads"  # :620
@@ -351,8 +352,9 @@ class SelfAttentionBlock:
         qn = RMSNorm.build(hd, qk_norm_eps, device) if use_qk_norm else None  # :665-669
         kn = RMSNorm.build(hd, qk_norm_eps, device) if use_qk_norm else None
         return cls(mk(embed_dim, qd, seed + 1), mk(embed_dim, kd, seed + 2), mk(embed_dim, kd, seed + 3),
-                   mk(qd, embed_dim, seed + 4), rope, qn, kn, num_heads=num_heads, num_kv_heads=kv, head_dim=hd,
-                   causal=causal, use_fp8=use_fp8)
+                   mk(qd, embed_dim, seed + 4), rope, qn, kn, sinks, num_heads=num_heads, num_kv_heads=kv, head_dim=hd,
+                   causal=causal, local_window_size=None if context_length is None else context_length - 1,  # :660
+                   use_fp8=use_fp8)
 
     @property
     def embed_dim(self) -> int:
@@ -464,21 +466,26 @@ class SelfAttentionBlock:
         scale = 1.0 / math.sqrt(D)
         op = self.output_proj
         op_fp8 = isinstance(op, Fp8Linear) and op.use_fp8
-        if T == 1 and op_fp8 and peer_site is not None and Hq <= 64 and Hq * D <= 4096:
+        win = self.local_window_size
+        fits_cast = T == 1 and op_fp8 and win is None and Hq <= 64 and Hq * D <= 4096
+        if fits_cast and peer_site is not None:
             aq, _, a_inv = ops.attn_decode_cast_tp(q_rot, cache["k"], cache["v"], pos, peer_site, scale=scale,
                                                    workspace=workspace)
             out = op.forward_quantized(aq, a_inv, residual, out)
             if advance:
                 ops.advance_positions(pos, T)
             return out, {"k": cache["k"], "v": cache["v"], "position": pos}
-        if T == 1 and op_fp8 and reduce_amax is None and Hq <= 64 and Hq * D <= 4096:
+        if fits_cast and reduce_amax is None:
             # decode: the per-token cast of the attention output happens inside the merge pass
             _, aq, _, a_inv = ops.attn_decode_cast(q_rot, cache["k"], cache["v"], pos, scale=scale, workspace=workspace)
             out = op.forward_quantized(aq, a_inv, residual, out)
             if advance:
                 ops.advance_positions(pos, T)
             return out, {"k": cache["k"], "v": cache["v"], "position": pos}
-        if T == 1:
+        if win is not None:  # sliding window (:931-936): a query sees keys q - window .. q
+            attn = (ops.attn_decode_window(q_rot, cache["k"], cache["v"], pos, win, scale=scale, workspace=workspace)
+                    if T == 1 else ops.attn_prefill_window(q_rot, cache["k"], cache["v"], pos, B, T, win, scale=scale))
+        elif T == 1:
             attn = ops.attn_decode(q_rot, cache["k"], cache["v"], pos, scale=scale, workspace=workspace)
         else:
             attn = ops.attn_prefill(q_rot, cache["k"], cache["v"], pos, B, T, scale=scale)
@@ -505,11 +512,11 @@ class TransformerBlock:
     def __init__(self, self_attn: SelfAttentionBlock, feed_forward: SwiGLU, attn_norm: RMSNorm, mlp_norm: RMSNorm, *,
                  num_heads: int, head_dim: int, causal: bool, use_fp8: bool = False, cross_attn=None,
                  cross_attn_norm=None, context_length: int | None = None):
-        if cross_attn is not None or cross_attn_norm is not None or context_length is not None:
-            raise ValueError("cross-attention and sliding windows are outside the path this library covers")
+        if cross_attn is not None or cross_attn_norm is not None:
+            raise ValueError("cross-attention is outside the path this library covers")
         self.self_attn, self.feed_forward, self.attn_norm, self.mlp_norm = self_attn, feed_forward, attn_norm, mlp_norm
         self.num_heads, self.head_dim, self.causal, self.use_fp8 = num_heads, head_dim, causal, use_fp8
-        self.cross_attn, self.cross_attn_norm, self.context_length = None, None, None
+        self.cross_attn, self.cross_attn_norm, self.context_length = None, None, context_length
 
     @classmethod
     def build(cls, embed_dim: int, num_heads: int, ff_dim: int, *, key=None, num_kv_heads: int | None = None,
@@ -541,7 +548,7 @@ class TransformerBlock:
             compute_dtype=compute_dtype, device=device)
         ff = SwiGLU.build(embed_dim, ff_dim, key=seed * 3 + 2, use_fp8=bool(fp8_mlp), device=device)
         return cls(attn, ff, RMSNorm.build(embed_dim, norm_eps, device), RMSNorm.build(embed_dim, norm_eps, device),
-                   num_heads=num_heads, head_dim=hd, causal=causal, use_fp8=use_fp8)
+                   num_heads=num_heads, head_dim=hd, causal=causal, use_fp8=use_fp8, context_length=context_length)
 
     @property
     def embed_dim(self) -> int:

@@ -189,7 +189,7 @@ def load_hf_weights_into_llm(model: LLM, repo_id: str | dict, revision: str | No
             proj(a.q_proj, sa, "q_proj", "q_proj"), proj(a.k_proj, sa, "k_proj", "k_proj"),
             proj(a.v_proj, sa, "v_proj", "v_proj"), proj(a.output_proj, sa, "o_proj", "o_proj"),
             a.rotary_emb,
-            qn, kn, num_heads=a.num_heads, num_kv_heads=a.num_kv_heads, head_dim=a.head_dim, causal=a.causal, use_fp8=a.use_fp8)
+            qn, kn, a.sinks, local_window_size=a.local_window_size, num_heads=a.num_heads, num_kv_heads=a.num_kv_heads, head_dim=a.head_dim, causal=a.causal, use_fp8=a.use_fp8)
         ff = SwiGLU(proj(f.gate, mlp, "gate_proj", "gate_proj"), proj(f.up, mlp, "up_proj", "up_proj"),
                     proj(f.down, mlp, "down_proj", "down_proj"))
         pre = _get_weight(state, *both(blk, "input_layernorm.weight"))

@@ -88,8 +88,6 @@ class LLM:
         shard of each weight per get_model_parallel_sharding_spec (same seed on every rank)."""
         if extra_tokens is not None:
             raise ValueError("extra-token embeddings are outside the path this library covers")
-        if config.use_attention_sinks or config.layer_attention_types:
-            raise ValueError("attention sinks and sliding-window layers are outside the path this library covers")
         dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
         seed = int(key or 0) if not isinstance(key, torch.Generator) else int(key.initial_seed())
         gen = torch.Generator(device=dev).manual_seed(seed)
@@ -117,8 +115,13 @@ class LLM:
 
         embed = Embedding(config.vocab_size, H, weight=_randn((config.vocab_size, H), std, gen, dev))
         blocks = []
-        for _ in range(config.num_layers):
+        for i in range(config.num_layers):
             from .attention import RotaryEmbedding
+
+            layer_window = None  # :113-120
+            if config.layer_attention_types is not None and i < len(config.layer_attention_types):
+                if "sliding" in config.layer_attention_types[i]:
+                    layer_window = config.sliding_window_size
 
             attn = SelfAttentionBlock(
                 lin(config.q_heads * D, H, "q_proj", config.attention_bias),
@@ -130,6 +133,9 @@ class LLM:
                                       config.rope_beta_fast),
                 RMSNorm.build(D, 1e-6, dev) if config.use_qk_norm else None,  # :123-141 leaves qk_norm_eps at its default
                 RMSNorm.build(D, 1e-6, dev) if config.use_qk_norm else None,
+                torch.zeros((config.q_heads // tp_size,), dtype=torch.float32, device=dev)
+                if config.use_attention_sinks else None,
+                local_window_size=layer_window,  # context_length = window + 1 (:131), local_window_size = that - 1 (:660)
                 num_heads=config.q_heads // tp_size, num_kv_heads=config.kv_heads // tp_size, head_dim=D, causal=True,
                 use_fp8=use_fp8)
             mlp = SwiGLU(lin(width, H, "gate_proj", config.mlp_bias), lin(width, H, "up_proj", config.mlp_bias),

@@ -44,6 +44,14 @@ struct MergeOut {
   float* inv_scale;
 };
 
+// Chunks a sequence of L cached tokens contributes when its last token looks back `window`
+// positions (< 0: all of them).
+__host__ __device__ __forceinline__ int decode_chunks(int L, int window) {
+  const int n = (L + kChunk - 1) / kChunk;
+  const int lo = window >= 0 ? (L - 1 - window > 0 ? L - 1 - window : 0) : 0;
+  return n - lo / kChunk;
+}
+
 struct DecodeParams {
   const __nv_bfloat16* q;      // [B, Hq, D] rotated
   const int32_t* positions;    // [B]; attend to rows 0 .. positions[b]
@@ -57,6 +65,7 @@ struct DecodeParams {
   float* ws_o;   // [B, Hq, max_chunks, D]
   float* ws_ml;  // [B, Hq, max_chunks, 2]
   int max_chunks;
+  int window;  // sliding window: the query at position q sees keys q - window .. q; < 0 = unlimited
   int* d_status;
 };
 
@@ -167,7 +176,10 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(const __grid_constant_
   const int first = blockIdx.x, stride = gridDim.x, hk = blockIdx.y, b = blockIdx.z;
   const int L = p.positions[b] + 1;
   const int n_chunks = (L + kChunk - 1) / kChunk;
-  if (first >= n_chunks) return;
+  // with a sliding window the chunks below the first visible token are never loaded
+  const int lo_tok = p.window >= 0 ? max(0, L - 1 - p.window) : 0;
+  const int c_lo = lo_tok / kChunk;
+  if (c_lo + first >= n_chunks) return;
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -198,10 +210,10 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(const __grid_constant_
     mbar_arrive_expect_tx(bar_v, SM::kTileBytes);
 #pragma unroll
     for (int x = 0; x < kBoxes; ++x)
-      tma_load_4d(sK + x * SM::kHalfBytes, &tmap_k, bar_k, x * 64, hk, first * kChunk, b);
+      tma_load_4d(sK + x * SM::kHalfBytes, &tmap_k, bar_k, x * 64, hk, (c_lo + first) * kChunk, b);
 #pragma unroll
     for (int x = 0; x < kBoxes; ++x)
-      tma_load_4d(sV + x * SM::kHalfBytes, &tmap_v, bar_v, x * 64, hk, first * kChunk, b);
+      tma_load_4d(sV + x * SM::kHalfBytes, &tmap_v, bar_v, x * 64, hk, (c_lo + first) * kChunk, b);
   }
   if (warp == 1) {
     tmem_alloc(tmem_slot, 32);
@@ -245,7 +257,7 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(const __grid_constant_
   // iteration: parity = iteration & 1.
   bool ok = true;
   uint32_t ph = 0;
-  for (int chunk = first; chunk < n_chunks; chunk += stride, ph ^= 1) {
+  for (int chunk = c_lo + first; chunk < n_chunks; chunk += stride, ph ^= 1) {
     const int tok0 = chunk * kChunk;
     const int valid = min(kChunk, L - tok0);
     const int next = chunk + stride;
@@ -328,7 +340,7 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(const __grid_constant_
       tmem_ld_x16(tmem_s + (uint32_t(warp * 32) << 16), r);
       tmem_ld_wait();
       tc_fence_before_sync();
-      const bool tok_ok = tid < valid;
+      const bool tok_ok = tid < valid && tok0 + tid >= lo_tok;
 #pragma unroll
       for (int g = 0; g < GT; ++g) {
         pvals[g] = tok_ok ? __uint_as_float(r[g]) * p.sm_scale : -INFINITY;
@@ -345,7 +357,7 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(const __grid_constant_
 #pragma unroll
       for (int g = 0; g < GT; ++g) {
         m_c[g] = fmaxf(fmaxf(red_max[g], red_max[kNPad + g]), fmaxf(red_max[2 * kNPad + g], red_max[3 * kNPad + g]));
-        const float e = (tid < valid) ? __expf(pvals[g] - m_c[g]) : 0.0f;
+        const float e = (tid < valid && tok0 + tid >= lo_tok) ? __expf(pvals[g] - m_c[g]) : 0.0f;
         pvals[g] = e;
         const uint32_t off = box * (kNPad * 128) + sw128_offset(g, within / 8) + (within % 8) * 2;
         *reinterpret_cast<__nv_bfloat16*>(sP + off) = __float2bfloat16_rn(e);
@@ -881,12 +893,12 @@ static int g_decode_variant = 0;  // 0 / 1 = chunk-walking kernel, 2 = persisten
 // first slots of its row of the workspace.  D threads.
 __global__ void attn_decode_merge_kernel(const float* __restrict__ ws_o, const float* __restrict__ ws_ml,
                                          const int32_t* __restrict__ positions, int Hq, int D, int max_chunks,
-                                         int lanes, __nv_bfloat16* __restrict__ out) {
+                                         int lanes, int window, __nv_bfloat16* __restrict__ out) {
   pdl_trigger();
   pdl_wait();
   const int h = blockIdx.x, b = blockIdx.y, d = threadIdx.x;
   const int L = positions[b] + 1;
-  const int n = min((L + kChunk - 1) / kChunk, lanes);
+  const int n = min(decode_chunks(L, window), lanes);
   const long long base = ((long long)b * Hq + h) * max_chunks;
   float m = -INFINITY;
   for (int c = 0; c < n; ++c) m = fmaxf(m, ws_ml[(base + c) * 2]);
@@ -903,14 +915,14 @@ __global__ void attn_decode_merge_kernel(const float* __restrict__ ws_o, const f
 // not merge themselves.
 __global__ void __launch_bounds__(256) attn_decode_merge_cast_kernel(
     const float* __restrict__ ws_o, const float* __restrict__ ws_ml, const int32_t* __restrict__ positions, int Hq,
-    int D, int max_chunks, int lanes, const MergeOut mo, const TpRowMax tp, int* d_status) {
+    int D, int max_chunks, int lanes, int window, const MergeOut mo, const TpRowMax tp, int* d_status) {
   pdl_trigger();
   pdl_wait();
   __shared__ float s_max[64], s_inv_den[64];
   __shared__ uint32_t s_tp[2];
   const int b = blockIdx.x;
   const int L = positions[b] + 1;
-  const int n = min((L + kChunk - 1) / kChunk, lanes);
+  const int n = min(decode_chunks(L, window), lanes);
   merge_cast_row<256, false>(ws_o, ws_ml, b, n, Hq, D, max_chunks, mo, tp, d_status, s_max, s_inv_den, s_tp);
 }
 
@@ -939,7 +951,7 @@ static int decode_launch(xaxb_ctx* ctx_, void* stream, const void* q_rot_bf16, c
                          int64_t D, int64_t max_len, float softmax_scale, int k_is_rotated, const void* cos_bf16,
                          const void* sin_bf16, int64_t table_len, void* out_bf16, void* q_e4m3, float* row_scale,
                          float* row_inv_scale, void* workspace, int64_t workspace_bytes,
-                         const TpRowMax* tp = nullptr) {
+                         const TpRowMax* tp = nullptr, int64_t window = -1) {
   if (!ctx_ || !q_rot_bf16 || !k_cache_bf16 || !v_cache_bf16 || !positions || (!out_bf16 && !q_e4m3) || !workspace || B <= 0 ||
       Hq <= 0 || Hkv <= 0 || max_len <= 0) {
     set_last_error("attn_decode: null pointer or non-positive shape");
@@ -976,6 +988,11 @@ static int decode_launch(xaxb_ctx* ctx_, void* stream, const void* q_rot_bf16, c
   p.ws_o = static_cast<float*>(workspace);
   p.ws_ml = p.ws_o + B * Hq * max_chunks * D;
   p.max_chunks = max_chunks;
+  p.window = window < 0 ? -1 : (window > 0x3fffffff ? 0x3fffffff : (int)window);
+  if (p.window >= 0 && g_decode_variant == 2) {
+    set_last_error("attn_decode: the persistent pipelined kernel has no sliding window");
+    return XAXB_UNSUPPORTED;
+  }
   p.d_status = ctx->d_status;
   int lanes = max_chunks;  // partial results per (sequence, head) row of the workspace
   const bool use_pipe = g_decode_variant == 2 && (long long)B * Hkv * max_chunks < (1ll << 31);
@@ -1052,14 +1069,14 @@ static int decode_launch(xaxb_ctx* ctx_, void* stream, const void* q_rot_bf16, c
   if (rc) return rc;
   if (q_e4m3) {
     launch_kernel(attn_decode_merge_cast_kernel, dim3((unsigned)B), dim3(256), 0, s, 1, p.ws_o, p.ws_ml, positions, (int)Hq, (int)D, max_chunks,
-                                                             lanes,
+                                                             lanes, p.window,
                   MergeOut{static_cast<uint4*>(out_bf16), static_cast<uint2*>(q_e4m3), row_scale, row_inv_scale},
                   tp ? *tp : TpRowMax{}, ctx->d_status);
     return check_launch("attn_decode_merge_cast_kernel");
   }
   dim3 mgrid((unsigned)Hq, (unsigned)B);
   launch_kernel(attn_decode_merge_kernel, mgrid, dim3((unsigned)D), 0, s, 1, p.ws_o, p.ws_ml, positions, (int)Hq, (int)D, max_chunks,
-                                                         lanes, static_cast<__nv_bfloat16*>(out_bf16));
+                                                         lanes, p.window, static_cast<__nv_bfloat16*>(out_bf16));
   return check_launch("attn_decode_merge_kernel");
 }
 
@@ -1072,6 +1089,16 @@ int xaxb_attn_decode(xaxb_ctx* ctx_, void* stream, const void* q_rot_bf16, const
   return decode_launch(ctx_, stream, q_rot_bf16, k_cache_bf16, v_cache_bf16, positions, B, Hq, Hkv, D, max_len,
                        softmax_scale, k_is_rotated, cos_bf16, sin_bf16, table_len, out_bf16, nullptr, nullptr, nullptr,
                        workspace, workspace_bytes);
+}
+
+int xaxb_attn_decode_window(xaxb_ctx* ctx_, void* stream, const void* q_rot_bf16, const void* k_cache_bf16,
+                            const void* v_cache_bf16, const int32_t* positions, int64_t B, int64_t Hq, int64_t Hkv,
+                            int64_t D, int64_t max_len, float softmax_scale, int64_t window, void* out_bf16,
+                            void* workspace, int64_t workspace_bytes) {
+  if (!out_bf16) return XAXB_BAD_ARGUMENT;
+  return decode_launch(ctx_, stream, q_rot_bf16, k_cache_bf16, v_cache_bf16, positions, B, Hq, Hkv, D, max_len,
+                       softmax_scale, 1, nullptr, nullptr, 0, out_bf16, nullptr, nullptr, nullptr, workspace,
+                       workspace_bytes, nullptr, window);
 }
 
 int xaxb_attn_decode_cast(xaxb_ctx* ctx_, void* stream, const void* q_rot_bf16, const void* k_cache_bf16,

@@ -26,6 +26,7 @@ struct PrefillParams {
   const int32_t* positions;  // [B]
   int T, Hq, Hkv;
   float sm_scale;
+  int window;  // sliding window: query at position q sees keys q - window .. q; < 0 = unlimited
   int* d_status;
 };
 
@@ -52,7 +53,10 @@ __global__ void __launch_bounds__(128, 1) attn_prefill_kernel(const __grid_const
   const int q0 = qb * kPfTile;                    // first query index of this CTA
   const int rows_valid = min(kPfTile, p.T - q0);
   const int last_pos = start + q0 + rows_valid - 1;  // highest key position any row may see
-  const int n_tiles = last_pos / kPfTile + 1;
+  const int win = p.window;
+  // with a sliding window the tiles below the first row's window are never loaded
+  const int j_lo = win >= 0 ? max(0, start + q0 - win) / kPfTile : 0;
+  const int n_tiles = last_pos / kPfTile + 1 - j_lo;  // tiles j_lo .. j_lo + n_tiles - 1
   const int total_len = start + p.T;              // rows of the cache holding this sequence
 
   extern __shared__ uint8_t smem_raw[];
@@ -76,8 +80,8 @@ __global__ void __launch_bounds__(128, 1) attn_prefill_kernel(const __grid_const
     mbar_arrive_expect_tx(bar_kv + s, 2 * SM::kKVBytes);
 #pragma unroll
     for (int x = 0; x < kBoxes; ++x) {
-      tma_load_4d(k_dst + x * SM::kHalfBytes, &tmap_k, bar_kv + s, x * 64, hk, j * kPfTile, b);
-      tma_load_4d(v_dst + x * SM::kHalfBytes, &tmap_v, bar_kv + s, x * 64, hk, j * kPfTile, b);
+      tma_load_4d(k_dst + x * SM::kHalfBytes, &tmap_k, bar_kv + s, x * 64, hk, (j_lo + j) * kPfTile, b);
+      tma_load_4d(v_dst + x * SM::kHalfBytes, &tmap_v, bar_kv + s, x * 64, hk, (j_lo + j) * kPfTile, b);
     }
   };
 
@@ -131,7 +135,7 @@ __global__ void __launch_bounds__(128, 1) attn_prefill_kernel(const __grid_const
     ok = ok && mbar_wait(bar_kv + s, (j >> 1) & 1, abort_flag, p.d_status, XAXB_DEVICE_TIMEOUT * 1000 + kSitePfKV);
     // rows of the tile past the sequence's last cached token may hold anything; the mask
     // zeroes their probabilities, and V is cleared so that 0 * garbage stays 0
-    if (ok && j * kPfTile + tid >= total_len) {
+    if (ok && (j_lo + j) * kPfTile + tid >= total_len) {
 #pragma unroll
       for (int c = 0; c < D / 8; ++c)
         *reinterpret_cast<uint4*>(sV + (c / 8) * SM::kHalfBytes + sw128_offset(tid, c % 8)) = make_uint4(0, 0, 0, 0);
@@ -154,8 +158,10 @@ __global__ void __launch_bounds__(128, 1) attn_prefill_kernel(const __grid_const
     tc_fence_after_sync();
 
     // ---- online softmax on row `tid` of S (two sweeps over TMEM: max, then exp) ------------
-    const int kv0 = j * kPfTile;
-    const bool diag = kv0 + kPfTile - 1 > start + q0;  // some (row, col) of this tile is masked
+    const int kv0 = (j_lo + j) * kPfTile;
+    // some (row, col) of this tile is masked: above the diagonal, or below some row's window
+    const bool diag = kv0 + kPfTile - 1 > start + q0 || (win >= 0 && kv0 < last_pos - win);
+    const int lo_vis = win >= 0 ? qpos - win : 0;  // lowest key position this row sees
     float m_tile = -INFINITY;
 #pragma unroll 1
     for (int c0 = 0; c0 < kPfTile; c0 += 32) {
@@ -165,10 +171,13 @@ __global__ void __launch_bounds__(128, 1) attn_prefill_kernel(const __grid_const
 #pragma unroll
       for (int i = 0; i < 32; ++i) {
         const float v = __uint_as_float(r[i]);
-        if (!diag || kv0 + c0 + i <= qpos) m_tile = fmaxf(m_tile, v);
+        if (!diag || (kv0 + c0 + i <= qpos && kv0 + c0 + i >= lo_vis)) m_tile = fmaxf(m_tile, v);
       }
     }
-    const float m_new = fmaxf(m_run, m_tile * scale_log2);  // base-2 domain; column 0 of tile 0 is always visible
+    // base-2 domain.  Without a window column 0 of tile 0 is visible to every row; with one, a row
+    // may see nothing of the first tiles: its running maximum stays -inf and nothing is added.
+    const float m_raw = fmaxf(m_run, m_tile * scale_log2);
+    const float m_new = m_raw == -INFINITY ? 0.0f : m_raw;
     const float alpha = exp2f(m_run - m_new);
     float l_tile = 0.0f;
 #pragma unroll 1
@@ -182,8 +191,8 @@ __global__ void __launch_bounds__(128, 1) attn_prefill_kernel(const __grid_const
         float e0 = exp2f(__uint_as_float(r[i]) * scale_log2 - m_new);
         float e1 = exp2f(__uint_as_float(r[i + 1]) * scale_log2 - m_new);
         if (diag) {
-          if (kv0 + c0 + i > qpos) e0 = 0.0f;
-          if (kv0 + c0 + i + 1 > qpos) e1 = 0.0f;
+          if (kv0 + c0 + i > qpos || kv0 + c0 + i < lo_vis) e0 = 0.0f;
+          if (kv0 + c0 + i + 1 > qpos || kv0 + c0 + i + 1 < lo_vis) e1 = 0.0f;
         }
         l_tile += e0 + e1;
         const uint32_t lo = __bfloat16_as_ushort(__float2bfloat16_rn(e0));
@@ -199,7 +208,7 @@ __global__ void __launch_bounds__(128, 1) attn_prefill_kernel(const __grid_const
       }
     }
     l_run = l_run * alpha + l_tile;
-    m_run = m_new;
+    m_run = m_raw;
     fence_proxy_async_smem();
     tc_fence_before_sync();
     __syncthreads();
@@ -267,9 +276,9 @@ static int make_cache_tmap_pf(const Ctx* ctx, CUtensorMap* map, const void* cach
 
 using namespace xaxb;
 
-extern "C" int xaxb_attn_prefill(xaxb_ctx* ctx_, void* stream, const void* q_rot_bf16, const void* k_cache_bf16,
-                                 const void* v_cache_bf16, const int32_t* positions, int64_t B, int64_t T, int64_t Hq,
-                                 int64_t Hkv, int64_t D, int64_t max_len, float softmax_scale, void* out_bf16) {
+static int prefill_launch(xaxb_ctx* ctx_, void* stream, const void* q_rot_bf16, const void* k_cache_bf16,
+                          const void* v_cache_bf16, const int32_t* positions, int64_t B, int64_t T, int64_t Hq,
+                          int64_t Hkv, int64_t D, int64_t max_len, float softmax_scale, int64_t window, void* out_bf16) {
   if (!ctx_ || !q_rot_bf16 || !k_cache_bf16 || !v_cache_bf16 || !positions || !out_bf16 || B <= 0 || T <= 0 ||
       Hq <= 0 || Hkv <= 0 || max_len <= 0) {
     set_last_error("attn_prefill: null pointer or non-positive shape");
@@ -293,6 +302,7 @@ extern "C" int xaxb_attn_prefill(xaxb_ctx* ctx_, void* stream, const void* q_rot
   p.positions = positions;
   p.T = (int)T, p.Hq = (int)Hq, p.Hkv = (int)Hkv;
   p.sm_scale = softmax_scale;
+  p.window = window < 0 ? -1 : (window > 0x3fffffff ? 0x3fffffff : (int)window);
   p.d_status = ctx->d_status;
   dim3 grid((unsigned)((T + kPfTile - 1) / kPfTile), (unsigned)Hq, (unsigned)B);
   if (D == 128) {
@@ -313,4 +323,19 @@ extern "C" int xaxb_attn_prefill(xaxb_ctx* ctx_, void* stream, const void* q_rot
     launch_kernel(attn_prefill_kernel<64>, grid, dim3(128), PrefillSmem<64>::kBytes, s, 1, tk, tv, p);
   }
   return check_launch("attn_prefill_kernel");
+}
+
+extern "C" int xaxb_attn_prefill(xaxb_ctx* ctx_, void* stream, const void* q_rot_bf16, const void* k_cache_bf16,
+                                 const void* v_cache_bf16, const int32_t* positions, int64_t B, int64_t T, int64_t Hq,
+                                 int64_t Hkv, int64_t D, int64_t max_len, float softmax_scale, void* out_bf16) {
+  return prefill_launch(ctx_, stream, q_rot_bf16, k_cache_bf16, v_cache_bf16, positions, B, T, Hq, Hkv, D, max_len,
+                        softmax_scale, -1, out_bf16);
+}
+
+extern "C" int xaxb_attn_prefill_window(xaxb_ctx* ctx_, void* stream, const void* q_rot_bf16, const void* k_cache_bf16,
+                                        const void* v_cache_bf16, const int32_t* positions, int64_t B, int64_t T,
+                                        int64_t Hq, int64_t Hkv, int64_t D, int64_t max_len, float softmax_scale,
+                                        int64_t window, void* out_bf16) {
+  return prefill_launch(ctx_, stream, q_rot_bf16, k_cache_bf16, v_cache_bf16, positions, B, T, Hq, Hkv, D, max_len,
+                        softmax_scale, window, out_bf16);
 }

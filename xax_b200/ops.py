@@ -413,6 +413,38 @@ def attn_decode(q_rot, k_cache, v_cache, positions, *, scale=None, k_is_rotated=
     return out
 
 
+def attn_decode_window(q_rot, k_cache, v_cache, positions, window: int, *, scale=None, workspace=None, out=None):
+    """attn_decode with a sliding window: the query at position q attends to keys q - window .. q."""
+    B, Hq, D = q_rot.shape
+    _, max_len, Hkv, _ = k_cache.shape
+    ctx, st, lib = _c(2)
+    if workspace is None:
+        workspace = attn_decode_workspace(B, Hq, D, max_len, q_rot.device)
+    if out is None:
+        out = torch.empty_like(q_rot)
+    if scale is None:
+        scale = 1.0 / math.sqrt(D)
+    with _Timed("attn_decode"):
+        check(lib.xaxb_attn_decode_window(ctx, st, ptr(q_rot), ptr(k_cache), ptr(v_cache), ptr(positions), B, Hq, Hkv, D,
+                                          max_len, float(scale), int(window), ptr(out), ptr(workspace),
+                                          workspace.numel() * 4), "attn_decode_window")
+    return out
+
+
+def attn_prefill_window(q_rot, k_cache, v_cache, positions, B, T, window: int, *, scale=None, out=None):
+    """attn_prefill with a sliding window."""
+    _, Hq, D = q_rot.shape
+    _, max_len, Hkv, _ = k_cache.shape
+    ctx, st, lib = _c()
+    if out is None:
+        out = torch.empty_like(q_rot)
+    if scale is None:
+        scale = 1.0 / math.sqrt(D)
+    check(lib.xaxb_attn_prefill_window(ctx, st, ptr(q_rot), ptr(k_cache), ptr(v_cache), ptr(positions), B, T, Hq, Hkv, D,
+                                       max_len, float(scale), int(window), ptr(out)), "attn_prefill_window")
+    return out
+
+
 def attn_decode_cast(q_rot, k_cache, v_cache, positions, *, scale=None, k_is_rotated=True, cos=None, sin=None,
                      workspace=None, want_out=False):
     """Decode attention whose output row [Hq*D] per sequence is cast to e4m3 with a per-token
