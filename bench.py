@@ -9,7 +9,9 @@ tokens/s device-timed over K CUDA-graph replays (`value`), the same through the 
 step API with pinned host token buffers (`e2e`), the roofline of the dominant kernel (decode
 attention), the CPU oracle timed on a bounded sample (`cpu_baseline`), SM clocks sampled
 during the timed region, and per-kernel figures for benchmark configs 1 and 3 (`kernels`).
-With N > 1 (torchrun) the model is tensor-parallel over N GPUs: strong scaling.
+With N > 1 (torchrun) the model is tensor-parallel over N GPUs: strong scaling; the line then
+also carries `parity`, the first block's output on the sharded model against the unsharded one.
+`config` is the same in both arms; what only describes how this arm ran sits under `run`.
 """
 
 from __future__ import annotations
@@ -88,7 +90,8 @@ class ClockSampler:
 def oracle_decode_sample(w: dict, seconds_budget: float, steps: int, warmup: int):
     """Times the CPU oracle (the reference's algorithm restated in NumPy) on a bounded sample of
     the decode workload: ONE transformer layer of the workload's shape plus the lm_head, ONE
-    sequence, a short context; a full step is extrapolated as layers * t_layer + t_head."""
+    sequence, at the workload's context (the prompt length); a full step of one sequence is
+    extrapolated as layers * t_layer + t_head."""
     import numpy as np
 
     from oracle import llm as ollm
@@ -98,12 +101,14 @@ def oracle_decode_sample(w: dict, seconds_budget: float, steps: int, warmup: int
                          rms_eps=1e-5)
     rng = np.random.default_rng(0)
     om = ollm.LLM.build(cfg, rng, use_fp8=True, tie=w["tied"])
-    ctx = 64
+    ctx = w["prompt"]
     caches = om.init_cache(ctx + warmup + steps + 1)
-    toks = rng.integers(0, w["vocab"], ctx).astype(np.int32)
-    x = om.embed_tokens(toks)
-    _, c0 = om.blocks[0].forward(x, cache=caches[0])
-    caches = [c0]
+    # the cache of the sample sequence: seeded N(0,1) rows stand in for a prefill (untimed either way)
+    c0 = caches[0]["self_attn"]
+    c0["k"][:ctx] = rng.standard_normal((ctx,) + c0["k"].shape[1:], dtype=np.float32).astype(c0["k"].dtype)
+    c0["v"][:ctx] = rng.standard_normal((ctx,) + c0["v"].shape[1:], dtype=np.float32).astype(c0["v"].dtype)
+    c0["position"] = np.int32(ctx)
+    caches = [caches[0]]
     t_layer, t_head = [], []
     t_start = time.perf_counter()
     tok = np.array([1], np.int32)
@@ -126,8 +131,8 @@ def oracle_decode_sample(w: dict, seconds_budget: float, steps: int, warmup: int
     tl, th = float(np.median(t_layer)), float(np.median(t_head))
     step_s = w["layers"] * tl + th  # one sequence
     return {"tokens_per_s": 1.0 / step_s, "step_s_one_sequence": step_s, "steps_timed": done,
-            "sample": f"NumPy oracle, 1 of {w['layers']} layers + lm_head, 1 of {w['batch']} sequences, context {ctx} "
-                      f"(not {w['prompt']}+); step time extrapolated as {w['layers']}*t_layer+t_head; "
+            "sample": f"NumPy oracle, 1 of {w['layers']} layers + lm_head, 1 of {w['batch']} sequences, context {ctx}; "
+                      f"step time extrapolated as {w['layers']}*t_layer+t_head; "
                       f"{done} steps timed; the reference re-quantises every weight on every call and so does this"}
 
 
@@ -200,6 +205,15 @@ def kernel_figures(peak_gbs: float) -> dict:
     t = _time_kernel(lambda i: ops.gemm_fp8(xq, wq, x_inv, w_inv[:1], bias, out=o), flush=flush)
     out["gemm_fp8_cfg1"] = {"tflops": 2.0 * M * N * K / t / 1e12, "us": t * 1e6,
                             "frac_of_4500_nominal": 2.0 * M * N * K / t / 4.5e15}
+    # Yardstick on the same box, bench side only (never on the product path): the vendor library's FP8
+    # GEMM (cuBLASLt through torch._scaled_mm) on the same operands, per-tensor scales, bias, bf16 out.
+    one = torch.ones((), device=dev)
+    try:
+        t = _time_kernel(lambda i: torch._scaled_mm(xq, wq.t(), scale_a=one, scale_b=one, bias=bias,
+                                                    out_dtype=torch.bfloat16), flush=flush)
+        out["cublaslt_fp8_cfg1"] = {"tflops": 2.0 * M * N * K / t / 1e12, "us": t * 1e6}
+    except Exception as e:  # noqa: BLE001
+        out["cublaslt_fp8_cfg1"] = {"error": repr(e)[:200]}
     M2 = N2 = K2 = 8192
     a8 = (torch.randn((M2, K2), generator=g, device=dev)).to(torch.float8_e4m3fn)
     b8 = (torch.randn((N2, K2), generator=g, device=dev)).to(torch.float8_e4m3fn)
@@ -207,6 +221,12 @@ def kernel_figures(peak_gbs: float) -> dict:
     t = _time_kernel(lambda i: ops.gemm_fp8(a8, b8, None, None, None, out=o2), iters=10, flush=flush)
     out["gemm_fp8_8192"] = {"tflops": 2.0 * M2 * N2 * K2 / t / 1e12, "us": t * 1e6,
                             "frac_of_4500_nominal": 2.0 * M2 * N2 * K2 / t / 4.5e15}
+    try:
+        t = _time_kernel(lambda i: torch._scaled_mm(a8, b8.t(), scale_a=one, scale_b=one, out_dtype=torch.bfloat16),
+                         iters=10, flush=flush)
+        out["cublaslt_fp8_8192"] = {"tflops": 2.0 * M2 * N2 * K2 / t / 1e12, "us": t * 1e6}
+    except Exception as e:  # noqa: BLE001
+        out["cublaslt_fp8_8192"] = {"error": repr(e)[:200]}
     del a8, b8, o2
     # ---- cfg3: B=32, 32q/8kv x 128, lengths U[512, 8192], theta 5e5
     B, Hq, Hkv, D, max_len = 32, 32, 8, 128, 8192
@@ -226,7 +246,39 @@ def kernel_figures(peak_gbs: float) -> dict:
                                                sin=sin), flush=flush)
     out["attn_decode_cfg3_rope_on_load"] = {"gbs": nbytes / t / 1e9, "frac_of_hbm_peak": nbytes / t / 1e9 / peak_gbs,
                                             "us": t * 1e6}
+    del kc, vc
+    out["block_prefill_cfg2"] = block_prefill_figure(flush)
     return out
+
+
+def block_prefill_figure(flush) -> dict:
+    """cfg2: one pre-norm block, prefill of 4 sequences x 1024 tokens (hidden 2048, 16 query / 4 kv heads
+    x 128, SwiGLU 5632, FP8 linears for QKV / out / MLP), captured in a CUDA graph so the figure is device
+    time of the kernel chain.  FLOPs: the seven linears plus causal attention (half of the full square)."""
+    import torch
+
+    from xax_b200.arch.attention import TransformerBlock
+
+    B, T, H, Hq, Hkv, D, F = 4, 1024, 2048, 16, 4, 128, 5632
+    blk = TransformerBlock.build(H, Hq, F, key=0, num_kv_heads=Hkv, head_dim=D, causal=True,
+                                 use_rotary_embeddings=True, rotary_base=10000.0, norm_type="rmsnorm", norm_eps=1e-5,
+                                 feedforward_type="swiglu", use_fp8=True, fp8_mlp=True)
+    g = torch.Generator(device="cuda").manual_seed(2)
+    x = torch.randn((B * T, H), generator=g, device="cuda").to(torch.bfloat16)
+    cache = blk.self_attn.init_cache(T, batch=B)
+    blk.forward_tokens(x, B, T, cache=cache, advance=False)  # quantises the weights, sizes the allocator
+    graph = torch.cuda.CUDAGraph()
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        blk.forward_tokens(x, B, T, cache=cache, advance=False)
+    torch.cuda.current_stream().wait_stream(side)
+    with torch.cuda.graph(graph):
+        blk.forward_tokens(x, B, T, cache=cache, advance=False)
+    t = _time_kernel(lambda i: graph.replay(), iters=10, flush=flush)
+    lin = 2.0 * B * T * (H * (Hq + 2 * Hkv) * D + Hq * D * H + 3 * H * F)
+    att = 4.0 * B * Hq * T * T * D / 2
+    return {"us": t * 1e6, "tflops": (lin + att) / t / 1e12, "linear_gflop": lin / 1e9, "attention_gflop": att / 1e9}
 
 
 # ---------------------------------------------------------------------------------------
@@ -277,13 +329,20 @@ def main() -> None:
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
     tp = None
+    host_group = None
     if world > 1:
+        # NCCL carries barriers, the prefill's all-reduces and a few scalars; its NVLink multicast
+        # path is not needed and stays off, so that ranks may leave without tearing NCCL down.
+        os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
         dist.init_process_group("nccl", device_id=dev)
+        host_group = dist.new_group(backend="gloo")  # host-side barriers: a waiting rank leaves its GPU idle
         from xax_b200.parallel import TensorParallel
 
         tp = TensorParallel(rank, world, local_amax=os.environ.get("XAXB_TP_AMAX", "global") == "local")
     from xax_b200 import _lib, ops
     from xax_b200.arch.llm import LLM, DecodeState, LLMConfig, tie_embedding_and_head
+
+    run_info: dict = {}
 
     cfg = LLMConfig(vocab_size=w["vocab"], embed_dim=w["hidden"], q_heads=w["q_heads"], kv_heads=w["kv_heads"],
                     head_dim=w["head_dim"], num_layers=w["layers"], mlp_hidden_dim=w["ffn"], rope_theta=w["theta"],
@@ -296,11 +355,10 @@ def main() -> None:
         tp.shard_lm_head(model)
         if os.environ.get("XAXB_TP_EXCHANGE", "peer") != "nccl":
             tp.enable_peer_exchange(dev, rows=w["batch"], cols=w["hidden"])
-        base["config"]["tp_exchange"] = "peer-memory kernels" if tp.peer is not None else "nccl"
-        base["config"]["tp_amax"] = ("per-rank slice (deviation from the reference)" if tp.local_amax
-                                     else "max over ranks (the reference's per-token scale)")
-    base["config"]["launch"] = ("stream-ordered" if world > 1 or os.environ.get("XAXB_PROGRAMMATIC_LAUNCH", "1")[:1] == "0"
-                                else "programmatic dependent launch")
+        run_info["tp_exchange"] = "peer-memory kernels" if tp.peer is not None else "nccl"
+        run_info["tp_amax"] = ("per-rank slice (deviation from the reference)" if tp.local_amax
+                               else "max over ranks (the reference's per-token scale)")
+    run_info["launch"] = "programmatic dependent launch" if _lib.load().xaxb_programmatic_launch_enabled() else "stream-ordered"
     B, T0 = w["batch"], w["prompt"]
     K = args.steps
     max_len = (T0 + warmup + K + 8 + 127) // 128 * 128
@@ -326,9 +384,11 @@ def main() -> None:
         torch.cuda.synchronize()
         t_prefill = e0.elapsed_time(e1) * 1e-3
     _lib.device_status()
-    ops.LAUNCH_COUNT = 0
+    parity = tp_block_parity(tp, model, cfg, w, dev) if tp is not None else None
+    lib = _lib.load()
+    lib.xaxb_launch_count(1)
     st.capture()
-    launches_per_step = ops.LAUNCH_COUNT // 2  # capture() runs the step twice (warm-up + capture)
+    launches_per_step = int(lib.xaxb_launch_count(1)) // 2  # capture() runs the step twice (warm-up + capture)
 
     def barrier():
         if world > 1:
@@ -377,13 +437,28 @@ def main() -> None:
     peak, peak_kind = measured_peaks()
     hkv_local, hq_local, D = w["kv_heads"] // world, w["q_heads"] // world, w["head_dim"]
     st.positions.fill_(int(mean_len_timed) - 1)  # representative length: the mean of the timed region
-    ops.KERNEL_TIMES = []
+    events: list = []
+
+    def timed(fn):
+        def wrapper(*a, **k):
+            e_a, e_b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e_a.record()
+            r = fn(*a, **k)
+            e_b.record()
+            events.append((e_a, e_b))
+            return r
+        return wrapper
+
+    saved = {n: getattr(ops, n) for n in ("attn_decode", "attn_decode_cast", "attn_decode_cast_tp")}
+    for n, fn in saved.items():  # the model reaches decode attention through one of these three
+        setattr(ops, n, timed(fn))
     n_eager = 2
     for _ in range(n_eager):
         st.step()
     torch.cuda.synchronize()
-    durs = [a.elapsed_time(b) * 1e-3 for name, a, b in ops.KERNEL_TIMES if name == "attn_decode"]
-    ops.KERNEL_TIMES = None
+    for n, fn in saved.items():
+        setattr(ops, n, fn)
+    durs = [a.elapsed_time(b) * 1e-3 for a, b in events]
     attn_len = int(mean_len_timed) + 0.5
     attn_bytes = B * attn_len * (2 * hkv_local * D * 2) + 2 * B * hq_local * D * 2
     avg = sum(durs) / max(len(durs), 1)
@@ -392,17 +467,21 @@ def main() -> None:
                 "frac": attn_bytes / avg / 1e9 / peak,
                 # DRAM bytes per launch: ncu on a smaller case of the same kernel (B=32, same context, heads)
                 # measured dram read+write = 1.088 x the algorithmic bytes; traffic is proportional to tokens x
-                # kv heads, so the factor carries over (profiles/attn_decode_kernel_small_case_ncu.md)
+                # kv heads, so the factor carries over
                 "traffic": attn_bytes * 1.088, "bytes_per_launch": attn_bytes,
                 "avg_launch_us": avg * 1e6, "launches_timed": len(durs)}
     _lib.device_status()
 
     if rank != 0:
-        if world > 1:
-            dist.barrier()
-            _leave()
-        return
+        # The other ranks have nothing left to compute: they wait on the host (no kernel spins on
+        # their GPUs) until rank 0 has printed its line, then leave.
+        torch.cuda.synchronize()
+        dist.barrier(group=host_group)
+        _leave()
     line = dict(base)
+    line["run"] = run_info
+    if parity is not None:
+        line["parity"] = parity
     line.update({"value": B * K / elapsed, "ms_per_step": elapsed / K * 1e3, "clocks": clocks,
                  "e2e": {"value": B * K / e2e_elapsed, "unit": unit, "h2d_bytes_per_step": B * 4,
                          "d2h_bytes_per_step": B * 4, "ms_per_step": e2e_elapsed / K * 1e3},
@@ -424,13 +503,46 @@ def main() -> None:
         line["cpu_baseline"] = None
     print(json.dumps(line), flush=True)
     if world > 1:
-        dist.barrier()
+        dist.barrier(group=host_group)
         _leave()
+
+
+def tp_block_parity(tp, model, cfg, w: dict, dev) -> dict:
+    """First transformer block, one decode step of the workload's batch at position 0: the sharded
+    block (every rank takes part) against the same block unsharded on rank 0, whose full weights
+    are re-drawn from the model's seed (LLM.build draws whole tensors and slices them, in a fixed
+    order, so a one-layer build with the same seed holds block 0's full tensors).  Relative
+    Frobenius error of the block output, computed on rank 0."""
+    from dataclasses import replace
+
+    import torch
+
+    from xax_b200.arch.llm import LLM
+
+    B = w["batch"]
+    gen = torch.Generator(device=dev).manual_seed(7)
+    toks = torch.randint(0, w["vocab"], (B,), generator=gen, device=dev, dtype=torch.int32)
+    x = model.embed_tokens(toks)
+    blk = model.blocks[0]
+    cache = blk.self_attn.init_cache(128, batch=B, device=dev)
+    if tp.peer is not None and tp.peer.exchanges & 1:  # keep the two data buffers alternating in step
+        tp.all_reduce_sum(tp.partial_out(B, x.shape[1]).zero_())
+    y_tp, _ = tp.block_forward(blk, x, B, 1, cache=cache)
+    out = {"what": f"block 0, one decode step, batch {B}: tp{tp.size} vs unsharded, relative Frobenius error"}
+    if tp.rank == 0:
+        full = LLM.build(replace(cfg, num_layers=1), key=0, use_fp8=True, init_std=0.02, device=dev)
+        fb = full.blocks[0]
+        y_1, _ = fb.forward_tokens(x, B, 1, cache=fb.self_attn.init_cache(128, batch=B, device=dev))
+        out["block0_rel_fro"] = float((y_tp.float() - y_1.float()).norm() / y_1.float().norm())
+        del full, fb
+        torch.cuda.empty_cache()
+    return out
 
 
 def _leave() -> None:
     """Multi-rank exit.  Tearing down an NCCL process group whose collectives were captured in a
-    CUDA graph can block forever, so the ranks synchronise, flush and leave without it."""
+    CUDA graph can block for the whole time limit, so the ranks synchronise, flush and leave without
+    it; by then every rank has passed the last host-side barrier with its GPU idle."""
     import torch
 
     torch.cuda.synchronize()

@@ -9,7 +9,7 @@
  * Conventions
  *   - every pointer except `ctx`, `stream` and out-parameters of the ctx_* calls is a
  *     DEVICE pointer owned by the caller; no entry point allocates or frees device memory
- *     (xaxb_ctx_create allocates one 4-byte status word, released by xaxb_ctx_destroy);
+ *     (xaxb_ctx_create allocates one 32-byte status block, released by xaxb_ctx_destroy);
  *   - `stream` is a cudaStream_t passed as void*; all work is stream-ordered and returns
  *     without synchronising, so calls may be captured in a CUDA graph;
  *   - the return value is an xaxb_status; device-side waits that ran out of time are
@@ -54,6 +54,17 @@ const char* xaxb_last_error(void);
  * predecessor before touching memory another kernel touches.  Results do not depend on it; 0
  * restores plain stream-ordered launches.  No counterpart in the reference. */
 int xaxb_set_programmatic_launch(int on);
+int xaxb_programmatic_launch_enabled(void); /* 1 / 0: the switch's current state */
+/* Number of kernels this library has launched in the process since the counter was last reset
+ * (reset != 0 returns the count and clears it).  Launches recorded into a CUDA graph count once,
+ * at capture; replays do not pass through the library.  No counterpart in the reference. */
+long long xaxb_launch_count(int reset);
+/* Limits of the bounded device-side waits of this context, in milliseconds: `local_ms` for waits
+ * inside one GPU (shared-memory barriers fed by TMA / tensor-core completions; default 1000),
+ * `peer_ms` for waits on flags that another GPU raises (default 10000).  0 restores the default.
+ * A wait that runs out records XAXB_DEVICE_TIMEOUT and its site (xaxb_ctx_status) and the kernel
+ * runs to its normal end.  Synchronises with the device.  No counterpart in the reference. */
+int xaxb_set_wait_limit_ms(xaxb_ctx* ctx, int local_ms, int peer_ms);
 
 /* ---- kernel 1: amax / scale / e4m3 cast ------------------------------------------- */
 
@@ -216,6 +227,8 @@ int64_t xaxb_attn_decode_workspace_bytes(int64_t B, int64_t Hq, int64_t D, int64
  * cos/sin table (cos/sin may be NULL otherwise).  out: bf16 [B, Hq, D].
  * Split over 128-token chunks; per-chunk partial results go through `workspace`
  * (xaxb_attn_decode_workspace_bytes; contents need no initialisation).
+ * A position outside 0 .. max_len - 1 is clamped into that range and reported as
+ * XAXB_CACHE_OVERFLOW (site 15) through the device status word; the output stays finite.
  */
 int xaxb_attn_decode(xaxb_ctx* ctx, void* stream, const void* q_rot_bf16, const void* k_cache_bf16,
                      const void* v_cache_bf16, const int32_t* positions, int64_t B, int64_t Hq, int64_t Hkv,
@@ -231,9 +244,8 @@ int xaxb_attn_decode_window(xaxb_ctx* ctx, void* stream, const void* q_rot_bf16,
                             int64_t D, int64_t max_len, float softmax_scale, int64_t window, void* out_bf16,
                             void* workspace, int64_t workspace_bytes);
 
-/* Test hook: 0 = automatic choice of the decode-attention kernel (currently 1), 1 = the
- * chunk-walking kernel with its own choice of chunks per CTA, 2 = persistent software-pipelined
- * kernel, 10 + n (n = 1 .. 64) = the chunk-walking kernel with n 128-token chunks per CTA.
+/* Test hook: how many 128-token chunks one CTA of the decode-attention kernel walks.  0 or 1 = the
+ * library's own choice (about four, fewer when that would leave SMs idle), 10 + n (n = 1 .. 64) = n.
  * Process-wide.  No counterpart in the reference. */
 int xaxb_attn_decode_force_variant(int variant);
 

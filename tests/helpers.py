@@ -97,3 +97,49 @@ def llm_from_oracle(om, device="cuda"):
     head = Linear(hw.shape[1], hw.shape[0], use_bias=False, weight=hw)
     return LLM(embed, [block_from_oracle(b, device) for b in om.blocks],
                RMSNorm(to_torch(om.norm.weight, device), om.norm.eps), head, cfg)
+
+
+def attn_setup(ops, B, T, Hq, Hkv, D, max_len, starts, theta, seed, rotated=True):
+    """Seeded decode / prefill attention case shared by the kernel tests: K/V caches holding ``starts[b]``
+    tokens per sequence (K stored rotated like the reference, or as projected when ``rotated`` is False), T
+    new tokens per sequence appended through the device kernel (checked bit for bit against the oracle's
+    rotation), and the oracle's attention output for the new tokens."""
+    from oracle.attention import RotaryEmbedding
+
+    rng = np.random.default_rng(seed)
+    rope = RotaryEmbedding(D, theta, "concatenated")
+    kc = np.zeros((B, max_len, Hkv, D), bf16)
+    vc = np.zeros((B, max_len, Hkv, D), bf16)
+    k_raw = np.zeros_like(kc)
+    for b in range(B):
+        n = starts[b]
+        kr = rng.standard_normal((n, Hkv, D)).astype(np.float32).astype(bf16)
+        k_raw[b, :n] = kr
+        kc[b, :n] = rope.apply_rotary_embeddings(kr, np.arange(n, dtype=np.int32)) if n else kr
+        vc[b, :n] = rng.standard_normal((n, Hkv, D)).astype(np.float32).astype(bf16)
+    qkv = rng.standard_normal((B * T, (Hq + 2 * Hkv) * D)).astype(np.float32).astype(bf16)
+    cos, sin = ops.rope_tables(D, theta, max_len, "cuda")
+    pos = to_torch(np.asarray(starts, np.int32))
+    kct, vct = to_torch(kc if rotated else k_raw), to_torch(vc)
+    q_rot = ops.kv_append_rope(to_torch(qkv), B, T, Hq, Hkv, D, pos, cos, sin, kct, vct, store_rotated_k=rotated)
+    # oracle: rotate q, k of the new tokens and append
+    exp_out = np.zeros((B * T, Hq, D), bf16)
+    from oracle.attention import dot_product_attention
+
+    for b in range(B):
+        rows = qkv[b * T:(b + 1) * T]
+        q = rows[:, :Hq * D].reshape(T, Hq, D)
+        k = rows[:, Hq * D:(Hq + Hkv) * D].reshape(T, Hkv, D)
+        v = rows[:, (Hq + Hkv) * D:].reshape(T, Hkv, D)
+        p = (np.arange(T) + starts[b]).astype(np.int32)
+        qr, kr = rope.apply_rotary_embeddings(q, p), rope.apply_rotary_embeddings(k, p)
+        kc[b, starts[b]:starts[b] + T] = kr
+        vc[b, starts[b]:starts[b] + T] = v
+        S = starts[b] + T
+        allow = np.arange(S)[None, :] <= p[:, None]
+        exp_out[b * T:(b + 1) * T] = dot_product_attention(qr, kc[b, :S], vc[b, :S], mask=allow)
+        assert np.array_equal(to_numpy(q_rot)[b * T:(b + 1) * T].view(np.uint16), qr.view(np.uint16))
+    if rotated:
+        assert np.array_equal(to_numpy(kct).view(np.uint16), kc.view(np.uint16))
+    assert np.array_equal(to_numpy(vct).view(np.uint16), vc.view(np.uint16))
+    return q_rot, kct, vct, pos, cos, sin, exp_out

@@ -250,12 +250,16 @@ def test_llm_reduced_cfg4_layerwise_and_logits():
     Every FP8 cast is discontinuous, so two correct FP8 pipelines that differ in the last bit of
     one GEMM output drift apart over chained layers: the reference's own two executions of this
     model -- CPU "dequantise, bf16 matmul" and GPU "FP8 matmul" (xax/nn/fp8.py:3-11) -- differ by
-    7 % after one block and 13 % at the logits (oracle against oracle, no GPU involved).  Single
-    linears and single attention calls meet 1e-2 against the strict oracle (test_kernels_gpu.py);
-    here the stack is checked
-      * layer by layer, fed the activations of the oracle run with FP8-matmul semantics: <= 1e-2;
+    several per cent after one block and more at the logits (oracle against oracle, no GPU involved).
+    Single linears and single attention calls meet 1e-2 against the strict oracle (test_kernels_gpu.py,
+    test_baseline_shapes_gpu.py); here the stack is checked
+      * layer by layer, each layer fed the activations of the oracle run with FP8-matmul semantics:
+        no further from that execution than the reference's other execution (QDQ) of the same layer on
+        the same input is (+25 %);
       * logits from the oracle's final hidden state: <= 1e-2 and >= 99 % top-1 agreement;
-      * free-running against both oracle executions: bounded (printed for the record)."""
+      * free-running logits against both oracle executions: no further from either than they are from
+        each other (+25 %).
+    The measured figures are printed for the record."""
     from oracle import fp8 as ofp8
     from oracle import llm as ollm
 
@@ -271,25 +275,89 @@ def test_llm_reduced_cfg4_layerwise_and_logits():
         layer_in, finals, exp_fp8 = _oracle_pass(om, toks)
     finally:
         ofp8.MATMUL_MODE = "qdq"
-    errs = []
+    errs, refs = [], []
     for i, blk in enumerate(m.blocks):
         out, _ = blk.forward_tokens(to_torch(layer_in[i]).reshape(B * T, -1), B, T)
         nxt = layer_in[i + 1] if i + 1 < len(m.blocks) else finals
         errs.append(rel_fro(f32(to_numpy(out)).reshape(B, T, -1), f32(nxt)))
-    print("teacher-forced per-layer rel err vs FP8-matmul oracle:", [f"{e:.2e}" for e in errs])
+        qdq_out = np.stack([om.blocks[i].forward(layer_in[i][b])[0] for b in range(B)])  # QDQ execution, same input
+        refs.append(rel_fro(f32(qdq_out), f32(nxt)))
+    print("teacher-forced per-layer rel err vs FP8-matmul oracle:", [f"{e:.2e}" for e in errs],
+          "| QDQ oracle vs FP8-matmul oracle, same layer, same input:", [f"{e:.2e}" for e in refs])
     h = m.norm(to_torch(finals).reshape(B * T, -1))
     got = f32(to_numpy(m.get_logits(h))).reshape(B, T, -1)
-    assert rel_fro(got, f32(exp_fp8)) < TOL
-    assert np.mean(np.argmax(got, -1) == np.argmax(f32(exp_fp8), -1)) >= 0.99
+    head_err = rel_fro(got, f32(exp_fp8))
+    head_top1 = np.mean(np.argmax(got, -1) == np.argmax(f32(exp_fp8), -1))
+    print(f"lm_head on the oracle's final hidden state: rel err {head_err:.2e}, top-1 {head_top1:.4f}")
+    assert head_err < TOL and head_top1 >= 0.99
     logits, _ = m.forward_batch(to_torch(toks))
     free = f32(to_numpy(logits))
     e_fp8, e_qdq = rel_fro(free, f32(exp_fp8)), rel_fro(free, f32(exp_qdq))
     agree = np.mean(np.argmax(free, -1) == np.argmax(f32(exp_fp8), -1))
+    agree_oo = np.mean(np.argmax(f32(exp_qdq), -1) == np.argmax(f32(exp_fp8), -1))
     oo = rel_fro(f32(exp_fp8), f32(exp_qdq))
     print(f"free-running logits: {e_fp8:.3e} vs FP8-matmul oracle (top-1 {agree:.3f}), {e_qdq:.3e} vs QDQ oracle; "
-          f"oracle vs oracle {oo:.3e}")
-    # no further from either execution of the reference than they are from each other (+25 %)
-    assert max(errs) < 0.1 and e_fp8 < 1.25 * oo and e_qdq < 1.25 * oo
+          f"oracle vs oracle {oo:.3e} (top-1 {agree_oo:.3f})")
+    for e, r in zip(errs, refs):
+        assert e < 1.25 * r + 2e-3, (errs, refs)
+    assert e_fp8 < 1.25 * oo and e_qdq < 1.25 * oo
+
+
+def test_fp8_stack_greedy_64_steps_top1_agreement():
+    """Greedy decoding of an FP8 stack over 64 new tokens against the oracle's loop (FP8-matmul execution).
+
+    Two models of the reduced config-4 shape.  With independent random weights the logits are nearly flat
+    (the top-1 margin is a fraction of the FP8 rounding noise), and no two executions -- the reference's own
+    two included -- pick the same tokens for long: the figure is printed, and the bar is that the device
+    agrees with the FP8-matmul oracle at least as often as the reference's QDQ execution does, minus 10
+    points.  With the embedding tied to the head and the blocks' output projections scaled by 0.1 the residual
+    stream carries the input token, the median top-1 margin is about ten times the rounding noise (margins of
+    that order are what a trained model has), and the bar is the path's stated one: >= 99 % top-1 agreement,
+    teacher-forced and free-running."""
+    from oracle import fp8 as ofp8
+    from oracle import llm as ollm
+    from xax_b200.arch.llm import llm_generate_batch
+
+    ofp8.CACHE_WEIGHT_QUANT = True
+    try:
+        for tied, bar in ((False, None), (True, 0.99)):
+            cfg = ollm.LLMConfig(vocab_size=2048, embed_dim=512, q_heads=8, kv_heads=2, head_dim=64, num_layers=4,
+                                 mlp_hidden_dim=1408, rms_eps=1e-5)
+            om = ollm.LLM.build(cfg, np.random.default_rng(3), use_fp8=True, tie=tied, std=0.05)
+            if tied:
+                for blk in om.blocks:
+                    for lin in (blk.self_attn.output_proj, blk.feed_forward.down):
+                        lin.weight = (f32(lin.weight) * np.float32(0.1)).astype(bf16)
+            m = llm_from_oracle(om)
+            prompt = np.random.default_rng(4).integers(0, 2048, 16).astype(np.int32)
+            n_new = 64
+            ofp8.MATMUL_MODE = "fp8_gemm"
+            try:
+                exp, _ = ollm.llm_generate_greedy(om, prompt, -1, n_new)
+                tf_logits = f32(om.forward(exp[:-1]))  # the oracle's logits along its own token history
+            finally:
+                ofp8.MATMUL_MODE = "qdq"
+            qdq_logits = f32(om.forward(exp[:-1]))
+            got, _ = llm_generate_batch(m, to_torch(prompt.reshape(1, -1)), n_new)
+            got = got[0].cpu().numpy()
+            free = float(np.mean(got[16:] == exp[16:]))
+            first_diff = int(np.argmax(got != exp)) if (got != exp).any() else len(exp)
+            dev_logits, _ = m.forward_batch(to_torch(exp[:-1].reshape(1, -1)))
+            dev_logits = f32(to_numpy(dev_logits))[0]
+            tf = float(np.mean(np.argmax(dev_logits[15:], -1) == exp[16:]))
+            tf_ref = float(np.mean(np.argmax(qdq_logits[15:], -1) == exp[16:]))
+            srt = np.sort(tf_logits[15:], axis=-1)
+            margin = float(np.median(srt[:, -1] - srt[:, -2]))
+            noise = float(np.sqrt(np.mean((dev_logits[15:] - tf_logits[15:]) ** 2)))
+            print(f"greedy 64 steps, tied={tied}: free-running top-1 {free:.3f} (first difference at token {first_diff} of "
+                  f"{len(exp)}), teacher-forced top-1 {tf:.3f} (reference QDQ vs FP8-matmul execution: {tf_ref:.3f}); "
+                  f"median top-1 margin {margin:.3e}, rms logit difference {noise:.3e}")
+            if bar is None:
+                assert tf >= tf_ref - 0.10, (tf, tf_ref)
+            else:
+                assert tf >= bar and free >= bar, (tf, free)
+    finally:
+        ofp8.CACHE_WEIGHT_QUANT = False
 
 
 @pytest.mark.parametrize("style", ["concatenated", "interleaved"])

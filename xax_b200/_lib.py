@@ -38,6 +38,9 @@ SIGNATURES: dict[str, tuple] = {
     "xaxb_status_string": (c_char_p, [_I]),
     "xaxb_last_error": (c_char_p, []),
     "xaxb_set_programmatic_launch": (_I, [_I]),
+    "xaxb_programmatic_launch_enabled": (_I, []),
+    "xaxb_launch_count": (ctypes.c_longlong, [_I]),
+    "xaxb_set_wait_limit_ms": (_I, [_P, _I, _I]),
     "xaxb_quantize_current": (_I, [_P, _P, _P, _I64, _I64, _I64, _P, _P, _P, _P]),
     "xaxb_quantize_delayed": (_I, [_P, _P, _P, _I64, _I64, _P, _P, _I, _P, _P, _P, _P, _P]),
     "xaxb_quantize_with_amax": (_I, [_P, _P, _P, _I64, _I64, _I64, _P, _P, _P, _P]),

@@ -12,8 +12,8 @@ vmapped reference: per-token activation scales inside attention projections
 
 Caches are donated: ``forward(..., cache=c)`` appends into ``c``'s buffers and returns a
 cache sharing them (the reference donates at its jit boundary, xax/arch/llm.py:1446).
-Pass ``donate=False`` to copy first.  Outside the path (not built): cross-attention, LoRA,
-QK-norm, attention sinks, sliding windows, LayerNorm / MLP feed-forward.
+Pass ``donate=False`` to copy first.  QK-norm, sliding windows and attention sinks are built.
+Outside the path: LayerNorm / MLP feed-forward variants of the block.
 """
 
 from __future__ import annotations
@@ -61,6 +61,17 @@ class Embedding:
 
     def __call__(self, token):
         return ops.embed(torch.as_tensor(token, dtype=torch.int32, device=self.weight.device).reshape(-1), self.weight)[0]
+
+
+def _weights_key(*layers):
+    """Identity of the weights (and biases) a stacked operand was built from: reassigning or updating
+    one of them in place makes the stacked copy stale."""
+    out = []
+    for m in layers:
+        wq = m.weight_q_current()[0] if isinstance(m, Fp8Linear) and m.use_fp8 else None  # (re)made if stale
+        for t in (m.weight, m.bias, wq):
+            out.append(None if t is None else (t.data_ptr(), t._version))
+    return tuple(out)
 
 
 def apply_linear(x: torch.Tensor, linear, *, residual: torch.Tensor | None = None) -> torch.Tensor:
@@ -132,6 +143,7 @@ class SwiGLU:
     def __init__(self, gate, up, down):
         self.gate, self.up, self.down = gate, up, down
         self._fused = None
+        self._fused_key = None
 
     @classmethod
     def build(cls, embed_dim: int, hidden_dim: int | None = None, *, key=None, use_bias: bool = False,
@@ -151,6 +163,10 @@ class SwiGLU:
 
     def fused_gate_up(self):
         """gate | up weights stacked into one [2F, H] operand so one GEMM reads x once."""
+        key = _weights_key(self.gate, self.up)
+        if self._fused is not None and self._fused_key != key:
+            self._fused = None
+        self._fused_key = key
         if self._fused is None:
             if self.is_fp8():
                 gq, g_inv = self.gate.weight_q_current()
@@ -329,6 +345,7 @@ class SelfAttentionBlock:
         self.num_heads, self.num_kv_heads, self.head_dim = num_heads, num_kv_heads, head_dim
         self.causal, self.local_window_size, self.use_fp8 = causal, local_window_size, use_fp8
         self._fused = None
+        self._fused_key = None
 
     @classmethod
     def build(cls, embed_dim: int, num_heads: int, *, key=None, num_kv_heads: int | None = None,
@@ -366,6 +383,10 @@ class SelfAttentionBlock:
     def fused_qkv(self):
         """q | k | v weights stacked into one [(Hq + 2 Hkv) D, H] operand; per-column
         dequantisation multipliers keep each projection's own weight scale."""
+        key = _weights_key(self.q_proj, self.k_proj, self.v_proj)
+        if self._fused is not None and self._fused_key != key:
+            self._fused = None
+        self._fused_key = key
         if self._fused is None:
             projs = (self.q_proj, self.k_proj, self.v_proj)
             if self._is_fp8():

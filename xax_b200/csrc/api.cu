@@ -1,4 +1,5 @@
 // Context, status reporting and tensor-map construction for the C ABI.
+#include <atomic>
 #include <cstdarg>
 #include <cstdio>
 #include <cstdlib>
@@ -25,6 +26,10 @@ static bool pdl_default() {
 static bool g_pdl = pdl_default();
 bool pdl_enabled() { return g_pdl; }
 void set_pdl_enabled(bool on) { g_pdl = on; }
+
+// Kernels launched by this library in this process (all contexts, all streams).
+static std::atomic<long long> g_launches{0};
+void count_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }
 
 int check_launch(const char* what) {
   cudaError_t e = cudaGetLastError();
@@ -132,8 +137,11 @@ int xaxb_ctx_create(int device, xaxb_ctx** out) {
     delete c;
     return XAXB_UNSUPPORTED;
   }
-  e = cudaMalloc(&c->d_status, 2 * sizeof(int));
-  if (e == cudaSuccess) e = cudaMemset(c->d_status, 0, 2 * sizeof(int));
+  e = cudaMalloc(&c->d_status, kStatusBlockBytes);
+  if (e == cudaSuccess) {
+    unsigned long long block[kStatusBlockBytes / 8] = {0, kDefaultWaitLimitNs, kDefaultPeerWaitLimitNs, 0};
+    e = cudaMemcpy(c->d_status, block, sizeof(block), cudaMemcpyHostToDevice);
+  }
   if (e != cudaSuccess) {
     set_last_error("status word: %s", cudaGetErrorString(e));
     delete c;
@@ -190,6 +198,31 @@ const char* xaxb_last_error(void) { return g_last_error; }
 
 int xaxb_set_programmatic_launch(int on) {
   xaxb::set_pdl_enabled(on != 0);
+  return XAXB_OK;
+}
+
+int xaxb_programmatic_launch_enabled(void) { return xaxb::pdl_enabled() ? 1 : 0; }
+
+long long xaxb_launch_count(int reset) {
+  return reset ? g_launches.exchange(0, std::memory_order_relaxed) : g_launches.load(std::memory_order_relaxed);
+}
+
+int xaxb_set_wait_limit_ms(xaxb_ctx* ctx, int local_ms, int peer_ms) {
+  if (!ctx || local_ms < 0 || peer_ms < 0) {
+    set_last_error("set_wait_limit_ms: null context or negative limit");
+    return XAXB_BAD_ARGUMENT;
+  }
+  Ctx* c = reinterpret_cast<Ctx*>(ctx);
+  unsigned long long limits[2] = {local_ms ? (unsigned long long)local_ms * 1000000ull : kDefaultWaitLimitNs,
+                                  peer_ms ? (unsigned long long)peer_ms * 1000000ull : kDefaultPeerWaitLimitNs};
+  cudaError_t e = cudaSetDevice(c->device);
+  // plain cudaMemcpy: ordered after all work already issued to the device, done when it returns
+  if (e == cudaSuccess)
+    e = cudaMemcpy(reinterpret_cast<unsigned char*>(c->d_status) + 8, limits, sizeof(limits), cudaMemcpyHostToDevice);
+  if (e != cudaSuccess) {
+    set_last_error("set_wait_limit_ms: %s", cudaGetErrorString(e));
+    return XAXB_LAUNCH_FAILED;
+  }
   return XAXB_OK;
 }
 

@@ -44,6 +44,18 @@ struct MergeOut {
   float* inv_scale;
 };
 
+constexpr int kSiteDecPos = 15;
+
+// Tokens sequence b attends to: positions[b] + 1, which must lie in 1 .. max_len.  A position
+// outside that range is recorded (XAXB_CACHE_OVERFLOW, site 15) and clamped, so the kernels
+// never divide by an empty softmax and never count rows past the cache as keys.
+__device__ __forceinline__ int decode_len(const int32_t* positions, int b, long long max_len, int* d_status) {
+  const int L = positions[b] + 1;
+  if (L >= 1 && L <= max_len) return L;
+  if (threadIdx.x == 0) atomicCAS(d_status, 0, XAXB_CACHE_OVERFLOW * 1000 + kSiteDecPos);
+  return L < 1 ? 1 : (int)max_len;
+}
+
 // Chunks a sequence of L cached tokens contributes when its last token looks back `window`
 // positions (< 0: all of them).
 __host__ __device__ __forceinline__ int decode_chunks(int L, int window) {
@@ -174,7 +186,7 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(const __grid_constant_
   using SM = DecodeSmem<D>;
   constexpr int kBoxes = D / 64;  // 128-byte-wide boxes per row
   const int first = blockIdx.x, stride = gridDim.x, hk = blockIdx.y, b = blockIdx.z;
-  const int L = p.positions[b] + 1;
+  const int L = decode_len(p.positions, b, p.max_len, p.d_status);
   const int n_chunks = (L + kChunk - 1) / kChunk;
   // with a sliding window the chunks below the first visible token are never loaded
   const int lo_tok = p.window >= 0 ? max(0, L - 1 - p.window) : 0;
@@ -448,445 +460,7 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(const __grid_constant_
   }
 }
 
-// ---------------------------------------------------------------------------------------
-// Persistent, software-pipelined variant (selected with xaxb_attn_decode_force_variant(2); the
-// one-CTA-per-chunk kernel above is the default because it is currently the faster of the two
-// on B200: three co-resident CTAs per SM overlap each other's load and compute phases better
-// than this kernel's single softmax group does).  One CTA per SM walks the list of
-// (sequence, kv head, 128-token chunk) work items with its warps specialised:
-//   warp 0     TMA producer: Q (16 heads x D, so the G heads of the group plus neighbours that
-//              are ignored), K and V tiles into a ring of shared-memory stages;
-//   warp 1     MMA issuer: S^T = K Q^T of item n+1 is issued before P^T V of item n, into
-//              double-buffered TMEM accumulators, so the tensor core never waits for a softmax;
-//   warps 2-5  softmax: thread = token for the scores, thread = head dimension for the output;
-//              writes P^T (bf16) for the second MMA and the chunk's (max, sum, O^T) to scratch.
-// Shared memory holds three K/V stages (192 KiB for D = 128), i.e. two tiles are always in
-// flight while one is being consumed: the kernel is bound by HBM, not by a load -> compute ->
-// store chain per CTA.
-
-constexpr int kPipeThreads = 192;
-constexpr int kSiteP_KV = 15, kSiteP_Q = 16, kSiteM_Acc = 17, kSiteM_QK = 18, kSiteM_P = 19, kSiteS_S = 20,
-              kSiteS_V = 25, kSiteS_O = 26, kSiteS_K = 27;
-
-template <int D>
-struct PipeSmem {
-  static constexpr int kHalfBytes = kChunk * 128;
-  static constexpr int kKBytes = kChunk * D * 2;
-  static constexpr int kVBytes = 2 * kHalfBytes;  // D = 64: upper half is a zero pad (UMMA M = 128)
-  static constexpr int kStageBytes = kKBytes + kVBytes;
-  static constexpr int kStages = D == 128 ? 3 : 4;
-  static constexpr int kQBytes = kNPad * D * 2;
-  static constexpr int kPBytes = kNPad * kChunk * 2;
-  static constexpr int kBytes = kStages * kStageBytes + 2 * kQBytes + 2 * kPBytes + 1024 /*alignment*/ + 2048;
-};
-
-__device__ __forceinline__ bool softmax_all(bool pred) {  // all-of vote over the 128 softmax threads
-  uint32_t r;
-  asm volatile(
-      "{\n\t.reg .pred p, q;\n\t"
-      "setp.ne.u32 q, %1, 0;\n\t"
-      "bar.red.and.pred p, 1, 128, q;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(r)
-      : "r"((uint32_t)pred)
-      : "memory");
-  return r != 0;
-}
-
-__device__ __forceinline__ void softmax_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
-
-__device__ __forceinline__ void tma_load_3d(void* smem_dst, const CUtensorMap* map, uint64_t* bar, int x, int y, int z) {
-  asm volatile(
-      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
-      ::"r"(smem_u32(smem_dst)), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y), "r"(z)
-      : "memory");
-}
-
-template <int D>
-__global__ void __launch_bounds__(kPipeThreads, 1)
-attn_decode_pipe_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
-                        const __grid_constant__ CUtensorMap tmap_v, const DecodeParams p, const int B) {
-  pdl_wait();  // nothing below may run ahead of the previous kernel in the stream
-  using SM = PipeSmem<D>;
-  constexpr int kStages = SM::kStages;
-  constexpr int kBoxes = D / 64;
-
-  extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint8_t* sKV = smem;                                  // stage s: K then V
-  uint8_t* sQ = sKV + kStages * SM::kStageBytes;        // [2]
-  uint8_t* sP = sQ + 2 * SM::kQBytes;                   // [2]
-  uint64_t* bars = reinterpret_cast<uint64_t*>(sP + 2 * SM::kPBytes);
-  uint64_t* k_full = bars;                   // [kStages] TMA bytes of K
-  uint64_t* v_full = k_full + kStages;       // [kStages] TMA bytes of V
-  uint64_t* kv_empty = v_full + kStages;     // [kStages] second MMA done with the stage
-  uint64_t* k_ready = kv_empty + kStages;    // [kStages] K rotated in place (rotate-on-load only)
-  uint64_t* q_full = k_ready + kStages;      // [2]
-  uint64_t* q_empty = q_full + 2;            // [2] first MMA done with Q
-  uint64_t* s_full = q_empty + 2;            // [2] scores in TMEM
-  uint64_t* p_full = s_full + 2;             // [2] probabilities in shared memory
-  uint64_t* o_full = p_full + 2;             // [2] output in TMEM
-  uint64_t* s_empty = o_full + 2;            // [2] softmax warps have read the scores
-  uint64_t* o_empty = s_empty + 2;           // [2] softmax warps have read the output
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_empty + 2);
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-  float* red = reinterpret_cast<float*>(tmem_slot + 2);  // [2 buffers][2 (max, sum)][4 warps][16]
-
-  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int total = B * p.Hkv * p.max_chunks;
-
-  if (tid == 0) {
-    for (int s = 0; s < kStages; ++s) {
-      mbar_init(k_full + s, 1);
-      mbar_init(v_full + s, 1);
-      mbar_init(kv_empty + s, 1);
-      mbar_init(k_ready + s, 4);
-    }
-    for (int i = 0; i < 2; ++i) {
-      mbar_init(q_full + i, 1);
-      mbar_init(q_empty + i, 1);
-      mbar_init(s_full + i, 1);
-      mbar_init(p_full + i, 4);
-      mbar_init(o_full + i, 1);
-      mbar_init(s_empty + i, 4);
-      mbar_init(o_empty + i, 4);
-    }
-    *abort_flag = 0;
-    fence_mbar_init();
-    prefetch_tmap(&tmap_q);
-    prefetch_tmap(&tmap_k);
-    prefetch_tmap(&tmap_v);
-  }
-  if (warp == 2) {
-    tmem_alloc(tmem_slot, 64);
-    tmem_relinquish();
-  }
-  if (D == 64) {  // zero pads standing in for V dims 64..127, written once
-    for (int s = 0; s < kStages; ++s)
-      for (int i = tid; i < SM::kHalfBytes / 16; i += kPipeThreads)
-        reinterpret_cast<uint4*>(sKV + s * SM::kStageBytes + SM::kKBytes + SM::kHalfBytes)[i] = make_uint4(0, 0, 0, 0);
-    fence_proxy_async_smem();
-  }
-  tc_fence_before_sync();
-  __syncthreads();
-  tc_fence_after_sync();
-  const uint32_t tmem_base = *tmem_slot;
-  pdl_trigger();  // tensor memory is allocated: the next kernel may be scheduled
-
-  // work item w -> (b, hk, chunk), chunk fastest; an item is valid if its chunk starts inside the sequence
-  auto decode = [&](int w, int& b, int& hk, int& chunk) -> bool {
-    chunk = w % p.max_chunks;
-    const int t = w / p.max_chunks;
-    hk = t % p.Hkv;
-    b = t / p.Hkv;
-    return chunk * kChunk <= p.positions[b];
-  };
-
-  if (warp == 0) {
-    // ------------------------------------------------------------------------ producer
-    if (lane == 0) {
-      int n = 0;
-      for (int w = blockIdx.x; w < total; w += gridDim.x) {
-        int b, hk, chunk;
-        if (!decode(w, b, hk, chunk)) continue;
-        const int s = n % kStages, qb = n & 1;
-        const uint32_t ph = (n / kStages) & 1, qph = (n >> 1) & 1;
-        if (!mbar_wait(kv_empty + s, ph ^ 1, abort_flag, p.d_status, XAXB_DEVICE_TIMEOUT * 1000 + kSiteP_KV)) break;
-        if (!mbar_wait(q_empty + qb, qph ^ 1, abort_flag, p.d_status, XAXB_DEVICE_TIMEOUT * 1000 + kSiteP_Q)) break;
-        uint8_t* k_dst = sKV + s * SM::kStageBytes;
-        uint8_t* v_dst = k_dst + SM::kKBytes;
-        uint8_t* q_dst = sQ + qb * SM::kQBytes;
-        mbar_arrive_expect_tx(q_full + qb, SM::kQBytes);
-        mbar_arrive_expect_tx(k_full + s, SM::kKBytes);
-        mbar_arrive_expect_tx(v_full + s, SM::kKBytes);
-#pragma unroll
-        for (int x = 0; x < kBoxes; ++x) tma_load_3d(q_dst + x * (kNPad * 128), &tmap_q, q_full + qb, x * 64, hk * p.G, b);
-#pragma unroll
-        for (int x = 0; x < kBoxes; ++x)
-          tma_load_4d(k_dst + x * SM::kHalfBytes, &tmap_k, k_full + s, x * 64, hk, chunk * kChunk, b);
-#pragma unroll
-        for (int x = 0; x < kBoxes; ++x)
-          tma_load_4d(v_dst + x * SM::kHalfBytes, &tmap_v, v_full + s, x * 64, hk, chunk * kChunk, b);
-        ++n;
-      }
-    }
-  } else if (warp == 1) {
-    // ------------------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
-      constexpr uint32_t idesc_qk = umma_idesc(kFmtBF16, kFmtBF16, 0, 0, 128, kNPad);
-      constexpr uint32_t idesc_pv = umma_idesc(kFmtBF16, kFmtBF16, 1, 0, 128, kNPad);
-      bool ok = true;
-      auto issue_qk = [&](int n) {  // scores of the n-th valid item
-        const int s = n % kStages, qb = n & 1, ab = n & 1;
-        const uint32_t ph = (n / kStages) & 1, qph = (n >> 1) & 1;
-        ok = ok && mbar_wait(s_empty + ab, qph ^ 1, abort_flag, p.d_status, XAXB_DEVICE_TIMEOUT * 1000 + kSiteM_Acc);
-        ok = ok && mbar_wait(q_full + qb, qph, abort_flag, p.d_status, XAXB_DEVICE_TIMEOUT * 1000 + kSiteM_QK);
-        ok = ok && mbar_wait((p.k_is_rotated ? k_full : k_ready) + s, ph, abort_flag, p.d_status,
-                             XAXB_DEVICE_TIMEOUT * 1000 + kSiteM_QK);
-        if (!ok) return;
-        tc_fence_after_sync();
-        const uint8_t* k_src = sKV + s * SM::kStageBytes;
-        const uint8_t* q_src = sQ + qb * SM::kQBytes;
-#pragma unroll
-        for (int k = 0; k < D / 16; ++k) {
-          const uint32_t box = k / 4, off = (k % 4) * 32;
-          umma_f16(tmem_base + ab * kNPad, umma_desc_kmajor_sw128(smem_u32(k_src + box * SM::kHalfBytes) + off),
-                   umma_desc_kmajor_sw128(smem_u32(q_src + box * (kNPad * 128)) + off), idesc_qk, k != 0);
-        }
-        umma_commit(s_full + ab);
-        umma_commit(q_empty + qb);
-      };
-      auto issue_pv = [&](int n) {
-        const int s = n % kStages, ab = n & 1;
-        const uint32_t ph = (n / kStages) & 1, aph = (n >> 1) & 1;
-        ok = ok && mbar_wait(o_empty + ab, aph ^ 1, abort_flag, p.d_status, XAXB_DEVICE_TIMEOUT * 1000 + kSiteM_Acc);
-        ok = ok && mbar_wait(p_full + ab, aph, abort_flag, p.d_status, XAXB_DEVICE_TIMEOUT * 1000 + kSiteM_P);
-        ok = ok && mbar_wait(v_full + s, ph, abort_flag, p.d_status, XAXB_DEVICE_TIMEOUT * 1000 + kSiteM_P);
-        if (!ok) return;
-        tc_fence_after_sync();
-        const uint8_t* v_src = sKV + s * SM::kStageBytes + SM::kKBytes;
-        const uint8_t* p_src = sP + ab * SM::kPBytes;
-#pragma unroll
-        for (int k = 0; k < kChunk / 16; ++k) {
-          umma_f16(tmem_base + 32 + ab * kNPad, umma_desc_mnmajor_sw128(smem_u32(v_src) + k * 16 * 128, SM::kHalfBytes),
-                   umma_desc_kmajor_sw128(smem_u32(p_src + (k / 4) * (kNPad * 128)) + (k % 4) * 32), idesc_pv, k != 0);
-        }
-        umma_commit(o_full + ab);
-        umma_commit(kv_empty + s);
-      };
-      // Greedy issue order: whichever MMA has its operands ready goes out, so a tile that is
-      // still in flight never holds back the second MMA of an older item (and with it the
-      // release of that item's stage).
-      int n_items = 0;
-      for (int w = blockIdx.x; w < total; w += gridDim.x) {
-        int b, hk, chunk;
-        n_items += decode(w, b, hk, chunk) ? 1 : 0;
-      }
-      int nq = 0, np = 0;
-      unsigned long long t_idle = globaltimer_ns();
-      while (np < n_items && ok) {
-        bool progressed = false;
-        if (nq < n_items) {
-          const int s = nq % kStages, b2 = nq & 1;
-          const uint32_t ph = (nq / kStages) & 1, qph = (nq >> 1) & 1;
-          if (mbar_test(s_empty + b2, qph ^ 1) && mbar_test(q_full + b2, qph) &&
-              mbar_test((p.k_is_rotated ? k_full : k_ready) + s, ph)) {
-            issue_qk(nq);
-            ++nq;
-            progressed = true;
-          }
-        }
-        if (np < nq) {
-          const int s = np % kStages, b2 = np & 1;
-          const uint32_t ph = (np / kStages) & 1, aph = (np >> 1) & 1;
-          if (mbar_test(o_empty + b2, aph ^ 1) && mbar_test(p_full + b2, aph) && mbar_test(v_full + s, ph)) {
-            issue_pv(np);
-            ++np;
-            progressed = true;
-          }
-        }
-        if (progressed) {
-          t_idle = globaltimer_ns();
-        } else if (*abort_flag) {
-          ok = false;
-        } else if (globaltimer_ns() - t_idle > kWaitLimitNs) {
-          *abort_flag = 1;
-          atomicCAS(p.d_status, 0, XAXB_DEVICE_TIMEOUT * 1000 + kSiteM_QK);
-          ok = false;
-        }
-      }
-    }
-  } else {
-    // ------------------------------------------------------------------------ softmax warps
-    const int q4 = warp & 3;                 // TMEM lane quarter of this warp
-    const int tok = q4 * 32 + lane;          // token within the chunk; also the head dimension for O
-    const uint32_t lane_off = uint32_t(q4 * 32) << 16;
-    const int G = p.G;
-    bool ok = true;
-
-    auto rotate_k = [&](int n, int chunk) {  // rotate-on-load: K row `tok` of stage n % kStages, in place
-      const int s = n % kStages;
-      const uint32_t ph = (n / kStages) & 1;
-      ok = mbar_wait(k_full + s, ph, abort_flag, p.d_status, XAXB_DEVICE_TIMEOUT * 1000 + kSiteS_K);
-      ok = softmax_all(ok);
-      if (!ok) return;
-      uint8_t* sK = sKV + s * SM::kStageBytes;
-      const long long pos = (long long)chunk * kChunk + tok;
-      if (pos < p.table_len) {
-        constexpr int half = D / 2;
-        const __nv_bfloat16* cr = p.cos_t + pos * half;
-        const __nv_bfloat16* sr = p.sin_t + pos * half;
-        for (int c = 0; c < half / 8; ++c) {
-          const int c2 = c + half / 8;
-          uint4* p1 = reinterpret_cast<uint4*>(sK + (c / 8) * SM::kHalfBytes + sw128_offset(tok, c % 8));
-          uint4* p2 = reinterpret_cast<uint4*>(sK + (c2 / 8) * SM::kHalfBytes + sw128_offset(tok, c2 % 8));
-          uint4 a = *p1, bb = *p2;
-          const uint4 cv = __ldg(reinterpret_cast<const uint4*>(cr) + c);
-          const uint4 sv = __ldg(reinterpret_cast<const uint4*>(sr) + c);
-          uint32_t* aw = reinterpret_cast<uint32_t*>(&a);
-          uint32_t* bw = reinterpret_cast<uint32_t*>(&bb);
-          const uint32_t* cw = reinterpret_cast<const uint32_t*>(&cv);
-          const uint32_t* sw = reinterpret_cast<const uint32_t*>(&sv);
-#pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            uint32_t o1 = 0, o2 = 0;
-#pragma unroll
-            for (int hsel = 0; hsel < 2; ++hsel) {
-              const int sh = hsel * 16;
-              const float x1 = bf16_bits_to_float((aw[j] >> sh) & 0xFFFFu);
-              const float x2 = bf16_bits_to_float((bw[j] >> sh) & 0xFFFFu);
-              const float cc = bf16_bits_to_float((cw[j] >> sh) & 0xFFFFu);
-              const float ss = bf16_bits_to_float((sw[j] >> sh) & 0xFFFFu);
-              const float r1 = bf16_round(x1 * cc) - bf16_round(x2 * ss);
-              const float r2 = bf16_round(x2 * cc) + bf16_round(x1 * ss);
-              o1 |= (uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(r1)) << sh;
-              o2 |= (uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(r2)) << sh;
-            }
-            aw[j] = o1;
-            bw[j] = o2;
-          }
-          *p1 = a;
-          *p2 = bb;
-        }
-      }
-      fence_proxy_async_smem();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(k_ready + s);
-    };
-
-    // the list of valid items is walked twice when K is rotated on load: once one item ahead
-    int w_rot = blockIdx.x, n_rot = 0;
-    auto rotate_next = [&]() {
-      while (w_rot < total) {
-        int b, hk, chunk;
-        const bool v = decode(w_rot, b, hk, chunk);
-        w_rot += gridDim.x;
-        if (v) {
-          rotate_k(n_rot, chunk);
-          ++n_rot;
-          return;
-        }
-      }
-    };
-    if (!p.k_is_rotated) rotate_next();
-
-    // Scores of item n are turned into probabilities BEFORE the output of item n-1 is read
-    // out, so the second MMA of item n-1 and its completion latency hide behind the softmax.
-    auto softmax_item = [&](int n, int b, int hk, int chunk) {
-      const int s = n % kStages, ab = n & 1;
-      const uint32_t ph = (n / kStages) & 1, aph = (n >> 1) & 1;
-      const int valid = min(kChunk, p.positions[b] + 1 - chunk * kChunk);
-      float* red_max = red + ab * 128;
-      float* red_sum = red_max + 64;
-      ok = mbar_wait(s_full + ab, aph, abort_flag, p.d_status, XAXB_DEVICE_TIMEOUT * 1000 + kSiteS_S);
-      ok = softmax_all(ok);
-      if (!ok) return;
-      tc_fence_after_sync();
-      uint32_t r[16];
-      tmem_ld_x16(tmem_base + lane_off + ab * kNPad, r);
-      tmem_ld_wait();
-      tc_fence_before_sync();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(s_empty + ab);  // the scores are in registers: TMEM buffer free
-      const bool tok_ok = tok < valid;
-      float sc[kNPad];
-#pragma unroll
-      for (int g = 0; g < kNPad; ++g) {
-        sc[g] = (tok_ok && g < G) ? __uint_as_float(r[g]) * p.sm_scale : -INFINITY;
-        if (g < G) {
-          float m = sc[g];
-          for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
-          if (lane == 0) red_max[q4 * kNPad + g] = m;
-        }
-      }
-      softmax_sync();
-      uint8_t* sPb = sP + ab * SM::kPBytes;
-      const int box = tok / 64, within = tok % 64;
-#pragma unroll
-      for (int g = 0; g < kNPad; ++g) {
-        float e = 0.0f;
-        if (g < G) {
-          const float m = fmaxf(fmaxf(red_max[g], red_max[kNPad + g]), fmaxf(red_max[2 * kNPad + g], red_max[3 * kNPad + g]));
-          e = tok_ok ? __expf(sc[g] - m) : 0.0f;
-          float sum = e;
-          for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
-          if (lane == 0) red_sum[q4 * kNPad + g] = sum;
-          if (tok == g) p.ws_ml[(((long long)b * p.Hq + hk * G + g) * p.max_chunks + chunk) * 2 + 0] = m;
-        }
-        const uint32_t off = box * (kNPad * 128) + sw128_offset(g, within / 8) + (within % 8) * 2;
-        *reinterpret_cast<__nv_bfloat16*>(sPb + off) = __float2bfloat16_rn(e);
-      }
-      if (valid < kChunk) {
-        // the tile runs past the sequence: clear V rows that may hold anything, so 0 * x stays 0
-        ok = mbar_wait(v_full + s, ph, abort_flag, p.d_status, XAXB_DEVICE_TIMEOUT * 1000 + kSiteS_V);
-        if (ok && !tok_ok) {
-          uint8_t* sV = sKV + s * SM::kStageBytes + SM::kKBytes;
-#pragma unroll
-          for (int c = 0; c < D / 8; ++c)
-            *reinterpret_cast<uint4*>(sV + (c / 8) * SM::kHalfBytes + sw128_offset(tok, c % 8)) = make_uint4(0, 0, 0, 0);
-        }
-      }
-      fence_proxy_async_smem();
-      ok = softmax_all(ok);  // every thread's P (and V) writes are done and fenced
-      if (!ok) return;
-      if (lane == 0) mbar_arrive(p_full + ab);
-      if (tok < G) {
-        const float l = red_sum[tok] + red_sum[kNPad + tok] + red_sum[2 * kNPad + tok] + red_sum[3 * kNPad + tok];
-        p.ws_ml[(((long long)b * p.Hq + hk * G + tok) * p.max_chunks + chunk) * 2 + 1] = l;
-      }
-    };
-    auto read_out_item = [&](int n, int b, int hk, int chunk) {
-      const int ab = n & 1;
-      const uint32_t aph = (n >> 1) & 1;
-      ok = mbar_wait(o_full + ab, aph, abort_flag, p.d_status, XAXB_DEVICE_TIMEOUT * 1000 + kSiteS_O);
-      ok = softmax_all(ok);
-      if (!ok) return;
-      tc_fence_after_sync();
-      uint32_t r[16];
-      tmem_ld_x16(tmem_base + lane_off + 32 + ab * kNPad, r);
-      tmem_ld_wait();
-      tc_fence_before_sync();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(o_empty + ab);
-      if (tok < D) {
-#pragma unroll
-        for (int g = 0; g < kNPad; ++g)
-          if (g < G)
-            p.ws_o[(((long long)b * p.Hq + hk * G + g) * p.max_chunks + chunk) * D + tok] = __uint_as_float(r[g]);
-      }
-    };
-
-    int n = 0;
-    int pb = 0, phk = 0, pchunk = 0;
-    bool have_prev = false;
-    for (int w = blockIdx.x; w < total && ok; w += gridDim.x) {
-      int b, hk, chunk;
-      if (!decode(w, b, hk, chunk)) continue;
-      if (!p.k_is_rotated) {
-        rotate_next();  // K of the next item, so its first MMA can go out while this item's softmax runs
-        if (!ok) break;
-      }
-      softmax_item(n, b, hk, chunk);
-      if (!ok) break;
-      if (have_prev) {
-        read_out_item(n - 1, pb, phk, pchunk);
-        if (!ok) break;
-      }
-      pb = b, phk = hk, pchunk = chunk, have_prev = true;
-      ++n;
-    }
-    if (have_prev && ok) read_out_item(n - 1, pb, phk, pchunk);
-  }
-
-  tc_fence_before_sync();
-  __syncthreads();
-  if (warp == 2) {
-    tc_fence_after_sync();
-    tmem_dealloc(tmem_base, 64);
-  }
-}
-
-static int g_decode_variant = 0;  // 0 / 1 = chunk-walking kernel, 2 = persistent pipeline, 10 + n = n chunks per CTA
+static int g_decode_variant = 0;  // 0 / 1 = automatic choice of chunks per CTA, 10 + n = n chunks per CTA
 
 // Merge the partial results of one (sequence, query head): out = sum_c w_c O_c / sum_c w_c l_c
 // with w_c = exp(m_c - max m).  A sequence of n chunks has min(n, lanes) partial results, in the
@@ -897,7 +471,7 @@ __global__ void attn_decode_merge_kernel(const float* __restrict__ ws_o, const f
   pdl_trigger();
   pdl_wait();
   const int h = blockIdx.x, b = blockIdx.y, d = threadIdx.x;
-  const int L = positions[b] + 1;
+  const int L = min(max(positions[b] + 1, 1), max_chunks * kChunk);  // clamped like the attention kernel
   const int n = min(decode_chunks(L, window), lanes);
   const long long base = ((long long)b * Hq + h) * max_chunks;
   float m = -INFINITY;
@@ -921,7 +495,7 @@ __global__ void __launch_bounds__(256) attn_decode_merge_cast_kernel(
   __shared__ float s_max[64], s_inv_den[64];
   __shared__ uint32_t s_tp[2];
   const int b = blockIdx.x;
-  const int L = positions[b] + 1;
+  const int L = min(max(positions[b] + 1, 1), max_chunks * kChunk);  // clamped like the attention kernel
   const int n = min(decode_chunks(L, window), lanes);
   merge_cast_row<256, false>(ws_o, ws_ml, b, n, Hq, D, max_chunks, mo, tp, d_status, s_max, s_inv_den, s_tp);
 }
@@ -989,54 +563,9 @@ static int decode_launch(xaxb_ctx* ctx_, void* stream, const void* q_rot_bf16, c
   p.ws_ml = p.ws_o + B * Hq * max_chunks * D;
   p.max_chunks = max_chunks;
   p.window = window < 0 ? -1 : (window > 0x3fffffff ? 0x3fffffff : (int)window);
-  if (p.window >= 0 && g_decode_variant == 2) {
-    set_last_error("attn_decode: the persistent pipelined kernel has no sliding window");
-    return XAXB_UNSUPPORTED;
-  }
   p.d_status = ctx->d_status;
   int lanes = max_chunks;  // partial results per (sequence, head) row of the workspace
-  const bool use_pipe = g_decode_variant == 2 && (long long)B * Hkv * max_chunks < (1ll << 31);
-  if (use_pipe) {
-    CUtensorMap tq;
-    {
-      // q_rot [B, Hq, D]: dims innermost first (D, Hq, B); box = 64 d x 16 heads x 1
-      if ((reinterpret_cast<uintptr_t>(q_rot_bf16) & 15) != 0) return XAXB_BAD_ARGUMENT;
-      cuuint64_t dims[3] = {(cuuint64_t)D, (cuuint64_t)Hq, (cuuint64_t)B};
-      cuuint64_t strides[2] = {(cuuint64_t)D * 2, (cuuint64_t)Hq * D * 2};
-      cuuint32_t box[3] = {64, (cuuint32_t)kNPad, 1};
-      cuuint32_t estr[3] = {1, 1, 1};
-      typedef CUresult (*EncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-      CUresult r = reinterpret_cast<EncodeFn>(ctx->encode_tiled)(
-          &tq, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(q_rot_bf16), dims, strides, box, estr,
-          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-      if (r != CUDA_SUCCESS) {
-        set_last_error("cuTensorMapEncodeTiled(q) failed with CUresult %d", (int)r);
-        return XAXB_LAUNCH_FAILED;
-      }
-    }
-    const long long total = (long long)B * Hkv * max_chunks;
-    const int grid_p = (int)(total < ctx->num_sms ? total : ctx->num_sms);
-    if (D == 128) {
-      static bool setp128 = false;
-      if (!setp128) {
-        cudaFuncSetAttribute(attn_decode_pipe_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             PipeSmem<128>::kBytes);
-        setp128 = true;
-      }
-      launch_kernel(attn_decode_pipe_kernel<128>, grid_p, dim3(kPipeThreads), PipeSmem<128>::kBytes, s, 1, tq, tk, tv, p, (int)B);
-    } else {
-      static bool setp64 = false;
-      if (!setp64) {
-        cudaFuncSetAttribute(attn_decode_pipe_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             PipeSmem<64>::kBytes);
-        setp64 = true;
-      }
-      launch_kernel(attn_decode_pipe_kernel<64>, grid_p, dim3(kPipeThreads), PipeSmem<64>::kBytes, s, 1, tq, tk, tv, p, (int)B);
-    }
-  } else {
+  {
     // Chunks are dealt to `lanes` CTAs per (sequence, kv head); each CTA walks its chunks with
     // the next tile's loads in flight.  About four chunks per CTA amortise the set-up; fewer when
     // that would leave SMs without work.
@@ -1050,15 +579,11 @@ static int decode_launch(xaxb_ctx* ctx_, void* stream, const void* q_rot_bf16, c
     dim3 grid((unsigned)lanes, (unsigned)Hkv, (unsigned)B);
     const int G = p.G;
     const int gt = G <= 1 ? 1 : G <= 2 ? 2 : G <= 4 ? 4 : G <= 8 ? 8 : 16;
-#define XAXB_DECODE_CASE(DD, GG)                                                                    \
-  if (D == DD && gt == GG) {                                                                        \
-    static bool set = false;                                                                        \
-    if (!set) {                                                                                     \
-      cudaFuncSetAttribute(attn_decode_kernel<DD, GG>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
-                           DecodeSmem<DD>::kBytes);                                                 \
-      set = true;                                                                                   \
-    }                                                                                               \
-    launch_kernel(attn_decode_kernel<DD, GG>, grid, dim3(128), DecodeSmem<DD>::kBytes, s, 1, tk, tv, p);                \
+#define XAXB_DECODE_CASE(DD, GG)                                                                                 \
+  if (D == DD && gt == GG) {                                                                                     \
+    rc = ensure_dynamic_smem<attn_decode_kernel<DD, GG>>(ctx, DecodeSmem<DD>::kBytes, "attn_decode_kernel");     \
+    if (rc) return rc;                                                                                           \
+    launch_kernel(attn_decode_kernel<DD, GG>, grid, dim3(128), DecodeSmem<DD>::kBytes, s, 1, tk, tv, p);         \
   }
     XAXB_DECODE_CASE(128, 1) XAXB_DECODE_CASE(128, 2) XAXB_DECODE_CASE(128, 4) XAXB_DECODE_CASE(128, 8)
     XAXB_DECODE_CASE(128, 16) XAXB_DECODE_CASE(64, 1) XAXB_DECODE_CASE(64, 2) XAXB_DECODE_CASE(64, 4)
@@ -1171,7 +696,7 @@ extern "C" int xaxb_attn_decode_cast_tp(xaxb_ctx* ctx_, void* stream, const void
 }
 
 extern "C" int xaxb_attn_decode_force_variant(int variant) {
-  if (variant < 0 || (variant > 2 && variant < 11) || variant > 74) return XAXB_BAD_ARGUMENT;
+  if (variant < 0 || (variant > 1 && variant < 11) || variant > 74) return XAXB_BAD_ARGUMENT;
   xaxb::g_decode_variant = variant;
   return XAXB_OK;
 }

@@ -306,20 +306,12 @@ static int prefill_launch(xaxb_ctx* ctx_, void* stream, const void* q_rot_bf16, 
   p.d_status = ctx->d_status;
   dim3 grid((unsigned)((T + kPfTile - 1) / kPfTile), (unsigned)Hq, (unsigned)B);
   if (D == 128) {
-    static bool set128 = false;
-    if (!set128) {
-      cudaFuncSetAttribute(attn_prefill_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                           PrefillSmem<128>::kBytes);
-      set128 = true;
-    }
+    if (int rc2 = ensure_dynamic_smem<attn_prefill_kernel<128>>(ctx, PrefillSmem<128>::kBytes, "attn_prefill_kernel"))
+      return rc2;
     launch_kernel(attn_prefill_kernel<128>, grid, dim3(128), PrefillSmem<128>::kBytes, s, 1, tk, tv, p);
   } else {
-    static bool set64 = false;
-    if (!set64) {
-      cudaFuncSetAttribute(attn_prefill_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                           PrefillSmem<64>::kBytes);
-      set64 = true;
-    }
+    if (int rc2 = ensure_dynamic_smem<attn_prefill_kernel<64>>(ctx, PrefillSmem<64>::kBytes, "attn_prefill_kernel"))
+      return rc2;
     launch_kernel(attn_prefill_kernel<64>, grid, dim3(128), PrefillSmem<64>::kBytes, s, 1, tk, tv, p);
   }
   return check_launch("attn_prefill_kernel");

@@ -12,16 +12,34 @@
 
 namespace xaxb {
 
-// Device-side waits give up after this long (nanoseconds of %globaltimer), record a
-// status and let the CTA run to its normal teardown.
-constexpr unsigned long long kWaitLimitNs = 1000ull * 1000ull * 1000ull;
+// Device-side waits give up after a limit (nanoseconds of %globaltimer), record a status and
+// let the CTA run to its normal teardown.  The limits live next to the status word in device
+// memory so that xaxb_set_wait_limit_ms can change them without recompiling; a kernel reads
+// them only on the slow path of a wait.  Defaults: 1 s for waits inside one GPU, 10 s for waits
+// on other GPUs.
+constexpr unsigned long long kDefaultWaitLimitNs = 1000ull * 1000ull * 1000ull;
+constexpr unsigned long long kDefaultPeerWaitLimitNs = 10ull * 1000ull * 1000ull * 1000ull;
+
+// Layout of the context's block of device memory (d_status points at it; 32 bytes):
+//   int    [0]  status word: 0 = ok, else status * 1000 + site
+//   int    [1]  reserved
+//   uint64 [1]  limit of waits inside this GPU, ns
+//   uint64 [2]  limit of waits on other GPUs, ns
+constexpr int kStatusBlockBytes = 32;
 
 struct Ctx {
   int device;
   int num_sms;
-  int* d_status;  // one int in device memory; 0 = ok
+  int* d_status;  // the block described above
   void* encode_tiled;  // cuTensorMapEncodeTiled
 };
+
+__device__ __forceinline__ unsigned long long wait_limit_ns(const int* d_status) {
+  return reinterpret_cast<const volatile unsigned long long*>(d_status)[1];
+}
+__device__ __forceinline__ unsigned long long peer_wait_limit_ns(const int* d_status) {
+  return reinterpret_cast<const volatile unsigned long long*>(d_status)[2];
+}
 
 // ---------------------------------------------------------------------------------------
 // small utilities
@@ -101,10 +119,11 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
                                           int code) {
   if (mbar_try_wait(bar, parity)) return true;
   const unsigned long long t0 = globaltimer_ns();
+  const unsigned long long limit = wait_limit_ns(d_status);
   for (;;) {
     if (mbar_try_wait(bar, parity)) return true;
     if (*abort_flag) return false;
-    if (globaltimer_ns() - t0 > kWaitLimitNs) {
+    if (globaltimer_ns() - t0 > limit) {
       *abort_flag = 1;
       atomicCAS(d_status, 0, code);
       return false;
@@ -280,6 +299,24 @@ int check_launch(const char* what);
 // memory trigger only after their allocation, so a successor that is already resident can never
 // hold the columns a CTA of the running kernel still needs.
 bool pdl_enabled();
+void count_launch();  // feeds xaxb_launch_count
+
+// Kernels that need more than 48 KB of dynamic shared memory must opt in once per device (the
+// attribute belongs to the function on a device, and a process may hold a context per GPU).  One
+// bit per device ordinal and kernel instantiation.
+template <auto Kernel>
+inline int ensure_dynamic_smem(const Ctx* ctx, int bytes, const char* what) {
+  static unsigned long long done = 0;  // unsynchronised on purpose: setting the attribute twice is harmless
+  const unsigned long long bit = 1ull << (ctx->device & 63);
+  if (done & bit) return XAXB_OK;
+  cudaError_t e = cudaFuncSetAttribute(Kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+  if (e != cudaSuccess) {
+    set_last_error("%s: cudaFuncSetAttribute(%d bytes of shared memory): %s", what, bytes, cudaGetErrorString(e));
+    return XAXB_LAUNCH_FAILED;
+  }
+  done |= bit;
+  return XAXB_OK;
+}
 
 template <typename... KArgs, typename... Args>
 inline cudaError_t launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
@@ -305,6 +342,7 @@ inline cudaError_t launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block
   }
   cfg.attrs = attr;
   cfg.numAttrs = n;
+  count_launch();
   return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
 }
 

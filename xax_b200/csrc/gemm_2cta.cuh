@@ -302,16 +302,7 @@ static int launch_gemm_2cta(const Ctx* ctx, cudaStream_t stream, const void* a, 
   if (!getenv("XAXB_GEMM_BAND")) p.band = 16;
   p.tiles_n = (p.N + Cfg::kBN - 1) / Cfg::kBN;
   p.num_k_blocks = (int)(((long long)p.K * kElemBytes + kBKBytes - 1) / kBKBytes);
-  static bool attr_set = false;
-  if (!attr_set) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_2cta_kernel<IS_FP8>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         Cfg::kSmemBytes);
-    if (e != cudaSuccess) {
-      set_last_error("gemm 2-CTA: cudaFuncSetAttribute(%d bytes): %s", Cfg::kSmemBytes, cudaGetErrorString(e));
-      return XAXB_LAUNCH_FAILED;
-    }
-    attr_set = true;
-  }
+  if (int rc2 = ensure_dynamic_smem<gemm_2cta_kernel<IS_FP8>>(ctx, Cfg::kSmemBytes, "gemm_2cta_kernel")) return rc2;
   const int tiles = p.tiles_m * p.tiles_n;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((unsigned)(2 * (ctx->num_sms / 2)), 1, 1);

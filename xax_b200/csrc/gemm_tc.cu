@@ -775,16 +775,8 @@ static int launch_splitk(const Ctx* ctx, cudaStream_t stream, const void* a, lon
   p.tiles_m = 1;
   p.tiles_n = (p.N + BN - 1) / BN;
   p.num_k_blocks = (int)(((long long)p.K * kElemBytes + kBKBytes - 1) / kBKBytes);
-  static bool attr_set = false;
-  if (!attr_set) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_splitk_kernel<BN, IS_FP8>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         Cfg::kSmemBytes);
-    if (e != cudaSuccess) {
-      set_last_error("gemm split-K: cudaFuncSetAttribute(%d bytes): %s", Cfg::kSmemBytes, cudaGetErrorString(e));
-      return XAXB_LAUNCH_FAILED;
-    }
-    attr_set = true;
-  }
+  rc = ensure_dynamic_smem<gemm_splitk_kernel<BN, IS_FP8>>(ctx, Cfg::kSmemBytes, "gemm_splitk_kernel");
+  if (rc) return rc;
   cudaError_t e = launch_kernel(gemm_splitk_kernel<BN, IS_FP8>, dim3((unsigned)(p.tiles_n * S), 1, 1), dim3(kGemmThreads),
                                 Cfg::kSmemBytes, stream, (unsigned)S, ta, tb, p, S);
   if (e != cudaSuccess) {
@@ -816,16 +808,8 @@ static int launch_gemm(const Ctx* ctx, cudaStream_t stream, const void* a, long 
   p.tiles_m = (p.M + kBM - 1) / kBM;
   p.tiles_n = (p.N + BN - 1) / BN;
   p.num_k_blocks = (int)(((long long)p.K * kElemBytes + kBKBytes - 1) / kBKBytes);
-  static bool attr_set = false;  // per template instantiation
-  if (!attr_set) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, IS_FP8>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         Cfg::kSmemBytes);
-    if (e != cudaSuccess) {
-      set_last_error("gemm: cudaFuncSetAttribute(%d bytes): %s", Cfg::kSmemBytes, cudaGetErrorString(e));
-      return XAXB_LAUNCH_FAILED;
-    }
-    attr_set = true;
-  }
+  rc = ensure_dynamic_smem<gemm_tc_kernel<BN, IS_FP8>>(ctx, Cfg::kSmemBytes, "gemm_tc_kernel");
+  if (rc) return rc;
   const int tiles = p.tiles_m * p.tiles_n;
   const int grid = tiles < ctx->num_sms ? tiles : ctx->num_sms;
   launch_kernel(gemm_tc_kernel<BN, IS_FP8>, grid, dim3(kGemmThreads), Cfg::kSmemBytes, stream, 1, ta, tb, tout, p);

@@ -75,8 +75,8 @@ __device__ __forceinline__ float nan_max(float a, float b) { return (a != a) ? a
 // ---- delayed scaling: cast with the incoming scale while reducing max|x|; the CTA that finishes
 // last then produces the state for the next call:
 //   history_out = roll(history_in, -1) with slot 0 <- amax; scale_out from max(history_out).
-// One launch.  Four 16-byte loads are issued per thread before any is used, so a CTA keeps 16 KiB
-// in flight.  scratch[0] collects max|x| (bf16 bits << 16), scratch[1] counts finished CTAs; both
+// One launch of 256-thread CTAs.  Four 16-byte loads are issued per thread before any is used, so a
+// CTA keeps 16 KiB in flight.  scratch[0] collects max|x| (bf16 bits << 16), scratch[1] counts finished CTAs; both
 // are zero on entry and the last CTA leaves them zero.  The history is staged in shared memory,
 // so history_in and history_out may alias; scale_out may alias scale_in (every CTA has read it
 // before the last one can finish).
@@ -93,22 +93,24 @@ __global__ void __launch_bounds__(256) delayed_cast_kernel(const uint4* __restri
   const float old = *scale_in;
   const float s = bf16_round(old);
   uint32_t m = 0;
-  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
-  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-  for (; i + 3 * stride < n_vec; i += 4 * stride) {
+  // A CTA takes whole blocks of 4 x 256 vectors (16 KiB of x, contiguous), block index
+  // blockIdx.x, blockIdx.x + gridDim.x, ...: thread t issues its four loads -- all of them, a
+  // ragged last block included, under a predicate -- before it uses any of them.
+  const int64_t n_blocks = (n_vec + 1023) / 1024;
+  for (int64_t blk = blockIdx.x; blk < n_blocks; blk += gridDim.x) {
+    const int64_t i0 = blk * 1024 + threadIdx.x;
     uint4 v[4];
 #pragma unroll
-    for (int k = 0; k < 4; ++k) v[k] = __ldg(x + i + k * stride);
+    for (int k = 0; k < 4; ++k) {
+      const int64_t i = i0 + k * 256;
+      v[k] = i < n_vec ? __ldg(x + i) : make_uint4(0, 0, 0, 0);
+    }
 #pragma unroll
     for (int k = 0; k < 4; ++k) {
+      const int64_t i = i0 + k * 256;
       m = absmax_bits8(m, v[k]);
-      if (q) q[i + k * stride] = quantize8(v[k], s);
+      if (q && i < n_vec) q[i] = quantize8(v[k], s);
     }
-  }
-  for (; i < n_vec; i += stride) {
-    const uint4 v = __ldg(x + i);
-    m = absmax_bits8(m, v);
-    if (q) q[i] = quantize8(v, s);
   }
   const uint32_t r = block_max_u32(m);
   if (threadIdx.x == 0) {
@@ -264,7 +266,11 @@ int xaxb_quantize_delayed(xaxb_ctx* ctx, void* stream, const void* x_bf16, int64
   const Ctx* c = reinterpret_cast<const Ctx*>(ctx);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const int64_t n_vec = rows * cols / 8;
-  launch_kernel(delayed_cast_kernel, dim3(grid_for(n_vec, c->num_sms)), dim3(256), history_len * sizeof(float), s, 1, 
+  // one CTA per 16 KiB block of x while that fits one resident wave (8 CTAs per SM); beyond it the
+  // CTAs loop.  Fewer CTAs also mean fewer arrivals at the ticket that elects the last one.
+  int64_t grid = (n_vec + 1023) / 1024;
+  if (grid > (int64_t)c->num_sms * 8) grid = (int64_t)c->num_sms * 8;
+  launch_kernel(delayed_cast_kernel, dim3((unsigned)grid), dim3(256), history_len * sizeof(float), s, 1, 
       static_cast<const uint4*>(x_bf16), n_vec, scale_in, static_cast<uint2*>(q_e4m3),
       reinterpret_cast<unsigned int*>(amax_scratch), history_in, history_len, history_out, scale_out, inv_scale_out);
   return check_launch("delayed_cast_kernel");

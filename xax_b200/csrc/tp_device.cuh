@@ -10,9 +10,9 @@ namespace xaxb {
 constexpr int kTpMaxWorld = 8;
 constexpr int kTpMaxSlots = 1024;
 // Waits on other GPUs get a longer limit than waits inside one GPU (ranks reach an exchange at
-// different times: graph upload, host jitter), and once any wait of this context has given up --
-// the status word is set -- later waits return at once, so a broken run drains quickly.
-constexpr unsigned long long kTpWaitLimitNs = 10ull * 1000ull * 1000ull * 1000ull;
+// different times: graph upload, host jitter; peer_wait_limit_ns, 10 s unless changed), and once
+// any wait of this context has given up -- the status word is set -- later waits return at once,
+// so a broken run drains quickly.
 constexpr int kSiteTpSum = 41, kSiteTpMax = 42, kSiteTpSilu = 43, kSiteTpAttn = 44;
 
 // Flag region of one exchange kind: flags[kTpMaxSlots][kTpMaxWorld] then epoch[kTpMaxSlots].
@@ -69,9 +69,10 @@ __device__ __forceinline__ uint32_t tp_exchange_flags(const PeerTable& peers, in
     const uint32_t* mine = my_flags + slot * kTpMaxWorld + r;
     if ((int32_t)(ld_acquire_sys(mine) - epoch) < 0) {
       const unsigned long long t0 = globaltimer_ns();
+      const unsigned long long limit = peer_wait_limit_ns(d_status);
       while ((int32_t)(ld_acquire_sys(mine) - epoch) < 0) {
         if (*reinterpret_cast<volatile int*>(d_status) != 0) break;
-        if (globaltimer_ns() - t0 > kTpWaitLimitNs) {
+        if (globaltimer_ns() - t0 > limit) {
           atomicCAS(d_status, 0, XAXB_DEVICE_TIMEOUT * 1000 + site);
           break;
         }
@@ -121,9 +122,10 @@ __device__ __forceinline__ uint32_t tp_cta_max_u32(const TpRowMax& tp, int slot,
     const uint32_t* flag = my_flags + slot * kTpMaxWorld + r;
     if ((int32_t)(ld_acquire_sys(flag) - epoch) < 0) {
       const unsigned long long t0 = globaltimer_ns();
+      const unsigned long long limit = peer_wait_limit_ns(d_status);
       while ((int32_t)(ld_acquire_sys(flag) - epoch) < 0) {
         if (*reinterpret_cast<volatile int*>(d_status) != 0) break;
-        if (globaltimer_ns() - t0 > kTpWaitLimitNs) {
+        if (globaltimer_ns() - t0 > limit) {
           atomicCAS(d_status, 0, XAXB_DEVICE_TIMEOUT * 1000 + site);
           break;
         }

@@ -138,26 +138,50 @@ class Fp8Linear:
         self.weight = weight
         self.bias = bias
         self._wq_current = None  # (q, inv_scale) under current scaling
-        self._wq_delayed = None  # (scale tensor, its version, q, inv_scale)
+        self._wq_delayed = None  # (scale tensor, its version, q, inv_scale, weight key)
+        self._wq_key = None      # _weight_key() the current-scaling copy was made from
 
     # -- weight quantisation (cached) ----------------------------------------------------------
+    def _weight_key(self):
+        """Identity of the weight the cached e4m3 copies were made from: a new tensor assigned to
+        ``weight`` or an in-place update of it (torch bumps ``_version``) makes them stale."""
+        w = self.weight
+        return (w.data_ptr(), w._version, tuple(w.shape))
+
+    def invalidate(self) -> None:
+        """Drop the cached e4m3 weights (loaders that overwrite ``weight`` behind torch's back call this)."""
+        self._wq_current = None
+        self._wq_delayed = None
+        self._wq_key = None
+
+    def set_weight_q_current(self, q: torch.Tensor, inv_scale: torch.Tensor) -> None:
+        """Install e4m3 bytes made elsewhere for the current weight (tensor-parallel ranks quantise their
+        slice with the amax of the whole weight, which this layer cannot know on its own)."""
+        self._wq_current = (q, inv_scale)
+        self._wq_key = self._weight_key()
+
     def weight_q_current(self):
         """e4m3 weight and its dequantisation multiplier 1/sw under current scaling."""
-        if self._wq_current is None:
+        key = self._weight_key()
+        if self._wq_current is None or self._wq_key != key:
             w = self.weight.to(torch.bfloat16)
             q, _, inv, _ = ops.quantize_current(w, group_rows=w.shape[0])
             self._wq_current = (q, inv[:1].clone())
+            self._wq_delayed = None
+            self._wq_key = key
         return self._wq_current
 
     def _weight_q_delayed(self, scales: Fp8Scales):
         ks = scales.kernel_scale
         c = self._wq_delayed
-        if c is not None and c[0] is ks and c[1] == ks._version:
+        key = self._weight_key()
+        w = self.weight.to(torch.bfloat16)
+        if c is not None and c[0] is ks and c[1] == ks._version and c[4] == key:
             q, inv = c[2], c[3]
-            _, new_hist, new_scale, _ = ops.quantize_delayed(self.weight, ks, scales.kernel_amax_history, cast=False)
+            _, new_hist, new_scale, _ = ops.quantize_delayed(w, ks, scales.kernel_amax_history, cast=False)
         else:
-            q, new_hist, new_scale, inv = ops.quantize_delayed(self.weight, ks, scales.kernel_amax_history)
-            self._wq_delayed = (ks, ks._version, q, inv)
+            q, new_hist, new_scale, inv = ops.quantize_delayed(w, ks, scales.kernel_amax_history)
+            self._wq_delayed = (ks, ks._version, q, inv, key)
         return q, inv, new_hist, new_scale
 
     # -- forward --------------------------------------------------------------------------------

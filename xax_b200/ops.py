@@ -18,35 +18,9 @@ from ._lib import check, ptr
 E4M3 = torch.float8_e4m3fn
 BF16 = torch.bfloat16
 
-# Kernel launches issued through this module since the counter was last cleared (graph
-# replays re-issue the launches recorded at capture time; callers account for that).
-LAUNCH_COUNT = 0
-# When set to a list, (name, start_event, end_event) is appended around selected kernels.
-KERNEL_TIMES: list | None = None
 
-
-def _c(launches: int = 1):
-    global LAUNCH_COUNT
-    LAUNCH_COUNT += launches
+def _c():
     return _lib.ctx(), _lib.stream_ptr(), _lib.load()
-
-
-class _Timed:
-    def __init__(self, name: str):
-        self.name = name
-
-    def __enter__(self):
-        if KERNEL_TIMES is not None:
-            self.e0 = torch.cuda.Event(enable_timing=True)
-            self.e0.record()
-        return self
-
-    def __exit__(self, *exc):
-        if KERNEL_TIMES is not None:
-            e1 = torch.cuda.Event(enable_timing=True)
-            e1.record()
-            KERNEL_TIMES.append((self.name, self.e0, e1))
-        return False
 
 
 def _req(t: torch.Tensor, dtype, name: str) -> torch.Tensor:
@@ -67,7 +41,7 @@ def quantize_current(x: torch.Tensor, group_rows: int = 1):
     group_rows = 1: a scale per row (per token); group_rows = rows: one scale per tensor."""
     x = _req(x, BF16, "x")
     rows, cols = x.shape
-    ctx, st, lib = _c(1 if group_rows == 1 else 2)
+    ctx, st, lib = _c()
     q = torch.empty((rows, cols), dtype=E4M3, device=x.device)
     scale = torch.empty((rows,), dtype=torch.float32, device=x.device)
     inv = torch.empty((rows,), dtype=torch.float32, device=x.device)
@@ -99,7 +73,7 @@ def quantize_delayed(x: torch.Tensor, scale_in: torch.Tensor, history: torch.Ten
     rows, cols = x2.shape
     scale_in = _req(scale_in, torch.float32, "scale_in")
     history = _req(history, torch.float32, "history")
-    ctx, st, lib = _c(1)
+    ctx, st, lib = _c()
     q = torch.empty((rows, cols), dtype=E4M3, device=x.device) if cast else None
     new_hist = torch.empty_like(history)
     new_scale = torch.empty((), dtype=torch.float32, device=x.device)
@@ -144,9 +118,8 @@ def _gemm(fn_name, a, b, row_mul, col_mul, bias, residual, out):
     col_mul, cs = _mul_arg(col_mul, N, "col_mul")
     ldr = residual.stride(0) if residual is not None else 0
     fn = getattr(lib, fn_name)
-    with _Timed(fn_name):
-        check(fn(ctx, st, ptr(a), a.stride(0), ptr(b), b.stride(0), M, N, K, ptr(row_mul), rs, ptr(col_mul), cs,
-                 ptr(bias), ptr(residual), ldr, ptr(out), out.stride(0)), fn_name)
+    check(fn(ctx, st, ptr(a), a.stride(0), ptr(b), b.stride(0), M, N, K, ptr(row_mul), rs, ptr(col_mul), cs,
+             ptr(bias), ptr(residual), ldr, ptr(out), out.stride(0)), fn_name)
     return out
 
 
@@ -378,6 +351,11 @@ def kv_append_rope(qkv, B, T, Hq, Hkv, D, positions, cos, sin, k_cache, v_cache,
     """RoPE on q and k of the fused projection output, K/V written into the cache at
     positions[b] .. +T-1.  Returns q_rot [B*T, Hq, D]."""
     qkv = _req(qkv, BF16, "qkv")
+    for name, t in (("k_cache", k_cache), ("v_cache", v_cache)):
+        if not t.is_cuda or t.dtype != BF16 or not t.is_contiguous() or tuple(t.shape[::2]) != (B, Hkv):
+            raise ValueError(f"kv_append_rope: {name} must be a contiguous bfloat16 CUDA tensor [B, max_len, Hkv, D]")
+    if not positions.is_cuda or positions.dtype != torch.int32 or not positions.is_contiguous() or positions.numel() != B:
+        raise ValueError("kv_append_rope: positions must be a contiguous int32 CUDA tensor [B]")
     ctx, st, lib = _c()
     if q_rot is None:
         q_rot = torch.empty((B * T, Hq, D), dtype=BF16, device=qkv.device)
@@ -388,6 +366,25 @@ def kv_append_rope(qkv, B, T, Hq, Hkv, D, positions, cos, sin, k_cache, v_cache,
     return q_rot
 
 
+def _attn_args(q_rot, k_cache, v_cache, positions, rows_per_seq: int = 1):
+    """Checks shared by the attention wrappers: bf16 contiguous q [B * rows_per_seq, Hq, D] and caches
+    [B, max_len, Hkv, D], int32 contiguous positions [B], all on one CUDA device.  The kernels read raw
+    pointers, so a wrong dtype or a strided view would be read as something else without any error."""
+    if q_rot.dim() != 3 or k_cache.dim() != 4 or v_cache.shape != k_cache.shape:
+        raise ValueError(f"attention: q must be [rows, Hq, D] and both caches [B, max_len, Hkv, D], got "
+                         f"{tuple(q_rot.shape)}, {tuple(k_cache.shape)}, {tuple(v_cache.shape)}")
+    for name, t in (("q_rot", q_rot), ("k_cache", k_cache), ("v_cache", v_cache)):
+        if not t.is_cuda or t.dtype != BF16 or not t.is_contiguous():
+            raise ValueError(f"attention: {name} must be a contiguous bfloat16 CUDA tensor")
+    B = k_cache.shape[0]
+    if not positions.is_cuda or positions.dtype != torch.int32 or not positions.is_contiguous() or \
+            positions.numel() != B:
+        raise ValueError(f"attention: positions must be a contiguous int32 CUDA tensor with one entry per sequence ({B})")
+    if q_rot.shape[0] != B * rows_per_seq or q_rot.shape[2] != k_cache.shape[3]:
+        raise ValueError(f"attention: q {tuple(q_rot.shape)} does not match caches {tuple(k_cache.shape)} "
+                         f"with {rows_per_seq} query rows per sequence")
+
+
 def attn_decode_workspace(B, Hq, D, max_len, device):
     n = _lib.load().xaxb_attn_decode_workspace_bytes(B, Hq, D, max_len)
     return torch.empty((n // 4,), dtype=torch.float32, device=device)
@@ -396,43 +393,44 @@ def attn_decode_workspace(B, Hq, D, max_len, device):
 def attn_decode(q_rot, k_cache, v_cache, positions, *, scale=None, k_is_rotated=True, cos=None, sin=None,
                 workspace=None, out=None):
     """One query token per sequence; attends to cache rows 0 .. positions[b]."""
+    _attn_args(q_rot, k_cache, v_cache, positions)
     B, Hq, D = q_rot.shape
     _, max_len, Hkv, _ = k_cache.shape
-    ctx, st, lib = _c(2)
+    ctx, st, lib = _c()
     if workspace is None:
         workspace = attn_decode_workspace(B, Hq, D, max_len, q_rot.device)
     if out is None:
         out = torch.empty_like(q_rot)
     if scale is None:
         scale = 1.0 / math.sqrt(D)
-    with _Timed("attn_decode"):
-        check(lib.xaxb_attn_decode(ctx, st, ptr(q_rot), ptr(k_cache), ptr(v_cache), ptr(positions), B, Hq, Hkv, D,
-                                   max_len, float(scale), 1 if k_is_rotated else 0, ptr(cos), ptr(sin),
-                                   0 if cos is None else cos.shape[0], ptr(out), ptr(workspace),
-                                   workspace.numel() * 4), "attn_decode")
+    check(lib.xaxb_attn_decode(ctx, st, ptr(q_rot), ptr(k_cache), ptr(v_cache), ptr(positions), B, Hq, Hkv, D,
+                               max_len, float(scale), 1 if k_is_rotated else 0, ptr(cos), ptr(sin),
+                               0 if cos is None else cos.shape[0], ptr(out), ptr(workspace),
+                               workspace.numel() * 4), "attn_decode")
     return out
 
 
 def attn_decode_window(q_rot, k_cache, v_cache, positions, window: int, *, scale=None, workspace=None, out=None):
     """attn_decode with a sliding window: the query at position q attends to keys q - window .. q."""
+    _attn_args(q_rot, k_cache, v_cache, positions)
     B, Hq, D = q_rot.shape
     _, max_len, Hkv, _ = k_cache.shape
-    ctx, st, lib = _c(2)
+    ctx, st, lib = _c()
     if workspace is None:
         workspace = attn_decode_workspace(B, Hq, D, max_len, q_rot.device)
     if out is None:
         out = torch.empty_like(q_rot)
     if scale is None:
         scale = 1.0 / math.sqrt(D)
-    with _Timed("attn_decode"):
-        check(lib.xaxb_attn_decode_window(ctx, st, ptr(q_rot), ptr(k_cache), ptr(v_cache), ptr(positions), B, Hq, Hkv, D,
-                                          max_len, float(scale), int(window), ptr(out), ptr(workspace),
-                                          workspace.numel() * 4), "attn_decode_window")
+    check(lib.xaxb_attn_decode_window(ctx, st, ptr(q_rot), ptr(k_cache), ptr(v_cache), ptr(positions), B, Hq, Hkv, D,
+                                      max_len, float(scale), int(window), ptr(out), ptr(workspace),
+                                      workspace.numel() * 4), "attn_decode_window")
     return out
 
 
 def attn_prefill_window(q_rot, k_cache, v_cache, positions, B, T, window: int, *, scale=None, out=None):
     """attn_prefill with a sliding window."""
+    _attn_args(q_rot, k_cache, v_cache, positions, T)
     _, Hq, D = q_rot.shape
     _, max_len, Hkv, _ = k_cache.shape
     ctx, st, lib = _c()
@@ -449,9 +447,10 @@ def attn_decode_cast(q_rot, k_cache, v_cache, positions, *, scale=None, k_is_rot
                      workspace=None, want_out=False):
     """Decode attention whose output row [Hq*D] per sequence is cast to e4m3 with a per-token
     scale inside the merge pass.  Returns (out bf16 or None, q e4m3 [B, Hq*D], row_scale, row_inv_scale)."""
+    _attn_args(q_rot, k_cache, v_cache, positions)
     B, Hq, D = q_rot.shape
     _, max_len, Hkv, _ = k_cache.shape
-    ctx, st, lib = _c(2)
+    ctx, st, lib = _c()
     if workspace is None:
         workspace = attn_decode_workspace(B, Hq, D, max_len, q_rot.device)
     out = torch.empty_like(q_rot) if want_out else None
@@ -460,11 +459,10 @@ def attn_decode_cast(q_rot, k_cache, v_cache, positions, *, scale=None, k_is_rot
     ri = torch.empty((B,), dtype=torch.float32, device=q_rot.device)
     if scale is None:
         scale = 1.0 / math.sqrt(D)
-    with _Timed("attn_decode"):
-        check(lib.xaxb_attn_decode_cast(ctx, st, ptr(q_rot), ptr(k_cache), ptr(v_cache), ptr(positions), B, Hq, Hkv, D,
-                                        max_len, float(scale), 1 if k_is_rotated else 0, ptr(cos), ptr(sin),
-                                        0 if cos is None else cos.shape[0], ptr(out), ptr(q), ptr(rs), ptr(ri),
-                                        ptr(workspace), workspace.numel() * 4), "attn_decode_cast")
+    check(lib.xaxb_attn_decode_cast(ctx, st, ptr(q_rot), ptr(k_cache), ptr(v_cache), ptr(positions), B, Hq, Hkv, D,
+                                    max_len, float(scale), 1 if k_is_rotated else 0, ptr(cos), ptr(sin),
+                                    0 if cos is None else cos.shape[0], ptr(out), ptr(q), ptr(rs), ptr(ri),
+                                    ptr(workspace), workspace.numel() * 4), "attn_decode_cast")
     return out, q, rs, ri
 
 
@@ -472,9 +470,10 @@ def attn_decode_cast_tp(q_rot, k_cache, v_cache, positions, peer, *, scale=None,
     """attn_decode_cast for this rank's heads of a tensor-parallel model: the per-token scale comes
     from the amax over ALL ranks' heads, exchanged inside the merge pass.  ``peer`` = (ctypes table of
     peer mappings, rank, world, inbox offset, flag offset).  Returns (q e4m3 [B, Hq*D], scale, inv_scale)."""
+    _attn_args(q_rot, k_cache, v_cache, positions)
     B, Hq, D = q_rot.shape
     _, max_len, Hkv, _ = k_cache.shape
-    ctx, st, lib = _c(2)
+    ctx, st, lib = _c()
     if workspace is None:
         workspace = attn_decode_workspace(B, Hq, D, max_len, q_rot.device)
     q = torch.empty((B, Hq * D), dtype=E4M3, device=q_rot.device)
@@ -483,11 +482,10 @@ def attn_decode_cast_tp(q_rot, k_cache, v_cache, positions, peer, *, scale=None,
     if scale is None:
         scale = 1.0 / math.sqrt(D)
     ptrs, rank, world, inbox, sync = peer
-    with _Timed("attn_decode"):
-        check(lib.xaxb_attn_decode_cast_tp(ctx, st, ptr(q_rot), ptr(k_cache), ptr(v_cache), ptr(positions), B, Hq, Hkv,
-                                           D, max_len, float(scale), 1, None, None, 0, ptr(q), ptr(rs), ptr(ri),
-                                           ptr(workspace), workspace.numel() * 4, ptrs, rank, world, inbox, sync),
-              "attn_decode_cast_tp")
+    check(lib.xaxb_attn_decode_cast_tp(ctx, st, ptr(q_rot), ptr(k_cache), ptr(v_cache), ptr(positions), B, Hq, Hkv,
+                                       D, max_len, float(scale), 1, None, None, 0, ptr(q), ptr(rs), ptr(ri),
+                                       ptr(workspace), workspace.numel() * 4, ptrs, rank, world, inbox, sync),
+          "attn_decode_cast_tp")
     return q, rs, ri
 
 
@@ -512,9 +510,10 @@ def attn_decode_static(q_rot, k_cache, v_cache, positions, *, scale=None, k_is_r
     """Decode attention for callers that can hand over no scratch memory: identical to
     ``attn_decode`` except that the partial results live in an array inside the library (16 MiB
     per GPU).  Shapes needing more raise; calls must not overlap on the GPU."""
+    _attn_args(q_rot, k_cache, v_cache, positions)
     B, Hq, D = q_rot.shape
     _, max_len, Hkv, _ = k_cache.shape
-    ctx, st, lib = _c(2)
+    ctx, st, lib = _c()
     if out is None:
         out = torch.empty_like(q_rot)
     if scale is None:
@@ -530,6 +529,7 @@ def attn_decode_static(q_rot, k_cache, v_cache, positions, *, scale=None, k_is_r
 
 def attn_prefill(q_rot, k_cache, v_cache, positions, B, T, *, scale=None, out=None):
     """Causal attention of T new tokens per sequence (already in the cache) against the cache."""
+    _attn_args(q_rot, k_cache, v_cache, positions, T)
     _, Hq, D = q_rot.shape
     _, max_len, Hkv, _ = k_cache.shape
     ctx, st, lib = _c()
@@ -543,6 +543,7 @@ def attn_prefill(q_rot, k_cache, v_cache, positions, B, T, *, scale=None, out=No
 
 
 def attn_check(q_rot, k_cache, v_cache, positions, B, T, *, scale=None):
+    _attn_args(q_rot, k_cache, v_cache, positions, T)
     _, Hq, D = q_rot.shape
     _, max_len, Hkv, _ = k_cache.shape
     ctx, st, lib = _c()

@@ -71,7 +71,12 @@ class PeerExchange:
 
     def __init__(self, rank: int, size: int, group, device, rows: int, cols: int):
         import ctypes
+        import os
 
+        # The kernels use plain peer loads and stores only.  Left alone, torch would also bind the
+        # buffer to an NVLink multicast object on an NVSwitch box; nothing here needs it, and a rank
+        # that exits while its memory is bound to one can fault the other ranks' GPUs.
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
         import torch.distributed._symmetric_memory as symm
 
         from . import _lib
@@ -261,7 +266,7 @@ class TensorParallel:
                     amax = ops.group_amax(w, w.shape[0])
                     self.all_reduce_max(amax)
                     q, _, inv = ops.quantize_with_amax(w, amax, w.shape[0])
-                    lin._wq_current = (q, inv[:1].clone())
+                    lin.set_weight_q_current(q, inv[:1].clone())
             a._fused = None
             f._fused = None
 
