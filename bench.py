@@ -171,9 +171,11 @@ def _time_kernel(fn, iters=20, warm=3, flush=None):
     return total / iters * 1e-3
 
 
-def kernel_figures(peak_gbs: float) -> dict:
-    """cfg1: quantize (HBM) and FP8 GEMM (tensor); cfg3: decode attention (HBM).  L2 is flushed
-    (a 512 MiB buffer is rewritten and read back) between timed launches."""
+def kernel_figures(peak_gbs: float, only: str | None = None) -> dict:
+    """cfg1: quantize (HBM) and FP8 GEMM (tensor); cfg3: decode attention (HBM); cfg2: block prefill.  L2 is
+    flushed (a 512 MiB buffer is rewritten and read back) between timed launches.  ``only`` keeps the
+    groups whose name contains it ("quantize", "gemm", "attn_decode", "block_prefill"): what a profiler run
+    of one kernel uses."""
     import numpy as np
     import torch
 
@@ -182,6 +184,27 @@ def kernel_figures(peak_gbs: float) -> dict:
     dev = "cuda"
     out = {}
     flush = torch.empty(512 << 20, dtype=torch.uint8, device=dev)
+    if only is not None:
+        if "block_prefill".find(only) >= 0 or only.find("block_prefill") >= 0:
+            return {"block_prefill_cfg2": block_prefill_figure(flush)}
+        return _kernel_group(only, peak_gbs, flush)
+    out.update(_kernel_group("quantize", peak_gbs, flush))
+    out.update(_kernel_group("gemm", peak_gbs, flush))
+    out.update(_kernel_group("attn_decode", peak_gbs, flush))
+    out["block_prefill_cfg2"] = block_prefill_figure(flush)
+    return out
+
+
+def _kernel_group(group: str, peak_gbs: float, flush) -> dict:
+    import numpy as np
+    import torch
+
+    from xax_b200 import ops
+
+    dev = "cuda"
+    out = {}
+    if group not in ("quantize", "gemm", "attn_decode"):
+        raise SystemExit(f"unknown kernel group {group!r}: quantize, gemm, attn_decode or block_prefill")
     g = torch.Generator(device=dev).manual_seed(0)
     # ---- cfg1: x[2048,2048] bf16 N(0,1) with 0.1 % x20 outliers, W (8192,2048) N(0,0.02^2)
     M, K, N = 2048, 2048, 8192
@@ -191,6 +214,22 @@ def kernel_figures(peak_gbs: float) -> dict:
     bias = (torch.randn((N,), generator=g, device=dev) * 0.01).to(torch.bfloat16)
     scale = torch.tensor(448.0 / 100.0, device=dev)
     hist = torch.zeros(16, device=dev)
+    if group == "quantize":
+        return _quantize_figures(x, scale, hist, peak_gbs, flush)
+    if group == "attn_decode":
+        return _attn_decode_figures(g, peak_gbs, flush)
+    return _gemm_figures(x, w, bias, scale, hist, g, flush)
+
+
+def _quantize_figures(x, scale, hist, peak_gbs, flush) -> dict:
+    import torch
+
+    from xax_b200 import ops
+
+    out = {}
+    M, K = x.shape
+    dev = x.device
+    g = torch.Generator(device=dev).manual_seed(3)
     t = _time_kernel(lambda i: ops.quantize_delayed(x, scale, hist), flush=flush)
     out["quantize_cfg1"] = {"gbs": M * K * 3 / t / 1e9, "frac_of_hbm_peak": M * K * 3 / t / 1e9 / peak_gbs,
                             "us": t * 1e6, "bytes": M * K * 3}
@@ -199,6 +238,18 @@ def kernel_figures(peak_gbs: float) -> dict:
     out["quantize_8192x8192"] = {"gbs": 8192 * 8192 * 3 / t / 1e9, "frac_of_hbm_peak": 8192 * 8192 * 3 / t / 1e9 / peak_gbs,
                                  "us": t * 1e6, "bytes": 8192 * 8192 * 3}
     del xl
+    return out
+
+
+def _gemm_figures(x, w, bias, scale, hist, g, flush) -> dict:
+    import torch
+
+    from xax_b200 import ops
+
+    out = {}
+    dev = x.device
+    M, K = x.shape
+    N = w.shape[0]
     xq, _, _, x_inv = ops.quantize_delayed(x, scale, hist)
     wq, _, w_inv, _ = ops.quantize_current(w, N)
     o = torch.empty((M, N), dtype=torch.bfloat16, device=dev)
@@ -228,6 +279,17 @@ def kernel_figures(peak_gbs: float) -> dict:
     except Exception as e:  # noqa: BLE001
         out["cublaslt_fp8_8192"] = {"error": repr(e)[:200]}
     del a8, b8, o2
+    return out
+
+
+def _attn_decode_figures(g, peak_gbs, flush) -> dict:
+    import numpy as np
+    import torch
+
+    from xax_b200 import ops
+
+    out = {}
+    dev = "cuda"
     # ---- cfg3: B=32, 32q/8kv x 128, lengths U[512, 8192], theta 5e5
     B, Hq, Hkv, D, max_len = 32, 32, 8, 128, 8192
     lens = torch.from_numpy(np.random.default_rng(0).integers(512, 8193, B).astype(np.int32)).to(dev)
@@ -246,8 +308,6 @@ def kernel_figures(peak_gbs: float) -> dict:
                                                sin=sin), flush=flush)
     out["attn_decode_cfg3_rope_on_load"] = {"gbs": nbytes / t / 1e9, "frac_of_hbm_peak": nbytes / t / 1e9 / peak_gbs,
                                             "us": t * 1e6}
-    del kc, vc
-    out["block_prefill_cfg2"] = block_prefill_figure(flush)
     return out
 
 
@@ -292,6 +352,9 @@ def main() -> None:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="cfg5", choices=sorted(WORKLOADS))
     ap.add_argument("--no-kernels", action="store_true", help="skip the per-kernel figures")
+    ap.add_argument("--kernels-only", default=None, metavar="GROUP",
+                    help="only the per-kernel figures of one group (quantize, gemm, attn_decode, block_prefill, or "
+                         "'all'); prints {\"kernels\": ...} -- the command profiler captures of one kernel run")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU oracle timing")
     ap.add_argument("--synthetic-kv", action="store_true", help="fill the KV cache with N(0,1) instead of a prefill")
     args = ap.parse_args()
@@ -308,6 +371,12 @@ def main() -> None:
                                             "parallelism": f"tp{args.gpus}",
                                             "l2": "inputs (weights + KV cache) far larger than L2"}}
 
+    if args.kernels_only is not None:
+        if rank == 0:
+            peak, _ = measured_peaks()
+            print(json.dumps({"kernels": kernel_figures(peak, None if args.kernels_only == "all" else args.kernels_only)}),
+                  flush=True)
+        return
     if args.impl == "reference":
         if rank != 0:
             return

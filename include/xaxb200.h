@@ -134,6 +134,15 @@ int xaxb_gemm_bf16(xaxb_ctx* ctx, void* stream, const void* a_bf16, int64_t lda,
  * in the reference. */
 int xaxb_gemm_force_plan(int bn, int split);
 
+/* What a GEMM launched with programmatic dependent launch fetches of operand b (the weights: constant
+ * while a model runs) before it waits for the previous kernel of the stream: mode 0 nothing, 1 a hint
+ * to L2 for the first `l2_blocks` 128-byte K blocks of each CTA's first tile, 2 the b half of as many
+ * K blocks as the shared-memory ring holds, plus the L2 hint for `l2_blocks` more.  Operand a and
+ * everything else is touched only after the wait, so results do not depend on the setting; b must not
+ * be written by the kernel that precedes the GEMM in its stream.  Process-wide.  No counterpart in
+ * the reference. */
+int xaxb_gemm_set_prefetch(int mode, int l2_blocks);
+
 /* Plain CUDA-core GEMM with the same contract as xaxb_gemm_fp8 (one thread per output,
  * float32 accumulation in k order).  A second opinion for the tensor-core kernel in tests;
  * never used by the module layer. */
@@ -194,6 +203,24 @@ int xaxb_argmax(xaxb_ctx* ctx, void* stream, const void* logits_bf16, int64_t ro
  * xaxb_argmax on each slice; out[i] is the global index, lower index on ties. */
 int xaxb_argmax_merge(xaxb_ctx* ctx, void* stream, const float* part_max, const int32_t* part_idx, int64_t parts,
                       int64_t rows, int64_t slice, int32_t* out);
+
+/*
+ * One token per row from logits [rows, vocab] bf16 (row stride ld) the way the generation loop picks it
+ * (xax/arch/llm.py:1446-1489 with the masks of :1547-1570):
+ *   - tokens outside [allowed_min, allowed_max) are masked (allowed_min < 0: no range); eos_id (< 0:
+ *     none) is masked while allow_eos == 0 and, with a range, allowed in addition to it once
+ *     allow_eos != 0; a masked logit counts as the most negative finite bf16;
+ *   - temperature <= 0: arg-max in float32, first index on ties;
+ *   - otherwise the logits are divided by the temperature, the nucleus is the tokens whose cumulative
+ *     softmax probability in descending order (ties in index order) does not exceed top_p, the first
+ *     always included, and out[r] is the token at quantile uniforms[r] (float32 in [0, 1), one per
+ *     row) of the nucleus in that order.
+ * The reference draws with jax.random.categorical from its own PRNG stream; the distribution is the
+ * same, the random numbers are the caller's.  No sort: bisection on the 16-bit order of bf16 values.
+ */
+int xaxb_sample_top_p(xaxb_ctx* ctx, void* stream, const void* logits_bf16, int64_t rows, int64_t vocab, int64_t ld,
+                      float temperature, float top_p, const float* uniforms, int32_t allowed_min,
+                      int32_t allowed_max, int32_t eos_id, int allow_eos, int32_t* out);
 
 /* ---- kernel 3: GQA attention with RoPE and a bf16 KV cache -------------------------- */
 
@@ -360,6 +387,34 @@ int xaxb_tp_allreduce_sum_rmsnorm(xaxb_ctx* ctx, void* stream, void* const* peer
                                   int64_t data_offset_bytes, int64_t sync_offset_bytes, int64_t rows, int64_t cols,
                                   void* x_bf16, const void* weight_bf16, float eps, void* q_e4m3, float* row_scale,
                                   float* row_inv_scale);
+
+/*
+ * The all-reduce fused into the row-parallel GEMM's epilogue (what xax/arch/llm.py:965-968 leaves to the
+ * compiler after o_proj / down_proj), for the decode step (M <= 128 token rows).
+ *
+ * xaxb_gemm_fp8_push: xaxb_gemm_fp8 whose epilogue writes every 16-byte piece of the bf16 output straight
+ *   into slot `rank` of EVERY rank's staging buffer (row-major [M, N] at slot_offset_bytes of each mapping in
+ *   peer_bases; plain peer stores over NVLink) and then adds the number of pieces it completed to the 32-bit
+ *   arrival counter at flag_offset_bytes of every rank's buffer (system-scope release).  No local `out`.
+ * xaxb_tp_push_sum_rmsnorm: the consumer, one CTA per token row.  `staging` is THIS rank's buffer of `world`
+ *   slots, slot_stride_bytes apart, `counter` its arrival counter, `totals` xaxb_tp_push_totals_bytes() of
+ *   local memory, zero-filled once, holding the running number of pieces expected per row.  It waits (bounded,
+ *   site 46) until world * rows * cols / 8 further pieces have arrived, sums the slots in rank order in
+ *   float32 -- every rank gets the same bits -- and writes x_bf16 [rows, cols]; with weight_bf16 non-NULL also
+ *   RMSNorm + per-token e4m3 cast of the sum as xaxb_tp_allreduce_sum_rmsnorm does.  It reads local memory only.
+ * Staging buffer and counter must alternate between two pairs from one exchange to the next, every rank must
+ * issue the same sequence, and a (staging, counter, totals) triple must see the same world on every use.
+ */
+int xaxb_gemm_fp8_push(xaxb_ctx* ctx, void* stream, const void* a_e4m3, int64_t lda, const void* b_e4m3, int64_t ldb,
+                       int64_t M, int64_t N, int64_t K, const float* row_mul, int row_mul_stride, const float* col_mul,
+                       int col_mul_stride, const void* bias_bf16, const void* residual_bf16, int64_t ldr,
+                       void* const* peer_bases, int rank, int world, int64_t slot_offset_bytes,
+                       int64_t flag_offset_bytes);
+int64_t xaxb_tp_push_totals_bytes(void);
+int xaxb_tp_push_sum_rmsnorm(xaxb_ctx* ctx, void* stream, const void* staging, int64_t slot_stride_bytes,
+                             const void* counter, void* totals, int world, int64_t rows, int64_t cols, void* x_bf16,
+                             const void* weight_bf16, float eps, void* q_e4m3, float* row_scale,
+                             float* row_inv_scale);
 
 /* The two places of a block where an activation amax spans the ranks, with the exchange done
  * inside the kernel that produces the activation (each CTA owns one token row: it pushes the

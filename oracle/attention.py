@@ -256,6 +256,33 @@ class SelfAttentionBlock:
         shape = (max_len, self.num_kv_heads, self.head_dim)
         return {"k": np.zeros(shape, dtype), "v": np.zeros(shape, dtype), "position": np.int32(0)}
 
+    def call_batched(self, x_btd, positions_bt=None):
+        """:700-773, ``__call__``: batched, no cache.  Every projection goes through apply_linear on the whole
+        (batch, seq, dim) tensor (an FP8 layer: one activation scale for everything), RoPE takes explicit
+        positions, the causal mask goes by token index."""
+        x_btd = np.asarray(x_btd)
+        assert x_btd.ndim == 3
+        B, T, _ = x_btd.shape
+        if positions_bt is None:
+            positions_bt = np.broadcast_to(np.arange(T)[None, :], (B, T))
+        q = apply_linear(x_btd, self.q_proj).reshape(B, T, self.num_heads, self.head_dim)
+        k = apply_linear(x_btd, self.k_proj).reshape(B, T, self.num_kv_heads, self.head_dim)
+        v = apply_linear(x_btd, self.v_proj).reshape(B, T, self.num_kv_heads, self.head_dim)
+        if self.q_norm is not None:
+            q = self.q_norm(q)
+        if self.k_norm is not None:
+            k = self.k_norm(k)
+        outs = []
+        for b in range(B):
+            qb, kb = q[b], k[b]
+            if self.rotary_emb is not None:
+                pos = np.asarray(positions_bt[b]).astype(np.int32)
+                qb = self.rotary_emb.apply_rotary_embeddings(qb, pos)
+                kb = self.rotary_emb.apply_rotary_embeddings(kb, pos)
+            lw = (self.local_window_size, 0) if self.local_window_size else None  # :765
+            outs.append(dot_product_attention(qb, kb, v[b], is_causal=self.causal, local_window_size=lw).reshape(T, -1))
+        return apply_linear(np.stack(outs), self.output_proj)
+
     def forward(self, x_tn, *, cache=None):
         """:826-980 (mask=None, fp8_scales=None)."""
         x_tn = np.asarray(x_tn)

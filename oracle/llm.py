@@ -96,6 +96,94 @@ def greedy_token(logits_v) -> int:
     return int(np.argmax(f32(logits_v)))
 
 
+def apply_sampling_mask(logits_1v, generated_count: int, eos_id: int, min_new_tokens_before_eos: int = 0,
+                        allowed_token_range=None):
+    """xax/arch/llm.py:1547-1570: tokens outside the allowed range -- and EOS before
+    ``min_new_tokens_before_eos`` tokens were generated -- get the most negative finite value of the
+    logits' dtype."""
+    logits_1v = np.asarray(logits_1v)
+    ids = np.arange(logits_1v.shape[-1], dtype=np.int32)
+    allow_eos = generated_count >= min_new_tokens_before_eos
+    if allowed_token_range is None:
+        allowed = np.ones_like(ids, dtype=bool)
+        if eos_id >= 0 and not allow_eos:
+            allowed &= ids != eos_id
+    else:
+        lo, hi = allowed_token_range
+        if hi <= lo:
+            raise ValueError("allowed_token_range must satisfy max_id > min_id.")
+        allowed = (ids >= lo) & (ids < hi)
+        if eos_id >= 0 and allow_eos:
+            allowed |= ids == eos_id
+    import ml_dtypes
+
+    min_logit = np.asarray(ml_dtypes.finfo(logits_1v.dtype).min).astype(logits_1v.dtype)
+    return np.where(allowed[None, :], logits_1v, min_logit)
+
+
+def nucleus(logits_v, temperature: float, top_p: float):
+    """xax/arch/llm.py:1472-1482 for one row: (token ids in sorted order, their probabilities, kept mask).
+    Descending stable sort of logits / temperature, float32 softmax and cumulative sum over the sorted
+    order, a token is dropped when its inclusive cumulative probability exceeds top_p, the first never."""
+    scaled = (f32(logits_v) / float32(temperature)).astype(float32)
+    order = np.argsort(-scaled, kind="stable")
+    srt = scaled[order]
+    e = np.exp(srt - srt[0], dtype=float32)
+    probs = (e / e.sum(dtype=float32)).astype(float32)
+    cum = np.cumsum(probs, dtype=float32)
+    drop = cum > float32(top_p)
+    drop[0] = False
+    return order, probs, ~drop
+
+
+def sample_next_token(logits_tv, temperature: float, top_p: float, uniforms=None):
+    """xax/arch/llm.py:1446-1489 with the random draw restated as an inverse CDF: the reference draws with
+    jax.random.categorical over the kept logits (same distribution, its own PRNG stream); here row t takes
+    the token at quantile ``uniforms[t]`` of the kept tokens in sorted order.  Returns int32 (tsz, 1)."""
+    logits_tv = np.asarray(logits_tv)
+    out = np.zeros((logits_tv.shape[0], 1), np.int32)
+    for t in range(logits_tv.shape[0]):
+        if temperature <= 0:  # :1469-1470, :1489
+            out[t, 0] = int(np.argmax(f32(logits_tv[t])))
+            continue
+        order, probs, keep = nucleus(logits_tv[t], temperature, top_p)
+        p = np.where(keep, probs, 0.0).astype(np.float64)
+        cdf = np.cumsum(p)
+        j = int(np.searchsorted(cdf, float(uniforms[t]) * cdf[-1], side="right"))
+        j = min(j, int(np.nonzero(keep)[0][-1]))
+        out[t, 0] = int(order[j])
+    return out
+
+
+def llm_generate_sampled(model: LLM, tokens_t, eos_id: int, max_new_tokens: int, temperature: float, top_p: float,
+                         uniforms, allowed_token_range=None, min_new_tokens_before_eos: int = 0):
+    """xax/arch/llm.py:1492-1614 with sampling: ``uniforms[i]`` drives the draw of the i-th new token (the
+    reference splits its PRNG key once per token instead).  Returns (tokens[max_len] int32, final_len)."""
+    if min_new_tokens_before_eos < 0:
+        raise ValueError("min_new_tokens_before_eos must be >= 0.")
+    tokens_t = np.asarray(tokens_t, dtype=np.int32)
+    initial_len = tokens_t.shape[-1]
+    max_len = initial_len + max_new_tokens
+    if max_new_tokens <= 0:
+        return tokens_t, initial_len
+    padded = np.zeros(max_len, dtype=np.int32)
+    padded[:initial_len] = tokens_t
+    caches = model.init_cache(max_len, model.embed.weight.dtype)
+    logits, caches = model.forward(tokens_t, caches=caches)
+    cur, done = initial_len, False
+    last = logits[-1:]
+    while True:
+        masked = apply_sampling_mask(last, cur - initial_len, eos_id, min_new_tokens_before_eos, allowed_token_range)
+        nxt = int(sample_next_token(masked, temperature, top_p, uniforms[cur - initial_len:cur - initial_len + 1])[0, 0])
+        padded[cur] = nxt
+        done = eos_id >= 0 and nxt == eos_id
+        cur += 1
+        if cur >= max_len or done:
+            break
+        last, caches = model.forward(padded[cur - 1:cur], caches=caches)
+    return padded, cur
+
+
 def llm_generate_greedy(model: LLM, tokens_t, eos_id: int, max_new_tokens: int):
     """xax/arch/llm.py:1492-1614 with temperature <= 0 (greedy), no context, no token
     range: prefill the cache with the prompt, then one token per iteration until max_len or

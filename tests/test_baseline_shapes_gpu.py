@@ -12,12 +12,13 @@ dimensions the benchmark names, so the kernels and plans that are timed are the 
             enough for the CTA-pair GEMM, and two decode steps of 128 sequences (split-K clusters, the
             fused q|k|v and gate|up operands with per-column multipliers, the 256-wide tile kernel).
 
-Bars: e4m3 bytes, amax history and scales bit-exact; outputs within a relative Frobenius error of 1e-2
-of the oracle.  For the blocks of config 2 and 5 -- several FP8 linears chained, so the two ways the
-reference itself can execute them ("dequantise, bf16 matmul" on CPU; an FP8 matmul on a GPU) already
-differ by more than 1e-2 -- the bar is 1e-2 against the FP8-matmul execution for every linear fed the
-oracle's own input, and the measured whole-block figures against both executions are asserted at the
-level the two executions agree with each other.
+Bars: e4m3 bytes, amax history and scales bit-exact; single linears, attention and the config-2 block
+within a relative Frobenius error of 1e-2 of the oracle.  The config-5 layer chains four FP8 casts with
+unscaled N(0, 0.02^2) weights, so what the block adds outweighs the residual stream and the two ways the
+reference itself can execute it ("dequantise, bf16 matmul" on CPU; an FP8 matmul on a GPU,
+xax/nn/fp8.py:3-11) differ by about 4e-2 (oracle against oracle): there the bar is 1e-2 for every linear
+fed the oracle's own input, and for the whole block "no further from either execution than they are from
+each other" (+25 %).  The measured figures are printed.
 """
 
 import numpy as np
@@ -211,8 +212,11 @@ def test_cfg5_layer_prefill_pair_kernel_size(cfg5_layer):
     print(f"cfg5 layer prefill: {e_mm:.3e} vs FP8-matmul oracle, {e_qdq:.3e} vs QDQ oracle, oracle vs oracle {oo:.3e}; "
           f"block delta only: {rel_fro(d_got, d_mm):.3e} / {rel_fro(d_got, d_qdq):.3e} (oracle vs oracle "
           f"{rel_fro(d_mm, d_qdq):.3e})")
-    assert e_mm < TOL and e_qdq < TOL
-    assert rel_fro(d_got, d_mm) < 1.25 * rel_fro(d_mm, d_qdq) + 1e-2
+    lw = _linearwise(ob, blk, x[0, :256])
+    print(f"cfg5 linears at M = 256, teacher-forced vs FP8-matmul oracle: {({k: float(f'{v:.2e}') for k, v in lw.items()})}")
+    assert max(lw.values()) < TOL, lw
+    assert e_mm < 1.25 * oo + 2e-3 and e_qdq < 1.25 * oo + 2e-3
+    assert rel_fro(d_got, d_mm) < 1.25 * rel_fro(d_mm, d_qdq) + 2e-3
 
 
 def test_cfg5_layer_decode_batch_128(cfg5_layer):
@@ -253,8 +257,9 @@ def test_cfg5_layer_decode_batch_128(cfg5_layer):
         d_got, d_mm, d_qdq = f32(got) - xs, f32(exp_mm) - xs, f32(exp_qdq) - xs
         print(f"cfg5 layer decode step {step}: {e_mm:.3e} vs FP8-matmul oracle, {e_qdq:.3e} vs QDQ oracle; block delta "
               f"only: {rel_fro(d_got, d_mm):.3e} / {rel_fro(d_got, d_qdq):.3e} (oracle vs oracle {rel_fro(d_mm, d_qdq):.3e})")
-        assert e_mm < TOL and e_qdq < TOL
-        assert rel_fro(d_got, d_mm) < 1.25 * rel_fro(d_mm, d_qdq) + 1e-2
+        oo = rel_fro(f32(exp_mm), f32(exp_qdq))
+        assert e_mm < 1.25 * oo + 2e-3 and e_qdq < 1.25 * oo + 2e-3
+        assert rel_fro(d_got, d_mm) < 1.25 * rel_fro(d_mm, d_qdq) + 2e-3
         n = lens + step + 1
         assert to_numpy(cache["position"]).tolist() == n.tolist()
         # the rows appended to the cache this step

@@ -1,6 +1,8 @@
-"""Tensor-parallel run on two GPUs (NCCL, then the peer-memory exchange kernels) against the unsharded model on
-one GPU, same seed.
-Skipped when fewer than two GPUs are visible."""
+"""Tensor-parallel run on 2, 4 and 8 GPUs (NCCL, then the peer-memory exchange kernels: the all-reduce pushed
+from the row-parallel GEMM's epilogue, and the pull variant) against the unsharded model on one GPU, same seed.
+Each case is skipped when fewer GPUs are visible.  NVLink multicast stays off in every library used
+(NCCL_NVLS_ENABLE=0; the symmetric buffer is never bound to a multicast object), the ranks meet at a host-side
+barrier with idle GPUs before they leave, and every device-side wait is bounded."""
 
 import os
 import socket
@@ -24,18 +26,21 @@ def _worker(rank: int, world: int, port: int, results):
     sys.path.insert(0, ROOT)
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    os.environ["TORCH_SYMM_MEM_DISABLE_MULTICAST"] = "1"
     import torch.distributed as dist
 
     torch.cuda.set_device(rank)
     dev = torch.device("cuda", rank)
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    host = dist.new_group(backend="gloo")
     try:
         from xax_b200 import _lib
         from xax_b200.arch.llm import LLM, DecodeState, LLMConfig
         from xax_b200.parallel import TensorParallel
 
-        cfg = LLMConfig(vocab_size=1024, embed_dim=512, q_heads=8, kv_heads=4, head_dim=64, num_layers=3,
-                        mlp_hidden_dim=1024, rms_eps=1e-5)
+        cfg = LLMConfig(vocab_size=1024, embed_dim=512, q_heads=8, kv_heads=4 if world <= 4 else 8, head_dim=64,
+                        num_layers=3, mlp_hidden_dim=1024, rms_eps=1e-5)
         B, T = 4, 48
         toks = torch.randint(0, 1024, (B, T), generator=torch.Generator().manual_seed(3), dtype=torch.int32).to(dev)
         tp = TensorParallel(rank, world)
@@ -121,6 +126,17 @@ def _worker(rank: int, world: int, port: int, results):
             seq2.append(st2.replay().clone())
         _lib.device_status()
         peer_same = all(bool(torch.equal(a, b)) for a, b in zip(seq, seq2))
+        # the same again with the pull variant of the sum (the GEMM writes locally, the sum kernel reads the
+        # peers' rows): same arithmetic in the same order, so the tokens are the push run's
+        tp4 = TensorParallel(rank, world, push=False)
+        tp4.peer = tp2.peer
+        st4 = DecodeState(m, B, T + 8, tp=tp4)
+        seq4 = [st4.prefill(toks).clone()]
+        st4.capture()
+        for _ in range(3):
+            seq4.append(st4.replay().clone())
+        _lib.device_status()
+        push_same = tp2.push and all(bool(torch.equal(a, b)) for a, b in zip(seq2, seq4))
         # per-rank-slice scaling (opt-in deviation): still the projection's output, to FP8 accuracy
         tp3 = TensorParallel(rank, world, local_amax=True)
         tp3.peer = tp2.peer
@@ -135,6 +151,7 @@ def _worker(rank: int, world: int, port: int, results):
         yd_l, _ = tp3.block_forward(m.blocks[0], xd, B, 1, cache=cache_b)
         err_local_decode = float((yd_l.float() - yd_g.float()).norm() / yd_g.float().norm())
         results[rank] = dict(err=err, same_bytes=same_bytes, agree=agree, consistent=consistent, max_ok=max_ok,
+                             push_same=push_same,
                              err_local=err_local, err_local_decode=err_local_decode,
                              sum_ok=sum_ok, peer_same=peer_same, fused_ok=fused_ok)
     except Exception:  # noqa: BLE001
@@ -143,17 +160,23 @@ def _worker(rank: int, world: int, port: int, results):
         results[rank] = traceback.format_exc()
     finally:
         # A process group whose collectives were captured in a CUDA graph can block in
-        # destroy_process_group; leave without tearing NCCL down (results are already stored).
-        torch.cuda.synchronize()
+        # destroy_process_group; leave without tearing NCCL down (results are already stored).  The ranks
+        # first drain their GPUs and meet on the host, so nobody leaves while a peer still waits on it.
+        try:
+            torch.cuda.synchronize()
+            dist.barrier(group=host)
+        except Exception:  # noqa: BLE001  (a rank that failed may never arrive: the others time out and leave)
+            pass
         sys.stdout.flush()
         os._exit(0)
 
 
-@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
-def test_tensor_parallel_two_gpus_matches_one_gpu():
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_tensor_parallel_matches_one_gpu(world):
     import torch.multiprocessing as mp
 
-    world = 2
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
     with mp.Manager() as mgr:
         results = mgr.dict()
         mp.spawn(_worker, args=(world, _free_port(), results), nprocs=world, join=True)
@@ -170,4 +193,6 @@ def test_tensor_parallel_two_gpus_matches_one_gpu():
         # per-rank-slice scales put the e4m3 grid elsewhere than the unsharded model's: the block output moves
         # by FP8 rounding noise (the reference's own two executions of one block differ by 7e-2)
         assert res[r]["err_local"] < 6e-2 and res[r]["err_local_decode"] < 6e-2, res[r]
-        assert res[r]["max_ok"] and res[r]["sum_ok"] and res[r]["fused_ok"] and res[r]["peer_same"], res[r]
+        assert res[r]["max_ok"] and res[r]["sum_ok"] and res[r]["fused_ok"] and res[r]["push_same"], res[r]
+        if world == 2:  # two ranks: a + b rounds the same either way, so NCCL's sum gives the same tokens
+            assert res[r]["peer_same"], res[r]

@@ -17,9 +17,11 @@ NAME_MAP = {
     "RMSNorm": "arch.attention", "RotaryEmbedding": "arch.attention", "SelfAttentionBlock": "arch.attention",
     "SwiGLU": "arch.attention", "TransformerBlock": "arch.attention", "apply_linear": "arch.attention",
     "can_use_cudnn_attention": "arch.attention", "Linear": "arch.attention", "Embedding": "arch.attention",
+    "TransformerStack": "arch.attention", "Transformer": "arch.attention", "TransformerCache": "arch.attention",
     # xax.arch.llm
     "LLM": "arch.llm", "LLMConfig": "arch.llm", "llm_generate": "arch.llm", "llm_generate_jit": "arch.llm",
-    "llm_generate_batch": "arch.llm", "tie_embedding_and_head": "arch.llm",
+    "llm_generate_batch": "arch.llm", "llm_generate_stream": "arch.llm", "TokenSampler": "arch.llm",
+    "tie_embedding_and_head": "arch.llm",
     "get_model_parallel_sharding_spec": "arch.llm", "DecodeState": "arch.llm",
     "build_pretrained_llm": "arch.hf", "hf_config_to_llm_config": "arch.hf", "load_hf_weights_into_llm": "arch.hf",
     # xax.nn.fp8 (not re-exported by xax at top level; offered here for convenience)

@@ -47,12 +47,14 @@ SIGNATURES: dict[str, tuple] = {
     "xaxb_gemm_fp8": (_I, [_P, _P, _P, _I64, _P, _I64, _I64, _I64, _I64, _P, _I, _P, _I, _P, _P, _I64, _P, _I64]),
     "xaxb_gemm_bf16": (_I, [_P, _P, _P, _I64, _P, _I64, _I64, _I64, _I64, _P, _I, _P, _I, _P, _P, _I64, _P, _I64]),
     "xaxb_gemm_force_plan": (_I, [_I, _I]),
+    "xaxb_gemm_set_prefetch": (_I, [_I, _I]),
     "xaxb_gemm_fp8_check": (_I, [_P, _P, _P, _I64, _P, _I64, _I64, _I64, _I64, _P, _I, _P, _I, _P, _P, _I64, _P, _I64]),
     "xaxb_rmsnorm": (_I, [_P, _P, _P, _P, _F, _I64, _I64, _P, _P, _P, _P, _P, _I64]),
     "xaxb_silu_mul": (_I, [_P, _P, _P, _P, _I64, _I64, _I64, _P, _P, _P, _P, _P, _I64]),
     "xaxb_embed": (_I, [_P, _P, _P, _I64, _P, _I64, _I64, _P]),
     "xaxb_argmax": (_I, [_P, _P, _P, _I64, _I64, _I64, _P, _P]),
     "xaxb_argmax_merge": (_I, [_P, _P, _P, _P, _I64, _I64, _I64, _P]),
+    "xaxb_sample_top_p": (_I, [_P, _P, _P, _I64, _I64, _I64, _F, _F, _P, c_int32, c_int32, c_int32, _I, _P]),
     "xaxb_group_amax": (_I, [_P, _P, _P, _I64, _I64, _I64, _P]),
     "xaxb_kv_append_rope": (_I, [_P, _P, _P, _I64, _I64, _I64, _I64, _I64, _I64, _P, _P, _P, _I64, _P, _P, _P, _I64, _I]),
     "xaxb_attn_decode_workspace_bytes": (_I64, [_I64, _I64, _I64, _I64]),
@@ -76,6 +78,10 @@ SIGNATURES: dict[str, tuple] = {
     "xaxb_silu_mul_cast_tp": (_I, [_P, _P, _P, _P, _I64, _I64, _I64, _P, _P, _P, _P, _I, _I, _I64, _I64]),
     "xaxb_attn_decode_cast_tp": (_I, [_P, _P, _P, _P, _P, _P, _I64, _I64, _I64, _I64, _I64, _F, _I, _P, _P, _I64, _P, _P,
                                       _P, _P, _I64, _P, _I, _I, _I64, _I64]),
+    "xaxb_gemm_fp8_push": (_I, [_P, _P, _P, _I64, _P, _I64, _I64, _I64, _I64, _P, _I, _P, _I, _P, _P, _I64, _P, _I, _I,
+                                _I64, _I64]),
+    "xaxb_tp_push_totals_bytes": (_I64, []),
+    "xaxb_tp_push_sum_rmsnorm": (_I, [_P, _P, _P, _I64, _P, _P, _I, _I64, _I64, _P, _P, _F, _P, _P, _P]),
     "xaxb_tp_argmax_inbox_bytes": (_I64, []),
     "xaxb_tp_argmax": (_I, [_P, _P, _P, _I, _I, _I64, _I64, _P, _P, _I64, _I64, _P]),
     "xaxb_tp_allreduce_max_f32": (_I, [_P, _P, _P, _I, _I, _I64, _I64, _P, _P, _I64]),

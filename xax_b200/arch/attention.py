@@ -433,7 +433,7 @@ class SelfAttentionBlock:
         if x_tn.dim() != 2:
             raise ValueError(f"expected rank 2 input, got rank {x_tn.dim()}")
         if mask is not None:
-            raise ValueError("explicit masks are outside the path this library covers (causal masking is built in)")
+            self._require_builtin_mask(mask, x_tn.shape[0], cache)
         if fp8_scales is not None:
             raise ValueError("delayed scaling through the attention block is undefined in the reference "
                              "(its Fp8Scales is not a pytree); call Fp8Linear directly with scales")
@@ -442,6 +442,69 @@ class SelfAttentionBlock:
             bc = {"k": cache["k"].unsqueeze(0), "v": cache["v"].unsqueeze(0), "position": cache["position"].reshape(1)}
         out, nc = self.forward_tokens(x_tn, 1, x_tn.shape[0], cache=bc, donate=donate)
         return out, {"k": nc["k"][0], "v": nc["v"][0], "position": nc["position"].reshape(())}, None
+
+    def _require_builtin_mask(self, mask: torch.Tensor, T: int, cache) -> None:
+        """The reference hands an explicit mask to dot_product_attention in place of every built-in rule
+        (xax/arch/attention.py:907-909).  The kernels mask by position, so an explicit mask is accepted when
+        it is the mask they apply anyway -- filled cache rows that are causal for the query and inside the
+        window, (T, max_len) with a cache and (T, T) without (any leading singleton dimensions) -- and
+        refused otherwise."""
+        if not self.causal:
+            raise ValueError("the attention kernels are causal")
+        start = int(cache["position"]) if cache is not None else 0
+        S = cache["k"].shape[-3] if cache is not None else T
+        if mask.numel() != T * S:
+            raise ValueError(f"mask has {mask.numel()} elements, expected ({T}, {S})")
+        qpos = torch.arange(T, device=mask.device)[:, None] + start
+        kpos = torch.arange(S, device=mask.device)[None, :]
+        want = kpos <= qpos
+        if self.local_window_size is not None:
+            want &= kpos >= qpos - self.local_window_size
+        if not torch.equal(mask.reshape(T, S).to(torch.bool), want):
+            raise ValueError("explicit masks other than the causal (and sliding-window) mask the kernels apply are "
+                             "outside the path this library covers")
+
+    def __call__(self, x_btd: torch.Tensor, positions_bt: torch.Tensor | None = None, *, key=None,
+                 inference: bool = True) -> torch.Tensor:
+        """xax/arch/attention.py:700-773: batched self-attention without a cache.  As there, every projection
+        goes through ``apply_linear`` on the whole (batch, seq, dim) tensor -- an FP8 layer therefore uses ONE
+        activation scale for the whole batch (:52-58) -- RoPE takes explicit positions (default 0 .. seq-1) and
+        the causal mask goes by token index, not by position.  ``key`` and ``inference`` are unused, as in
+        the reference."""
+        if x_btd.dim() != 3:
+            raise ValueError(f"expected rank 3 input (batch, seq_len, embed_dim), got rank {x_btd.dim()}")
+        if not self.causal:
+            raise ValueError("the attention kernels are causal")
+        B, T, _ = x_btd.shape
+        Hq, Hkv, D = self.num_heads, self.num_kv_heads, self.head_dim
+        x2 = x_btd.reshape(B * T, -1).to(BF16).contiguous()
+        projs = (self.q_proj, self.k_proj, self.v_proj)
+        if self._is_fp8():  # the three layers quantise the same tensor the same way: do it once
+            xq, _, x_inv, _ = ops.quantize_current(x2, B * T)
+            q, k, v = (p.forward_quantized(xq, x_inv) for p in projs)
+        else:
+            q, k, v = (apply_linear(x2, p) for p in projs)
+        if self.q_norm is not None:  # :739-742, per head
+            q = self.q_norm(q.reshape(B * T * Hq, D)).reshape(B * T, Hq * D)
+        if self.k_norm is not None:
+            k = self.k_norm(k.reshape(B * T * Hkv, D)).reshape(B * T, Hkv * D)
+        if self.rotary_emb is not None:  # :745-747
+            if positions_bt is None:
+                positions_bt = torch.arange(T, device=x2.device, dtype=torch.int32)[None, :].expand(B, T)
+            pos = positions_bt.to(torch.int32).contiguous()
+            q = self.rotary_emb.apply_rotary_embeddings(q.reshape(B, T, Hq, D), pos)
+            k = self.rotary_emb.apply_rotary_embeddings(k.reshape(B, T, Hkv, D), pos)
+        # the new keys and values ARE a cache of T rows per sequence whose queries start at row 0
+        q3 = q.reshape(B * T, Hq, D).contiguous()
+        kc, vc = k.reshape(B, T, Hkv, D).contiguous(), v.reshape(B, T, Hkv, D).contiguous()
+        zero = torch.zeros((B,), dtype=torch.int32, device=x2.device)
+        scale = 1.0 / math.sqrt(D)
+        if self.local_window_size:  # :765 (a window of 0 counts as "none" there)
+            ctx = ops.attn_prefill_window(q3, kc, vc, zero, B, T, self.local_window_size, scale=scale)
+        else:
+            ctx = ops.attn_prefill(q3, kc, vc, zero, B, T, scale=scale)
+        out = apply_linear(ctx.reshape(B * T, Hq * D), self.output_proj)
+        return out.reshape(B, T, -1)
 
     def forward_tokens(self, y: torch.Tensor, B: int, T: int, *, cache=None, donate: bool = True, y_q=None,
                        residual=None, workspace=None, advance: bool = True, reduce_amax=None, out=None,
@@ -594,8 +657,10 @@ class TransformerBlock:
         """xax/arch/attention.py:1443-1510 for one sequence (T, H)."""
         if x_tn.dim() != 2:
             raise ValueError(f"expected rank 2 input, got rank {x_tn.dim()}")
-        if context_sn is not None or mask is not None:
-            raise ValueError("cross-attention context and explicit masks are outside the path this library covers")
+        if context_sn is not None:
+            raise ValueError("cross-attention context is outside the path this library covers")
+        if mask is not None:  # accepted when it is the mask the kernels apply anyway
+            self.self_attn._require_builtin_mask(mask, x_tn.shape[0], None if cache is None else cache["self_attn"])
         bc = None
         if cache is not None:
             a = cache["self_attn"]
@@ -635,3 +700,149 @@ class TransformerBlock:
             y, _ = ops.rmsnorm(x1, wm, self.mlp_norm.eps)
             x2 = ff.forward_tokens(y, B, T, residual=x1)
         return x2, new_cache
+
+
+class TransformerCache(TypedDict):
+    """xax/arch/attention.py:1208-1211: {"layers": {"layer_<i>": TransformerBlockCache}}."""
+
+    layers: dict[str, TransformerBlockCache]
+
+
+class TransformerStack:
+    """xax/arch/attention.py:1513-1654: a stack of transformer blocks with the reference's cache layout.
+
+    The reference's ``build`` makes LayerNorm + GELU-MLP blocks (it leaves ``norm_type`` / ``feedforward_type``
+    of TransformerBlock.build at their defaults); the kernels of this library cover the RMSNorm + SwiGLU
+    block of the LLM path, so ``build`` takes the two keywords explicitly (an extension), defaults to what
+    the kernels cover, and refuses the rest like TransformerBlock.build does.  Stacks can also be made from
+    existing blocks through the constructor."""
+
+    def __init__(self, layers, num_layers: int | None = None, causal: bool = True, use_fp8: bool = False):
+        self.layers = tuple(layers)
+        self.num_layers = len(self.layers) if num_layers is None else num_layers
+        self.causal, self.use_fp8 = causal, use_fp8
+
+    @classmethod
+    def build(cls, embed_dim: int, num_heads: int, ff_dim: int, num_layers: int, *, key=None, causal: bool = False,
+              cross_attention: bool = False, context_length: int | None = None, use_rotary_embeddings: bool = False,
+              rotary_base: float = 10000.0, use_fp8: bool = False, compute_dtype=BF16, norm_type: str = "rmsnorm",
+              feedforward_type: str = "swiglu", num_kv_heads: int | None = None, head_dim: int | None = None,
+              norm_eps: float = 1e-6, fp8_mlp: bool | None = None, device=None) -> "TransformerStack":
+        seed = int(key or 0) if not isinstance(key, torch.Generator) else int(key.initial_seed())
+        layers = tuple(
+            TransformerBlock.build(embed_dim, num_heads, ff_dim, key=seed * 1000 + i, num_kv_heads=num_kv_heads,
+                                   head_dim=head_dim, causal=causal, cross_attention=cross_attention,
+                                   context_length=context_length, use_rotary_embeddings=use_rotary_embeddings,
+                                   rotary_base=rotary_base, norm_type=norm_type, norm_eps=norm_eps,
+                                   feedforward_type=feedforward_type, use_fp8=use_fp8, compute_dtype=compute_dtype,
+                                   fp8_mlp=fp8_mlp, device=device)
+            for i in range(num_layers))
+        return cls(layers, num_layers, causal, use_fp8)
+
+    def init_cache(self, dtype=None, x_tn=None, fp8_history_length: int | None = None,
+                   max_len: int | None = None) -> TransformerCache:
+        """:1583-1602.  The reference sizes the cache from the blocks' ``context_length``; ``max_len`` (an
+        extension) overrides it for blocks built without one."""
+        if x_tn is not None:
+            raise ValueError("cross-attention context is outside the path this library covers")
+        return {"layers": {f"layer_{i}": layer.init_cache(max_len=max_len, dtype=dtype,
+                                                          fp8_history_length=fp8_history_length)
+                           for i, layer in enumerate(self.layers)}}
+
+    def init_mask(self, seq_len: int, add_cache: bool = False, batch_dim: bool = False) -> torch.Tensor:
+        return self.layers[0].init_mask(seq_len, add_cache=add_cache, batch_dim=batch_dim)  # :1604-1614
+
+    def forward(self, x_tn: torch.Tensor, *, context_sn=None, mask=None, cache: TransformerCache | None = None,
+                donate: bool = True):
+        """:1616-1654: (output (seq_len, embed_dim), updated cache)."""
+        if cache is None:
+            cache = {"layers": {}}
+        updated: TransformerCache = {"layers": {}}
+        for i, layer in enumerate(self.layers):
+            x_tn, updated["layers"][f"layer_{i}"] = layer.forward(x_tn, context_sn=context_sn, mask=mask,
+                                                                   cache=cache["layers"].get(f"layer_{i}"), donate=donate)
+        return x_tn, updated
+
+
+class Transformer:
+    """xax/arch/attention.py:1657-1912: token embedding, a TransformerStack, a final norm and an optional output
+    projection, with ``encode`` / ``forward`` / ``predict_sequence`` / ``generate_sequence``.  The final norm is
+    an RMSNorm here (the reference's is a LayerNorm; see TransformerStack); ``decode`` with a cross-attention
+    context is refused."""
+
+    def __init__(self, token_embedding: Embedding, layers: TransformerStack, layer_norm: RMSNorm, embed_dim: int,
+                 causal: bool, use_fp8: bool = False, output_layer=None, context_length: int | None = None):
+        self.token_embedding, self.layers, self.layer_norm = token_embedding, layers, layer_norm
+        self.embed_dim, self.causal, self.use_fp8 = embed_dim, causal, use_fp8
+        self.output_layer, self.context_length = output_layer, context_length
+
+    @classmethod
+    def build(cls, vocab_size: int, embed_dim: int, num_heads: int, ff_dim: int, num_layers: int,
+              output_size: int | None = None, *, key=None, causal: bool = False, cross_attention: bool = False,
+              context_length: int | None = None, use_rotary_embeddings: bool = False, rotary_base: float = 10000.0,
+              use_fp8: bool = False, compute_dtype=BF16, device=None, **stack_kwargs) -> "Transformer":
+        seed = int(key or 0) if not isinstance(key, torch.Generator) else int(key.initial_seed())
+        emb = Embedding(vocab_size, embed_dim, key=seed * 4 + 1, device=device)
+        stack = TransformerStack.build(embed_dim, num_heads, ff_dim, num_layers, key=seed * 4 + 3, causal=causal,
+                                       cross_attention=cross_attention, context_length=context_length,
+                                       use_rotary_embeddings=use_rotary_embeddings, rotary_base=rotary_base,
+                                       use_fp8=use_fp8, compute_dtype=compute_dtype, device=device, **stack_kwargs)
+        out = None
+        if output_size is not None:
+            out = _make_linear(embed_dim, output_size, seed * 4 + 4, use_fp8=use_fp8, compute_dtype=compute_dtype,
+                               device=device)
+        return cls(emb, stack, RMSNorm.build(embed_dim, device=device), embed_dim, causal, use_fp8, out, context_length)
+
+    def init_cache(self, dtype=None, x_tn=None, fp8_history_length: int | None = None,
+                   max_len: int | None = None) -> TransformerCache:
+        return self.layers.init_cache(dtype=dtype, x_tn=x_tn, fp8_history_length=fp8_history_length, max_len=max_len)
+
+    def init_mask(self, seq_len: int, add_cache: bool = False, batch_dim: bool = False) -> torch.Tensor:
+        return self.layers.init_mask(seq_len, add_cache=add_cache, batch_dim=batch_dim)
+
+    def encode(self, x: torch.Tensor, *, mask=None, cache: TransformerCache | None = None):
+        """:1765-1786: token ids (seq_len,) -> (normalised hidden states, updated cache)."""
+        emb = ops.embed(x.to(torch.int32).reshape(-1), self.token_embedding.weight)
+        h, updated = self.layers.forward(emb, mask=mask, cache=cache)
+        return self.layer_norm(h), updated
+
+    def decode(self, x_t, context_s, *, mask=None, cache=None):
+        raise ValueError("cross-attention decoding is outside the path this library covers")  # :1788-1818
+
+    def forward(self, x: torch.Tensor, *, mask=None, cache: TransformerCache | None = None):
+        """:1820-1842."""
+        if x.dim() != 1:
+            raise ValueError(f"expected rank 1 token ids, got rank {x.dim()}")
+        out, updated = self.encode(x, mask=mask, cache=cache)
+        if self.output_layer is not None:
+            out, _ = _apply_linear_batched(self.output_layer, out)
+        return out, updated
+
+    def predict_sequence(self, x_seq: torch.Tensor) -> torch.Tensor:
+        return self.forward(x_seq)[0]  # :1844-1846
+
+    def generate_sequence(self, prompt_seq: torch.Tensor, max_len: int, temperature: float = 1.0,
+                          top_k: int | None = None, key=None, jit_level: int | None = None) -> torch.Tensor:
+        """:1848-1912: prime the cache with the prompt, then ``max_len`` steps, each feeding the last token and
+        drawing the next from softmax(logits / temperature).  ``key``: a torch.Generator on the model's device or
+        an int seed (default 0); the reference draws through jax.random.categorical from its own stream, the
+        distribution is the same.  ``top_k`` is outside the path this library covers."""
+        if top_k is not None:
+            raise ValueError("top-k truncation is outside the path this library covers")
+        if self.output_layer is None:
+            raise ValueError("generate_sequence needs an output projection onto the vocabulary")
+        dev = self.token_embedding.weight.device
+        prompt_seq = prompt_seq.to(device=dev, dtype=torch.int32)
+        n0 = prompt_seq.shape[0]
+        out = torch.zeros((n0 + max_len,), dtype=torch.int32, device=dev)
+        out[:n0] = prompt_seq
+        cache = self.init_cache(max_len=n0 + max_len if self.context_length is None else None)
+        # the prompt primes the cache; like the reference's scan, the first step then feeds the prompt's last
+        # token once more (at cache row n0) and every later step the token drawn before it
+        _, cache = self.encode(prompt_seq, cache=cache)
+        gen = key if isinstance(key, torch.Generator) else torch.Generator(device=dev).manual_seed(int(key or 0))
+        for pos in range(n0 - 1, n0 - 1 + max_len):
+            logits, cache = self.forward(out[pos:pos + 1], cache=cache)
+            u = torch.rand((1,), generator=gen, device=dev, dtype=torch.float32)
+            out[pos + 1] = ops.sample_top_p(logits[-1:].to(BF16).contiguous(), float(temperature), 1.0, u)[0]
+        return out

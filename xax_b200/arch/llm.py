@@ -3,10 +3,10 @@
 tensor-parallel placement rule ``get_model_parallel_sharding_spec``.
 
 The reference generates one sequence at a time and leaves batching to ``jax.vmap``;
-``llm_generate_batch`` is the batched greedy loop (B prompts of equal length), with one
-decode step captured in a CUDA graph and replayed.  Sampling with temperature / top-p,
-HF checkpoint loading, extra-token embeddings and cross-attention are not on the path this
-library covers and raise.
+``llm_generate_batch`` is the batched loop (B prompts of equal length); the greedy decode step is
+captured in a CUDA graph and replayed, a sampled one (temperature / top-p, token-range and EOS
+masks) runs step by step because the random numbers and the EOS rule change per step.
+Extra-token embeddings are outside the path this library covers and raise.
 """
 
 from __future__ import annotations
@@ -262,41 +262,105 @@ def get_model_parallel_sharding_spec(weight_shape: tuple[int, ...], weight_name:
 
 
 # ---------------------------------------------------------------------------------------
-# generation (greedy)
+# generation
 
 
-def _require_greedy(temperature: float) -> None:
-    if temperature > 0:
-        raise NotImplementedError("temperature / top-p sampling is not on the path this library covers; "
-                                  "pass temperature <= 0 for greedy decoding")
+class TokenSampler:
+    """Next-token choice of the generation loop (xax/arch/llm.py:1446-1489 and :1547-1570): the
+    allowed-token-range and minimum-length masks, then arg-max (``temperature <= 0``) or a draw from the
+    top-p nucleus of softmax(logits / temperature).
+
+    ``key`` seeds the draws: a ``torch.Generator`` on the logits' device, an int seed, or None (seed 0,
+    as the reference defaults to ``jax.random.key(0)``); ``uniforms`` (float32 [steps, rows] or [steps])
+    overrides it with explicit numbers in [0, 1), one per row and step.  The reference draws through
+    jax.random.categorical from its own PRNG stream; the distribution is the same, the stream is not."""
+
+    def __init__(self, temperature: float, top_p: float, key=None, *, eos_id: int = -1, allowed_token_range=None,
+                 min_new_tokens_before_eos: int = 0, uniforms: torch.Tensor | None = None):
+        if allowed_token_range is not None and allowed_token_range[1] <= allowed_token_range[0]:
+            raise ValueError("allowed_token_range must satisfy max_id > min_id.")  # :1525-1526
+        if min_new_tokens_before_eos < 0:
+            raise ValueError("min_new_tokens_before_eos must be >= 0.")  # :1527-1528
+        self.temperature, self.top_p, self.key = float(temperature), float(top_p), key
+        self.eos_id, self.range, self.min_new = int(eos_id), allowed_token_range, int(min_new_tokens_before_eos)
+        self.uniforms = uniforms
+        self.generated = 0  # tokens drawn so far per sequence (the loop's generated_count)
+        self._gen: torch.Generator | None = None
+
+    def _draw(self, rows: int, device) -> torch.Tensor | None:
+        if self.temperature <= 0:
+            return None
+        if self.uniforms is not None:
+            u = self.uniforms[self.generated]
+            return u.reshape(-1).expand(rows).to(device=device, dtype=torch.float32).contiguous()
+        if self._gen is None:
+            if isinstance(self.key, torch.Generator):
+                self._gen = self.key
+            else:
+                self._gen = torch.Generator(device=device).manual_seed(int(self.key or 0))
+        return torch.rand((rows,), generator=self._gen, device=device, dtype=torch.float32)
+
+    def __call__(self, logits_bv: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+        rows = logits_bv.shape[0]
+        ops.sample_top_p(logits_bv, self.temperature, self.top_p, self._draw(rows, logits_bv.device),
+                         allowed_token_range=self.range, eos_id=self.eos_id,
+                         allow_eos=self.generated >= self.min_new, out=out)
+        self.generated += 1
+        return out
 
 
 def llm_generate_jit(model: LLM, tokens_t: torch.Tensor, eos_id: int, max_new_tokens: int, context_tn=None,
                      temperature: float = 0.0, top_p: float = 1.0, key=None, allowed_token_range=None,
                      min_new_tokens_before_eos: int = 0):
-    """xax/arch/llm.py:1492-1614 with temperature <= 0: prefill, then one token per step until
-    max_len or EOS.  Returns (tokens[max_len] int32, final_len)."""
-    _require_greedy(temperature)
-    if allowed_token_range is not None or min_new_tokens_before_eos:
-        raise NotImplementedError("sampling masks are not on the path this library covers")
+    """xax/arch/llm.py:1492-1614: prefill, then one token per step until max_len or EOS.  Returns
+    (tokens[max_len] int32, final_len).  ``key``: see TokenSampler."""
+    if allowed_token_range is not None and allowed_token_range[1] <= allowed_token_range[0]:
+        raise ValueError("allowed_token_range must satisfy max_id > min_id.")
+    if min_new_tokens_before_eos < 0:
+        raise ValueError("min_new_tokens_before_eos must be >= 0.")
     if context_tn is not None:
         raise NotImplementedError("context embeddings are not on the path this library covers")
     tokens_t = tokens_t.to(torch.int32)
     initial_len = tokens_t.shape[-1]
-    max_len = initial_len + max_new_tokens
     if max_new_tokens <= 0:  # :1537-1538
         return tokens_t, initial_len
-    out, lens = llm_generate_batch(model, tokens_t.reshape(1, -1), max_new_tokens, eos_id=eos_id)
+    sampler = None
+    if temperature > 0 or allowed_token_range is not None or (eos_id >= 0 and min_new_tokens_before_eos > 0):
+        sampler = TokenSampler(temperature, top_p, key, eos_id=eos_id, allowed_token_range=allowed_token_range,
+                               min_new_tokens_before_eos=min_new_tokens_before_eos)
+    out, lens = llm_generate_batch(model, tokens_t.reshape(1, -1), max_new_tokens, eos_id=eos_id, sampler=sampler)
     return out[0], int(lens[0])
 
 
 def llm_generate(model: LLM, tokens: list[int], eos_id: int | None, max_new_tokens: int = 20, *, context_tn=None,
-                 temperature: float = 0.0, top_p: float = 0.9, key=None) -> list[int]:
-    """xax/arch/llm.py:1419-1443 (greedy only; the reference defaults to temperature 0.7)."""
+                 temperature: float = 0.7, top_p: float = 0.9, key=None) -> list[int]:
+    """xax/arch/llm.py:1419-1443."""
     dev = model.embed.weight.device
     toks, n = llm_generate_jit(model, torch.tensor(tokens, dtype=torch.int32, device=dev),
                                eos_id if eos_id is not None else -1, max_new_tokens, context_tn, temperature, top_p, key)
     return toks[:n].tolist()
+
+
+def llm_generate_stream(model: LLM, tokens: list[int], eos_id: int | None, max_new_tokens: int = 256, *,
+                        context_tn=None, temperature: float = 0.7, top_p: float = 0.9, key=None):
+    """xax/arch/llm.py:1617-1693: yields the generated tokens one at a time (the prompt is not yielded) and
+    stops at EOS, which is not yielded either."""
+    if context_tn is not None:
+        raise NotImplementedError("context embeddings are not on the path this library covers")
+    if max_new_tokens <= 0:
+        return
+    dev = model.embed.weight.device
+    prompt = torch.tensor(tokens, dtype=torch.int32, device=dev).reshape(1, -1)
+    st = DecodeState(model, 1, prompt.shape[1] + max_new_tokens, sampler=TokenSampler(temperature, top_p, key))
+    tok = int(st.prefill(prompt).item())
+    if eos_id is not None and tok == eos_id:
+        return
+    yield tok
+    for _ in range(max_new_tokens - 1):
+        tok = int(st.step().item())
+        if eos_id is not None and tok == eos_id:
+            return
+        yield tok
 
 
 class DecodeState:
@@ -304,8 +368,12 @@ class DecodeState:
     one decode step captured in a CUDA graph.  All layers append at the same position, so they
     share one position vector that is advanced once per step."""
 
-    def __init__(self, model: LLM, batch: int, max_len: int, tp=None):
-        self.model, self.B, self.max_len, self.tp = model, batch, max_len, tp
+    def __init__(self, model: LLM, batch: int, max_len: int, tp=None, sampler=None):
+        """``sampler`` (a TokenSampler) replaces the arg-max; its state lives on the host, so a decode
+        step with a sampler is not captured in a graph."""
+        if sampler is not None and tp is not None:
+            raise ValueError("sampling over a vocabulary-sharded lm_head is outside the path this library covers")
+        self.model, self.B, self.max_len, self.tp, self.sampler = model, batch, max_len, tp, sampler
         dev = model.embed.weight.device
         self.caches = [c["self_attn"] for c in model.init_cache(max_len, batch=batch)]
         self.positions = self.caches[0]["position"]
@@ -317,7 +385,9 @@ class DecodeState:
         self.graph = None
 
     def _next_tokens(self, hidden_bh: torch.Tensor, out: torch.Tensor) -> None:
-        if self.tp is None:
+        if self.sampler is not None:
+            self.sampler(self.model.get_logits(hidden_bh), out)
+        elif self.tp is None:
             ops.argmax(self.model.get_logits(hidden_bh), out=out)
         else:
             self.tp.greedy_tokens(self.model, hidden_bh, out)
@@ -327,6 +397,8 @@ class DecodeState:
         activation memory), fill the caches, return the first generated token per sequence."""
         B, T = tokens_bt.shape
         chunk = chunk or B
+        if self.sampler is not None:
+            chunk = B  # one draw per step for the whole batch
         for b0 in range(0, B, chunk):
             b1 = min(B, b0 + chunk)
             sub = [{"k": c["k"][b0:b1], "v": c["v"][b0:b1], "position": self.positions[b0:b1]} for c in self.caches]
@@ -350,6 +422,9 @@ class DecodeState:
         so the same graph serves every step).  A warm-up step runs first on a side stream; its
         effects (one cache row that the real step rewrites, the position advance, the token)
         are rolled back."""
+        if self.sampler is not None:
+            raise ValueError("a decode step with a sampler cannot be captured (its random numbers and EOS rule "
+                             "change per step); call step()")
         saved_pos = self.positions.clone()
         saved_cur = self.cur.clone()
         s = torch.cuda.Stream()
@@ -386,23 +461,30 @@ class DecodeState:
 
 
 def _sample_next_token(logits_tv: torch.Tensor, temperature: float, top_p: float, key=None, num_samples: int = 1):
-    """xax/arch/llm.py:1446-1489 for the greedy case (``temperature <= 0``, :1469-1470 and :1489):
-    arg-max over the vocabulary in float32, first index on ties, shape (tsz, 1).  Temperature /
-    top-p sampling needs the reference's PRNG stream and is outside the path this library covers."""
-    if temperature > 0:
-        raise ValueError("temperature / top-p sampling is outside the path this library covers (greedy only)")
-    if num_samples != 1:
-        raise ValueError("greedy decoding yields one token per position")
+    """xax/arch/llm.py:1446-1489: next token for every row of logits (tsz, vocab), shape (tsz, num_samples).
+    ``temperature <= 0`` is the arg-max in float32 (first index on ties) whatever ``num_samples`` -- as in
+    the reference, whose final ``where`` broadcasts it; otherwise every sample is a draw from the top-p
+    nucleus.  ``key``: a torch.Generator on the logits' device, an int seed, None (seed 0), or a float32
+    tensor of explicit uniforms [tsz, num_samples]."""
     if logits_tv.dtype != BF16:
-        raise ValueError("the logits of this path are bf16 (the arg-max compares them as float32)")
-    logits = logits_tv
-    return ops.argmax(logits.reshape(-1, logits.shape[-1]).contiguous()).reshape(*logits.shape[:-1], 1)
+        raise ValueError("the logits of this path are bf16 (they are compared and exponentiated as float32)")
+    logits = logits_tv.reshape(-1, logits_tv.shape[-1]).contiguous()
+    rows = logits.shape[0]
+    cols = []
+    if isinstance(key, torch.Tensor):
+        u_all = key.to(device=logits.device, dtype=torch.float32).reshape(rows, num_samples)
+    else:
+        gen = key if isinstance(key, torch.Generator) else torch.Generator(device=logits.device).manual_seed(int(key or 0))
+        u_all = torch.rand((rows, num_samples), generator=gen, device=logits.device, dtype=torch.float32)
+    for j in range(num_samples):
+        cols.append(ops.sample_top_p(logits, temperature, top_p, u_all[:, j].contiguous() if temperature > 0 else None))
+    return torch.stack(cols, dim=-1).reshape(*logits_tv.shape[:-1], num_samples)
 
 
 def llm_generate_batch(model: LLM, tokens_bt: torch.Tensor, max_new_tokens: int, *, eos_id: int = -1,
-                       use_graph: bool = True, prefill_chunk: int | None = None, tp=None):
-    """Batched greedy generation: the loop of xax/arch/llm.py:1572-1613 for B prompts of equal
-    length.  Returns (tokens [B, max_len] int32, final lengths [B])."""
+                       use_graph: bool = True, prefill_chunk: int | None = None, tp=None, sampler=None):
+    """Batched generation: the loop of xax/arch/llm.py:1572-1613 for B prompts of equal length, greedy
+    unless ``sampler`` (a TokenSampler) is given.  Returns (tokens [B, max_len] int32, final lengths [B])."""
     tokens_bt = tokens_bt.to(torch.int32)
     B, T0 = tokens_bt.shape
     max_len = T0 + max_new_tokens
@@ -410,7 +492,8 @@ def llm_generate_batch(model: LLM, tokens_bt: torch.Tensor, max_new_tokens: int,
     out[:, :T0] = tokens_bt
     if max_new_tokens <= 0:
         return out, torch.full((B,), T0, dtype=torch.int64)
-    st = DecodeState(model, B, max_len, tp=tp)
+    st = DecodeState(model, B, max_len, tp=tp, sampler=sampler)
+    use_graph = use_graph and sampler is None
     first = st.prefill(tokens_bt, prefill_chunk)
     out[:, T0] = first
     if max_new_tokens > 1:

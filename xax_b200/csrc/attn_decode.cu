@@ -115,13 +115,36 @@ __device__ __forceinline__ void merge_cast_row(const float* __restrict__ ws_o, c
                                                const TpRowMax& tp, int* d_status, float* s_max, float* s_inv_den,
                                                uint32_t* s_tp) {
   constexpr int kPer = 512 / NT;
+  // (max, sum) of every partial result of the sequence, fetched by all threads at once: the
+  // arithmetic below then runs from shared memory in the same order as before, without a chain of
+  // dependent trips to L2 per head.  Up to kMlCache partial results per head are cached.
+  constexpr int kMlCache = 16;
+  __shared__ float s_ml[64 * kMlCache * 2];
+  const bool cached = n <= kMlCache;
+  if (cached) {
+    for (int i = threadIdx.x; i < Hq * n; i += NT) {
+      const int h = i / n, c = i - h * n;
+      const long long base = ((long long)b * Hq + h) * max_chunks + c;
+      const float2 v = kFresh ? __ldcg(reinterpret_cast<const float2*>(ws_ml + base * 2))
+                              : *reinterpret_cast<const float2*>(ws_ml + base * 2);
+      s_ml[(h * kMlCache + c) * 2] = v.x;
+      s_ml[(h * kMlCache + c) * 2 + 1] = v.y;
+    }
+    __syncthreads();
+  }
   for (int h = threadIdx.x; h < Hq; h += NT) {
     const long long base = ((long long)b * Hq + h) * max_chunks;
     float m = -INFINITY;
-    for (int c = 0; c < n; ++c) m = fmaxf(m, ws_ld<kFresh>(ws_ml + (base + c) * 2));
     float den = 0.0f;
-    for (int c = 0; c < n; ++c)
-      den = fmaf(__expf(ws_ld<kFresh>(ws_ml + (base + c) * 2) - m), ws_ld<kFresh>(ws_ml + (base + c) * 2 + 1), den);
+    if (cached) {
+      const float* ml = s_ml + h * kMlCache * 2;
+      for (int c = 0; c < n; ++c) m = fmaxf(m, ml[c * 2]);
+      for (int c = 0; c < n; ++c) den = fmaf(__expf(ml[c * 2] - m), ml[c * 2 + 1], den);
+    } else {
+      for (int c = 0; c < n; ++c) m = fmaxf(m, ws_ld<kFresh>(ws_ml + (base + c) * 2));
+      for (int c = 0; c < n; ++c)
+        den = fmaf(__expf(ws_ld<kFresh>(ws_ml + (base + c) * 2) - m), ws_ld<kFresh>(ws_ml + (base + c) * 2 + 1), den);
+    }
     s_max[h] = m;
     s_inv_den[h] = 1.0f / den;
   }
@@ -137,8 +160,10 @@ __device__ __forceinline__ void merge_cast_row(const float* __restrict__ ws_o, c
       const int h = it / dv, d0 = (it % dv) * 8;
       const long long base = ((long long)b * Hq + h) * max_chunks;
       float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+#pragma unroll 4
       for (int c = 0; c < n; ++c) {
-        const float w = __expf(ws_ld<kFresh>(ws_ml + (base + c) * 2) - s_max[h]);
+        const float mc = cached ? s_ml[(h * kMlCache + c) * 2] : ws_ld<kFresh>(ws_ml + (base + c) * 2);
+        const float w = __expf(mc - s_max[h]);
         const float4 lo = ws_ld4<kFresh>(ws_o + (base + c) * D + d0);
         const float4 hi = ws_ld4<kFresh>(ws_o + (base + c) * D + d0 + 4);
         acc[0] = fmaf(w, lo.x, acc[0]), acc[1] = fmaf(w, lo.y, acc[1]), acc[2] = fmaf(w, lo.z, acc[2]);
@@ -175,11 +200,59 @@ __device__ __forceinline__ float warp_max_f32(float v) {
   return r;
 }
 
+// Rotate-on-load: thread `tid` rotates row `tid` of the K tile in shared memory in place, once the tile
+// has landed (barrier `bar`, parity `parity`).  Pair (i, i + D/2) lives in 16-byte piece i/8 of box
+// (i / 64) and piece (i + D/2)/8 of the other half.  The row's cos / sin values do not depend on the
+// tile, so they are requested before the wait for it; the rotation itself is packed bf16 arithmetic --
+// every product and every sum rounds to bf16 on its own, which is exactly the reference's bf16 op
+// sequence (xax/arch/attention.py:510-515) -- six instructions per two pairs.  Returns false if the wait
+// gave up.  The caller fences (generic -> async proxy) and synchronises before the tile is multiplied.
+template <int D>
+__device__ __forceinline__ bool rotate_k_tile(uint8_t* sK, const DecodeParams& p, int tok0, int valid, uint64_t* bar,
+                                              uint32_t parity, volatile int* abort_flag) {
+  using SM = DecodeSmem<D>;
+  constexpr int half = D / 2, kPieces = half / 8;
+  const int tid = threadIdx.x;
+  const long long pos = tok0 + tid;
+  const bool row_ok = tid < valid && pos < p.table_len;
+  uint4 cv[kPieces], sv[kPieces];
+  if (row_ok) {
+    const uint4* cr = reinterpret_cast<const uint4*>(p.cos_t + pos * half);
+    const uint4* sr = reinterpret_cast<const uint4*>(p.sin_t + pos * half);
+#pragma unroll
+    for (int c = 0; c < kPieces; ++c) cv[c] = __ldg(cr + c), sv[c] = __ldg(sr + c);
+  }
+  const bool ok = mbar_wait(bar, parity, abort_flag, p.d_status, XAXB_DEVICE_TIMEOUT * 1000 + kSiteDecK);
+  if (ok && row_ok) {
+#pragma unroll
+    for (int c = 0; c < kPieces; ++c) {
+      const int c2 = c + kPieces;
+      uint4* p1 = reinterpret_cast<uint4*>(sK + (c / 8) * SM::kHalfBytes + sw128_offset(tid, c % 8));
+      uint4* p2 = reinterpret_cast<uint4*>(sK + (c2 / 8) * SM::kHalfBytes + sw128_offset(tid, c2 % 8));
+      uint4 a = *p1, bb = *p2;
+      __nv_bfloat162* aw = reinterpret_cast<__nv_bfloat162*>(&a);
+      __nv_bfloat162* bw = reinterpret_cast<__nv_bfloat162*>(&bb);
+      const __nv_bfloat162* cw = reinterpret_cast<const __nv_bfloat162*>(&cv[c]);
+      const __nv_bfloat162* sw = reinterpret_cast<const __nv_bfloat162*>(&sv[c]);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const __nv_bfloat162 x1 = aw[j], x2 = bw[j];
+        // the _rn forms are never contracted into a fused multiply-add
+        aw[j] = __hsub2_rn(__hmul2_rn(x1, cw[j]), __hmul2_rn(x2, sw[j]));
+        bw[j] = __hadd2_rn(__hmul2_rn(x2, cw[j]), __hmul2_rn(x1, sw[j]));
+      }
+      *p1 = a;
+      *p2 = bb;
+    }
+  }
+  return ok;
+}
+
 // GT = the group size rounded up to a power of two: only GT of the 16 UMMA columns are read back,
 // reduced and written as P^T.  (Column n of either product depends on row n of its B operand
 // only, so whatever the unused rows of Q and P^T hold never reaches a column that is read.)
-template <int D, int GT>
-__global__ void __launch_bounds__(128) attn_decode_kernel(const __grid_constant__ CUtensorMap tmap_k,
+template <int D, int GT, bool kRotate>
+__global__ void __launch_bounds__(128, 3) attn_decode_kernel(const __grid_constant__ CUtensorMap tmap_k,
                                                           const __grid_constant__ CUtensorMap tmap_v,
                                                           const DecodeParams p) {
   pdl_wait();  // nothing below may run ahead of the previous kernel in the stream
@@ -274,51 +347,13 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(const __grid_constant_
     const int valid = min(kChunk, L - tok0);
     const int next = chunk + stride;
 
-    if (!p.k_is_rotated) {
-      // Rotate K row `tid` in place: pair (i, i + D/2) lives in chunk i/8 of box (i / 64) and
-      // chunk (i + D/2)/8 of the other half.
-      ok = mbar_wait(bar_k, ph, abort_flag, p.d_status, XAXB_DEVICE_TIMEOUT * 1000 + kSiteDecK);
-      const long long pos = tok0 + tid;
-      if (ok && tid < valid && pos < p.table_len) {
-        constexpr int half = D / 2;
-        const __nv_bfloat16* cr = p.cos_t + pos * half;
-        const __nv_bfloat16* sr = p.sin_t + pos * half;
-        for (int c = 0; c < half / 8; ++c) {
-          const int c2 = c + half / 8;
-          uint4* p1 = reinterpret_cast<uint4*>(sK + (c / 8) * SM::kHalfBytes + sw128_offset(tid, c % 8));
-          uint4* p2 = reinterpret_cast<uint4*>(sK + (c2 / 8) * SM::kHalfBytes + sw128_offset(tid, c2 % 8));
-          uint4 a = *p1, bb = *p2;
-          const uint4 cv = __ldg(reinterpret_cast<const uint4*>(cr) + c);
-          const uint4 sv = __ldg(reinterpret_cast<const uint4*>(sr) + c);
-          uint32_t* aw = reinterpret_cast<uint32_t*>(&a);
-          uint32_t* bw = reinterpret_cast<uint32_t*>(&bb);
-          const uint32_t* cw = reinterpret_cast<const uint32_t*>(&cv);
-          const uint32_t* sw = reinterpret_cast<const uint32_t*>(&sv);
-#pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            uint32_t o1 = 0, o2 = 0;
-#pragma unroll
-            for (int hsel = 0; hsel < 2; ++hsel) {
-              const int sh = hsel * 16;
-              const float x1 = bf16_bits_to_float((aw[j] >> sh) & 0xFFFFu);
-              const float x2 = bf16_bits_to_float((bw[j] >> sh) & 0xFFFFu);
-              const float cc = bf16_bits_to_float((cw[j] >> sh) & 0xFFFFu);
-              const float ss = bf16_bits_to_float((sw[j] >> sh) & 0xFFFFu);
-              const float r1 = bf16_round(x1 * cc) - bf16_round(x2 * ss);
-              const float r2 = bf16_round(x2 * cc) + bf16_round(x1 * ss);
-              o1 |= (uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(r1)) << sh;
-              o2 |= (uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(r2)) << sh;
-            }
-            aw[j] = o1;
-            bw[j] = o2;
-          }
-          *p1 = a;
-          *p2 = bb;
-        }
+    if constexpr (kRotate) {
+      if (chunk == c_lo + first) {  // later tiles are rotated at the end of the iteration before theirs
+        ok = rotate_k_tile<D>(sK, p, tok0, valid, bar_k, ph, abort_flag);
+        fence_proxy_async_smem();
+        ok = __syncthreads_and(ok);
+        if (!ok) break;
       }
-      fence_proxy_async_smem();
-      ok = __syncthreads_and(ok);
-      if (!ok) break;
     }
 
     // ---- S^T = K Q^T ---------------------------------------------------------------------
@@ -406,7 +441,18 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(const __grid_constant_
       for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
       if (lane == 0) red_sum[warp * kNPad + g] = s;
     }
-    __syncthreads();
+    if constexpr (kRotate) {
+      // The next K tile was requested as soon as S^T had consumed this one; it is rotated here, under
+      // the second MMA and the wait for it, so the next iteration finds it ready.
+      if (next < n_chunks) {
+        ok = rotate_k_tile<D>(sK, p, next * kChunk, min(kChunk, L - next * kChunk), bar_k, ph ^ 1, abort_flag);
+        fence_proxy_async_smem();
+      }
+      ok = __syncthreads_and(ok);
+      if (!ok) break;
+    } else {
+      __syncthreads();
+    }
     float wa[GT], wb[GT];  // weights of the running state and of this chunk in the merged state
 #pragma unroll
     for (int g = 0; g < GT; ++g) {
@@ -581,9 +627,15 @@ static int decode_launch(xaxb_ctx* ctx_, void* stream, const void* q_rot_bf16, c
     const int gt = G <= 1 ? 1 : G <= 2 ? 2 : G <= 4 ? 4 : G <= 8 ? 8 : 16;
 #define XAXB_DECODE_CASE(DD, GG)                                                                                 \
   if (D == DD && gt == GG) {                                                                                     \
-    rc = ensure_dynamic_smem<attn_decode_kernel<DD, GG>>(ctx, DecodeSmem<DD>::kBytes, "attn_decode_kernel");     \
-    if (rc) return rc;                                                                                           \
-    launch_kernel(attn_decode_kernel<DD, GG>, grid, dim3(128), DecodeSmem<DD>::kBytes, s, 1, tk, tv, p);         \
+    if (k_is_rotated) {                                                                                          \
+      rc = ensure_dynamic_smem<attn_decode_kernel<DD, GG, false>>(ctx, DecodeSmem<DD>::kBytes, "attn_decode");   \
+      if (rc) return rc;                                                                                         \
+      launch_kernel(attn_decode_kernel<DD, GG, false>, grid, dim3(128), DecodeSmem<DD>::kBytes, s, 1, tk, tv, p);\
+    } else {                                                                                                     \
+      rc = ensure_dynamic_smem<attn_decode_kernel<DD, GG, true>>(ctx, DecodeSmem<DD>::kBytes, "attn_decode");    \
+      if (rc) return rc;                                                                                         \
+      launch_kernel(attn_decode_kernel<DD, GG, true>, grid, dim3(128), DecodeSmem<DD>::kBytes, s, 1, tk, tv, p); \
+    }                                                                                                            \
   }
     XAXB_DECODE_CASE(128, 1) XAXB_DECODE_CASE(128, 2) XAXB_DECODE_CASE(128, 4) XAXB_DECODE_CASE(128, 8)
     XAXB_DECODE_CASE(128, 16) XAXB_DECODE_CASE(64, 1) XAXB_DECODE_CASE(64, 2) XAXB_DECODE_CASE(64, 4)

@@ -37,8 +37,23 @@ struct GemmParams {
   __nv_bfloat16* out;
   long long ldo;
   int* d_status;
-  int prefetch_b;  // the launch may overlap the previous kernel: ask L2 for B ahead of the wait
+  // The launch may overlap the previous kernel (programmatic dependent launch).  Operand B -- the
+  // weights of a linear layer -- is never written by a kernel of the same stream section, so the
+  // producer may fetch it before it waits for the previous kernel:
+  //   0  nothing ahead of the wait;
+  //   1  ask L2 for the first `prefetch_l2` K blocks of B;
+  //   2  load B of the first K blocks into the shared-memory ring (all stages), and ask L2 for
+  //      `prefetch_l2` blocks beyond the ring; A follows after the wait.
+  int prefetch_b;
+  int prefetch_l2;
   int band;        // tile rows per band of the tile order (see tile_coords)
+  // Tensor-parallel push (split-K kernel only): with push_world > 0 the epilogue writes every 16-byte
+  // piece of the output to push_out[r] for each rank r < push_world (this rank's slot of rank r's
+  // staging buffer; plain peer stores over NVLink) instead of `out`, and when a CTA's pieces are all
+  // written it adds their number to push_flag[r] on every rank with a system-scope release.
+  __nv_bfloat16* push_out[8];
+  unsigned int* push_flag[8];
+  int push_world;
 };
 
 // Tile order: bands of kBand tile rows, column by column inside a band (row index fastest).  The
@@ -52,7 +67,8 @@ __device__ __forceinline__ void tile_coords(int kBand, int tile, int tiles_m, in
   tm = band * kBand + (r - tn * rows);
 }
 
-// K blocks of operand B that a producer asks L2 for ahead of the wait on the previous kernel.
+// Default number of K blocks of operand B that a producer asks L2 for ahead of the wait on the
+// previous kernel (GemmParams::prefetch_l2).
 constexpr int kMaxPrefetchBlocks = 4;
 
 template <int BN>
@@ -167,15 +183,24 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      // While the previous kernel is still running, pull this CTA's first B tile (the weights:
-      // what a decode-sized GEMM streams from HBM) towards L2.  A prefetch carries no data into
-      // the SM, and L2 is the point of coherence, so this is safe whatever wrote B and whenever.
+      // While the previous kernel is still running, bring in operand B of this CTA's first tile
+      // (the weights: what a decode-sized GEMM streams from HBM).  L2 is the point of coherence and
+      // nothing in flight writes B, so this is safe whatever precedes the kernel.
+      int pre = 0;  // K blocks of the first tile whose B half is already on its way into the ring
       if (p.prefetch_b && (int)blockIdx.x < num_tiles) {
         int tm, tn;
         tile_coords(p.band, (int)blockIdx.x, p.tiles_m, p.tiles_n, tm, tn);
         int kk = (int)(((long long)blockIdx.x * 5) % p.num_k_blocks);
-        const int n_pre = p.num_k_blocks < kMaxPrefetchBlocks ? p.num_k_blocks : kMaxPrefetchBlocks;
-        for (int i = 0; i < n_pre; ++i) {
+        if (p.prefetch_b == 2) {
+          pre = p.num_k_blocks < kStages ? p.num_k_blocks : kStages;
+          for (int i = 0; i < pre; ++i) {
+            mbar_arrive_expect_tx(full + i, Cfg::kStageBytes);
+            tma_load_2d(smem_b + i * BN * kBKBytes, &tmap_b, full + i, kk * kBKElems, tn * BN);
+            if (++kk == p.num_k_blocks) kk = 0;
+          }
+        }
+        const int n_l2 = min(p.num_k_blocks - pre, p.prefetch_l2);
+        for (int i = 0; i < n_l2; ++i) {
           tma_prefetch_l2_2d(&tmap_b, kk * kBKElems, tn * BN);
           if (++kk == p.num_k_blocks) kk = 0;
         }
@@ -189,14 +214,19 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         // N tiles read the same rows of A) then ask L2 for different lines at any moment.
         int kk = (int)(((long long)tile * 5) % p.num_k_blocks);
         for (int kb = 0; kb < p.num_k_blocks; ++kb) {
-          ok = mbar_wait(empty + stage, phase ^ 1, abort_flag, p.d_status, XAXB_DEVICE_TIMEOUT * 1000 + kSiteProducer);
-          if (!ok) break;
-          mbar_arrive_expect_tx(full + stage, Cfg::kStageBytes);
-          tma_load_2d(smem_a + stage * kBM * kBKBytes, &tmap_a, full + stage, kk * kBKElems, m0);
-          tma_load_2d(smem_b + stage * BN * kBKBytes, &tmap_b, full + stage, kk * kBKElems, n0);
+          if (kb < pre) {  // first tile only: the stage is armed and its B half requested already
+            tma_load_2d(smem_a + stage * kBM * kBKBytes, &tmap_a, full + stage, kk * kBKElems, m0);
+          } else {
+            ok = mbar_wait(empty + stage, phase ^ 1, abort_flag, p.d_status, XAXB_DEVICE_TIMEOUT * 1000 + kSiteProducer);
+            if (!ok) break;
+            mbar_arrive_expect_tx(full + stage, Cfg::kStageBytes);
+            tma_load_2d(smem_a + stage * kBM * kBKBytes, &tmap_a, full + stage, kk * kBKElems, m0);
+            tma_load_2d(smem_b + stage * BN * kBKBytes, &tmap_b, full + stage, kk * kBKElems, n0);
+          }
           if (++kk == p.num_k_blocks) kk = 0;
           if (++stage == kStages) stage = 0, phase ^= 1;
         }
+        pre = 0;
       }
     }
   } else if (warp == 1) {
@@ -507,7 +537,13 @@ __device__ __forceinline__ void splitk_finish_item(const GemmParams& p, float (&
     const uint32_t hi16 = __bfloat16_as_ushort(__float2bfloat16_rn(f[2 * j + 1]));
     ow[j] = lo16 | (hi16 << 16);
   }
-  *reinterpret_cast<uint4*>(p.out + (long long)m * p.ldo + n) = o;
+  if (p.push_world > 0) {
+#pragma unroll
+    for (int r = 0; r < 8; ++r)
+      if (r < p.push_world) *reinterpret_cast<uint4*>(p.push_out[r] + (long long)m * p.ldo + n) = o;
+  } else {
+    *reinterpret_cast<uint4*>(p.out + (long long)m * p.ldo + n) = o;
+  }
 }
 
 template <int BN, bool IS_FP8>
@@ -569,21 +605,34 @@ gemm_splitk_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
       int stage = 0;
       uint32_t phase = 0;
       int kk = nkb > 0 ? kb0 + (tile_n * 3) % nkb : kb0;  // staggered start, see gemm_tc_kernel
-      if (p.prefetch_b) {  // B towards L2 while the previous kernel is still running (see gemm_tc_kernel)
+      int pre = 0;
+      if (p.prefetch_b) {  // B ahead of the wait on the previous kernel (see GemmParams::prefetch_b)
         int k2 = kk;
-        const int n_pre = nkb < kMaxPrefetchBlocks ? nkb : kMaxPrefetchBlocks;
-        for (int i = 0; i < n_pre; ++i) {
+        if (p.prefetch_b == 2) {
+          pre = nkb < kStages ? nkb : kStages;
+          for (int i = 0; i < pre; ++i) {
+            mbar_arrive_expect_tx(full + i, Cfg::kStageBytes);
+            tma_load_2d(smem_b + i * BN * kBKBytes, &tmap_b, full + i, k2 * kBKElems, n0);
+            if (++k2 == kb1) k2 = kb0;
+          }
+        }
+        const int n_l2 = min(nkb - pre, p.prefetch_l2);
+        for (int i = 0; i < n_l2; ++i) {
           tma_prefetch_l2_2d(&tmap_b, k2 * kBKElems, n0);
           if (++k2 == kb1) k2 = kb0;
         }
       }
       pdl_wait();
       for (int i = 0; i < nkb; ++i) {
-        if (!mbar_wait(empty + stage, phase ^ 1, abort_flag, p.d_status, XAXB_DEVICE_TIMEOUT * 1000 + kSiteSkProducer))
-          break;
-        mbar_arrive_expect_tx(full + stage, Cfg::kStageBytes);
-        tma_load_2d(smem_a + stage * kBM * kBKBytes, &tmap_a, full + stage, kk * kBKElems, 0);
-        tma_load_2d(smem_b + stage * BN * kBKBytes, &tmap_b, full + stage, kk * kBKElems, n0);
+        if (i < pre) {  // the stage is armed and its B half requested already
+          tma_load_2d(smem_a + stage * kBM * kBKBytes, &tmap_a, full + stage, kk * kBKElems, 0);
+        } else {
+          if (!mbar_wait(empty + stage, phase ^ 1, abort_flag, p.d_status, XAXB_DEVICE_TIMEOUT * 1000 + kSiteSkProducer))
+            break;
+          mbar_arrive_expect_tx(full + stage, Cfg::kStageBytes);
+          tma_load_2d(smem_a + stage * kBM * kBKBytes, &tmap_a, full + stage, kk * kBKElems, 0);
+          tma_load_2d(smem_b + stage * BN * kBKBytes, &tmap_b, full + stage, kk * kBKElems, n0);
+        }
         if (++kk == kb1) kk = kb0;
         if (++stage == kStages) stage = 0, phase ^= 1;
       }
@@ -751,6 +800,22 @@ gemm_splitk_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
       }
     }
   }
+  if (p.push_world > 0 && warp >= 2) {
+    // Every epilogue thread's peer stores precede the barrier; one thread then makes them visible
+    // system-wide and tells every rank how many 16-byte pieces of its staging slot are complete.
+    epilogue_sync();
+    if (threadIdx.x == 64 && ok) {
+      const int row0 = r * rows_per;
+      const int rows_ok = max(0, min(p.M, row0 + rows_per) - row0);
+      const int cols_ok = max(0, min(BN, p.N - n0));
+      const unsigned int pieces = (unsigned int)(rows_ok * (cols_ok / 8));
+      __threadfence_system();
+#pragma unroll
+      for (int dst = 0; dst < 8; ++dst)
+        if (dst < p.push_world)
+          asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(p.push_flag[dst]), "r"(pieces) : "memory");
+    }
+  }
   __syncwarp();
   cluster_wait();  // the peers have finished reading this CTA's shared memory
   __syncthreads();
@@ -832,8 +897,12 @@ struct GemmPlan {
 };
 
 static int g_force_bn = 0, g_force_split = 0;  // test hook (xaxb_gemm_force_plan)
+static int g_prefetch_mode = 1, g_prefetch_l2 = kMaxPrefetchBlocks;  // xaxb_gemm_set_prefetch
 
-static GemmPlan pick_plan(long long M, long long N, long long K, int elem_bytes, int num_sms) {
+// `one_wave_kernel`: every candidate runs on the split-K kernel (one tile per CTA, not persistent), as
+// the pushing epilogue requires; a "split" of 1 is then a plain tile per CTA, in as many waves as needed.
+static GemmPlan pick_plan(long long M, long long N, long long K, int elem_bytes, int num_sms,
+                          bool one_wave_kernel = false) {
   // Fitted to measurements on B200 (decode shapes, weights streamed from HBM): a CTA whose
   // shared memory is all load stages ingests ~60 GB/s (in-flight bytes / loaded latency); a
   // launch has ~2.4 us of fixed time; every further wave of tiles on the persistent kernel
@@ -861,6 +930,7 @@ static GemmPlan pick_plan(long long M, long long N, long long K, int elem_bytes,
       if (t_hbm > t) t = t_hbm;
       t += 2.4e-6 + (waves - 1) * 2e-6;
       if (s > 1) t += (s == 2 ? 1.8e-6 : 3.9e-6) + 0.02e-6 * bn;
+      if (one_wave_kernel && s == 1) t += 0.8e-6;  // the tile still goes through shared memory once
       if (t < best_t) best_t = t, best = {bn, s};
     }
   }
@@ -869,11 +939,34 @@ static GemmPlan pick_plan(long long M, long long N, long long K, int elem_bytes,
   return best;
 }
 
+// Where a tensor-parallel GEMM pushes its output (see GemmParams::push_out).
+struct PushTarget {
+  void* const* peer_bases;
+  int rank, world;
+  int64_t slot_offset_bytes;  // of this rank's slot inside every rank's buffer
+  int64_t flag_offset_bytes;  // of the arrival counter inside every rank's buffer
+};
+
 template <bool IS_FP8>
 static int gemm_entry(xaxb_ctx* ctx_, void* stream, const void* a, int64_t lda, const void* b, int64_t ldb, int64_t M,
                       int64_t N, int64_t K, const float* row_mul, int row_mul_stride, const float* col_mul,
                       int col_mul_stride, const void* bias, const void* residual, int64_t ldr, void* out,
-                      int64_t ldo) {
+                      int64_t ldo, const PushTarget* push = nullptr) {
+  if (push) {
+    if (!push->peer_bases || push->world < 1 || push->world > 8 || push->rank < 0 || push->rank >= push->world ||
+        (push->slot_offset_bytes & 15) || (push->flag_offset_bytes & 3) || push->slot_offset_bytes < 0 ||
+        push->flag_offset_bytes < 0 || M > kBM) {
+      set_last_error("gemm push: needs 1 <= world <= 8, 0 <= rank < world, aligned offsets and M <= %d", kBM);
+      return XAXB_BAD_ARGUMENT;
+    }
+    for (int r = 0; r < push->world; ++r)
+      if (!push->peer_bases[r] || (reinterpret_cast<uintptr_t>(push->peer_bases[r]) & 15)) {
+        set_last_error("gemm push: mapping of rank %d is null or not 16-byte aligned", r);
+        return XAXB_BAD_ARGUMENT;
+      }
+    out = static_cast<uint8_t*>(push->peer_bases[push->rank]) + push->slot_offset_bytes;  // for the argument checks
+    ldo = N;
+  }
   if (!ctx_ || !a || !b || !out || M <= 0 || N <= 0 || K <= 0) {
     set_last_error("gemm: null pointer or non-positive shape");
     return XAXB_BAD_ARGUMENT;
@@ -897,19 +990,31 @@ static int gemm_entry(xaxb_ctx* ctx_, void* stream, const void* a, int64_t lda, 
   p.out = static_cast<__nv_bfloat16*>(out);
   p.ldo = ldo;
   p.d_status = ctx->d_status;
-  p.prefetch_b = pdl_enabled() ? 1 : 0;
+  p.prefetch_b = pdl_enabled() ? g_prefetch_mode : 0;
+  p.prefetch_l2 = g_prefetch_l2;
+  p.push_world = 0;
+  for (int r = 0; r < 8; ++r) p.push_out[r] = nullptr, p.push_flag[r] = nullptr;
+  if (push) {
+    p.push_world = push->world;
+    for (int r = 0; r < push->world; ++r) {
+      uint8_t* base = static_cast<uint8_t*>(push->peer_bases[r]);
+      p.push_out[r] = reinterpret_cast<__nv_bfloat16*>(base + push->slot_offset_bytes);
+      p.push_flag[r] = reinterpret_cast<unsigned int*>(base + push->flag_offset_bytes);
+    }
+  }
   p.band = 32;  // measured best for 128-row tiles at 8192^3 (2, 4, 8, 16, 32 tried); 16 for the pair kernel
   if (const char* e = getenv("XAXB_GEMM_BAND")) p.band = atoi(e) > 0 ? atoi(e) : 32;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  const GemmPlan plan = pick_plan(M, N, K, eb, ctx->num_sms);
+  GemmPlan plan = pick_plan(M, N, K, eb, ctx->num_sms, push != nullptr);
   // Large problems go to the CTA-pair kernel: 256 x 256 tiles need a third less operand traffic
   // per SM, which is what bounds the single-CTA kernel.  It wants at least two waves of tiles.
   const bool pair_ok = M > kBM && N >= 256;
   const long long pair_tiles = ((long long)(M + 255) / 256) * ((N + 255) / 256);
-  if ((g_force_bn == 512 && pair_ok) ||
-      (g_force_bn == 0 && pair_ok && plan.bn == 256 && plan.split == 1 && pair_tiles >= ctx->num_sms))
+  if (!push && ((g_force_bn == 512 && pair_ok) ||
+                (g_force_bn == 0 && pair_ok && plan.bn == 256 && plan.split == 1 && pair_tiles >= ctx->num_sms)))
     return launch_gemm_2cta<IS_FP8>(ctx, s, a, lda * eb, b, ldb * eb, p);
-  if (plan.split > 1) {
+  if (plan.split > 1 || push) {  // the pushing epilogue lives in the split-K kernel (a "split" of 1 included)
+    if (plan.bn == 512) plan.bn = 256;
     if (M > kBM || plan.split > 8) {
       set_last_error("gemm: split-K plan (bn=%d, split=%d) is invalid for M=%lld", plan.bn, plan.split, (long long)M);
       return XAXB_BAD_ARGUMENT;
@@ -944,12 +1049,29 @@ int xaxb_gemm_force_plan(int bn, int split) {
   return XAXB_OK;
 }
 
+int xaxb_gemm_set_prefetch(int mode, int l2_blocks) {
+  if (mode < 0 || mode > 2 || l2_blocks < 0 || l2_blocks > 4096) return XAXB_BAD_ARGUMENT;
+  g_prefetch_mode = mode;
+  g_prefetch_l2 = l2_blocks;
+  return XAXB_OK;
+}
+
 int xaxb_gemm_fp8(xaxb_ctx* ctx, void* stream, const void* a_e4m3, int64_t lda, const void* b_e4m3, int64_t ldb,
                   int64_t M, int64_t N, int64_t K, const float* row_mul, int row_mul_stride, const float* col_mul,
                   int col_mul_stride, const void* bias_bf16, const void* residual_bf16, int64_t ldr, void* out_bf16,
                   int64_t ldo) {
   return gemm_entry<true>(ctx, stream, a_e4m3, lda, b_e4m3, ldb, M, N, K, row_mul, row_mul_stride, col_mul,
                           col_mul_stride, bias_bf16, residual_bf16, ldr, out_bf16, ldo);
+}
+
+int xaxb_gemm_fp8_push(xaxb_ctx* ctx, void* stream, const void* a_e4m3, int64_t lda, const void* b_e4m3, int64_t ldb,
+                       int64_t M, int64_t N, int64_t K, const float* row_mul, int row_mul_stride, const float* col_mul,
+                       int col_mul_stride, const void* bias_bf16, const void* residual_bf16, int64_t ldr,
+                       void* const* peer_bases, int rank, int world, int64_t slot_offset_bytes,
+                       int64_t flag_offset_bytes) {
+  const PushTarget push = {peer_bases, rank, world, slot_offset_bytes, flag_offset_bytes};
+  return gemm_entry<true>(ctx, stream, a_e4m3, lda, b_e4m3, ldb, M, N, K, row_mul, row_mul_stride, col_mul,
+                          col_mul_stride, bias_bf16, residual_bf16, ldr, nullptr, 0, &push);
 }
 
 int xaxb_gemm_bf16(xaxb_ctx* ctx, void* stream, const void* a_bf16, int64_t lda, const void* b_bf16, int64_t ldb,

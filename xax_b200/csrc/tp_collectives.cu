@@ -149,6 +149,101 @@ __global__ void __launch_bounds__(256) tp_allreduce_sum_norm_kernel(
   }
 }
 
+// ---- push variant of the sum -----------------------------------------------------------------
+// The row-parallel GEMM itself writes its bf16 partial output into slot `rank` of EVERY rank's
+// staging buffer ([world][rows][cols]) from its epilogue and adds the number of 16-byte pieces it
+// completed to an arrival counter on every rank (xaxb_gemm_fp8_push).  The consumer below waits
+// until the local counter has reached the running total expected so far -- world x rows x cols / 8
+// pieces per exchange -- and then reads LOCAL memory only: no flag raising, no trip over NVLink on
+// its critical path.  Staging buffer and counter come in pairs used in alternation, so that pieces of
+// exchange k+1 can never be taken for pieces of exchange k.  The running totals live in local
+// memory (one per token row and counter), so a captured step can be replayed.
+constexpr int kSiteTpPush = 46;
+
+template <int VPT>
+__global__ void __launch_bounds__(256) tp_push_sum_norm_kernel(
+    const uint8_t* __restrict__ staging, int64_t slot_stride, const unsigned int* counter, unsigned int* totals,
+    unsigned int pieces_per_exchange, int world, int vec, uint4* __restrict__ x_out, const uint4* __restrict__ w,
+    float eps, uint2* __restrict__ q, float* __restrict__ scale, float* __restrict__ inv_scale, int* d_status) {
+  pdl_trigger();
+  pdl_wait();
+  const int64_t row = blockIdx.x;
+  if (threadIdx.x == 0) {
+    const unsigned int want = totals[row] + pieces_per_exchange;
+    totals[row] = want;
+    if ((int32_t)(ld_acquire_sys(counter) - want) < 0) {
+      const unsigned long long t0 = globaltimer_ns();
+      const unsigned long long limit = peer_wait_limit_ns(d_status);
+      while ((int32_t)(ld_acquire_sys(counter) - want) < 0) {
+        if (*reinterpret_cast<volatile int*>(d_status) != 0) break;
+        if (globaltimer_ns() - t0 > limit) {
+          atomicCAS(d_status, 0, XAXB_DEVICE_TIMEOUT * 1000 + kSiteTpPush);
+          break;
+        }
+      }
+    }
+  }
+  __syncthreads();
+  const int64_t row_off = row * vec * 16;
+  float v[VPT][8];
+  float acc = 0.0f;
+#pragma unroll
+  for (int k = 0; k < VPT; ++k) {
+    const int i = threadIdx.x + k * 256;
+    if (i < vec) {
+      uint4 part[kTpMaxWorld];
+#pragma unroll
+      for (int r = 0; r < kTpMaxWorld; ++r)
+        if (r < world) part[r] = ld_relaxed_sys_v4(staging + r * slot_stride + row_off + (int64_t)i * 16);
+      float s[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+#pragma unroll
+      for (int r = 0; r < kTpMaxWorld; ++r) {
+        if (r < world) {
+          float f[8];
+          unpack8(part[r], f);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) s[j] += f[j];
+        }
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        v[k][j] = bf16_round(s[j]);
+        acc += bf16_round(v[k][j] * v[k][j]);
+      }
+      x_out[row * vec + i] = pack8(v[k]);
+    }
+  }
+  if (!w) return;  // plain sum: no norm, no cast (uniform over the CTA)
+  const float total = block_sum_f32(acc);
+  const float mean = bf16_round(total / (float)(vec * 8));
+  const float n = bf16_round(sqrtf(bf16_round(mean + bf16_round(eps))));
+  uint32_t m = 0;
+#pragma unroll
+  for (int k = 0; k < VPT; ++k) {
+    const int i = threadIdx.x + k * 256;
+    if (i < vec) {
+      float wv[8];
+      unpack8(__ldg(w + i), wv);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        v[k][j] = bf16_round(bf16_round(v[k][j] / n) * wv[j]);
+        m = max(m, mag_bits16(v[k][j]));
+      }
+    }
+  }
+  const uint32_t row_bits = block_max_u32(m);
+  const float s = current_scale_from_amax(bf16_bits_to_float(row_bits));
+#pragma unroll
+  for (int k = 0; k < VPT; ++k) {
+    const int i = threadIdx.x + k * 256;
+    if (i < vec) q[row * vec + i] = quantize8f(v[k], s);
+  }
+  if (threadIdx.x == 0) {
+    scale[row] = s;
+    inv_scale[row] = 1.0f / s;
+  }
+}
+
 // One CTA; n <= 1024 values.  inbox_off: float32 [2][kTpMaxWorld][kTpMaxSlots] in the symmetric
 // buffer (two copies, used in alternation by epoch parity).
 __global__ void __launch_bounds__(1024) tp_allreduce_max_kernel(const PeerTable peers, int64_t inbox_off,
@@ -319,6 +414,51 @@ int xaxb_tp_allreduce_sum_rmsnorm(xaxb_ctx* ctx_, void* stream, void* const* pee
                                                                  vec, xo, wp, eps, qp, row_scale, row_inv_scale,
                                                                  ctx->d_status);
   return check_launch("tp_allreduce_sum_norm_kernel");
+}
+
+int64_t xaxb_tp_push_totals_bytes(void) { return (int64_t)kTpMaxSlots * 4; }
+
+int xaxb_tp_push_sum_rmsnorm(xaxb_ctx* ctx_, void* stream, const void* staging, int64_t slot_stride_bytes,
+                             const void* counter, void* totals, int world, int64_t rows, int64_t cols, void* x_bf16,
+                             const void* weight_bf16, float eps, void* q_e4m3, float* row_scale,
+                             float* row_inv_scale) {
+  if (!ctx_ || !staging || !counter || !totals || !x_bf16 || rows <= 0 || cols <= 0 || world < 1 ||
+      world > kTpMaxWorld || (slot_stride_bytes & 15) || slot_stride_bytes < rows * cols * 2 ||
+      (reinterpret_cast<uintptr_t>(staging) & 15) || (reinterpret_cast<uintptr_t>(x_bf16) & 15) ||
+      (reinterpret_cast<uintptr_t>(counter) & 3) || (reinterpret_cast<uintptr_t>(totals) & 3)) {
+    set_last_error("tp_push_sum_rmsnorm: null pointer, bad shape, world outside 1..%d or misaligned pointer", kTpMaxWorld);
+    return XAXB_BAD_ARGUMENT;
+  }
+  if (weight_bf16 && (!q_e4m3 || !row_scale || !row_inv_scale || (reinterpret_cast<uintptr_t>(weight_bf16) & 15) ||
+                      (reinterpret_cast<uintptr_t>(q_e4m3) & 7))) {
+    set_last_error("tp_push_sum_rmsnorm: with a norm weight the cast outputs are required and must be aligned");
+    return XAXB_BAD_ARGUMENT;
+  }
+  if (rows > kTpMaxSlots || cols % 8 != 0 || cols > 256 * 4 * 8) {
+    set_last_error("tp_push_sum_rmsnorm: at most %d rows; columns a multiple of 8, at most 8192", kTpMaxSlots);
+    return XAXB_UNSUPPORTED;
+  }
+  const Ctx* ctx = reinterpret_cast<const Ctx*>(ctx_);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const int vec = (int)(cols / 8);
+  const int vpt = (vec + 255) / 256;
+  const unsigned int pieces = (unsigned int)((long long)world * rows * vec);
+  const uint8_t* st = static_cast<const uint8_t*>(staging);
+  const unsigned int* cnt = static_cast<const unsigned int*>(counter);
+  unsigned int* tot = static_cast<unsigned int*>(totals);
+  uint4* xo = static_cast<uint4*>(x_bf16);
+  const uint4* wp = static_cast<const uint4*>(weight_bf16);
+  uint2* qp = static_cast<uint2*>(q_e4m3);
+  if (vpt == 1)
+    launch_kernel(tp_push_sum_norm_kernel<1>, dim3((unsigned)rows), dim3(256), 0, s, 1, st, slot_stride_bytes, cnt, tot,
+                  pieces, world, vec, xo, wp, eps, qp, row_scale, row_inv_scale, ctx->d_status);
+  else if (vpt == 2)
+    launch_kernel(tp_push_sum_norm_kernel<2>, dim3((unsigned)rows), dim3(256), 0, s, 1, st, slot_stride_bytes, cnt, tot,
+                  pieces, world, vec, xo, wp, eps, qp, row_scale, row_inv_scale, ctx->d_status);
+  else
+    launch_kernel(tp_push_sum_norm_kernel<4>, dim3((unsigned)rows), dim3(256), 0, s, 1, st, slot_stride_bytes, cnt, tot,
+                  pieces, world, vec, xo, wp, eps, qp, row_scale, row_inv_scale, ctx->d_status);
+  return check_launch("tp_push_sum_norm_kernel");
 }
 
 int64_t xaxb_tp_argmax_inbox_bytes(void) { return 2ll * kTpMaxWorld * kTpMaxSlots * 8; }

@@ -209,9 +209,13 @@ class Fp8Linear:
         out = ops.gemm_fp8(xq, wq, x_inv, w_inv, self.bias, res2)
         return out.reshape(*shape[:-1], self.out_features), updated
 
-    def forward_quantized(self, xq: torch.Tensor, x_inv: torch.Tensor, residual=None, out=None) -> torch.Tensor:
-        """GEMM on activations that an upstream kernel (RMSNorm / SiLU*up) already cast."""
+    def forward_quantized(self, xq: torch.Tensor, x_inv: torch.Tensor, residual=None, out=None):
+        """GEMM on activations that an upstream kernel (RMSNorm / SiLU*up) already cast.  ``out`` may be a
+        tensor to write into, or a tensor-parallel push target (an object with ``push_gemm``): the epilogue
+        then writes the partial output to every rank's staging buffer and the target is returned."""
         wq, w_inv = self.weight_q_current()
+        if out is not None and hasattr(out, "push_gemm"):
+            return out.push_gemm(xq, wq, x_inv, w_inv, self.bias, residual)
         return ops.gemm_fp8(xq, wq, x_inv, w_inv, self.bias, residual, out)
 
 

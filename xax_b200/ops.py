@@ -130,6 +130,45 @@ def gemm_fp8(a_q, b_q, row_mul=None, col_mul=None, bias=None, residual=None, out
     return _gemm("xaxb_gemm_fp8", a_q, b_q, row_mul, col_mul, bias, residual, out)
 
 
+def gemm_fp8_push(a_q, b_q, row_mul, col_mul, bias, residual, peer_ptrs, rank: int, world: int, slot_offset: int,
+                  flag_offset: int):
+    """gemm_fp8 whose epilogue writes the bf16 output into this rank's slot of every rank's staging buffer and
+    counts the pieces in on every rank (xaxb_gemm_fp8_push); M <= 128.  Nothing is returned: the consumer is
+    tp_push_sum_rmsnorm on each rank."""
+    if a_q.dtype != E4M3 or b_q.dtype != E4M3:
+        raise ValueError("gemm_fp8_push needs float8_e4m3fn operands")
+    ctx, st, lib = _c()
+    M, K = a_q.shape
+    N, Kb = b_q.shape
+    if K != Kb or a_q.stride(1) != 1 or b_q.stride(1) != 1:
+        raise ValueError("gemm_fp8_push: operands must be K-contiguous with equal inner dimensions")
+    row_mul, rs = _mul_arg(row_mul, M, "row_mul")
+    col_mul, cs = _mul_arg(col_mul, N, "col_mul")
+    ldr = residual.stride(0) if residual is not None else 0
+    check(lib.xaxb_gemm_fp8_push(ctx, st, ptr(a_q), a_q.stride(0), ptr(b_q), b_q.stride(0), M, N, K, ptr(row_mul), rs,
+                                 ptr(col_mul), cs, ptr(bias), ptr(residual), ldr, peer_ptrs, rank, world, slot_offset,
+                                 flag_offset), "gemm_fp8_push")
+
+
+def tp_push_sum_rmsnorm(staging_ptr: int, slot_stride: int, counter_ptr: int, totals_ptr: int, world: int, rows: int,
+                        cols: int, device, weight=None, eps: float = 0.0):
+    """Consumer of gemm_fp8_push on this rank: sum of the `world` staged partial outputs (local reads only) into
+    x bf16 [rows, cols]; with ``weight`` also RMSNorm + per-token e4m3 cast.  Returns (x, q, scale, inv_scale)
+    (the last three None without a weight)."""
+    ctx, st, lib = _c()
+    x = torch.empty((rows, cols), dtype=BF16, device=device)
+    q = scale = inv = None
+    if weight is not None:
+        weight = _req(weight, BF16, "weight")
+        q = torch.empty((rows, cols), dtype=E4M3, device=device)
+        scale = torch.empty((rows,), dtype=torch.float32, device=device)
+        inv = torch.empty((rows,), dtype=torch.float32, device=device)
+    check(lib.xaxb_tp_push_sum_rmsnorm(ctx, st, staging_ptr, slot_stride, counter_ptr, totals_ptr, world, rows, cols,
+                                       ptr(x), ptr(weight), float(eps), ptr(q), ptr(scale), ptr(inv)),
+          "tp_push_sum_rmsnorm")
+    return x, q, scale, inv
+
+
 def gemm_fp8_check(a_q, b_q, row_mul=None, col_mul=None, bias=None, residual=None, out=None):
     return _gemm("xaxb_gemm_fp8_check", a_q, b_q, row_mul, col_mul, bias, residual, out)
 
@@ -194,6 +233,30 @@ def argmax(logits, out=None, max_out=None):
     if out is None:
         out = torch.empty((rows,), dtype=torch.int32, device=logits.device)
     check(lib.xaxb_argmax(ctx, st, ptr(logits), rows, vocab, logits.stride(0), ptr(out), ptr(max_out)), "argmax")
+    return out
+
+
+def sample_top_p(logits, temperature: float, top_p: float, uniforms=None, *, allowed_token_range=None, eos_id: int = -1,
+                 allow_eos: bool = True, out=None):
+    """One token per row of bf16 logits [rows, vocab]: arg-max when ``temperature <= 0``, else the token at
+    quantile ``uniforms[r]`` of the top-p nucleus of softmax(logits / temperature); ``allowed_token_range``
+    (min, max) and the EOS rule mask tokens first (see xaxb_sample_top_p)."""
+    logits = _req(logits, BF16, "logits")
+    rows, vocab = logits.shape
+    if temperature > 0:
+        if uniforms is None:
+            raise ValueError("sample_top_p: sampling needs one uniform per row")
+        uniforms = _req(uniforms, torch.float32, "uniforms")
+        if uniforms.numel() != rows:
+            raise ValueError(f"sample_top_p: {uniforms.numel()} uniforms for {rows} rows")
+    lo, hi = (-1, -1) if allowed_token_range is None else (int(allowed_token_range[0]), int(allowed_token_range[1]))
+    if allowed_token_range is not None and hi <= lo:
+        raise ValueError("allowed_token_range must satisfy max_id > min_id.")
+    ctx, st, lib = _c()
+    if out is None:
+        out = torch.empty((rows,), dtype=torch.int32, device=logits.device)
+    check(lib.xaxb_sample_top_p(ctx, st, ptr(logits), rows, vocab, logits.stride(0), float(temperature), float(top_p),
+                                ptr(uniforms), lo, hi, int(eos_id), 1 if allow_eos else 0, ptr(out)), "sample_top_p")
     return out
 
 

@@ -99,7 +99,11 @@ class PeerExchange:
         self.argmax_sync = self.argmax_inbox + up(lib.xaxb_tp_argmax_inbox_bytes())
         self.data = [self.argmax_sync + sync]
         self.data.append(self.data[0] + up(rows * cols * 2))
-        total = self.data[1] + up(rows * cols * 2)
+        # push exchange: two (arrival counter, staging buffer of `size` slots) pairs used in alternation
+        self.slot = up(rows * cols * 2)
+        self.push_flag = [self.data[1] + up(rows * cols * 2), self.data[1] + up(rows * cols * 2) + 4096]
+        self.push_data = [self.push_flag[1] + 4096, self.push_flag[1] + 4096 + size * self.slot]
+        total = self.push_data[1] + size * self.slot
         self.buf = symm.empty(total, dtype=torch.uint8, device=device)
         self.buf.zero_()
         self.handle = symm.rendezvous(self.buf, group if group is not None else dist.group.WORLD)
@@ -110,6 +114,8 @@ class PeerExchange:
         torch.cuda.synchronize(device)
         dist.barrier(group)  # every rank's flags are zero before anyone raises one
         self.exchanges = 0  # sum exchanges issued (or captured) so far: picks the data buffer
+        self.pushes = 0     # push exchanges issued (or captured) so far: picks the (counter, staging) pair
+        self.push_totals = torch.zeros((2, lib.xaxb_tp_push_totals_bytes() // 4), dtype=torch.int32, device=device)
 
     def partial_out(self, rows: int, cols: int) -> torch.Tensor:
         """Where the next row-parallel GEMM must write its partial output (bf16 [rows, cols])."""
@@ -144,6 +150,12 @@ class PeerExchange:
         self.exchanges += 1
         return x, q, inv
 
+    def push_target(self, rows: int, cols: int) -> "PushTarget":
+        """Where the next row-parallel GEMM of a decode step pushes its partial output."""
+        if rows > self.rows or cols != self.cols or rows > 128:
+            raise ValueError(f"push exchange covers up to {min(self.rows, 128)} rows of {self.cols} columns")
+        return PushTarget(self, self.pushes & 1, rows, cols)
+
     def silu_site(self):
         """Arguments that route the SiLU*up kernel's row-amax exchange through this buffer."""
         return (self.peer_ptrs, self.rank, self.size, self.silu_inbox, self.silu_sync)
@@ -157,10 +169,45 @@ class PeerExchange:
         return ops.tp_allreduce_max(self.peer_ptrs, self.rank, self.size, self.inbox, self.max_sync, values)
 
 
+class PushTarget:
+    """One push exchange: the row-parallel GEMM writes its partial output into this rank's slot of every
+    rank's staging buffer from its epilogue (``push_gemm``); ``sum_norm`` then waits for every rank's pieces
+    and reduces them from local memory.  Made by PeerExchange.push_target; used once."""
+
+    def __init__(self, peer: PeerExchange, parity: int, rows: int, cols: int):
+        self.peer, self.parity, self.rows, self.cols = peer, parity, rows, cols
+        self.pushed = False
+
+    def push_gemm(self, xq, wq, x_inv, w_inv, bias, residual) -> "PushTarget":
+        from . import ops
+
+        p = self.peer
+        if xq.shape[0] != self.rows or wq.shape[0] != self.cols:
+            raise ValueError(f"push target was made for [{self.rows}, {self.cols}], got [{xq.shape[0]}, {wq.shape[0]}]")
+        ops.gemm_fp8_push(xq, wq, x_inv, w_inv, bias, residual, p.peer_ptrs, p.rank, p.size,
+                          p.push_data[self.parity] + p.rank * p.slot, p.push_flag[self.parity])
+        self.pushed = True
+        p.pushes += 1
+        return self
+
+    def sum_norm(self, weight_bf16=None, eps: float = 0.0):
+        """(x, q, inv_scale) with a norm weight, (x, None, None) without."""
+        from . import ops
+
+        if not self.pushed:
+            raise ValueError("nothing was pushed to this target")
+        p = self.peer
+        base = p.buf.data_ptr()
+        x, q, _, inv = ops.tp_push_sum_rmsnorm(base + p.push_data[self.parity], p.slot, base + p.push_flag[self.parity],
+                                               p.push_totals[self.parity].data_ptr(), p.size, self.rows, self.cols,
+                                               p.buf.device, weight_bf16, eps)
+        return x, q, inv
+
+
 class TensorParallel:
     """Collectives and the tensor-parallel forward of one transformer block."""
 
-    def __init__(self, rank: int, size: int, group=None, local_amax: bool = False):
+    def __init__(self, rank: int, size: int, group=None, local_amax: bool = False, push: bool = True):
         """``local_amax=False`` (default) keeps the reference's numerics: the activations feeding the
         row-parallel FP8 layers are cast with the amax of the WHOLE row, max-reduced over the ranks, so
         their e4m3 bytes equal the unsharded model's.  ``local_amax=True`` casts each rank's slice with
@@ -169,6 +216,9 @@ class TensorParallel:
         exchanges per block disappear.  It is a deviation from the reference and is never the default."""
         self.rank, self.size, self.group = rank, size, group
         self.local_amax = bool(local_amax)
+        # decode steps: the row-parallel GEMMs push their partial outputs to every rank from the epilogue
+        # (False: they write locally and the sum kernel pulls the rows from the peers)
+        self.push = bool(push)
         self.peer: PeerExchange | None = None
         if size > 1 and torch.cuda.is_available():
             # Kernels that wait for other GPUs do not mix well with successors that are scheduled
@@ -205,12 +255,19 @@ class TensorParallel:
         return self.peer is not None and rows <= self.peer.rows and cols == self.peer.cols
 
     # -- collectives ------------------------------------------------------------------------------
-    def partial_out(self, rows: int, cols: int):
-        """Output tensor for a row-parallel GEMM whose result all_reduce_sum will take next
-        (None: let the GEMM allocate; the exchange then goes through NCCL)."""
-        return self.peer.partial_out(rows, cols) if self._peer_fits(rows, cols) else None
+    def partial_out(self, rows: int, cols: int, decode: bool = False):
+        """Output of a row-parallel GEMM whose result all_reduce_sum(_norm) will take next: a push target for
+        a decode step on the push path, else the tensor in the symmetric buffer the peers pull from, else
+        None (let the GEMM allocate; the exchange then goes through NCCL)."""
+        if not self._peer_fits(rows, cols):
+            return None
+        if decode and self.push and rows <= 128:
+            return self.peer.push_target(rows, cols)
+        return self.peer.partial_out(rows, cols)
 
-    def all_reduce_sum(self, t: torch.Tensor) -> torch.Tensor:
+    def all_reduce_sum(self, t) -> torch.Tensor:
+        if isinstance(t, PushTarget):
+            return t.sum_norm()[0]
         if self.size > 1:
             if self.peer is not None and t.dim() == 2 and self._peer_fits(*t.shape) and \
                     t.data_ptr() == self.peer.partial_out(*t.shape).data_ptr():
@@ -224,6 +281,8 @@ class TensorParallel:
         from . import ops
 
         w = norm.weight_bf16()
+        if isinstance(t, PushTarget):
+            return t.sum_norm(w, norm.eps)
         if self.size > 1 and self.peer is not None and t.dim() == 2 and self._peer_fits(*t.shape) and \
                 t.shape[1] <= 8192 and t.data_ptr() == self.peer.partial_out(*t.shape).data_ptr():
             return self.peer.all_reduce_sum_norm(t, w, norm.eps)
@@ -324,7 +383,7 @@ class TensorParallel:
         part, new_cache = attn.forward_tokens(x, B, T, cache=cache, y_q=x_q, residual=x if first else None,
                                               workspace=workspace, advance=advance,
                                               reduce_amax=None if local else self.all_reduce_max,
-                                              out=self.partial_out(B * T, x.shape[1]),
+                                              out=self.partial_out(B * T, x.shape[1], decode=T == 1),
                                               peer_site=self.peer.attn_site() if fused else None)
         wq, col, bias = ff.fused_gate_up()
         F = ff.gate.out_features  # local width
@@ -349,7 +408,8 @@ class TensorParallel:
             h, _ = ops.silu_mul(gu, F, group_amax=hmax, group_rows=T)
             self.all_reduce_max(hmax)  # the down projection's input spans all ranks
             hq, _, h_inv = ops.quantize_with_amax(h, hmax, T)
-        part = ff.down.forward_quantized(hq, h_inv, x1 if first else None, self.partial_out(B * T, x.shape[1]))
+        part = ff.down.forward_quantized(hq, h_inv, x1 if first else None,
+                                         self.partial_out(B * T, x.shape[1], decode=T == 1))
         if next_norm is not None and T == 1:
             x2, q2, inv2 = self.all_reduce_sum_norm(part, next_norm)
             return x2, new_cache, (q2, inv2)
