@@ -60,6 +60,25 @@ def test_pushed_partial_outputs_sum_like_separate_gemms(world, M, N, K):
 
     rng = np.random.default_rng(world * 1000 + K)
     fake = _FakeRanks(world, M, N)
+    lib = _lib.load()
+    # The order in which float32 partial sums over K are added depends on the tile plan (how K is split over
+    # a cluster), and the pushing GEMM picks its plan from the kernels that can push.  Both sides of the
+    # comparison run under the same forced plan, so equality is bit for bit.
+    assert lib.xaxb_gemm_force_plan(64, 2) == 0
+    try:
+        _push_exchanges(fake, rng, world, M, N, K)
+    finally:
+        lib.xaxb_gemm_force_plan(0, 0)
+    # the counters hold exactly the pieces announced: world * M * N / 8 per exchange on each pair
+    for r in range(world):
+        c0 = int(fake.bufs[r][0:4].view(torch.int32).item())
+        c1 = int(fake.bufs[r][4096:4100].view(torch.int32).item())
+        assert c0 == 2 * world * M * N // 8 and c1 == world * M * N // 8
+
+
+def _push_exchanges(fake, rng, world, M, N, K):
+    from xax_b200 import _lib, ops
+
     w_norm = to_torch((1 + 0.1 * rng.standard_normal(N)).astype(np.float32).astype(bf16))
     for exchange in range(3):  # pairs 0, 1, 0: alternation and the running totals
         parity = exchange & 1
@@ -88,11 +107,27 @@ def test_pushed_partial_outputs_sum_like_separate_gemms(world, M, N, K):
                 assert torch.equal(scale, s_ref) and torch.equal(inv, i_ref)
             else:
                 assert q is None
-    # the counters hold exactly the pieces announced: world * M * N / 8 per exchange on each pair
+
+
+def test_push_with_the_library_own_plan_matches_within_rounding():
+    """Without a forced plan the pushing GEMM and the plain GEMM may split K differently: the sums then agree to
+    float32 summation order, i.e. a bf16 ulp here and there."""
+    from xax_b200 import _lib, ops
+
+    world, M, N, K = 4, 128, 4096, 3584
+    rng = np.random.default_rng(3)
+    fake = _FakeRanks(world, M, N)
+    acc = torch.zeros((M, N), dtype=torch.float32, device="cuda")
     for r in range(world):
-        c0 = int(fake.bufs[r][0:4].view(torch.int32).item())
-        c1 = int(fake.bufs[r][4096:4100].view(torch.int32).item())
-        assert c0 == 2 * world * M * N // 8 and c1 == world * M * N // 8
+        a = to_torch((rng.standard_normal((M, K)) * 30).astype(np.float32).astype(e4m3))
+        b = to_torch((rng.standard_normal((N, K)) * 30).astype(np.float32).astype(e4m3))
+        rm = to_torch(rng.uniform(0.005, 0.02, M).astype(np.float32))
+        fake.push(r, 0, a, b, rm, None, None, None)
+        acc += ops.gemm_fp8(a, b, rm, None, None, None).float()
+    x, _, _, _ = fake.consume(0, 0)
+    _lib.device_status()
+    want = acc.to(torch.bfloat16).float()
+    assert float((x.float() - want).norm() / want.norm()) < 2e-3
 
 
 def test_push_arguments_are_checked():

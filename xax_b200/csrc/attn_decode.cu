@@ -531,9 +531,10 @@ __global__ void attn_decode_merge_kernel(const float* __restrict__ ws_o, const f
   out[((long long)b * Hq + h) * D + d] = __float2bfloat16_rn(num / den);
 }
 
-// Merge + per-token cast as a kernel of its own (one CTA per sequence), for the kernels that do
-// not merge themselves.
-__global__ void __launch_bounds__(256) attn_decode_merge_cast_kernel(
+// Merge + per-token cast as a kernel of its own: one CTA of 512 threads per sequence, one work item
+// (a head's 8 consecutive dimensions) per thread -- with one CTA per SM the kernel is bound by the
+// latency of each thread's own instruction stream, so the stream is kept short.
+__global__ void __launch_bounds__(512) attn_decode_merge_cast_kernel(
     const float* __restrict__ ws_o, const float* __restrict__ ws_ml, const int32_t* __restrict__ positions, int Hq,
     int D, int max_chunks, int lanes, int window, const MergeOut mo, const TpRowMax tp, int* d_status) {
   pdl_trigger();
@@ -543,7 +544,7 @@ __global__ void __launch_bounds__(256) attn_decode_merge_cast_kernel(
   const int b = blockIdx.x;
   const int L = min(max(positions[b] + 1, 1), max_chunks * kChunk);  // clamped like the attention kernel
   const int n = min(decode_chunks(L, window), lanes);
-  merge_cast_row<256, false>(ws_o, ws_ml, b, n, Hq, D, max_chunks, mo, tp, d_status, s_max, s_inv_den, s_tp);
+  merge_cast_row<512, false>(ws_o, ws_ml, b, n, Hq, D, max_chunks, mo, tp, d_status, s_max, s_inv_den, s_tp);
 }
 
 static int make_cache_tmap(const Ctx* ctx, CUtensorMap* map, const void* cache, int64_t B, int64_t max_len,
@@ -645,7 +646,7 @@ static int decode_launch(xaxb_ctx* ctx_, void* stream, const void* q_rot_bf16, c
   rc = check_launch("attn_decode_kernel");
   if (rc) return rc;
   if (q_e4m3) {
-    launch_kernel(attn_decode_merge_cast_kernel, dim3((unsigned)B), dim3(256), 0, s, 1, p.ws_o, p.ws_ml, positions, (int)Hq, (int)D, max_chunks,
+    launch_kernel(attn_decode_merge_cast_kernel, dim3((unsigned)B), dim3(512), 0, s, 1, p.ws_o, p.ws_ml, positions, (int)Hq, (int)D, max_chunks,
                                                              lanes, p.window,
                   MergeOut{static_cast<uint4*>(out_bf16), static_cast<uint2*>(q_e4m3), row_scale, row_inv_scale},
                   tp ? *tp : TpRowMax{}, ctx->d_status);

@@ -117,11 +117,13 @@ __global__ void __launch_bounds__(256) silu_mul_kernel(const uint4* __restrict__
 }
 
 
-// Register-resident variant for rows of up to 256 * VPT * 8 elements: the row is read from
+// Register-resident variant for rows of up to NT * VPT * 8 elements: the row is read from
 // global memory once and stays in registers through the three phases (sum of squares,
-// normalise + amax, cast).
-template <int VPT>
-__global__ void __launch_bounds__(256) rmsnorm_reg_kernel(const uint4* __restrict__ x, const uint4* __restrict__ w,
+// normalise + amax, cast).  With few rows (a decode step) a CTA is alone on its SM, and what bounds
+// it is the dependent-instruction latency of its own warps: such launches spread a row over more
+// threads (NT = 512 or 1024, one 16-byte piece each).
+template <int VPT, int NT = 256>
+__global__ void __launch_bounds__(NT) rmsnorm_reg_kernel(const uint4* __restrict__ x, const uint4* __restrict__ w,
                                                           float eps, int vec, uint4* __restrict__ y,
                                                           uint2* __restrict__ q, float* __restrict__ scale,
                                                           float* __restrict__ inv_scale,
@@ -134,7 +136,7 @@ __global__ void __launch_bounds__(256) rmsnorm_reg_kernel(const uint4* __restric
   float acc = 0.0f;
 #pragma unroll
   for (int k = 0; k < VPT; ++k) {
-    const int i = threadIdx.x + k * 256;
+    const int i = threadIdx.x + k * NT;
     if (i < vec) {
       unpack8(__ldg(xr + i), v[k]);
 #pragma unroll
@@ -147,7 +149,7 @@ __global__ void __launch_bounds__(256) rmsnorm_reg_kernel(const uint4* __restric
   uint32_t m = 0;
 #pragma unroll
   for (int k = 0; k < VPT; ++k) {
-    const int i = threadIdx.x + k * 256;
+    const int i = threadIdx.x + k * NT;
     if (i < vec) {
       float wv[8];
       unpack8(__ldg(w + i), wv);
@@ -166,7 +168,7 @@ __global__ void __launch_bounds__(256) rmsnorm_reg_kernel(const uint4* __restric
   const float s = current_scale_from_amax(bf16_bits_to_float(row_bits));
 #pragma unroll
   for (int k = 0; k < VPT; ++k) {
-    const int i = threadIdx.x + k * 256;
+    const int i = threadIdx.x + k * NT;
     if (i < vec) q[row * vec + i] = quantize8f(v[k], s);
   }
   if (threadIdx.x == 0) {
@@ -592,7 +594,12 @@ int xaxb_rmsnorm(xaxb_ctx* ctx, void* stream, const void* x_bf16, const void* we
   uint2* qp = static_cast<uint2*>(q_e4m3);
   unsigned int* gp = reinterpret_cast<unsigned int*>(group_amax);
   const int64_t gr = group_rows > 0 ? group_rows : 1;
-  if (vec > 64 && vec <= 256)
+  const bool few_rows = rows <= 2 * reinterpret_cast<const Ctx*>(ctx)->num_sms;
+  if (few_rows && vec > 256 && vec <= 512)
+    launch_kernel(rmsnorm_reg_kernel<1, 512>, dim3((unsigned)rows), dim3(512), 0, st, 1, xp, wp, eps, (int)vec, yp, qp, scale, inv_scale, gp, gr);
+  else if (few_rows && vec > 512 && vec <= 1024)
+    launch_kernel(rmsnorm_reg_kernel<1, 1024>, dim3((unsigned)rows), dim3(1024), 0, st, 1, xp, wp, eps, (int)vec, yp, qp, scale, inv_scale, gp, gr);
+  else if (vec > 64 && vec <= 256)
     launch_kernel(rmsnorm_reg_kernel<1>, dim3((unsigned)rows), dim3(256), 0, st, 1, xp, wp, eps, (int)vec, yp, qp, scale, inv_scale, gp, gr);
   else if (vec > 256 && vec <= 512)
     launch_kernel(rmsnorm_reg_kernel<2>, dim3((unsigned)rows), dim3(256), 0, st, 1, xp, wp, eps, (int)vec, yp, qp, scale, inv_scale, gp, gr);

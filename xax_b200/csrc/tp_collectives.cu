@@ -80,8 +80,8 @@ __global__ void __launch_bounds__(256) tp_allreduce_sum_kernel(const PeerTable p
 // block's attn_norm) done on the summed row while it is still in registers: x (bf16) goes to
 // local memory for the residual path, the normalised row only as e4m3 bytes and its scale.
 // Arithmetic and rounding are those of rmsnorm_reg_kernel, so the bytes equal the unfused path's.
-template <int VPT>
-__global__ void __launch_bounds__(256) tp_allreduce_sum_norm_kernel(
+template <int VPT, int NT = 256>
+__global__ void __launch_bounds__(NT) tp_allreduce_sum_norm_kernel(
     const PeerTable peers, int64_t data_off, int64_t sync_off, int rank, int world, int vec, uint4* __restrict__ x_out,
     const uint4* __restrict__ w, float eps, uint2* __restrict__ q, float* __restrict__ scale,
     float* __restrict__ inv_scale, int* d_status) {
@@ -95,7 +95,7 @@ __global__ void __launch_bounds__(256) tp_allreduce_sum_norm_kernel(
   float acc = 0.0f;
 #pragma unroll
   for (int k = 0; k < VPT; ++k) {
-    const int i = threadIdx.x + k * 256;
+    const int i = threadIdx.x + k * NT;
     if (i < vec) {
       uint4 part[kTpMaxWorld];
 #pragma unroll
@@ -125,7 +125,7 @@ __global__ void __launch_bounds__(256) tp_allreduce_sum_norm_kernel(
   uint32_t m = 0;
 #pragma unroll
   for (int k = 0; k < VPT; ++k) {
-    const int i = threadIdx.x + k * 256;
+    const int i = threadIdx.x + k * NT;
     if (i < vec) {
       float wv[8];
       unpack8(__ldg(w + i), wv);
@@ -140,7 +140,7 @@ __global__ void __launch_bounds__(256) tp_allreduce_sum_norm_kernel(
   const float s = current_scale_from_amax(bf16_bits_to_float(row_bits));
 #pragma unroll
   for (int k = 0; k < VPT; ++k) {
-    const int i = threadIdx.x + k * 256;
+    const int i = threadIdx.x + k * NT;
     if (i < vec) q[row * vec + i] = quantize8f(v[k], s);
   }
   if (threadIdx.x == 0) {
@@ -160,8 +160,8 @@ __global__ void __launch_bounds__(256) tp_allreduce_sum_norm_kernel(
 // memory (one per token row and counter), so a captured step can be replayed.
 constexpr int kSiteTpPush = 46;
 
-template <int VPT>
-__global__ void __launch_bounds__(256) tp_push_sum_norm_kernel(
+template <int VPT, int NT = 256>
+__global__ void __launch_bounds__(NT) tp_push_sum_norm_kernel(
     const uint8_t* __restrict__ staging, int64_t slot_stride, const unsigned int* counter, unsigned int* totals,
     unsigned int pieces_per_exchange, int world, int vec, uint4* __restrict__ x_out, const uint4* __restrict__ w,
     float eps, uint2* __restrict__ q, float* __restrict__ scale, float* __restrict__ inv_scale, int* d_status) {
@@ -189,7 +189,7 @@ __global__ void __launch_bounds__(256) tp_push_sum_norm_kernel(
   float acc = 0.0f;
 #pragma unroll
   for (int k = 0; k < VPT; ++k) {
-    const int i = threadIdx.x + k * 256;
+    const int i = threadIdx.x + k * NT;
     if (i < vec) {
       uint4 part[kTpMaxWorld];
 #pragma unroll
@@ -220,7 +220,7 @@ __global__ void __launch_bounds__(256) tp_push_sum_norm_kernel(
   uint32_t m = 0;
 #pragma unroll
   for (int k = 0; k < VPT; ++k) {
-    const int i = threadIdx.x + k * 256;
+    const int i = threadIdx.x + k * NT;
     if (i < vec) {
       float wv[8];
       unpack8(__ldg(w + i), wv);
@@ -235,7 +235,7 @@ __global__ void __launch_bounds__(256) tp_push_sum_norm_kernel(
   const float s = current_scale_from_amax(bf16_bits_to_float(row_bits));
 #pragma unroll
   for (int k = 0; k < VPT; ++k) {
-    const int i = threadIdx.x + k * 256;
+    const int i = threadIdx.x + k * NT;
     if (i < vec) q[row * vec + i] = quantize8f(v[k], s);
   }
   if (threadIdx.x == 0) {
@@ -401,18 +401,18 @@ int xaxb_tp_allreduce_sum_rmsnorm(xaxb_ctx* ctx_, void* stream, void* const* pee
   uint4* xo = static_cast<uint4*>(x_bf16);
   const uint4* wp = static_cast<const uint4*>(weight_bf16);
   uint2* qp = static_cast<uint2*>(q_e4m3);
-  if (vpt == 1)
-    launch_kernel(tp_allreduce_sum_norm_kernel<1>, dim3((unsigned)rows), dim3(256), 0, s, 1, t, data_offset_bytes, sync_offset_bytes, rank, world,
-                                                                 vec, xo, wp, eps, qp, row_scale, row_inv_scale,
-                                                                 ctx->d_status);
-  else if (vpt == 2)
-    launch_kernel(tp_allreduce_sum_norm_kernel<2>, dim3((unsigned)rows), dim3(256), 0, s, 1, t, data_offset_bytes, sync_offset_bytes, rank, world,
-                                                                 vec, xo, wp, eps, qp, row_scale, row_inv_scale,
-                                                                 ctx->d_status);
-  else
-    launch_kernel(tp_allreduce_sum_norm_kernel<4>, dim3((unsigned)rows), dim3(256), 0, s, 1, t, data_offset_bytes, sync_offset_bytes, rank, world,
-                                                                 vec, xo, wp, eps, qp, row_scale, row_inv_scale,
-                                                                 ctx->d_status);
+  // the same thread layout as xaxb_rmsnorm picks for this shape, so that the sum of squares is added
+  // in the same order and the bytes equal the unfused path's
+#define XAXB_SUMNORM(V, N)                                                                                          \
+  launch_kernel(tp_allreduce_sum_norm_kernel<V, N>, dim3((unsigned)rows), dim3(N), 0, s, 1, t, data_offset_bytes, \
+                sync_offset_bytes, rank, world, vec, xo, wp, eps, qp, row_scale, row_inv_scale, ctx->d_status)
+  const bool few_rows = rows <= 2 * ctx->num_sms;
+  if (few_rows && vec > 256 && vec <= 512) XAXB_SUMNORM(1, 512);
+  else if (few_rows && vec > 512) XAXB_SUMNORM(1, 1024);
+  else if (vpt == 1) XAXB_SUMNORM(1, 256);
+  else if (vpt == 2) XAXB_SUMNORM(2, 256);
+  else XAXB_SUMNORM(4, 256);
+#undef XAXB_SUMNORM
   return check_launch("tp_allreduce_sum_norm_kernel");
 }
 
@@ -449,15 +449,16 @@ int xaxb_tp_push_sum_rmsnorm(xaxb_ctx* ctx_, void* stream, const void* staging, 
   uint4* xo = static_cast<uint4*>(x_bf16);
   const uint4* wp = static_cast<const uint4*>(weight_bf16);
   uint2* qp = static_cast<uint2*>(q_e4m3);
-  if (vpt == 1)
-    launch_kernel(tp_push_sum_norm_kernel<1>, dim3((unsigned)rows), dim3(256), 0, s, 1, st, slot_stride_bytes, cnt, tot,
-                  pieces, world, vec, xo, wp, eps, qp, row_scale, row_inv_scale, ctx->d_status);
-  else if (vpt == 2)
-    launch_kernel(tp_push_sum_norm_kernel<2>, dim3((unsigned)rows), dim3(256), 0, s, 1, st, slot_stride_bytes, cnt, tot,
-                  pieces, world, vec, xo, wp, eps, qp, row_scale, row_inv_scale, ctx->d_status);
-  else
-    launch_kernel(tp_push_sum_norm_kernel<4>, dim3((unsigned)rows), dim3(256), 0, s, 1, st, slot_stride_bytes, cnt, tot,
-                  pieces, world, vec, xo, wp, eps, qp, row_scale, row_inv_scale, ctx->d_status);
+#define XAXB_PUSHNORM(V, N)                                                                                      \
+  launch_kernel(tp_push_sum_norm_kernel<V, N>, dim3((unsigned)rows), dim3(N), 0, s, 1, st, slot_stride_bytes, cnt, \
+                tot, pieces, world, vec, xo, wp, eps, qp, row_scale, row_inv_scale, ctx->d_status)
+  const bool few_rows = rows <= 2 * ctx->num_sms;  // the thread layout xaxb_rmsnorm picks for this shape
+  if (few_rows && vec > 256 && vec <= 512) XAXB_PUSHNORM(1, 512);
+  else if (few_rows && vec > 512) XAXB_PUSHNORM(1, 1024);
+  else if (vpt == 1) XAXB_PUSHNORM(1, 256);
+  else if (vpt == 2) XAXB_PUSHNORM(2, 256);
+  else XAXB_PUSHNORM(4, 256);
+#undef XAXB_PUSHNORM
   return check_launch("tp_push_sum_norm_kernel");
 }
 

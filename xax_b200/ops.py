@@ -573,10 +573,14 @@ def attn_decode_static(q_rot, k_cache, v_cache, positions, *, scale=None, k_is_r
     """Decode attention for callers that can hand over no scratch memory: identical to
     ``attn_decode`` except that the partial results live in an array inside the library (16 MiB
     per GPU).  Shapes needing more raise; calls must not overlap on the GPU."""
-    _attn_args(q_rot, k_cache, v_cache, positions)
     B, Hq, D = q_rot.shape
     _, max_len, Hkv, _ = k_cache.shape
     ctx, st, lib = _c()
+    need, have = lib.xaxb_attn_decode_workspace_bytes(B, Hq, D, max_len), lib.xaxb_attn_decode_static_capacity_bytes()
+    if need > have:  # refused on the shape alone, before anything is looked at or read
+        raise ValueError(f"attn_decode_static: B={B} Hq={Hq} D={D} max_len={max_len} needs {need} bytes of scratch, the "
+                         f"built-in array holds {have}; use attn_decode with a caller-provided workspace")
+    _attn_args(q_rot, k_cache, v_cache, positions)
     if out is None:
         out = torch.empty_like(q_rot)
     if scale is None:
