@@ -100,6 +100,15 @@ int xaxb_quantize_delayed(xaxb_ctx* ctx, void* stream, const void* x_bf16, int64
                           const float* scale_in, const float* history_in, int history_len, void* q_e4m3,
                           float* history_out, float* scale_out, float* inv_scale_out, float* amax_scratch);
 
+/*
+ * Dequantise (xax/nn/fp8.py:123-138): out[r, c] = T(q[r, c]) / T(scale[r * scale_stride]) with T = bfloat16
+ * (out_is_bf16 != 0; the quotient rounds once to bf16) or float32; scale_stride 0 = one scale for the tensor,
+ * 1 = one per row.  cols a multiple of 8.  The linear layer never calls this (its GEMM consumes the e4m3
+ * bytes and applies 1 / scale in the epilogue); it serves the free function of the same name.
+ */
+int xaxb_dequantize(xaxb_ctx* ctx, void* stream, const void* q_e4m3, int64_t rows, int64_t cols, const float* scale,
+                    int scale_stride, int out_is_bf16, void* out);
+
 /* ---- kernel 2: e4m3 x e4m3 (and bf16 x bf16) GEMM on tcgen05 / TMEM ------------- */
 
 /*

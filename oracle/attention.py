@@ -30,9 +30,31 @@ class Embedding:
         self.weight = np.asarray(weight)
 
 
+class LoRALinear:
+    """xax/nn/lora.py:14-97 (fields only; the forward is the LoRA branch of apply_linear)."""
+
+    def __init__(self, weight_oi, bias_o, lora_a_ir, lora_b_ro, rank, alpha=16.0):
+        self.weight_oi, self.lora_a_ir, self.lora_b_ro = np.asarray(weight_oi), np.asarray(lora_a_ir), np.asarray(lora_b_ro)
+        self.bias_o = None if bias_o is None else np.asarray(bias_o)
+        self.rank, self.alpha = rank, alpha
+
+    @property
+    def scaling(self):
+        return self.alpha / self.rank
+
+
 def apply_linear(x, linear):
-    """xax/arch/attention.py:30-69 (LoRA branch out of scope)."""
+    """xax/arch/attention.py:30-69."""
     x = np.asarray(x)
+    if isinstance(linear, LoRALinear):  # :44-51
+        dt = promote(x.dtype, linear.weight_oi.dtype)
+        y = matmul_nt(x, linear.weight_oi, dt)
+        if linear.bias_o is not None:
+            y = rnd(f32(y) + f32(linear.bias_o), promote(dt, linear.bias_o.dtype))
+        low = rnd(f32(x) @ f32(linear.lora_a_ir), promote(x.dtype, linear.lora_a_ir.dtype))
+        delta = rnd(f32(low) @ f32(linear.lora_b_ro), promote(low.dtype, linear.lora_b_ro.dtype))
+        delta = rnd(f32(delta) * float32(linear.scaling), delta.dtype)  # weak Python scalar keeps the dtype
+        return rnd(f32(y) + f32(delta), promote(y.dtype, delta.dtype))
     if isinstance(linear, Fp8Linear):  # :52-58 -- whole tensor at once, scales dropped
         return linear(x)[0]
     if isinstance(linear, Linear):  # :59-64

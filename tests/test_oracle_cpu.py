@@ -247,3 +247,53 @@ def test_hf_config_parsing_defaults_and_aliases():
     assert q.rope_beta_slow == 1.0 and q.rope_beta_fast == 32.0
     with pytest.raises(ValueError, match="hidden_size"):
         hf_config_to_llm_config({"num_attention_heads": 8, "num_hidden_layers": 1, "vocab_size": 10})
+
+
+def test_weight_quantisation_cache_changes_nothing():
+    """oracle.fp8.CACHE_WEIGHT_QUANT computes the weight's scale / bytes once per layer: same outputs, both
+    matmul executions, whole-tensor and per-row scaling."""
+    from oracle import fp8 as ofp8
+
+    rng = np.random.default_rng(21)
+    w = (rng.standard_normal((48, 64)) * 0.05).astype(np.float32).astype(ofp8.bfloat16)
+    x = rng.standard_normal((9, 64)).astype(np.float32).astype(ofp8.bfloat16)
+    layer = ofp8.Fp8Linear(w, None)
+    outs = {}
+    for cache in (False, True):
+        ofp8.CACHE_WEIGHT_QUANT = cache
+        try:
+            for mode in ("qdq", "fp8_gemm"):
+                ofp8.MATMUL_MODE = mode
+                for _ in range(2):
+                    outs[(cache, mode)] = (layer(x)[0], layer.call_rows(x)[0])
+        finally:
+            ofp8.CACHE_WEIGHT_QUANT, ofp8.MATMUL_MODE = False, "qdq"
+    for mode in ("qdq", "fp8_gemm"):
+        for a, b in zip(outs[(False, mode)], outs[(True, mode)]):
+            assert np.array_equal(np.asarray(a).view(np.uint16), np.asarray(b).view(np.uint16))
+
+
+def test_sampling_restatement_properties():
+    """xax/arch/llm.py:1446-1489 / :1547-1570 as restated in oracle.llm: the nucleus always holds the arg-max,
+    shrinks to it as top_p -> 0, is everything at top_p = 1; masks use the most negative finite value; the
+    quantile draw is monotone in u."""
+    from oracle import llm as ollm
+
+    rng = np.random.default_rng(22)
+    lg = (rng.standard_normal((4, 300)) * 2).astype(np.float32).astype(ollm.bfloat16)
+    order, probs, keep = ollm.nucleus(lg[0], 0.7, 0.9)
+    assert order[0] == int(np.argmax(lg[0].astype(np.float32))) and keep[0]
+    assert abs(float(probs.sum()) - 1.0) < 1e-4 and float(probs[keep].sum()) <= 0.9 + 1e-6
+    assert not keep[int(keep.sum()):].any()  # a prefix of the sorted order
+    assert ollm.nucleus(lg[0], 0.7, 1e-6)[2].sum() == 1 and ollm.nucleus(lg[0], 0.7, 1.0)[2].all()
+    toks = [int(ollm.sample_next_token(lg[:1], 0.7, 0.9, np.array([u], np.float32))[0, 0]) for u in np.linspace(0, 0.999, 50)]
+    ranks = [int(np.nonzero(order == t)[0][0]) for t in toks]
+    assert ranks == sorted(ranks) and ranks[0] == 0
+    assert np.array_equal(ollm.sample_next_token(lg, 0.0, 0.9)[:, 0], np.argmax(lg.astype(np.float32), -1))
+    m = ollm.apply_sampling_mask(lg[:1], 1, 7, 3, (10, 20))  # EOS 7 not yet allowed: only 10..19 survive
+    low = np.asarray(m.astype(np.float32))[0]
+    assert (low[:10] == low[25]).all() and low[25] < -3e38 and 10 <= int(np.argmax(low)) < 20
+    m2 = ollm.apply_sampling_mask(lg[:1], 3, 7, 3, (10, 20))
+    assert float(m2.astype(np.float32)[0, 7]) == float(lg[0, 7].astype(np.float32))
+    with pytest.raises(ValueError, match="max_id > min_id"):
+        ollm.apply_sampling_mask(lg[:1], 0, -1, 0, (5, 5))

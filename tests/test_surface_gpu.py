@@ -106,3 +106,55 @@ def test_transformer_stack_and_transformer():
     assert int(a.max()) < 96 and int(a.min()) >= 0
     with pytest.raises(ValueError, match="cross-attention"):
         model.decode(toks, toks)
+
+
+def test_lora_branch_of_apply_linear_vs_oracle():
+    """xax/arch/attention.py:44-51 with xax/nn/lora.py: y = x W^T + b + ((x A) B) * alpha / rank."""
+    from oracle import attention as oattn
+    from xax_b200.arch.attention import Linear, apply_linear
+    from xax_b200.nn.lora import LoRALinear, loraize_linear
+
+    rng = np.random.default_rng(12)
+    I, O, R = 256, 136, 16
+    w = (rng.standard_normal((O, I)) * 0.05).astype(np.float32).astype(bf16)
+    b = (rng.standard_normal(O) * 0.1).astype(np.float32).astype(bf16)
+    a = (rng.standard_normal((I, R)) / np.sqrt(I)).astype(np.float32).astype(bf16)
+    bb = (rng.standard_normal((R, O)) * 0.3).astype(np.float32).astype(bf16)
+    x = rng.standard_normal((3, 21, I), dtype=np.float32).astype(bf16)
+    for bias in (b, None):
+        exp = oattn.apply_linear(x, oattn.LoRALinear(w, bias, a, bb, R, alpha=8.0))
+        layer = LoRALinear(to_torch(w), None if bias is None else to_torch(bias), to_torch(a), to_torch(bb), R, alpha=8.0)
+        got = apply_linear(to_torch(x), layer)
+        assert got.shape == (3, 21, O) and layer.scaling == 0.5
+        assert rel_fro(f32(to_numpy(got)), f32(exp)) < 5e-3
+    # a fresh LoRA layer (B = 0) equals its base layer (xax/nn/lora.py:63-64)
+    base = Linear(I, O, use_bias=True, weight=to_torch(w), bias=to_torch(b))
+    fresh = loraize_linear(base, 8, key=3)
+    assert torch.equal(apply_linear(to_torch(x), fresh), apply_linear(to_torch(x), base))
+    with pytest.raises(ValueError, match="rank"):
+        loraize_linear(base, 0)
+
+
+def test_dequantize_and_quantize_dequantize_match_oracle_bit_for_bit():
+    """xax/nn/fp8.py:123-162: dequantize and the quantise -> dequantise round trip, bf16 and float32."""
+    from oracle import fp8 as ofp8
+    from xax_b200 import ops
+    from xax_b200.nn import fp8
+
+    rng = np.random.default_rng(13)
+    x = (rng.standard_normal((37, 200)) * 3).astype(np.float32).astype(bf16)
+    scale = ofp8.current_scale(x, ofp8.float8_e4m3fn, bf16)
+    q = ofp8.quantize(x, ofp8.float8_e4m3fn, scale, bf16)
+    got = fp8.dequantize(to_torch(q), torch.bfloat16, torch.tensor(float(f32(scale))))
+    exp = ofp8.dequantize(q, bf16, scale)
+    assert np.array_equal(to_numpy(got).view(np.uint16), exp.view(np.uint16))
+    got32 = fp8.dequantize(to_torch(q), torch.float32, torch.tensor(float(f32(scale))))
+    assert np.array_equal(to_numpy(got32), ofp8.dequantize(q, np.float32, f32(scale)))
+    rt = fp8.quantize_dequantize(to_torch(x), torch.float8_e4m3fn, torch.tensor(float(f32(scale))), torch.bfloat16)
+    assert np.array_equal(to_numpy(rt).view(np.uint16), ofp8.quantize_dequantize(x, ofp8.float8_e4m3fn, scale, bf16).view(np.uint16))
+    # per-row scales through the functional layer
+    qr, s_rows, _, _ = ops.quantize_current(to_torch(x[:, :192].copy()), 1)
+    d = to_numpy(ops.dequantize(qr, s_rows))
+    for r in range(5):
+        e = ofp8.dequantize(to_numpy(qr)[r], bf16, to_numpy(s_rows)[r].astype(bf16))
+        assert np.array_equal(d[r].view(np.uint16), e.view(np.uint16))

@@ -92,6 +92,29 @@ def _worker(rank: int, world: int, port: int, results):
             take = v > best
             best, tok = np.where(take, v, best), np.where(take, i, tok)
         assert np.array_equal(tok, logits.argmax(axis=1))
+
+        # ---- the push exchange's arithmetic: every rank holds every rank's bf16 partial output (its slot of
+        # the staging buffer), sums the slots in rank order in float32 and rounds once -- so all ranks get the
+        # same bits, whatever order the pieces arrived in
+        part_bf = torch.from_numpy(part.astype(np.float32)).to(torch.bfloat16)
+        slots = tp.all_gather(part_bf.view(torch.int16).to(torch.int32)).to(torch.int16).view(torch.bfloat16)  # [world, M, N]
+        acc = torch.zeros(part_bf.shape, dtype=torch.float32)
+        for r in range(world):
+            acc += slots[r].float()
+        mine = acc.to(torch.bfloat16)
+        others = tp.all_gather(mine.view(torch.int16).to(torch.int32))
+        assert all(torch.equal(others[r], mine.view(torch.int16).to(torch.int32)) for r in range(world))
+        pieces = world * part_bf.shape[0] * part_bf.shape[1] // 8  # what each rank's arrival counter must reach
+        assert pieces == world * 16 * 64 // 8
+
+        # ---- make_sharded_array (xax/arch/llm.py:1244-1265): this rank's slice, or the whole tensor
+        from xax_b200.parallel import make_sharded_array
+
+        assert torch.equal(make_sharded_array(wt, "layers.3.mlp.down_proj", rank, world), wt[:, k0:k0 + 256 // world])
+        assert torch.equal(make_sharded_array(wt, "layers.3.self_attn.q_proj", rank, world),
+                           wt[rank * (64 // world):(rank + 1) * (64 // world)])
+        assert make_sharded_array(wt, "layers.3.input_layernorm.weight", rank, world) is wt
+        assert make_sharded_array(wt[0], "layers.3.mlp.up_proj.bias", rank, world).shape == (256,)  # 1-D: replicated
         results[rank] = "ok"
     except Exception as e:  # noqa: BLE001
         import traceback

@@ -26,6 +26,8 @@ NAME_MAP = {
     "build_pretrained_llm": "arch.hf", "hf_config_to_llm_config": "arch.hf", "load_hf_weights_into_llm": "arch.hf",
     # xax.nn.fp8 (not re-exported by xax at top level; offered here for convenience)
     "Fp8Linear": "nn.fp8", "Fp8Scales": "nn.fp8", "init_fp8_scales": "nn.fp8", "fp8_matmul": "nn.fp8",
+    # xax.nn.lora
+    "LoRALinear": "nn.lora", "loraize_linear": "nn.lora",
     # tensor parallelism
     "setup_model_parallel_mesh": "parallel", "TensorParallel": "parallel", "make_sharded_array": "parallel",
 }

@@ -43,6 +43,7 @@ SIGNATURES: dict[str, tuple] = {
     "xaxb_set_wait_limit_ms": (_I, [_P, _I, _I]),
     "xaxb_quantize_current": (_I, [_P, _P, _P, _I64, _I64, _I64, _P, _P, _P, _P]),
     "xaxb_quantize_delayed": (_I, [_P, _P, _P, _I64, _I64, _P, _P, _I, _P, _P, _P, _P, _P]),
+    "xaxb_dequantize": (_I, [_P, _P, _P, _I64, _I64, _P, _I, _I, _P]),
     "xaxb_quantize_with_amax": (_I, [_P, _P, _P, _I64, _I64, _I64, _P, _P, _P, _P]),
     "xaxb_gemm_fp8": (_I, [_P, _P, _P, _I64, _P, _I64, _I64, _I64, _I64, _P, _I, _P, _I, _P, _P, _I64, _P, _I64]),
     "xaxb_gemm_bf16": (_I, [_P, _P, _P, _I64, _P, _I64, _I64, _I64, _I64, _P, _I, _P, _I, _P, _P, _I64, _P, _I64]),

@@ -26,6 +26,7 @@ import torch
 
 from .. import ops
 from ..nn.fp8 import Fp8Linear, Fp8Scales, init_fp8_scales
+from ..nn.lora import LoRALinear
 
 BF16 = torch.bfloat16
 
@@ -78,6 +79,10 @@ def apply_linear(x: torch.Tensor, linear, *, residual: torch.Tensor | None = Non
     """xax/arch/attention.py:30-69: dispatch on the layer type.  An Fp8Linear is applied to the
     whole tensor at once (one activation scale, scales dropped).  A leading batch dimension
     (rank 3) reproduces the vmapped reference: one activation scale per sequence."""
+    if isinstance(linear, LoRALinear):  # :44-51: the frozen layer plus the low-rank residual
+        if residual is not None:
+            raise ValueError("a LoRA layer does not take a fused residual")
+        return linear(x)
     if isinstance(linear, Fp8Linear):
         if x.dim() == 3 and linear.use_fp8:
             B, T, _ = x.shape

@@ -200,52 +200,59 @@ __device__ __forceinline__ float warp_max_f32(float v) {
   return r;
 }
 
-// Rotate-on-load: thread `tid` rotates row `tid` of the K tile in shared memory in place, once the tile
-// has landed (barrier `bar`, parity `parity`).  Pair (i, i + D/2) lives in 16-byte piece i/8 of box
-// (i / 64) and piece (i + D/2)/8 of the other half.  The row's cos / sin values do not depend on the
-// tile, so they are requested before the wait for it; the rotation itself is packed bf16 arithmetic --
-// every product and every sum rounds to bf16 on its own, which is exactly the reference's bf16 op
-// sequence (xax/arch/attention.py:510-515) -- six instructions per two pairs.  Returns false if the wait
-// gave up.  The caller fences (generic -> async proxy) and synchronises before the tile is multiplied.
+// Rotate-on-load.  Thread `tid` owns row `tid` of every K tile of its CTA.  The row's cos / sin values
+// (D/2 of each, from the table row of the token's position) are fetched into registers one tile ahead --
+// right after the previous tile was rotated -- so that they have arrived by the time the K tile lands;
+// the rotation itself then only touches shared memory.  It is packed bf16 arithmetic: every product
+// and every sum rounds to bf16 on its own, which is exactly the reference's bf16 op sequence
+// (xax/arch/attention.py:510-515), six instructions per two pairs.  Pair (i, i + D/2) lives in 16-byte
+// piece i/8 of box (i / 64) and piece (i + D/2)/8 of the other half of the row.
 template <int D>
-__device__ __forceinline__ bool rotate_k_tile(uint8_t* sK, const DecodeParams& p, int tok0, int valid, uint64_t* bar,
-                                              uint32_t parity, volatile int* abort_flag) {
-  using SM = DecodeSmem<D>;
-  constexpr int half = D / 2, kPieces = half / 8;
-  const int tid = threadIdx.x;
-  const long long pos = tok0 + tid;
-  const bool row_ok = tid < valid && pos < p.table_len;
-  uint4 cv[kPieces], sv[kPieces];
-  if (row_ok) {
+struct RopeRow {
+  static constexpr int kPieces = D / 16;
+  uint4 c[kPieces], s[kPieces];
+  bool ok;
+};
+
+template <int D>
+__device__ __forceinline__ void load_rope_row(RopeRow<D>& r, const DecodeParams& p, int tok0, int valid) {
+  constexpr int half = D / 2;
+  const long long pos = tok0 + (int)threadIdx.x;
+  r.ok = (int)threadIdx.x < valid && pos < p.table_len;
+  if (r.ok) {
     const uint4* cr = reinterpret_cast<const uint4*>(p.cos_t + pos * half);
     const uint4* sr = reinterpret_cast<const uint4*>(p.sin_t + pos * half);
 #pragma unroll
-    for (int c = 0; c < kPieces; ++c) cv[c] = __ldg(cr + c), sv[c] = __ldg(sr + c);
+    for (int i = 0; i < RopeRow<D>::kPieces; ++i) r.c[i] = __ldg(cr + i), r.s[i] = __ldg(sr + i);
   }
-  const bool ok = mbar_wait(bar, parity, abort_flag, p.d_status, XAXB_DEVICE_TIMEOUT * 1000 + kSiteDecK);
-  if (ok && row_ok) {
+}
+
+template <int D>
+__device__ __forceinline__ void rotate_k_row(uint8_t* sK, const RopeRow<D>& r) {
+  using SM = DecodeSmem<D>;
+  constexpr int kPieces = RopeRow<D>::kPieces;
+  const int tid = threadIdx.x;
+  if (!r.ok) return;
 #pragma unroll
-    for (int c = 0; c < kPieces; ++c) {
-      const int c2 = c + kPieces;
-      uint4* p1 = reinterpret_cast<uint4*>(sK + (c / 8) * SM::kHalfBytes + sw128_offset(tid, c % 8));
-      uint4* p2 = reinterpret_cast<uint4*>(sK + (c2 / 8) * SM::kHalfBytes + sw128_offset(tid, c2 % 8));
-      uint4 a = *p1, bb = *p2;
-      __nv_bfloat162* aw = reinterpret_cast<__nv_bfloat162*>(&a);
-      __nv_bfloat162* bw = reinterpret_cast<__nv_bfloat162*>(&bb);
-      const __nv_bfloat162* cw = reinterpret_cast<const __nv_bfloat162*>(&cv[c]);
-      const __nv_bfloat162* sw = reinterpret_cast<const __nv_bfloat162*>(&sv[c]);
+  for (int c = 0; c < kPieces; ++c) {
+    const int c2 = c + kPieces;
+    uint4* p1 = reinterpret_cast<uint4*>(sK + (c / 8) * SM::kHalfBytes + sw128_offset(tid, c % 8));
+    uint4* p2 = reinterpret_cast<uint4*>(sK + (c2 / 8) * SM::kHalfBytes + sw128_offset(tid, c2 % 8));
+    uint4 a = *p1, bb = *p2;
+    __nv_bfloat162* aw = reinterpret_cast<__nv_bfloat162*>(&a);
+    __nv_bfloat162* bw = reinterpret_cast<__nv_bfloat162*>(&bb);
+    const __nv_bfloat162* cw = reinterpret_cast<const __nv_bfloat162*>(&r.c[c]);
+    const __nv_bfloat162* sw = reinterpret_cast<const __nv_bfloat162*>(&r.s[c]);
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const __nv_bfloat162 x1 = aw[j], x2 = bw[j];
-        // the _rn forms are never contracted into a fused multiply-add
-        aw[j] = __hsub2_rn(__hmul2_rn(x1, cw[j]), __hmul2_rn(x2, sw[j]));
-        bw[j] = __hadd2_rn(__hmul2_rn(x2, cw[j]), __hmul2_rn(x1, sw[j]));
-      }
-      *p1 = a;
-      *p2 = bb;
+    for (int j = 0; j < 4; ++j) {
+      const __nv_bfloat162 x1 = aw[j], x2 = bw[j];
+      // the _rn forms are never contracted into a fused multiply-add
+      aw[j] = __hsub2_rn(__hmul2_rn(x1, cw[j]), __hmul2_rn(x2, sw[j]));
+      bw[j] = __hadd2_rn(__hmul2_rn(x2, cw[j]), __hmul2_rn(x1, sw[j]));
     }
+    *p1 = a;
+    *p2 = bb;
   }
-  return ok;
 }
 
 // GT = the group size rounded up to a power of two: only GT of the 16 UMMA columns are read back,
@@ -342,18 +349,21 @@ __global__ void __launch_bounds__(128, 3) attn_decode_kernel(const __grid_consta
   // iteration: parity = iteration & 1.
   bool ok = true;
   uint32_t ph = 0;
+  RopeRow<kRotate ? D : 16> rope;  // (a one-piece dummy when K is stored rotated)
+  if constexpr (kRotate) load_rope_row<D>(rope, p, (c_lo + first) * kChunk, min(kChunk, L - (c_lo + first) * kChunk));
   for (int chunk = c_lo + first; chunk < n_chunks; chunk += stride, ph ^= 1) {
     const int tok0 = chunk * kChunk;
     const int valid = min(kChunk, L - tok0);
     const int next = chunk + stride;
 
     if constexpr (kRotate) {
-      if (chunk == c_lo + first) {  // later tiles are rotated at the end of the iteration before theirs
-        ok = rotate_k_tile<D>(sK, p, tok0, valid, bar_k, ph, abort_flag);
-        fence_proxy_async_smem();
-        ok = __syncthreads_and(ok);
-        if (!ok) break;
-      }
+      ok = mbar_wait(bar_k, ph, abort_flag, p.d_status, XAXB_DEVICE_TIMEOUT * 1000 + kSiteDecK);
+      if (ok) rotate_k_row<D>(sK, rope);
+      fence_proxy_async_smem();
+      ok = __syncthreads_and(ok);
+      if (!ok) break;
+      // the table rows of the next tile, requested a whole iteration before they are needed
+      if (next < n_chunks) load_rope_row<D>(rope, p, next * kChunk, min(kChunk, L - next * kChunk));
     }
 
     // ---- S^T = K Q^T ---------------------------------------------------------------------
@@ -441,18 +451,7 @@ __global__ void __launch_bounds__(128, 3) attn_decode_kernel(const __grid_consta
       for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
       if (lane == 0) red_sum[warp * kNPad + g] = s;
     }
-    if constexpr (kRotate) {
-      // The next K tile was requested as soon as S^T had consumed this one; it is rotated here, under
-      // the second MMA and the wait for it, so the next iteration finds it ready.
-      if (next < n_chunks) {
-        ok = rotate_k_tile<D>(sK, p, next * kChunk, min(kChunk, L - next * kChunk), bar_k, ph ^ 1, abort_flag);
-        fence_proxy_async_smem();
-      }
-      ok = __syncthreads_and(ok);
-      if (!ok) break;
-    } else {
-      __syncthreads();
-    }
+    __syncthreads();
     float wa[GT], wb[GT];  // weights of the running state and of this chunk in the merged state
 #pragma unroll
     for (int g = 0; g < GT; ++g) {

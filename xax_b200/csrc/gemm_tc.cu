@@ -14,6 +14,9 @@
 //             dequantisation multipliers, bias and residual, cast to bf16 and store; then
 //             hand the accumulator back ("acc_empty") so the next tile's main loop overlaps.
 // Tiles whose rows or columns run past M / N / K rely on TMA's zero fill; stores are guarded.
+#include <cstdio>
+#include <cstdlib>
+
 #include "common.cuh"
 
 namespace xaxb {
@@ -54,6 +57,7 @@ struct GemmParams {
   __nv_bfloat16* push_out[8];
   unsigned int* push_flag[8];
   int push_world;
+  int push_mode;  // experiment knob: 0 fence + releasing adds, 1 fence + relaxed adds, 2 releasing adds only
 };
 
 // Tile order: bands of kBand tile rows, column by column inside a band (row index fastest).  The
@@ -809,11 +813,15 @@ gemm_splitk_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
       const int rows_ok = max(0, min(p.M, row0 + rows_per) - row0);
       const int cols_ok = max(0, min(BN, p.N - n0));
       const unsigned int pieces = (unsigned int)(rows_ok * (cols_ok / 8));
-      __threadfence_system();
+      if (p.push_mode != 2) __threadfence_system();
 #pragma unroll
       for (int dst = 0; dst < 8; ++dst)
-        if (dst < p.push_world)
-          asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(p.push_flag[dst]), "r"(pieces) : "memory");
+        if (dst < p.push_world) {
+          if (p.push_mode == 1)
+            asm volatile("red.relaxed.sys.global.add.u32 [%0], %1;" ::"l"(p.push_flag[dst]), "r"(pieces) : "memory");
+          else
+            asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(p.push_flag[dst]), "r"(pieces) : "memory");
+        }
     }
   }
   __syncwarp();
@@ -993,6 +1001,8 @@ static int gemm_entry(xaxb_ctx* ctx_, void* stream, const void* a, int64_t lda, 
   p.prefetch_b = pdl_enabled() ? g_prefetch_mode : 0;
   p.prefetch_l2 = g_prefetch_l2;
   p.push_world = 0;
+  p.push_mode = 0;
+  if (const char* e = getenv("XAXB_PUSH_MODE")) p.push_mode = atoi(e);
   for (int r = 0; r < 8; ++r) p.push_out[r] = nullptr, p.push_flag[r] = nullptr;
   if (push) {
     p.push_world = push->world;
@@ -1006,6 +1016,12 @@ static int gemm_entry(xaxb_ctx* ctx_, void* stream, const void* a, int64_t lda, 
   if (const char* e = getenv("XAXB_GEMM_BAND")) p.band = atoi(e) > 0 ? atoi(e) : 32;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   GemmPlan plan = pick_plan(M, N, K, eb, ctx->num_sms, push != nullptr);
+  if (push) {
+    if (const char* e = getenv("XAXB_PUSH_PLAN")) {  // experiment knob: "bn,split"
+      int bn = 0, sp = 0;
+      if (sscanf(e, "%d,%d", &bn, &sp) == 2 && bn > 0 && sp > 0) plan.bn = bn, plan.split = sp;
+    }
+  }
   // Large problems go to the CTA-pair kernel: 256 x 256 tiles need a third less operand traffic
   // per SM, which is what bounds the single-CTA kernel.  It wants at least two waves of tiles.
   const bool pair_ok = M > kBM && N >= 256;

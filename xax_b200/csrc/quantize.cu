@@ -147,6 +147,36 @@ __global__ void __launch_bounds__(256) delayed_cast_kernel(const uint4* __restri
   }
 }
 
+// ---- dequantise (xax/nn/fp8.py:123-138): out = compute_dtype(q) / compute_dtype(scale), one scale per
+// row (stride 1) or one for the tensor (stride 0).  bf16: the quotient of the exact float32 images rounded to
+// bf16, which is what a bf16 division yields; float32: a float32 division.  8 values per thread.
+template <bool OUT_BF16>
+__global__ void __launch_bounds__(256) dequantize_kernel(const uint2* __restrict__ q, int64_t vec_per_row,
+                                                         int64_t n_vec, const float* __restrict__ scale,
+                                                         int scale_stride, void* __restrict__ out) {
+  pdl_trigger();
+  pdl_wait();
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n_vec; i += (int64_t)gridDim.x * blockDim.x) {
+    const float s_raw = scale[(i / vec_per_row) * scale_stride];
+    const float s = OUT_BF16 ? bf16_round(s_raw) : s_raw;
+    const uint2 v = __ldg(q + i);
+    const uint32_t w[2] = {v.x, v.y};
+    float f[8];
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      const __nv_fp8_storage_t byte = (__nv_fp8_storage_t)((w[k >> 2] >> ((k & 3) * 8)) & 0xFFu);
+      const __half_raw h = __nv_cvt_fp8_to_halfraw(byte, __NV_E4M3);  // exact: every e4m3 value is a half
+      f[k] = __half2float(__half(h)) / s;
+    }
+    if (OUT_BF16) {
+      reinterpret_cast<uint4*>(out)[i] = pack8(f);
+    } else {
+      reinterpret_cast<float4*>(out)[2 * i] = make_float4(f[0], f[1], f[2], f[3]);
+      reinterpret_cast<float4*>(out)[2 * i + 1] = make_float4(f[4], f[5], f[6], f[7]);
+    }
+  }
+}
+
 static int grid_for(int64_t n_vec, int num_sms, int64_t cap_per_group = 0) {
   int64_t blocks = (n_vec + 255) / 256;
   int64_t limit = cap_per_group > 0 ? cap_per_group : (int64_t)num_sms * 8;
@@ -251,6 +281,28 @@ int xaxb_quantize_with_amax(xaxb_ctx* ctx, void* stream, const void* x_bf16, int
   launch_kernel(group_cast_kernel, grid, dim3(256), 0, s, 1, static_cast<const uint4*>(x_bf16), vec_per_group, group_rows, group_amax,
                                          static_cast<uint2*>(q_e4m3), scale, inv_scale);
   return check_launch("group_cast_kernel");
+}
+
+int xaxb_dequantize(xaxb_ctx* ctx, void* stream, const void* q_e4m3, int64_t rows, int64_t cols, const float* scale,
+                    int scale_stride, int out_is_bf16, void* out) {
+  if (!ctx || !q_e4m3 || !scale || !out || rows <= 0 || cols <= 0 || cols % 8 != 0 ||
+      (scale_stride != 0 && scale_stride != 1) || (reinterpret_cast<uintptr_t>(q_e4m3) & 7) ||
+      (reinterpret_cast<uintptr_t>(out) & 15)) {
+    set_last_error("dequantize: null pointer, cols (%lld) not a multiple of 8, scale stride not 0 / 1, or misaligned "
+                   "pointer", (long long)cols);
+    return XAXB_BAD_ARGUMENT;
+  }
+  const Ctx* c = reinterpret_cast<const Ctx*>(ctx);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const int64_t n_vec = rows * cols / 8;
+  const dim3 grid(grid_for(n_vec, c->num_sms));
+  if (out_is_bf16)
+    launch_kernel(dequantize_kernel<true>, grid, dim3(256), 0, s, 1, static_cast<const uint2*>(q_e4m3), cols / 8, n_vec,
+                  scale, scale_stride, out);
+  else
+    launch_kernel(dequantize_kernel<false>, grid, dim3(256), 0, s, 1, static_cast<const uint2*>(q_e4m3), cols / 8, n_vec,
+                  scale, scale_stride, out);
+  return check_launch("dequantize_kernel");
 }
 
 int xaxb_quantize_delayed(xaxb_ctx* ctx, void* stream, const void* x_bf16, int64_t rows, int64_t cols,

@@ -107,9 +107,20 @@ def quantize(x: torch.Tensor, fp8_dtype: torch.dtype, scale: torch.Tensor,
 
 
 def dequantize(x: torch.Tensor, compute_dtype: torch.dtype, scale: torch.Tensor) -> torch.Tensor:
-    """xax/nn/fp8.py:123-138.  Kept for API completeness; the linear layer never materialises
-    the dequantised tensor."""
-    return (x.to(compute_dtype) / torch.as_tensor(scale, device=x.device).to(compute_dtype)).to(compute_dtype)
+    """xax/nn/fp8.py:123-138 for a scalar scale: compute_dtype(x) / compute_dtype(scale).  The linear layer
+    never materialises the dequantised tensor; this is the free function."""
+    if x.dtype != torch.float8_e4m3fn:
+        _only_e4m3(x.dtype)
+    shape = x.shape
+    x2 = x.reshape(-1, shape[-1]) if x.dim() > 1 else x.reshape(1, -1)
+    cols = x2.shape[-1]
+    pad = (-cols) % 8
+    if pad:
+        x2 = torch.nn.functional.pad(x2.view(torch.uint8), (0, pad)).view(torch.float8_e4m3fn)
+    s = torch.as_tensor(scale, dtype=torch.float32, device=x.device).reshape(-1)
+    if s.numel() != 1:
+        raise ValueError("dequantize: the kernel path takes a scalar scale")
+    return ops.dequantize(x2.contiguous(), s, compute_dtype)[:, :cols].reshape(shape)
 
 
 def quantize_dequantize(x, fp8_dtype, scale, compute_dtype=torch.float32):

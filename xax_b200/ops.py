@@ -63,6 +63,22 @@ def quantize_with_amax(x: torch.Tensor, group_amax: torch.Tensor, group_rows: in
     return q, scale, inv
 
 
+def dequantize(q: torch.Tensor, scale: torch.Tensor, out_dtype=BF16) -> torch.Tensor:
+    """q e4m3 [rows, cols] / scale (one float32 value, or one per row) -> bf16 or float32 [rows, cols]."""
+    q = _req(q, E4M3, "q")
+    scale = _req(scale, torch.float32, "scale").reshape(-1)
+    rows, cols = q.shape
+    if scale.numel() not in (1, rows):
+        raise ValueError(f"dequantize: scale has {scale.numel()} elements, expected 1 or {rows}")
+    if out_dtype not in (BF16, torch.float32):
+        raise ValueError("dequantize: output must be bfloat16 or float32")
+    ctx, st, lib = _c()
+    out = torch.empty((rows, cols), dtype=out_dtype, device=q.device)
+    check(lib.xaxb_dequantize(ctx, st, ptr(q), rows, cols, ptr(scale), 0 if scale.numel() == 1 else 1,
+                              1 if out_dtype == BF16 else 0, ptr(out)), "dequantize")
+    return out
+
+
 _DELAYED_SCRATCH: dict = {}
 
 
