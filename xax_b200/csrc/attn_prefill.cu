@@ -2,12 +2,14 @@
 // pass, float32 online softmax), on tcgen05 tensor cores.
 //
 // One CTA = 128 consecutive queries of one (sequence, query head); 128 threads, thread r owns
-// query row r.  For every 128-token tile of the cache up to the diagonal:
-//   S  = Q K^T      UMMA M = 128 queries, N = 128 tokens, K = D      (A = Q, B = K tile; K-major)
+// query row r.  Two CTAs share an SM (112 KB of shared memory and 256 TMEM columns each), so one CTA's
+// tensor-core work runs under the other's softmax.  For every 64-token tile of the cache up to the
+// diagonal:
+//   S  = Q K^T      UMMA M = 128 queries, N = 64 tokens, K = D       (A = Q, B = K tile; K-major)
 //   thread r reads row r of S from TMEM, applies the causal mask and the online-softmax
 //   update, writes bf16 probabilities to shared memory (the reference also rounds the
 //   probabilities to the value dtype before P.V),
-//   PV = P V        UMMA M = 128 queries, N = D, K = 128 tokens      (A = P K-major, B = V tile
+//   PV = P V        UMMA M = 128 queries, N = D, K = 64 tokens       (A = P K-major, B = V tile
 //                                                                     MN-major: D contiguous)
 //   thread r reads row r of PV and folds it into its float32 output row: o = o * alpha + PV.
 // K / V tiles arrive by TMA (128-byte swizzle) into a two-stage ring, so the next tile loads
@@ -17,7 +19,8 @@
 
 namespace xaxb {
 
-constexpr int kPfTile = 128;
+constexpr int kPfTile = 128;  // queries per CTA
+constexpr int kPfKeys = 64;   // cache rows per K / V tile
 constexpr int kSitePfKV = 21, kSitePfS = 22, kSitePfO = 23;
 
 struct PrefillParams {
@@ -32,16 +35,17 @@ struct PrefillParams {
 
 template <int D>
 struct PrefillSmem {
-  static constexpr int kHalfBytes = kPfTile * 128;          // 128 rows x 128 B
+  static constexpr int kHalfBytes = kPfTile * 128;          // Q: 128 rows x 128 B per 64-element box
+  static constexpr int kKVHalfBytes = kPfKeys * 128;        // K / V: 64 rows x 128 B per box
   static constexpr int kQBytes = kPfTile * D * 2;
-  static constexpr int kKVBytes = kPfTile * D * 2;          // one K or one V tile
-  static constexpr int kPBytes = kPfTile * kPfTile * 2;
-  static constexpr int kBytes = kQBytes + 4 * kKVBytes + kPBytes + 1024 + 256;
-  static constexpr int kTmemCols = 256;
+  static constexpr int kKVBytes = kPfKeys * D * 2;          // one K or one V tile
+  static constexpr int kPBytes = kPfTile * kPfKeys * 2;     // 128 rows x 128 B
+  static constexpr int kBytes = kQBytes + 4 * kKVBytes + kPBytes + 256;  // the dynamic array is 1024-aligned
+  static constexpr int kTmemCols = 256;                     // S: 64 columns, PV: D columns
 };
 
 template <int D>
-__global__ void __launch_bounds__(128, 1) attn_prefill_kernel(const __grid_constant__ CUtensorMap tmap_k,
+__global__ void __launch_bounds__(128, 2) attn_prefill_kernel(const __grid_constant__ CUtensorMap tmap_k,
                                                               const __grid_constant__ CUtensorMap tmap_v,
                                                               const PrefillParams p) {
   pdl_wait();  // nothing below may run ahead of the previous kernel in the stream
@@ -55,12 +59,11 @@ __global__ void __launch_bounds__(128, 1) attn_prefill_kernel(const __grid_const
   const int last_pos = start + q0 + rows_valid - 1;  // highest key position any row may see
   const int win = p.window;
   // with a sliding window the tiles below the first row's window are never loaded
-  const int j_lo = win >= 0 ? max(0, start + q0 - win) / kPfTile : 0;
-  const int n_tiles = last_pos / kPfTile + 1 - j_lo;  // tiles j_lo .. j_lo + n_tiles - 1
+  const int j_lo = win >= 0 ? max(0, start + q0 - win) / kPfKeys : 0;
+  const int n_tiles = last_pos / kPfKeys + 1 - j_lo;  // tiles j_lo .. j_lo + n_tiles - 1
   const int total_len = start + p.T;              // rows of the cache holding this sequence
 
-  extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  extern __shared__ __align__(1024) uint8_t smem[];  // swizzled tiles need 1024-byte alignment
   uint8_t* sQ = smem;
   uint8_t* sKV = sQ + SM::kQBytes;                // stage s: K at s*2*kKVBytes, V right after
   uint8_t* sP = sKV + 4 * SM::kKVBytes;
@@ -80,8 +83,8 @@ __global__ void __launch_bounds__(128, 1) attn_prefill_kernel(const __grid_const
     mbar_arrive_expect_tx(bar_kv + s, 2 * SM::kKVBytes);
 #pragma unroll
     for (int x = 0; x < kBoxes; ++x) {
-      tma_load_4d(k_dst + x * SM::kHalfBytes, &tmap_k, bar_kv + s, x * 64, hk, (j_lo + j) * kPfTile, b);
-      tma_load_4d(v_dst + x * SM::kHalfBytes, &tmap_v, bar_kv + s, x * 64, hk, (j_lo + j) * kPfTile, b);
+      tma_load_4d(k_dst + x * SM::kKVHalfBytes, &tmap_k, bar_kv + s, x * 64, hk, (j_lo + j) * kPfKeys, b);
+      tma_load_4d(v_dst + x * SM::kKVHalfBytes, &tmap_v, bar_kv + s, x * 64, hk, (j_lo + j) * kPfKeys, b);
     }
   };
 
@@ -116,8 +119,8 @@ __global__ void __launch_bounds__(128, 1) attn_prefill_kernel(const __grid_const
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
   pdl_trigger();  // tensor memory is allocated: the next kernel may be scheduled
-  const uint32_t tmem_s = tmem_base;          // columns [0, 128)
-  const uint32_t tmem_pv = tmem_base + 128;   // columns [128, 128 + D)
+  const uint32_t tmem_s = tmem_base;          // columns [0, 64)
+  const uint32_t tmem_pv = tmem_base + 64;    // columns [64, 64 + D)
   const uint32_t lane_off = uint32_t(warp * 32) << 16;
 
   float o[D];
@@ -135,20 +138,20 @@ __global__ void __launch_bounds__(128, 1) attn_prefill_kernel(const __grid_const
     ok = ok && mbar_wait(bar_kv + s, (j >> 1) & 1, abort_flag, p.d_status, XAXB_DEVICE_TIMEOUT * 1000 + kSitePfKV);
     // rows of the tile past the sequence's last cached token may hold anything; the mask
     // zeroes their probabilities, and V is cleared so that 0 * garbage stays 0
-    if (ok && (j_lo + j) * kPfTile + tid >= total_len) {
+    if (ok && tid < kPfKeys && (j_lo + j) * kPfKeys + tid >= total_len) {
 #pragma unroll
       for (int c = 0; c < D / 8; ++c)
-        *reinterpret_cast<uint4*>(sV + (c / 8) * SM::kHalfBytes + sw128_offset(tid, c % 8)) = make_uint4(0, 0, 0, 0);
+        *reinterpret_cast<uint4*>(sV + (c / 8) * SM::kKVHalfBytes + sw128_offset(tid, c % 8)) = make_uint4(0, 0, 0, 0);
       fence_proxy_async_smem();
     }
     if (tid == 0 && ok) {
       tc_fence_after_sync();
-      constexpr uint32_t idesc = umma_idesc(kFmtBF16, kFmtBF16, 0, 0, 128, kPfTile);
+      constexpr uint32_t idesc = umma_idesc(kFmtBF16, kFmtBF16, 0, 0, 128, kPfKeys);
 #pragma unroll
       for (int k = 0; k < D / 16; ++k) {
         const uint32_t box = k / 4, off = (k % 4) * 32;
         umma_f16(tmem_s, umma_desc_kmajor_sw128(smem_u32(sQ + box * SM::kHalfBytes) + off),
-                 umma_desc_kmajor_sw128(smem_u32(sK + box * SM::kHalfBytes) + off), idesc, k != 0);
+                 umma_desc_kmajor_sw128(smem_u32(sK + box * SM::kKVHalfBytes) + off), idesc, k != 0);
       }
       umma_commit(bar_s);
     }
@@ -158,13 +161,13 @@ __global__ void __launch_bounds__(128, 1) attn_prefill_kernel(const __grid_const
     tc_fence_after_sync();
 
     // ---- online softmax on row `tid` of S (two sweeps over TMEM: max, then exp) ------------
-    const int kv0 = (j_lo + j) * kPfTile;
+    const int kv0 = (j_lo + j) * kPfKeys;
     // some (row, col) of this tile is masked: above the diagonal, or below some row's window
-    const bool diag = kv0 + kPfTile - 1 > start + q0 || (win >= 0 && kv0 < last_pos - win);
+    const bool diag = kv0 + kPfKeys - 1 > start + q0 || (win >= 0 && kv0 < last_pos - win);
     const int lo_vis = win >= 0 ? qpos - win : 0;  // lowest key position this row sees
     float m_tile = -INFINITY;
 #pragma unroll 1
-    for (int c0 = 0; c0 < kPfTile; c0 += 32) {
+    for (int c0 = 0; c0 < kPfKeys; c0 += 32) {
       uint32_t r[32];
       tmem_ld_x32(tmem_s + lane_off + c0, r);
       tmem_ld_wait();
@@ -181,7 +184,7 @@ __global__ void __launch_bounds__(128, 1) attn_prefill_kernel(const __grid_const
     const float alpha = exp2f(m_run - m_new);
     float l_tile = 0.0f;
 #pragma unroll 1
-    for (int c0 = 0; c0 < kPfTile; c0 += 32) {
+    for (int c0 = 0; c0 < kPfKeys; c0 += 32) {
       uint32_t r[32];
       tmem_ld_x32(tmem_s + lane_off + c0, r);
       tmem_ld_wait();
@@ -199,11 +202,11 @@ __global__ void __launch_bounds__(128, 1) attn_prefill_kernel(const __grid_const
         const uint32_t hi = __bfloat16_as_ushort(__float2bfloat16_rn(e1));
         packed[i / 2] = lo | (hi << 16);
       }
-      // 32 tokens = 4 chunks of 16 bytes in box c0 / 64
+      // 32 tokens = 4 chunks of 16 bytes of the row's single 128-byte span
 #pragma unroll
       for (int cc = 0; cc < 4; ++cc) {
-        const int chunk = (c0 % 64) / 8 + cc;
-        *reinterpret_cast<uint4*>(sP + (c0 / 64) * SM::kHalfBytes + sw128_offset(tid, chunk)) =
+        const int chunk = c0 / 8 + cc;
+        *reinterpret_cast<uint4*>(sP + sw128_offset(tid, chunk)) =
             make_uint4(packed[cc * 4], packed[cc * 4 + 1], packed[cc * 4 + 2], packed[cc * 4 + 3]);
       }
     }
@@ -218,9 +221,9 @@ __global__ void __launch_bounds__(128, 1) attn_prefill_kernel(const __grid_const
       tc_fence_after_sync();
       constexpr uint32_t idesc = umma_idesc(kFmtBF16, kFmtBF16, 0, 1, 128, D);
 #pragma unroll
-      for (int k = 0; k < kPfTile / 16; ++k) {
-        umma_f16(tmem_pv, umma_desc_kmajor_sw128(smem_u32(sP + (k / 4) * SM::kHalfBytes) + (k % 4) * 32),
-                 umma_desc_mnmajor_sw128(smem_u32(sV) + k * 16 * 128, SM::kHalfBytes), idesc, k != 0);
+      for (int k = 0; k < kPfKeys / 16; ++k) {
+        umma_f16(tmem_pv, umma_desc_kmajor_sw128(smem_u32(sP) + k * 32),
+                 umma_desc_mnmajor_sw128(smem_u32(sV) + k * 16 * 128, SM::kKVHalfBytes), idesc, k != 0);
       }
       umma_commit(bar_o);
     }
@@ -268,7 +271,7 @@ static int make_cache_tmap_pf(const Ctx* ctx, CUtensorMap* map, const void* cach
                               int64_t Hkv, int64_t D) {
   const uint64_t dims[4] = {(uint64_t)D, (uint64_t)Hkv, (uint64_t)max_len, (uint64_t)B};
   const uint64_t strides[3] = {(uint64_t)D * 2, (uint64_t)Hkv * D * 2, (uint64_t)max_len * Hkv * D * 2};
-  const uint32_t box[4] = {64, 1, (uint32_t)kPfTile, 1};
+  const uint32_t box[4] = {64, 1, (uint32_t)kPfKeys, 1};
   return make_tmap_4d(ctx, map, cache, 2, dims, strides, box);
 }
 

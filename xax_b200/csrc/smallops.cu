@@ -77,7 +77,7 @@ __device__ __forceinline__ void silu_mul8(const uint4 gv, const uint4 uv, float 
   }
 }
 
-__global__ void __launch_bounds__(256) silu_mul_kernel(const uint4* __restrict__ gate, const uint4* __restrict__ up,
+__global__ void __launch_bounds__(1024) silu_mul_kernel(const uint4* __restrict__ gate, const uint4* __restrict__ up,
                                                        int64_t ld_vec, int64_t vec, uint4* __restrict__ h,
                                                        uint2* __restrict__ q, float* __restrict__ scale,
                                                        float* __restrict__ inv_scale,
@@ -681,7 +681,12 @@ int xaxb_silu_mul_cast_tp(xaxb_ctx* ctx, void* stream, const void* gate_bf16, co
     return XAXB_BAD_ARGUMENT;
   }
   const int64_t vec = dim / 8;
-  launch_kernel(silu_mul_kernel, dim3((unsigned)rows), dim3(256), 0, static_cast<cudaStream_t>(stream), 1, 
+  // one CTA per token row (the row's amax is exchanged by the CTA as a whole); with at most 1024 rows a CTA
+  // is alone on its SM or nearly so, and what bounds it is each thread's own instruction stream: one 16-byte
+  // piece per thread where the row allows
+  int threads = (int)((vec + 31) / 32 * 32);
+  threads = threads < 256 ? 256 : (threads > 1024 ? 1024 : threads);
+  launch_kernel(silu_mul_kernel, dim3((unsigned)rows), dim3((unsigned)threads), 0, static_cast<cudaStream_t>(stream), 1,
       gate, up, ld / 8, vec, nullptr, static_cast<uint2*>(q_e4m3), scale, inv_scale, nullptr, 1, tp,
       reinterpret_cast<Ctx*>(ctx)->d_status);
   return check_launch("silu_mul_kernel (tensor-parallel)");
