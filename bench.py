@@ -203,9 +203,14 @@ def _kernel_group(group: str, peak_gbs: float, flush) -> dict:
 
     dev = "cuda"
     out = {}
-    if group not in ("quantize", "gemm", "attn_decode"):
-        raise SystemExit(f"unknown kernel group {group!r}: quantize, gemm, attn_decode or block_prefill")
+    if group not in ("quantize", "gemm", "attn_decode", "attn_decode_small", "gemm_8192_1cta"):
+        raise SystemExit(f"unknown kernel group {group!r}: quantize, gemm, attn_decode, block_prefill, or the small "
+                         "cases for profiler captures attn_decode_small, gemm_8192_1cta")
     g = torch.Generator(device=dev).manual_seed(0)
+    if group == "attn_decode_small":
+        return _attn_decode_small(g, peak_gbs, flush)
+    if group == "gemm_8192_1cta":
+        return _gemm_8192_single_cta(g, flush)
     # ---- cfg1: x[2048,2048] bf16 N(0,1) with 0.1 % x20 outliers, W (8192,2048) N(0,0.02^2)
     M, K, N = 2048, 2048, 8192
     x = torch.randn((M, K), generator=g, device=dev)
@@ -311,6 +316,47 @@ def _attn_decode_figures(g, peak_gbs, flush) -> dict:
     return out
 
 
+def _attn_decode_small(g, peak_gbs, flush) -> dict:
+    """Decode attention on a case small enough for a many-pass profiler capture and larger than L2:
+    B = 32 sequences of 2053 tokens, 32 query / 8 kv heads x 128 (0.27 GB of K and V)."""
+    import torch
+
+    from xax_b200 import ops
+
+    B, Hq, Hkv, D, L = 32, 32, 8, 128, 2053
+    max_len = 2304
+    kc = torch.randn((B, max_len, Hkv, D), generator=g, device="cuda", dtype=torch.bfloat16)
+    vc = torch.randn((B, max_len, Hkv, D), generator=g, device="cuda", dtype=torch.bfloat16)
+    q = torch.randn((B, Hq, D), generator=g, device="cuda", dtype=torch.bfloat16)
+    pos = torch.full((B,), L - 1, dtype=torch.int32, device="cuda")
+    ws = ops.attn_decode_workspace(B, Hq, D, max_len, "cuda")
+    ao = torch.empty_like(q)
+    nbytes = B * L * (2 * Hkv * D * 2) + 2 * B * Hq * D * 2
+    t = _time_kernel(lambda i: ops.attn_decode(q, kc, vc, pos, workspace=ws, out=ao), iters=5, warm=1, flush=flush)
+    return {"attn_decode_small": {"gbs": nbytes / t / 1e9, "frac_of_hbm_peak": nbytes / t / 1e9 / peak_gbs,
+                                  "us": t * 1e6, "bytes": nbytes}}
+
+
+def _gemm_8192_single_cta(g, flush) -> dict:
+    """FP8 GEMM 8192^3 forced onto the single-CTA kernel with 256-wide tiles (the library itself picks the
+    CTA-pair kernel at this size): the case the profiler summary of that kernel was captured on."""
+    import torch
+
+    from xax_b200 import _lib, ops
+
+    n = 8192
+    a8 = torch.randn((n, n), generator=g, device="cuda").to(torch.float8_e4m3fn)
+    b8 = torch.randn((n, n), generator=g, device="cuda").to(torch.float8_e4m3fn)
+    o = torch.empty((n, n), dtype=torch.bfloat16, device="cuda")
+    lib = _lib.load()
+    lib.xaxb_gemm_force_plan(256, 0)
+    try:
+        t = _time_kernel(lambda i: ops.gemm_fp8(a8, b8, None, None, None, out=o), iters=5, warm=1, flush=flush)
+    finally:
+        lib.xaxb_gemm_force_plan(0, 0)
+    return {"gemm_fp8_8192_single_cta": {"tflops": 2.0 * n ** 3 / t / 1e12, "us": t * 1e6}}
+
+
 def block_prefill_figure(flush) -> dict:
     """cfg2: one pre-norm block, prefill of 4 sequences x 1024 tokens (hidden 2048, 16 query / 4 kv heads
     x 128, SwiGLU 5632, FP8 linears for QKV / out / MLP), captured in a CUDA graph so the figure is device
@@ -353,8 +399,9 @@ def main() -> None:
     ap.add_argument("--workload", default="cfg5", choices=sorted(WORKLOADS))
     ap.add_argument("--no-kernels", action="store_true", help="skip the per-kernel figures")
     ap.add_argument("--kernels-only", default=None, metavar="GROUP",
-                    help="only the per-kernel figures of one group (quantize, gemm, attn_decode, block_prefill, or "
-                         "'all'); prints {\"kernels\": ...} -- the command profiler captures of one kernel run")
+                    help="only the per-kernel figures of one group (quantize, gemm, attn_decode, block_prefill, "
+                         "'all', or the small profiler cases attn_decode_small / gemm_8192_1cta); prints "
+                         "{\"kernels\": ...} -- the command profiler captures of one kernel run")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU oracle timing")
     ap.add_argument("--synthetic-kv", action="store_true", help="fill the KV cache with N(0,1) instead of a prefill")
     args = ap.parse_args()

@@ -143,14 +143,13 @@ int xaxb_gemm_bf16(xaxb_ctx* ctx, void* stream, const void* a_bf16, int64_t lda,
  * in the reference. */
 int xaxb_gemm_force_plan(int bn, int split);
 
-/* What a GEMM launched with programmatic dependent launch fetches of operand b (the weights: constant
- * while a model runs) before it waits for the previous kernel of the stream: mode 0 nothing, 1 a hint
- * to L2 for the first `l2_blocks` 128-byte K blocks of each CTA's first tile, 2 the b half of as many
- * K blocks as the shared-memory ring holds, plus the L2 hint for `l2_blocks` more.  Operand a and
- * everything else is touched only after the wait, so results do not depend on the setting; b must not
- * be written by the kernel that precedes the GEMM in its stream.  Process-wide.  No counterpart in
- * the reference. */
-int xaxb_gemm_set_prefetch(int mode, int l2_blocks);
+/* Requests to L2 for operand b (the weights: constant while a model runs) that carry no data to the SM:
+ * a GEMM launched with programmatic dependent launch asks for the first `blocks_before_wait` 128-byte K
+ * blocks of each CTA's first tile before it waits for the previous kernel of the stream (default 4; 0 =
+ * nothing ahead of the wait).  Operand a and everything else is touched only after the wait, so results
+ * do not depend on the setting; b must not be written by the kernel that precedes the GEMM in its
+ * stream.  Process-wide.  No counterpart in the reference. */
+int xaxb_gemm_set_prefetch(int blocks_before_wait);
 
 /* Plain CUDA-core GEMM with the same contract as xaxb_gemm_fp8 (one thread per output,
  * float32 accumulation in k order).  A second opinion for the tensor-core kernel in tests;

@@ -200,49 +200,61 @@ __device__ __forceinline__ float warp_max_f32(float v) {
   return r;
 }
 
-// Rotate-on-load.  Thread `tid` owns row `tid` of every K tile of its CTA.  The row's cos / sin values
-// (D/2 of each, from the table row of the token's position) are fetched into registers one tile ahead --
-// right after the previous tile was rotated -- so that they have arrived by the time the K tile lands;
-// the rotation itself then only touches shared memory.  It is packed bf16 arithmetic: every product
-// and every sum rounds to bf16 on its own, which is exactly the reference's bf16 op sequence
-// (xax/arch/attention.py:510-515), six instructions per two pairs.  Pair (i, i + D/2) lives in 16-byte
-// piece i/8 of box (i / 64) and piece (i + D/2)/8 of the other half of the row.
+// Rotate-on-load.  A warp owns 32 rows of every K tile of its CTA and walks them a few rows at a time:
+// D/16 neighbouring lanes share a row, lane l taking 16-byte piece l % (D/16) of the row's first half and
+// the piece it pairs with in the second half, so that one warp-wide load of cos (or sin) values reads whole,
+// consecutive table rows -- every byte the memory system moves is used; with a thread per row each load
+// touched 32 different rows and half of every sector fetched was thrown away.  The table values
+// are fetched into registers one tile ahead -- right after the previous tile was rotated -- so that they
+// have arrived by the time the K tile lands; the rotation itself then only touches shared memory.
+// It is packed bf16 arithmetic: every product and every sum rounds to bf16 on its own, which is exactly
+// the reference's bf16 op sequence (xax/arch/attention.py:510-515), six instructions per two pairs.
+// Pair (i, i + D/2) lives in 16-byte piece i/8 of box (i / 64) and piece (i + D/2)/8 of the row.
 template <int D>
 struct RopeRow {
-  static constexpr int kPieces = D / 16;
-  uint4 c[kPieces], s[kPieces];
-  bool ok;
+  static constexpr int kPieces = D / 16;           // 16-byte pieces of a table row = lanes per K row
+  static constexpr int kRowsPerStep = 32 / kPieces;
+  static constexpr int kSteps = 32 / kRowsPerStep;  // (= kPieces)
+  uint4 c[kSteps], s[kSteps];
+  int rows;  // rows of the tile that have a token and a table row
 };
 
 template <int D>
 __device__ __forceinline__ void load_rope_row(RopeRow<D>& r, const DecodeParams& p, int tok0, int valid) {
+  using R = RopeRow<D>;
   constexpr int half = D / 2;
-  const long long pos = tok0 + (int)threadIdx.x;
-  r.ok = (int)threadIdx.x < valid && pos < p.table_len;
-  if (r.ok) {
-    const uint4* cr = reinterpret_cast<const uint4*>(p.cos_t + pos * half);
-    const uint4* sr = reinterpret_cast<const uint4*>(p.sin_t + pos * half);
+  const long long in_table = p.table_len - tok0;
+  r.rows = (int)max(0LL, min((long long)valid, in_table));
+  const int lane = threadIdx.x & 31, piece = lane % R::kPieces;
+  const int row0 = (threadIdx.x & ~31) + lane / R::kPieces;
 #pragma unroll
-    for (int i = 0; i < RopeRow<D>::kPieces; ++i) r.c[i] = __ldg(cr + i), r.s[i] = __ldg(sr + i);
+  for (int i = 0; i < R::kSteps; ++i) {
+    const int row = row0 + i * R::kRowsPerStep;
+    if (row < r.rows) {
+      const long long pos = tok0 + row;
+      r.c[i] = __ldg(reinterpret_cast<const uint4*>(p.cos_t + pos * half) + piece);
+      r.s[i] = __ldg(reinterpret_cast<const uint4*>(p.sin_t + pos * half) + piece);
+    }
   }
 }
 
 template <int D>
 __device__ __forceinline__ void rotate_k_row(uint8_t* sK, const RopeRow<D>& r) {
   using SM = DecodeSmem<D>;
-  constexpr int kPieces = RopeRow<D>::kPieces;
-  const int tid = threadIdx.x;
-  if (!r.ok) return;
+  using R = RopeRow<D>;
+  const int lane = threadIdx.x & 31, piece = lane % R::kPieces, piece2 = piece + R::kPieces;
+  const int row0 = (threadIdx.x & ~31) + lane / R::kPieces;
 #pragma unroll
-  for (int c = 0; c < kPieces; ++c) {
-    const int c2 = c + kPieces;
-    uint4* p1 = reinterpret_cast<uint4*>(sK + (c / 8) * SM::kHalfBytes + sw128_offset(tid, c % 8));
-    uint4* p2 = reinterpret_cast<uint4*>(sK + (c2 / 8) * SM::kHalfBytes + sw128_offset(tid, c2 % 8));
+  for (int i = 0; i < R::kSteps; ++i) {
+    const int row = row0 + i * R::kRowsPerStep;
+    if (row >= r.rows) break;
+    uint4* p1 = reinterpret_cast<uint4*>(sK + (piece / 8) * SM::kHalfBytes + sw128_offset(row, piece % 8));
+    uint4* p2 = reinterpret_cast<uint4*>(sK + (piece2 / 8) * SM::kHalfBytes + sw128_offset(row, piece2 % 8));
     uint4 a = *p1, bb = *p2;
     __nv_bfloat162* aw = reinterpret_cast<__nv_bfloat162*>(&a);
     __nv_bfloat162* bw = reinterpret_cast<__nv_bfloat162*>(&bb);
-    const __nv_bfloat162* cw = reinterpret_cast<const __nv_bfloat162*>(&r.c[c]);
-    const __nv_bfloat162* sw = reinterpret_cast<const __nv_bfloat162*>(&r.s[c]);
+    const __nv_bfloat162* cw = reinterpret_cast<const __nv_bfloat162*>(&r.c[i]);
+    const __nv_bfloat162* sw = reinterpret_cast<const __nv_bfloat162*>(&r.s[i]);
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
       const __nv_bfloat162 x1 = aw[j], x2 = bw[j];

@@ -43,11 +43,10 @@ struct GemmParams {
   // The launch may overlap the previous kernel (programmatic dependent launch).  Operand B -- the
   // weights of a linear layer -- is never written by a kernel of the same stream section, so the
   // producer may fetch it before it waits for the previous kernel:
-  //   0  nothing ahead of the wait;
-  //   1  ask L2 for the first `prefetch_l2` K blocks of B;
-  //   2  load B of the first K blocks into the shared-memory ring (all stages), and ask L2 for
-  //      `prefetch_l2` blocks beyond the ring; A follows after the wait.
-  int prefetch_b;
+  // it asks L2 for the first `prefetch_l2` K blocks of B there (0: nothing ahead of the wait).
+  // (Requests further ahead than that do not pay: an SM keeps about 42 KB in flight whatever the
+  // depth of its shared-memory ring, and a request to L2 occupies that budget like a load does --
+  // asking 8 to 64 blocks ahead while streaming made every decode shape 3 to 50 % slower.)
   int prefetch_l2;
   int band;        // tile rows per band of the tile order (see tile_coords)
   // Tensor-parallel push (split-K kernel only): with push_world > 0 the epilogue writes every 16-byte
@@ -57,7 +56,6 @@ struct GemmParams {
   __nv_bfloat16* push_out[8];
   unsigned int* push_flag[8];
   int push_world;
-  int push_mode;  // experiment knob: 0 fence + releasing adds, 1 fence + relaxed adds, 2 releasing adds only
 };
 
 // Tile order: bands of kBand tile rows, column by column inside a band (row index fastest).  The
@@ -190,20 +188,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       // While the previous kernel is still running, bring in operand B of this CTA's first tile
       // (the weights: what a decode-sized GEMM streams from HBM).  L2 is the point of coherence and
       // nothing in flight writes B, so this is safe whatever precedes the kernel.
-      int pre = 0;  // K blocks of the first tile whose B half is already on its way into the ring
-      if (p.prefetch_b && (int)blockIdx.x < num_tiles) {
+      if (p.prefetch_l2 && (int)blockIdx.x < num_tiles) {
         int tm, tn;
         tile_coords(p.band, (int)blockIdx.x, p.tiles_m, p.tiles_n, tm, tn);
         int kk = (int)(((long long)blockIdx.x * 5) % p.num_k_blocks);
-        if (p.prefetch_b == 2) {
-          pre = p.num_k_blocks < kStages ? p.num_k_blocks : kStages;
-          for (int i = 0; i < pre; ++i) {
-            mbar_arrive_expect_tx(full + i, Cfg::kStageBytes);
-            tma_load_2d(smem_b + i * BN * kBKBytes, &tmap_b, full + i, kk * kBKElems, tn * BN);
-            if (++kk == p.num_k_blocks) kk = 0;
-          }
-        }
-        const int n_l2 = min(p.num_k_blocks - pre, p.prefetch_l2);
+        const int n_l2 = min(p.num_k_blocks, p.prefetch_l2);
         for (int i = 0; i < n_l2; ++i) {
           tma_prefetch_l2_2d(&tmap_b, kk * kBKElems, tn * BN);
           if (++kk == p.num_k_blocks) kk = 0;
@@ -218,19 +207,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         // N tiles read the same rows of A) then ask L2 for different lines at any moment.
         int kk = (int)(((long long)tile * 5) % p.num_k_blocks);
         for (int kb = 0; kb < p.num_k_blocks; ++kb) {
-          if (kb < pre) {  // first tile only: the stage is armed and its B half requested already
-            tma_load_2d(smem_a + stage * kBM * kBKBytes, &tmap_a, full + stage, kk * kBKElems, m0);
-          } else {
-            ok = mbar_wait(empty + stage, phase ^ 1, abort_flag, p.d_status, XAXB_DEVICE_TIMEOUT * 1000 + kSiteProducer);
-            if (!ok) break;
-            mbar_arrive_expect_tx(full + stage, Cfg::kStageBytes);
-            tma_load_2d(smem_a + stage * kBM * kBKBytes, &tmap_a, full + stage, kk * kBKElems, m0);
-            tma_load_2d(smem_b + stage * BN * kBKBytes, &tmap_b, full + stage, kk * kBKElems, n0);
-          }
+          ok = mbar_wait(empty + stage, phase ^ 1, abort_flag, p.d_status, XAXB_DEVICE_TIMEOUT * 1000 + kSiteProducer);
+          if (!ok) break;
+          mbar_arrive_expect_tx(full + stage, Cfg::kStageBytes);
+          tma_load_2d(smem_a + stage * kBM * kBKBytes, &tmap_a, full + stage, kk * kBKElems, m0);
+          tma_load_2d(smem_b + stage * BN * kBKBytes, &tmap_b, full + stage, kk * kBKElems, n0);
           if (++kk == p.num_k_blocks) kk = 0;
           if (++stage == kStages) stage = 0, phase ^= 1;
         }
-        pre = 0;
       }
     }
   } else if (warp == 1) {
@@ -609,18 +593,9 @@ gemm_splitk_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
       int stage = 0;
       uint32_t phase = 0;
       int kk = nkb > 0 ? kb0 + (tile_n * 3) % nkb : kb0;  // staggered start, see gemm_tc_kernel
-      int pre = 0;
-      if (p.prefetch_b) {  // B ahead of the wait on the previous kernel (see GemmParams::prefetch_b)
+      {  // B of the first K blocks -> L2, ahead of the wait on the previous kernel (GemmParams::prefetch_l2)
         int k2 = kk;
-        if (p.prefetch_b == 2) {
-          pre = nkb < kStages ? nkb : kStages;
-          for (int i = 0; i < pre; ++i) {
-            mbar_arrive_expect_tx(full + i, Cfg::kStageBytes);
-            tma_load_2d(smem_b + i * BN * kBKBytes, &tmap_b, full + i, k2 * kBKElems, n0);
-            if (++k2 == kb1) k2 = kb0;
-          }
-        }
-        const int n_l2 = min(nkb - pre, p.prefetch_l2);
+        const int n_l2 = min(nkb, p.prefetch_l2);
         for (int i = 0; i < n_l2; ++i) {
           tma_prefetch_l2_2d(&tmap_b, k2 * kBKElems, n0);
           if (++k2 == kb1) k2 = kb0;
@@ -628,15 +603,11 @@ gemm_splitk_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
       }
       pdl_wait();
       for (int i = 0; i < nkb; ++i) {
-        if (i < pre) {  // the stage is armed and its B half requested already
-          tma_load_2d(smem_a + stage * kBM * kBKBytes, &tmap_a, full + stage, kk * kBKElems, 0);
-        } else {
-          if (!mbar_wait(empty + stage, phase ^ 1, abort_flag, p.d_status, XAXB_DEVICE_TIMEOUT * 1000 + kSiteSkProducer))
-            break;
-          mbar_arrive_expect_tx(full + stage, Cfg::kStageBytes);
-          tma_load_2d(smem_a + stage * kBM * kBKBytes, &tmap_a, full + stage, kk * kBKElems, 0);
-          tma_load_2d(smem_b + stage * BN * kBKBytes, &tmap_b, full + stage, kk * kBKElems, n0);
-        }
+        if (!mbar_wait(empty + stage, phase ^ 1, abort_flag, p.d_status, XAXB_DEVICE_TIMEOUT * 1000 + kSiteSkProducer))
+          break;
+        mbar_arrive_expect_tx(full + stage, Cfg::kStageBytes);
+        tma_load_2d(smem_a + stage * kBM * kBKBytes, &tmap_a, full + stage, kk * kBKElems, 0);
+        tma_load_2d(smem_b + stage * BN * kBKBytes, &tmap_b, full + stage, kk * kBKElems, n0);
         if (++kk == kb1) kk = kb0;
         if (++stage == kStages) stage = 0, phase ^= 1;
       }
@@ -806,22 +777,20 @@ gemm_splitk_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
   }
   if (p.push_world > 0 && warp >= 2) {
     // Every epilogue thread's peer stores precede the barrier; one thread then makes them visible
-    // system-wide and tells every rank how many 16-byte pieces of its staging slot are complete.
+    // system-wide (one fence) and tells every rank how many 16-byte pieces of its staging slot are
+    // complete with relaxed adds: fence + relaxed add is a release, and it is paid once.  Releasing
+    // adds instead (each one a fence of its own) cost 6.7 us more per GEMM on two GPUs.
     epilogue_sync();
     if (threadIdx.x == 64 && ok) {
       const int row0 = r * rows_per;
       const int rows_ok = max(0, min(p.M, row0 + rows_per) - row0);
       const int cols_ok = max(0, min(BN, p.N - n0));
       const unsigned int pieces = (unsigned int)(rows_ok * (cols_ok / 8));
-      if (p.push_mode != 2) __threadfence_system();
+      __threadfence_system();
 #pragma unroll
       for (int dst = 0; dst < 8; ++dst)
-        if (dst < p.push_world) {
-          if (p.push_mode == 1)
-            asm volatile("red.relaxed.sys.global.add.u32 [%0], %1;" ::"l"(p.push_flag[dst]), "r"(pieces) : "memory");
-          else
-            asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(p.push_flag[dst]), "r"(pieces) : "memory");
-        }
+        if (dst < p.push_world)
+          asm volatile("red.relaxed.sys.global.add.u32 [%0], %1;" ::"l"(p.push_flag[dst]), "r"(pieces) : "memory");
     }
   }
   __syncwarp();
@@ -905,7 +874,7 @@ struct GemmPlan {
 };
 
 static int g_force_bn = 0, g_force_split = 0;  // test hook (xaxb_gemm_force_plan)
-static int g_prefetch_mode = 1, g_prefetch_l2 = kMaxPrefetchBlocks;  // xaxb_gemm_set_prefetch
+static int g_prefetch_l2 = kMaxPrefetchBlocks;  // xaxb_gemm_set_prefetch
 
 // `one_wave_kernel`: every candidate runs on the split-K kernel (one tile per CTA, not persistent), as
 // the pushing epilogue requires; a "split" of 1 is then a plain tile per CTA, in as many waves as needed.
@@ -939,6 +908,7 @@ static GemmPlan pick_plan(long long M, long long N, long long K, int elem_bytes,
       t += 2.4e-6 + (waves - 1) * 2e-6;
       if (s > 1) t += (s == 2 ? 1.8e-6 : 3.9e-6) + 0.02e-6 * bn;
       if (one_wave_kernel && s == 1) t += 0.8e-6;  // the tile still goes through shared memory once
+      if (bn == 32) t += 3e-6;  // measured: 32-wide tiles pay ~3 us more than their byte count says
       if (t < best_t) best_t = t, best = {bn, s};
     }
   }
@@ -998,11 +968,8 @@ static int gemm_entry(xaxb_ctx* ctx_, void* stream, const void* a, int64_t lda, 
   p.out = static_cast<__nv_bfloat16*>(out);
   p.ldo = ldo;
   p.d_status = ctx->d_status;
-  p.prefetch_b = pdl_enabled() ? g_prefetch_mode : 0;
-  p.prefetch_l2 = g_prefetch_l2;
+  p.prefetch_l2 = pdl_enabled() ? g_prefetch_l2 : 0;
   p.push_world = 0;
-  p.push_mode = 0;
-  if (const char* e = getenv("XAXB_PUSH_MODE")) p.push_mode = atoi(e);
   for (int r = 0; r < 8; ++r) p.push_out[r] = nullptr, p.push_flag[r] = nullptr;
   if (push) {
     p.push_world = push->world;
@@ -1016,12 +983,6 @@ static int gemm_entry(xaxb_ctx* ctx_, void* stream, const void* a, int64_t lda, 
   if (const char* e = getenv("XAXB_GEMM_BAND")) p.band = atoi(e) > 0 ? atoi(e) : 32;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   GemmPlan plan = pick_plan(M, N, K, eb, ctx->num_sms, push != nullptr);
-  if (push) {
-    if (const char* e = getenv("XAXB_PUSH_PLAN")) {  // experiment knob: "bn,split"
-      int bn = 0, sp = 0;
-      if (sscanf(e, "%d,%d", &bn, &sp) == 2 && bn > 0 && sp > 0) plan.bn = bn, plan.split = sp;
-    }
-  }
   // Large problems go to the CTA-pair kernel: 256 x 256 tiles need a third less operand traffic
   // per SM, which is what bounds the single-CTA kernel.  It wants at least two waves of tiles.
   const bool pair_ok = M > kBM && N >= 256;
@@ -1065,10 +1026,9 @@ int xaxb_gemm_force_plan(int bn, int split) {
   return XAXB_OK;
 }
 
-int xaxb_gemm_set_prefetch(int mode, int l2_blocks) {
-  if (mode < 0 || mode > 2 || l2_blocks < 0 || l2_blocks > 4096) return XAXB_BAD_ARGUMENT;
-  g_prefetch_mode = mode;
-  g_prefetch_l2 = l2_blocks;
+int xaxb_gemm_set_prefetch(int blocks_before_wait) {
+  if (blocks_before_wait < 0 || blocks_before_wait > 4096) return XAXB_BAD_ARGUMENT;
+  g_prefetch_l2 = blocks_before_wait;
   return XAXB_OK;
 }
 

@@ -354,7 +354,7 @@ extern "C" {
 
 int64_t xaxb_tp_sync_bytes(void) { return kTpSyncBytes; }
 
-int64_t xaxb_tp_max_inbox_bytes(void) { return 2ll * kTpMaxWorld * kTpMaxSlots * 4; }
+int64_t xaxb_tp_max_inbox_bytes(void) { return kTpRowMaxInboxBytes; }
 
 int xaxb_tp_allreduce_sum_bf16(xaxb_ctx* ctx_, void* stream, void* const* peer_bases, int rank, int world,
                                int64_t data_offset_bytes, int64_t sync_offset_bytes, int64_t rows, int64_t cols,

@@ -64,8 +64,7 @@ __device__ __forceinline__ uint32_t tp_exchange_flags(const PeerTable& peers, in
   if ((int)threadIdx.x < world) {
     const int r = threadIdx.x;
     uint32_t* theirs = reinterpret_cast<uint32_t*>(peers.base[r] + sync_off) + slot * kTpMaxWorld + rank;
-    __threadfence_system();
-    st_release_sys(theirs, epoch);
+    st_release_sys(theirs, epoch);  // cumulative over the CTA's stores: they precede the barrier above
     const uint32_t* mine = my_flags + slot * kTpMaxWorld + r;
     if ((int32_t)(ld_acquire_sys(mine) - epoch) < 0) {
       const unsigned long long t0 = globaltimer_ns();
@@ -83,12 +82,15 @@ __device__ __forceinline__ uint32_t tp_exchange_flags(const PeerTable& peers, in
   return epoch;
 }
 
-// Inbox of the per-CTA maximum: uint32 [2][kTpMaxWorld][kTpMaxSlots], used in alternation by
-// epoch parity.
-constexpr int64_t kTpRowMaxInboxBytes = 2ll * kTpMaxWorld * kTpMaxSlots * 4;
+// Inbox of the per-CTA maximum: uint64 [2][kTpMaxWorld][kTpMaxSlots], used in alternation by
+// epoch parity.  An entry is (epoch << 32 | value): value and "it has arrived" travel in ONE 8-byte
+// store, which is single-copy atomic, so the exchange needs no fence, no releasing store and no
+// acquiring load -- each of those costs a few microseconds at system scope, and this exchange sits
+// on the critical path of two kernels per transformer block.
+constexpr int64_t kTpRowMaxInboxBytes = 2ll * kTpMaxWorld * kTpMaxSlots * 8;
 
 // What a kernel needs to take the maximum of one 32-bit value per CTA over the ranks; world <= 1
-// means "no exchange".  Passed by value.
+// means "no exchange".  Passed by value.  sync_off: only the epoch counters of the flag region are used.
 struct TpRowMax {
   PeerTable peers;
   int64_t inbox_off, sync_off;
@@ -97,9 +99,11 @@ struct TpRowMax {
 
 // max over ranks of `mine` (compared as unsigned integers: the bit pattern of a non-negative
 // amax, so NaN wins as it does in the quantiser) for CTA `slot`; the matching CTA of every rank
-// must call it.  Thread r < world pushes the value into rank r's inbox, raises this rank's flag
-// there, waits for rank r's flag here and reads rank r's value; the maximum is then shared
-// through `s_tmp` (two uint32 of shared memory).  Called by all threads of the CTA.
+// must call it.  Thread r < world stores (epoch, value) into rank r's inbox and polls this rank's
+// inbox until rank r's entry carries this epoch; the maximum is then shared through `s_tmp` (two
+// uint32 of shared memory).  Called by all threads of the CTA.  An entry of epoch e is overwritten
+// by epoch e + 2 at the earliest, which its writer reaches only after it has seen this rank's entry
+// of epoch e + 1, i.e. after this CTA finished reading epoch e (stream order on this rank).
 __device__ __forceinline__ uint32_t tp_cta_max_u32(const TpRowMax& tp, int slot, uint32_t mine, uint32_t* s_tmp,
                                                    int* d_status, int site) {
   uint32_t* my_flags = reinterpret_cast<uint32_t*>(tp.peers.base[tp.rank] + tp.sync_off);
@@ -114,16 +118,21 @@ __device__ __forceinline__ uint32_t tp_cta_max_u32(const TpRowMax& tp, int slot,
   const uint32_t epoch = s_tmp[0];
   if ((int)threadIdx.x < tp.world) {
     const int r = threadIdx.x;
-    const int64_t box = tp.inbox_off + (int64_t)(epoch & 1) * kTpMaxWorld * kTpMaxSlots * 4;
-    uint32_t* their_box = reinterpret_cast<uint32_t*>(tp.peers.base[r] + box) + tp.rank * kTpMaxSlots + slot;
-    asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(their_box), "r"(mine) : "memory");
-    uint32_t* theirs = reinterpret_cast<uint32_t*>(tp.peers.base[r] + tp.sync_off) + slot * kTpMaxWorld + tp.rank;
-    st_release_sys(theirs, epoch);
-    const uint32_t* flag = my_flags + slot * kTpMaxWorld + r;
-    if ((int32_t)(ld_acquire_sys(flag) - epoch) < 0) {
+    const int64_t box = tp.inbox_off + (int64_t)(epoch & 1) * kTpMaxWorld * kTpMaxSlots * 8;
+    unsigned long long* their_box =
+        reinterpret_cast<unsigned long long*>(tp.peers.base[r] + box) + tp.rank * kTpMaxSlots + slot;
+    const unsigned long long word = ((unsigned long long)epoch << 32) | mine;
+    asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(their_box), "l"(word) : "memory");
+    const unsigned long long* my_box =
+        reinterpret_cast<const unsigned long long*>(tp.peers.base[tp.rank] + box) + r * kTpMaxSlots + slot;
+    unsigned long long w;
+    asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(w) : "l"(my_box) : "memory");
+    if ((uint32_t)(w >> 32) != epoch) {
       const unsigned long long t0 = globaltimer_ns();
       const unsigned long long limit = peer_wait_limit_ns(d_status);
-      while ((int32_t)(ld_acquire_sys(flag) - epoch) < 0) {
+      for (;;) {
+        asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(w) : "l"(my_box) : "memory");
+        if ((uint32_t)(w >> 32) == epoch) break;
         if (*reinterpret_cast<volatile int*>(d_status) != 0) break;
         if (globaltimer_ns() - t0 > limit) {
           atomicCAS(d_status, 0, XAXB_DEVICE_TIMEOUT * 1000 + site);
@@ -131,10 +140,7 @@ __device__ __forceinline__ uint32_t tp_cta_max_u32(const TpRowMax& tp, int slot,
         }
       }
     }
-    const uint32_t* my_box = reinterpret_cast<const uint32_t*>(tp.peers.base[tp.rank] + box) + r * kTpMaxSlots + slot;
-    uint32_t v;
-    asm volatile("ld.relaxed.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(my_box) : "memory");
-    atomicMax(&s_tmp[1], v);
+    if ((uint32_t)(w >> 32) == epoch) atomicMax(&s_tmp[1], (uint32_t)w);
   }
   __syncthreads();
   return s_tmp[1];
