@@ -565,8 +565,8 @@ def main() -> None:
             return r
         return wrapper
 
-    saved = {n: getattr(ops, n) for n in ("attn_decode", "attn_decode_cast", "attn_decode_cast_tp")}
-    for n, fn in saved.items():  # the model reaches decode attention through one of these three
+    saved = {n: getattr(ops, n) for n in ("attn_decode", "attn_decode_cast", "attn_decode_cast_tp", "attn_decode_append")}
+    for n, fn in saved.items():  # the model reaches decode attention through one of these
         setattr(ops, n, timed(fn))
     n_eager = 2
     for _ in range(n_eager):
@@ -578,7 +578,7 @@ def main() -> None:
     attn_len = int(mean_len_timed) + 0.5
     attn_bytes = B * attn_len * (2 * hkv_local * D * 2) + 2 * B * hq_local * D * 2
     avg = sum(durs) / max(len(durs), 1)
-    roofline = {"bound": "hbm", "kernel": "attn_decode_kernel (+ its merge pass)", "achieved": attn_bytes / avg / 1e9,
+    roofline = {"bound": "hbm", "kernel": "attn_decode_kernel (RoPE + cache append fused in, + its merge pass)", "achieved": attn_bytes / avg / 1e9,
                 "peak": peak, "peak_kind": f"of {peak_kind} copy bandwidth", "unit": "GB/s",
                 "frac": attn_bytes / avg / 1e9 / peak,
                 # DRAM bytes per launch: ncu on a smaller case of the same kernel (B=32, same context, heads)

@@ -317,6 +317,28 @@ int xaxb_attn_decode_static(xaxb_ctx* ctx, void* stream, const void* q_rot_bf16,
                             const void* sin_bf16, int64_t table_len, void* out_bf16);
 
 /*
+ * Decode attention with the cache append fused in: xaxb_kv_append_rope (T = 1) + xaxb_attn_decode[_cast,
+ * _window, _cast_tp] as one call, without the separate append launch and without the rotated-query
+ * buffer.  qkv: bf16 [B, ld], the fused projection's output of the step's new token (q | k | v column
+ * blocks as for xaxb_kv_append_rope), not yet in the cache; positions[b] = tokens already cached.  The
+ * attention kernel rotates the query heads as it stages them, and the CTA that owns the cache chunk of
+ * position positions[b] rotates the new key (k_is_rotated = 1; 0 stores and rotates on load as in
+ * xaxb_attn_decode), places key and value into its tiles and writes them to cache row positions[b]:
+ * results and cache contents are bit-identical to the two separate calls.  cos/sin [table_len >= max_len,
+ * D/2] are always needed.  window < 0: unlimited.  out_bf16 and / or (q_e4m3, row_scale, row_inv_scale)
+ * as in xaxb_attn_decode_cast; peer_bases != NULL with world > 1 adds the exchange of
+ * xaxb_attn_decode_cast_tp.  positions are not advanced (xaxb_advance_positions).
+ * (xax/arch/attention.py:870-946 for seq_len = 1.)
+ */
+int xaxb_attn_decode_append(xaxb_ctx* ctx, void* stream, const void* qkv_bf16, int64_t ld, void* k_cache_bf16,
+                            void* v_cache_bf16, const int32_t* positions, int64_t B, int64_t Hq, int64_t Hkv,
+                            int64_t D, int64_t max_len, float softmax_scale, int k_is_rotated, const void* cos_bf16,
+                            const void* sin_bf16, int64_t table_len, int64_t window, void* out_bf16, void* q_e4m3,
+                            float* row_scale, float* row_inv_scale, void* workspace, int64_t workspace_bytes,
+                            void* const* peer_bases, int rank, int world, int64_t inbox_offset_bytes,
+                            int64_t sync_offset_bytes);
+
+/*
  * Causal prefill attention for T new tokens per sequence against the cache (which
  * already holds them, written by xaxb_kv_append_rope): query i of sequence b sits at
  * position positions[b] + i and attends to cache rows 0 .. positions[b] + i

@@ -551,12 +551,35 @@ class SelfAttentionBlock:
                         None if nk is None else nk.weight_bf16(), eps)
         cos, sin = self.rotary_emb.tables(max_len, dev)
         pos = cache["position"]
-        q_rot = ops.kv_append_rope(qkv, B, T, Hq, Hkv, D, pos, cos, sin, cache["k"], cache["v"])
         scale = 1.0 / math.sqrt(D)
         op = self.output_proj
         op_fp8 = isinstance(op, Fp8Linear) and op.use_fp8
         win = self.local_window_size
         fits_cast = T == 1 and op_fp8 and win is None and Hq <= 64 and Hq * D <= 4096
+        if T == 1 and D in (64, 128):
+            # decode: RoPE, cache append, attention (and, where it fits, the per-token cast of its output with
+            # the amax exchange over ranks) are one attention launch + one merge launch
+            use_cast = fits_cast and (peer_site is not None or reduce_amax is None)
+            attn, aq, _, a_inv = ops.attn_decode_append(qkv, cache["k"], cache["v"], pos, cos, sin, Hq, scale=scale,
+                                                        window=win, want_out=not use_cast, cast=use_cast,
+                                                        peer=peer_site if use_cast else None, workspace=workspace)
+            if not use_cast:
+                attn2 = attn.reshape(B, Hq * D)
+                if op_fp8:
+                    if reduce_amax is None:
+                        aq, _, a_inv, _ = ops.quantize_current(attn2, 1)
+                    else:
+                        amax = ops.group_amax(attn2, 1)
+                        reduce_amax(amax)
+                        aq, _, a_inv = ops.quantize_with_amax(attn2, amax, 1)
+            if op_fp8:
+                out = op.forward_quantized(aq, a_inv, residual, out)
+            else:
+                out = apply_linear(attn2, op, residual=residual)
+            if advance:
+                ops.advance_positions(pos, T)  # new_position = p + seq_len (:888), on the device
+            return out, {"k": cache["k"], "v": cache["v"], "position": pos}
+        q_rot = ops.kv_append_rope(qkv, B, T, Hq, Hkv, D, pos, cos, sin, cache["k"], cache["v"])
         if fits_cast and peer_site is not None:
             aq, _, a_inv = ops.attn_decode_cast_tp(q_rot, cache["k"], cache["v"], pos, peer_site, scale=scale,
                                                    workspace=workspace)

@@ -79,6 +79,16 @@ struct DecodeParams {
   int max_chunks;
   int window;  // sliding window: the query at position q sees keys q - window .. q; < 0 = unlimited
   int* d_status;
+  // Fused append (qkv != nullptr): the step's new token has not been written to the cache yet.  Row b of
+  // qkv -- the fused projection's output, [q heads | k heads | v heads] x D, row stride qkv_ld -- holds
+  // its query, key and value.  Every CTA rotates the query heads of its group as it stages them; the one
+  // CTA that owns the chunk of position positions[b] rotates the new key (unless K is stored
+  // un-rotated), places key and value in the row of its K / V tiles in shared memory where the cache
+  // row will be, and writes them to the cache.  This replaces the append kernel of a decode step.
+  const __nv_bfloat16* qkv;
+  long long qkv_ld;
+  __nv_bfloat16* k_cache;  // [B, max_len, Hkv, D]
+  __nv_bfloat16* v_cache;
 };
 
 template <int D>
@@ -267,12 +277,74 @@ __device__ __forceinline__ void rotate_k_row(uint8_t* sK, const RopeRow<D>& r) {
   }
 }
 
+// Fused append: the new token's key -> row r_new of the K tile in shared memory and row t_new of the
+// cache.  Threads 0 .. D/16 - 1, one pair of 16-byte pieces each; the tile has landed.
+template <int D>
+__device__ __forceinline__ void place_new_key(uint8_t* sK, const DecodeParams& p, int b, int hk, int t_new, int r_new) {
+  using SM = DecodeSmem<D>;
+  constexpr int kPairs = D / 16;
+  const int c = threadIdx.x;
+  if (c >= kPairs) return;
+  const uint4* src = reinterpret_cast<const uint4*>(p.qkv + (long long)b * p.qkv_ld + (long long)(p.Hq + hk) * D);
+  uint4 a = __ldg(src + c), bb = __ldg(src + c + kPairs);
+  if (p.k_is_rotated) {
+    const uint4* cr = reinterpret_cast<const uint4*>(p.cos_t + (long long)t_new * (D / 2));
+    const uint4* sr = reinterpret_cast<const uint4*>(p.sin_t + (long long)t_new * (D / 2));
+    rope_rotate_pieces(a, bb, __ldg(cr + c), __ldg(sr + c), a, bb);
+  }
+  const int c2 = c + kPairs;
+  *reinterpret_cast<uint4*>(sK + (c / 8) * SM::kHalfBytes + sw128_offset(r_new, c % 8)) = a;
+  *reinterpret_cast<uint4*>(sK + (c2 / 8) * SM::kHalfBytes + sw128_offset(r_new, c2 % 8)) = bb;
+  uint4* dst = reinterpret_cast<uint4*>(p.k_cache + (((long long)b * p.max_len + t_new) * p.Hkv + hk) * D);
+  dst[c] = a;
+  dst[c2] = bb;
+}
+
+// Same for the value (copied as it is).  Threads 0 .. D/8 - 1, one 16-byte piece each.
+template <int D>
+__device__ __forceinline__ void place_new_value(uint8_t* sV, const DecodeParams& p, int b, int hk, int t_new, int r_new) {
+  using SM = DecodeSmem<D>;
+  const int c = threadIdx.x;
+  if (c >= D / 8) return;
+  const uint4 v =
+      __ldg(reinterpret_cast<const uint4*>(p.qkv + (long long)b * p.qkv_ld + (long long)(p.Hq + p.Hkv + hk) * D) + c);
+  *reinterpret_cast<uint4*>(sV + (c / 8) * SM::kHalfBytes + sw128_offset(r_new, c % 8)) = v;
+  reinterpret_cast<uint4*>(p.v_cache + (((long long)b * p.max_len + t_new) * p.Hkv + hk) * D)[c] = v;
+}
+
+// One K or V tile -> shared memory.  A chunk that the sequence fills only in part (its last one) is
+// fetched in boxes of 32 token rows through the second tensor map, only as many as hold tokens: the
+// rows behind them keep whatever the previous tile left, which the softmax masks (K) and the threads
+// clear (V) as they do for any row past the sequence end.  Fetching the whole 128-row box regardless
+// cost 3 % of the traffic at a context of ~2100 tokens (64 wasted rows per sequence on average).
+constexpr int kPartRows = 32;
+template <int D>
+__device__ __forceinline__ void load_tile(uint8_t* dst, const CUtensorMap* whole, const CUtensorMap* part,
+                                          uint64_t* bar, int hk, int tok0, int b, int rows) {
+  using SM = DecodeSmem<D>;
+  constexpr int kBoxes = D / 64;
+  if (rows > kChunk - kPartRows) {
+    mbar_arrive_expect_tx(bar, SM::kTileBytes);
+#pragma unroll
+    for (int x = 0; x < kBoxes; ++x) tma_load_4d(dst + x * SM::kHalfBytes, whole, bar, x * 64, hk, tok0, b);
+  } else {
+    const int n = (rows + kPartRows - 1) / kPartRows;
+    mbar_arrive_expect_tx(bar, n * kPartRows * D * 2);
+#pragma unroll
+    for (int x = 0; x < kBoxes; ++x)
+      for (int j = 0; j < n; ++j)
+        tma_load_4d(dst + x * SM::kHalfBytes + j * kPartRows * 128, part, bar, x * 64, hk, tok0 + j * kPartRows, b);
+  }
+}
+
 // GT = the group size rounded up to a power of two: only GT of the 16 UMMA columns are read back,
 // reduced and written as P^T.  (Column n of either product depends on row n of its B operand
 // only, so whatever the unused rows of Q and P^T hold never reaches a column that is read.)
 template <int D, int GT, bool kRotate>
 __global__ void __launch_bounds__(128, 3) attn_decode_kernel(const __grid_constant__ CUtensorMap tmap_k,
                                                           const __grid_constant__ CUtensorMap tmap_v,
+                                                          const __grid_constant__ CUtensorMap tmap_k_part,
+                                                          const __grid_constant__ CUtensorMap tmap_v_part,
                                                           const DecodeParams p) {
   pdl_wait();  // nothing below may run ahead of the previous kernel in the stream
   using SM = DecodeSmem<D>;
@@ -310,22 +382,34 @@ __global__ void __launch_bounds__(128, 3) attn_decode_kernel(const __grid_consta
     mbar_init(bar_o, 1);
     *abort_flag = 0;
     fence_mbar_init();
-    mbar_arrive_expect_tx(bar_k, SM::kTileBytes);
-    mbar_arrive_expect_tx(bar_v, SM::kTileBytes);
-#pragma unroll
-    for (int x = 0; x < kBoxes; ++x)
-      tma_load_4d(sK + x * SM::kHalfBytes, &tmap_k, bar_k, x * 64, hk, (c_lo + first) * kChunk, b);
-#pragma unroll
-    for (int x = 0; x < kBoxes; ++x)
-      tma_load_4d(sV + x * SM::kHalfBytes, &tmap_v, bar_v, x * 64, hk, (c_lo + first) * kChunk, b);
+    const int t0 = (c_lo + first) * kChunk;
+    load_tile<D>(sK, &tmap_k, &tmap_k_part, bar_k, hk, t0, b, min(kChunk, L - t0));
+    load_tile<D>(sV, &tmap_v, &tmap_v_part, bar_v, hk, t0, b, min(kChunk, L - t0));
   }
   if (warp == 1) {
     tmem_alloc(tmem_slot, 32);
     tmem_relinquish();
   }
 
+  const bool append = p.qkv != nullptr;
+  const int t_new = L - 1, c_new = t_new / kChunk, r_new = t_new % kChunk;  // the step's new token
   // Q of this group -> shared memory, K-major rows of D elements; rows G .. GT-1 zero.
-  {
+  if (append) {  // ... rotated here, from the fused projection's output
+    constexpr int kPairs = D / 16;
+    const uint4* cr = reinterpret_cast<const uint4*>(p.cos_t + (long long)t_new * (D / 2));
+    const uint4* sr = reinterpret_cast<const uint4*>(p.sin_t + (long long)t_new * (D / 2));
+    for (int i = tid; i < GT * kPairs; i += 128) {
+      const int g = i / kPairs, c = i % kPairs, c2 = c + kPairs;
+      uint4 o1 = make_uint4(0, 0, 0, 0), o2 = o1;
+      if (g < p.G) {
+        const uint4* src =
+            reinterpret_cast<const uint4*>(p.qkv + (long long)b * p.qkv_ld + (long long)(hk * p.G + g) * D);
+        rope_rotate_pieces(__ldg(src + c), __ldg(src + c2), __ldg(cr + c), __ldg(sr + c), o1, o2);
+      }
+      *reinterpret_cast<uint4*>(sQ + (c / 8) * (kNPad * 128) + sw128_offset(g, c % 8)) = o1;
+      *reinterpret_cast<uint4*>(sQ + (c2 / 8) * (kNPad * 128) + sw128_offset(g, c2 % 8)) = o2;
+    }
+  } else {
     constexpr int kChunksPerRow = D / 8;  // 16-byte chunks
     for (int i = tid; i < GT * kChunksPerRow; i += 128) {
       const int g = i / kChunksPerRow, c = i % kChunksPerRow;
@@ -368,14 +452,25 @@ __global__ void __launch_bounds__(128, 3) attn_decode_kernel(const __grid_consta
     const int valid = min(kChunk, L - tok0);
     const int next = chunk + stride;
 
+    const bool has_new = append && chunk == c_new;  // (uniform over the CTA)
     if constexpr (kRotate) {
       ok = mbar_wait(bar_k, ph, abort_flag, p.d_status, XAXB_DEVICE_TIMEOUT * 1000 + kSiteDecK);
+      if (has_new) {  // the un-rotated new key goes in first; other threads rotate its row below
+        if (ok) place_new_key<D>(sK, p, b, hk, t_new, r_new);
+        __syncthreads();
+      }
       if (ok) rotate_k_row<D>(sK, rope);
       fence_proxy_async_smem();
       ok = __syncthreads_and(ok);
       if (!ok) break;
       // the table rows of the next tile, requested a whole iteration before they are needed
       if (next < n_chunks) load_rope_row<D>(rope, p, next * kChunk, min(kChunk, L - next * kChunk));
+    } else if (has_new) {
+      ok = mbar_wait(bar_k, ph, abort_flag, p.d_status, XAXB_DEVICE_TIMEOUT * 1000 + kSiteDecK);
+      if (ok) place_new_key<D>(sK, p, b, hk, t_new, r_new);
+      fence_proxy_async_smem();
+      ok = __syncthreads_and(ok);
+      if (!ok) break;
     }
 
     // ---- S^T = K Q^T ---------------------------------------------------------------------
@@ -394,12 +489,8 @@ __global__ void __launch_bounds__(128, 3) attn_decode_kernel(const __grid_consta
       }
     }
     ok = mbar_wait(bar_s, ph, abort_flag, p.d_status, XAXB_DEVICE_TIMEOUT * 1000 + kSiteDecS);
-    if (tid == 0 && ok && next < n_chunks) {  // the K tile has been consumed: fetch the next one
-      mbar_arrive_expect_tx(bar_k, SM::kTileBytes);
-#pragma unroll
-      for (int x = 0; x < kBoxes; ++x)
-        tma_load_4d(sK + x * SM::kHalfBytes, &tmap_k, bar_k, x * 64, hk, next * kChunk, b);
-    }
+    if (tid == 0 && ok && next < n_chunks)  // the K tile has been consumed: fetch the next one
+      load_tile<D>(sK, &tmap_k, &tmap_k_part, bar_k, hk, next * kChunk, b, min(kChunk, L - next * kChunk));
 
     // ---- softmax numerators: thread = token ------------------------------------------------
     float pvals[GT];
@@ -439,6 +530,7 @@ __global__ void __launch_bounds__(128, 3) attn_decode_kernel(const __grid_consta
       for (int c = 0; c < D / 8; ++c)
         *reinterpret_cast<uint4*>(sV + (c / 8) * SM::kHalfBytes + sw128_offset(tid, c % 8)) = make_uint4(0, 0, 0, 0);
     }
+    if (ok && has_new) place_new_value<D>(sV, p, b, hk, t_new, r_new);
     fence_proxy_async_smem();
     ok = __syncthreads_and(ok);
     if (!ok) break;
@@ -475,12 +567,8 @@ __global__ void __launch_bounds__(128, 3) attn_decode_kernel(const __grid_consta
       m_run[g] = m_new;
     }
     ok = mbar_wait(bar_o, ph, abort_flag, p.d_status, XAXB_DEVICE_TIMEOUT * 1000 + kSiteDecO);
-    if (tid == 0 && ok && next < n_chunks) {  // the V tile has been consumed: fetch the next one
-      mbar_arrive_expect_tx(bar_v, SM::kTileBytes);
-#pragma unroll
-      for (int x = 0; x < kBoxes; ++x)
-        tma_load_4d(sV + x * SM::kHalfBytes, &tmap_v, bar_v, x * 64, hk, next * kChunk, b);
-    }
+    if (tid == 0 && ok && next < n_chunks)  // the V tile has been consumed: fetch the next one
+      load_tile<D>(sV, &tmap_v, &tmap_v_part, bar_v, hk, next * kChunk, b, min(kChunk, L - next * kChunk));
     if (ok) {
       tc_fence_after_sync();
       // accumulator row d (a head dimension) sits in TMEM lane d
@@ -559,11 +647,11 @@ __global__ void __launch_bounds__(512) attn_decode_merge_cast_kernel(
 }
 
 static int make_cache_tmap(const Ctx* ctx, CUtensorMap* map, const void* cache, int64_t B, int64_t max_len,
-                           int64_t Hkv, int64_t D) {
-  // cache[b][token][head][d]: dims innermost first (d, head, token, b); box = 64 d x 1 head x 128 tokens x 1.
+                           int64_t Hkv, int64_t D, int box_rows = kChunk) {
+  // cache[b][token][head][d]: dims innermost first (d, head, token, b); box = 64 d x 1 head x box_rows tokens x 1.
   const uint64_t dims[4] = {(uint64_t)D, (uint64_t)Hkv, (uint64_t)max_len, (uint64_t)B};
   const uint64_t strides[3] = {(uint64_t)D * 2, (uint64_t)Hkv * D * 2, (uint64_t)max_len * Hkv * D * 2};
-  const uint32_t box[4] = {64, 1, (uint32_t)kChunk, 1};
+  const uint32_t box[4] = {64, 1, (uint32_t)box_rows, 1};
   return make_tmap_4d(ctx, map, cache, 2, dims, strides, box);
 }
 
@@ -583,10 +671,19 @@ static int decode_launch(xaxb_ctx* ctx_, void* stream, const void* q_rot_bf16, c
                          int64_t D, int64_t max_len, float softmax_scale, int k_is_rotated, const void* cos_bf16,
                          const void* sin_bf16, int64_t table_len, void* out_bf16, void* q_e4m3, float* row_scale,
                          float* row_inv_scale, void* workspace, int64_t workspace_bytes,
-                         const TpRowMax* tp = nullptr, int64_t window = -1) {
-  if (!ctx_ || !q_rot_bf16 || !k_cache_bf16 || !v_cache_bf16 || !positions || (!out_bf16 && !q_e4m3) || !workspace || B <= 0 ||
-      Hq <= 0 || Hkv <= 0 || max_len <= 0) {
+                         const TpRowMax* tp = nullptr, int64_t window = -1, const void* qkv_bf16 = nullptr,
+                         int64_t qkv_ld = 0) {
+  // qkv_bf16: fused append (DecodeParams::qkv); q_rot_bf16 is then unused and the caches are written
+  if (!ctx_ || (!q_rot_bf16 && !qkv_bf16) || !k_cache_bf16 || !v_cache_bf16 || !positions || (!out_bf16 && !q_e4m3) ||
+      !workspace || B <= 0 || Hq <= 0 || Hkv <= 0 || max_len <= 0) {
     set_last_error("attn_decode: null pointer or non-positive shape");
+    return XAXB_BAD_ARGUMENT;
+  }
+  if (qkv_bf16 && (!cos_bf16 || !sin_bf16 || table_len < max_len || qkv_ld < (Hq + 2 * Hkv) * D || qkv_ld % 8 != 0 ||
+                   (reinterpret_cast<uintptr_t>(qkv_bf16) & 15) || (reinterpret_cast<uintptr_t>(cos_bf16) & 15) ||
+                   (reinterpret_cast<uintptr_t>(sin_bf16) & 15))) {
+    set_last_error("attn_decode_append: needs cos/sin tables covering max_len, a row stride of at least "
+                   "(Hq + 2 Hkv) * D that is a multiple of 8, and 16-byte aligned qkv / tables");
     return XAXB_BAD_ARGUMENT;
   }
   if (Hq % Hkv != 0 || Hq / Hkv > kNPad || (D != 128 && D != 64) || Hkv > 65535 || B > 65535) {
@@ -599,12 +696,19 @@ static int decode_launch(xaxb_ctx* ctx_, void* stream, const void* q_rot_bf16, c
   }
   if (workspace_bytes < xaxb_attn_decode_workspace_bytes(B, Hq, D, max_len)) return XAXB_WORKSPACE_TOO_SMALL;
   if (reinterpret_cast<uintptr_t>(q_rot_bf16) & 15) return XAXB_BAD_ARGUMENT;
+  if (!k_is_rotated && ((reinterpret_cast<uintptr_t>(cos_bf16) | reinterpret_cast<uintptr_t>(sin_bf16)) & 15))
+    return XAXB_BAD_ARGUMENT;
   const Ctx* ctx = reinterpret_cast<const Ctx*>(ctx_);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   CUtensorMap tk, tv;
   int rc = make_cache_tmap(ctx, &tk, k_cache_bf16, B, max_len, Hkv, D);
   if (rc) return rc;
   rc = make_cache_tmap(ctx, &tv, v_cache_bf16, B, max_len, Hkv, D);
+  if (rc) return rc;
+  CUtensorMap tkp, tvp;  // the same caches in boxes of kPartRows token rows, for partly filled chunks
+  rc = make_cache_tmap(ctx, &tkp, k_cache_bf16, B, max_len, Hkv, D, kPartRows);
+  if (rc) return rc;
+  rc = make_cache_tmap(ctx, &tvp, v_cache_bf16, B, max_len, Hkv, D, kPartRows);
   if (rc) return rc;
   const int max_chunks = (int)((max_len + kChunk - 1) / kChunk);
   DecodeParams p;
@@ -622,18 +726,27 @@ static int decode_launch(xaxb_ctx* ctx_, void* stream, const void* q_rot_bf16, c
   p.max_chunks = max_chunks;
   p.window = window < 0 ? -1 : (window > 0x3fffffff ? 0x3fffffff : (int)window);
   p.d_status = ctx->d_status;
+  p.qkv = static_cast<const __nv_bfloat16*>(qkv_bf16);
+  p.qkv_ld = qkv_ld;
+  p.k_cache = static_cast<__nv_bfloat16*>(const_cast<void*>(k_cache_bf16));  // written only with qkv set
+  p.v_cache = static_cast<__nv_bfloat16*>(const_cast<void*>(v_cache_bf16));
   int lanes = max_chunks;  // partial results per (sequence, head) row of the workspace
   {
     // Chunks are dealt to `lanes` CTAs per (sequence, kv head); each CTA walks its chunks with
-    // the next tile's loads in flight.  About four chunks per CTA amortise the set-up; fewer when
-    // that would leave SMs without work.
-    int per_cta = 4;
-    if (g_decode_variant >= 11) per_cta = g_decode_variant - 10;
-    lanes = (max_chunks + per_cta - 1) / per_cta;
+    // the next tile's loads in flight.  As few lanes as still give about five resident waves of CTAs
+    // (three CTAs fit an SM): long walks amortise a CTA's set-up and leave fewer partial results to
+    // merge, but with only two or three waves the last one leaves SMs idle.  Measured at B = 128, 8 kv
+    // heads, 17 chunks: 1 lane 175 us, 2 - 4 lanes 171, 5 lanes 173, 7 lanes 175, 10 lanes 177; on the
+    // ragged B = 32 case (4 - 64 chunks): 2 lanes 103.5, 4 lanes 101.4, 8 lanes 99.3, 16 lanes 103.3.
     const long long groups = (long long)B * Hkv;
-    const long long want = 3ll * ctx->num_sms;  // one resident wave (three CTAs fit an SM)
-    if (g_decode_variant < 11 && groups * lanes < want) lanes = (int)((want + groups - 1) / groups);
+    const long long want = 5ll * 3ll * ctx->num_sms;
+    lanes = (int)((want + groups - 1) / groups);
+    if (g_decode_variant >= 11) {  // test hook: a fixed number of chunks per CTA
+      const int per_cta = g_decode_variant - 10;
+      lanes = (max_chunks + per_cta - 1) / per_cta;
+    }
     if (lanes > max_chunks) lanes = max_chunks;
+    if (lanes < 1) lanes = 1;
     dim3 grid((unsigned)lanes, (unsigned)Hkv, (unsigned)B);
     const int G = p.G;
     const int gt = G <= 1 ? 1 : G <= 2 ? 2 : G <= 4 ? 4 : G <= 8 ? 8 : 16;
@@ -642,11 +755,11 @@ static int decode_launch(xaxb_ctx* ctx_, void* stream, const void* q_rot_bf16, c
     if (k_is_rotated) {                                                                                          \
       rc = ensure_dynamic_smem<attn_decode_kernel<DD, GG, false>>(ctx, DecodeSmem<DD>::kBytes, "attn_decode");   \
       if (rc) return rc;                                                                                         \
-      launch_kernel(attn_decode_kernel<DD, GG, false>, grid, dim3(128), DecodeSmem<DD>::kBytes, s, 1, tk, tv, p);\
+      launch_kernel(attn_decode_kernel<DD, GG, false>, grid, dim3(128), DecodeSmem<DD>::kBytes, s, 1, tk, tv, tkp, tvp, p);\
     } else {                                                                                                     \
       rc = ensure_dynamic_smem<attn_decode_kernel<DD, GG, true>>(ctx, DecodeSmem<DD>::kBytes, "attn_decode");    \
       if (rc) return rc;                                                                                         \
-      launch_kernel(attn_decode_kernel<DD, GG, true>, grid, dim3(128), DecodeSmem<DD>::kBytes, s, 1, tk, tv, p); \
+      launch_kernel(attn_decode_kernel<DD, GG, true>, grid, dim3(128), DecodeSmem<DD>::kBytes, s, 1, tk, tv, tkp, tvp, p); \
     }                                                                                                            \
   }
     XAXB_DECODE_CASE(128, 1) XAXB_DECODE_CASE(128, 2) XAXB_DECODE_CASE(128, 4) XAXB_DECODE_CASE(128, 8)
@@ -757,6 +870,39 @@ extern "C" int xaxb_attn_decode_cast_tp(xaxb_ctx* ctx_, void* stream, const void
   return decode_launch(ctx_, stream, q_rot_bf16, k_cache_bf16, v_cache_bf16, positions, B, Hq, Hkv, D, max_len,
                        softmax_scale, k_is_rotated, cos_bf16, sin_bf16, table_len, nullptr, q_e4m3, row_scale,
                        row_inv_scale, workspace, workspace_bytes, &tp);
+}
+
+extern "C" int xaxb_attn_decode_append(xaxb_ctx* ctx_, void* stream, const void* qkv_bf16, int64_t ld, void* k_cache_bf16,
+                                       void* v_cache_bf16, const int32_t* positions, int64_t B, int64_t Hq,
+                                       int64_t Hkv, int64_t D, int64_t max_len, float softmax_scale,
+                                       int k_is_rotated, const void* cos_bf16, const void* sin_bf16,
+                                       int64_t table_len, int64_t window, void* out_bf16, void* q_e4m3,
+                                       float* row_scale, float* row_inv_scale, void* workspace,
+                                       int64_t workspace_bytes, void* const* peer_bases, int rank, int world,
+                                       int64_t inbox_offset_bytes, int64_t sync_offset_bytes) {
+  if (!qkv_bf16) return XAXB_BAD_ARGUMENT;
+  if (q_e4m3) {
+    if (!row_scale || !row_inv_scale) return XAXB_BAD_ARGUMENT;
+    if (Hq > 64 || Hq * D > 4096 || (reinterpret_cast<uintptr_t>(q_e4m3) & 7) ||
+        (reinterpret_cast<uintptr_t>(out_bf16) & 15)) {
+      set_last_error("attn_decode_append: the cast output needs Hq <= 64, Hq * D <= 4096 and aligned outputs");
+      return XAXB_UNSUPPORTED;
+    }
+  }
+  xaxb::TpRowMax tp;
+  const bool with_tp = peer_bases != nullptr && world > 1;
+  if (with_tp) {
+    if (!q_e4m3 || B > xaxb::kTpMaxSlots) {
+      set_last_error("attn_decode_append: the exchange over ranks needs the cast output and B <= %d", xaxb::kTpMaxSlots);
+      return XAXB_UNSUPPORTED;
+    }
+    int rc = xaxb::fill_tp_rowmax(tp, peer_bases, rank, world, inbox_offset_bytes, sync_offset_bytes,
+                                  "attn_decode_append");
+    if (rc) return rc;
+  }
+  return decode_launch(ctx_, stream, nullptr, k_cache_bf16, v_cache_bf16, positions, B, Hq, Hkv, D, max_len,
+                       softmax_scale, k_is_rotated, cos_bf16, sin_bf16, table_len, out_bf16, q_e4m3, row_scale,
+                       row_inv_scale, workspace, workspace_bytes, with_tp ? &tp : nullptr, window, qkv_bf16, ld);
 }
 
 extern "C" int xaxb_attn_decode_force_variant(int variant) {

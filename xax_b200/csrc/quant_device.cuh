@@ -129,6 +129,25 @@ __device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
   return r;
 }
 
+// RoPE, "concatenated" style (xax/arch/attention.py:510-515), on eight pairs (i, i + D/2): a holds
+// x[i .. i+7], b holds x[i + D/2 .. i + D/2 + 7], c / s the cos / sin values of those eight
+// frequencies.  Every product and every sum is rounded to bf16 as the reference's bf16 ops do.
+__device__ __forceinline__ void rope_rotate_pieces(const uint4 a, const uint4 b, const uint4 c, const uint4 s, uint4& o1,
+                                                   uint4& o2) {
+  float x1[8], x2[8], cc[8], ss[8], r1[8], r2[8];
+  unpack8(a, x1);
+  unpack8(b, x2);
+  unpack8(c, cc);
+  unpack8(s, ss);
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    r1[j] = bf16_round(x1[j] * cc[j]) - bf16_round(x2[j] * ss[j]);
+    r2[j] = bf16_round(x2[j] * cc[j]) + bf16_round(x1[j] * ss[j]);
+  }
+  o1 = pack8(r1);
+  o2 = pack8(r2);
+}
+
 // magnitude bits (bf16, sign cleared) of a float that already holds a bf16 value
 __device__ __forceinline__ uint32_t mag_bits16(float v) { return (__float_as_uint(v) >> 16) & 0x7FFFu; }
 

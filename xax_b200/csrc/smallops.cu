@@ -265,19 +265,7 @@ __global__ void __launch_bounds__(256) kv_append_rope_vec_kernel(
     const uint4 a = __ldg(src + c), bb = __ldg(src + c + hv);
     uint4 o1 = a, o2 = bb;
     if (head < Hq + Hkv && (head < Hq || store_rotated_k)) {
-      const uint4 cv = __ldg(cos_t + pos * hv + c), sv = __ldg(sin_t + pos * hv + c);
-      float x1[8], x2[8], cc[8], ss[8], r1[8], r2[8];
-      unpack8(a, x1);
-      unpack8(bb, x2);
-      unpack8(cv, cc);
-      unpack8(sv, ss);
-#pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        r1[j] = bf16_round(x1[j] * cc[j]) - bf16_round(x2[j] * ss[j]);
-        r2[j] = bf16_round(x2[j] * cc[j]) + bf16_round(x1[j] * ss[j]);
-      }
-      o1 = pack8(r1);
-      o2 = pack8(r2);
+      rope_rotate_pieces(a, bb, __ldg(cos_t + pos * hv + c), __ldg(sin_t + pos * hv + c), o1, o2);
     }
     uint4* dst;
     if (head < Hq)

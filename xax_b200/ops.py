@@ -568,6 +568,52 @@ def attn_decode_cast_tp(q_rot, k_cache, v_cache, positions, peer, *, scale=None,
     return q, rs, ri
 
 
+def attn_decode_append(qkv, k_cache, v_cache, positions, cos, sin, Hq: int, *, scale=None, k_is_rotated=True,
+                       window=None, want_out=True, cast=False, peer=None, workspace=None):
+    """A decode step's cache append and attention as one call: ``qkv`` [B, (Hq + 2 Hkv) * D] is the fused
+    projection's output for the new token of every sequence (not yet in the cache); the query is rotated
+    inside the attention kernel, the new key / value are written to cache row positions[b] by it.  Same
+    results, bit for bit, as kv_append_rope followed by attn_decode / attn_decode_cast / attn_decode_window /
+    attn_decode_cast_tp.  Returns (out bf16 [B, Hq, D] or None, q e4m3 [B, Hq*D] or None, scale, inv_scale)."""
+    if qkv.dim() != 2 or k_cache.dim() != 4 or v_cache.shape != k_cache.shape:
+        raise ValueError(f"attention: qkv must be [B, (Hq + 2 Hkv) * D] and both caches [B, max_len, Hkv, D], got "
+                         f"{tuple(qkv.shape)}, {tuple(k_cache.shape)}, {tuple(v_cache.shape)}")
+    B, max_len, Hkv, D = k_cache.shape
+    for name, t in (("qkv", qkv), ("k_cache", k_cache), ("v_cache", v_cache), ("cos", cos), ("sin", sin)):
+        if not t.is_cuda or t.dtype != BF16 or not t.is_contiguous():
+            raise ValueError(f"attention: {name} must be a contiguous bfloat16 CUDA tensor")
+    if not positions.is_cuda or positions.dtype != torch.int32 or not positions.is_contiguous() or \
+            positions.numel() != B:
+        raise ValueError(f"attention: positions must be a contiguous int32 CUDA tensor with one entry per sequence ({B})")
+    if qkv.shape[0] != B or qkv.shape[1] < (Hq + 2 * Hkv) * D:
+        raise ValueError(f"attention: qkv {tuple(qkv.shape)} does not hold {Hq} + 2 x {Hkv} heads of {D} for {B} sequences")
+    if cos.shape != sin.shape or cos.dim() != 2 or cos.shape[1] != D // 2 or cos.shape[0] < max_len:
+        raise ValueError("attention: cos / sin must be [table_len >= max_len, D/2]")
+    if peer is not None and not cast:
+        raise ValueError("attention: the exchange over ranks goes with the cast output")
+    ctx, st, lib = _c()
+    dev = qkv.device
+    if workspace is None:
+        workspace = attn_decode_workspace(B, Hq, D, max_len, dev)
+    out = torch.empty((B, Hq, D), dtype=BF16, device=dev) if want_out else None
+    q = rs = ri = None
+    if cast:
+        q = torch.empty((B, Hq * D), dtype=E4M3, device=dev)
+        rs = torch.empty((B,), dtype=torch.float32, device=dev)
+        ri = torch.empty((B,), dtype=torch.float32, device=dev)
+    elif not want_out:
+        raise ValueError("attention: nothing to compute (neither out nor the cast output wanted)")
+    if scale is None:
+        scale = 1.0 / math.sqrt(D)
+    ptrs, rank, world, inbox, sync = peer if peer is not None else (None, 0, 1, 0, 0)
+    check(lib.xaxb_attn_decode_append(ctx, st, ptr(qkv), qkv.stride(0), ptr(k_cache), ptr(v_cache), ptr(positions), B,
+                                      Hq, Hkv, D, max_len, float(scale), 1 if k_is_rotated else 0, ptr(cos), ptr(sin),
+                                      cos.shape[0], -1 if window is None else int(window), ptr(out), ptr(q), ptr(rs),
+                                      ptr(ri), ptr(workspace), workspace.numel() * 4, ptrs, rank, world, inbox, sync),
+          "attn_decode_append")
+    return out, q, rs, ri
+
+
 def silu_mul_cast_tp(gate_up, dim: int, peer):
     """silu(gate) * up of this rank's slice of the hidden width, cast per row with the amax over all
     ranks (exchanged inside the kernel).  gate_up: bf16 [rows, 2*dim] (gate | up).  Returns
