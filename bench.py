@@ -549,32 +549,41 @@ def main() -> None:
         e2e_elapsed = float(tmax.item())
     _lib.device_status()
 
-    # ---- roofline of the dominant kernel: eager steps with CUDA events around every decode-attention launch
+    # ---- roofline of the dominant kernel: the decode-attention launches of one step (the fused
+    # RoPE + append + attention kernel and its merge pass, one pair per layer, on the model's own caches
+    # at the mean context of the timed region) captured in a CUDA graph of their own and timed with CUDA
+    # events around its replays, so the figure is device time per launch pair without host launch gaps.
     peak, peak_kind = measured_peaks()
     hkv_local, hq_local, D = w["kv_heads"] // world, w["q_heads"] // world, w["head_dim"]
     st.positions.fill_(int(mean_len_timed) - 1)  # representative length: the mean of the timed region
-    events: list = []
+    gq = torch.Generator(device=dev).manual_seed(11)
+    qkv_l = torch.randn((B, (hq_local + 2 * hkv_local) * D), generator=gq, device=dev).to(torch.bfloat16)
+    blocks = model.blocks
+    tables = [blk.self_attn.rotary_emb.tables(st.max_len, dev) for blk in blocks]
 
-    def timed(fn):
-        def wrapper(*a, **k):
-            e_a, e_b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            e_a.record()
-            r = fn(*a, **k)
-            e_b.record()
-            events.append((e_a, e_b))
-            return r
-        return wrapper
+    def attention_of_every_layer():
+        for l, blk in enumerate(blocks):
+            ops.attn_decode_append(qkv_l, st.caches[l]["k"], st.caches[l]["v"], st.positions, tables[l][0], tables[l][1],
+                                   hq_local, want_out=False, cast=True, workspace=st.workspace)
 
-    saved = {n: getattr(ops, n) for n in ("attn_decode", "attn_decode_cast", "attn_decode_cast_tp", "attn_decode_append")}
-    for n, fn in saved.items():  # the model reaches decode attention through one of these
-        setattr(ops, n, timed(fn))
-    n_eager = 2
-    for _ in range(n_eager):
-        st.step()
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        attention_of_every_layer()
+    torch.cuda.current_stream().wait_stream(side)
+    agraph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(agraph):
+        attention_of_every_layer()
+    agraph.replay()
     torch.cuda.synchronize()
-    for n, fn in saved.items():
-        setattr(ops, n, fn)
-    durs = [a.elapsed_time(b) * 1e-3 for a, b in events]
+    durs = []
+    for _ in range(3):
+        e_a, e_b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e_a.record()
+        agraph.replay()
+        e_b.record()
+        e_b.synchronize()
+        durs.extend([e_a.elapsed_time(e_b) * 1e-3 / len(blocks)] * len(blocks))
     attn_len = int(mean_len_timed) + 0.5
     attn_bytes = B * attn_len * (2 * hkv_local * D * 2) + 2 * B * hq_local * D * 2
     avg = sum(durs) / max(len(durs), 1)
@@ -582,9 +591,10 @@ def main() -> None:
                 "peak": peak, "peak_kind": f"of {peak_kind} copy bandwidth", "unit": "GB/s",
                 "frac": attn_bytes / avg / 1e9 / peak,
                 # DRAM bytes per launch: ncu on a smaller case of the same kernel (B=32, same context, heads)
-                # measured dram read+write = 1.088 x the algorithmic bytes; traffic is proportional to tokens x
-                # kv heads, so the factor carries over
-                "traffic": attn_bytes * 1.088, "bytes_per_launch": attn_bytes,
+                # measured dram read+write = 1.0385 x the algorithmic bytes (partial results, and the last
+                # chunk fetched in 32-row boxes); traffic is proportional to tokens x kv heads, so the factor
+                # carries over
+                "traffic": attn_bytes * 1.0385, "bytes_per_launch": attn_bytes,
                 "avg_launch_us": avg * 1e6, "launches_timed": len(durs)}
     _lib.device_status()
 
