@@ -627,7 +627,8 @@ __global__ void attn_decode_merge_kernel(const float* __restrict__ ws_o, const f
     num = fmaf(w, ws_o[(base + c) * D + d], num);
     den = fmaf(w, ws_ml[(base + c) * 2 + 1], den);
   }
-  out[((long long)b * Hq + h) * D + d] = __float2bfloat16_rn(num / den);
+  // (times the reciprocal, as the merge + cast pass and the prefill kernel normalise: the three agree bit for bit)
+  out[((long long)b * Hq + h) * D + d] = __float2bfloat16_rn(num * (1.0f / den));
 }
 
 // Merge + per-token cast as a kernel of its own: one CTA of 512 threads per sequence, one work item
@@ -733,14 +734,15 @@ static int decode_launch(xaxb_ctx* ctx_, void* stream, const void* q_rot_bf16, c
   int lanes = max_chunks;  // partial results per (sequence, head) row of the workspace
   {
     // Chunks are dealt to `lanes` CTAs per (sequence, kv head); each CTA walks its chunks with
-    // the next tile's loads in flight.  As few lanes as still give about five resident waves of CTAs
-    // (three CTAs fit an SM): long walks amortise a CTA's set-up and leave fewer partial results to
-    // merge, but with only two or three waves the last one leaves SMs idle.  Measured at B = 128, 8 kv
-    // heads, 17 chunks: 1 lane 175 us, 2 - 4 lanes 171, 5 lanes 173, 7 lanes 175, 10 lanes 177; on the
-    // ragged B = 32 case (4 - 64 chunks): 2 lanes 103.5, 4 lanes 101.4, 8 lanes 99.3, 16 lanes 103.3.
+    // the next tile's loads in flight.  About seven chunks per CTA: long walks amortise a CTA's set-up
+    // and leave fewer partial results to merge, short ones balance the SMs.  Measured (attention +
+    // merge): B = 128, 8 kv heads, 17 of 20 chunks: 1 / 2-4 / 5 / 7 / 10 lanes 175 / 171 / 173 / 175 /
+    // 177 us; the ragged B = 32 case of 4 - 64 chunks: 2 / 4 / 8 / 16 lanes 103.5 / 101.4 / 99.3 /
+    // 103.3 us; B = 64, 4 kv heads, 5 of 6 chunks: 1 / 2 / 3 / 6 lanes 20.2 / 23.0 / 22.9 / 25.7 us.
+    // With fewer (sequence, head) groups than SMs the lanes are raised so that every SM has a CTA.
     const long long groups = (long long)B * Hkv;
-    const long long want = 5ll * 3ll * ctx->num_sms;
-    lanes = (int)((want + groups - 1) / groups);
+    lanes = (max_chunks + 6) / 7;
+    if (groups * lanes < ctx->num_sms) lanes = (int)((ctx->num_sms + groups - 1) / groups);
     if (g_decode_variant >= 11) {  // test hook: a fixed number of chunks per CTA
       const int per_cta = g_decode_variant - 10;
       lanes = (max_chunks + per_cta - 1) / per_cta;
