@@ -355,6 +355,17 @@ int xaxb_attn_prefill_window(xaxb_ctx* ctx, void* stream, const void* q_rot_bf16
                              int64_t Hkv, int64_t D, int64_t max_len, float softmax_scale, int64_t window,
                              void* out_bf16);
 
+/*
+ * Cross-attention core (xax/arch/attention.py:1176-1182: jax.nn.dot_product_attention with
+ * is_causal=False): T query rows per sequence, every one of which sees all kv_lens[b] rows of that
+ * sequence's keys / values.  q: bf16 [B*T, Hq, D] (rotated by the caller where the block has RoPE);
+ * k, v: bf16 [B, max_len, Hkv, D], rows kv_lens[b] .. max_len-1 ignored; query head h reads kv head
+ * h / (Hq/Hkv).  The prefill kernel with its causal mask switched off.  out: bf16 [B*T, Hq, D].
+ */
+int xaxb_attn_cross(xaxb_ctx* ctx, void* stream, const void* q_bf16, const void* k_bf16, const void* v_bf16,
+                    const int32_t* kv_lens, int64_t B, int64_t T, int64_t Hq, int64_t Hkv, int64_t D, int64_t max_len,
+                    float softmax_scale, void* out_bf16);
+
 /* Straightforward CUDA-core attention with the contract of xaxb_attn_prefill (T = 1 gives
  * decode): a second opinion for the tensor-core kernels in tests; never used by the
  * module layer. */

@@ -351,26 +351,87 @@ class SelfAttentionBlock:
         return out, {"k": k, "v": v, "position": np.int32(new_position)}
 
 
-class TransformerBlock:
-    """xax/arch/attention.py:1214-1510 (pre-norm, self-attention + feed-forward)."""
+class CrossAttentionBlock:
+    """xax/arch/attention.py:983-1205: queries from x, keys / values from a context sequence, every query sees
+    every context token (is_causal=False), as many kv heads as query heads.  RoPE, when enabled, is the class
+    default style of RotaryEmbedding.build ("interleaved", :1035), keys at positions 0 .. S-1 (:1090-1093), queries
+    at cache position + 0 .. T-1 (:1179-1181)."""
 
-    def __init__(self, self_attn, feed_forward, attn_norm, mlp_norm):
+    def __init__(self, q_proj, k_proj, v_proj, output_proj, rotary_emb=None, *, num_heads, head_dim):
+        self.q_proj, self.k_proj, self.v_proj, self.output_proj = q_proj, k_proj, v_proj, output_proj
+        self.rotary_emb, self.num_heads, self.head_dim = rotary_emb, num_heads, head_dim
+
+    def _project_kv(self, kv_sn):
+        kv_sn = np.asarray(kv_sn)
+        assert kv_sn.ndim == 2
+        k, _ = apply_linear_batched(self.k_proj, kv_sn)  # :1082-1083
+        v, _ = apply_linear_batched(self.v_proj, kv_sn)
+        S = kv_sn.shape[0]
+        k = k.reshape(S, self.num_heads, self.head_dim)
+        v = v.reshape(S, self.num_heads, self.head_dim)
+        if self.rotary_emb is not None:  # :1090-1093
+            k = self.rotary_emb.apply_rotary_embeddings(k, np.arange(S).astype(np.int32))
+        return k, v
+
+    def init_cache(self, kv_sn):
+        """:1062-1108 (fp8_scales=None)."""
+        k, v = self._project_kv(kv_sn)
+        return {"k": k, "v": v, "position": np.int32(0)}
+
+    def forward(self, q_tn, *, kv_sn=None, cache=None):
+        """:1110-1205 (fp8_scales=None)."""
+        q_tn = np.asarray(q_tn)
+        assert q_tn.ndim == 2
+        q, _ = apply_linear_batched(self.q_proj, q_tn)  # :1135
+        T = q_tn.shape[0]
+        q = q.reshape(T, self.num_heads, self.head_dim)
+        if cache is not None:  # :1146-1149
+            k, v, start = cache["k"], cache["v"], int(cache["position"])
+        elif kv_sn is not None:  # :1150-1167
+            k, v = self._project_kv(kv_sn)
+            start = 0
+        else:
+            raise ValueError("Either `cache` or `kv_sn` must be provided.")
+        if self.rotary_emb is not None:  # :1171-1173
+            q = self.rotary_emb.apply_rotary_embeddings(q, (np.arange(T) + start).astype(np.int32))
+        attn = dot_product_attention(q, k, v, is_causal=False, scale=1.0 / math.sqrt(self.head_dim))  # :1176-1182
+        out, _ = apply_linear_batched(self.output_proj, attn.reshape(T, -1))  # :1188-1189
+        return out, {"k": k, "v": v, "position": np.int32(start + T)}
+
+
+class TransformerBlock:
+    """xax/arch/attention.py:1214-1510 (pre-norm: self-attention, optional cross-attention, feed-forward)."""
+
+    def __init__(self, self_attn, feed_forward, attn_norm, mlp_norm, cross_attn=None, cross_attn_norm=None):
         self.self_attn, self.feed_forward = self_attn, feed_forward
         self.attn_norm, self.mlp_norm = attn_norm, mlp_norm
+        self.cross_attn, self.cross_attn_norm = cross_attn, cross_attn_norm
 
-    def init_cache(self, max_len=None, dtype=bfloat16):
-        return {"self_attn": self.self_attn.init_cache(max_len, dtype)}  # :1404-1405
+    def init_cache(self, max_len=None, dtype=bfloat16, context_sn=None):
+        cache = {"self_attn": self.self_attn.init_cache(max_len, dtype)}  # :1404-1405
+        if self.cross_attn is not None:  # :1407-1411
+            if context_sn is None:
+                raise ValueError("context_sn must be provided if cross_attn is not None")
+            cache["cross_attn"] = self.cross_attn.init_cache(context_sn)
+        return cache
 
-    def forward(self, x_tn, *, cache=None):
+    def forward(self, x_tn, *, cache=None, context_sn=None):
         """:1443-1510."""
         x_tn = np.asarray(x_tn)
         norm_x = self.attn_norm(x_tn)  # :1468
         attn_out, attn_cache = self.self_attn.forward(norm_x, cache=None if cache is None else cache["self_attn"])
         x_tn = rnd(f32(x_tn) + f32(attn_out), promote(x_tn.dtype, attn_out.dtype))  # :1481
+        new_cache = {"self_attn": attn_cache}
+        if self.cross_attn is not None:  # :1483-1500
+            norm_x = self.cross_attn_norm(x_tn)
+            c_out, c_cache = self.cross_attn.forward(norm_x, kv_sn=context_sn,
+                                                     cache=None if cache is None else cache.get("cross_attn"))
+            new_cache["cross_attn"] = c_cache
+            x_tn = rnd(f32(x_tn) + f32(c_out), promote(x_tn.dtype, c_out.dtype))
         norm_x = self.mlp_norm(x_tn)  # :1503
         ff = self.feed_forward(norm_x)  # :1507
         x_tn = rnd(f32(x_tn) + f32(ff), promote(x_tn.dtype, ff.dtype))  # :1508
-        return x_tn, {"self_attn": attn_cache}
+        return x_tn, new_cache
 
 
 def build_block(rng, *, embed_dim, num_heads, num_kv_heads, head_dim, ff_dim, rope_theta=10000.0, norm_eps=1e-6,

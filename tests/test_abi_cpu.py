@@ -141,8 +141,12 @@ def test_unsupported_features_raise_clearly():
 
     sa = xax.SelfAttentionBlock.build(64, 2, key=0, context_length=8, use_attention_sinks=True, device="cpu")
     assert sa.local_window_size == 7 and sa.sinks.shape == (2,)  # :660, :652-654
-    with pytest.raises(ValueError, match="outside the path"):
-        xax.TransformerBlock.build(64, 2, 128, key=0, cross_attention=True, device="cpu")
+    xblk = xax.TransformerBlock.build(64, 2, 128, key=0, cross_attention=True, causal=True, use_rotary_embeddings=True,
+                                      norm_type="rmsnorm", feedforward_type="swiglu", device="cpu")
+    assert type(xblk.cross_attn).__name__ == "CrossAttentionBlock" and xblk.cross_attn_norm is not None
+    assert xblk.cross_attn.rotary_emb.style == "interleaved"  # the class default, as CrossAttentionBlock.build gets it
+    with pytest.raises(ValueError, match="context_sn must be provided"):
+        xblk.init_cache(max_len=8)
     with pytest.raises(ValueError):
         xax.TransformerBlock.build(64, 2, 128, key=0, device="cpu")  # layernorm / mlp defaults are not on the path
     with pytest.raises(ValueError, match="float8_e4m3fn only"):

@@ -1,0 +1,161 @@
+"""Cross-attention (xax/arch/attention.py:983-1205 and the cross-attention branch of TransformerBlock.forward,
+:1483-1500) against the CPU restatement: the attention core with the causal mask off, the block with and
+without RoPE / FP8 / a cache, a transformer block with the cross-attention sub-block, Transformer.decode."""
+
+import numpy as np
+import pytest
+import torch
+
+from helpers import _lin_from_oracle, bf16, block_from_oracle, rel_fro, to_numpy, to_torch
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("B,T,S,Hq,Hkv,D", [(1, 1, 5, 4, 4, 64), (2, 77, 64, 8, 8, 128), (2, 130, 200, 8, 2, 128),
+                                            (3, 5, 129, 4, 4, 64), (1, 300, 63, 2, 2, 128)])
+def test_attention_core_without_the_causal_mask(B, T, S, Hq, Hkv, D):
+    from oracle import attention as oattn
+    from xax_b200 import _lib, ops
+
+    rng = np.random.default_rng(B * 100 + T + S)
+    q = rng.standard_normal((B, T, Hq, D)).astype(np.float32).astype(bf16)
+    k = rng.standard_normal((B, S, Hkv, D)).astype(np.float32).astype(bf16)
+    v = rng.standard_normal((B, S, Hkv, D)).astype(np.float32).astype(bf16)
+    lens = rng.integers(max(1, S // 2), S + 1, B).astype(np.int32)
+    lens[0] = S
+    got = ops.attn_cross(to_torch(q.reshape(B * T, Hq, D)), to_torch(k), to_torch(v), to_torch(lens))
+    _lib.device_status()
+    got = to_numpy(got).reshape(B, T, Hq, D)
+    for b in range(B):
+        want = oattn.dot_product_attention(q[b], k[b, :lens[b]], v[b, :lens[b]], is_causal=False)
+        assert rel_fro(got[b], want) < 1e-2, (b, rel_fro(got[b], want))
+    # rows past a sequence's length hold NaN: they must not leak into the result
+    k2, v2 = k.copy(), v.copy()
+    for b in range(B):
+        k2[b, lens[b]:] = np.nan
+        v2[b, lens[b]:] = np.nan
+    again = ops.attn_cross(to_torch(q.reshape(B * T, Hq, D)), to_torch(k2), to_torch(v2), to_torch(lens))
+    assert torch.equal(again.reshape(B, T, Hq, D), to_torch(got))
+
+
+def _oracle_cross(rng, embed, heads, fp8, rope):
+    from oracle import attention as oattn
+    from oracle.fp8 import Fp8Linear
+
+    D = embed // heads
+
+    def lin(s=1.0):
+        w = (rng.standard_normal((embed, embed), dtype=np.float32) * np.float32(0.05 * s)).astype(bf16)
+        b = (rng.standard_normal(embed, dtype=np.float32) * np.float32(0.01)).astype(bf16)
+        return Fp8Linear(w, b) if fp8 else oattn.Linear(w, b)
+
+    rot = oattn.RotaryEmbedding(D, base=10000.0, style="interleaved") if rope else None
+    return oattn.CrossAttentionBlock(lin(), lin(), lin(), lin(0.5), rot, num_heads=heads, head_dim=D)
+
+
+def _mirror_cross(oc):
+    from xax_b200.arch.attention import CrossAttentionBlock, RotaryEmbedding
+
+    rot = None if oc.rotary_emb is None else RotaryEmbedding.build(oc.head_dim, oc.rotary_emb.base, oc.rotary_emb.style)
+    return CrossAttentionBlock(_lin_from_oracle(oc.q_proj), _lin_from_oracle(oc.k_proj), _lin_from_oracle(oc.v_proj),
+                               _lin_from_oracle(oc.output_proj), num_heads=oc.num_heads, head_dim=oc.head_dim,
+                               use_fp8=type(oc.q_proj).__name__ == "Fp8Linear", rotary_emb=rot)
+
+
+@pytest.mark.parametrize("fp8,rope", [(False, False), (False, True), (True, True)])
+def test_cross_attention_block_matches_the_restatement(fp8, rope):
+    from xax_b200 import _lib
+
+    rng = np.random.default_rng(17 + fp8 + 2 * rope)
+    embed, heads, T, S = 256, 4, 37, 90
+    oc = _oracle_cross(rng, embed, heads, fp8, rope)
+    mc = _mirror_cross(oc)
+    x = rng.standard_normal((T, embed)).astype(np.float32).astype(bf16)
+    ctx = rng.standard_normal((S, embed)).astype(np.float32).astype(bf16)
+    want, wcache = oc.forward(x, kv_sn=ctx)
+    got, gcache, scales = mc.forward(to_torch(x), kv_sn=to_torch(ctx))
+    _lib.device_status()
+    assert scales is None
+    e = rel_fro(to_numpy(got), want)
+    if fp8:
+        # Chained FP8 layers (projections -> attention -> output projection): the reference's own two
+        # executions -- dequantise + bf16 matmul on a CPU, FP8 matmul on a GPU -- already differ by more than
+        # 1e-2 after two layers, because a bf16-ulp difference flips e4m3 codes of the next cast.  The device
+        # path has FP8-matmul semantics and must be no further from that execution than the two are from each other.
+        from oracle import fp8 as ofp8
+
+        old = ofp8.MATMUL_MODE
+        try:
+            ofp8.MATMUL_MODE = "fp8_gemm"
+            want_mm, _ = oc.forward(x, kv_sn=ctx)
+        finally:
+            ofp8.MATMUL_MODE = old
+        oo, e_mm = rel_fro(want_mm, want), rel_fro(to_numpy(got), want_mm)
+        print(f"cross-attention block (fp8, rope={rope}): {e_mm:.3e} vs FP8-matmul oracle, {e:.3e} vs QDQ oracle, "
+              f"oracle vs oracle {oo:.3e}")
+        assert e_mm <= 1.25 * oo + 2e-3
+    else:
+        print(f"cross-attention block (bf16, rope={rope}): rel err {e:.3e}")
+        assert e < 1e-2
+    assert int(gcache["position"]) == T == int(wcache["position"])
+    assert rel_fro(to_numpy(gcache["k"]), wcache["k"]) < 1e-2 and rel_fro(to_numpy(gcache["v"]), wcache["v"]) < 1e-2
+    # second call through the cache: the context is not projected again, the queries' positions continue at T
+    x2 = rng.standard_normal((3, embed)).astype(np.float32).astype(bf16)
+    want2, wcache2 = oc.forward(x2, cache=wcache)
+    got2, gcache2, _ = mc.forward(to_torch(x2), cache=gcache)
+    assert rel_fro(to_numpy(got2), want2) < (5e-2 if fp8 else 1e-2)
+    assert int(gcache2["position"]) == T + 3 == int(wcache2["position"])
+    assert gcache2["k"] is gcache["k"]
+    # init_cache gives the same keys / values as the first forward
+    c0, _ = mc.init_cache(to_torch(ctx))
+    assert torch.equal(c0["k"], gcache["k"]) and torch.equal(c0["v"], gcache["v"]) and int(c0["position"]) == 0
+    with pytest.raises(ValueError):
+        mc.forward(to_torch(x))
+
+
+def test_transformer_block_with_cross_attention_and_transformer_decode():
+    from oracle import attention as oattn
+    from xax_b200 import _lib
+    from xax_b200.arch.attention import RMSNorm, Transformer
+
+    rng = np.random.default_rng(5)
+    embed, heads, T, S = 256, 4, 21, 50
+    ob = oattn.build_block(rng, embed_dim=embed, num_heads=heads, num_kv_heads=heads, head_dim=embed // heads, ff_dim=512,
+                           fp8_attn=False, fp8_mlp=False, out_scale=0.5, std=0.05)
+    ob.cross_attn = _oracle_cross(rng, embed, heads, False, True)
+    ob.cross_attn_norm = oattn.RMSNorm.build(embed, 1e-6, bf16)
+    mb = block_from_oracle(ob)
+    mb.cross_attn = _mirror_cross(ob.cross_attn)
+    mb.cross_attn_norm = RMSNorm(to_torch(ob.cross_attn_norm.weight), ob.cross_attn_norm.eps)
+    x = rng.standard_normal((T, embed)).astype(np.float32).astype(bf16)
+    ctx = rng.standard_normal((S, embed)).astype(np.float32).astype(bf16)
+    want, wcache = ob.forward(x, context_sn=ctx)
+    got, gcache = mb.forward(to_torch(x), context_sn=to_torch(ctx))
+    _lib.device_status()
+    e = rel_fro(to_numpy(got), want)
+    print(f"transformer block with cross-attention: rel err {e:.3e}")
+    assert e < 1e-2 and set(gcache) == {"self_attn", "cross_attn"}
+    # with caches: prime with the first tokens, then one more token
+    wc = ob.init_cache(max_len=T + 1, context_sn=ctx)
+    gc = mb.init_cache(max_len=T + 1, context_sn=to_torch(ctx))
+    w1, wc = ob.forward(x, cache=wc)
+    g1, gc = mb.forward(to_torch(x), cache=gc)
+    x_next = rng.standard_normal((1, embed)).astype(np.float32).astype(bf16)
+    w2, _ = ob.forward(x_next, cache=wc)
+    g2, _ = mb.forward(to_torch(x_next), cache=gc)
+    assert rel_fro(to_numpy(g1), w1) < 1e-2 and rel_fro(to_numpy(g2), w2) < 1e-2
+
+    # the encoder-decoder entry point: shapes, finiteness, and the cache it returns can be fed back
+    tr = Transformer.build(100, 128, 2, 256, 2, output_size=100, key=3, causal=True, cross_attention=True,
+                           use_rotary_embeddings=True, device="cuda")
+    toks = torch.tensor([1, 5, 7, 9], device="cuda")
+    ctx_toks = torch.tensor([2, 4, 6, 8, 10, 12], device="cuda")
+    h, cache = tr.decode(toks, ctx_toks)
+    assert h.shape == (4, 128) and bool(torch.isfinite(h.float()).all())
+    cache0 = tr.layers.init_cache(x_tn=tr.token_embedding.weight[ctx_toks.long()], max_len=16)
+    h1, cache1 = tr.decode(toks, ctx_toks, cache=cache0)
+    # a primed context cache gives the same result as projecting the context inside the call
+    assert float((h1.float() - h.float()).norm() / h.float().norm()) < 1e-3
+    h2, _ = tr.decode(torch.tensor([11], device="cuda"), ctx_toks, cache=cache1)
+    assert h2.shape == (1, 128) and bool(torch.isfinite(h2.float()).all())
+    _lib.device_status()

@@ -104,8 +104,10 @@ def test_transformer_stack_and_transformer():
     b = model.generate_sequence(toks, 6, temperature=0.8, key=11)
     assert a.shape == (10,) and torch.equal(a, b) and torch.equal(a[:4], toks)
     assert int(a.max()) < 96 and int(a.min()) >= 0
-    with pytest.raises(ValueError, match="cross-attention"):
-        model.decode(toks, toks)
+    # a stack built without cross-attention ignores the context, as the reference's blocks do (:1483)
+    h_dec, _ = model.decode(toks, toks)
+    h_enc, _ = model.encode(toks)
+    assert torch.equal(h_dec, h_enc)
 
 
 def test_lora_branch_of_apply_linear_vs_oracle():

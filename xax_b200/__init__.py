@@ -18,6 +18,7 @@ NAME_MAP = {
     "SwiGLU": "arch.attention", "TransformerBlock": "arch.attention", "apply_linear": "arch.attention",
     "can_use_cudnn_attention": "arch.attention", "Linear": "arch.attention", "Embedding": "arch.attention",
     "TransformerStack": "arch.attention", "Transformer": "arch.attention", "TransformerCache": "arch.attention",
+    "CrossAttentionBlock": "arch.attention",
     # xax.arch.llm
     "LLM": "arch.llm", "LLMConfig": "arch.llm", "llm_generate": "arch.llm", "llm_generate_jit": "arch.llm",
     "llm_generate_batch": "arch.llm", "llm_generate_stream": "arch.llm", "TokenSampler": "arch.llm",

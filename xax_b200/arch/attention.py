@@ -101,19 +101,20 @@ def apply_linear(x: torch.Tensor, linear, *, residual: torch.Tensor | None = Non
     raise ValueError(f"Unsupported linear layer type: {type(linear)}")
 
 
-def _apply_linear_batched(layer, x: torch.Tensor, scales=None):
+def _apply_linear_batched(layer, x: torch.Tensor, scales=None, residual=None):
     """xax/arch/attention.py:244-287: the layer applied to every row of x on its own.  Current
     scaling: every row gets its own scale (:279).  Delayed scaling: all rows are cast with the
-    incoming scales and the updated scales of the LAST row are returned (:273-275)."""
+    incoming scales and the updated scales of the LAST row are returned (:273-275).  ``residual`` (not in
+    the reference's signature) is added in the GEMM's epilogue."""
     if isinstance(layer, Fp8Linear):
         flat = x.reshape(-1, x.shape[-1])
         if scales is not None and layer.use_fp8:
-            out, _ = layer(flat, scales)            # shared incoming scales: same bytes row by row
+            out, _ = layer(flat, scales, residual=residual)  # shared incoming scales: same bytes row by row
             _, new_scales = layer(flat[-1:], scales)  # history slot 0 <- amax of the last row
             return out.reshape(*x.shape[:-1], -1), new_scales
-        out, _ = layer(flat, per_row=True)
+        out, _ = layer(flat, per_row=True, residual=residual)
         return out.reshape(*x.shape[:-1], -1), None
-    return apply_linear(x, layer), None  # :286
+    return apply_linear(x, layer, residual=residual), None  # :286
 
 
 class RMSNorm:
@@ -618,17 +619,102 @@ class SelfAttentionBlock:
         return out, new_cache
 
 
+class CrossAttentionBlock:
+    """xax/arch/attention.py:983-1205: queries from the decoder stream, keys and values from a context
+    sequence; every query sees every context token (``is_causal=False``), as many kv heads as query heads.
+    The cache holds the projected (and, with RoPE, rotated) context once; ``forward`` then only projects
+    the queries.  Attention runs on the prefill kernel with its causal mask switched off
+    (``ops.attn_cross``)."""
+
+    def __init__(self, q_proj, k_proj, v_proj, output_proj, *, num_heads: int, head_dim: int, use_fp8: bool = False,
+                 rotary_emb: RotaryEmbedding | None = None):
+        self.q_proj, self.k_proj, self.v_proj, self.output_proj = q_proj, k_proj, v_proj, output_proj
+        self.num_heads, self.head_dim, self.use_fp8, self.rotary_emb = num_heads, head_dim, use_fp8, rotary_emb
+
+    @classmethod
+    def build(cls, embed_dim: int, num_heads: int, *, key=None, use_rotary_embeddings: bool = False,
+              rotary_base: float = 10000.0, use_fp8: bool = False, compute_dtype=BF16, device=None) -> "CrossAttentionBlock":
+        """Same keyword arguments as the reference (:995-1047).  RoPE, when asked for, has the class default
+        style of ``RotaryEmbedding.build`` ("interleaved"), as there (:1035)."""
+        head_dim = embed_dim // num_heads
+        assert head_dim * num_heads == embed_dim, "embed_dim must be divisible by num_heads"  # :1025
+        seed = int(key or 0) if not isinstance(key, torch.Generator) else int(key.initial_seed())
+        projs = [_make_linear(embed_dim, embed_dim, seed * 4 + i, use_fp8=use_fp8, compute_dtype=compute_dtype,
+                              device=device) for i in range(4)]
+        rotary = RotaryEmbedding.build(head_dim=head_dim, base=rotary_base) if use_rotary_embeddings else None
+        return cls(*projs, num_heads=num_heads, head_dim=head_dim, use_fp8=use_fp8, rotary_emb=rotary)
+
+    def _project_kv(self, kv_sn: torch.Tensor, fp8_scales):
+        if kv_sn.dim() != 2:
+            raise ValueError(f"expected rank 2 context (kv_seq_len, embed_dim), got rank {kv_sn.dim()}")
+        S = kv_sn.shape[0]
+        x = kv_sn.to(BF16).contiguous()
+        k, new_k = _apply_linear_batched(self.k_proj, x, fp8_scales.get("k_proj") if fp8_scales else None)
+        v, new_v = _apply_linear_batched(self.v_proj, x, fp8_scales.get("v_proj") if fp8_scales else None)
+        k = k.reshape(S, self.num_heads, self.head_dim)
+        v = v.reshape(S, self.num_heads, self.head_dim).contiguous()
+        if self.rotary_emb is not None:  # :1090-1093: the context's positions are fixed, K is stored rotated
+            k = self.rotary_emb.apply_rotary_embeddings(k, torch.arange(S, device=x.device, dtype=torch.int32))
+        return k.contiguous(), v, new_k, new_v
+
+    def init_cache(self, kv_sn: torch.Tensor, fp8_scales=None):
+        """:1062-1108.  Returns (cache, updated FP8 scales or None)."""
+        k, v, new_k, new_v = self._project_kv(kv_sn, fp8_scales)
+        updated = None
+        if fp8_scales is not None and self.use_fp8:
+            updated = dict(fp8_scales)
+            if new_k is not None:
+                updated["k_proj"] = new_k
+            if new_v is not None:
+                updated["v_proj"] = new_v
+        return {"k": k, "v": v, "position": torch.zeros((), dtype=torch.int32, device=k.device)}, updated
+
+    def forward(self, q_tn: torch.Tensor, *, kv_sn=None, cache=None, fp8_scales=None, residual=None):
+        """:1110-1205: (output (q_seq_len, embed_dim), cache, updated FP8 scales or None).  ``residual`` (an
+        extension) is added to the output inside the output projection's GEMM."""
+        if q_tn.dim() != 2:
+            raise ValueError(f"expected rank 2 input (q_seq_len, embed_dim), got rank {q_tn.dim()}")
+        T = q_tn.shape[0]
+        H, D = self.num_heads, self.head_dim
+        q, new_q = _apply_linear_batched(self.q_proj, q_tn.to(BF16).contiguous(),
+                                         fp8_scales.get("q_proj") if fp8_scales else None)
+        q = q.reshape(T, H, D)
+        new_k = new_v = None
+        if cache is not None:  # :1146-1149
+            k, v, start = cache["k"], cache["v"], cache["position"]
+        elif kv_sn is not None:  # :1150-1167
+            k, v, new_k, new_v = self._project_kv(kv_sn, fp8_scales)
+            start = torch.zeros((), dtype=torch.int32, device=q.device)
+        else:
+            raise ValueError("Either `cache` or `kv_sn` must be provided.")  # :1169
+        if self.rotary_emb is not None:  # :1171-1173
+            q = self.rotary_emb.apply_rotary_embeddings(
+                q, torch.arange(T, device=q.device, dtype=torch.int32) + start.to(torch.int32))
+        attn = ops.attn_cross(q.contiguous(), k.unsqueeze(0), v.unsqueeze(0), scale=1.0 / math.sqrt(D))
+        out, new_o = _apply_linear_batched(self.output_proj, attn.reshape(T, H * D),
+                                           fp8_scales.get("output_proj") if fp8_scales else None, residual=residual)
+        updated = None
+        if fp8_scales is not None and self.use_fp8:  # :1192-1202
+            updated = {}
+            for name, val in (("q_proj", new_q), ("k_proj", new_k), ("v_proj", new_v), ("output_proj", new_o)):
+                if val is not None:
+                    updated[name] = val
+        new_cache = {"k": k, "v": v, "position": (start + T).to(torch.int32)}
+        return out, new_cache, updated
+
+
 class TransformerBlock:
-    """xax/arch/attention.py:1214-1510: pre-norm block, x + attn(norm(x)), x + ffn(norm(x))."""
+    """xax/arch/attention.py:1214-1510: pre-norm block, x + attn(norm(x)), optionally x + cross_attn(norm(x),
+    context), x + ffn(norm(x))."""
 
     def __init__(self, self_attn: SelfAttentionBlock, feed_forward: SwiGLU, attn_norm: RMSNorm, mlp_norm: RMSNorm, *,
                  num_heads: int, head_dim: int, causal: bool, use_fp8: bool = False, cross_attn=None,
                  cross_attn_norm=None, context_length: int | None = None):
-        if cross_attn is not None or cross_attn_norm is not None:
-            raise ValueError("cross-attention is outside the path this library covers")
+        if (cross_attn is None) != (cross_attn_norm is None):
+            raise ValueError("cross_attn and cross_attn_norm go together")
         self.self_attn, self.feed_forward, self.attn_norm, self.mlp_norm = self_attn, feed_forward, attn_norm, mlp_norm
         self.num_heads, self.head_dim, self.causal, self.use_fp8 = num_heads, head_dim, causal, use_fp8
-        self.cross_attn, self.cross_attn_norm, self.context_length = None, None, context_length
+        self.cross_attn, self.cross_attn_norm, self.context_length = cross_attn, cross_attn_norm, context_length
 
     @classmethod
     def build(cls, embed_dim: int, num_heads: int, ff_dim: int, *, key=None, num_kv_heads: int | None = None,
@@ -644,8 +730,6 @@ class TransformerBlock:
         ``feedforward_type`` "swiglu" (the LLM path).  Like the reference, ``use_fp8`` makes the
         four attention projections FP8 and leaves the SwiGLU on plain linears (:1354-1355);
         ``fp8_mlp=True`` (an extension) builds the SwiGLU from Fp8Linear too."""
-        if cross_attention:
-            raise ValueError("cross-attention is outside the path this library covers")
         if norm_type != "rmsnorm" or feedforward_type != "swiglu":
             raise ValueError("only norm_type='rmsnorm' with feedforward_type='swiglu' is on the path this library covers")
         seed = int(key or 0) if not isinstance(key, torch.Generator) else int(key.initial_seed())
@@ -659,8 +743,15 @@ class TransformerBlock:
             qk_norm_eps=qk_norm_eps, use_attention_sinks=use_attention_sinks, use_fp8=use_fp8,
             compute_dtype=compute_dtype, device=device)
         ff = SwiGLU.build(embed_dim, ff_dim, key=seed * 3 + 2, use_fp8=bool(fp8_mlp), device=device)
+        cross = cross_norm = None
+        if cross_attention:  # :1312-1322
+            cross = CrossAttentionBlock.build(embed_dim, num_heads, key=seed * 3 + 3,
+                                              use_rotary_embeddings=use_rotary_embeddings, rotary_base=rotary_base,
+                                              use_fp8=use_fp8, compute_dtype=compute_dtype, device=device)
+            cross_norm = RMSNorm.build(embed_dim, norm_eps, device)
         return cls(attn, ff, RMSNorm.build(embed_dim, norm_eps, device), RMSNorm.build(embed_dim, norm_eps, device),
-                   num_heads=num_heads, head_dim=hd, causal=causal, use_fp8=use_fp8, context_length=context_length)
+                   num_heads=num_heads, head_dim=hd, causal=causal, use_fp8=use_fp8, cross_attn=cross,
+                   cross_attn_norm=cross_norm, context_length=context_length)
 
     @property
     def embed_dim(self) -> int:
@@ -670,8 +761,15 @@ class TransformerBlock:
                    batch: int | None = None) -> TransformerBlockCache:
         """xax/arch/attention.py:1384-1419."""
         cache: TransformerBlockCache = {"self_attn": self.self_attn.init_cache(max_len=max_len, dtype=dtype, batch=batch)}
-        if fp8_history_length is not None and self.self_attn.use_fp8:
-            cache["self_attn_fp8"] = _init_fp8_scales_cache(fp8_history_length)
+        if self.cross_attn is not None:  # :1407-1411
+            if context_sn is None:
+                raise ValueError("context_sn must be provided if cross_attn is not None")
+            cache["cross_attn"], _ = self.cross_attn.init_cache(kv_sn=context_sn)
+        if fp8_history_length is not None:
+            if self.self_attn.use_fp8:
+                cache["self_attn_fp8"] = _init_fp8_scales_cache(fp8_history_length)
+            if self.cross_attn is not None and self.cross_attn.use_fp8:
+                cache["cross_attn_fp8"] = _init_fp8_scales_cache(fp8_history_length)
         return cache
 
     def init_mask(self, seq_len: int, add_cache: bool = False, batch_dim: bool = False) -> torch.Tensor:
@@ -685,8 +783,8 @@ class TransformerBlock:
         """xax/arch/attention.py:1443-1510 for one sequence (T, H)."""
         if x_tn.dim() != 2:
             raise ValueError(f"expected rank 2 input, got rank {x_tn.dim()}")
-        if context_sn is not None:
-            raise ValueError("cross-attention context is outside the path this library covers")
+        if self.cross_attn is not None:
+            return self._forward_with_cross_attention(x_tn, context_sn, mask, cache, donate)
         if mask is not None:  # accepted when it is the mask the kernels apply anyway
             self.self_attn._require_builtin_mask(mask, x_tn.shape[0], None if cache is None else cache["self_attn"])
         bc = None
@@ -697,6 +795,31 @@ class TransformerBlock:
         out_cache: TransformerBlockCache = {
             "self_attn": {"k": nc["k"][0], "v": nc["v"][0], "position": nc["position"].reshape(())}}
         return x, out_cache
+
+    def _forward_with_cross_attention(self, x_tn, context_sn, mask, cache, donate):
+        """:1466-1508 with the cross-attention sub-block: the three sub-blocks one after the other, each a
+        pre-norm residual branch.  (The fused kernel sequence of ``forward_tokens`` covers the decoder-only
+        block; this path is module by module.)"""
+        x = x_tn.to(BF16).contiguous()
+        T = x.shape[0]
+        attn = self.self_attn
+        if mask is not None:
+            attn._require_builtin_mask(mask, T, None if cache is None else cache["self_attn"])
+        bc = None
+        if cache is not None:
+            a = cache["self_attn"]
+            bc = {"k": a["k"].unsqueeze(0), "v": a["v"].unsqueeze(0), "position": a["position"].reshape(1)}
+        y, _ = ops.rmsnorm(x, self.attn_norm.weight_bf16(), self.attn_norm.eps)
+        x1, nc = attn.forward_tokens(y, 1, T, cache=bc, donate=donate, residual=x)
+        out_cache: TransformerBlockCache = {
+            "self_attn": {"k": nc["k"][0], "v": nc["v"][0], "position": nc["position"].reshape(())}}
+        y, _ = ops.rmsnorm(x1, self.cross_attn_norm.weight_bf16(), self.cross_attn_norm.eps)
+        x2, c_cache, _ = self.cross_attn.forward(y, kv_sn=context_sn, residual=x1,
+                                                 cache=None if cache is None else cache.get("cross_attn"))
+        out_cache["cross_attn"] = c_cache
+        y, _ = ops.rmsnorm(x2, self.mlp_norm.weight_bf16(), self.mlp_norm.eps)
+        x3 = self.feed_forward.forward_tokens(y, 1, T, residual=x2)
+        return x3, out_cache
 
     def forward_tokens(self, x: torch.Tensor, B: int, T: int, *, cache=None, donate: bool = True, workspace=None,
                        advance: bool = True):
@@ -771,9 +894,7 @@ class TransformerStack:
                    max_len: int | None = None) -> TransformerCache:
         """:1583-1602.  The reference sizes the cache from the blocks' ``context_length``; ``max_len`` (an
         extension) overrides it for blocks built without one."""
-        if x_tn is not None:
-            raise ValueError("cross-attention context is outside the path this library covers")
-        return {"layers": {f"layer_{i}": layer.init_cache(max_len=max_len, dtype=dtype,
+        return {"layers": {f"layer_{i}": layer.init_cache(max_len=max_len, dtype=dtype, context_sn=x_tn,
                                                           fp8_history_length=fp8_history_length)
                            for i, layer in enumerate(self.layers)}}
 
@@ -795,8 +916,8 @@ class TransformerStack:
 class Transformer:
     """xax/arch/attention.py:1657-1912: token embedding, a TransformerStack, a final norm and an optional output
     projection, with ``encode`` / ``forward`` / ``predict_sequence`` / ``generate_sequence``.  The final norm is
-    an RMSNorm here (the reference's is a LayerNorm; see TransformerStack); ``decode`` with a cross-attention
-    context is refused."""
+    an RMSNorm here (the reference's is a LayerNorm; see TransformerStack); ``decode`` runs the stack with its
+    cross-attention sub-blocks against an embedded context."""
 
     def __init__(self, token_embedding: Embedding, layers: TransformerStack, layer_norm: RMSNorm, embed_dim: int,
                  causal: bool, use_fp8: bool = False, output_layer=None, context_length: int | None = None):
@@ -834,8 +955,14 @@ class Transformer:
         h, updated = self.layers.forward(emb, mask=mask, cache=cache)
         return self.layer_norm(h), updated
 
-    def decode(self, x_t, context_s, *, mask=None, cache=None):
-        raise ValueError("cross-attention decoding is outside the path this library covers")  # :1788-1818
+    def decode(self, x_t: torch.Tensor, context_s: torch.Tensor, *, mask=None, cache: TransformerCache | None = None):
+        """:1788-1818: token ids (seq_len,) and context token ids (context_len,), both looked up in the token
+        embedding, through the stack with cross-attention -> (normalised hidden states, updated cache)."""
+        table = self.token_embedding.weight
+        emb = ops.embed(x_t.to(torch.int32).reshape(-1), table)
+        ctx = ops.embed(context_s.to(torch.int32).reshape(-1), table)
+        h, updated = self.layers.forward(emb, context_sn=ctx, mask=mask, cache=cache)
+        return self.layer_norm(h), updated
 
     def forward(self, x: torch.Tensor, *, mask=None, cache: TransformerCache | None = None):
         """:1820-1842."""

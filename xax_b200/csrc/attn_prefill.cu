@@ -30,6 +30,10 @@ struct PrefillParams {
   int T, Hq, Hkv;
   float sm_scale;
   int window;  // sliding window: query at position q sees keys q - window .. q; < 0 = unlimited
+  // cross-attention (xax/arch/attention.py:1176-1182, is_causal=False): positions[b] is the number of
+  // context rows of sequence b and every query row sees all of them; only the length mask remains
+  int cross;
+  long long max_len;
   int* d_status;
 };
 
@@ -53,10 +57,12 @@ __global__ void __launch_bounds__(128, 2) attn_prefill_kernel(const __grid_const
   constexpr int kBoxes = D / 64;
   const int qb = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
   const int hk = h / (p.Hq / p.Hkv);
-  const int start = p.positions[b];
   const int q0 = qb * kPfTile;                    // first query index of this CTA
   const int rows_valid = min(kPfTile, p.T - q0);
-  const int last_pos = start + q0 + rows_valid - 1;  // highest key position any row may see
+  // cross-attention: as if every query sat at the context's last position and the sequence began at -T
+  const int kv_len = p.cross ? (int)max(1LL, min((long long)p.positions[b], p.max_len)) : 0;
+  const int start = p.cross ? kv_len - p.T : p.positions[b];
+  const int last_pos = p.cross ? kv_len - 1 : start + q0 + rows_valid - 1;  // highest key position any row may see
   const int win = p.window;
   // with a sliding window the tiles below the first row's window are never loaded
   const int j_lo = win >= 0 ? max(0, start + q0 - win) / kPfKeys : 0;
@@ -127,7 +133,7 @@ __global__ void __launch_bounds__(128, 2) attn_prefill_kernel(const __grid_const
 #pragma unroll
   for (int i = 0; i < D; ++i) o[i] = 0.0f;
   float m_run = -INFINITY, l_run = 0.0f;
-  const int qpos = start + q0 + min(tid, rows_valid - 1);  // rows past T mirror the last valid row
+  const int qpos = p.cross ? kv_len - 1 : start + q0 + min(tid, rows_valid - 1);  // rows past T mirror the last valid row
   const float scale_log2 = p.sm_scale * 1.4426950408889634f;
 
   bool ok = true;
@@ -163,7 +169,7 @@ __global__ void __launch_bounds__(128, 2) attn_prefill_kernel(const __grid_const
     // ---- online softmax on row `tid` of S (two sweeps over TMEM: max, then exp) ------------
     const int kv0 = (j_lo + j) * kPfKeys;
     // some (row, col) of this tile is masked: above the diagonal, or below some row's window
-    const bool diag = kv0 + kPfKeys - 1 > start + q0 || (win >= 0 && kv0 < last_pos - win);
+    const bool diag = kv0 + kPfKeys - 1 > (p.cross ? kv_len - 1 : start + q0) || (win >= 0 && kv0 < last_pos - win);
     const int lo_vis = win >= 0 ? qpos - win : 0;  // lowest key position this row sees
     float m_tile = -INFINITY;
 #pragma unroll 1
@@ -281,7 +287,8 @@ using namespace xaxb;
 
 static int prefill_launch(xaxb_ctx* ctx_, void* stream, const void* q_rot_bf16, const void* k_cache_bf16,
                           const void* v_cache_bf16, const int32_t* positions, int64_t B, int64_t T, int64_t Hq,
-                          int64_t Hkv, int64_t D, int64_t max_len, float softmax_scale, int64_t window, void* out_bf16) {
+                          int64_t Hkv, int64_t D, int64_t max_len, float softmax_scale, int64_t window, void* out_bf16,
+                          int cross = 0) {
   if (!ctx_ || !q_rot_bf16 || !k_cache_bf16 || !v_cache_bf16 || !positions || !out_bf16 || B <= 0 || T <= 0 ||
       Hq <= 0 || Hkv <= 0 || max_len <= 0) {
     set_last_error("attn_prefill: null pointer or non-positive shape");
@@ -306,6 +313,8 @@ static int prefill_launch(xaxb_ctx* ctx_, void* stream, const void* q_rot_bf16, 
   p.T = (int)T, p.Hq = (int)Hq, p.Hkv = (int)Hkv;
   p.sm_scale = softmax_scale;
   p.window = window < 0 ? -1 : (window > 0x3fffffff ? 0x3fffffff : (int)window);
+  p.cross = cross;
+  p.max_len = max_len;
   p.d_status = ctx->d_status;
   dim3 grid((unsigned)((T + kPfTile - 1) / kPfTile), (unsigned)Hq, (unsigned)B);
   if (D == 128) {
@@ -333,4 +342,11 @@ extern "C" int xaxb_attn_prefill_window(xaxb_ctx* ctx_, void* stream, const void
                                         int64_t window, void* out_bf16) {
   return prefill_launch(ctx_, stream, q_rot_bf16, k_cache_bf16, v_cache_bf16, positions, B, T, Hq, Hkv, D, max_len,
                         softmax_scale, window, out_bf16);
+}
+
+extern "C" int xaxb_attn_cross(xaxb_ctx* ctx_, void* stream, const void* q_bf16, const void* k_bf16, const void* v_bf16,
+                               const int32_t* kv_lens, int64_t B, int64_t T, int64_t Hq, int64_t Hkv, int64_t D,
+                               int64_t max_len, float softmax_scale, void* out_bf16) {
+  return prefill_launch(ctx_, stream, q_bf16, k_bf16, v_bf16, kv_lens, B, T, Hq, Hkv, D, max_len, softmax_scale, -1,
+                        out_bf16, 1);
 }

@@ -671,6 +671,30 @@ def attn_prefill(q_rot, k_cache, v_cache, positions, B, T, *, scale=None, out=No
     return out
 
 
+def attn_cross(q, k, v, kv_lens=None, *, scale=None, out=None):
+    """Cross-attention: q bf16 [B*T, Hq, D] (or [T, Hq, D] with B = 1) against k, v bf16 [B, S, Hkv, D]; every
+    query of sequence b sees rows 0 .. kv_lens[b]-1 (default: all S).  Returns bf16 like q."""
+    if k.dim() != 4 or v.shape != k.shape or q.dim() != 3:
+        raise ValueError(f"attention: q must be [rows, Hq, D] and k, v [B, S, Hkv, D], got {tuple(q.shape)}, "
+                         f"{tuple(k.shape)}, {tuple(v.shape)}")
+    B, S, Hkv, D = k.shape
+    if kv_lens is None:
+        kv_lens = torch.full((B,), S, dtype=torch.int32, device=k.device)
+    _attn_args(q, k, v, kv_lens, q.shape[0] // max(B, 1))
+    if q.shape[0] % B:
+        raise ValueError("attention: the query rows must divide evenly over the sequences")
+    T = q.shape[0] // B
+    Hq = q.shape[1]
+    ctx, st, lib = _c()
+    if out is None:
+        out = torch.empty_like(q)
+    if scale is None:
+        scale = 1.0 / math.sqrt(D)
+    check(lib.xaxb_attn_cross(ctx, st, ptr(q), ptr(k), ptr(v), ptr(kv_lens), B, T, Hq, Hkv, D, S, float(scale), ptr(out)),
+          "attn_cross")
+    return out
+
+
 def attn_check(q_rot, k_cache, v_cache, positions, B, T, *, scale=None):
     _attn_args(q_rot, k_cache, v_cache, positions, T)
     _, Hq, D = q_rot.shape
