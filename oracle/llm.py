@@ -91,6 +91,59 @@ class LLM:
         return self.get_logits(x), caches
 
 
+class CrossAttentionLLM:
+    """xax/arch/llm.py:362-623: an LLM with one cross-attention block (and its pre-norm) shared by all layers,
+    applied after every transformer block."""
+
+    def __init__(self, llm: LLM, cross_attn, cross_attn_norm):
+        self.llm, self.cross_attn, self.cross_attn_norm, self.config = llm, cross_attn, cross_attn_norm, llm.config
+
+    def init_cache(self, max_len=None, dtype=bfloat16, encoder_output_sn=None):  # :445-470
+        cross = None if encoder_output_sn is None else self.cross_attn.init_cache(encoder_output_sn)
+        return self.llm.init_cache(max_len, dtype), cross
+
+    def _cross(self, x, encoder_output_sn, cross_cache):  # :537-545 / :551-559
+        from .attention import promote, rnd
+
+        norm_x = self.cross_attn_norm(x)
+        out, new_cache = self.cross_attn.forward(norm_x, kv_sn=encoder_output_sn if cross_cache is None else None,
+                                                 cache=cross_cache)
+        return rnd(f32(x) + f32(out), promote(x.dtype, out.dtype)), new_cache
+
+    def forward_hidden(self, tokens_t, *, encoder_output_sn=None, context_tn=None, caches=None, cross_cache=None):
+        """:502-560."""
+        from .attention import promote, rnd
+
+        tokens_t = np.asarray(tokens_t)
+        assert tokens_t.ndim == 1
+        x = self.llm.embed_tokens(tokens_t)
+        if context_tn is not None:  # :529-530
+            context_tn = np.asarray(context_tn)
+            x = rnd(f32(context_tn) + f32(x), promote(context_tn.dtype, x.dtype))
+        if caches is None:
+            for b in self.llm.blocks:
+                x, _ = b.forward(x, cache=None)
+                if encoder_output_sn is not None:
+                    x, _ = self._cross(x, encoder_output_sn, None)
+            return self.llm.norm(x)
+        out, updated_cross = [], cross_cache
+        for b, c in zip(self.llm.blocks, caches, strict=True):
+            x, c = b.forward(x, cache=c)
+            out.append(c)
+            if cross_cache is not None or encoder_output_sn is not None:
+                x, updated_cross = self._cross(x, encoder_output_sn, cross_cache)
+        return self.llm.norm(x), out, updated_cross
+
+    def forward(self, tokens_t, *, context_tn=None, encoder_output_sn=None, caches=None, cross_cache=None):
+        """:594-623."""
+        if caches is None:
+            return self.llm.get_logits(self.forward_hidden(tokens_t, context_tn=context_tn,
+                                                           encoder_output_sn=encoder_output_sn))
+        x, caches_out, cross_out = self.forward_hidden(tokens_t, context_tn=context_tn, encoder_output_sn=encoder_output_sn,
+                                                       caches=caches, cross_cache=cross_cache)
+        return self.llm.get_logits(x), caches_out, cross_out
+
+
 def greedy_token(logits_v) -> int:
     """xax/arch/llm.py:1466-1470: argmax of float32 logits, first index on ties."""
     return int(np.argmax(f32(logits_v)))

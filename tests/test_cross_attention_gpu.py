@@ -159,3 +159,49 @@ def test_transformer_block_with_cross_attention_and_transformer_decode():
     h2, _ = tr.decode(torch.tensor([11], device="cuda"), ctx_toks, cache=cache1)
     assert h2.shape == (1, 128) and bool(torch.isfinite(h2.float()).all())
     _lib.device_status()
+
+
+def test_cross_attention_llm_matches_the_restatement():
+    """xax/arch/llm.py:362-623: logits with and without an encoder output, and the cached path (prompt, then one
+    token) with the cross-attention cache made once by init_cache."""
+    from helpers import llm_from_oracle
+    from oracle import attention as oattn
+    from oracle import llm as ollm
+    from xax_b200 import _lib
+    from xax_b200.arch.attention import RMSNorm
+    from xax_b200.arch.llm import CrossAttentionLLM
+
+    rng = np.random.default_rng(23)
+    cfg = ollm.LLMConfig(vocab_size=96, embed_dim=256, q_heads=4, kv_heads=2, head_dim=64, num_layers=2, mlp_hidden_dim=512,
+                         rope_theta=10000.0, rms_eps=1e-5)
+    om = ollm.LLM.build(cfg, rng, use_fp8=False, tie=True, std=0.02)
+    oc = ollm.CrossAttentionLLM(om, _oracle_cross(rng, 256, 4, False, False), oattn.RMSNorm.build(256, 1e-5, bf16))
+    mm = llm_from_oracle(om)
+    mc = CrossAttentionLLM(mm, _mirror_cross(oc.cross_attn),
+                           RMSNorm(to_torch(oc.cross_attn_norm.weight), oc.cross_attn_norm.eps), mm.config)
+    toks = rng.integers(0, 96, 19)
+    enc = rng.standard_normal((33, 256)).astype(np.float32).astype(bf16)
+    t_toks, t_enc = torch.tensor(toks, device="cuda"), to_torch(enc)
+
+    want = oc.forward(toks, encoder_output_sn=enc)
+    got = mc.forward(t_toks, encoder_output_sn=t_enc)
+    _lib.device_status()
+    e = rel_fro(to_numpy(got), want)
+    plain = rel_fro(to_numpy(mc.forward(t_toks)), oc.forward(toks))
+    print(f"cross-attention LLM logits: rel err {e:.3e} with an encoder output, {plain:.3e} without")
+    assert e < 1e-2 and plain < 1e-2
+    assert rel_fro(want, oc.forward(toks)) > 5e-2  # the encoder output does change the result
+
+    # cached: prime with the prompt, then one more token; the cross-attention cache comes from init_cache
+    w_self, w_cross = oc.init_cache(max_len=24, encoder_output_sn=enc)
+    g_self, g_cross = mc.init_cache(max_len=24, encoder_output_sn=t_enc)
+    w1, w_self, w_cross1 = oc.forward(toks, caches=w_self, cross_cache=w_cross)
+    g1, g_self, g_cross1 = mc.forward(t_toks, caches=g_self, cross_cache=g_cross)
+    assert rel_fro(to_numpy(g1), w1) < 1e-2
+    assert int(g_cross1["position"]) == 19 == int(w_cross1["position"])  # advanced once, not once per layer
+    nxt = np.array([int(np.argmax(w1[-1].astype(np.float32)))])
+    w2, _, _ = oc.forward(nxt, caches=w_self, cross_cache=w_cross1)
+    g2, _, _ = mc.forward(torch.tensor(nxt, device="cuda"), caches=g_self, cross_cache=g_cross1)
+    _lib.device_status()
+    assert rel_fro(to_numpy(g2), w2) < 1e-2
+    assert int(np.argmax(w2[-1].astype(np.float32))) == int(g2[-1].float().argmax())

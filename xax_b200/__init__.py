@@ -20,7 +20,7 @@ NAME_MAP = {
     "TransformerStack": "arch.attention", "Transformer": "arch.attention", "TransformerCache": "arch.attention",
     "CrossAttentionBlock": "arch.attention",
     # xax.arch.llm
-    "LLM": "arch.llm", "LLMConfig": "arch.llm", "llm_generate": "arch.llm", "llm_generate_jit": "arch.llm",
+    "LLM": "arch.llm", "LLMConfig": "arch.llm", "CrossAttentionLLM": "arch.llm", "llm_generate": "arch.llm", "llm_generate_jit": "arch.llm",
     "llm_generate_batch": "arch.llm", "llm_generate_stream": "arch.llm", "TokenSampler": "arch.llm",
     "tie_embedding_and_head": "arch.llm",
     "get_model_parallel_sharding_spec": "arch.llm", "DecodeState": "arch.llm",

@@ -221,6 +221,80 @@ class LLM:
         return self.get_logits(h), caches
 
 
+class CrossAttentionLLM:
+    """xax/arch/llm.py:362-623: an LLM plus ONE cross-attention block (no RoPE, as many heads as the LLM has
+    query heads) and its pre-norm, shared by all layers and applied after every transformer block, so that
+    the decoder attends to an encoder's output (text embeddings while generating audio tokens, say)."""
+
+    def __init__(self, llm: LLM, cross_attn, cross_attn_norm: RMSNorm, config: LLMConfig):
+        self.llm, self.cross_attn, self.cross_attn_norm, self.config = llm, cross_attn, cross_attn_norm, config
+
+    @classmethod
+    def build(cls, config: LLMConfig, *, key=None, extra_tokens: int | None = None, **llm_kwargs) -> "CrossAttentionLLM":
+        """:376-412.  ``llm_kwargs`` go to ``LLM.build`` (use_fp8, init_std, device)."""
+        seed = int(key or 0) if not isinstance(key, torch.Generator) else int(key.initial_seed())
+        llm = LLM.build(config, extra_tokens=extra_tokens, key=seed * 2 + 1, **llm_kwargs)
+        return cls.from_llm(llm, key=seed * 2 + 2)
+
+    @classmethod
+    def from_llm(cls, llm: LLM, *, key=None) -> "CrossAttentionLLM":
+        """:414-443: wrap an existing (possibly pretrained) LLM; the cross-attention starts from a fresh init."""
+        from .attention import CrossAttentionBlock
+
+        dev = llm.embed.weight.device
+        cross = CrossAttentionBlock.build(llm.config.embed_dim, llm.config.q_heads, key=key,
+                                          use_rotary_embeddings=False, device=dev)
+        return cls(llm, cross, RMSNorm.build(llm.config.embed_dim, eps=llm.config.rms_eps, device=dev), llm.config)
+
+    def init_cache(self, max_len: int | None = None, dtype=BF16, encoder_output_sn=None):
+        """:445-470: (self-attention caches per layer, cross-attention cache or None)."""
+        self_caches = self.llm.init_cache(max_len=max_len, dtype=dtype)
+        cross_cache = None
+        if encoder_output_sn is not None:
+            cross_cache, _ = self.cross_attn.init_cache(kv_sn=encoder_output_sn)
+        return self_caches, cross_cache
+
+    def _cross(self, x, encoder_output_sn, cross_cache):
+        y, _ = ops.rmsnorm(x, self.cross_attn_norm.weight_bf16(), self.cross_attn_norm.eps)
+        out, new_cache, _ = self.cross_attn.forward(y, kv_sn=encoder_output_sn if cross_cache is None else None,
+                                                    cache=cross_cache, residual=x)  # x + cross_out in the GEMM
+        return out, new_cache
+
+    def forward_hidden(self, tokens_t: torch.Tensor, *, encoder_output_sn=None, context_tn=None, caches=None,
+                       cross_cache=None):
+        """:502-560: hidden states (after the final norm); with ``caches`` also the updated self-attention caches
+        and cross-attention cache.  Every layer's cross-attention call gets the cache that came IN (its position
+        therefore advances by the number of new tokens once per call of this method, not once per layer)."""
+        if tokens_t.dim() != 1:
+            raise ValueError(f"expected rank 1 tokens, got rank {tokens_t.dim()}")
+        x = self.llm.embed_tokens(tokens_t)
+        if context_tn is not None:  # :529-530
+            x = (context_tn.to(BF16) + x).to(BF16)
+        if caches is None:
+            for block in self.llm.blocks:
+                x, _ = block.forward(x, cache=None)
+                if encoder_output_sn is not None:
+                    x, _ = self._cross(x, encoder_output_sn, None)
+            return self.llm.norm(x)
+        caches_out = []
+        updated_cross = cross_cache
+        for block, cache in zip(self.llm.blocks, caches, strict=True):
+            x, cache = block.forward(x, cache=cache)
+            caches_out.append(cache)
+            if cross_cache is not None or encoder_output_sn is not None:
+                x, updated_cross = self._cross(x, encoder_output_sn, cross_cache)
+        return self.llm.norm(x), caches_out, updated_cross
+
+    def forward(self, tokens_t: torch.Tensor, *, context_tn=None, encoder_output_sn=None, caches=None, cross_cache=None):
+        """:594-623: logits, and with ``caches`` the updated caches."""
+        if caches is None:
+            x = self.forward_hidden(tokens_t, context_tn=context_tn, encoder_output_sn=encoder_output_sn)
+            return apply_linear(x, self.llm.lm_head)
+        x, caches_out, cross_out = self.forward_hidden(tokens_t, context_tn=context_tn, encoder_output_sn=encoder_output_sn,
+                                                       caches=caches, cross_cache=cross_cache)
+        return apply_linear(x, self.llm.lm_head), caches_out, cross_out
+
+
 def tie_embedding_and_head(model: LLM) -> LLM:
     """xax/arch/llm.py:713-715: the returned model's lm_head shares the embedding array."""
     tied = LLM(model.embed, model.blocks, model.norm,
