@@ -136,6 +136,25 @@ int xaxb_gemm_bf16(xaxb_ctx* ctx, void* stream, const void* a_bf16, int64_t lda,
                    int col_mul_stride, const void* bias_bf16, const void* residual_bf16, int64_t ldr, void* out_bf16,
                    int64_t ldo);
 
+/*
+ * lm_head + cross-entropy loss / accuracy without materialising the logits (xax/arch/llm.py:718-887,
+ * chunked_cross_entropy_loss and chunked_cross_entropy_acc, forward only): logits = hidden @ weight^T in
+ * float32 (bf16 operands, float32 accumulation -- the reference casts the hidden states to float32 and
+ * multiplies by the bf16 head), loss[t] = logsumexp(logits[t]) - logits[t, targets[t]], pred[t] = arg-max
+ * (first index on ties).  The GEMM's epilogue reduces every 256-column slice of a row to (max, sum of
+ * exponentials, target logit, arg-max) in registers; a second kernel merges the slices and a third takes
+ * the masked means in a fixed order.  hidden: bf16 [T, H] (row stride ldh elements), weight: bf16 [V, H]
+ * (row stride ldw), targets: int32 [T], mask: one byte per position (non-zero = counted) or NULL for all.
+ * workspace: xaxb_lm_head_cross_entropy_workspace_bytes(T, V) bytes, 16-byte aligned.  Outputs: row_loss
+ * float32 [T], row_pred int32 [T], result float32 [3] = {mean loss over counted positions (0 if none),
+ * fraction of counted positions with pred == target, number counted}.
+ */
+int64_t xaxb_lm_head_cross_entropy_workspace_bytes(int64_t T, int64_t V);
+int xaxb_lm_head_cross_entropy(xaxb_ctx* ctx, void* stream, const void* hidden_bf16, int64_t ldh, const void* weight_bf16,
+                               int64_t ldw, int64_t T, int64_t V, int64_t H, const int32_t* targets, const uint8_t* mask,
+                               void* workspace, int64_t workspace_bytes, float* row_loss, int32_t* row_pred,
+                               float* result);
+
 /* Test hook: force the tile width (32/64/128/256, 512 = the CTA-pair kernel with 256 x 256 tiles
  * where M > 128 and N >= 256, 0 = automatic) and the split-K factor
  * (1/2/4/8, 0 = automatic; > 1 needs M <= 128) of the following xaxb_gemm_* calls in this

@@ -91,6 +91,26 @@ class LLM:
         return self.get_logits(x), caches
 
 
+def chunked_cross_entropy(hidden_td, targets_t, head_weight, mask_t=None):
+    """xax/arch/llm.py:718-887, loss and accuracy at once: the hidden states are cast to float32 and multiplied
+    by the (bf16) head weight in float32, log_softmax in float32, masked mean.  Returns (loss, accuracy) float32.
+    (The chunking of the reference changes memory use, not the value, apart from float32 summation order.)"""
+    h = f32(np.asarray(hidden_td))
+    w = f32(np.asarray(head_weight))
+    targets_t = np.asarray(targets_t).astype(np.int64)
+    T = h.shape[0]
+    mask = np.ones((T,), dtype=bool) if mask_t is None else np.asarray(mask_t).astype(bool)
+    logits = (h @ w.T).astype(float32)
+    m = logits.max(axis=-1, keepdims=True)
+    lse = (m[:, 0] + np.log(np.exp(logits - m, dtype=float32).sum(axis=-1, dtype=float32))).astype(float32)
+    loss_t = (lse - logits[np.arange(T), targets_t]).astype(float32)
+    correct = logits.argmax(axis=-1) == targets_t
+    n = float32(mask.sum())
+    if n == 0:
+        return float32(0.0), float32(0.0)
+    return float32(loss_t[mask].sum(dtype=float32) / n), float32(float32(correct[mask].sum()) / n)
+
+
 class CrossAttentionLLM:
     """xax/arch/llm.py:362-623: an LLM with one cross-attention block (and its pre-norm) shared by all layers,
     applied after every transformer block."""

@@ -22,7 +22,8 @@ NAME_MAP = {
     # xax.arch.llm
     "LLM": "arch.llm", "LLMConfig": "arch.llm", "CrossAttentionLLM": "arch.llm", "llm_generate": "arch.llm", "llm_generate_jit": "arch.llm",
     "llm_generate_batch": "arch.llm", "llm_generate_stream": "arch.llm", "TokenSampler": "arch.llm",
-    "tie_embedding_and_head": "arch.llm",
+    "tie_embedding_and_head": "arch.llm", "chunked_cross_entropy_loss": "arch.llm",
+    "chunked_cross_entropy_acc": "arch.llm",
     "get_model_parallel_sharding_spec": "arch.llm", "DecodeState": "arch.llm",
     "build_pretrained_llm": "arch.hf", "hf_config_to_llm_config": "arch.hf", "load_hf_weights_into_llm": "arch.hf",
     # xax.nn.fp8 (not re-exported by xax at top level; offered here for convenience)

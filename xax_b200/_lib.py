@@ -79,6 +79,8 @@ SIGNATURES: dict[str, tuple] = {
     "xaxb_silu_mul_cast_tp": (_I, [_P, _P, _P, _P, _I64, _I64, _I64, _P, _P, _P, _P, _I, _I, _I64, _I64]),
     "xaxb_attn_decode_cast_tp": (_I, [_P, _P, _P, _P, _P, _P, _I64, _I64, _I64, _I64, _I64, _F, _I, _P, _P, _I64, _P, _P,
                                       _P, _P, _I64, _P, _I, _I, _I64, _I64]),
+    "xaxb_lm_head_cross_entropy_workspace_bytes": (_I64, [_I64, _I64]),
+    "xaxb_lm_head_cross_entropy": (_I, [_P, _P, _P, _I64, _P, _I64, _I64, _I64, _I64, _P, _P, _P, _I64, _P, _P, _P]),
     "xaxb_attn_cross": (_I, [_P, _P, _P, _P, _P, _P, _I64, _I64, _I64, _I64, _I64, _I64, _F, _P]),
     "xaxb_attn_decode_append": (_I, [_P, _P, _P, _I64, _P, _P, _P, _I64, _I64, _I64, _I64, _I64, _F, _I, _P, _P, _I64,
                                      _I64, _P, _P, _P, _P, _P, _I64, _P, _I, _I, _I64, _I64]),

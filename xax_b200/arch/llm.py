@@ -221,6 +221,35 @@ class LLM:
         return self.get_logits(h), caches
 
 
+def _head_weight(lm_head) -> torch.Tensor:
+    w = getattr(lm_head, "weight", None)
+    if not isinstance(w, torch.Tensor) or w.dim() != 2 or isinstance(lm_head, Fp8Linear) or getattr(lm_head, "bias", None) is not None:
+        raise ValueError("the fused loss takes the head as a layer with a bf16 (vocab, hidden) weight and no bias "
+                         "(model.lm_head); an arbitrary callable is outside the path this library covers")
+    return w.to(BF16)
+
+
+def chunked_cross_entropy_loss(hidden_td: torch.Tensor, targets_t: torch.Tensor, lm_head, mask_t=None,
+                               chunk_size: int = 1) -> torch.Tensor:
+    """xax/arch/llm.py:718-788: mean cross-entropy over the valid positions, float32 scalar, without ever
+    holding the (seq, vocab) logits: they are reduced to (max, sum-exp, target logit) inside the head GEMM's
+    epilogue, 256 vocabulary columns at a time, so ``chunk_size`` (the reference's way of bounding memory) is
+    accepted and not needed.  ``lm_head``: the model's head layer (the reference takes its ``__call__``)."""
+    if hidden_td.dim() != 2:
+        raise ValueError(f"expected rank 2 hidden states (seq, hidden_dim), got rank {hidden_td.dim()}")
+    result, _, _ = ops.lm_head_cross_entropy(hidden_td.to(BF16).contiguous(), _head_weight(lm_head), targets_t, mask_t)
+    return result[0]
+
+
+def chunked_cross_entropy_acc(hidden_td: torch.Tensor, targets_t: torch.Tensor, lm_head, mask_t=None,
+                              chunk_size: int = 1) -> torch.Tensor:
+    """xax/arch/llm.py:791-887: fraction of valid positions whose arg-max logit is the target, float32 scalar."""
+    if hidden_td.dim() != 2:
+        raise ValueError(f"expected rank 2 hidden states (seq, hidden_dim), got rank {hidden_td.dim()}")
+    result, _, _ = ops.lm_head_cross_entropy(hidden_td.to(BF16).contiguous(), _head_weight(lm_head), targets_t, mask_t)
+    return result[1]
+
+
 class CrossAttentionLLM:
     """xax/arch/llm.py:362-623: an LLM plus ONE cross-attention block (no RoPE, as many heads as the LLM has
     query heads) and its pre-norm, shared by all layers and applied after every transformer block, so that

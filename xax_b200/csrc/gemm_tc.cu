@@ -56,6 +56,13 @@ struct GemmParams {
   __nv_bfloat16* push_out[8];
   unsigned int* push_flag[8];
   int push_world;
+  // Cross-entropy epilogue (gemm_tc_kernel, tiles of 64 columns and more): with ce_part set the output
+  // tile is never stored.  Each epilogue thread owns a row and reduces the tile's columns of that row --
+  // the logits of a vocabulary slice -- to (max, sum of exp(logit - max), the logit of column
+  // ce_targets[row] if it lies in the tile else -inf, the column of the max) and writes that to
+  // ce_part[row * tiles_n + tile column]; a second kernel merges the slices of a row.
+  float4* ce_part;
+  const int32_t* ce_targets;
 };
 
 // Tile order: bands of kBand tile rows, column by column inside a band (row index fastest).  The
@@ -296,6 +303,43 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         if (!epilogue_all(ok)) break;  // (also publishes cmul_s / bias_s)
         tc_fence_after_sync();
         const uint32_t taddr = tmem_base + (uint32_t(quarter * 32) << 16) + acc * BN;
+        if (p.ce_part) {
+          const int tgt = row_ok ? p.ce_targets[m] : -1;
+          float mx = -INFINITY, l = 0.0f, tv = -INFINITY;
+          int best = 0x7fffffff;
+#pragma unroll 1
+          for (int c0 = 0; c0 < BN; c0 += 32) {
+            uint32_t r[32];
+            tmem_ld_x32(taddr + c0, r);
+            tmem_ld_wait();
+            if (c0 + 32 >= BN) {  // accumulator fully read: hand it back to the MMA warp
+              tc_fence_before_sync();
+              __syncwarp();
+              if (lane == 0) mbar_arrive(acc_empty + acc);
+            }
+            float f[32];
+            float cmx = -INFINITY;
+            int cidx = 0x7fffffff;
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+              const int n = n0 + c0 + i;
+              f[i] = n < p.N ? fmaf(__uint_as_float(r[i]) * rm, cmul_s[c0 + i], bias_s[c0 + i]) : -INFINITY;
+              if (f[i] > cmx) cmx = f[i], cidx = n;  // strictly greater: the first index wins a tie
+              if (n == tgt) tv = f[i];
+            }
+            if (cmx > mx) {
+              l *= expf(mx - cmx);  // (mx = -inf on the first chunk: l is 0 and stays 0)
+              mx = cmx;
+              best = cidx;
+            }
+#pragma unroll
+            for (int i = 0; i < 32; ++i) l += expf(f[i] - mx);
+          }
+          if (row_ok) p.ce_part[(long long)m * p.tiles_n + tn] = make_float4(mx, l, tv, __int_as_float(best));
+          epilogue_sync();  // every thread has read cmul_s / bias_s before the next tile overwrites them
+          if (++acc == 2) acc = 0, acc_phase ^= 1;
+          continue;
+        }
 #pragma unroll 1
         for (int c0 = 0; c0 < BN; c0 += 64) {
           // the TMA unit must have finished reading the staging block of the previous store
@@ -970,6 +1014,8 @@ static int gemm_entry(xaxb_ctx* ctx_, void* stream, const void* a, int64_t lda, 
   p.d_status = ctx->d_status;
   p.prefetch_l2 = pdl_enabled() ? g_prefetch_l2 : 0;
   p.push_world = 0;
+  p.ce_part = nullptr;
+  p.ce_targets = nullptr;
   for (int r = 0; r < 8; ++r) p.push_out[r] = nullptr, p.push_flag[r] = nullptr;
   if (push) {
     p.push_world = push->world;
@@ -1059,3 +1105,132 @@ int xaxb_gemm_bf16(xaxb_ctx* ctx, void* stream, const void* a_bf16, int64_t lda,
 }
 
 }  // extern "C"
+
+// ---------------------------------------------------------------------------------------
+// lm_head + cross-entropy / accuracy without materialising the logits
+// (xax/arch/llm.py:718-887: chunked_cross_entropy_loss / chunked_cross_entropy_acc, forward).
+
+namespace xaxb {
+
+constexpr int kCeTile = 256;  // vocabulary columns per partial result
+
+// One warp per row: merges the row's per-tile (max, sum, target logit, arg-max) in tile order.
+// loss = logsumexp(logits) - logit[target]; pred = first index of the maximum.
+__global__ void __launch_bounds__(256) ce_merge_kernel(const float4* __restrict__ part, int tiles_n, int T,
+                                                       float* __restrict__ row_loss, int32_t* __restrict__ row_pred) {
+  pdl_trigger();
+  pdl_wait();
+  const int row = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (row >= T) return;
+  float m = -INFINITY, l = 0.0f, tv = -INFINITY;
+  int best = 0x7fffffff;
+  for (int t = lane; t < tiles_n; t += 32) {
+    const float4 v = part[(long long)row * tiles_n + t];
+    const int idx = __float_as_int(v.w);
+    if (v.x > m || (v.x == m && idx < best)) best = idx;  // tiles ascend, so do their columns
+    const float mn = fmaxf(m, v.x);
+    l = l * expf(m - mn) + v.y * expf(v.x - mn);
+    m = mn;
+    tv = fmaxf(tv, v.z);
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float m2 = __shfl_xor_sync(0xffffffffu, m, o), l2 = __shfl_xor_sync(0xffffffffu, l, o);
+    const float t2 = __shfl_xor_sync(0xffffffffu, tv, o);
+    const int b2 = __shfl_xor_sync(0xffffffffu, best, o);
+    if (m2 > m || (m2 == m && b2 < best)) best = b2;
+    const float mn = fmaxf(m, m2);
+    // (both sides -inf only when a lane had no tile: its l is 0 and exp(-inf - -inf) is never formed)
+    const float a = m == -INFINITY ? 0.0f : l * expf(m - mn), b = m2 == -INFINITY ? 0.0f : l2 * expf(m2 - mn);
+    l = a + b;
+    m = mn;
+    tv = fmaxf(tv, t2);
+  }
+  if (lane == 0) {
+    if (row_loss) row_loss[row] = (m + logf(l)) - tv;
+    if (row_pred) row_pred[row] = best;
+  }
+}
+
+// Masked means over the rows, one CTA, fixed summation order: result = {mean loss, accuracy, count}.
+__global__ void __launch_bounds__(1024) ce_finish_kernel(const float* __restrict__ row_loss,
+                                                         const int32_t* __restrict__ row_pred,
+                                                         const int32_t* __restrict__ targets,
+                                                         const uint8_t* __restrict__ mask, int T, float* result) {
+  pdl_trigger();
+  pdl_wait();
+  __shared__ float s_loss[1024], s_hit[1024], s_cnt[1024];
+  float a = 0.0f, h = 0.0f, c = 0.0f;
+  for (int i = threadIdx.x; i < T; i += 1024) {
+    if (mask && !mask[i]) continue;
+    a += row_loss[i];
+    h += row_pred[i] == targets[i] ? 1.0f : 0.0f;
+    c += 1.0f;
+  }
+  s_loss[threadIdx.x] = a, s_hit[threadIdx.x] = h, s_cnt[threadIdx.x] = c;
+  __syncthreads();
+  for (int o = 512; o > 0; o >>= 1) {
+    if ((int)threadIdx.x < o) {
+      s_loss[threadIdx.x] += s_loss[threadIdx.x + o];
+      s_hit[threadIdx.x] += s_hit[threadIdx.x + o];
+      s_cnt[threadIdx.x] += s_cnt[threadIdx.x + o];
+    }
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) {
+    const float n = s_cnt[0];
+    result[0] = n > 0.0f ? s_loss[0] / n : 0.0f;  // :788 / :887: no valid position -> 0
+    result[1] = n > 0.0f ? s_hit[0] / n : 0.0f;
+    result[2] = n;
+  }
+}
+
+}  // namespace xaxb
+
+extern "C" int64_t xaxb_lm_head_cross_entropy_workspace_bytes(int64_t T, int64_t V) {
+  if (T <= 0 || V <= 0) return 0;
+  return T * ((V + kCeTile - 1) / kCeTile) * (int64_t)sizeof(float4);
+}
+
+extern "C" int xaxb_lm_head_cross_entropy(xaxb_ctx* ctx_, void* stream, const void* hidden_bf16, int64_t ldh,
+                                          const void* weight_bf16, int64_t ldw, int64_t T, int64_t V, int64_t H,
+                                          const int32_t* targets, const uint8_t* mask, void* workspace,
+                                          int64_t workspace_bytes, float* row_loss, int32_t* row_pred, float* result) {
+  if (!ctx_ || !hidden_bf16 || !weight_bf16 || !targets || !workspace || !row_loss || !row_pred || !result || T <= 0 ||
+      V <= 0 || H <= 0) {
+    set_last_error("lm_head_cross_entropy: null pointer or non-positive shape");
+    return XAXB_BAD_ARGUMENT;
+  }
+  if ((H * 2) % 16 != 0 || T > 0x7fffffff || V > 0x7fffffff || (reinterpret_cast<uintptr_t>(workspace) & 15)) {
+    set_last_error("lm_head_cross_entropy: hidden size %lld must be a multiple of 8 and the workspace 16-byte aligned",
+                   (long long)H);
+    return XAXB_BAD_ARGUMENT;
+  }
+  if (workspace_bytes < xaxb_lm_head_cross_entropy_workspace_bytes(T, V)) return XAXB_WORKSPACE_TOO_SMALL;
+  const Ctx* ctx = reinterpret_cast<const Ctx*>(ctx_);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  GemmParams p;
+  p.M = (int)T, p.N = (int)V, p.K = (int)H;
+  p.row_mul = nullptr, p.row_mul_stride = 0, p.col_mul = nullptr, p.col_mul_stride = 0;
+  p.bias = nullptr, p.residual = nullptr, p.ldr = 0;
+  // never stored to: the store's tensor map only needs an aligned base and a row stride that is a multiple of 16 bytes
+  p.out = static_cast<__nv_bfloat16*>(workspace);
+  p.ldo = (V + 7) / 8 * 8;
+  p.d_status = ctx->d_status;
+  p.prefetch_l2 = pdl_enabled() ? g_prefetch_l2 : 0;
+  p.band = 32;
+  p.push_world = 0;
+  for (int r = 0; r < 8; ++r) p.push_out[r] = nullptr, p.push_flag[r] = nullptr;
+  p.ce_part = static_cast<float4*>(workspace);
+  p.ce_targets = targets;
+  int rc = launch_gemm<kCeTile, false>(ctx, s, hidden_bf16, ldh * 2, weight_bf16, ldw * 2, p);
+  if (rc) return rc;
+  const int tiles_n = (int)((V + kCeTile - 1) / kCeTile);
+  launch_kernel(ce_merge_kernel, dim3((unsigned)((T + 7) / 8)), dim3(256), 0, s, 1, static_cast<const float4*>(workspace),
+                tiles_n, (int)T, row_loss, row_pred);
+  rc = check_launch("ce_merge_kernel");
+  if (rc) return rc;
+  launch_kernel(ce_finish_kernel, dim3(1), dim3(1024), 0, s, 1, static_cast<const float*>(row_loss),
+                static_cast<const int32_t*>(row_pred), targets, mask, (int)T, result);
+  return check_launch("ce_finish_kernel");
+}

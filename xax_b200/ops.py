@@ -146,6 +146,37 @@ def gemm_fp8(a_q, b_q, row_mul=None, col_mul=None, bias=None, residual=None, out
     return _gemm("xaxb_gemm_fp8", a_q, b_q, row_mul, col_mul, bias, residual, out)
 
 
+def lm_head_cross_entropy(hidden, weight, targets, mask=None):
+    """Cross-entropy loss and accuracy of hidden bf16 [T, H] against targets int [T] under the head weight bf16
+    [V, H], without materialising the [T, V] logits (they are reduced inside the GEMM's epilogue).  ``mask``:
+    bool / uint8 [T], True = counted.  Returns (result float32 [3] = mean loss, accuracy, count; row_loss float32
+    [T]; row_pred int32 [T])."""
+    hidden = _req(hidden, BF16, "hidden")
+    weight = _req(weight, BF16, "weight")
+    if hidden.dim() != 2 or weight.dim() != 2 or hidden.shape[1] != weight.shape[1]:
+        raise ValueError(f"lm_head_cross_entropy: hidden [T, H] and weight [V, H] expected, got {tuple(hidden.shape)}, "
+                         f"{tuple(weight.shape)}")
+    T, H = hidden.shape
+    V = weight.shape[0]
+    targets = targets.to(device=hidden.device, dtype=torch.int32).contiguous()
+    if targets.shape != (T,):
+        raise ValueError(f"lm_head_cross_entropy: targets must be [T] = [{T}], got {tuple(targets.shape)}")
+    if mask is not None:
+        mask = mask.to(device=hidden.device).reshape(-1).to(torch.uint8).contiguous()
+        if mask.shape != (T,):
+            raise ValueError(f"lm_head_cross_entropy: mask must be [T] = [{T}]")
+    ctx, st, lib = _c()
+    nws = int(lib.xaxb_lm_head_cross_entropy_workspace_bytes(T, V))
+    ws = torch.empty((nws // 4,), dtype=torch.float32, device=hidden.device)
+    row_loss = torch.empty((T,), dtype=torch.float32, device=hidden.device)
+    row_pred = torch.empty((T,), dtype=torch.int32, device=hidden.device)
+    result = torch.empty((3,), dtype=torch.float32, device=hidden.device)
+    check(lib.xaxb_lm_head_cross_entropy(ctx, st, ptr(hidden), hidden.stride(0), ptr(weight), weight.stride(0), T, V, H,
+                                         ptr(targets), ptr(mask), ptr(ws), nws, ptr(row_loss), ptr(row_pred), ptr(result)),
+          "lm_head_cross_entropy")
+    return result, row_loss, row_pred
+
+
 def gemm_fp8_push(a_q, b_q, row_mul, col_mul, bias, residual, peer_ptrs, rank: int, world: int, slot_offset: int,
                   flag_offset: int):
     """gemm_fp8 whose epilogue writes the bf16 output into this rank's slot of every rank's staging buffer and
