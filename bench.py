@@ -87,7 +87,7 @@ class ClockSampler:
 # CPU oracle arm
 
 
-def oracle_decode_sample(w: dict, seconds_budget: float, steps: int, warmup: int):
+def oracle_decode_sample(w: dict, seconds_limit: float, steps: int, warmup: int):
     """Times the CPU oracle (the reference's algorithm restated in NumPy) on a bounded sample of
     the decode workload: ONE transformer layer of the workload's shape plus the lm_head, ONE
     sequence, at the workload's context (the prompt length); a full step of one sequence is
@@ -126,7 +126,7 @@ def oracle_decode_sample(w: dict, seconds_budget: float, steps: int, warmup: int
             t_layer.append(t1 - t0)
             t_head.append(t2 - t1)
             done += 1
-        if time.perf_counter() - t_start > seconds_budget and done >= 1:
+        if time.perf_counter() - t_start > seconds_limit and done >= 1:
             break
     tl, th = float(np.median(t_layer)), float(np.median(t_head))
     step_s = w["layers"] * tl + th  # one sequence
@@ -427,7 +427,7 @@ def main() -> None:
     if args.impl == "reference":
         if rank != 0:
             return
-        r = oracle_decode_sample(w, seconds_budget=150.0, steps=args.steps, warmup=1)
+        r = oracle_decode_sample(w, seconds_limit=150.0, steps=args.steps, warmup=1)
         line = dict(base)
         line.update({"impl": "reference", "value": r["tokens_per_s"], "ms_per_step": r["step_s_one_sequence"] * 1e3,
                      "dtype": "bf16/e4m3 emulated in float32 (NumPy)",
@@ -622,7 +622,7 @@ def main() -> None:
         except Exception as e:  # noqa: BLE001
             line["kernels"] = {"error": repr(e)}
     if not args.no_cpu:
-        r = oracle_decode_sample(w, seconds_budget=20.0, steps=2, warmup=0)
+        r = oracle_decode_sample(w, seconds_limit=20.0, steps=2, warmup=0)
         line["cpu_baseline"] = {"value": r["tokens_per_s"], "unit": unit, "cores": host_threads(), "kind": "port",
                                 "sample": r["sample"]}
     else:
