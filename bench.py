@@ -284,7 +284,47 @@ def _gemm_figures(x, w, bias, scale, hist, g, flush) -> dict:
     except Exception as e:  # noqa: BLE001
         out["cublaslt_fp8_8192"] = {"error": repr(e)[:200]}
     del a8, b8, o2
+    out["gemm_fp8_decode_cfg5_layer"] = _decode_gemm_figures(g, flush)
     return out
+
+
+def _decode_gemm_figures(g, flush) -> dict:
+    """The four FP8 GEMMs of one cfg5 layer at decode size (M = 128 token rows): fused q|k|v, out-proj,
+    gate|up, down.  Each shape is timed as a CUDA graph of eight launches on eight different weight
+    matrices (so the weights stream from HBM, as in the model, and launch gaps are the device's own);
+    the figure is weight bytes / time against the measured copy bandwidth."""
+    import torch
+
+    from xax_b200 import ops
+
+    peak, _ = measured_peaks()
+    M, reps = 128, 8
+    shapes = (("qkv", 6144, 4096), ("out", 4096, 4096), ("gate_up", 28672, 4096), ("down", 4096, 14336))
+    res, total_us, total_bytes = {}, 0.0, 0
+    for name, N, K in shapes:
+        a = torch.randn((M, K), generator=g, device="cuda").to(torch.float8_e4m3fn)
+        ws = [torch.randn((N, K), generator=g, device="cuda").to(torch.float8_e4m3fn) for _ in range(reps)]
+        rm = torch.ones(M, device="cuda")
+        cm = torch.ones(1, device="cuda")
+        o = torch.empty((M, N), dtype=torch.bfloat16, device="cuda")
+
+        def chain():
+            for w_ in ws:
+                ops.gemm_fp8(a, w_, rm, cm, None, None, out=o)
+
+        chain()
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            chain()
+        t = _time_kernel(lambda i: graph.replay(), iters=5, warm=1, flush=flush) / reps
+        res[name] = {"us": t * 1e6, "gbs": N * K / t / 1e9, "frac_of_hbm_peak": N * K / t / 1e9 / peak}
+        total_us += t * 1e6
+        total_bytes += N * K
+        del ws
+    res["layer"] = {"us": total_us, "gbs": total_bytes / total_us / 1e3, "frac_of_hbm_peak": total_bytes / total_us / 1e3 / peak,
+                    "weight_bytes": total_bytes}
+    return res
 
 
 def _attn_decode_figures(g, peak_gbs, flush) -> dict:
