@@ -48,6 +48,19 @@ struct PrefillSmem {
   static constexpr int kTmemCols = 256;                     // S: 64 columns, PV: D columns
 };
 
+__device__ __forceinline__ float ex2_approx(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+// two float32 -> one register of two bf16 (round to nearest even), lo in the low half
+__device__ __forceinline__ uint32_t pack_bf16x2_rn(float lo, float hi) {
+  uint32_t r;
+  asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+  return r;
+}
+
 template <int D>
 __global__ void __launch_bounds__(128, 2) attn_prefill_kernel(const __grid_constant__ CUtensorMap tmap_k,
                                                               const __grid_constant__ CUtensorMap tmap_v,
@@ -129,140 +142,190 @@ __global__ void __launch_bounds__(128, 2) attn_prefill_kernel(const __grid_const
   const uint32_t tmem_pv = tmem_base + 64;    // columns [64, 64 + D)
   const uint32_t lane_off = uint32_t(warp * 32) << 16;
 
-  float o[D];
-#pragma unroll
-  for (int i = 0; i < D; ++i) o[i] = 0.0f;
-  float m_run = -INFINITY, l_run = 0.0f;
+  // Thread r owns query row r.  The output accumulates in tensor memory: the second MMA adds P V to it,
+  // so the threads read it only once, at the end.  The scores of a tile are read from tensor memory once
+  // (64 registers).  Exponentials are taken against a reference maximum m_ref that follows the running
+  // maximum lazily: only when a tile's maximum exceeds it by more than kSlack (in the base-2 domain) is the
+  // accumulator row -- and the running denominator -- rescaled; until then probabilities may be as
+  // large as 2^kSlack, which bf16 and the float32 accumulator hold without loss of accuracy.  A row
+  // that has seen no visible key yet keeps m_ref = -inf and contributes nothing.
+  constexpr float kSlack = 8.0f;
+  float m_ref = -INFINITY, l_run = 0.0f;
   const int qpos = p.cross ? kv_len - 1 : start + q0 + min(tid, rows_valid - 1);  // rows past T mirror the last valid row
   const float scale_log2 = p.sm_scale * 1.4426950408889634f;
+  const int lo_vis = win >= 0 ? qpos - win : 0;  // lowest key position this row sees
+
+  auto issue_qk = [&](int j) {  // thread 0: S = Q K_j^T into tensor memory, completion on bar_s
+    const uint8_t* sK = sKV + (j & 1) * 2 * SM::kKVBytes;
+    tc_fence_after_sync();
+    constexpr uint32_t idesc = umma_idesc(kFmtBF16, kFmtBF16, 0, 0, 128, kPfKeys);
+#pragma unroll
+    for (int k = 0; k < D / 16; ++k) {
+      const uint32_t box = k / 4, off = (k % 4) * 32;
+      umma_f16(tmem_s, umma_desc_kmajor_sw128(smem_u32(sQ + box * SM::kHalfBytes) + off),
+               umma_desc_kmajor_sw128(smem_u32(sK + box * SM::kKVHalfBytes) + off), idesc, k != 0);
+    }
+    umma_commit(bar_s);
+  };
 
   bool ok = true;
+  if (tid == 0) {
+    ok = mbar_wait(bar_kv, 0, abort_flag, p.d_status, XAXB_DEVICE_TIMEOUT * 1000 + kSitePfKV);
+    if (ok) issue_qk(0);
+  }
   for (int j = 0; j < n_tiles; ++j) {
     const int s = j & 1;
-    uint8_t* sK = sKV + s * 2 * SM::kKVBytes;
-    uint8_t* sV = sK + SM::kKVBytes;
+    uint8_t* sV = sKV + s * 2 * SM::kKVBytes + SM::kKVBytes;
+    const int kv0 = (j_lo + j) * kPfKeys;
+    // ---- scores of tile j: one read from tensor memory ------------------------------------------
+    ok = ok && mbar_wait(bar_s, j & 1, abort_flag, p.d_status, XAXB_DEVICE_TIMEOUT * 1000 + kSitePfS);
+    uint32_t sreg[kPfKeys];
+    __syncwarp();  // the tensor-memory loads below are warp-wide
+    if (ok) {
+      tc_fence_after_sync();
+#pragma unroll
+      for (int c0 = 0; c0 < kPfKeys; c0 += 32) {
+        uint32_t r[32];
+        tmem_ld_x32(tmem_s + lane_off + c0, r);
+#pragma unroll
+        for (int i = 0; i < 32; ++i) sreg[c0 + i] = r[i];
+      }
+      tmem_ld_wait();
+    }
+    // some (row, col) of this tile is masked: above the diagonal (past the context's end for
+    // cross-attention), or below some row's window
+    const bool diag = kv0 + kPfKeys - 1 > (p.cross ? kv_len - 1 : start + q0) || (win >= 0 && kv0 < last_pos - win);
+    // column i of the tile is visible to this row iff lim_lo <= i <= lim_hi
+    const int lim_hi = qpos - kv0, lim_lo = lo_vis - kv0;
+    float m_tile = -INFINITY;
+    if (diag) {
+#pragma unroll
+      for (int i = 0; i < kPfKeys; ++i)
+        if (i <= lim_hi && i >= lim_lo) m_tile = fmaxf(m_tile, __uint_as_float(sreg[i]));
+    } else {
+#pragma unroll
+      for (int i = 0; i < kPfKeys; ++i) m_tile = fmaxf(m_tile, __uint_as_float(sreg[i]));
+    }
+    m_tile *= scale_log2;
+    // ---- the previous tile's P V must be complete before its operands (sP, the V stage) or the
+    // accumulator are touched; its K/V stage is then free for tile j + 1's successor
+    if (j > 0) {
+      ok = ok && mbar_wait(bar_o, (j - 1) & 1, abort_flag, p.d_status, XAXB_DEVICE_TIMEOUT * 1000 + kSitePfO);
+      if (ok) tc_fence_after_sync();
+      if (tid == 0 && ok && j + 1 < n_tiles) issue_tile(j + 1);  // into the stage tile j - 1 used
+    }
+    // ---- lazy rescale of the row's accumulator --------------------------------------------------
+    const bool grow = m_tile > m_ref + kSlack;  // (false while both are -inf)
+    const bool first = m_ref == -INFINITY && m_tile > -INFINITY;
+    __syncwarp();
+    if (__any_sync(0xffffffffu, ok && grow && !first && j > 0)) {
+      const float alpha = (grow && !first) ? exp2f(m_ref - m_tile) : 1.0f;
+#pragma unroll 1
+      for (int c0 = 0; c0 < D; c0 += 32) {
+        uint32_t r[32];
+        tmem_ld_x32(tmem_pv + lane_off + c0, r);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
+        tmem_st_x32(tmem_pv + lane_off + c0, r);
+      }
+      tmem_st_wait();
+      l_run *= alpha;
+    }
+    if (grow || first) m_ref = m_tile;
+    // ---- probabilities -> shared memory (bf16, the A operand of the second MMA) -------------------
+    // One multiply-add and one ex2.approx per score (arguments are <= kSlack: no range handling needed;
+    // -inf and very negative arguments give 0), one cvt per pair.  Tiles that the diagonal or the sequence
+    // end crosses take the branch with the per-column tests, the others (most of a long sequence) skip them.
+    const float m_use = m_ref == -INFINITY ? 0.0f : m_ref;
+    float l_tile = 0.0f;
+    if (diag) {
+#pragma unroll
+      for (int c0 = 0; c0 < kPfKeys; c0 += 8) {
+        uint32_t packed[4];
+#pragma unroll
+        for (int i = 0; i < 8; i += 2) {
+          float e0 = ex2_approx(fmaf(__uint_as_float(sreg[c0 + i]), scale_log2, -m_use));
+          float e1 = ex2_approx(fmaf(__uint_as_float(sreg[c0 + i + 1]), scale_log2, -m_use));
+          if (c0 + i > lim_hi || c0 + i < lim_lo) e0 = 0.0f;
+          if (c0 + i + 1 > lim_hi || c0 + i + 1 < lim_lo) e1 = 0.0f;
+          l_tile += e0 + e1;
+          packed[i / 2] = pack_bf16x2_rn(e0, e1);
+        }
+        *reinterpret_cast<uint4*>(sP + sw128_offset(tid, c0 / 8)) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+      }
+    } else {
+#pragma unroll
+      for (int c0 = 0; c0 < kPfKeys; c0 += 8) {
+        uint32_t packed[4];
+#pragma unroll
+        for (int i = 0; i < 8; i += 2) {
+          const float e0 = ex2_approx(fmaf(__uint_as_float(sreg[c0 + i]), scale_log2, -m_use));
+          const float e1 = ex2_approx(fmaf(__uint_as_float(sreg[c0 + i + 1]), scale_log2, -m_use));
+          l_tile += e0 + e1;
+          packed[i / 2] = pack_bf16x2_rn(e0, e1);
+        }
+        *reinterpret_cast<uint4*>(sP + sw128_offset(tid, c0 / 8)) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+      }
+    }
+    l_run += l_tile;
+    // rows of the tile past the sequence's last cached token may hold anything; the mask zeroed
+    // their probabilities, and V is cleared so that 0 * garbage stays 0
     ok = ok && mbar_wait(bar_kv + s, (j >> 1) & 1, abort_flag, p.d_status, XAXB_DEVICE_TIMEOUT * 1000 + kSitePfKV);
-    // rows of the tile past the sequence's last cached token may hold anything; the mask
-    // zeroes their probabilities, and V is cleared so that 0 * garbage stays 0
-    if (ok && tid < kPfKeys && (j_lo + j) * kPfKeys + tid >= total_len) {
+    if (ok && tid < kPfKeys && kv0 + tid >= total_len) {
 #pragma unroll
       for (int c = 0; c < D / 8; ++c)
         *reinterpret_cast<uint4*>(sV + (c / 8) * SM::kKVHalfBytes + sw128_offset(tid, c % 8)) = make_uint4(0, 0, 0, 0);
-      fence_proxy_async_smem();
     }
-    if (tid == 0 && ok) {
-      tc_fence_after_sync();
-      constexpr uint32_t idesc = umma_idesc(kFmtBF16, kFmtBF16, 0, 0, 128, kPfKeys);
-#pragma unroll
-      for (int k = 0; k < D / 16; ++k) {
-        const uint32_t box = k / 4, off = (k % 4) * 32;
-        umma_f16(tmem_s, umma_desc_kmajor_sw128(smem_u32(sQ + box * SM::kHalfBytes) + off),
-                 umma_desc_kmajor_sw128(smem_u32(sK + box * SM::kKVHalfBytes) + off), idesc, k != 0);
-      }
-      umma_commit(bar_s);
-    }
-    ok = ok && mbar_wait(bar_s, j & 1, abort_flag, p.d_status, XAXB_DEVICE_TIMEOUT * 1000 + kSitePfS);
-    ok = __syncthreads_and(ok);
-    if (!ok) break;
-    tc_fence_after_sync();
-
-    // ---- online softmax on row `tid` of S (two sweeps over TMEM: max, then exp) ------------
-    const int kv0 = (j_lo + j) * kPfKeys;
-    // some (row, col) of this tile is masked: above the diagonal, or below some row's window
-    const bool diag = kv0 + kPfKeys - 1 > (p.cross ? kv_len - 1 : start + q0) || (win >= 0 && kv0 < last_pos - win);
-    const int lo_vis = win >= 0 ? qpos - win : 0;  // lowest key position this row sees
-    float m_tile = -INFINITY;
-#pragma unroll 1
-    for (int c0 = 0; c0 < kPfKeys; c0 += 32) {
-      uint32_t r[32];
-      tmem_ld_x32(tmem_s + lane_off + c0, r);
-      tmem_ld_wait();
-#pragma unroll
-      for (int i = 0; i < 32; ++i) {
-        const float v = __uint_as_float(r[i]);
-        if (!diag || (kv0 + c0 + i <= qpos && kv0 + c0 + i >= lo_vis)) m_tile = fmaxf(m_tile, v);
-      }
-    }
-    // base-2 domain.  Without a window column 0 of tile 0 is visible to every row; with one, a row
-    // may see nothing of the first tiles: its running maximum stays -inf and nothing is added.
-    const float m_raw = fmaxf(m_run, m_tile * scale_log2);
-    const float m_new = m_raw == -INFINITY ? 0.0f : m_raw;
-    const float alpha = exp2f(m_run - m_new);
-    float l_tile = 0.0f;
-#pragma unroll 1
-    for (int c0 = 0; c0 < kPfKeys; c0 += 32) {
-      uint32_t r[32];
-      tmem_ld_x32(tmem_s + lane_off + c0, r);
-      tmem_ld_wait();
-      uint32_t packed[16];
-#pragma unroll
-      for (int i = 0; i < 32; i += 2) {
-        float e0 = exp2f(__uint_as_float(r[i]) * scale_log2 - m_new);
-        float e1 = exp2f(__uint_as_float(r[i + 1]) * scale_log2 - m_new);
-        if (diag) {
-          if (kv0 + c0 + i > qpos || kv0 + c0 + i < lo_vis) e0 = 0.0f;
-          if (kv0 + c0 + i + 1 > qpos || kv0 + c0 + i + 1 < lo_vis) e1 = 0.0f;
-        }
-        l_tile += e0 + e1;
-        const uint32_t lo = __bfloat16_as_ushort(__float2bfloat16_rn(e0));
-        const uint32_t hi = __bfloat16_as_ushort(__float2bfloat16_rn(e1));
-        packed[i / 2] = lo | (hi << 16);
-      }
-      // 32 tokens = 4 chunks of 16 bytes of the row's single 128-byte span
-#pragma unroll
-      for (int cc = 0; cc < 4; ++cc) {
-        const int chunk = c0 / 8 + cc;
-        *reinterpret_cast<uint4*>(sP + sw128_offset(tid, chunk)) =
-            make_uint4(packed[cc * 4], packed[cc * 4 + 1], packed[cc * 4 + 2], packed[cc * 4 + 3]);
-      }
-    }
-    l_run = l_run * alpha + l_tile;
-    m_run = m_raw;
     fence_proxy_async_smem();
     tc_fence_before_sync();
-    __syncthreads();
-
-    // ---- PV = P V ------------------------------------------------------------------------------
+    ok = __syncthreads_and(ok);
+    if (!ok) break;
+    // ---- O += P V; then, behind it in the tensor pipe, the next tile's scores --------------------
     if (tid == 0) {
       tc_fence_after_sync();
       constexpr uint32_t idesc = umma_idesc(kFmtBF16, kFmtBF16, 0, 1, 128, D);
 #pragma unroll
       for (int k = 0; k < kPfKeys / 16; ++k) {
         umma_f16(tmem_pv, umma_desc_kmajor_sw128(smem_u32(sP) + k * 32),
-                 umma_desc_mnmajor_sw128(smem_u32(sV) + k * 16 * 128, SM::kKVHalfBytes), idesc, k != 0);
+                 umma_desc_mnmajor_sw128(smem_u32(sV) + k * 16 * 128, SM::kKVHalfBytes), idesc, (j | k) != 0);
       }
       umma_commit(bar_o);
+      if (j + 1 < n_tiles) {
+        if (mbar_wait(bar_kv + ((j + 1) & 1), ((j + 1) >> 1) & 1, abort_flag, p.d_status,
+                      XAXB_DEVICE_TIMEOUT * 1000 + kSitePfKV))
+          issue_qk(j + 1);
+      }
     }
-    ok = mbar_wait(bar_o, j & 1, abort_flag, p.d_status, XAXB_DEVICE_TIMEOUT * 1000 + kSitePfO);
-    ok = __syncthreads_and(ok);
-    if (!ok) break;
-    tc_fence_after_sync();
-    if (tid == 0 && j + 2 < n_tiles) issue_tile(j + 2);  // stage s is free again
-#pragma unroll
-    for (int c0 = 0; c0 < D; c0 += 32) {
-      uint32_t r[32];
-      tmem_ld_x32(tmem_pv + lane_off + c0, r);
-      tmem_ld_wait();
-#pragma unroll
-      for (int i = 0; i < 32; ++i) o[c0 + i] = fmaf(o[c0 + i], alpha, __uint_as_float(r[i]));
-    }
-    tc_fence_before_sync();
+  }
+  if (ok) {
+    ok = mbar_wait(bar_o, (n_tiles - 1) & 1, abort_flag, p.d_status, XAXB_DEVICE_TIMEOUT * 1000 + kSitePfO);
+    if (ok) tc_fence_after_sync();
   }
 
-  if (ok && tid < rows_valid) {
+  __syncwarp();
+  if (ok) {
     const float inv = 1.0f / l_run;
     __nv_bfloat16* dst = p.out + (((long long)b * p.T + q0 + tid) * p.Hq + h) * D;
+#pragma unroll 1
+    for (int c0 = 0; c0 < D; c0 += 32) {
+      uint32_t r[32];
+      tmem_ld_x32(tmem_pv + lane_off + c0, r);  // (warp-wide: rows past T read their lanes too)
+      tmem_ld_wait();
+      if (tid < rows_valid) {
 #pragma unroll
-    for (int c = 0; c < D / 8; ++c) {
-      uint4 v;
-      uint32_t* w = reinterpret_cast<uint32_t*>(&v);
+        for (int c = 0; c < 4; ++c) {
+          uint4 v;
+          uint32_t* w = reinterpret_cast<uint32_t*>(&v);
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const uint32_t lo = __bfloat16_as_ushort(__float2bfloat16_rn(o[c * 8 + 2 * i] * inv));
-        const uint32_t hi = __bfloat16_as_ushort(__float2bfloat16_rn(o[c * 8 + 2 * i + 1] * inv));
-        w[i] = lo | (hi << 16);
+          for (int i = 0; i < 4; ++i) {
+            const uint32_t lo = __bfloat16_as_ushort(__float2bfloat16_rn(__uint_as_float(r[c * 8 + 2 * i]) * inv));
+            const uint32_t hi = __bfloat16_as_ushort(__float2bfloat16_rn(__uint_as_float(r[c * 8 + 2 * i + 1]) * inv));
+            w[i] = lo | (hi << 16);
+          }
+          *reinterpret_cast<uint4*>(dst + c0 + c * 8) = v;
+        }
       }
-      *reinterpret_cast<uint4*>(dst + c * 8) = v;
     }
   }
   tc_fence_before_sync();

@@ -67,8 +67,13 @@ __device__ __forceinline__ void umma_pair(uint32_t d_tmem, uint64_t a_desc, uint
 struct Gemm2Cfg {
   static constexpr int kBN = 256;                       // columns per pair tile
   static constexpr int kStageBytes = 2 * kBM * kBKBytes;  // per CTA: 128 rows of A + 128 rows of B
-  static constexpr int kEpiBytes = kBM * 128 + 2 * kBN * 4;
-  static constexpr int kStages = 6;
+  // Two staging blocks for the TMA stores: while the TMA unit reads one, the epilogue warps fill the other.
+  // With a single block every 64-column store waited for the previous one's read, and a tile's epilogue
+  // (four stores) took longer than the main loop of a short-K tile (config 1: K = 2048, 16 K blocks).
+  // Five load stages of 32 KiB keep far more in flight than an SM's request capacity needs.
+  static constexpr int kOutBlockBytes = kBM * 128;
+  static constexpr int kEpiBytes = 2 * kOutBlockBytes + 2 * kBN * 4;
+  static constexpr int kStages = 5;
   static constexpr int kTmemCols = 512;                 // two 256-column accumulators
   static constexpr int kSmemBytes = kStages * kStageBytes + kEpiBytes + 1024 + 256;
 };
@@ -89,7 +94,7 @@ gemm_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   uint8_t* smem_a = smem;                              // kStages x 16 KiB
   uint8_t* smem_b = smem + kStages * kBM * kBKBytes;   // kStages x 16 KiB
   uint8_t* stage_out = smem + kStages * Cfg::kStageBytes;
-  float* cmul_s = reinterpret_cast<float*>(stage_out + kBM * 128);
+  float* cmul_s = reinterpret_cast<float*>(stage_out + 2 * Cfg::kOutBlockBytes);
   float* bias_s = cmul_s + BN;
   uint64_t* bars = reinterpret_cast<uint64_t*>(stage_out + Cfg::kEpiBytes);
   uint64_t* full = bars;
@@ -201,9 +206,8 @@ gemm_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       tile_coords(p.band, tile, p.tiles_m, p.tiles_n, tm, tn);
       const int m0 = tm * (2 * kBM) + (int)rank * kBM;
       const int n0 = tn * BN;
-      bool ok = mbar_wait(acc_full + acc, acc_phase, abort_flag, p.d_status, XAXB_DEVICE_TIMEOUT * 1000 + kSite2Epilogue);
-      if (!epilogue_all(ok)) break;
-      tc_fence_after_sync();
+      // The tile's multipliers and bias are fetched while its main loop is still running (every thread
+      // passed the previous tile's last barrier after its last read of cmul_s / bias_s).
       for (int i = t; i < BN; i += 128) {
         const int n = n0 + i;
         float cm = 0.0f, bs = 0.0f;
@@ -217,10 +221,16 @@ gemm_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       const int m = m0 + row_in_tile;
       const bool row_ok = m < p.M;
       const float rm = (row_ok && p.row_mul) ? __ldg(p.row_mul + (long long)m * p.row_mul_stride) : 1.0f;
+      bool ok = mbar_wait(acc_full + acc, acc_phase, abort_flag, p.d_status, XAXB_DEVICE_TIMEOUT * 1000 + kSite2Epilogue);
+      if (!epilogue_all(ok)) break;  // (also publishes cmul_s / bias_s)
+      tc_fence_after_sync();
       const uint32_t taddr = tmem_base + (uint32_t(quarter * 32) << 16) + acc * BN;
 #pragma unroll 1
       for (int c0 = 0; c0 < BN; c0 += 64) {
-        if (t == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+        // the staging block about to be written was handed to the TMA unit two stores ago: that
+        // store must have finished reading it (the one issued last may still be reading the other block)
+        uint8_t* stage_blk = stage_out + ((c0 / 64) & 1) * Cfg::kOutBlockBytes;
+        if (t == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
         epilogue_sync();
 #pragma unroll
         for (int h = 0; h < 64; h += 32) {
@@ -255,15 +265,18 @@ gemm_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
               const uint32_t hi16 = __bfloat16_as_ushort(__float2bfloat16_rn(f[2 * j + 1]));
               ow[j] = lo16 | (hi16 << 16);
             }
-            *reinterpret_cast<uint4*>(stage_out + sw128_offset(row_in_tile, (h + v * 8) / 8)) = o;
+            *reinterpret_cast<uint4*>(stage_blk + sw128_offset(row_in_tile, (h + v * 8) / 8)) = o;
           }
         }
         fence_proxy_async_smem();
         epilogue_sync();
-        if (t == 0 && n0 + c0 < p.N && m0 < p.M) {
-          asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
-                       ::"l"(&tmap_out), "r"(smem_u32(stage_out)), "r"(n0 + c0), "r"(m0)
-                       : "memory");
+        if (t == 0) {
+          if (n0 + c0 < p.N && m0 < p.M)
+            asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
+                         ::"l"(&tmap_out), "r"(smem_u32(stage_blk)), "r"(n0 + c0), "r"(m0)
+                         : "memory");
+          // one group per block, stored or not, so that "all but the latest group" always means "the
+          // store that used the other staging block"
           asm volatile("cp.async.bulk.commit_group;" ::: "memory");
         }
       }
