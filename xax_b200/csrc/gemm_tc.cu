@@ -1030,11 +1030,13 @@ static int gemm_entry(xaxb_ctx* ctx_, void* stream, const void* a, int64_t lda, 
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   GemmPlan plan = pick_plan(M, N, K, eb, ctx->num_sms, push != nullptr);
   // Large problems go to the CTA-pair kernel: 256 x 256 tiles need a third less operand traffic
-  // per SM, which is what bounds the single-CTA kernel.  It wants at least two waves of tiles.
+  // per SM, which is what bounds the single-CTA kernel.  It wants at least one full round of tiles
+  // for the pairs (measured on the prefill shapes of configs 2 and 5 and on config 1: equal or faster
+  // than 128 x 256 tiles from 128 pair tiles up, e.g. 95 against 104 us for 2048 x 4096 x 14336).
   const bool pair_ok = M > kBM && N >= 256;
   const long long pair_tiles = ((long long)(M + 255) / 256) * ((N + 255) / 256);
   if (!push && ((g_force_bn == 512 && pair_ok) ||
-                (g_force_bn == 0 && pair_ok && plan.bn == 256 && plan.split == 1 && pair_tiles >= ctx->num_sms)))
+                (g_force_bn == 0 && pair_ok && plan.bn == 256 && plan.split == 1 && 2 * pair_tiles >= ctx->num_sms)))
     return launch_gemm_2cta<IS_FP8>(ctx, s, a, lda * eb, b, ldb * eb, p);
   if (plan.split > 1 || push) {  // the pushing epilogue lives in the split-K kernel (a "split" of 1 included)
     if (plan.bn == 512) plan.bn = 256;
