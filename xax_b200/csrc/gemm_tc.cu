@@ -359,8 +359,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             for (int v = 0; v < 4; ++v) {
               const int cc = c0 + h + v * 8;  // column within the tile
               float f[8];
+              {  // column multipliers and bias of the eight columns: four 16-byte shared-memory reads
+                const float4 ca = *reinterpret_cast<const float4*>(cmul_s + cc), cb = *reinterpret_cast<const float4*>(cmul_s + cc + 4);
+                const float4 ba = *reinterpret_cast<const float4*>(bias_s + cc), bb = *reinterpret_cast<const float4*>(bias_s + cc + 4);
+                const float cm[8] = {ca.x, ca.y, ca.z, ca.w, cb.x, cb.y, cb.z, cb.w};
+                const float bs[8] = {ba.x, ba.y, ba.z, ba.w, bb.x, bb.y, bb.z, bb.w};
 #pragma unroll
-              for (int j = 0; j < 8; ++j) f[j] = fmaf(__uint_as_float(r[v * 8 + j]) * rm, cmul_s[cc + j], bias_s[cc + j]);
+                for (int j = 0; j < 8; ++j) f[j] = fmaf(__uint_as_float(r[v * 8 + j]) * rm, cm[j], bs[j]);
+              }
               if (p.residual && row_ok && n0 + cc < p.N) {
                 const uint4 rv = *reinterpret_cast<const uint4*>(p.residual + (long long)m * p.ldr + n0 + cc);
                 const uint32_t rw[4] = {rv.x, rv.y, rv.z, rv.w};
