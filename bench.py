@@ -7,8 +7,12 @@ FP8 linears, batch 128, prompt 2048; config 4: 1.1B shape, batch 64, prompt 512)
 cache is filled by a real prefill before the timed region.  Rank 0 prints ONE JSON line:
 tokens/s device-timed over K CUDA-graph replays (`value`), the same through the host-facing
 step API with pinned host token buffers (`e2e`), the roofline of the dominant kernel (decode
-attention), the CPU oracle timed on a bounded sample (`cpu_baseline`), SM clocks sampled
-during the timed region, and per-kernel figures for benchmark configs 1 and 3 (`kernels`).
+attention with RoPE and the cache append fused in, plus its merge pass: the step's 32 launch pairs
+captured as a graph of their own and timed with CUDA events), the CPU oracle timed on a bounded
+sample (`cpu_baseline`), SM clocks sampled during the timed region, and per-kernel figures
+(`kernels`): quantize and FP8 GEMM of config 1 and 8192^3 with the cuBLASLt time of the same problems
+beside them, the four decode-size GEMMs of a config 5 layer, decode attention of config 3 in both
+cache layouts, and the block prefill of config 2.
 With N > 1 (torchrun) the model is tensor-parallel over N GPUs: strong scaling; the line then
 also carries `parity`, the first block's output on the sharded model against the unsharded one.
 `config` is the same in both arms; what only describes how this arm ran sits under `run`.
