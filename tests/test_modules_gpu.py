@@ -529,6 +529,15 @@ def test_pretrained_checkpoint_with_qk_norm(tmp_path):
     l_qk, _ = m.forward_batch(toks)
     l_plain, _ = llm_from_oracle(om).forward_batch(toks)
     assert l_qk.shape == l_plain.shape and not torch.equal(l_qk, l_plain)
+    # use_cross_attention wraps the loaded model with a freshly initialised shared cross-attention block (:706-708)
+    with pytest.raises(ValueError, match="key is required"):
+        build_pretrained_llm(str(tmp_path), use_fp8=False, use_cross_attention=True)
+    x = build_pretrained_llm(str(tmp_path), use_fp8=False, use_cross_attention=True, key=5)
+    assert type(x).__name__ == "CrossAttentionLLM" and x.cross_attn.num_heads == 4 and x.cross_attn.rotary_emb is None
+    enc = torch.randn((9, 128), device="cuda").to(torch.bfloat16)
+    out = x.forward(toks[0], encoder_output_sn=enc)
+    assert out.shape == (6, 256) and bool(torch.isfinite(out.float()).all())
+    assert torch.equal(x.forward(toks[0]), m.forward(toks[0]))  # without an encoder output: the plain model
 
 
 def test_yarn_tables_match_oracle_and_feed_the_block():

@@ -218,9 +218,16 @@ def build_pretrained_llm(repo: str, dtype=None, *, use_cross_attention: bool = F
     """xax/arch/llm.py:658-710 for a local checkpoint directory.  ``use_fp8`` (an extension, as in
     LLM.build) makes the projections Fp8Linear layers; the reference reaches the same by swapping
     them into the module tree."""
-    if use_cross_attention or extra_tokens is not None or tied_extra_embed:
-        raise ValueError("cross-attention wrappers and extra tokens are outside the path this library covers")
+    if extra_tokens is not None or tied_extra_embed:
+        raise ValueError("extra tokens are outside the path this library covers")
+    if use_cross_attention and key is None:
+        raise ValueError("key is required if use_cross_attention is True or extra_tokens is not None.")  # :691-693
     config = hf_config_to_llm_config(load_hf_config(repo))
     shape = LLM.build(config, key=0 if key is None else key, use_fp8=use_fp8, init_std=0.0, device=device,
                       tp_rank=tp_rank, tp_size=tp_size)
-    return load_hf_weights_into_llm(shape, repo, dtype=dtype)
+    llm = load_hf_weights_into_llm(shape, repo, dtype=dtype)
+    if use_cross_attention:  # :706-708: the cross-attention weights are freshly initialised
+        from .llm import CrossAttentionLLM
+
+        return CrossAttentionLLM.from_llm(llm, key=key)
+    return llm
