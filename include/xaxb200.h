@@ -155,8 +155,8 @@ int xaxb_lm_head_cross_entropy(xaxb_ctx* ctx, void* stream, const void* hidden_b
                                void* workspace, int64_t workspace_bytes, float* row_loss, int32_t* row_pred,
                                float* result);
 
-/* Test hook: force the tile width (32/64/128/256, 512 = the CTA-pair kernel with 256 x 256 tiles
- * where M > 128 and N >= 256, 0 = automatic) and the split-K factor
+/* Test hook: force the tile width (32/64/128/256; 512, 448, 384 = the CTA-pair kernel with 256 x 256,
+ * 256 x 224, 256 x 192 tiles where M > 128 and N >= 256; 0 = automatic) and the split-K factor
  * (1/2/4/8, 0 = automatic; > 1 needs M <= 128) of the following xaxb_gemm_* calls in this
  * process, so that tests can drive every kernel variant on the same inputs.  No counterpart
  * in the reference. */

@@ -201,8 +201,8 @@ def test_gemm_fp8_split_k_cluster_variants(ops, M, N, K, bn, split):
                                            (1024, 2048, 2048, True), (129, 256, 4096, True), (512, 512, 512, False),
                                            (2048, 8192, 2048, True)])
 def test_gemm_cta_pair_kernel(ops, M, N, K, fp8):
-    """The CTA-pair kernel (tcgen05.mma.cta_group::2, 256 x 256 tiles) against the single-CTA kernel
-    on the same inputs, with every epilogue term; integer-valued operands make both exact."""
+    """The CTA-pair kernel (tcgen05.mma.cta_group::2; 256 x 256, 256 x 224 and 256 x 192 tiles) against the
+    single-CTA kernel on the same inputs, with every epilogue term; integer-valued operands make all exact."""
     from xax_b200 import _lib
 
     rng = np.random.default_rng(M + N)
@@ -220,14 +220,15 @@ def test_gemm_cta_pair_kernel(ops, M, N, K, fp8):
     res = to_torch(rng.standard_normal((M, N)).astype(bf16))
     lib = _lib.load()
     outs = {}
-    for bn in (256, 512):
-        assert lib.xaxb_gemm_force_plan(bn, 1) == 0
+    for bn in (256, 512, 448, 384, 0):  # 0: the width the library picks by itself
+        assert lib.xaxb_gemm_force_plan(bn, 1 if bn else 0) == 0
         try:
             outs[bn] = f(a, b, rm, cm, bias, res)
         finally:
             lib.xaxb_gemm_force_plan(0, 0)
     _lib.device_status()
-    assert torch.equal(outs[256], outs[512])
+    for bn in (512, 448, 384, 0):
+        assert torch.equal(outs[256], outs[bn]), bn
 
 
 @pytest.mark.parametrize("M,N,K", [(128, 256, 512), (200, 1000, 1088), (64, 32000, 2048)])

@@ -517,7 +517,8 @@ def test_pretrained_checkpoint_with_qk_norm(tmp_path):
     from oracle import llm as ollm
     from xax_b200.arch.hf import build_pretrained_llm
 
-    cfg = ollm.LLMConfig(vocab_size=256, embed_dim=128, q_heads=4, kv_heads=2, head_dim=64, num_layers=2, max_tsz=128,
+    # embed_dim / q_heads = 64: the shared cross-attention block derives its head size from that quotient
+    cfg = ollm.LLMConfig(vocab_size=256, embed_dim=256, q_heads=4, kv_heads=2, head_dim=64, num_layers=2, max_tsz=128,
                          mlp_hidden_dim=256, rope_theta=1e6, rms_eps=1e-6)
     om = ollm.LLM.build(cfg, np.random.default_rng(4), use_fp8=False, tie=True, std=0.2)
     st = _write_hf_checkpoint(om, tmp_path, qk_norm=True)
@@ -534,7 +535,7 @@ def test_pretrained_checkpoint_with_qk_norm(tmp_path):
         build_pretrained_llm(str(tmp_path), use_fp8=False, use_cross_attention=True)
     x = build_pretrained_llm(str(tmp_path), use_fp8=False, use_cross_attention=True, key=5)
     assert type(x).__name__ == "CrossAttentionLLM" and x.cross_attn.num_heads == 4 and x.cross_attn.rotary_emb is None
-    enc = torch.randn((9, 128), device="cuda").to(torch.bfloat16)
+    enc = torch.randn((9, 256), device="cuda").to(torch.bfloat16)
     out = x.forward(toks[0], encoder_output_sn=enc)
     assert out.shape == (6, 256) and bool(torch.isfinite(out.float()).all())
     assert torch.equal(x.forward(toks[0]), m.forward(toks[0]))  # without an encoder output: the plain model

@@ -71,6 +71,30 @@ int make_tmap_2d(const Ctx* ctx, CUtensorMap* map, const void* base, int elem_by
   return XAXB_OK;
 }
 
+// The same tensor with an un-swizzled box: box rows lie back to back in shared memory, box_inner * elem_bytes
+// apart (a multiple of 16 bytes).
+int make_tmap_2d_plain(const Ctx* ctx, CUtensorMap* map, const void* base, int elem_bytes, uint64_t inner,
+                       uint64_t outer, uint64_t row_stride_bytes, uint32_t box_inner, uint32_t box_outer) {
+  if ((reinterpret_cast<uintptr_t>(base) & 15) || (row_stride_bytes & 15) || ((box_inner * elem_bytes) & 15) ||
+      box_inner == 0 || box_inner > 256 || box_outer > 256 || box_outer == 0) {
+    set_last_error("tensor map: base %p / row stride %llu must be 16-byte aligned, box %ux%u", base,
+                   (unsigned long long)row_stride_bytes, box_inner, box_outer);
+    return XAXB_BAD_ARGUMENT;
+  }
+  cuuint64_t dims[2] = {inner, outer};
+  cuuint64_t strides[1] = {row_stride_bytes};
+  cuuint32_t box[2] = {box_inner, box_outer};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = reinterpret_cast<EncodeTiledFn>(ctx->encode_tiled)(
+      map, tmap_dtype(elem_bytes), 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+      CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    set_last_error("cuTensorMapEncodeTiled(2d, plain) failed with CUresult %d", (int)r);
+    return XAXB_LAUNCH_FAILED;
+  }
+  return XAXB_OK;
+}
+
 int make_tmap_4d(const Ctx* ctx, CUtensorMap* map, const void* base, int elem_bytes, const uint64_t dims_in[4],
                  const uint64_t strides_bytes[3], const uint32_t box_in[4]) {
   if ((reinterpret_cast<uintptr_t>(base) & 15) || box_in[0] * elem_bytes != 128) {

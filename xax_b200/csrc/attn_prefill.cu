@@ -68,7 +68,12 @@ __global__ void __launch_bounds__(128, 2) attn_prefill_kernel(const __grid_const
   pdl_wait();  // nothing below may run ahead of the previous kernel in the stream
   using SM = PrefillSmem<D>;
   constexpr int kBoxes = D / 64;
-  const int qb = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
+  // CTAs start in the order of their linear index; under the causal mask the last query tile of a sequence has
+  // the most key tiles to walk, so the index is unfolded heaviest tile first (all heads and sequences of the
+  // last query tile, then the one before it, ...) and the short tiles fill the tail of the launch.
+  const int lin = blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z);
+  const int hb = gridDim.y * gridDim.z;
+  const int qb = (int)gridDim.x - 1 - lin / hb, h = (lin % hb) % (int)gridDim.y, b = (lin % hb) / (int)gridDim.y;
   const int hk = h / (p.Hq / p.Hkv);
   const int q0 = qb * kPfTile;                    // first query index of this CTA
   const int rows_valid = min(kPfTile, p.T - q0);

@@ -299,6 +299,8 @@ __device__ __forceinline__ uint32_t sw128_offset(uint32_t row, uint32_t chunk) {
 
 int make_tmap_2d(const Ctx* ctx, CUtensorMap* map, const void* base, int elem_bytes, uint64_t inner, uint64_t outer,
                  uint64_t row_stride_bytes, uint32_t box_inner, uint32_t box_outer);
+int make_tmap_2d_plain(const Ctx* ctx, CUtensorMap* map, const void* base, int elem_bytes, uint64_t inner,
+                       uint64_t outer, uint64_t row_stride_bytes, uint32_t box_inner, uint32_t box_outer);
 int make_tmap_4d(const Ctx* ctx, CUtensorMap* map, const void* base, int elem_bytes, const uint64_t dims[4],
                  const uint64_t strides_bytes[3], const uint32_t box[4]);
 void set_last_error(const char* fmt, ...);

@@ -1,5 +1,5 @@
-// Kernel 2, large-problem variant: 256 x 256 output tiles computed by PAIRS of CTAs (a thread-block
-// cluster of two SMs issuing tcgen05.mma.cta_group::2).
+// Kernel 2, large-problem variant: 256 x BN output tiles (BN = 256, 224 or 192) computed by PAIRS of CTAs
+// (a thread-block cluster of two SMs issuing tcgen05.mma.cta_group::2).
 //
 // The single-CTA kernel's 128 x 256 tile pulls 48 KiB of operands out of L2 for every
 // 128 x 256 x 128-byte MMA block and is bound by the SM's L2 read port (~105 GB/s per SM
@@ -8,6 +8,12 @@
 // per SM -- and one tcgen05.mma reads A and B halves from both CTAs' shared memory and writes
 // each CTA's 128 accumulator rows into that CTA's tensor memory.  No multicast is involved: each
 // CTA fetches its own halves with ordinary TMA tile loads.
+//
+// The narrower tiles exist for problems whose 256-wide tiles fill the last round of the persistent loop badly:
+// 2048 x 8192 x 2048 is 256 tiles of 256 x 256, 3.46 rounds for 74 pairs and therefore four tile-times, but
+// 296 tiles of 256 x 224, exactly four rounds of shorter tiles.  The launcher picks the width (see
+// pick_pair_width).  224 columns are three 64-column output blocks and one of 32, which is stored
+// through a second tensor map (32-column box, no swizzle).
 //
 // Synchronisation (leader = CTA rank 0 of the pair):
 //   full[s]      in the leader, 2 arrivals (one arrive.expect_tx per CTA) + both CTAs' TMA bytes;
@@ -64,26 +70,32 @@ __device__ __forceinline__ void umma_pair(uint32_t d_tmem, uint64_t a_desc, uint
   }
 }
 
+template <int BN_>
 struct Gemm2Cfg {
-  static constexpr int kBN = 256;                       // columns per pair tile
-  static constexpr int kStageBytes = 2 * kBM * kBKBytes;  // per CTA: 128 rows of A + 128 rows of B
+  static_assert(BN_ % 32 == 0 && BN_ >= 128 && BN_ <= 256, "pair tile width");
+  static constexpr int kBN = BN_;                       // columns per pair tile
+  static constexpr int kBRows = BN_ / 2;                // rows of the B tile each CTA loads
+  static constexpr int kStageBytes = 2 * kBM * kBKBytes;  // per CTA: a 16 KiB slot for A and one for B
+  static constexpr int kLoadBytes = (kBM + kBRows) * kBKBytes;  // what the two loads of a stage deliver
+  static constexpr int kAccStride = 256;                // columns between the two accumulators
   // Two staging blocks for the TMA stores: while the TMA unit reads one, the epilogue warps fill the other.
   // With a single block every 64-column store waited for the previous one's read, and a tile's epilogue
   // (four stores) took longer than the main loop of a short-K tile (config 1: K = 2048, 16 K blocks).
   // Five load stages of 32 KiB keep far more in flight than an SM's request capacity needs.
   static constexpr int kOutBlockBytes = kBM * 128;
-  static constexpr int kEpiBytes = 2 * kOutBlockBytes + 2 * kBN * 4;
+  static constexpr int kEpiBytes = 2 * kOutBlockBytes + 2 * 256 * 4;
   static constexpr int kStages = 5;
   static constexpr int kTmemCols = 512;                 // two 256-column accumulators
   static constexpr int kSmemBytes = kStages * kStageBytes + kEpiBytes + 1024 + 256;
 };
 
-template <bool IS_FP8>
+template <bool IS_FP8, int BN_>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-                 const __grid_constant__ CUtensorMap tmap_out, const GemmParams p) {
+                 const __grid_constant__ CUtensorMap tmap_out, const __grid_constant__ CUtensorMap tmap_out_half,
+                 const GemmParams p) {
   pdl_wait();  // nothing below may run ahead of the previous kernel in the stream
-  using Cfg = Gemm2Cfg;
+  using Cfg = Gemm2Cfg<BN_>;
   constexpr int kStages = Cfg::kStages, BN = Cfg::kBN;
   constexpr int kElemBytes = IS_FP8 ? 1 : 2;
   constexpr int kBKElems = kBKBytes / kElemBytes;
@@ -95,7 +107,7 @@ gemm_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   uint8_t* smem_b = smem + kStages * kBM * kBKBytes;   // kStages x 16 KiB
   uint8_t* stage_out = smem + kStages * Cfg::kStageBytes;
   float* cmul_s = reinterpret_cast<float*>(stage_out + 2 * Cfg::kOutBlockBytes);
-  float* bias_s = cmul_s + BN;
+  float* bias_s = cmul_s + 256;
   uint64_t* bars = reinterpret_cast<uint64_t*>(stage_out + Cfg::kEpiBytes);
   uint64_t* full = bars;
   uint64_t* empty = bars + kStages;
@@ -107,7 +119,7 @@ gemm_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t rank = cluster_ctarank();  // 0 = leader
   const int pair = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
-  const int num_tiles = p.tiles_m * p.tiles_n;  // 256 x 256 tiles
+  const int num_tiles = p.tiles_m * p.tiles_n;  // 256 x BN tiles
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) {
@@ -123,6 +135,7 @@ gemm_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     prefetch_tmap(&tmap_a);
     prefetch_tmap(&tmap_b);
     prefetch_tmap(&tmap_out);
+    if (BN % 64) prefetch_tmap(&tmap_out_half);
   }
   if (warp == 2) {
     asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
@@ -148,13 +161,13 @@ gemm_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         int tm, tn;
         tile_coords(p.band, tile, p.tiles_m, p.tiles_n, tm, tn);
         const int m0 = tm * (2 * kBM) + (int)rank * kBM;
-        const int n0 = tn * BN + (int)rank * kBM;
+        const int n0 = tn * BN + (int)rank * Cfg::kBRows;
         int kk = (int)(((long long)tile * 5) % p.num_k_blocks);
         for (int kb = 0; kb < p.num_k_blocks; ++kb) {
           ok = mbar_wait(empty + stage, phase ^ 1, abort_flag, p.d_status, XAXB_DEVICE_TIMEOUT * 1000 + kSite2Producer);
           if (!ok) break;
           const uint32_t leader_full = dsmem_addr(smem_u32(full + stage), 0);
-          mbar_arrive_expect_tx_cluster(leader_full, Cfg::kStageBytes);
+          mbar_arrive_expect_tx_cluster(leader_full, Cfg::kLoadBytes);
           tma_load_2d_pair(smem_a + stage * kBM * kBKBytes, &tmap_a, leader_full, kk * kBKElems, m0);
           tma_load_2d_pair(smem_b + stage * kBM * kBKBytes, &tmap_b, leader_full, kk * kBKElems, n0);
           if (++kk == p.num_k_blocks) kk = 0;
@@ -174,7 +187,7 @@ gemm_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         ok = mbar_wait(acc_empty + acc, acc_phase ^ 1, abort_flag, p.d_status, XAXB_DEVICE_TIMEOUT * 1000 + kSite2MmaAcc);
         if (!ok) break;
         tc_fence_after_sync();
-        const uint32_t d_tmem = tmem_base + acc * BN;
+        const uint32_t d_tmem = tmem_base + acc * Cfg::kAccStride;
         for (int kb = 0; kb < p.num_k_blocks; ++kb) {
           ok = mbar_wait(full + stage, phase, abort_flag, p.d_status, XAXB_DEVICE_TIMEOUT * 1000 + kSite2Mma);
           if (!ok) break;
@@ -224,20 +237,22 @@ gemm_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       bool ok = mbar_wait(acc_full + acc, acc_phase, abort_flag, p.d_status, XAXB_DEVICE_TIMEOUT * 1000 + kSite2Epilogue);
       if (!epilogue_all(ok)) break;  // (also publishes cmul_s / bias_s)
       tc_fence_after_sync();
-      const uint32_t taddr = tmem_base + (uint32_t(quarter * 32) << 16) + acc * BN;
+      const uint32_t taddr = tmem_base + (uint32_t(quarter * 32) << 16) + acc * Cfg::kAccStride;
 #pragma unroll 1
       for (int c0 = 0; c0 < BN; c0 += 64) {
         // the staging block about to be written was handed to the TMA unit two stores ago: that
         // store must have finished reading it (the one issued last may still be reading the other block)
         uint8_t* stage_blk = stage_out + ((c0 / 64) & 1) * Cfg::kOutBlockBytes;
+        const bool half_blk = (BN % 64) != 0 && c0 + 64 > BN;  // the tile's last 32 columns: rows of 64 bytes, no swizzle
         if (t == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
         epilogue_sync();
 #pragma unroll
         for (int h = 0; h < 64; h += 32) {
+          if ((BN % 64) != 0 && c0 + h >= BN) break;
           uint32_t r[32];
           tmem_ld_x32(taddr + c0 + h, r);
           tmem_ld_wait();
-          if (c0 + 64 >= BN && h == 32) {  // accumulator read out: tell the leader's MMA thread
+          if (c0 + h + 32 >= BN) {  // accumulator read out: tell the leader's MMA thread
             tc_fence_before_sync();
             __syncwarp();
             if (lane == 0) mbar_arrive_cluster(dsmem_addr(smem_u32(acc_empty + acc), 0));
@@ -271,7 +286,10 @@ gemm_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
               const uint32_t hi16 = __bfloat16_as_ushort(__float2bfloat16_rn(f[2 * j + 1]));
               ow[j] = lo16 | (hi16 << 16);
             }
-            *reinterpret_cast<uint4*>(stage_blk + sw128_offset(row_in_tile, (h + v * 8) / 8)) = o;
+            if (half_blk)
+              *reinterpret_cast<uint4*>(stage_blk + row_in_tile * 64 + v * 16) = o;
+            else
+              *reinterpret_cast<uint4*>(stage_blk + sw128_offset(row_in_tile, (h + v * 8) / 8)) = o;
           }
         }
         fence_proxy_async_smem();
@@ -279,7 +297,7 @@ gemm_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         if (t == 0) {
           if (n0 + c0 < p.N && m0 < p.M)
             asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
-                         ::"l"(&tmap_out), "r"(smem_u32(stage_blk)), "r"(n0 + c0), "r"(m0)
+                         ::"l"(half_blk ? &tmap_out_half : &tmap_out), "r"(smem_u32(stage_blk)), "r"(n0 + c0), "r"(m0)
                          : "memory");
           // one group per block, stored or not, so that "all but the latest group" always means "the
           // store that used the other staging block"
@@ -303,54 +321,101 @@ gemm_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   }
 }
 
+// How many CTA pairs can be resident at once.  Not every SM has a partner it can form a pair with, so the
+// driver is asked instead of assuming num_sms / 2.  (All tile widths use the same shared memory and threads.)
 template <bool IS_FP8>
-static int launch_gemm_2cta(const Ctx* ctx, cudaStream_t stream, const void* a, long long lda_bytes, const void* b,
-                            long long ldb_bytes, GemmParams& p) {
-  using Cfg = Gemm2Cfg;
+static int max_resident_pairs(const Ctx* ctx) {
+  static int max_pairs = 0;
+  if (max_pairs == 0) {
+    // the query fails for more than 48 KiB of dynamic shared memory unless the kernel has opted in
+    if (ensure_dynamic_smem<gemm_2cta_kernel<IS_FP8, 256>>(ctx, Gemm2Cfg<256>::kSmemBytes, "gemm_2cta_kernel"))
+      return ctx->num_sms / 2 - 8;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)(2 * (ctx->num_sms / 2)), 1, 1);
+    cfg.blockDim = dim3(kGemmThreads, 1, 1);
+    cfg.dynamicSmemBytes = Gemm2Cfg<256>::kSmemBytes;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    int n = 0;
+    cudaError_t qe = cudaOccupancyMaxActiveClusters(&n, gemm_2cta_kernel<IS_FP8, 256>, &cfg);
+    max_pairs = (qe == cudaSuccess && n > 0) ? n : ctx->num_sms / 2 - 8;
+    if (getenv("XAXB_GEMM_DEBUG")) fprintf(stderr, "gemm_2cta_kernel: %d resident pairs (query %s)\n", max_pairs, cudaGetErrorString(qe));
+  }
+  return max_pairs;
+}
+
+template <bool IS_FP8, int BN>
+static int launch_gemm_2cta_bn(const Ctx* ctx, cudaStream_t stream, const void* a, long long lda_bytes, const void* b,
+                               long long ldb_bytes, GemmParams& p, int max_pairs) {
+  using Cfg = Gemm2Cfg<BN>;
   constexpr int kElemBytes = IS_FP8 ? 1 : 2;
-  CUtensorMap ta, tb, tout;
+  CUtensorMap ta, tb, tout, thalf;
   int rc = make_tmap_2d(ctx, &ta, a, kElemBytes, (uint64_t)p.K, (uint64_t)p.M, (uint64_t)lda_bytes,
                         kBKBytes / kElemBytes, kBM);
   if (rc) return rc;
   rc = make_tmap_2d(ctx, &tb, b, kElemBytes, (uint64_t)p.K, (uint64_t)p.N, (uint64_t)ldb_bytes, kBKBytes / kElemBytes,
-                    kBM);
+                    Cfg::kBRows);
   if (rc) return rc;
   rc = make_tmap_2d(ctx, &tout, p.out, 2, (uint64_t)p.N, (uint64_t)p.M, (uint64_t)p.ldo * 2, 64, kBM);
   if (rc) return rc;
+  if (BN % 64) {  // the tile's last 32 columns
+    rc = make_tmap_2d_plain(ctx, &thalf, p.out, 2, (uint64_t)p.N, (uint64_t)p.M, (uint64_t)p.ldo * 2, 32, kBM);
+    if (rc) return rc;
+  } else {
+    thalf = tout;  // never read
+  }
   p.tiles_m = (p.M + 2 * kBM - 1) / (2 * kBM);
   if (!getenv("XAXB_GEMM_BAND")) p.band = 16;
-  p.tiles_n = (p.N + Cfg::kBN - 1) / Cfg::kBN;
+  p.tiles_n = (p.N + BN - 1) / BN;
   p.num_k_blocks = (int)(((long long)p.K * kElemBytes + kBKBytes - 1) / kBKBytes);
-  if (int rc2 = ensure_dynamic_smem<gemm_2cta_kernel<IS_FP8>>(ctx, Cfg::kSmemBytes, "gemm_2cta_kernel")) return rc2;
+  if (int rc2 = ensure_dynamic_smem<gemm_2cta_kernel<IS_FP8, BN>>(ctx, Cfg::kSmemBytes, "gemm_2cta_kernel")) return rc2;
   const int tiles = p.tiles_m * p.tiles_n;
-  cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3((unsigned)(2 * (ctx->num_sms / 2)), 1, 1);
-  cfg.blockDim = dim3(kGemmThreads, 1, 1);
-  cfg.dynamicSmemBytes = Cfg::kSmemBytes;
-  cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeClusterDimension;
-  attr[0].val.clusterDim.x = 2;
-  attr[0].val.clusterDim.y = 1;
-  attr[0].val.clusterDim.z = 1;
-  cfg.attrs = attr;
-  cfg.numAttrs = 1;
-  // The kernel is persistent: every pair must be resident at once.  Not every SM has a partner
-  // it can form a pair with, so ask how many pairs fit instead of assuming num_sms / 2.
-  static int max_pairs = 0;
-  if (max_pairs == 0) {
-    int n = 0;
-    cudaError_t qe = cudaOccupancyMaxActiveClusters(&n, gemm_2cta_kernel<IS_FP8>, &cfg);
-    max_pairs = (qe == cudaSuccess && n > 0) ? n : ctx->num_sms / 2 - 8;
-  }
+  // The kernel is persistent: every pair must be resident at once.
   const int pairs = tiles < max_pairs ? tiles : max_pairs;
-  cudaError_t e = launch_kernel(gemm_2cta_kernel<IS_FP8>, dim3((unsigned)(2 * pairs), 1, 1), dim3(kGemmThreads),
-                                Cfg::kSmemBytes, stream, 2u, ta, tb, tout, p);
+  cudaError_t e = launch_kernel(gemm_2cta_kernel<IS_FP8, BN>, dim3((unsigned)(2 * pairs), 1, 1), dim3(kGemmThreads),
+                                Cfg::kSmemBytes, stream, 2u, ta, tb, tout, thalf, p);
   if (e != cudaSuccess) {
     set_last_error("gemm_2cta_kernel launch: %s", cudaGetErrorString(e));
     return XAXB_LAUNCH_FAILED;
   }
   return check_launch("gemm_2cta_kernel");
+}
+
+// Width of the pair tiles: every pair walks ceil(tiles / pairs) tiles.  A tile's time follows the operand bytes
+// its CTAs pull in per K block (128 rows of A plus width / 2 rows of B each), not its flops: measured per round,
+// 224 columns cost 0.94 and 192 columns 0.86 of what 256 columns cost.  So the width with the smallest
+// rounds x (256 + width + 32) wins; 256 unless a narrower one is at least 3 % cheaper (2048 x 8192 x 2048:
+// 40.0 us with 224 columns against 42.0).  force_bn (256 / 224 / 192) overrides (tests).
+static int pick_pair_width(long long M, long long N, int max_pairs, int force_bn) {
+  if (force_bn) return force_bn;
+  const long long tiles_m = (M + 2 * kBM - 1) / (2 * kBM);
+  auto cost = [&](int bn) {
+    const long long tiles = tiles_m * ((N + bn - 1) / bn);
+    return ((tiles + max_pairs - 1) / max_pairs) * (long long)(256 + bn + 32);
+  };
+  int best = 256;
+  long long best_cost = cost(256) * 97;  // in hundredths: a narrower tile must beat 97 % of this
+  for (int bn : {224, 192}) {
+    const long long c = cost(bn) * 100;
+    if (c < best_cost) best = bn, best_cost = c;
+  }
+  return best;
+}
+
+template <bool IS_FP8>
+static int launch_gemm_2cta(const Ctx* ctx, cudaStream_t stream, const void* a, long long lda_bytes, const void* b,
+                            long long ldb_bytes, GemmParams& p, int force_bn) {
+  const int max_pairs = max_resident_pairs<IS_FP8>(ctx);
+  switch (pick_pair_width(p.M, p.N, max_pairs, force_bn)) {
+    case 224: return launch_gemm_2cta_bn<IS_FP8, 224>(ctx, stream, a, lda_bytes, b, ldb_bytes, p, max_pairs);
+    case 192: return launch_gemm_2cta_bn<IS_FP8, 192>(ctx, stream, a, lda_bytes, b, ldb_bytes, p, max_pairs);
+    default: return launch_gemm_2cta_bn<IS_FP8, 256>(ctx, stream, a, lda_bytes, b, ldb_bytes, p, max_pairs);
+  }
 }
 
 }  // namespace xaxb

@@ -962,7 +962,7 @@ static GemmPlan pick_plan(long long M, long long N, long long K, int elem_bytes,
       if (t < best_t) best_t = t, best = {bn, s};
     }
   }
-  if (g_force_bn && g_force_bn != 512) best.bn = g_force_bn;
+  if (g_force_bn && g_force_bn < 384) best.bn = g_force_bn;
   if (g_force_split) best.split = g_force_split;
   return best;
 }
@@ -1041,9 +1041,10 @@ static int gemm_entry(xaxb_ctx* ctx_, void* stream, const void* a, int64_t lda, 
   // than 128 x 256 tiles from 128 pair tiles up, e.g. 95 against 104 us for 2048 x 4096 x 14336).
   const bool pair_ok = M > kBM && N >= 256;
   const long long pair_tiles = ((long long)(M + 255) / 256) * ((N + 255) / 256);
-  if (!push && ((g_force_bn == 512 && pair_ok) ||
+  const bool force_pair = g_force_bn == 512 || g_force_bn == 448 || g_force_bn == 384;  // 2 x the tile width
+  if (!push && ((force_pair && pair_ok) ||
                 (g_force_bn == 0 && pair_ok && plan.bn == 256 && plan.split == 1 && 2 * pair_tiles >= ctx->num_sms)))
-    return launch_gemm_2cta<IS_FP8>(ctx, s, a, lda * eb, b, ldb * eb, p);
+    return launch_gemm_2cta<IS_FP8>(ctx, s, a, lda * eb, b, ldb * eb, p, force_pair ? g_force_bn / 2 : 0);
   if (plan.split > 1 || push) {  // the pushing epilogue lives in the split-K kernel (a "split" of 1 included)
     if (plan.bn == 512) plan.bn = 256;
     if (M > kBM || plan.split > 8) {
@@ -1072,7 +1073,7 @@ using namespace xaxb;
 extern "C" {
 
 int xaxb_gemm_force_plan(int bn, int split) {
-  if ((bn != 0 && bn != 32 && bn != 64 && bn != 128 && bn != 256 && bn != 512) ||
+  if ((bn != 0 && bn != 32 && bn != 64 && bn != 128 && bn != 256 && bn != 512 && bn != 448 && bn != 384) ||
       (split != 0 && split != 1 && split != 2 && split != 4 && split != 8))
     return XAXB_BAD_ARGUMENT;
   g_force_bn = bn;
