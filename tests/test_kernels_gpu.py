@@ -201,7 +201,7 @@ def test_gemm_fp8_split_k_cluster_variants(ops, M, N, K, bn, split):
                                            (1024, 2048, 2048, True), (129, 256, 4096, True), (512, 512, 512, False),
                                            (2048, 8192, 2048, True)])
 def test_gemm_cta_pair_kernel(ops, M, N, K, fp8):
-    """The CTA-pair kernel (tcgen05.mma.cta_group::2; 256 x 256, 256 x 224 and 256 x 192 tiles) against the
+    """The CTA-pair kernels (tcgen05.mma.cta_group::2; 256 x 256, 256 x 224 and 256 x 192 tiles) against the
     single-CTA kernel on the same inputs, with every epilogue term; integer-valued operands make all exact."""
     from xax_b200 import _lib
 

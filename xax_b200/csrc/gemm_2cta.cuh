@@ -344,7 +344,6 @@ static int max_resident_pairs(const Ctx* ctx) {
     int n = 0;
     cudaError_t qe = cudaOccupancyMaxActiveClusters(&n, gemm_2cta_kernel<IS_FP8, 256>, &cfg);
     max_pairs = (qe == cudaSuccess && n > 0) ? n : ctx->num_sms / 2 - 8;
-    if (getenv("XAXB_GEMM_DEBUG")) fprintf(stderr, "gemm_2cta_kernel: %d resident pairs (query %s)\n", max_pairs, cudaGetErrorString(qe));
   }
   return max_pairs;
 }
