@@ -32,6 +32,43 @@ __global__ void __launch_bounds__(256) quantize_rows_kernel(const uint4* __restr
   }
 }
 
+// The same for rows of up to NT * VPT pieces of 16 bytes, kept in registers between the two sweeps.  Launched
+// with narrow CTAs when there are many rows: a row is one dependent chain (load, maximum, cast, store), and an
+// SM overlaps as many chains as it has CTAs resident.
+template <int VPT, int NT>
+__global__ void __launch_bounds__(NT) quantize_rows_reg_kernel(const uint4* __restrict__ x, int vec_per_row,
+                                                               uint2* __restrict__ q, float* __restrict__ scale,
+                                                               float* __restrict__ inv_scale,
+                                                               float* __restrict__ amax) {
+  pdl_trigger();
+  pdl_wait();
+  const int64_t row = blockIdx.x;
+  const uint4* xr = x + row * vec_per_row;
+  uint4 v[VPT];
+  uint32_t m = 0;
+#pragma unroll
+  for (int k = 0; k < VPT; ++k) {
+    const int i = threadIdx.x + k * NT;
+    v[k] = i < vec_per_row ? __ldg(xr + i) : make_uint4(0, 0, 0, 0);
+  }
+#pragma unroll
+  for (int k = 0; k < VPT; ++k) m = absmax_bits8(m, v[k]);
+  const uint32_t row_bits = block_max_u32(m);
+  const float a = bf16_bits_to_float(row_bits);
+  const float s = current_scale_from_amax(a);
+  uint2* qr = q + row * vec_per_row;
+#pragma unroll
+  for (int k = 0; k < VPT; ++k) {
+    const int i = threadIdx.x + k * NT;
+    if (i < vec_per_row) qr[i] = quantize8(v[k], s);
+  }
+  if (threadIdx.x == 0) {
+    scale[row] = s;
+    inv_scale[row] = 1.0f / s;
+    amax[row] = a;
+  }
+}
+
 // ---- per-group current scaling, pass 1: amax of each group of rows -------------------------
 __global__ void __launch_bounds__(256) group_amax_kernel(const uint4* __restrict__ x, int64_t vec_per_group,
                                                          unsigned int* __restrict__ amax_bits) {
@@ -221,7 +258,14 @@ int xaxb_quantize_current(xaxb_ctx* ctx, void* stream, const void* x_bf16, int64
     const int64_t vec = cols / 8;
     int threads = (int)((vec + 31) / 32 * 32);
     if (threads > 256) threads = 256;
-    launch_kernel(quantize_rows_kernel, dim3((unsigned)rows), dim3(threads), 0, s, 1, x, vec, q, scale, inv_scale, amax);
+    if (rows > 2 * c->num_sms && vec > 64 && vec <= 256)
+      launch_kernel(quantize_rows_reg_kernel<4, 64>, dim3((unsigned)rows), dim3(64), 0, s, 1, x, (int)vec, q, scale, inv_scale, amax);
+    else if (rows > 2 * c->num_sms && vec > 256 && vec <= 512)
+      launch_kernel(quantize_rows_reg_kernel<4, 128>, dim3((unsigned)rows), dim3(128), 0, s, 1, x, (int)vec, q, scale, inv_scale, amax);
+    else if (rows > 2 * c->num_sms && vec > 512 && vec <= 1024)
+      launch_kernel(quantize_rows_reg_kernel<4, 256>, dim3((unsigned)rows), dim3(256), 0, s, 1, x, (int)vec, q, scale, inv_scale, amax);
+    else
+      launch_kernel(quantize_rows_kernel, dim3((unsigned)rows), dim3(threads), 0, s, 1, x, vec, q, scale, inv_scale, amax);
     return check_launch("quantize_rows_kernel");
   }
   const int64_t groups = rows / group_rows;

@@ -188,6 +188,54 @@ __device__ __forceinline__ uint32_t ld_dsmem_u32(uint32_t local_smem_addr, uint3
   return v;
 }
 
+// Many rows (prefill): one CTA per row as in silu_mul_kernel, but silu(g) * u -- an exponential and a division
+// per element -- is computed once and kept as packed bf16 (VPT x 16 bytes per thread) across the row-maximum
+// reduction instead of being recomputed for the cast.  Same values, same bytes.
+template <int VPT>
+__global__ void __launch_bounds__(256) silu_mul_reg_kernel(const uint4* __restrict__ gate, const uint4* __restrict__ up,
+                                                           int64_t ld_vec, int vec, uint4* __restrict__ h,
+                                                           uint2* __restrict__ q, float* __restrict__ scale,
+                                                           float* __restrict__ inv_scale,
+                                                           unsigned int* __restrict__ group_amax, int64_t group_rows) {
+  pdl_trigger();
+  pdl_wait();
+  const int64_t row = blockIdx.x;
+  const uint4* gr = gate + row * ld_vec;
+  const uint4* ur = up + row * ld_vec;
+  uint4 hv[VPT];
+  uint32_t m = 0;
+#pragma unroll
+  for (int k = 0; k < VPT; ++k) {
+    const int i = threadIdx.x + k * 256;
+    hv[k] = make_uint4(0, 0, 0, 0);
+    if (i < vec) {
+      float f[8];
+      silu_mul8(__ldg(gr + i), __ldg(ur + i), f);
+      hv[k] = pack8(f);
+      if (h) h[row * vec + i] = hv[k];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) m = max(m, mag_bits16(f[j]));
+    }
+  }
+  const uint32_t row_bits = block_max_u32(m);
+  if (group_amax && threadIdx.x == 0) atomicMax(group_amax + row / group_rows, row_bits << 16);
+  if (!q) return;
+  const float s = current_scale_from_amax(bf16_bits_to_float(row_bits));
+#pragma unroll
+  for (int k = 0; k < VPT; ++k) {
+    const int i = threadIdx.x + k * 256;
+    if (i < vec) {
+      float f[8];
+      unpack8(hv[k], f);
+      q[row * vec + i] = quantize8f(f, s);
+    }
+  }
+  if (threadIdx.x == 0) {
+    scale[row] = s;
+    inv_scale[row] = 1.0f / s;
+  }
+}
+
 template <int VPT>
 __global__ void __launch_bounds__(256) silu_mul_cluster_kernel(const uint4* __restrict__ gate,
                                                                const uint4* __restrict__ up, int64_t ld_vec, int vec,
@@ -587,6 +635,13 @@ int xaxb_rmsnorm(xaxb_ctx* ctx, void* stream, const void* x_bf16, const void* we
     launch_kernel(rmsnorm_reg_kernel<1, 512>, dim3((unsigned)rows), dim3(512), 0, st, 1, xp, wp, eps, (int)vec, yp, qp, scale, inv_scale, gp, gr);
   else if (few_rows && vec > 512 && vec <= 1024)
     launch_kernel(rmsnorm_reg_kernel<1, 1024>, dim3((unsigned)rows), dim3(1024), 0, st, 1, xp, wp, eps, (int)vec, yp, qp, scale, inv_scale, gp, gr);
+  // Many rows (prefill): a row's work is one dependent chain (load, sum, normalise, maximum, store), so what
+  // counts is how many rows an SM has in flight: narrow CTAs with four 16-byte pieces per thread keep four times
+  // as many rows and loads in flight as one piece per thread (4096 x 2048: 17 -> 9 us).
+  else if (!few_rows && vec > 64 && vec <= 256)
+    launch_kernel(rmsnorm_reg_kernel<4, 64>, dim3((unsigned)rows), dim3(64), 0, st, 1, xp, wp, eps, (int)vec, yp, qp, scale, inv_scale, gp, gr);
+  else if (!few_rows && vec > 256 && vec <= 512)
+    launch_kernel(rmsnorm_reg_kernel<4, 128>, dim3((unsigned)rows), dim3(128), 0, st, 1, xp, wp, eps, (int)vec, yp, qp, scale, inv_scale, gp, gr);
   else if (vec > 64 && vec <= 256)
     launch_kernel(rmsnorm_reg_kernel<1>, dim3((unsigned)rows), dim3(256), 0, st, 1, xp, wp, eps, (int)vec, yp, qp, scale, inv_scale, gp, gr);
   else if (vec > 256 && vec <= 512)
@@ -641,6 +696,20 @@ int xaxb_silu_mul(xaxb_ctx* ctx, void* stream, const void* gate_bf16, const void
       }
       return check_launch("silu_mul_cluster_kernel");
     }
+  }
+  if ((qp || gp) && vec > 256 && vec <= 8 * 256) {  // the row fits the registers of one 256-thread CTA
+    const int vpt = (int)((vec + 255) / 256);
+    const dim3 grid((unsigned)rows);
+#define XAXB_SILU_REG(V)                                                                                        \
+  launch_kernel(silu_mul_reg_kernel<V>, grid, dim3(256), 0, st, 1, gate, up, ld / 8, (int)vec, hp, qp, scale, \
+                inv_scale, gp, gr)
+    if (vpt <= 2) XAXB_SILU_REG(2);
+    else if (vpt <= 3) XAXB_SILU_REG(3);
+    else if (vpt <= 4) XAXB_SILU_REG(4);
+    else if (vpt <= 6) XAXB_SILU_REG(6);
+    else XAXB_SILU_REG(8);
+#undef XAXB_SILU_REG
+    return check_launch("silu_mul_reg_kernel");
   }
   launch_kernel(silu_mul_kernel, dim3((unsigned)rows), dim3(row_threads(vec)), 0, st, 1, gate, up, ld / 8, vec, hp, qp, scale, inv_scale, gp, gr,
                                                                TpRowMax{}, nullptr);
