@@ -175,6 +175,7 @@ __global__ void __launch_bounds__(NT) tp_push_sum_norm_kernel(
       const unsigned long long t0 = globaltimer_ns();
       const unsigned long long limit = peer_wait_limit_ns(d_status);
       while ((int32_t)(ld_acquire_sys(counter) - want) < 0) {
+        __nanosleep(32);  // a hundred CTAs poll at once: leave the memory system to the stores they wait for
         if (*reinterpret_cast<volatile int*>(d_status) != 0) break;
         if (globaltimer_ns() - t0 > limit) {
           atomicCAS(d_status, 0, XAXB_DEVICE_TIMEOUT * 1000 + kSiteTpPush);

@@ -133,6 +133,7 @@ __device__ __forceinline__ uint32_t tp_cta_max_u32(const TpRowMax& tp, int slot,
       for (;;) {
         asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(w) : "l"(my_box) : "memory");
         if ((uint32_t)(w >> 32) == epoch) break;
+        __nanosleep(32);  // a hundred CTAs poll at once: leave the memory system to the stores they wait for
         if (*reinterpret_cast<volatile int*>(d_status) != 0) break;
         if (globaltimer_ns() - t0 > limit) {
           atomicCAS(d_status, 0, XAXB_DEVICE_TIMEOUT * 1000 + site);
