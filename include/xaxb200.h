@@ -109,6 +109,22 @@ int xaxb_quantize_delayed(xaxb_ctx* ctx, void* stream, const void* x_bf16, int64
 int xaxb_dequantize(xaxb_ctx* ctx, void* stream, const void* q_e4m3, int64_t rows, int64_t cols, const float* scale,
                     int scale_stride, int out_is_bf16, void* out);
 
+/*
+ * float8_e5m2 for the free functions (xax/nn/fp8.py:97-162 and :347-378 called with fp8_dtype=float8_e5m2; the
+ * reference's tests/nn/test_fp8.py parametrises them over both formats).  The transformer path itself quantises
+ * to e4m3 only.  x is [rows, cols] bf16, cols a multiple of 8; groups of group_rows rows share a scale, which is
+ * either bf16(*scale_in) for every group (quantize with a given scalar scale) or
+ * bf16(57344 / max(group_amax[g], bf16(1e-12))) (current scaling; group_amax as xaxb_group_amax leaves it).
+ * Exactly one of scale_in / group_amax is non-null.  q = e5m2(clip(bf16(x * s), +-57344)); NaN -> 0x7E / 0xFE.
+ * scale / inv_scale ([rows] float32, both or neither) receive s and 1 / s per row.
+ */
+int xaxb_quantize_e5m2(xaxb_ctx* ctx, void* stream, const void* x_bf16, int64_t rows, int64_t cols, int64_t group_rows,
+                       const float* scale_in, const float* group_amax, void* q_e5m2, float* scale, float* inv_scale);
+
+/* xaxb_dequantize for e5m2 bytes (same contract). */
+int xaxb_dequantize_e5m2(xaxb_ctx* ctx, void* stream, const void* q_e5m2, int64_t rows, int64_t cols, const float* scale,
+                         int scale_stride, int out_is_bf16, void* out);
+
 /* ---- kernel 2: e4m3 x e4m3 (and bf16 x bf16) GEMM on tcgen05 / TMEM ------------- */
 
 /*
@@ -128,6 +144,14 @@ int xaxb_gemm_fp8(xaxb_ctx* ctx, void* stream, const void* a_e4m3, int64_t lda, 
                   int64_t M, int64_t N, int64_t K, const float* row_mul, int row_mul_stride, const float* col_mul,
                   int col_mul_stride, const void* bias_bf16, const void* residual_bf16, int64_t ldr, void* out_bf16,
                   int64_t ldo);
+
+/* xaxb_gemm_fp8 with the format of each operand stated (0 = e4m3, non-zero = e5m2): the tensor core's
+ * f8f6f4 kind takes either format on either side.  Serves fp8_matmul(..., fp8_dtype=float8_e5m2)
+ * (xax/nn/fp8.py:347-378). */
+int xaxb_gemm_fp8_formats(xaxb_ctx* ctx, void* stream, const void* a_fp8, int64_t lda, int a_is_e5m2,
+                          const void* b_fp8, int64_t ldb, int b_is_e5m2, int64_t M, int64_t N, int64_t K,
+                          const float* row_mul, int row_mul_stride, const float* col_mul, int col_mul_stride,
+                          const void* bias_bf16, const void* residual_bf16, int64_t ldr, void* out_bf16, int64_t ldo);
 
 /* Same contract for bf16 operands (lda/ldb in elements): the un-quantised linear /
  * lm_head einsum of xax/arch/attention.py:59-67 (xax/arch/llm.py:213-219). */

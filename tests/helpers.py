@@ -6,6 +6,7 @@ import torch
 
 bf16 = ml_dtypes.bfloat16
 e4m3 = ml_dtypes.float8_e4m3fn
+e5m2 = ml_dtypes.float8_e5m2
 
 
 def to_torch(a: np.ndarray, device="cuda") -> torch.Tensor:
@@ -14,6 +15,8 @@ def to_torch(a: np.ndarray, device="cuda") -> torch.Tensor:
         return torch.from_numpy(a.view(np.uint16).astype(np.int32)).to(torch.int16).view(torch.bfloat16).to(device)
     if a.dtype == np.dtype(e4m3):
         return torch.from_numpy(a.view(np.uint8).copy()).view(torch.float8_e4m3fn).to(device)
+    if a.dtype == np.dtype(e5m2):
+        return torch.from_numpy(a.view(np.uint8).copy()).view(torch.float8_e5m2).to(device)
     return torch.from_numpy(a).to(device)
 
 
@@ -23,6 +26,8 @@ def to_numpy(t: torch.Tensor) -> np.ndarray:
         return t.view(torch.int16).numpy().view(np.uint16).view(bf16)
     if t.dtype == torch.float8_e4m3fn:
         return t.view(torch.uint8).numpy().view(e4m3)
+    if t.dtype == torch.float8_e5m2:
+        return t.view(torch.uint8).numpy().view(e5m2)
     return t.numpy()
 
 

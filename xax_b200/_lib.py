@@ -45,6 +45,10 @@ SIGNATURES: dict[str, tuple] = {
     "xaxb_quantize_delayed": (_I, [_P, _P, _P, _I64, _I64, _P, _P, _I, _P, _P, _P, _P, _P]),
     "xaxb_dequantize": (_I, [_P, _P, _P, _I64, _I64, _P, _I, _I, _P]),
     "xaxb_quantize_with_amax": (_I, [_P, _P, _P, _I64, _I64, _I64, _P, _P, _P, _P]),
+    "xaxb_quantize_e5m2": (_I, [_P, _P, _P, _I64, _I64, _I64, _P, _P, _P, _P, _P]),
+    "xaxb_dequantize_e5m2": (_I, [_P, _P, _P, _I64, _I64, _P, _I, _I, _P]),
+    "xaxb_gemm_fp8_formats": (_I, [_P, _P, _P, _I64, _I, _P, _I64, _I, _I64, _I64, _I64, _P, _I, _P, _I, _P, _P, _I64,
+                                   _P, _I64]),
     "xaxb_gemm_fp8": (_I, [_P, _P, _P, _I64, _P, _I64, _I64, _I64, _I64, _P, _I, _P, _I, _P, _P, _I64, _P, _I64]),
     "xaxb_gemm_bf16": (_I, [_P, _P, _P, _I64, _P, _I64, _I64, _I64, _I64, _P, _I, _P, _I, _P, _P, _I64, _P, _I64]),
     "xaxb_gemm_force_plan": (_I, [_I, _I]),

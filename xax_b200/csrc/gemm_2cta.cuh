@@ -196,7 +196,7 @@ gemm_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           const uint64_t b_desc = umma_desc_kmajor_sw128(smem_u32(smem_b + stage * kBM * kBKBytes));
 #pragma unroll
           for (int k = 0; k < kBKBytes / 32; ++k)
-            umma_pair<IS_FP8>(d_tmem, a_desc + 2 * k, b_desc + 2 * k, kIdesc, (kb | k) != 0);
+            umma_pair<IS_FP8>(d_tmem, a_desc + 2 * k, b_desc + 2 * k, kIdesc | p.idesc_or, (kb | k) != 0);
           umma_commit_pair(smem_u32(empty + stage));
           umma_commit_pair(dsmem_addr(smem_u32(empty + stage), 1));
           if (++stage == kStages) stage = 0, phase ^= 1;

@@ -40,6 +40,9 @@ struct GemmParams {
   __nv_bfloat16* out;
   long long ldo;
   int* d_status;
+  // OR-ed into the MMA instruction descriptor: the operand formats when they are not e4m3 (bit 7 = A is e5m2,
+  // bit 10 = B is e5m2; the f8f6f4 kind mixes the two freely).  0 for e4m3 x e4m3 and for bf16.
+  uint32_t idesc_or;
   // The launch may overlap the previous kernel (programmatic dependent launch).  Operand B -- the
   // weights of a linear layer -- is never written by a kernel of the same stream section, so the
   // producer may fetch it before it waits for the previous kernel:
@@ -248,7 +251,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
           for (int k = 0; k < kBKBytes / 32; ++k) {
             // advancing the start address by 32 bytes (>> 4 = 2) walks K inside the swizzle span
             if (IS_FP8)
-              umma_f8(d_tmem, a_desc + 2 * k, b_desc + 2 * k, kIdesc, (kb | k) != 0);
+              umma_f8(d_tmem, a_desc + 2 * k, b_desc + 2 * k, kIdesc | p.idesc_or, (kb | k) != 0);
             else
               umma_f16(d_tmem, a_desc + 2 * k, b_desc + 2 * k, kIdesc, (kb | k) != 0);
           }
@@ -676,7 +679,7 @@ gemm_splitk_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
 #pragma unroll
         for (int k = 0; k < kBKBytes / 32; ++k) {
           if (IS_FP8)
-            umma_f8(tmem_base, a_desc + 2 * k, b_desc + 2 * k, kIdesc, (i | k) != 0);
+            umma_f8(tmem_base, a_desc + 2 * k, b_desc + 2 * k, kIdesc | p.idesc_or, (i | k) != 0);
           else
             umma_f16(tmem_base, a_desc + 2 * k, b_desc + 2 * k, kIdesc, (i | k) != 0);
         }
@@ -979,7 +982,7 @@ template <bool IS_FP8>
 static int gemm_entry(xaxb_ctx* ctx_, void* stream, const void* a, int64_t lda, const void* b, int64_t ldb, int64_t M,
                       int64_t N, int64_t K, const float* row_mul, int row_mul_stride, const float* col_mul,
                       int col_mul_stride, const void* bias, const void* residual, int64_t ldr, void* out,
-                      int64_t ldo, const PushTarget* push = nullptr) {
+                      int64_t ldo, const PushTarget* push = nullptr, uint32_t idesc_or = 0) {
   if (push) {
     if (!push->peer_bases || push->world < 1 || push->world > 8 || push->rank < 0 || push->rank >= push->world ||
         (push->slot_offset_bytes & 15) || (push->flag_offset_bytes & 3) || push->slot_offset_bytes < 0 ||
@@ -1017,6 +1020,7 @@ static int gemm_entry(xaxb_ctx* ctx_, void* stream, const void* a, int64_t lda, 
   p.ldr = ldr;
   p.out = static_cast<__nv_bfloat16*>(out);
   p.ldo = ldo;
+  p.idesc_or = idesc_or;
   p.d_status = ctx->d_status;
   p.prefetch_l2 = pdl_enabled() ? g_prefetch_l2 : 0;
   p.push_world = 0;
@@ -1085,6 +1089,15 @@ int xaxb_gemm_set_prefetch(int blocks_before_wait) {
   if (blocks_before_wait < 0 || blocks_before_wait > 4096) return XAXB_BAD_ARGUMENT;
   g_prefetch_l2 = blocks_before_wait;
   return XAXB_OK;
+}
+
+int xaxb_gemm_fp8_formats(xaxb_ctx* ctx, void* stream, const void* a_fp8, int64_t lda, int a_is_e5m2,
+                          const void* b_fp8, int64_t ldb, int b_is_e5m2, int64_t M, int64_t N, int64_t K,
+                          const float* row_mul, int row_mul_stride, const float* col_mul, int col_mul_stride,
+                          const void* bias_bf16, const void* residual_bf16, int64_t ldr, void* out_bf16, int64_t ldo) {
+  const uint32_t idesc_or = (a_is_e5m2 ? 1u << 7 : 0u) | (b_is_e5m2 ? 1u << 10 : 0u);
+  return gemm_entry<true>(ctx, stream, a_fp8, lda, b_fp8, ldb, M, N, K, row_mul, row_mul_stride, col_mul,
+                          col_mul_stride, bias_bf16, residual_bf16, ldr, out_bf16, ldo, nullptr, idesc_or);
 }
 
 int xaxb_gemm_fp8(xaxb_ctx* ctx, void* stream, const void* a_e4m3, int64_t lda, const void* b_e4m3, int64_t ldb,
@@ -1226,6 +1239,7 @@ extern "C" int xaxb_lm_head_cross_entropy(xaxb_ctx* ctx_, void* stream, const vo
   p.out = static_cast<__nv_bfloat16*>(workspace);
   p.ldo = (V + 7) / 8 * 8;
   p.d_status = ctx->d_status;
+  p.idesc_or = 0;
   p.prefetch_l2 = pdl_enabled() ? g_prefetch_l2 : 0;
   p.band = 32;
   p.push_world = 0;

@@ -9,7 +9,9 @@ Differences from the reference, all deliberate:
     reference's; the output differs from the QDQ formulation by ~4e-3 relative;
   * the weight is quantised once per (weight, scale) and cached instead of on every call
     (xax/nn/fp8.py:336);
-  * ``float8_e5m2`` is accepted by the free functions' signatures but rejected by the kernels.
+  * ``float8_e5m2`` is served by the free functions (``quantize``, ``dequantize``, ``quantize_dequantize``,
+    ``fp8_matmul``: what the reference's tests exercise in both formats); ``Fp8Linear`` itself, i.e. the
+    transformer path, takes ``float8_e4m3fn`` only.
 """
 
 from __future__ import annotations
@@ -33,7 +35,13 @@ def _dev(device=None):
 
 def _only_e4m3(fp8_dtype) -> None:
     if fp8_dtype != torch.float8_e4m3fn:
-        raise ValueError(f"unsupported fp8 dtype {fp8_dtype}: the sm_100a kernels implement float8_e4m3fn only")
+        raise ValueError(f"unsupported fp8 dtype {fp8_dtype}: the fused sm_100a kernels of the linear layer implement "
+                         "float8_e4m3fn only")
+
+
+def _fp8_format(fp8_dtype) -> None:
+    if fp8_dtype not in (torch.float8_e4m3fn, torch.float8_e5m2):
+        raise ValueError(f"unsupported fp8 dtype {fp8_dtype}: float8_e4m3fn or float8_e5m2")
 
 
 def get_fp8_max(fp8_dtype: torch.dtype, compute_dtype: torch.dtype = torch.float32) -> torch.Tensor:
@@ -93,7 +101,7 @@ def quantize(x: torch.Tensor, fp8_dtype: torch.dtype, scale: torch.Tensor,
              compute_dtype: torch.dtype = torch.float32) -> torch.Tensor:
     """xax/nn/fp8.py:97-120 for a scalar scale.  The kernels implement the bf16 compute dtype
     that Fp8Linear uses; x is cast to bf16 first."""
-    _only_e4m3(fp8_dtype)
+    _fp8_format(fp8_dtype)
     if torch.as_tensor(scale).numel() != 1:
         raise ValueError("quantize: the kernel path takes a scalar scale")
     shape = x.shape
@@ -101,6 +109,9 @@ def quantize(x: torch.Tensor, fp8_dtype: torch.dtype, scale: torch.Tensor,
     cols = x2.shape[-1]
     x2 = _pad_cols(x2)
     s = torch.as_tensor(scale, dtype=torch.float32, device=x.device).reshape(())
+    if fp8_dtype == torch.float8_e5m2:
+        q, _, _ = ops.quantize_e5m2(x2.contiguous(), scale=s)
+        return q[:, :cols].reshape(shape)
     hist = torch.zeros((1,), dtype=torch.float32, device=x.device)
     q, _, _, _ = ops.quantize_delayed(x2, s, hist)
     return q[:, :cols].reshape(shape)
@@ -109,18 +120,18 @@ def quantize(x: torch.Tensor, fp8_dtype: torch.dtype, scale: torch.Tensor,
 def dequantize(x: torch.Tensor, compute_dtype: torch.dtype, scale: torch.Tensor) -> torch.Tensor:
     """xax/nn/fp8.py:123-138 for a scalar scale: compute_dtype(x) / compute_dtype(scale).  The linear layer
     never materialises the dequantised tensor; this is the free function."""
-    if x.dtype != torch.float8_e4m3fn:
-        _only_e4m3(x.dtype)
+    _fp8_format(x.dtype)
     shape = x.shape
     x2 = x.reshape(-1, shape[-1]) if x.dim() > 1 else x.reshape(1, -1)
     cols = x2.shape[-1]
     pad = (-cols) % 8
     if pad:
-        x2 = torch.nn.functional.pad(x2.view(torch.uint8), (0, pad)).view(torch.float8_e4m3fn)
+        x2 = torch.nn.functional.pad(x2.view(torch.uint8), (0, pad)).view(x.dtype)
     s = torch.as_tensor(scale, dtype=torch.float32, device=x.device).reshape(-1)
     if s.numel() != 1:
         raise ValueError("dequantize: the kernel path takes a scalar scale")
-    return ops.dequantize(x2.contiguous(), s, compute_dtype)[:, :cols].reshape(shape)
+    deq = ops.dequantize_e5m2 if x.dtype == torch.float8_e5m2 else ops.dequantize
+    return deq(x2.contiguous(), s, compute_dtype)[:, :cols].reshape(shape)
 
 
 def quantize_dequantize(x, fp8_dtype, scale, compute_dtype=torch.float32):
@@ -233,9 +244,14 @@ class Fp8Linear:
 def fp8_matmul(a: torch.Tensor, b: torch.Tensor, compute_dtype: torch.dtype = torch.bfloat16,
                fp8_dtype: torch.dtype = torch.float8_e4m3fn) -> torch.Tensor:
     """xax/nn/fp8.py:347-378: a @ b with per-tensor current scaling of both operands."""
-    _only_e4m3(fp8_dtype)
+    _fp8_format(fp8_dtype)
     a2 = a.to(torch.bfloat16).reshape(-1, a.shape[-1]).contiguous()
     bt = b.to(torch.bfloat16).t().contiguous()  # (N, K), K-contiguous
+    if fp8_dtype == torch.float8_e5m2:
+        aq, _, a_inv = ops.quantize_e5m2(a2)
+        bq, _, b_inv = ops.quantize_e5m2(bt)
+        out = ops.gemm_fp8_formats(aq, bq, a_inv, b_inv[:1])
+        return out.reshape(*a.shape[:-1], b.shape[-1])
     aq, _, a_inv, _ = ops.quantize_current(a2, a2.shape[0])
     bq, _, b_inv, _ = ops.quantize_current(bt, bt.shape[0])
     out = ops.gemm_fp8(aq, bq, a_inv, b_inv[:1])

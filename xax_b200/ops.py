@@ -146,6 +146,74 @@ def gemm_fp8(a_q, b_q, row_mul=None, col_mul=None, bias=None, residual=None, out
     return _gemm("xaxb_gemm_fp8", a_q, b_q, row_mul, col_mul, bias, residual, out)
 
 
+E5M2 = torch.float8_e5m2
+
+
+def gemm_fp8_formats(a_q, b_q, row_mul=None, col_mul=None, bias=None, residual=None, out=None):
+    """gemm_fp8 for operands that are float8_e4m3fn or float8_e5m2, in any combination."""
+    for t in (a_q, b_q):
+        if t.dtype not in (E4M3, E5M2):
+            raise ValueError("gemm_fp8_formats needs float8_e4m3fn / float8_e5m2 operands")
+    ctx, st, lib = _c()
+    M, K = a_q.shape
+    N, Kb = b_q.shape
+    if K != Kb:
+        raise ValueError(f"gemm: inner dimensions differ ({K} vs {Kb})")
+    if a_q.stride(1) != 1 or b_q.stride(1) != 1:
+        raise ValueError("gemm: operands must be K-contiguous")
+    if out is None:
+        out = torch.empty((M, N), dtype=BF16, device=a_q.device)
+    row_mul, rs = _mul_arg(row_mul, M, "row_mul")
+    col_mul, cs = _mul_arg(col_mul, N, "col_mul")
+    ldr = residual.stride(0) if residual is not None else 0
+    check(lib.xaxb_gemm_fp8_formats(ctx, st, ptr(a_q), a_q.stride(0), int(a_q.dtype == E5M2), ptr(b_q), b_q.stride(0),
+                                    int(b_q.dtype == E5M2), M, N, K, ptr(row_mul), rs, ptr(col_mul), cs, ptr(bias),
+                                    ptr(residual), ldr, ptr(out), out.stride(0)), "gemm_fp8_formats")
+    return out
+
+
+def quantize_e5m2(x: torch.Tensor, *, scale=None, group_rows: int | None = None):
+    """x bf16 [rows, cols] -> (q float8_e5m2, scale float32 [rows], inv_scale float32 [rows]).  With ``scale`` (one
+    float32 value) every element is multiplied by it; without, groups of ``group_rows`` rows (default: all rows)
+    get the current scale 57344 / max|x| of the group."""
+    x = _req(x, BF16, "x")
+    rows, cols = x.shape
+    ctx, st, lib = _c()
+    q = torch.empty((rows, cols), dtype=E5M2, device=x.device)
+    sc = torch.empty((rows,), dtype=torch.float32, device=x.device)
+    inv = torch.empty((rows,), dtype=torch.float32, device=x.device)
+    if scale is not None:
+        scale = _req(scale, torch.float32, "scale").reshape(-1)
+        if scale.numel() != 1:
+            raise ValueError("quantize_e5m2: scale must hold one value")
+        check(lib.xaxb_quantize_e5m2(ctx, st, ptr(x), rows, cols, rows, ptr(scale), None, ptr(q), ptr(sc), ptr(inv)),
+              "quantize_e5m2")
+    else:
+        g = rows if group_rows is None else int(group_rows)
+        if g <= 0 or rows % g:
+            raise ValueError(f"quantize_e5m2: group_rows {g} must divide rows {rows}")
+        amax = group_amax(x, g)
+        check(lib.xaxb_quantize_e5m2(ctx, st, ptr(x), rows, cols, g, None, ptr(amax), ptr(q), ptr(sc), ptr(inv)),
+              "quantize_e5m2")
+    return q, sc, inv
+
+
+def dequantize_e5m2(q: torch.Tensor, scale: torch.Tensor, out_dtype=BF16) -> torch.Tensor:
+    """dequantize for float8_e5m2 bytes."""
+    q = _req(q, E5M2, "q")
+    scale = _req(scale, torch.float32, "scale").reshape(-1)
+    rows, cols = q.shape
+    if scale.numel() not in (1, rows):
+        raise ValueError(f"dequantize: scale has {scale.numel()} elements, expected 1 or {rows}")
+    if out_dtype not in (BF16, torch.float32):
+        raise ValueError("dequantize: output must be bfloat16 or float32")
+    ctx, st, lib = _c()
+    out = torch.empty((rows, cols), dtype=out_dtype, device=q.device)
+    check(lib.xaxb_dequantize_e5m2(ctx, st, ptr(q), rows, cols, ptr(scale), 0 if scale.numel() == 1 else 1,
+                                   1 if out_dtype == BF16 else 0, ptr(out)), "dequantize_e5m2")
+    return out
+
+
 def lm_head_cross_entropy(hidden, weight, targets, mask=None):
     """Cross-entropy loss and accuracy of hidden bf16 [T, H] against targets int [T] under the head weight bf16
     [V, H], without materialising the [T, V] logits (they are reduced inside the GEMM's epilogue).  ``mask``:
