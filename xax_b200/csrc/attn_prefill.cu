@@ -166,16 +166,37 @@ __global__ void __launch_bounds__(kPfThreads, 2) attn_prefill_kernel(const __gri
         tma_load_4d(sV + s * SM::kKVBytes + x * SM::kKVHalfBytes, &tmap_v, bar_v + s, x * 64, hk, (j_lo + j) * kPfKeys, b);
     };
 
-    // Q rows -> shared memory (K-major, swizzled); rows past T are zero.  (The previous item's MMAs are
-    // complete: its softmax warps waited for the last of them before the barrier that ended the item.)
+    // The previous item's MMAs are complete (its softmax warps waited for the last of them before the barrier
+    // that ended the item), so every shared-memory tile is free: the first K / V tiles are requested before the
+    // query tile is staged, and land while it is.
+    if (warp == 5 && lane == 0) {
+      load_k(0);
+      load_v(0);
+      if (n_tiles > 1) {
+        load_k(1);
+        load_v(1);
+      }
+    }
+    // Q rows -> shared memory (K-major, swizzled); rows past T are zero.  All of a thread's loads are issued
+    // before the first store so that they overlap.
     {
       constexpr int kChunksPerRow = D / 8;
-      for (int i = tid; i < kPfTile * kChunksPerRow; i += kPfThreads) {
+      constexpr int kPerThread = (kPfTile * kChunksPerRow + kPfThreads - 1) / kPfThreads;
+      uint4 qv[kPerThread];
+#pragma unroll
+      for (int u = 0; u < kPerThread; ++u) {
+        const int i = tid + u * kPfThreads;
         const int r = i / kChunksPerRow, c = i % kChunksPerRow;
-        uint4 v = make_uint4(0, 0, 0, 0);
-        if (r < rows_valid)
-          v = __ldg(reinterpret_cast<const uint4*>(p.q + (((long long)b * p.T + q0 + r) * p.Hq + h) * D) + c);
-        *reinterpret_cast<uint4*>(sQ + (c / 8) * SM::kHalfBytes + sw128_offset(r, c % 8)) = v;
+        qv[u] = make_uint4(0, 0, 0, 0);
+        if (i < kPfTile * kChunksPerRow && r < rows_valid)
+          qv[u] = __ldg(reinterpret_cast<const uint4*>(p.q + (((long long)b * p.T + q0 + r) * p.Hq + h) * D) + c);
+      }
+#pragma unroll
+      for (int u = 0; u < kPerThread; ++u) {
+        const int i = tid + u * kPfThreads;
+        const int r = i / kChunksPerRow, c = i % kChunksPerRow;
+        if (i < kPfTile * kChunksPerRow)
+          *reinterpret_cast<uint4*>(sQ + (c / 8) * SM::kHalfBytes + sw128_offset(r, c % 8)) = qv[u];
       }
     }
     fence_proxy_async_smem();
@@ -186,13 +207,7 @@ __global__ void __launch_bounds__(kPfThreads, 2) attn_prefill_kernel(const __gri
 
   if (warp == 5) {
     // ------------------------------------------------------------------ loader (one lane)
-    if (lane == 0) {
-      load_k(0);
-      load_v(0);
-      if (n_tiles > 1) {
-        load_k(1);
-        load_v(1);
-      }
+    if (lane == 0) {  // (tiles 0 and 1 were requested before the query tile was staged)
       for (int j = 0; j < n_tiles && ok; ++j) {
         const int g = gb + j;
         // the V slot of tile j + 1 was last read by P V of tile j - 1
