@@ -75,8 +75,15 @@ struct Gemm2Cfg {
   static_assert(BN_ % 32 == 0 && BN_ >= 128 && BN_ <= 256, "pair tile width");
   static constexpr int kBN = BN_;                       // columns per pair tile
   static constexpr int kBRows = BN_ / 2;                // rows of the B tile each CTA loads
-  static constexpr int kStageBytes = 2 * kBM * kBKBytes;  // per CTA: a 16 KiB slot for A and one for B
-  static constexpr int kLoadBytes = (kBM + kBRows) * kBKBytes;  // what the two loads of a stage deliver
+  // A stage holds 256 bytes of K: two 128-byte swizzle spans ("boxes") per operand, eight MMAs.  What the
+  // MMA thread spends per stage beyond the MMAs themselves (finding the stage's barrier complete, the
+  // commits that free it: about a hundred cycles each, like an MMA) is then paid once per eight MMAs instead
+  // of once per four; with 128-byte stages the thread needed ~650 cycles for four MMAs that keep the tensor
+  // pipe busy for 512, and the pipe idled a fifth of the time.
+  static constexpr int kBoxesPerStage = 2;
+  static constexpr int kSlotBytes = kBoxesPerStage * kBM * kBKBytes;  // per CTA: a 32 KiB slot for A, one for B
+  static constexpr int kStageBytes = 2 * kSlotBytes;
+  static constexpr int kLoadBytes = kBoxesPerStage * (kBM + kBRows) * kBKBytes;  // what the loads of a stage deliver
   static constexpr int kAccStride = 256;                // columns between the two accumulators
   // Two staging blocks for the TMA stores: while the TMA unit reads one, the epilogue warps fill the other.
   // With a single block every 64-column store waited for the previous one's read, and a tile's epilogue
@@ -84,9 +91,9 @@ struct Gemm2Cfg {
   // Five load stages of 32 KiB keep far more in flight than an SM's request capacity needs.
   static constexpr int kOutBlockBytes = kBM * 128;
   static constexpr int kEpiBytes = 2 * kOutBlockBytes + 2 * 256 * 4;
-  static constexpr int kStages = 5;
+  static constexpr int kStages = 3;                     // 192 KiB of operands in flight
   static constexpr int kTmemCols = 512;                 // two 256-column accumulators
-  static constexpr int kSmemBytes = kStages * kStageBytes + kEpiBytes + 1024 + 256;
+  static constexpr int kSmemBytes = kStages * kStageBytes + kEpiBytes + 256;  // (the array is declared 1024-aligned)
 };
 
 template <bool IS_FP8, int BN_>
@@ -101,10 +108,10 @@ gemm_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   constexpr int kBKElems = kBKBytes / kElemBytes;
   constexpr uint32_t kIdesc = umma_idesc(IS_FP8 ? kFmtE4M3 : kFmtBF16, IS_FP8 ? kFmtE4M3 : kFmtBF16, 0, 0, 2 * kBM, BN);
 
-  extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint8_t* smem_a = smem;                              // kStages x 16 KiB
-  uint8_t* smem_b = smem + kStages * kBM * kBKBytes;   // kStages x 16 KiB
+  extern __shared__ __align__(1024) uint8_t smem2[];   // swizzled tiles need 1024-byte alignment
+  uint8_t* smem = smem2;
+  uint8_t* smem_a = smem;                              // kStages x 32 KiB
+  uint8_t* smem_b = smem + kStages * Cfg::kSlotBytes;  // kStages x 32 KiB
   uint8_t* stage_out = smem + kStages * Cfg::kStageBytes;
   float* cmul_s = reinterpret_cast<float*>(stage_out + 2 * Cfg::kOutBlockBytes);
   float* bias_s = cmul_s + 256;
@@ -168,8 +175,12 @@ gemm_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           if (!ok) break;
           const uint32_t leader_full = dsmem_addr(smem_u32(full + stage), 0);
           mbar_arrive_expect_tx_cluster(leader_full, Cfg::kLoadBytes);
-          tma_load_2d_pair(smem_a + stage * kBM * kBKBytes, &tmap_a, leader_full, kk * kBKElems, m0);
-          tma_load_2d_pair(smem_b + stage * kBM * kBKBytes, &tmap_b, leader_full, kk * kBKElems, n0);
+#pragma unroll
+          for (int x = 0; x < Cfg::kBoxesPerStage; ++x) {
+            const int k0 = (kk * Cfg::kBoxesPerStage + x) * kBKElems;  // (past K: zero fill)
+            tma_load_2d_pair(smem_a + stage * Cfg::kSlotBytes + x * kBM * kBKBytes, &tmap_a, leader_full, k0, m0);
+            tma_load_2d_pair(smem_b + stage * Cfg::kSlotBytes + x * Cfg::kBRows * kBKBytes, &tmap_b, leader_full, k0, n0);
+          }
           if (++kk == p.num_k_blocks) kk = 0;
           if (++stage == kStages) stage = 0, phase ^= 1;
         }
@@ -192,11 +203,15 @@ gemm_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           ok = mbar_wait(full + stage, phase, abort_flag, p.d_status, XAXB_DEVICE_TIMEOUT * 1000 + kSite2Mma);
           if (!ok) break;
           tc_fence_after_sync();
-          const uint64_t a_desc = umma_desc_kmajor_sw128(smem_u32(smem_a + stage * kBM * kBKBytes));
-          const uint64_t b_desc = umma_desc_kmajor_sw128(smem_u32(smem_b + stage * kBM * kBKBytes));
 #pragma unroll
-          for (int k = 0; k < kBKBytes / 32; ++k)
-            umma_pair<IS_FP8>(d_tmem, a_desc + 2 * k, b_desc + 2 * k, kIdesc | p.idesc_or, (kb | k) != 0);
+          for (int x = 0; x < Cfg::kBoxesPerStage; ++x) {
+            const uint64_t a_desc = umma_desc_kmajor_sw128(smem_u32(smem_a + stage * Cfg::kSlotBytes + x * kBM * kBKBytes));
+            const uint64_t b_desc =
+                umma_desc_kmajor_sw128(smem_u32(smem_b + stage * Cfg::kSlotBytes + x * Cfg::kBRows * kBKBytes));
+#pragma unroll
+            for (int k = 0; k < kBKBytes / 32; ++k)
+              umma_pair<IS_FP8>(d_tmem, a_desc + 2 * k, b_desc + 2 * k, kIdesc | p.idesc_or, (kb | x | k) != 0);
+          }
           umma_commit_pair(smem_u32(empty + stage));
           umma_commit_pair(dsmem_addr(smem_u32(empty + stage), 1));
           if (++stage == kStages) stage = 0, phase ^= 1;
@@ -371,7 +386,8 @@ static int launch_gemm_2cta_bn(const Ctx* ctx, cudaStream_t stream, const void* 
   p.tiles_m = (p.M + 2 * kBM - 1) / (2 * kBM);
   if (!getenv("XAXB_GEMM_BAND")) p.band = 16;
   p.tiles_n = (p.N + BN - 1) / BN;
-  p.num_k_blocks = (int)(((long long)p.K * kElemBytes + kBKBytes - 1) / kBKBytes);
+  constexpr int kStageKBytes = Cfg::kBoxesPerStage * kBKBytes;
+  p.num_k_blocks = (int)(((long long)p.K * kElemBytes + kStageKBytes - 1) / kStageKBytes);
   if (int rc2 = ensure_dynamic_smem<gemm_2cta_kernel<IS_FP8, BN>>(ctx, Cfg::kSmemBytes, "gemm_2cta_kernel")) return rc2;
   const int tiles = p.tiles_m * p.tiles_n;
   // The kernel is persistent: every pair must be resident at once.
