@@ -183,16 +183,19 @@ def test_tensor_parallel_matches_one_gpu(world):
         res = dict(results)
     for r in range(world):
         assert isinstance(res[r], dict), res[r]
-        # partial sums travel as bf16, so one block differs from the unsharded one by bf16 rounding,
-        # amplified by the two FP8 casts inside the block
-        assert res[r]["err"] < 3e-2, res[r]
-        assert res[r]["same_bytes"] and res[r]["consistent"], res[r]
-        assert res[r]["agree"] >= 0.5, res[r]
+        msg = f"rank {r}: " + ", ".join(f"{k}={v}" for k, v in res[r].items())
+        # Partial sums travel as bf16, so one block differs from the unsharded one by bf16 rounding -- of
+        # `world` partial sums per row-parallel projection -- amplified by the two FP8 casts inside the block:
+        # below 3e-2 at 2 and 4 ranks, 3.8e-2 measured at 8, where two executions of a block by the reference's
+        # own two formulations (quantise-dequantise and FP8 matmul) differ by 4.4e-2.
+        assert res[r]["err"] < (3e-2 if world <= 4 else 5e-2), msg
+        assert res[r]["same_bytes"] and res[r]["consistent"], msg
+        assert res[r]["agree"] >= 0.5, msg
         # peer-memory exchange: exact maximum, rank-ordered float32 sum, and (two ranks: one rounding of
         # a + b either way) the same greedy tokens as the NCCL run, prefill and three replayed steps
         # per-rank-slice scales put the e4m3 grid elsewhere than the unsharded model's: the block output moves
         # by FP8 rounding noise (the reference's own two executions of one block differ by 7e-2)
-        assert res[r]["err_local"] < 6e-2 and res[r]["err_local_decode"] < 6e-2, res[r]
-        assert res[r]["max_ok"] and res[r]["sum_ok"] and res[r]["fused_ok"] and res[r]["push_same"], res[r]
+        assert res[r]["err_local"] < (6e-2 if world <= 4 else 8e-2) and res[r]["err_local_decode"] < 6e-2, msg
+        assert res[r]["max_ok"] and res[r]["sum_ok"] and res[r]["fused_ok"] and res[r]["push_same"], msg
         if world == 2:  # two ranks: a + b rounds the same either way, so NCCL's sum gives the same tokens
-            assert res[r]["peer_same"], res[r]
+            assert res[r]["peer_same"], msg
