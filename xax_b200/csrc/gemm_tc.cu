@@ -656,7 +656,9 @@ gemm_splitk_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
       }
       pdl_wait();
       for (int i = 0; i < nkb; ++i) {
-        if (!mbar_wait(empty + stage, phase ^ 1, abort_flag, p.d_status, XAXB_DEVICE_TIMEOUT * 1000 + kSiteSkProducer))
+        // (the first trip round the ring finds every stage free: no barrier to test)
+        if (i >= kStages &&
+            !mbar_wait(empty + stage, phase ^ 1, abort_flag, p.d_status, XAXB_DEVICE_TIMEOUT * 1000 + kSiteSkProducer))
           break;
         mbar_arrive_expect_tx(full + stage, Cfg::kStageBytes);
         tma_load_2d(smem_a + stage * kBM * kBKBytes, &tmap_a, full + stage, kk * kBKElems, 0);
@@ -683,7 +685,9 @@ gemm_splitk_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
           else
             umma_f16(tmem_base, a_desc + 2 * k, b_desc + 2 * k, kIdesc, (i | k) != 0);
         }
-        umma_commit(empty + stage);
+        // a stage is handed back only if a later K block will use it: a commit costs this thread about as
+        // much as an MMA, and a CTA's share of K is often no longer than the ring
+        if (i + kStages < nkb) umma_commit(empty + stage);
         if (++stage == kStages) stage = 0, phase ^= 1;
       }
       if (ok) umma_commit(acc_full);  // with nkb == 0 this arrives at once: nothing was issued
