@@ -79,6 +79,25 @@ def test_quantize_special_values(ops, ofp8):
     assert np.all((qn[2] & 0x7F) == 0x7F)
 
 
+@pytest.mark.parametrize("scale", [1.0, 0.37, 300.0, 3.0e-3, 1.0e30])
+def test_quantize_delayed_special_values(ops, ofp8, scale):
+    """The delayed-scaling cast (packed bf16 multiply / clip) on zeros, -0, bf16 subnormals, values that clip,
+    infinities and NaN, and on random values of every magnitude: the bytes the oracle gives."""
+    rng = np.random.default_rng(7)
+    x = (rng.standard_normal((32, 256)) * np.exp(rng.uniform(-40, 40, (32, 256)))).astype(np.float32)
+    x[0, :12] = [0.0, -0.0, 1e-40, -1e-39, 3.0, -7.5, np.inf, -np.inf, np.nan, 448.0, -449.0, 1e38]
+    xb = x.astype(bf16)
+    s_in = np.asarray(scale, np.float32)
+    hist = np.zeros(16, np.float32)
+    q, _, _, inv = ops.quantize_delayed(to_torch(xb), to_torch(s_in), to_torch(hist))
+    with np.errstate(invalid="ignore", over="ignore"):
+        exp = ofp8.quantize(xb, e4m3, s_in, bf16).view(np.uint8)
+    got = to_numpy(q).view(np.uint8)
+    nan_exp = (exp & 0x7F) == 0x7F
+    assert np.array_equal(got[~nan_exp], exp[~nan_exp])
+    assert np.all((got[nan_exp] & 0x7F) == 0x7F)  # NaN stays NaN (sign is not pinned)
+
+
 @pytest.mark.parametrize("hist_len", [16, 1024])
 def test_quantize_delayed_matches_oracle(ops, ofp8, hist_len):
     """benchmark config 1's scaling: history pre-filled from seeded draws, quantise with the

@@ -24,7 +24,7 @@ __global__ void __launch_bounds__(256) quantize_rows_kernel(const uint4* __restr
   const float a = bf16_bits_to_float(row_bits);
   const float s = current_scale_from_amax(a);
   uint2* qr = q + row * vec_per_row;
-  for (int64_t i = threadIdx.x; i < vec_per_row; i += blockDim.x) qr[i] = quantize8(__ldg(xr + i), s);
+  for (int64_t i = threadIdx.x; i < vec_per_row; i += blockDim.x) qr[i] = quantize8_packed(__ldg(xr + i), s);
   if (threadIdx.x == 0) {
     scale[row] = s;
     inv_scale[row] = 1.0f / s;
@@ -60,7 +60,7 @@ __global__ void __launch_bounds__(NT) quantize_rows_reg_kernel(const uint4* __re
 #pragma unroll
   for (int k = 0; k < VPT; ++k) {
     const int i = threadIdx.x + k * NT;
-    if (i < vec_per_row) qr[i] = quantize8(v[k], s);
+    if (i < vec_per_row) qr[i] = quantize8_packed(v[k], s);
   }
   if (threadIdx.x == 0) {
     scale[row] = s;
@@ -98,7 +98,7 @@ __global__ void __launch_bounds__(256) group_cast_kernel(const uint4* __restrict
   uint2* qg = q + g * vec_per_group;
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < vec_per_group;
        i += (int64_t)gridDim.x * blockDim.x)
-    qg[i] = quantize8(__ldg(xg + i), s);
+    qg[i] = quantize8_packed(__ldg(xg + i), s);
   if (blockIdx.x == 0) {
     for (int64_t r = threadIdx.x; r < group_rows; r += blockDim.x) {
       scale[g * group_rows + r] = s;
@@ -117,7 +117,7 @@ __device__ __forceinline__ float nan_max(float a, float b) { return (a != a) ? a
 // are zero on entry and the last CTA leaves them zero.  The history is staged in shared memory,
 // so history_in and history_out may alias; scale_out may alias scale_in (every CTA has read it
 // before the last one can finish).
-__global__ void __launch_bounds__(256) delayed_cast_kernel(const uint4* __restrict__ x, int64_t n_vec,
+__global__ void __launch_bounds__(256, 8) delayed_cast_kernel(const uint4* __restrict__ x, int64_t n_vec,
                                                            const float* scale_in, uint2* __restrict__ q,
                                                            unsigned int* scratch, const float* history_in,
                                                            int history_len, float* history_out, float* scale_out,
@@ -146,7 +146,7 @@ __global__ void __launch_bounds__(256) delayed_cast_kernel(const uint4* __restri
     for (int k = 0; k < 4; ++k) {
       const int64_t i = i0 + k * 256;
       m = absmax_bits8(m, v[k]);
-      if (q && i < n_vec) q[i] = quantize8(v[k], s);
+      if (q && i < n_vec) q[i] = quantize8_packed(v[k], s);
     }
   }
   const uint32_t r = block_max_u32(m);

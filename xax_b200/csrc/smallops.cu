@@ -224,11 +224,7 @@ __global__ void __launch_bounds__(256) silu_mul_reg_kernel(const uint4* __restri
 #pragma unroll
   for (int k = 0; k < VPT; ++k) {
     const int i = threadIdx.x + k * 256;
-    if (i < vec) {
-      float f[8];
-      unpack8(hv[k], f);
-      q[row * vec + i] = quantize8f(f, s);
-    }
+    if (i < vec) q[row * vec + i] = quantize8_packed(hv[k], s);
   }
   if (threadIdx.x == 0) {
     scale[row] = s;
