@@ -155,18 +155,24 @@ __device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
 // frequencies.  Every product and every sum is rounded to bf16 as the reference's bf16 ops do.
 __device__ __forceinline__ void rope_rotate_pieces(const uint4 a, const uint4 b, const uint4 c, const uint4 s, uint4& o1,
                                                    uint4& o2) {
-  float x1[8], x2[8], cc[8], ss[8], r1[8], r2[8];
-  unpack8(a, x1);
-  unpack8(b, x2);
-  unpack8(c, cc);
-  unpack8(s, ss);
+  // Packed bf16 arithmetic, two pairs per instruction; the _rn forms are never contracted into a fused
+  // multiply-add.  A bf16 sum of two bf16 values rounds once where float32-then-bf16 rounds twice, but the
+  // first of those two roundings only happens for operands more than 2^16 apart, where the sum is nowhere
+  // near a bf16 tie: the bits are the same.
+  const __nv_bfloat162* aw = reinterpret_cast<const __nv_bfloat162*>(&a);
+  const __nv_bfloat162* bw = reinterpret_cast<const __nv_bfloat162*>(&b);
+  const __nv_bfloat162* cw = reinterpret_cast<const __nv_bfloat162*>(&c);
+  const __nv_bfloat162* sw = reinterpret_cast<const __nv_bfloat162*>(&s);
+  uint4 r1, r2;
+  __nv_bfloat162* w1 = reinterpret_cast<__nv_bfloat162*>(&r1);
+  __nv_bfloat162* w2 = reinterpret_cast<__nv_bfloat162*>(&r2);
 #pragma unroll
-  for (int j = 0; j < 8; ++j) {
-    r1[j] = bf16_round(x1[j] * cc[j]) - bf16_round(x2[j] * ss[j]);
-    r2[j] = bf16_round(x2[j] * cc[j]) + bf16_round(x1[j] * ss[j]);
+  for (int j = 0; j < 4; ++j) {
+    w1[j] = __hsub2_rn(__hmul2_rn(aw[j], cw[j]), __hmul2_rn(bw[j], sw[j]));
+    w2[j] = __hadd2_rn(__hmul2_rn(bw[j], cw[j]), __hmul2_rn(aw[j], sw[j]));
   }
-  o1 = pack8(r1);
-  o2 = pack8(r2);
+  o1 = r1;
+  o2 = r2;
 }
 
 // magnitude bits (bf16, sign cleared) of a float that already holds a bf16 value
